@@ -1,0 +1,809 @@
+// Flash attention forward and backward for sm_100a (tcgen05 + TMEM + TMA), causal or full,
+// MHA/GQA, head dim 64 or 128, operands addressed in place through 5-d tensor maps
+// (head_dim, q-head-in-group, kv-group, batch, sequence) so q/k/v may be views of a fused
+// QKV projection and the gradients are written into a fused buffer of the same layout.
+//
+// Three kernels share one structure - warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 one
+// thread per accumulator row (TMEM lane):
+//   fwd : per 128 query rows, loop over 64-key tiles.  S = Q K^T lands in TMEM, each thread
+//         reads its row, computes exp2 with a lazily updated reference max, writes P (bf16,
+//         128B-swizzled) to shared memory, and O += P V accumulates in TMEM; O is rescaled
+//         in TMEM only when the row max grows by more than 2^8.
+//   dq  : per 128 query rows, loop over 64-key tiles: S and dP = dO V^T in TMEM,
+//         dS = P (dP - delta) scale to shared memory, dQ += dS K accumulates in TMEM.
+//   dkv : per 128 key rows, loop over query heads of the group and 64-query tiles:
+//         S^T = K Q^T and dP^T = V dO^T in TMEM, P^T and dS^T to shared memory,
+//         dV += P^T dO and dK += dS^T Q accumulate in TMEM.
+// The K/V (resp. Q/dO) tiles are stored once in shared memory and read both as K-major and
+// as MN-major operands, which is what removes every transpose.  No atomics: gradients are
+// written once, so results are bitwise reproducible.
+//
+// Replaces the library attention the reference reaches through
+// megatron/core/extensions/transformer_engine.py:705-930 and the unfused path of
+// megatron/core/transformer/dot_product_attention.py:136-205.
+#include "tc05.cuh"
+
+namespace mlb {
+using namespace tc05;
+
+constexpr int kAttnThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnParams {
+  int sq, sk, b, ng, qpg, causal, off;     // off = sk - sq (last query sees last key)
+  float scale, scale_log2;
+  int lp_fmt;
+  int* status;
+  // forward
+  void* o; long o_s, o_b, o_g, o_j;
+  float* lse;                               // [b, ng, qpg, sq] natural log
+  // backward
+  const float* delta;                       // [b, ng, qpg, sq]
+  void* dq; long dq_s, dq_b, dq_g, dq_j;
+  void* dk; long dk_s, dk_b, dk_g;
+  void* dv; long dv_s, dv_b, dv_g;
+};
+
+__device__ __forceinline__ uint32_t pack_lp(float a, float b, int bf) {
+  if (bf) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// write 64 values of one row (as 32 packed words) into a [rows x 64] K-major 128B-swizzled tile
+__device__ __forceinline__ void store_row_sw128(uint8_t* tile, int row, const uint32_t (&w)[32]) {
+  uint8_t* base = tile + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 v = make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
+    *reinterpret_cast<uint4*>(base + ((c ^ (row & 7)) << 4)) = v;
+  }
+}
+// 32 fp32 accumulator values -> low precision -> 64 contiguous bytes in global memory
+__device__ __forceinline__ void store_chunk_global(void* dst, const float (&v)[32], int bf) {
+  uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    d[q] = make_uint4(pack_lp(v[q * 8], v[q * 8 + 1], bf), pack_lp(v[q * 8 + 2], v[q * 8 + 3], bf),
+                      pack_lp(v[q * 8 + 4], v[q * 8 + 5], bf), pack_lp(v[q * 8 + 6], v[q * 8 + 7], bf));
+}
+__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// K-major operand inside a [rows x D] tile stored as D/64 column chunks of [rows x 128 B]
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile, int kk, int chunk_bytes) {
+  return make_desc(tile + (kk >> 2) * chunk_bytes + (kk & 3) * 32, 16, 1024);
+}
+// MN-major operand: same storage, reduction along rows; 16 rows per step, 64-element chunks LBO apart
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile, int kk, int chunk_bytes) {
+  return make_desc(tile + kk * 2048, chunk_bytes, 1024);
+}
+
+// ============================================================================ forward
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  constexpr int BM = 128, BN = 64;
+  constexpr int QB = D * 256, KVB = D * 128, QC = 16384, KC = 8192;    // tile / chunk bytes
+  constexpr uint32_t TCOLS = (64 + D) > 128 ? 256 : 128;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + QB;
+  uint8_t* sV = sK + 2 * KVB;
+  uint8_t* sP = sV + 2 * KVB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 16384);
+  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 s_full | 6 s_empty | 7 p_full | 8 o_done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_qtiles = (p.sq + BM - 1) / BM;
+  const int heads = p.ng * p.qpg;
+  const int qt = n_qtiles - 1 - (int)(blockIdx.x / (heads * p.b));      // heavy (late) tiles first
+  const int hb = blockIdx.x % (heads * p.b);
+  const int bb = hb / heads, hh = hb % heads, g = hh / p.qpg, j = hh % p.qpg;
+  const int s0 = qt * BM;
+  int kv_end = p.sk;
+  if (p.causal) { kv_end = s0 + BM + p.off; if (kv_end > p.sk) kv_end = p.sk; }
+  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
+    mbar_init(B(5), 1); mbar_init(B(6), 4); mbar_init(B(7), 4); mbar_init(B(8), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 64;
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(B(0), QB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) tma_load_5d(smem_u32(sQ) + c * QC, &tmQ, B(0), c * 64, j, g, bb, s0);
+      for (int t = 0; t < n_kv; ++t) {
+        const int st = t & 1;
+        if (!mbar_wait(B(3 + st), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag, p.status, 11)) break;
+        mbar_expect_tx(B(1 + st), 2 * KVB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(1 + st), c * 64, 0, g, bb, t * BN);
+          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(1 + st), c * 64, 0, g, bb, t * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);
+      const uint32_t idesc_o = make_idesc(BM, D, p.lp_fmt, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+      auto issue_s = [&](int t) {
+        const uint32_t kb = aK + (t & 1) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS, kmajor_desc(aQ, kk, QC), kmajor_desc(kb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(5));
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 12) && mbar_wait(B(1), 0, abort_flag, p.status, 13);
+      if (ok) { fence_after_sync(); issue_s(0); }
+      for (int t = 0; t < n_kv && ok; ++t) {
+        if (t + 1 < n_kv) {
+          const int st1 = (t + 1) & 1;
+          if (!mbar_wait(B(1 + st1), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.status, 14)) { ok = false; break; }
+          if (!mbar_wait(B(6), (uint32_t)t & 1u, abort_flag, p.status, 15)) { ok = false; break; }
+          fence_after_sync();
+          issue_s(t + 1);
+        }
+        if (!mbar_wait(B(7), (uint32_t)t & 1u, abort_flag, p.status, 16)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t vb = aV + (t & 1) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16(tO, kmajor_desc(aP, kk, 0), mnmajor_desc(vb, kk, KC), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(3 + (t & 1)));
+        mma_commit(B(8));
+      }
+    }
+  } else if (n_kv > 0) {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int qrow = s0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_kv; ++t) {
+      const int n0 = t * BN;
+      if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 17)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tS + lane_base, r0);
+      tmem_ld32(tS + lane_base + 32, r1);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(6));
+      const bool need_mask = (p.causal && (n0 + BN - 1 > s0 + p.off)) || (n0 + BN > p.sk);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        float a = __uint_as_float(r0[c]) * p.scale_log2, bq = __uint_as_float(r1[c]) * p.scale_log2;
+        if (need_mask) {
+          const int k0 = n0 + c, k1 = n0 + 32 + c;
+          if ((p.causal && k0 > qrow + p.off) || k0 >= p.sk) a = -INFINITY;
+          if ((p.causal && k1 > qrow + p.off) || k1 >= p.sk) bq = -INFINITY;
+        }
+        r0[c] = __float_as_uint(a); r1[c] = __float_as_uint(bq);
+        mx = fmaxf(mx, fmaxf(a, bq));
+      }
+      const float m_new = fmaxf(m_ref, mx);
+      const bool resc = m_new > m_ref + 8.f;
+      float alpha = 1.f;
+      if (resc) { alpha = fast_exp2(m_ref - m_new); m_ref = m_new; l *= alpha; }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      uint32_t pw[32];
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const float a0 = fast_exp2(__uint_as_float(r0[2 * c]) - m_use), a1 = fast_exp2(__uint_as_float(r0[2 * c + 1]) - m_use);
+        const float b0 = fast_exp2(__uint_as_float(r1[2 * c]) - m_use), b1 = fast_exp2(__uint_as_float(r1[2 * c + 1]) - m_use);
+        lsum += (a0 + a1) + (b0 + b1);
+        pw[c] = pack_lp(a0, a1, p.lp_fmt);
+        pw[16 + c] = pack_lp(b0, b1, p.lp_fmt);
+      }
+      l += lsum;
+      if (t > 0) {
+        if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 18)) { ok = false; break; }
+        fence_after_sync();
+        if (__any_sync(0xffffffffu, resc)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tO + lane_base + c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + lane_base + c, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      store_row_sw128(sP, row, pw);
+      fence_async_smem();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(7));
+    }
+    if (ok && mbar_wait(B(8), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 19)) {
+      fence_after_sync();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      2 * ((long)qrow * p.o_s + (long)bb * p.o_b + (long)g * p.o_g + (long)j * p.o_j);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tO + lane_base + c, o);
+        tmem_wait_ld();
+        if (qrow < p.sq) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]) * inv_l;
+          store_chunk_global(orow + c * 2, v, p.lp_fmt);
+        }
+      }
+      if (qrow < p.sq)
+        p.lse[(((long)bb * p.ng + g) * p.qpg + j) * p.sq + qrow] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
+// ============================================================================ delta = rowsum(O * dO)
+__global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, float* __restrict__ delta,
+                                  int sq, int b, int ng, int qpg, int D, long o_s, long o_b, long o_g, long o_j,
+                                  long do_s, long do_b, long do_g, long do_j, int bf) {
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long total = (long)sq * b * ng * qpg;
+  if (row >= total) return;
+  const int lane = threadIdx.x & 31;
+  long r = row;
+  const int s = (int)(r % sq); r /= sq;
+  const int j = (int)(r % qpg); r /= qpg;
+  const int g = (int)(r % ng);
+  const int bb = (int)(r / ng);
+  const uint16_t* op = o + s * o_s + bb * o_b + g * o_g + j * o_j;
+  const uint16_t* dp = d_o + s * do_s + bb * do_b + g * do_g + j * do_j;
+  float acc = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(op + c), bq = *reinterpret_cast<const uint32_t*>(dp + c);
+    if (bf) {
+      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a));
+      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bq));
+      acc += x.x * y.x + x.y * y.y;
+    } else {
+      const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&a));
+      const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&bq));
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[row] = acc;      // index order (b, g, j, s) matches the decomposition above
+}
+
+// ============================================================================ backward: dQ
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const AttnParams p) {
+  constexpr int BM = 128, BN = 64;
+  constexpr int QB = D * 256, KVB = D * 128, QC = 16384, KC = 8192;
+  constexpr uint32_t TCOLS = (128 + D) > 128 ? 256 : 128;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + QB;
+  uint8_t* sK = sdO + QB;
+  uint8_t* sV = sK + 2 * KVB;
+  uint8_t* sdS = sV + 2 * KVB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 16384);
+  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 sdp_full | 6 sdp_empty | 7 ds_full | 8 dq_done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_qtiles = (p.sq + BM - 1) / BM;
+  const int heads = p.ng * p.qpg;
+  const int qt = n_qtiles - 1 - (int)(blockIdx.x / (heads * p.b));
+  const int hb = blockIdx.x % (heads * p.b);
+  const int bb = hb / heads, hh = hb % heads, g = hh / p.qpg, j = hh % p.qpg;
+  const int s0 = qt * BM;
+  int kv_end = p.sk;
+  if (p.causal) { kv_end = s0 + BM + p.off; if (kv_end > p.sk) kv_end = p.sk; }
+  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
+    mbar_init(B(5), 1); mbar_init(B(6), 4); mbar_init(B(7), 4); mbar_init(B(8), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 64, tdQ = tmem + 128;
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(B(0), 2 * QB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_5d(smem_u32(sQ) + c * QC, &tmQ, B(0), c * 64, j, g, bb, s0);
+        tma_load_5d(smem_u32(sdO) + c * QC, &tmdO, B(0), c * 64, j, g, bb, s0);
+      }
+      for (int t = 0; t < n_kv; ++t) {
+        const int st = t & 1;
+        if (!mbar_wait(B(3 + st), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(1 + st), 2 * KVB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(1 + st), c * 64, 0, g, bb, t * BN);
+          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(1 + st), c * 64, 0, g, bb, t * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);       // S, dP: both operands K-major
+      const uint32_t idesc_q = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dQ = dS (K-major) x K (MN-major)
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), adS = smem_u32(sdS);
+      auto issue_sdp = [&](int t) {
+        const uint32_t kb = aK + (t & 1) * KVB, vb = aV + (t & 1) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS, kmajor_desc(aQ, kk, QC), kmajor_desc(kb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP, kmajor_desc(adO, kk, QC), kmajor_desc(vb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(5));
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 22) && mbar_wait(B(1), 0, abort_flag, p.status, 23);
+      if (ok) { fence_after_sync(); issue_sdp(0); }
+      for (int t = 0; t < n_kv && ok; ++t) {
+        if (t + 1 < n_kv) {
+          const int st1 = (t + 1) & 1;
+          if (!mbar_wait(B(1 + st1), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.status, 24)) { ok = false; break; }
+          if (!mbar_wait(B(6), (uint32_t)t & 1u, abort_flag, p.status, 25)) { ok = false; break; }
+          fence_after_sync();
+          issue_sdp(t + 1);
+        }
+        if (!mbar_wait(B(7), (uint32_t)t & 1u, abort_flag, p.status, 26)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t kb = aK + (t & 1) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16(tdQ, kmajor_desc(adS, kk, 0), mnmajor_desc(kb, kk, KC), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(3 + (t & 1)));
+        mma_commit(B(8));
+      }
+    }
+  } else if (n_kv > 0) {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int qrow = s0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const long stat_idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qrow;
+    const float lse2 = qrow < p.sq ? p.lse[stat_idx] * kLog2e : 0.f;
+    const float dlt = qrow < p.sq ? p.delta[stat_idx] : 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_kv; ++t) {
+      const int n0 = t * BN;
+      if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 27)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t w[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_base + half * 32, rs);
+        tmem_ld32(tdP + lane_base + half * 32, rp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kv = n0 + half * 32 + 2 * c + e;
+            const bool masked = (p.causal && kv > qrow + p.off) || kv >= p.sk || qrow >= p.sq;
+            const float pr = masked ? 0.f : fast_exp2(__uint_as_float(rs[2 * c + e]) * p.scale_log2 - lse2);
+            ds[e] = pr * (__uint_as_float(rp[2 * c + e]) - dlt) * p.scale;
+          }
+          w[half * 16 + c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        }
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(6));
+      if (t > 0) {
+        if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 28)) { ok = false; break; }
+      }
+      store_row_sw128(sdS, row, w);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(7));
+    }
+    if (ok && mbar_wait(B(8), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 29)) {
+      fence_after_sync();
+      uint8_t* drow = reinterpret_cast<uint8_t*>(p.dq) +
+                      2 * ((long)qrow * p.dq_s + (long)bb * p.dq_b + (long)g * p.dq_g + (long)j * p.dq_j);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tdQ + lane_base + c, o);
+        tmem_wait_ld();
+        if (qrow < p.sq) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+          store_chunk_global(drow + c * 2, v, p.lp_fmt);
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
+// ============================================================================ backward: dK, dV
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const AttnParams p) {
+  constexpr int BM = 128, BN = 64;                 // BM key rows per CTA, BN query rows per step
+  constexpr int KB = D * 256, QB = D * 128, KC = 16384, QC = 8192;
+  constexpr uint32_t TCOLS = 512;                  // S^T 64 | dP^T 64 | dV D | dK D
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KB;
+  uint8_t* sQ = sV + KB;
+  uint8_t* sdO = sQ + 2 * QB;
+  uint8_t* sP = sdO + 2 * QB;
+  uint8_t* sdS = sP + 16384;
+  float* sStat = reinterpret_cast<float*>(sdS + 16384);       // [2][2][64] lse2 / delta per step parity
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 256);
+  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5 sdp_full | 6 sdp_empty | 7 pds_full | 8 pds_done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_ktiles = (p.sk + BM - 1) / BM;
+  const int kt = blockIdx.x / (p.ng * p.b);                    // early key tiles see the most queries
+  const int gb = blockIdx.x % (p.ng * p.b);
+  const int bb = gb / p.ng, g = gb % p.ng;
+  const int n0 = kt * BM;
+  (void)n_ktiles;
+  // query tiles that can see at least one key of this tile: q + off >= n0
+  int q_begin = 0;
+  if (p.causal) { q_begin = n0 - p.off; if (q_begin < 0) q_begin = 0; }
+  const int qt0 = q_begin / BN;
+  const int n_qt = (p.sq + BN - 1) / BN;
+  const int per_head = n_qt > qt0 ? n_qt - qt0 : 0;
+  const int n_steps = per_head * p.qpg;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
+    mbar_init(B(5), 1); mbar_init(B(6), 4); mbar_init(B(7), 4); mbar_init(B(8), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 64, tdV = tmem + 128, tdK = tmem + 128 + D;
+
+  if (warp == 0) {
+    if (lane == 0 && n_steps > 0) {
+      mbar_expect_tx(B(0), 2 * KB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_5d(smem_u32(sK) + c * KC, &tmK, B(0), c * 64, 0, g, bb, n0);
+        tma_load_5d(smem_u32(sV) + c * KC, &tmV, B(0), c * 64, 0, g, bb, n0);
+      }
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t & 1;
+        const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+        if (!mbar_wait(B(3 + st), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
+        mbar_expect_tx(B(1 + st), 2 * QB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_5d(smem_u32(sQ) + st * QB + c * QC, &tmQ, B(1 + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sdO) + st * QB + c * QC, &tmdO, B(1 + st), c * 64, j, g, bb, q0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_steps > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);       // S^T, dP^T
+      const uint32_t idesc_g = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dV, dK: A K-major, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      const uint32_t aP = smem_u32(sP), adS = smem_u32(sdS);
+      auto issue_sdp = [&](int t) {
+        const uint32_t qb = aQ + (t & 1) * QB, ob = adO + (t & 1) * QB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS, kmajor_desc(aK, kk, KC), kmajor_desc(qb, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP, kmajor_desc(aV, kk, KC), kmajor_desc(ob, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(5));
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 32) && mbar_wait(B(1), 0, abort_flag, p.status, 33);
+      if (ok) { fence_after_sync(); issue_sdp(0); }
+      for (int t = 0; t < n_steps && ok; ++t) {
+        if (t + 1 < n_steps) {
+          const int st1 = (t + 1) & 1;
+          if (!mbar_wait(B(1 + st1), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
+          if (!mbar_wait(B(6), (uint32_t)t & 1u, abort_flag, p.status, 35)) { ok = false; break; }
+          fence_after_sync();
+          issue_sdp(t + 1);
+        }
+        if (!mbar_wait(B(7), (uint32_t)t & 1u, abort_flag, p.status, 36)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t qb = aQ + (t & 1) * QB, ob = adO + (t & 1) * QB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16(tdV, kmajor_desc(aP, kk, 0), mnmajor_desc(ob, kk, QC), idesc_g, (t > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16(tdK, kmajor_desc(adS, kk, 0), mnmajor_desc(qb, kk, QC), idesc_g, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(3 + (t & 1)));
+        mma_commit(B(8));
+      }
+    }
+  } else if (n_steps > 0) {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int ct = threadIdx.x - 64;                 // 0..127 among the compute threads
+    const int krow = n0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    bool ok = true;
+    for (int t = 0; t < n_steps; ++t) {
+      const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+      // stage this step's per-query statistics (64 lse2 + 64 delta) in shared memory
+      {
+        float* dst = sStat + (t & 1) * 128;
+        const int qi = q0 + (ct & 63);
+        const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
+        float v = 0.f;
+        if (qi < p.sq) v = (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
+        dst[ct] = v;
+        bar_sync_compute();
+      }
+      const float* stat = sStat + (t & 1) * 128;
+      if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 37)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t wp[32], wd[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(tS + lane_base + half * 32, rs);
+        tmem_ld32(tdP + lane_base + half * 32, rp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = half * 32 + 2 * c + e;
+            const int qi = q0 + col;
+            const bool masked = (p.causal && krow > qi + p.off) || qi >= p.sq || krow >= p.sk;
+            pr[e] = masked ? 0.f : fast_exp2(__uint_as_float(rs[2 * c + e]) * p.scale_log2 - stat[col]);
+            ds[e] = pr[e] * (__uint_as_float(rp[2 * c + e]) - stat[64 + col]) * p.scale;
+          }
+          wp[half * 16 + c] = pack_lp(pr[0], pr[1], p.lp_fmt);
+          wd[half * 16 + c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        }
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(6));
+      if (t > 0) {
+        if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
+      }
+      store_row_sw128(sP, row, wp);
+      store_row_sw128(sdS, row, wd);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(7));
+    }
+    if (ok && mbar_wait(B(8), (uint32_t)(n_steps - 1) & 1u, abort_flag, p.status, 39)) {
+      fence_after_sync();
+      uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
+      uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        float v[32];
+        tmem_ld32(tdV + lane_base + c, o);
+        tmem_wait_ld();
+        if (krow < p.sk) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+          store_chunk_global(vrow + c * 2, v, p.lp_fmt);
+        }
+        tmem_ld32(tdK + lane_base + c, o);
+        tmem_wait_ld();
+        if (krow < p.sk) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+          store_chunk_global(krow_p + c * 2, v, p.lp_fmt);
+        }
+      }
+    }
+  } else {
+    // no query can see this key tile: its gradients are zero
+    const int ct = threadIdx.x - 64;
+    if (ct >= 0) {
+      const int krow = n0 + ct;
+      if (krow < p.sk) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* vrow = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g));
+        uint4* kr = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g));
+        for (int c = 0; c < D / 8; ++c) { vrow[c] = z; kr[c] = z; }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
+// ---------------------------------------------------------------------------- host side
+static int make_tmap5(CUtensorMap* m, const void* base, int D, int nj, int ng, int b, int s, long st_j, long st_g,
+                      long st_b, long st_s, int box_rows) {
+  uint64_t dims[5] = {(uint64_t)D, (uint64_t)nj, (uint64_t)ng, (uint64_t)b, (uint64_t)s};
+  uint64_t strides[4] = {(uint64_t)st_j * 2, (uint64_t)st_g * 2, (uint64_t)st_b * 2, (uint64_t)st_s * 2};
+  uint32_t box[5] = {64, 1, 1, 1, (uint32_t)box_rows};
+  for (int i = 0; i < 4; ++i) if (strides[i] % 16) return -3;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return -3;
+  return make_tmap(m, base, 5, dims, strides, box);
+}
+
+template <typename K> static int set_smem(K kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
+}  // namespace mlb
+
+using namespace mlb;
+
+// strides are in elements; head dim contiguous; D in {64, 128}
+MLB_API int mlb_attn_fwd(int lp_fmt, const void* q, const void* k, const void* v, void* o, float* lse,
+                         int sq, int sk, int b, int ng, int qpg, int D,
+                         long q_s, long q_b, long q_g, long q_j, long k_s, long k_b, long k_g,
+                         long v_s, long v_b, long v_g, long o_s, long o_b, long o_g, long o_j,
+                         float scale, int causal, int* status, cudaStream_t st) {
+  if (D != 64 && D != 128) return -5;
+  if (sq <= 0 || sk <= 0 || sk < sq) return -6;
+  if ((o_s % 8) || (o_b % 8) || (o_g % 8) || (o_j % 8) || (reinterpret_cast<uintptr_t>(o) & 15)) return -3;
+  CUtensorMap tmQ, tmK, tmV;
+  int rc;
+  if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
+  if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
+  if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
+  AttnParams p = {};
+  p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
+  p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
+  p.o = o; p.o_s = o_s; p.o_b = o_b; p.o_g = o_g; p.o_j = o_j; p.lse = lse;
+  const int grid = ((sq + 127) / 128) * ng * qpg * b;
+  const int smem = D * 256 + 4 * D * 128 + 16384 + 128;
+  if (D == 128) {
+    static bool set = false;
+    if (!set) { if ((rc = set_smem(attn_fwd_kernel<128>, smem))) return rc; set = true; }
+    attn_fwd_kernel<128><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, p);
+  } else {
+    static bool set = false;
+    if (!set) { if ((rc = set_smem(attn_fwd_kernel<64>, smem))) return rc; set = true; }
+    attn_fwd_kernel<64><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, p);
+  }
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+
+MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                         const float* lse, float* delta, void* dq, void* dk, void* dv,
+                         int sq, int sk, int b, int ng, int qpg, int D,
+                         long q_s, long q_b, long q_g, long q_j, long k_s, long k_b, long k_g,
+                         long v_s, long v_b, long v_g, long o_s, long o_b, long o_g, long o_j,
+                         long do_s, long do_b, long do_g, long do_j, long dq_s, long dq_b, long dq_g, long dq_j,
+                         long dk_s, long dk_b, long dk_g, long dv_s, long dv_b, long dv_g,
+                         float scale, int causal, int* status, cudaStream_t st) {
+  if (D != 64 && D != 128) return -5;
+  if (sq <= 0 || sk <= 0 || sk < sq) return -6;
+  const long chk[] = {dq_s, dq_b, dq_g, dq_j, dk_s, dk_b, dk_g, dv_s, dv_b, dv_g};
+  for (long x : chk) if (x % 8) return -3;
+  if ((reinterpret_cast<uintptr_t>(dq) & 15) || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15)) return -3;
+  {
+    const long rows = (long)sq * b * ng * qpg;
+    attn_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>((const uint16_t*)o, (const uint16_t*)d_o, delta, sq, b, ng,
+                                                                 qpg, D, o_s, o_b, o_g, o_j, do_s, do_b, do_g, do_j, lp_fmt);
+    MLB_CHECK_LAUNCH();
+  }
+  AttnParams p = {};
+  p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
+  p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
+  p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.dq = dq; p.dq_s = dq_s; p.dq_b = dq_b; p.dq_g = dq_g; p.dq_j = dq_j;
+  p.dk = dk; p.dk_s = dk_s; p.dk_b = dk_b; p.dk_g = dk_g;
+  p.dv = dv; p.dv_s = dv_s; p.dv_b = dv_b; p.dv_g = dv_g;
+  int rc;
+  {  // dQ: 128-row query tiles, 64-row key tiles
+    CUtensorMap tmQ, tmK, tmV, tmdO;
+    if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
+    if ((rc = make_tmap5(&tmdO, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 128))) return rc;
+    if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
+    if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
+    const int grid = ((sq + 127) / 128) * ng * qpg * b;
+    const int smem = 2 * D * 256 + 4 * D * 128 + 16384 + 128;
+    if (D == 128) {
+      static bool set = false;
+      if (!set) { if ((rc = set_smem(attn_bwd_dq_kernel<128>, smem))) return rc; set = true; }
+      attn_bwd_dq_kernel<128><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+    } else {
+      static bool set = false;
+      if (!set) { if ((rc = set_smem(attn_bwd_dq_kernel<64>, smem))) return rc; set = true; }
+      attn_bwd_dq_kernel<64><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+    }
+    MLB_CHECK_LAUNCH();
+  }
+  {  // dK, dV: 128-row key tiles, 64-row query tiles
+    CUtensorMap tmQ, tmK, tmV, tmdO;
+    if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 64))) return rc;
+    if ((rc = make_tmap5(&tmdO, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 64))) return rc;
+    if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
+    if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
+    const int grid = ((sk + 127) / 128) * ng * b;
+    const int smem = 2 * D * 256 + 4 * D * 128 + 2 * 16384 + 1024 + 128;
+    if (D == 128) {
+      static bool set = false;
+      if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, smem))) return rc; set = true; }
+      attn_bwd_dkv_kernel<128><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+    } else {
+      static bool set = false;
+      if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<64>, smem))) return rc; set = true; }
+      attn_bwd_dkv_kernel<64><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+    }
+    MLB_CHECK_LAUNCH();
+  }
+  return 0;
+}

@@ -1,0 +1,380 @@
+"""Transformer building blocks: norm, self/cross attention, MLP, layer, block.
+
+Behavioural parity targets in the reference: ``TransformerLayer``
+(megatron/core/transformer/transformer_layer.py:256, forward :432-700),
+``TransformerBlock`` (transformer_block.py:258, forward :477-620), ``SelfAttention``
+(attention.py:784; fused QKV layout [ng, (np/ng + 2) * hn] :919-965), ``MLP``
+(mlp.py:48, forward :127).  There is no spec tree or backend switch: each module
+is built directly from the config and calls the sm_100a ops of ``ops/``.
+Activations are [s, b, h] throughout.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..config import TransformerConfig
+from ..ops import core as ops
+from ..ops.attention import attention, fused_qkv_attention
+from ..parallel import state
+from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, _device
+from ..parallel.random import CheckpointWithoutOutput, checkpoint, get_cuda_rng_tracker
+
+
+# --------------------------------------------------------------------------- layer placement
+def get_num_layers_to_build(config: TransformerConfig, vp_stage: Optional[int] = None,
+                            pp_rank: Optional[int] = None) -> int:
+    """Layers held by this (pipeline rank, virtual stage) (reference: transformer_block.py:68)."""
+    pp = config.pipeline_model_parallel_size
+    if pp_rank is None:
+        pp_rank = state.get_pipeline_model_parallel_rank() if state.model_parallel_is_initialized() else 0
+    if config.pipeline_model_parallel_layout is not None:
+        from .pp_layout import PipelineParallelLayerLayout
+        layout = PipelineParallelLayerLayout.from_config(config)
+        return layout.get_num_layers_to_build(pp_rank, vp_stage)
+    first, last = config.num_layers_in_first_pipeline_stage, config.num_layers_in_last_pipeline_stage
+    if first is not None or last is not None:
+        middle_ranks = pp - (first is not None) - (last is not None)
+        rest = config.num_layers - (first or 0) - (last or 0)
+        per_mid = rest // middle_ranks if middle_ranks > 0 else 0
+        if pp_rank == 0 and first is not None:
+            n = first
+        elif pp_rank == pp - 1 and last is not None:
+            n = last
+        else:
+            n = per_mid
+    else:
+        total = config.num_layers
+        if config.account_for_embedding_in_pipeline_split:
+            total += 1
+        if config.account_for_loss_in_pipeline_split:
+            total += 1
+        n = total // pp
+        if config.account_for_embedding_in_pipeline_split and pp_rank == 0:
+            n -= 1
+        if config.account_for_loss_in_pipeline_split and pp_rank == pp - 1:
+            n -= 1
+    vpp = config.virtual_pipeline_model_parallel_size
+    if vpp is not None and vpp > 1:
+        n //= vpp
+    return n
+
+
+def get_transformer_layer_offset(config: TransformerConfig, vp_stage: Optional[int] = None,
+                                 pp_rank: Optional[int] = None) -> int:
+    """Global index of this chunk's first layer (reference: transformer_layer.py:37-193).
+    With v virtual stages, chunk c of rank r holds layers starting at
+    c * (num_layers / v) + r * (num_layers / (pp * v))."""
+    pp = config.pipeline_model_parallel_size
+    if pp_rank is None:
+        pp_rank = state.get_pipeline_model_parallel_rank() if state.model_parallel_is_initialized() else 0
+    if pp == 1:
+        return 0
+    if config.pipeline_model_parallel_layout is not None:
+        from .pp_layout import PipelineParallelLayerLayout
+        return PipelineParallelLayerLayout.from_config(config).get_layer_offset(pp_rank, vp_stage)
+    vpp = config.virtual_pipeline_model_parallel_size or 1
+    v = vp_stage or 0
+    first, last = config.num_layers_in_first_pipeline_stage, config.num_layers_in_last_pipeline_stage
+    if first is not None or last is not None:
+        middle_ranks = pp - (first is not None) - (last is not None)
+        rest = config.num_layers - (first or 0) - (last or 0)
+        per_mid = rest // middle_ranks if middle_ranks > 0 else 0
+        sizes = [(first if (r == 0 and first is not None) else last if (r == pp - 1 and last is not None) else per_mid)
+                 for r in range(pp)]
+        per_chunk = [s // vpp for s in sizes]
+        return v * sum(per_chunk) + sum(per_chunk[:pp_rank])
+    total = config.num_layers + int(config.account_for_embedding_in_pipeline_split) + \
+        int(config.account_for_loss_in_pipeline_split)
+    per_rank = total // pp
+    per_chunk = per_rank // vpp
+    off = v * (total // vpp) + pp_rank * per_chunk
+    if config.account_for_embedding_in_pipeline_split and not (pp_rank == 0 and v == 0):
+        off -= 1
+    return off
+
+
+# --------------------------------------------------------------------------- norm
+class Norm(nn.Module):
+    """LayerNorm or RMSNorm over the last dim with the fused fwd/bwd kernels."""
+
+    def __init__(self, config: TransformerConfig, hidden_size: int, eps: Optional[float] = None):
+        super().__init__()
+        self.rms = config.normalization == "RMSNorm"
+        if config.normalization not in ("LayerNorm", "RMSNorm"):
+            raise ValueError(f"unknown normalization {config.normalization}")
+        self.eps = config.layernorm_epsilon if eps is None else eps
+        self.zero_centered = config.layernorm_zero_centered_gamma
+        dev = _device(config)
+        init = torch.zeros if self.zero_centered else torch.ones
+        self.weight = nn.Parameter(init(hidden_size, device=dev, dtype=config.params_dtype))
+        if not self.rms:
+            self.bias = nn.Parameter(torch.zeros(hidden_size, device=dev, dtype=config.params_dtype))
+        else:
+            self.register_parameter("bias", None)
+        # gradients of these replicated parameters are partial sums under sequence parallelism
+        for p in self.parameters():
+            p.sequence_parallel = config.sequence_parallel
+
+    def forward(self, x):
+        if self.rms:
+            return ops.rmsnorm(x, self.weight, self.eps, self.zero_centered)
+        return ops.layernorm(x, self.weight, self.bias, self.eps, self.zero_centered)
+
+
+# --------------------------------------------------------------------------- attention
+class SelfAttention(nn.Module):
+    def __init__(self, config: TransformerConfig, layer_number: int, causal: bool = True):
+        super().__init__()
+        self.config, self.layer_number, self.causal = config, layer_number, causal
+        tp = state.get_tensor_model_parallel_world_size() if state.model_parallel_is_initialized() else 1
+        self.hn = config.kv_channels
+        self.np, self.ng = config.num_attention_heads, config.num_query_groups
+        if self.ng % tp != 0:
+            raise ValueError("num_query_groups must be divisible by the tensor-parallel size")
+        self.np_local, self.ng_local = self.np // tp, self.ng // tp
+        self.qpg = self.np // self.ng
+        qkv_out = (self.np + 2 * self.ng) * self.hn
+        self.linear_qkv = ColumnParallelLinear(config.hidden_size, qkv_out, config=config,
+                                               init_method=config.init_method,
+                                               bias=config.add_bias_linear or config.add_qkv_bias)
+        self.linear_proj = RowParallelLinear(self.np * self.hn, config.hidden_size, config=config,
+                                             init_method=config.output_layer_init_method,
+                                             bias=config.add_bias_linear, skip_bias_add=True)
+        if config.qk_layernorm:
+            self.q_layernorm = Norm(config, self.hn)
+            self.k_layernorm = Norm(config, self.hn)
+        else:
+            self.q_layernorm = self.k_layernorm = None
+        scale = config.softmax_scale if config.softmax_scale is not None else 1.0 / math.sqrt(self.hn)
+        self.softmax_scale = scale
+        self.recompute_core = config.recompute_granularity == "selective" and "core_attn" in config.recompute_modules
+
+    def _core(self, qkv5):
+        return fused_qkv_attention(qkv5, causal=self.causal, scale=self.softmax_scale)
+
+    def forward(self, hidden_states, rotary=None, inference_context=None, attention_mask=None):
+        qkv, _ = self.linear_qkv(hidden_states)                       # [s, b, (np+2ng)/tp * hn]
+        s, b = qkv.shape[0], qkv.shape[1]
+        qkv5 = qkv.view(s, b, self.ng_local, self.qpg + 2, self.hn)
+        if self.q_layernorm is not None:
+            q = self.q_layernorm(qkv5[:, :, :, :self.qpg].contiguous())
+            k = self.k_layernorm(qkv5[:, :, :, self.qpg:self.qpg + 1].contiguous())
+            qkv5 = torch.cat((q, k, qkv5[:, :, :, self.qpg + 1:]), dim=3)
+        if rotary is not None:
+            cos, sin = rotary
+            qkv5 = ops.apply_rope_qkv_(qkv5, cos, sin, self.config.rotary_interleaved)
+        if inference_context is not None:
+            ctx_out = inference_context.attend(self.layer_number, qkv5, self.softmax_scale)
+        elif self.recompute_core and self.training:
+            ctx_out = checkpoint(self._core, False, qkv5)
+        else:
+            ctx_out = self._core(qkv5)                                # [s, b, np_local * hn]
+        out, bias = self.linear_proj(ctx_out)
+        return out, bias
+
+
+class CrossAttention(nn.Module):
+    """Queries from the decoder stream, keys/values from an encoder output
+    (reference: attention.py:981)."""
+
+    def __init__(self, config: TransformerConfig, layer_number: int):
+        super().__init__()
+        self.config = config
+        tp = state.get_tensor_model_parallel_world_size() if state.model_parallel_is_initialized() else 1
+        self.hn, self.np = config.kv_channels, config.num_attention_heads
+        self.np_local = self.np // tp
+        self.linear_q = ColumnParallelLinear(config.hidden_size, self.np * self.hn, config=config,
+                                             init_method=config.init_method, bias=config.add_bias_linear)
+        self.linear_kv = ColumnParallelLinear(config.hidden_size, 2 * self.np * self.hn, config=config,
+                                              init_method=config.init_method, bias=config.add_bias_linear)
+        self.linear_proj = RowParallelLinear(self.np * self.hn, config.hidden_size, config=config,
+                                             init_method=config.output_layer_init_method,
+                                             bias=config.add_bias_linear, skip_bias_add=True)
+
+    def forward(self, hidden_states, key_value_states):
+        q, _ = self.linear_q(hidden_states)
+        kv, _ = self.linear_kv(key_value_states)
+        sq, b = q.shape[0], q.shape[1]
+        sk = kv.shape[0]
+        q5 = q.view(sq, b, self.np_local, 1, self.hn)
+        kv5 = kv.view(sk, b, self.np_local, 2, self.hn)
+        o = attention(q5, kv5[:, :, :, 0], kv5[:, :, :, 1], causal=False)
+        return self.linear_proj(o.reshape(sq, b, self.np_local * self.hn))
+
+
+# --------------------------------------------------------------------------- MLP
+class MLP(nn.Module):
+    def __init__(self, config: TransformerConfig, ffn_hidden_size: Optional[int] = None, is_expert: bool = False):
+        super().__init__()
+        self.config = config
+        ffn = ffn_hidden_size or config.ffn_hidden_size
+        self.gated = config.gated_linear_unit
+        act = config.activation_func if isinstance(config.activation_func, str) else getattr(
+            config.activation_func, "__name__", "gelu")
+        self.act = {"silu": "silu", "swiglu": "silu", "gelu": "gelu", "relu": "relu",
+                    "squared_relu": "squared_relu"}.get(act, act)
+        self.linear_fc1 = ColumnParallelLinear(config.hidden_size, ffn * (2 if self.gated else 1), config=config,
+                                               init_method=config.init_method, bias=config.add_bias_linear,
+                                               skip_bias_add=True, is_expert=is_expert,
+                                               stride=2 if self.gated else 1)
+        self.linear_fc2 = RowParallelLinear(ffn, config.hidden_size, config=config,
+                                            init_method=config.output_layer_init_method,
+                                            bias=config.add_bias_linear, skip_bias_add=True, is_expert=is_expert)
+
+    def activation(self, x, bias):
+        if self.gated:
+            if bias is not None:
+                x = x + bias
+            if self.act == "silu":
+                return ops.swiglu(x)
+            a, b = x.chunk(2, dim=-1)
+            f = torch.nn.functional.gelu if self.act == "gelu" else torch.relu
+            return f(a) * b
+        if self.act == "gelu":
+            return ops.bias_gelu(x, bias)
+        if bias is not None:
+            x = x + bias
+        if self.act == "relu":
+            return torch.relu(x)
+        if self.act == "squared_relu":
+            return torch.relu(x).pow(2)
+        if self.act == "silu":
+            return torch.nn.functional.silu(x)
+        raise ValueError(f"unsupported activation {self.act}")
+
+    def forward(self, hidden_states):
+        h, b1 = self.linear_fc1(hidden_states)
+        h = self.activation(h, b1)
+        return self.linear_fc2(h)
+
+
+# --------------------------------------------------------------------------- layer / block
+class TransformerLayer(nn.Module):
+    """Pre-norm residual block: x + drop(attn(norm(x)) + b); x + drop(mlp(norm(x)) + b)."""
+
+    def __init__(self, config: TransformerConfig, layer_number: int, is_moe: bool = False, causal: bool = True,
+                 cross_attention: bool = False):
+        super().__init__()
+        self.config, self.layer_number = config, layer_number
+        self.input_layernorm = Norm(config, config.hidden_size)
+        self.self_attention = SelfAttention(config, layer_number, causal=causal)
+        if cross_attention:
+            self.pre_cross_attn_layernorm = Norm(config, config.hidden_size)
+            self.cross_attention = CrossAttention(config, layer_number)
+        else:
+            self.cross_attention = None
+        self.pre_mlp_layernorm = Norm(config, config.hidden_size)
+        if is_moe:
+            from .moe import MoELayer
+            self.mlp = MoELayer(config, layer_number)
+        else:
+            self.mlp = MLP(config)
+        self.is_moe = is_moe
+        self.hidden_dropout = config.hidden_dropout
+        mods = config.recompute_modules if config.recompute_granularity == "selective" else []
+        self.recompute_input_ln = "layernorm" in mods
+        self.recompute_mlp = "mlp" in mods
+
+    def _bda(self, x, bias, residual):
+        p = self.hidden_dropout
+        if p > 0.0 and self.training and self.config.sequence_parallel:
+            with get_cuda_rng_tracker().fork():
+                seed = int(torch.randint(0, 2 ** 31 - 1, (1,)).item()) if not x.is_cuda else None
+                return ops.bias_dropout_add(x, bias, residual, p, True, seed)
+        return ops.bias_dropout_add(x, bias, residual, p, self.training)
+
+    def forward(self, hidden_states, rotary=None, inference_context=None, encoder_output=None,
+                attention_mask=None):
+        residual = hidden_states
+        if self.recompute_input_ln and self.training:
+            ck = CheckpointWithoutOutput()
+            ln = ck.checkpoint(self.input_layernorm, hidden_states)
+        else:
+            ck, ln = None, self.input_layernorm(hidden_states)
+        attn_out, attn_bias = self.self_attention(ln, rotary=rotary, inference_context=inference_context,
+                                                  attention_mask=attention_mask)
+        if ck is not None:
+            ck.discard_output_and_register_recompute(attn_out)
+        hidden_states = self._bda(attn_out, attn_bias, residual)
+        if self.cross_attention is not None:
+            residual = hidden_states
+            ln = self.pre_cross_attn_layernorm(hidden_states)
+            x_out, x_bias = self.cross_attention(ln, encoder_output)
+            hidden_states = self._bda(x_out, x_bias, residual)
+        residual = hidden_states
+        if self.recompute_input_ln and self.training and not self.is_moe:
+            ck = CheckpointWithoutOutput()
+            ln = ck.checkpoint(self.pre_mlp_layernorm, hidden_states)
+        else:
+            ck, ln = None, self.pre_mlp_layernorm(hidden_states)
+        if self.recompute_mlp and self.training:
+            mlp_out, mlp_bias = checkpoint(self.mlp, False, ln)
+        else:
+            mlp_out, mlp_bias = self.mlp(ln)
+        if ck is not None:
+            ck.discard_output_and_register_recompute(mlp_out)
+        return self._bda(mlp_out, mlp_bias, residual)
+
+
+class TransformerBlock(nn.Module):
+    """The layers of one pipeline (virtual) stage, plus the final norm on the last stage."""
+
+    def __init__(self, config: TransformerConfig, pre_process: bool = True, post_process: bool = True,
+                 vp_stage: Optional[int] = None, causal: bool = True, cross_attention: bool = False,
+                 post_layer_norm: bool = True):
+        super().__init__()
+        self.config, self.pre_process, self.post_process, self.vp_stage = config, pre_process, post_process, vp_stage
+        n = get_num_layers_to_build(config, vp_stage)
+        self.layer_offset = get_transformer_layer_offset(config, vp_stage)
+        pattern = config.moe_layer_pattern()
+        self.layers = nn.ModuleList([
+            TransformerLayer(config, self.layer_offset + i + 1, is_moe=bool(pattern[self.layer_offset + i]),
+                             causal=causal, cross_attention=cross_attention)
+            for i in range(n)])
+        self.final_layernorm = Norm(config, config.hidden_size) if (post_process and post_layer_norm) else None
+        self.input_tensor = None
+
+    def set_input_tensor(self, t):
+        """Activations received from the previous pipeline stage replace the forward input."""
+        self.input_tensor = t
+
+    def _run_layers(self, start, end):
+        def fn(h, cos, sin):
+            rotary = None if cos is None else (cos, sin)
+            for i in range(start, end):
+                h = self.layers[i](h, rotary=rotary)
+            return h
+        return fn
+
+    def forward(self, hidden_states, rotary=None, inference_context=None, encoder_output=None,
+                attention_mask=None):
+        if not self.pre_process and self.input_tensor is not None:
+            hidden_states = self.input_tensor
+        cfg = self.config
+        full = cfg.recompute_granularity == "full" and self.training
+        cos, sin = (None, None) if rotary is None else rotary
+        if full:
+            n = len(self.layers)
+            if cfg.recompute_method == "uniform":
+                step = cfg.recompute_num_layers
+                i = 0
+                while i < n:
+                    hidden_states = checkpoint(self._run_layers(i, min(i + step, n)), False, hidden_states, cos, sin)
+                    i += step
+            else:   # block: recompute only the first recompute_num_layers layers
+                for i in range(n):
+                    if i < cfg.recompute_num_layers:
+                        hidden_states = checkpoint(self._run_layers(i, i + 1), False, hidden_states, cos, sin)
+                    else:
+                        hidden_states = self.layers[i](hidden_states, rotary=rotary)
+        else:
+            for layer in self.layers:
+                hidden_states = layer(hidden_states, rotary=rotary, inference_context=inference_context,
+                                      encoder_output=encoder_output, attention_mask=attention_mask)
+        if self.final_layernorm is not None:
+            hidden_states = self.final_layernorm(hidden_states)
+        return hidden_states

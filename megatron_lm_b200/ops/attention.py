@@ -1,0 +1,156 @@
+"""Flash attention over strided q/k/v views (no split or transpose copies).
+
+Tensors are in the reference's [s, b, heads, head_dim] convention
+(megatron/core/transformer/attention.py:537-781).  ``q`` has ``ng * qpg`` heads
+organised as ``ng`` KV groups of ``qpg`` query heads; ``k``/``v`` have ``ng``
+heads.  Any strides are allowed on the s, b and head dims as long as head_dim is
+contiguous, so the three tensors may be views of one fused QKV projection
+output [s, b, ng, qpg + 2, hn] - the TMA descriptors address them in place, and
+the backward writes dq/dk/dv into one fused gradient buffer of the same layout.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_lib.register_signatures({
+    # fmt, q,k,v,o,lse, sq,sk,b,ng,qpg,hn, q strides(s,b,g,j) k(s,b,g) v(s,b,g) o(s,b,g,j), scale, causal, status, stream
+    "mlb_attn_fwd": "ippppp" "iiiiii" "llll" "lll" "lll" "llll" "fi" "pp",
+    # fmt, q,k,v,o,do,lse,delta, dq,dk,dv, sizes, strides q,k,v,o,do(s,b,g,j), dq(s,b,g,j), dk, dv, scale, causal, status, stream
+    "mlb_attn_bwd": "ipppppppppp" "iiiiii" "llll" "lll" "lll" "llll" "llll" "llll" "lll" "lll" "fi" "pp",
+})
+
+
+def _ref_attention(q, k, v, causal: bool, scale: float, q_offset: int = 0):
+    # q [sq, b, ng, qpg, d]; k, v [sk, b, ng, d]
+    sq, b, ng, qpg, d = q.shape
+    sk = k.shape[0]
+    qf = q.float().permute(1, 2, 3, 0, 4)                      # b ng qpg sq d
+    kf = k.float().permute(1, 2, 0, 3).unsqueeze(2)            # b ng 1 sk d
+    vf = v.float().permute(1, 2, 0, 3).unsqueeze(2)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale         # b ng qpg sq sk
+    if causal:
+        i = torch.arange(sq, device=q.device).unsqueeze(1) + q_offset + (sk - sq if q_offset == 0 else 0)
+        j = torch.arange(sk, device=q.device).unsqueeze(0)
+        s = s.masked_fill(j > i, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    o = torch.matmul(p, vf)                                    # b ng qpg sq d
+    return o.permute(3, 0, 1, 2, 4).reshape(sq, b, ng * qpg, d).to(q.dtype)
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        sq, b, ng, qpg, d = q.shape
+        sk = k.shape[0]
+        assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+        o = torch.empty(sq, b, ng, qpg, d, dtype=q.dtype, device=q.device)
+        lse = torch.empty(b, ng, qpg, sq, dtype=torch.float32, device=q.device)
+        st = _lib.status_word()
+        qs, ks, vs, os_ = q.stride(), k.stride(), v.stride(), o.stride()
+        _lib.check(_lib.lib().mlb_attn_fwd(
+            1 if q.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+            lse.data_ptr(), sq, sk, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2],
+            vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), st.data_ptr(),
+            _lib.stream()), "attn_fwd")
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.cfg = (causal, scale)
+        return o.view(sq, b, ng * qpg, d)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, scale = ctx.cfg
+        sq, b, ng, qpg, d = q.shape
+        sk = k.shape[0]
+        do = do.reshape(sq, b, ng, qpg, d)
+        if do.stride(-1) != 1:
+            do = do.contiguous()
+        dq = torch.empty(sq, b, ng, qpg, d, dtype=q.dtype, device=q.device)
+        dk = torch.empty(sk, b, ng, d, dtype=q.dtype, device=q.device)
+        dv = torch.empty(sk, b, ng, d, dtype=q.dtype, device=q.device)
+        delta = torch.empty(b, ng, qpg, sq, dtype=torch.float32, device=q.device)
+        st = _lib.status_word()
+        qs, ks, vs, os_, dos = q.stride(), k.stride(), v.stride(), o.stride(), do.stride()
+        dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
+        _lib.check(_lib.lib().mlb_attn_bwd(
+            1 if q.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+            do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            sq, sk, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2],
+            os_[0], os_[1], os_[2], os_[3], dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3],
+            dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), st.data_ptr(),
+            _lib.stream()), "attn_bwd")
+        return dq, dk, dv, None, None
+
+
+class _FusedQKVAttnFn(torch.autograd.Function):
+    """Attention on a fused QKV activation [s, b, ng, qpg + 2, hn]; the gradient comes back as
+    one tensor of the same layout, ready to be the QKV GEMM's output gradient."""
+
+    @staticmethod
+    def forward(ctx, qkv, causal, scale):
+        s, b, ng, tot, d = qkv.shape
+        qpg = tot - 2
+        q, k, v = qkv[:, :, :, :qpg], qkv[:, :, :, qpg], qkv[:, :, :, qpg + 1]
+        o = torch.empty(s, b, ng, qpg, d, dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty(b, ng, qpg, s, dtype=torch.float32, device=qkv.device)
+        st = _lib.status_word()
+        qs, ks, vs, os_ = q.stride(), k.stride(), v.stride(), o.stride()
+        _lib.check(_lib.lib().mlb_attn_fwd(
+            1 if qkv.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+            lse.data_ptr(), s, s, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2],
+            vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), st.data_ptr(),
+            _lib.stream()), "attn_fwd")
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.cfg = (causal, scale)
+        return o.view(s, b, ng * qpg * d)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse = ctx.saved_tensors
+        causal, scale = ctx.cfg
+        s, b, ng, tot, d = qkv.shape
+        qpg = tot - 2
+        q, k, v = qkv[:, :, :, :qpg], qkv[:, :, :, qpg], qkv[:, :, :, qpg + 1]
+        do = do.reshape(s, b, ng, qpg, d)
+        if do.stride(-1) != 1:
+            do = do.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :, :qpg], dqkv[:, :, :, qpg], dqkv[:, :, :, qpg + 1]
+        delta = torch.empty(b, ng, qpg, s, dtype=torch.float32, device=qkv.device)
+        st = _lib.status_word()
+        qs, ks, vs, os_, dos = q.stride(), k.stride(), v.stride(), o.stride(), do.stride()
+        dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
+        _lib.check(_lib.lib().mlb_attn_bwd(
+            1 if qkv.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+            do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            s, s, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2],
+            os_[0], os_[1], os_[2], os_[3], dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3],
+            dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), st.data_ptr(),
+            _lib.stream()), "attn_bwd")
+        return dqkv, None, None
+
+
+def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
+    """q [sq, b, ng, qpg, d], k/v [sk, b, ng, d] -> [sq, b, ng*qpg, d].  With ``causal`` the last
+    query row attends to the last key (sq <= sk)."""
+    d = q.shape[-1]
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    if not q.is_cuda:
+        return _ref_attention(q, k, v, causal, scale)
+    return _FlashAttnFn.apply(q, k, v, causal, scale)
+
+
+def fused_qkv_attention(qkv5, causal: bool = True, scale: Optional[float] = None):
+    """Self-attention straight from the fused projection [s, b, ng, qpg + 2, hn] -> [s, b, np*hn]."""
+    s, b, ng, tot, d = qkv5.shape
+    scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    if not qkv5.is_cuda:
+        qpg = tot - 2
+        o = _ref_attention(qkv5[:, :, :, :qpg], qkv5[:, :, :, qpg], qkv5[:, :, :, qpg + 1], causal, scale)
+        return o.reshape(s, b, ng * qpg * d)
+    return _FusedQKVAttnFn.apply(qkv5, causal, scale)

@@ -1,0 +1,72 @@
+"""tcgen05 flash attention (forward + backward) against the fp32 PyTorch body."""
+import math
+
+import pytest
+import torch
+
+from megatron_lm_b200.ops import _lib
+from megatron_lm_b200.ops.attention import _ref_attention, attention, fused_qkv_attention
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("s,b,ng,qpg,d", [(128, 1, 1, 1, 128), (256, 2, 2, 1, 128), (384, 1, 2, 2, 64),
+                                          (200, 1, 1, 2, 128), (1024, 1, 4, 1, 128)])
+def test_attention_fwd_bwd(s, b, ng, qpg, d, causal):
+    torch.manual_seed(0)
+    q = torch.randn(s, b, ng, qpg, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(s, b, ng, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(s, b, ng, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = attention(q, k, v, causal=causal)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = _ref_attention(qr, kr, vr, causal, 1.0 / math.sqrt(d))
+    assert _rel(out, ref) < 2e-2
+    do = torch.randn_like(ref)
+    out.backward(do.to(out.dtype))
+    ref.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(q.grad, qr.grad) < 3e-2
+    assert _rel(k.grad, kr.grad) < 3e-2
+    assert _rel(v.grad, vr.grad) < 3e-2
+
+
+def test_attention_rectangular_causal():
+    """sq < sk: the last query row sees the last key (decode / chunked prefill shape)."""
+    torch.manual_seed(1)
+    sq, sk, d = 128, 320, 128
+    q = torch.randn(sq, 1, 2, 1, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(sk, 1, 2, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(sk, 1, 2, d, device="cuda", dtype=torch.bfloat16)
+    out = attention(q, k, v, causal=True)
+    ref = _ref_attention(q.float(), k.float(), v.float(), True, 1.0 / math.sqrt(d))
+    assert _rel(out, ref) < 2e-2
+
+
+def test_fused_qkv_attention_in_place_views():
+    torch.manual_seed(2)
+    s, b, ng, qpg, d = 256, 2, 2, 2, 128
+    qkv = torch.randn(s, b, ng, qpg + 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = fused_qkv_attention(qkv, causal=True)
+    ref_in = qkv.detach().float().requires_grad_()
+    ref = fused_qkv_attention(ref_in.cpu().requires_grad_(), causal=True) if False else None
+    r = qkv.detach().float().requires_grad_()
+    o = _ref_attention(r[:, :, :, :qpg], r[:, :, :, qpg], r[:, :, :, qpg + 1], True, 1.0 / math.sqrt(d))
+    o = o.reshape(s, b, ng * qpg * d)
+    assert _rel(out, o) < 2e-2
+    do = torch.randn_like(o)
+    out.backward(do.to(out.dtype))
+    o.backward(do)
+    assert _rel(qkv.grad, r.grad) < 3e-2
+    # run-twice bitwise reproducibility (no atomics anywhere in the backward)
+    qkv2 = qkv.detach().clone().requires_grad_()
+    fused_qkv_attention(qkv2, causal=True).backward(do.to(out.dtype))
+    assert torch.equal(qkv2.grad, qkv.grad)
+    _lib.check_status()
