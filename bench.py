@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-2-7B-style pre-training step, tokens/s (whole job).
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 3 --warmup 3
+
+Config (fixed): 32 layers, hidden 4096, 32 heads (MHA), SwiGLU FFN 11008, RMSNorm eps 1e-5,
+RoPE theta 1e4, seq 4096, vocab 32000, micro-batch 1, global batch 64, bf16 compute with fp32
+master weights / fp32 gradient accumulation, AdamW, grad clipping 1.0; synthetic uniform-random
+tokens, random-init weights.  Parallel layout by GPU count: 1 -> tp1 pp1, 2 -> tp2, 4 -> tp4,
+8 -> tp4 pp2 with 2 virtual stages; sequence parallel and the distributed optimizer are on
+whenever tp > 1 / dp > 1.  Total work is fixed as N grows (strong scaling).
+
+Two timed regions of K optimizer steps each (after W warm-up steps):
+  * device-timed: inputs already on the GPU, CUDA events, max over ranks -> ``value``;
+  * end to end: every step copies its [64, 4097] int64 token batch from pinned host memory and
+    reads the step's loss back to the host -> ``e2e``.
+``--impl reference`` runs the unmodified reference library (megatron.core from baseline/_ref)
+on the same model/config through its own public API.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+LLAMA7B = dict(num_layers=32, hidden_size=4096, num_attention_heads=32, ffn_hidden_size=11008, seq_length=4096,
+               vocab_size=32000, micro_batch_size=1, global_batch_size=64)
+BASELINE_TOKENS_PER_SEC_PER_GPU = None      # the reference publishes no B200 number
+
+
+def layout_for(n: int):
+    return {1: (1, 1, None), 2: (2, 1, None), 4: (4, 1, None), 8: (4, 2, 2)}[n]
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def max_over_ranks(x: float, device) -> float:
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync():
+    import torch.distributed as dist
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+# ----------------------------------------------------------------------------- our implementation
+def run_ours(args):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig, TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.ops import _lib
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.parallel.random import model_parallel_cuda_manual_seed
+    from megatron_lm_b200.training.training import setup_model_and_optimizer, train_step
+
+    rank, world, local = dist_env()
+    assert world == args.gpus, f"launched with {world} ranks for --gpus {args.gpus}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    tp, pp, vpp = layout_for(args.gpus)
+    state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+                                    virtual_pipeline_model_parallel_size=vpp, create_gloo_process_groups=False)
+    model_parallel_cuda_manual_seed(1234 + 100 * state.get_pipeline_model_parallel_rank())
+    M = dict(LLAMA7B)
+    if args.layers:
+        M["num_layers"] = args.layers
+    dp = world // (tp * pp)
+    cfg = TransformerConfig(
+        num_layers=M["num_layers"], hidden_size=M["hidden_size"], num_attention_heads=M["num_attention_heads"],
+        ffn_hidden_size=M["ffn_hidden_size"], normalization="RMSNorm", layernorm_epsilon=1e-5,
+        gated_linear_unit=True, activation_func="silu", add_bias_linear=False, hidden_dropout=0.0,
+        attention_dropout=0.0, bf16=True, params_dtype=torch.bfloat16, tensor_model_parallel_size=tp,
+        pipeline_model_parallel_size=pp, virtual_pipeline_model_parallel_size=vpp, sequence_parallel=tp > 1,
+        pipeline_dtype=torch.bfloat16, tp_comm_overlap=args.tp_comm_overlap and tp > 1, init_method_std=0.02,
+        overlap_p2p_comm=pp > 1)
+
+    def provider(pre_process=True, post_process=True, vp_stage=None):
+        return GPTModel(cfg, vocab_size=M["vocab_size"], max_sequence_length=M["seq_length"], pre_process=pre_process,
+                        post_process=post_process, position_embedding_type="rope", rotary_base=10000.0,
+                        share_embeddings_and_output_weights=False, vp_stage=vp_stage)
+
+    ocfg = OptimizerConfig(optimizer="adam", lr=3e-4, min_lr=3e-5, weight_decay=0.1, adam_beta1=0.9, adam_beta2=0.95,
+                           adam_eps=1e-8, clip_grad=1.0, bf16=True, params_dtype=torch.bfloat16,
+                           use_distributed_optimizer=dp > 1)
+    dcfg = DistributedDataParallelConfig(grad_reduce_in_fp32=True, overlap_grad_reduce=dp > 1,
+                                         use_distributed_optimizer=dp > 1)
+    model, opt, sched = setup_model_and_optimizer(
+        provider, cfg, ocfg, dcfg,
+        scheduler_kwargs=dict(lr=3e-4, min_lr=3e-5, lr_decay_style="cosine", train_iters=1000,
+                              global_batch_size=M["global_batch_size"], lr_warmup_iters=10, weight_decay=0.1))
+    if cfg.tp_comm_overlap:
+        from megatron_lm_b200.ops.tp_fused import attach_fused_tp
+        attach_fused_tp(model, cfg, M["seq_length"], M["micro_batch_size"])
+
+    S, B, GB = M["seq_length"], M["micro_batch_size"], M["global_batch_size"]
+    nmb = GB // (B * dp)
+    gen = torch.Generator().manual_seed(1234 + state.get_data_parallel_rank())
+    host_batches = [torch.randint(0, M["vocab_size"], (nmb * B, S + 1), generator=gen, dtype=torch.int64).pin_memory()
+                    for _ in range(2)]
+    h2d_bytes = host_batches[0].numel() * host_batches[0].element_size()
+    first_stage = state.is_pipeline_first_stage()
+    last_stage = state.is_pipeline_last_stage()
+
+    def make_iters(batch):
+        def gen():
+            for i in range(nmb):
+                rows = batch[i * B:(i + 1) * B]
+                yield rows[:, :-1], rows[:, 1:]
+        return [gen() for _ in model] if len(model) > 1 else gen()
+
+    def forward_step(data_iterator, m):
+        tokens, labels = next(data_iterator)
+        out = m(tokens, labels=labels)
+
+        def loss_func(output):
+            loss = output.float().mean()
+            return loss, {"lm loss": loss.detach()}
+        return out, loss_func
+
+    def one_step(batch_dev):
+        return train_step(forward_step, make_iters(batch_dev), model, opt, sched, cfg, num_microbatches=nmb,
+                          seq_length=S, micro_batch_size=B, global_batch_size=GB)
+
+    dev_batches = [b.to(dev) for b in host_batches]
+    for w in range(args.warmup):
+        losses, *_ = one_step(dev_batches[w % 2])
+    _lib.check_status()
+    # ---- device-timed region
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    _lib.launch_count = 0
+    barrier_sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        losses, *_ = one_step(dev_batches[k % 2])
+    e1.record()
+    barrier_sync()
+    dev_ms = max_over_ranks(e0.elapsed_time(e1), dev)
+    launches = _lib.launch_count
+    clocks = sampler.stop() if rank == 0 else None
+    # ---- end-to-end region: pinned host batch -> device every step, loss -> host every step
+    barrier_sync()
+    t0 = time.perf_counter()
+    loss_val = 0.0
+    for k in range(args.steps):
+        b = host_batches[k % 2].to(dev, non_blocking=True)
+        losses, *_ = one_step(b)
+        if losses:
+            loss_val = float(losses["lm loss"].item())
+        else:
+            torch.cuda.current_stream().synchronize()
+    barrier_sync()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, dev)
+    _lib.check_status()
+    tokens_per_step = GB * S
+    value = tokens_per_step * args.steps / (dev_ms / 1e3)
+    e2e = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    if rank == 0:
+        from megatron_lm_b200.training.flops import flops_from_config
+        fl = flops_from_config(cfg, GB, S, M["vocab_size"])
+        par = f"tp{tp}pp{pp}" + (f"vpp{vpp}" if vpp else "") + f"dp{dp}" + ("-sp" if tp > 1 else "")
+        out = {
+            "metric": "tokens/sec (whole job) Llama-7B pre-training step", "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / args.gpus / BASELINE_TOKENS_PER_SEC_PER_GPU) if BASELINE_TOKENS_PER_SEC_PER_GPU else None,
+            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
+            "tokens_per_sec_per_gpu": value / args.gpus,
+            "model_tflops_per_gpu": fl / (dev_ms / args.steps / 1e3) / 1e12 / args.gpus,
+            "config": {"model": "llama2-7b (32L h4096 32 heads ffn11008 swiglu rmsnorm rope)" if not args.layers
+                       else f"llama2-7b truncated to {args.layers} layers (debug only)",
+                       "global_batch": GB, "seq_len": S, "micro_batch": B, "parallelism": par,
+                       "l2_note": "inputs and weights (>13 GB) far exceed the 126 MB L2 every step"},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": loss_val},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    state.destroy_model_parallel()
+    dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    rank, world, local = dist_env()
+    if not os.path.isdir(os.path.join(ref, "megatron", "core")):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this box"}))
+        return
+    sys.path.insert(0, ROOT)
+    from baseline.run_reference import run
+    run(args, ref, LLAMA7B, layout_for, ClockSampler, max_over_ranks, barrier_sync)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a bench value)")
+    ap.add_argument("--tp-comm-overlap", action="store_true", default=True)
+    ap.add_argument("--no-tp-comm-overlap", dest="tp_comm_overlap", action="store_false")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -126,6 +126,14 @@ class Norm(nn.Module):
 
 
 # --------------------------------------------------------------------------- attention
+def _rope_copy(qkv5, cos, sin, interleaved):
+    """Out-of-place RoPE on q and k of a fused QKV tensor (inference path, no autograd)."""
+    out = qkv5.clone()
+    view = out[:, :, :, :-1]
+    ops._rope_launch(view, view, cos, sin, interleaved, 1.0)
+    return out
+
+
 class SelfAttention(nn.Module):
     def __init__(self, config: TransformerConfig, layer_number: int, causal: bool = True):
         super().__init__()
@@ -153,8 +161,10 @@ class SelfAttention(nn.Module):
         self.softmax_scale = scale
         self.recompute_core = config.recompute_granularity == "selective" and "core_attn" in config.recompute_modules
 
-    def _core(self, qkv5):
-        return fused_qkv_attention(qkv5, causal=self.causal, scale=self.softmax_scale)
+    def _core(self, qkv5, cos=None, sin=None):
+        rope = None if cos is None else (cos, sin)
+        return fused_qkv_attention(qkv5, causal=self.causal, scale=self.softmax_scale, rope=rope,
+                                   rotary_interleaved=self.config.rotary_interleaved)
 
     def forward(self, hidden_states, rotary=None, inference_context=None, attention_mask=None):
         qkv, _ = self.linear_qkv(hidden_states)                       # [s, b, (np+2ng)/tp * hn]
@@ -164,15 +174,18 @@ class SelfAttention(nn.Module):
             q = self.q_layernorm(qkv5[:, :, :, :self.qpg].contiguous())
             k = self.k_layernorm(qkv5[:, :, :, self.qpg:self.qpg + 1].contiguous())
             qkv5 = torch.cat((q, k, qkv5[:, :, :, self.qpg + 1:]), dim=3)
-        if rotary is not None:
-            cos, sin = rotary
-            qkv5 = ops.apply_rope_qkv_(qkv5, cos, sin, self.config.rotary_interleaved)
+        cos, sin = rotary if rotary is not None else (None, None)
         if inference_context is not None:
+            if cos is not None:
+                qkv5 = _rope_copy(qkv5, cos, sin, self.config.rotary_interleaved) if qkv5.is_cuda else \
+                    ops.apply_rope_qkv_(qkv5, cos, sin, self.config.rotary_interleaved)
             ctx_out = inference_context.attend(self.layer_number, qkv5, self.softmax_scale)
         elif self.recompute_core and self.training:
-            ctx_out = checkpoint(self._core, False, qkv5)
+            # the in-place rotation must not run twice on one buffer: recompute works on a copy
+            ctx_out = checkpoint(lambda t, c, s_: self._core(t.clone() if t.is_cuda else t, c, s_), False,
+                                 qkv5, cos, sin)
         else:
-            ctx_out = self._core(qkv5)                                # [s, b, np_local * hn]
+            ctx_out = self._core(qkv5, cos, sin)                      # [s, b, np_local * hn]
         out, bias = self.linear_proj(ctx_out)
         return out, bias
 

@@ -178,7 +178,13 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+launch_count = 0          # kernels of this library launched so far (a caller may reset it)
+_KERNELS_PER_CALL = {"norm_bwd": 2, "colsum": 2, "sumsq": 2, "attn_bwd": 3, "set_device": 0}
+
+
 def check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += _KERNELS_PER_CALL.get(what, 1)
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}"
                            + (" (CUDA error)" if rc > 0 else " (argument/shape not supported)"))

@@ -92,9 +92,16 @@ class _FusedQKVAttnFn(torch.autograd.Function):
     one tensor of the same layout, ready to be the QKV GEMM's output gradient."""
 
     @staticmethod
-    def forward(ctx, qkv, causal, scale):
+    def forward(ctx, qkv, causal, scale, cos, sin, interleaved):
         s, b, ng, tot, d = qkv.shape
         qpg = tot - 2
+        if cos is not None:
+            # Rotate q and k inside the projection output itself.  Its producer keeps no
+            # reference to it for backward, and the rotation is undone on the gradient below.
+            from .core import _rope_launch
+            qk = qkv[:, :, :, :qpg + 1]
+            _rope_launch(qk, qk, cos, sin, interleaved, 1.0)
+        ctx.rope = (cos, sin, interleaved)
         q, k, v = qkv[:, :, :, :qpg], qkv[:, :, :, qpg], qkv[:, :, :, qpg + 1]
         o = torch.empty(s, b, ng, qpg, d, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(b, ng, qpg, s, dtype=torch.float32, device=qkv.device)
@@ -132,7 +139,12 @@ class _FusedQKVAttnFn(torch.autograd.Function):
             os_[0], os_[1], os_[2], os_[3], dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3],
             dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), st.data_ptr(),
             _lib.stream()), "attn_bwd")
-        return dqkv, None, None
+        cos, sin, interleaved = ctx.rope
+        if cos is not None:
+            from .core import _rope_launch
+            dqk = dqkv[:, :, :, :qpg + 1]
+            _rope_launch(dqk, dqk, cos, sin, interleaved, -1.0)       # inverse rotation of dq, dk
+        return dqkv, None, None, None, None, None
 
 
 def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
@@ -145,12 +157,19 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
     return _FlashAttnFn.apply(q, k, v, causal, scale)
 
 
-def fused_qkv_attention(qkv5, causal: bool = True, scale: Optional[float] = None):
-    """Self-attention straight from the fused projection [s, b, ng, qpg + 2, hn] -> [s, b, np*hn]."""
+def fused_qkv_attention(qkv5, causal: bool = True, scale: Optional[float] = None, rope=None,
+                        rotary_interleaved: bool = False):
+    """Self-attention straight from the fused projection [s, b, ng, qpg + 2, hn] -> [s, b, np*hn].
+    ``rope=(cos, sin)`` (fp32 [s, rot/2]) rotates q and k first; on CUDA this happens in place in
+    ``qkv5``, which must therefore not be read again by the caller."""
     s, b, ng, tot, d = qkv5.shape
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    cos, sin = rope if rope is not None else (None, None)
     if not qkv5.is_cuda:
         qpg = tot - 2
+        if cos is not None:
+            from .core import apply_rope_qkv_
+            qkv5 = apply_rope_qkv_(qkv5, cos, sin, rotary_interleaved)
         o = _ref_attention(qkv5[:, :, :, :qpg], qkv5[:, :, :, qpg], qkv5[:, :, :, qpg + 1], causal, scale)
         return o.reshape(s, b, ng * qpg * d)
-    return _FusedQKVAttnFn.apply(qkv5, causal, scale)
+    return _FusedQKVAttnFn.apply(qkv5, causal, scale, cos, sin, rotary_interleaved)

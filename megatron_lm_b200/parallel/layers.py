@@ -83,20 +83,24 @@ class _TPLinear(torch.autograd.Function):
         ctx.bias = bias
         ctx.x_shape = x.shape
         n = _size(group)
+        N = weight.shape[0]
+
+        def product(inp, lead):
+            # the result is allocated in its final shape so that the Function returns no view
+            if inp.is_cuda:
+                out = torch.empty(*lead, N, dtype=inp.dtype, device=inp.device)
+                gemm(_as2d(inp), weight, bias=bias, out=out.view(-1, N))
+                return out
+            return torch.nn.functional.linear(inp, weight, bias)
+
         if gather_input and n > 1:
-            if fused is not None and x.is_cuda:
-                total, y = fused.ag_gemm(x, weight, bias)
-                del total
-            else:
-                total = gather_first(x, group)
-                y = gemm(_as2d(total), weight, bias=bias) if x.is_cuda else \
-                    torch.nn.functional.linear(total, weight, bias).reshape(-1, weight.shape[0])
             lead = (x.shape[0] * n,) + tuple(x.shape[1:-1])
+            if fused is not None and x.is_cuda:
+                y = fused.ag_gemm(x, weight, bias).view(*lead, N)
+            else:
+                y = product(gather_first(x, group), lead)
         else:
-            y = gemm(_as2d(x), weight, bias=bias) if x.is_cuda else \
-                torch.nn.functional.linear(x, weight, bias).reshape(-1, weight.shape[0])
-            lead = tuple(x.shape[:-1])
-        y = y.view(*lead, weight.shape[0])
+            y = product(x, tuple(x.shape[:-1]))
         if n > 1 and reduce_output == "reduce_scatter":
             y = fused.reduce_scatter(y) if (fused is not None and x.is_cuda) else reduce_scatter_first(y, group)
         elif n > 1 and reduce_output == "all_reduce":

@@ -1,0 +1,85 @@
+"""Pipeline point-to-point transfers over the pipeline group (NCCL on GPUs, Gloo on CPU).
+
+The reference exposes nine send/recv combinations built on ``batch_isend_irecv``
+(megatron/core/pipeline_parallel/p2p_communication.py:119-604).  Here a
+communicator object owns the fixed activation shape and dtype of the run and
+offers four primitives - post a receive from the previous / next stage, send to
+the next / previous stage - all non-blocking; the schedule executor decides when
+to wait.  Sends are kept alive until complete and drained at the end of the step.
+Variable sequence lengths exchange a 3-element shape tensor first (:21).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+class _Pending:
+    __slots__ = ("tensor", "work")
+
+    def __init__(self, tensor, work):
+        self.tensor, self.work = tensor, work
+
+
+class P2PCommunicator:
+    def __init__(self, group, pp_rank: int, pp_size: int, shape: Tuple[int, ...], dtype, config=None):
+        self.group, self.rank, self.size = group, pp_rank, pp_size
+        self.shape, self.dtype = tuple(shape), dtype
+        self.config = config
+        self.variable = bool(config.variable_seq_lengths) if config is not None else False
+        self.prev = dist.get_global_rank(group, (pp_rank - 1) % pp_size) if group is not None else None
+        self.next = dist.get_global_rank(group, (pp_rank + 1) % pp_size) if group is not None else None
+        self._sends: List[_Pending] = []
+        backend = dist.get_backend(group) if group is not None else "gloo"
+        self.device = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+
+    # -- receives ------------------------------------------------------------
+    def _irecv(self, src: int) -> _Pending:
+        shape = self.shape
+        if self.variable:
+            sh = torch.empty(3, dtype=torch.int64, device=self.device)
+            dist.recv(sh, src=src, group=self.group)
+            shape = tuple(int(x) for x in sh.tolist())
+        buf = torch.empty(shape, dtype=self.dtype, device=self.device)
+        return _Pending(buf, dist.irecv(buf, src=src, group=self.group))
+
+    def irecv_forward(self) -> _Pending:
+        """Activation from the previous stage (the last stage's sender for rank 0 of a later chunk)."""
+        return self._irecv(self.prev)
+
+    def irecv_backward(self) -> _Pending:
+        """Output gradient from the next stage."""
+        return self._irecv(self.next)
+
+    def wait(self, pending: Optional[_Pending]) -> Optional[torch.Tensor]:
+        if pending is None:
+            return None
+        pending.work.wait()
+        return pending.tensor
+
+    # -- sends -----------------------------------------------------------------
+    def _isend(self, t: torch.Tensor, dst: int) -> None:
+        t = t.detach().contiguous()
+        if t.dtype != self.dtype:
+            t = t.to(self.dtype)
+        if self.variable:
+            sh = torch.tensor(list(t.shape) + [1] * (3 - t.dim()), dtype=torch.int64, device=self.device)
+            dist.send(sh, dst=dst, group=self.group)
+        self._sends.append(_Pending(t, dist.isend(t, dst=dst, group=self.group)))
+        self._reap()
+
+    def send_forward(self, t: torch.Tensor) -> None:
+        self._isend(t, self.next)
+
+    def send_backward(self, t: torch.Tensor) -> None:
+        self._isend(t, self.prev)
+
+    def _reap(self) -> None:
+        self._sends = [p for p in self._sends if not p.work.is_completed()]
+
+    def drain(self) -> None:
+        for p in self._sends:
+            p.work.wait()
+        self._sends = []
