@@ -165,8 +165,9 @@ def run_ours(args):
     S, B, GB = M["seq_length"], M["micro_batch_size"], M["global_batch_size"]
     nmb = GB // (B * dp)
     gen = torch.Generator().manual_seed(1234 + state.get_data_parallel_rank())
+    n_batches = args.warmup + 2 * args.steps          # a fresh batch for every step of the run
     host_batches = [torch.randint(0, M["vocab_size"], (nmb * B, S + 1), generator=gen, dtype=torch.int64).pin_memory()
-                    for _ in range(2)]
+                    for _ in range(n_batches)]
     h2d_bytes = host_batches[0].numel() * host_batches[0].element_size()
     first_stage = state.is_pipeline_first_stage()
     last_stage = state.is_pipeline_last_stage()
@@ -191,9 +192,9 @@ def run_ours(args):
         return train_step(forward_step, make_iters(batch_dev), model, opt, sched, cfg, num_microbatches=nmb,
                           seq_length=S, micro_batch_size=B, global_batch_size=GB)
 
-    dev_batches = [b.to(dev) for b in host_batches]
+    dev_batches = [b.to(dev) for b in host_batches[:args.warmup + args.steps]]
     for w in range(args.warmup):
-        losses, *_ = one_step(dev_batches[w % 2])
+        losses, *_ = one_step(dev_batches[w])
     _lib.check_status()
     # ---- device-timed region
     sampler = ClockSampler(local)
@@ -204,7 +205,7 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for k in range(args.steps):
-        losses, *_ = one_step(dev_batches[k % 2])
+        losses, *_ = one_step(dev_batches[args.warmup + k])
     e1.record()
     barrier_sync()
     dev_ms = max_over_ranks(e0.elapsed_time(e1), dev)
@@ -215,7 +216,7 @@ def run_ours(args):
     t0 = time.perf_counter()
     loss_val = 0.0
     for k in range(args.steps):
-        b = host_batches[k % 2].to(dev, non_blocking=True)
+        b = host_batches[args.warmup + args.steps + k].to(dev, non_blocking=True)
         losses, *_ = one_step(b)
         if losses:
             loss_val = float(losses["lm loss"].item())

@@ -150,6 +150,51 @@ __global__ void rope_kernel(const T* __restrict__ src, T* __restrict__ dst, cons
   }
 }
 
+// Vector form for the common case: rotate-half pairing, rot/2 a multiple of 8, 16-byte aligned heads.
+// One thread rotates 8 pairs: two 16-byte loads of activations, four of cos/sin.
+template <typename T>
+__global__ void rope_vec_kernel(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ cs,
+                                const float* __restrict__ sn, int s, int b, int n_outer, int n_inner, int hn,
+                                int rot, float sign, long ss_s, long ss_b, long ss_o, long ss_i,
+                                long ds_s, long ds_b, long ds_o, long ds_i) {
+  const int half = rot >> 1;
+  const int vec_per_head = half >> 3;
+  const int tail_vec = (hn - rot) >> 3;                     // pass-through channels (copied when out of place)
+  const int per_head = vec_per_head + ((src != dst) ? tail_vec : 0);
+  const size_t heads = (size_t)s * b * n_outer * n_inner;
+  const size_t total = heads * per_head;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % per_head);
+    size_t hidx = i / per_head;
+    const int ii = (int)(hidx % n_inner); hidx /= n_inner;
+    const int oo = (int)(hidx % n_outer); hidx /= n_outer;
+    const int bb = (int)(hidx % b);
+    const int sidx = (int)(hidx / b);
+    const T* sp = src + sidx * ss_s + bb * ss_b + oo * ss_o + ii * ss_i;
+    T* dp = dst + sidx * ds_s + bb * ds_b + oo * ds_o + ii * ds_i;
+    if (v < vec_per_head) {
+      float x0[8], x1[8], c[8], sv[8], o0[8], o1[8];
+      load8(sp + v * 8, x0);
+      load8(sp + half + v * 8, x1);
+      load8(cs + (size_t)sidx * half + v * 8, c);
+      load8(sn + (size_t)sidx * half + v * 8, sv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float sg = sign * sv[k];
+        o0[k] = x0[k] * c[k] - x1[k] * sg;
+        o1[k] = x1[k] * c[k] + x0[k] * sg;
+      }
+      store8(dp + v * 8, o0);
+      store8(dp + half + v * 8, o1);
+    } else {
+      const int j = rot + (v - vec_per_head) * 8;
+      float t[8];
+      load8(sp + j, t);
+      store8(dp + j, t);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- bias + dropout + residual
 __device__ __forceinline__ uint32_t hash32(uint64_t x) {
   x ^= x >> 33; x *= 0xff51afd7ed558ccdULL; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ULL; x ^= x >> 33;
@@ -320,6 +365,19 @@ MLB_API int mlb_rope(int dtype, const void* src, void* dst, const float* cs, con
                      long ss_s, long ss_b, long ss_o, long ss_i, long ds_s, long ds_b, long ds_o, long ds_i,
                      cudaStream_t st) {
   if (rot % 2 || rot > hn) return -3;
+  const int half = rot / 2;
+  const long strides[] = {ss_s, ss_b, ss_o, ss_i, ds_s, ds_b, ds_o, ds_i};
+  bool vec_ok = !interleaved && half % 8 == 0 && (hn - rot) % 8 == 0 && dtype != MLB_F32 &&
+                (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 &&
+                (reinterpret_cast<uintptr_t>(cs) & 31) == 0 && (reinterpret_cast<uintptr_t>(sn) & 31) == 0;
+  for (long st_ : strides) vec_ok = vec_ok && (st_ % 8 == 0);
+  if (vec_ok) {
+    const size_t vwork = (size_t)s * b * n_outer * n_inner * ((half + (src != dst ? hn - rot : 0)) / 8);
+    MLB_DISPATCH_ACT(dtype, T, (rope_vec_kernel<T><<<ew_grid(vwork), kEwThreads, 0, st>>>(
+        (const T*)src, (T*)dst, cs, sn, s, b, n_outer, n_inner, hn, rot, sign,
+        ss_s, ss_b, ss_o, ss_i, ds_s, ds_b, ds_o, ds_i)));
+    MLB_CHECK_LAUNCH(); return 0;
+  }
   const size_t work = (size_t)s * b * n_outer * n_inner * (hn - rot / 2);
   MLB_DISPATCH_ACT(dtype, T, (rope_kernel<T><<<ew_grid(work), kEwThreads, 0, st>>>(
       (const T*)src, (T*)dst, cs, sn, s, b, n_outer, n_inner, hn, rot, interleaved, sign,

@@ -31,25 +31,40 @@ struct GemmParams {
   int lp_fmt;                 // 1 = bf16, 0 = fp16 (inputs and OUT_LP output)
   int* status;
   int tiles_m, tiles_n;
+  int tma_out;                // 1: epilogue stages tiles in shared memory and stores / add-reduces them by TMA
 };
+
+__device__ __forceinline__ float load_bias(const void* bias, int col, int N, int bf) {
+  if (col >= N) return 0.f;
+  return bf ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col])
+            : __half2float(reinterpret_cast<const __half*>(bias)[col]);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, int bf) {
+  if (bf) { __nv_bfloat162 v = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&v); }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
 template <int BN> struct GemmSmem {
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
-  static constexpr int kBytes = kStages * (kABytes + kBBytes) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 4 * 2 * 4096;     // per epilogue warp: two 32-row x 128-byte staging buffers
+  static constexpr int kBytes = kStages * (kABytes + kBBytes) + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + kStages * S::kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (S::kABytes + S::kBBytes));
+  uint8_t* sEpi = smem + kStages * (S::kABytes + S::kBBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + S::kEpiBytes);
   // bars: full[kStages], empty[kStages], tfull[2], tempty[2]; then tmem slot + abort flag
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -66,6 +81,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+    if (p.tma_out) prefetch_tmap(&tmD);
   }
   if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 2 * BN >= 32 ? 2 * BN : 32); tmem_relinquish(); }
   fence_before_sync();
@@ -142,6 +158,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
     int t = 0;
+    int epi_buf = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
       const int acc = t & 1;
@@ -151,6 +168,57 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       fence_after_sync();
       const int row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+      if (p.tma_out) {
+        // ---- staged epilogue: registers -> 128B-swizzled shared tile -> TMA store / add-reduce.
+        // Each warp owns rows [quad*32, quad*32+32) of the tile and two private 4 KB buffers, so no
+        // cross-warp synchronisation is needed; out-of-range rows/columns are clipped by the TMA.
+        const int cw = (p.out_mode == OUT_LP) ? 64 : 32;          // columns per 128-byte staged row
+        uint8_t* my_stage = sEpi + (warp - 2) * 8192;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += cw) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(t_row + (uint32_t)c, r0);
+          if (cw == 64) tmem_ld32(t_row + (uint32_t)c + 32, r1);
+          tmem_wait_ld();
+          if (lane == 0) bulk_wait_read<1>();                      // the buffer used two chunks ago is free
+          __syncwarp();
+          uint8_t* stage = my_stage + epi_buf * 4096;
+          const int col = n0 + c;
+          uint32_t w[32];
+          if (p.out_mode == OUT_LP) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+              float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+              if (p.bias != nullptr) {
+                a0 += load_bias(p.bias, col + 2 * i, p.N, p.lp_fmt); a1 += load_bias(p.bias, col + 2 * i + 1, p.N, p.lp_fmt);
+                b0 += load_bias(p.bias, col + 32 + 2 * i, p.N, p.lp_fmt); b1 += load_bias(p.bias, col + 33 + 2 * i, p.N, p.lp_fmt);
+              }
+              w[i] = pack2(a0, a1, p.lp_fmt);
+              w[16 + i] = pack2(b0, b1, p.lp_fmt);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float a = __uint_as_float(r0[i]);
+              if (p.bias != nullptr) a += load_bias(p.bias, col + i, p.N, p.lp_fmt);
+              w[i] = __float_as_uint(a);
+            }
+          }
+          uint8_t* rowp = stage + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && col < p.N && (m0 + quad * 32) < p.M) {
+            if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(&tmD, smem_u32(stage), col, m0 + quad * 32);
+            else tma_store_2d(&tmD, smem_u32(stage), col, m0 + quad * 32);
+            bulk_commit();
+          }
+          epi_buf ^= 1;
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -206,11 +274,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
+      }
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty(acc));
     }
   }
+  if (p.tma_out && warp >= 2 && lane == 0) bulk_wait<0>();     // staged stores have landed
   // ---------------------------------------------------------------- teardown
   fence_before_sync();
   __syncthreads();
@@ -218,7 +288,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams p, int sm_count, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, GemmParams p,
+                       int sm_count, cudaStream_t st) {
   using S = GemmSmem<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
@@ -231,7 +302,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  kern<<<grid, kGemmThreads, S::kBytes, st>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, p);
   MLB_CHECK_LAUNCH();
   return 0;
 }
@@ -274,12 +345,22 @@ MLB_API int mlb_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* 
     strides[0] = (uint64_t)ldb * 2;
     if ((rc = make_tmap(&tmB, B, 2, dims, strides, box))) return rc;
   }
+  CUtensorMap tmD;
+  const int esz = (out_mode == OUT_LP) ? 2 : 4;
+  int tma_out = (((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
+  if (tma_out) {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)ldd * esz};
+    uint32_t box[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
+    if (make_tmap(&tmD, D, 2, dims, strides, box, esz)) tma_out = 0;
+  }
+  if (!tma_out) tmD = tmA;     // placeholder, unused
   GemmParams p;
+  p.tma_out = tma_out;
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
   int sms = sm_count_cached();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-#define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, p, sms, st)
+#define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, tmD, p, sms, st)
   if (bn == 256) {
     if (!a_mn && !b_mn) GO(256, false, false);
     if (!a_mn && b_mn) GO(256, false, true);

@@ -151,19 +151,29 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __re
   }
 }
 
-// Fold [nparts, 2, h] partials into dgamma (and dbeta).  One thread per column.
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int h,
-                                       float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= h) return;
+// Fold [nparts, 2, h] partials into dgamma (and dbeta).  A block owns 32 columns; its 8 warps split the
+// partial rows, each lane keeps one column (coalesced 128-byte reads), and shared memory joins the warps.
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ partial, int nparts, int h, float* __restrict__ dgamma,
+                       float* __restrict__ dbeta, int accumulate) {
+  __shared__ float sa[8][32], sb[8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float a = 0.f, b = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    a += partial[(size_t)p * 2 * h + c];
-    if (dbeta) b += partial[(size_t)p * 2 * h + h + c];
+  if (c < h) {
+    for (int p = w; p < nparts; p += 8) {
+      a += partial[(size_t)p * 2 * h + c];
+      if (dbeta) b += partial[(size_t)p * 2 * h + h + c];
+    }
   }
-  if (accumulate) { dgamma[c] += a; if (dbeta) dbeta[c] += b; }
-  else { dgamma[c] = a; if (dbeta) dbeta[c] = b; }
+  sa[w][lane] = a; sb[w][lane] = b;
+  __syncthreads();
+  if (w == 0 && c < h) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) { a += sa[k][lane]; b += sb[k][lane]; }
+    if (accumulate) { dgamma[c] += a; if (dbeta) dbeta[c] += b; }
+    else { dgamma[c] = a; if (dbeta) dbeta[c] = b; }
+  }
 }
 
 static int pick_nv(int h) {
@@ -231,7 +241,7 @@ MLB_API int mlb_norm_bwd(int dtype, int rms, const void* dy, const void* x, cons
              : mlb::launch_bwd<T, false>(dy, x, gamma, mean, rstd, dx, workspace, rows, h, zero_centered, grid, st);
   });
   if (rc) return rc;
-  mlb::norm_bwd_reduce_kernel<<<(h + 255) / 256, 256, 0, st>>>(workspace, grid, h, dgamma, rms ? nullptr : dbeta,
+  mlb::norm_bwd_reduce_kernel<<<(h + 31) / 32, 256, 0, st>>>(workspace, grid, h, dgamma, rms ? nullptr : dbeta,
                                                                accumulate);
   MLB_CHECK_LAUNCH();
   return 0;

@@ -1,0 +1,97 @@
+"""Whole-model numerics on the GPU against the same model evaluated in fp32 on the CPU."""
+import pytest
+import torch
+
+from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig, TransformerConfig
+from megatron_lm_b200.models.gpt import GPTModel
+from megatron_lm_b200.ops import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float().cpu() - b.float().cpu()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _cfg(kind, dtype, device_cpu):
+    kw = dict(num_layers=2, hidden_size=256, num_attention_heads=4, ffn_hidden_size=512, hidden_dropout=0.0,
+              attention_dropout=0.0, params_dtype=dtype, bf16=dtype == torch.bfloat16, use_cpu_initialization=device_cpu,
+              kv_channels=64)
+    if kind == "llama":
+        kw.update(normalization="RMSNorm", gated_linear_unit=True, activation_func="silu", add_bias_linear=False,
+                  num_query_groups=2)
+    return TransformerConfig(**kw)
+
+
+@pytest.mark.parametrize("kind", ["gpt", "llama"])
+def test_loss_and_grads_match_cpu_fp32(kind):
+    torch.manual_seed(0)
+    V, S, B = 512, 256, 2
+    pe = "rope" if kind == "llama" else "learned_absolute"
+    ref = GPTModel(_cfg(kind, torch.float32, True), V, S, position_embedding_type=pe,
+                   share_embeddings_and_output_weights=(kind == "gpt"))
+    gpu = GPTModel(_cfg(kind, torch.bfloat16, False), V, S, position_embedding_type=pe,
+                   share_embeddings_and_output_weights=(kind == "gpt"))
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(ref.named_parameters(), gpu.named_parameters()):
+            p.copy_(p.to(torch.bfloat16).float())          # both sides start from bf16-representable weights
+            q.copy_(p)
+    tokens = torch.randint(0, V, (B, S + 1))
+    lr = ref(tokens[:, :-1], labels=tokens[:, 1:]).mean()
+    lg = gpu(tokens[:, :-1].cuda(), labels=tokens[:, 1:].cuda()).mean()
+    assert abs(lr.item() - lg.item()) < 3e-2, (lr.item(), lg.item())
+    lr.backward()
+    lg.backward()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    worst = 0.0
+    for (n, p), (_, q) in zip(ref.named_parameters(), gpu.named_parameters()):
+        assert q.grad is not None, n
+        r = _rel(q.grad, p.grad)
+        worst = max(worst, r)
+        assert r < 8e-2, (n, r)
+    assert worst > 0
+
+
+def test_causality_future_tokens_do_not_change_past_logits():
+    torch.manual_seed(1)
+    V, S = 512, 384
+    m = GPTModel(_cfg("llama", torch.bfloat16, False), V, S, position_embedding_type="rope").eval()
+    t1 = torch.randint(0, V, (1, S), device="cuda")
+    t2 = t1.clone()
+    t2[:, 200:] = torch.randint(0, V, (1, S - 200), device="cuda")
+    with torch.no_grad():
+        a, b = m(t1), m(t2)
+    assert torch.equal(a[:, :200], b[:, :200])
+    assert not torch.equal(a[:, 200:], b[:, 200:])
+
+
+def test_train_step_reduces_loss_and_matches_cpu_trajectory():
+    from megatron_lm_b200.training.training import setup_model_and_optimizer, train_step
+    torch.manual_seed(2)
+    V, S, B = 256, 128, 2
+    tokens = torch.randint(0, V, (B, S + 1))
+    traj = {}
+    for dev in ("cpu", "cuda"):
+        torch.manual_seed(3)
+        cfg = _cfg("llama", torch.float32 if dev == "cpu" else torch.bfloat16, True)
+        cfg.use_cpu_initialization = True
+
+        def provider(pre_process=True, post_process=True, vp_stage=None):
+            m = GPTModel(cfg, V, S, position_embedding_type="rope")
+            return m.cuda() if dev == "cuda" else m
+        model, opt, _ = setup_model_and_optimizer(provider, cfg, OptimizerConfig(lr=2e-3, clip_grad=1.0, weight_decay=0.0),
+                                                  DistributedDataParallelConfig(grad_reduce_in_fp32=True))
+        tk = tokens.to(dev)
+
+        def fwd(it, m):
+            out = m(tk[:, :-1], labels=tk[:, 1:])
+            return out, (lambda o: (o.float().mean(), {"lm loss": o.float().mean().detach()}))
+        losses = []
+        for _ in range(6):
+            l, *_ = train_step(fwd, None, model, opt, None, cfg, num_microbatches=1, seq_length=S, micro_batch_size=B)
+            losses.append(float(l["lm loss"]))
+        traj[dev] = losses
+    assert traj["cuda"][-1] < traj["cuda"][0]
+    for a, b in zip(traj["cpu"], traj["cuda"]):
+        assert abs(a - b) < 0.08, (traj["cpu"], traj["cuda"])

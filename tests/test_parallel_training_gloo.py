@@ -1,0 +1,130 @@
+"""TP / SP / PP / VPP / DP(+ZeRO-1) on CPU Gloo ranks must reproduce the single-process training
+trajectory of the same model (same weights via name-seeded init, same data)."""
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+
+V, S, B, NMB, STEPS = 96, 16, 2, 4, 4
+
+
+def _make_cfg(tp, pp, vpp, sp, kind):
+    from megatron_lm_b200.config import TransformerConfig
+    kw = dict(num_layers=4, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+              attention_dropout=0.0, tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+              virtual_pipeline_model_parallel_size=vpp, sequence_parallel=sp, use_cpu_initialization=True)
+    if kind == "llama":
+        kw.update(normalization="RMSNorm", gated_linear_unit=True, activation_func="silu", add_bias_linear=False,
+                  num_query_groups=2)
+    return TransformerConfig(**kw)
+
+
+def _run(rank, world, tp, pp, vpp, sp, dist_opt, kind, out_path):
+    import torch.distributed as dist
+    from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.training.training import setup_model_and_optimizer, train_step
+    from tests.model_utils import reinit_by_global_name
+    state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+                                    virtual_pipeline_model_parallel_size=vpp)
+    cfg = _make_cfg(tp, pp, vpp, sp, kind)
+    tied = kind == "gpt"
+
+    def provider(pre_process=True, post_process=True, vp_stage=None):
+        m = GPTModel(cfg, V, S, pre_process=pre_process, post_process=post_process, vp_stage=vp_stage,
+                     position_embedding_type="rope" if kind == "llama" else "learned_absolute",
+                     share_embeddings_and_output_weights=tied)
+        reinit_by_global_name(m, cfg)
+        if tied and post_process and not pre_process:
+            # the last stage's copy of the tied weight starts equal to the first stage's
+            g = torch.Generator().manual_seed(__import__("tests.model_utils", fromlist=["_seed"])._seed(
+                "embedding.word_embeddings.weight"))
+            full = 0.05 * torch.randn(V, cfg.hidden_size, generator=g)
+            per = V // tp
+            r = state.get_tensor_model_parallel_rank()
+            with torch.no_grad():
+                m.output_layer.weight.copy_(full[r * per:(r + 1) * per])
+        return m
+
+    dp = world // (tp * pp)
+    model, opt, _ = setup_model_and_optimizer(
+        provider, cfg, OptimizerConfig(lr=5e-3, weight_decay=0.01, clip_grad=1.0, use_distributed_optimizer=dist_opt),
+        DistributedDataParallelConfig(grad_reduce_in_fp32=True, use_distributed_optimizer=dist_opt,
+                                      overlap_grad_reduce=dist_opt))
+    gen = torch.Generator().manual_seed(5)
+    data = torch.randint(0, V, (STEPS, NMB * B, S + 1), generator=gen)     # global batch per step
+    dpr = state.get_data_parallel_rank()
+    nmb_local = NMB // dp
+    losses = []
+    for step in range(STEPS):
+        rows = data[step][dpr * nmb_local * B:(dpr + 1) * nmb_local * B]
+
+        def gen_it():
+            for i in range(nmb_local):
+                r = rows[i * B:(i + 1) * B]
+                yield r[:, :-1], r[:, 1:]
+        its = [gen_it() for _ in model] if len(model) > 1 else gen_it()
+
+        def fwd(it, m):
+            tok, lab = next(it)
+            out = m(tok, labels=lab)
+            return out, (lambda o: (o.float().mean(), {"lm loss": o.float().mean().detach()}))
+        l, skipped, gnorm, _ = train_step(fwd, its, model, opt, None, cfg, num_microbatches=nmb_local, seq_length=S,
+                                          micro_batch_size=B)
+        losses.append((float(l["lm loss"]) if l else None, float(gnorm)))
+    last = state.is_pipeline_last_stage()
+    if last and state.get_tensor_model_parallel_rank() == 0 and dpr == 0:
+        torch.save(losses, out_path)
+
+
+def _trajectory(tmp_path, world, tp=1, pp=1, vpp=None, sp=False, dist_opt=False, kind="llama"):
+    out = str(tmp_path / f"traj_{world}_{tp}_{pp}_{vpp}_{sp}_{dist_opt}_{kind}.pt")
+    run_distributed(_run, world, tp, pp, vpp, sp, dist_opt, kind, out)
+    return torch.load(out)
+
+
+def _close(a, b, tol=2e-4):
+    for (la, ga), (lb, gb) in zip(a, b):
+        assert abs(la - lb) < tol * max(1.0, abs(la)), (a, b)
+        assert abs(ga - gb) < 5e-3 * max(1.0, abs(ga)), (a, b)
+
+
+@pytest.fixture(scope="module")
+def baseline(tmp_path_factory):
+    d = tmp_path_factory.mktemp("base")
+    return {k: _trajectory(d, 1, kind=k) for k in ("llama", "gpt")}
+
+
+def test_baseline_learns(baseline):
+    assert baseline["llama"][-1][0] < baseline["llama"][0][0]
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tensor_parallel_matches(tmp_path, baseline, sp):
+    _close(_trajectory(tmp_path, 2, tp=2, sp=sp), baseline["llama"])
+
+
+def test_tensor_parallel_gpt_tied_embeddings(tmp_path, baseline):
+    _close(_trajectory(tmp_path, 2, tp=2, sp=True, kind="gpt"), baseline["gpt"])
+
+
+def test_pipeline_parallel_matches(tmp_path, baseline):
+    _close(_trajectory(tmp_path, 2, pp=2), baseline["llama"])
+
+
+def test_pipeline_tied_embeddings_match(tmp_path, baseline):
+    _close(_trajectory(tmp_path, 2, pp=2, kind="gpt"), baseline["gpt"])
+
+
+def test_interleaved_pipeline_matches(tmp_path, baseline):
+    _close(_trajectory(tmp_path, 2, pp=2, vpp=2), baseline["llama"])
+
+
+@pytest.mark.parametrize("dist_opt", [False, True])
+def test_data_parallel_matches(tmp_path, baseline, dist_opt):
+    _close(_trajectory(tmp_path, 2, dist_opt=dist_opt), baseline["llama"])
+
+
+def test_tp2_pp2_sp_distopt(tmp_path, baseline):
+    _close(_trajectory(tmp_path, 4, tp=2, pp=2, sp=True), baseline["llama"])
