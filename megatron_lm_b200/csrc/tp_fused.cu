@@ -1,0 +1,47 @@
+// Tensor-parallel products fused with their sequence-parallel collective, one launch each
+// (the kernel is gemm_core.cuh in its AG / RS communication mode):
+//   mlb_ag_gemm : D = allgather_rows(X_r) * op(B)      column-parallel forward, row-parallel dgrad
+//   mlb_gemm_rs : out = reduce_scatter_rows(A * op(B)) (+ residual)   row-parallel forward, column-parallel dgrad
+// They replace the userbuffer-overlapped GEMMs the reference configures through
+// megatron/training/initialize.py:238-294 and megatron/core/extensions/transformer_engine.py:188-221.
+#include "gemm_core.cuh"
+
+using namespace mlb;
+
+// peer_x / peer_sig: host arrays of tp device addresses (symmetric-memory mappings, this rank's own included).
+// gathered: local [tp*rows_per_rank, K]; chunk_flags: local uint32[tp*rows_per_rank/128]; comm_counter: local uint32.
+// seq: 1, 2, 3, ... per call on this buffer set (flags and signals are monotonic, never reset).
+MLB_API int mlb_ag_gemm(int lp_fmt, const void* const* peer_x, uint32_t* const* peer_sig, void* gathered,
+                        uint32_t* chunk_flags, uint32_t* comm_counter, int rank, int tp, int rows_per_rank,
+                        unsigned seq, int n_comm, const void* B, long ldb, int b_mn, void* D, long ldd, int out_mode,
+                        const void* bias, int N, int K, int* status, cudaStream_t st) {
+  if (tp < 2 || tp > kMaxPeers || rows_per_rank % BM || K % 8) return -7;
+  const int sms = sm_count_cached();
+  if (n_comm < 1 || n_comm >= sms) return -7;
+  CommParams cp = {};
+  cp.mode = COMM_AG; cp.rank = rank; cp.tp = tp; cp.n_comm = n_comm; cp.bpr = rows_per_rank / BM; cp.seq = seq;
+  for (int i = 0; i < tp; ++i) { cp.peer_x[i] = peer_x[i]; cp.peer_sig[i] = peer_sig[i]; }
+  cp.gathered = gathered; cp.chunk_flags = chunk_flags; cp.comm_counter = comm_counter;
+  cp.shard_bytes = (long)rows_per_rank * K * 2;
+  return run_gemm(lp_fmt, gathered, K, 0, B, ldb, b_mn, D, ldd, out_mode, bias, tp * rows_per_rank, N, K, sms, status,
+                  cp, st);
+}
+
+// A: local [tp*rows_per_rank, K] (a_mn = 0).  peer_recv[i]: rank i's receive buffer [tp][rows_per_rank][N];
+// peer_cnt[i]: rank i's uint32[rows_per_rank/128] arrival counters.  cnt_target: cumulative arrivals expected on
+// this counter set once this call is complete (each call adds tp * ceil(N/BN) * 4 per row block).
+MLB_API int mlb_gemm_rs(int lp_fmt, const void* A, long lda, const void* B, long ldb, int b_mn, void* const* peer_recv,
+                        uint32_t* const* peer_cnt, unsigned cnt_target, int rank, int tp, int rows_per_rank,
+                        const void* residual, long ld_res, void* out, long ld_out, int N, int K, int* status,
+                        cudaStream_t st) {
+  if (tp < 2 || tp > kMaxPeers || rows_per_rank % BM || N % 32) return -7;
+  CommParams cp = {};
+  cp.mode = COMM_RS; cp.rank = rank; cp.tp = tp; cp.bpr = rows_per_rank / BM; cp.cnt_target = cnt_target;
+  for (int i = 0; i < tp; ++i) { cp.peer_recv[i] = peer_recv[i]; cp.peer_cnt[i] = peer_cnt[i]; }
+  cp.residual = residual; cp.ld_res = ld_res; cp.out = out; cp.ld_out = ld_out;
+  return run_gemm(lp_fmt, A, lda, 0, B, ldb, b_mn, out /*unused*/, ld_out, OUT_LP, nullptr, tp * rows_per_rank, N, K,
+                  sm_count_cached(), status, cp, st);
+}
+
+// Arrivals one mlb_gemm_rs call adds to each row-block counter.
+MLB_API int mlb_gemm_rs_arrivals(int tp, int N) { return tp * ((N + ((N > 128) ? 256 : 128) - 1) / ((N > 128) ? 256 : 128)) * 4; }

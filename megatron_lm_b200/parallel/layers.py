@@ -75,7 +75,10 @@ def _init_sharded(weight: torch.Tensor, full_shape, partition_dim: int, init_met
 
 class _TPLinear(torch.autograd.Function):
     """y = f(x) W^T with optional input all-gather (sequence parallel), output
-    reduce-scatter / all-reduce, and all-reduce of the data gradient."""
+    reduce-scatter / all-reduce, and all-reduce of the data gradient.
+
+    With a ``fused`` communicator (CUDA, sequence parallel) the gather and the reduce-scatter
+    happen inside the GEMM kernels and the gathered operand is kept for the weight gradient."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, group, gather_input, reduce_output, allreduce_dgrad, fused):
@@ -84,6 +87,9 @@ class _TPLinear(torch.autograd.Function):
         ctx.x_shape = x.shape
         n = _size(group)
         N = weight.shape[0]
+        use_fused = fused is not None and x.is_cuda and n > 1
+        ctx.use_fused = use_fused
+        saved_input = x
 
         def product(inp, lead):
             # the result is allocated in its final shape so that the Function returns no view
@@ -95,17 +101,22 @@ class _TPLinear(torch.autograd.Function):
 
         if gather_input and n > 1:
             lead = (x.shape[0] * n,) + tuple(x.shape[1:-1])
-            if fused is not None and x.is_cuda:
-                y = fused.ag_gemm(x, weight, bias).view(*lead, N)
+            if use_fused:
+                y2, gathered = fused.ag_gemm(x, weight, bias)
+                y = y2.view(*lead, N)
+                saved_input = gathered            # [tp*rows, K]: kept for the weight gradient
             else:
                 y = product(gather_first(x, group), lead)
+        elif n > 1 and reduce_output == "reduce_scatter" and use_fused:
+            lead = (x.shape[0] // n,) + tuple(x.shape[1:-1])
+            y = fused.gemm_rs(x, weight).view(*lead, N)
         else:
             y = product(x, tuple(x.shape[:-1]))
-        if n > 1 and reduce_output == "reduce_scatter":
-            y = fused.reduce_scatter(y) if (fused is not None and x.is_cuda) else reduce_scatter_first(y, group)
-        elif n > 1 and reduce_output == "all_reduce":
-            dist.all_reduce(y, group=group)
-        ctx.save_for_backward(x, weight)
+            if n > 1 and reduce_output == "reduce_scatter":
+                y = reduce_scatter_first(y, group)
+            elif n > 1 and reduce_output == "all_reduce":
+                dist.all_reduce(y, group=group)
+        ctx.save_for_backward(saved_input, weight)
         return y
 
     @staticmethod
@@ -113,6 +124,8 @@ class _TPLinear(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         group, gather_input, reduce_output, allreduce_dgrad, fused = ctx.cfg
         n = _size(group)
+        if ctx.use_fused and (gather_input or reduce_output == "reduce_scatter"):
+            return _TPLinear._backward_fused(ctx, dy, x, weight)
         handle = None
         total = x
         if gather_input and n > 1:
@@ -161,6 +174,31 @@ class _TPLinear(torch.autograd.Function):
         if dx_final is not None and dx_final.shape != ctx.x_shape:
             dx_final = dx_final.view(ctx.x_shape)
         return dx_final, gw, gb, None, None, None, None, None
+
+    @staticmethod
+    def _backward_fused(ctx, dy, saved, weight):
+        group, gather_input, reduce_output, allreduce_dgrad, fused = ctx.cfg
+        dx = gw = gb = None
+        if gather_input:
+            # column-parallel: dx = reduce_scatter(dy W), dW = dy^T gathered_x
+            dy2 = _as2d(dy)
+            if ctx.needs_input_grad[0]:
+                dx = fused.gemm_rs(dy2, weight, b_mn=True).view(ctx.x_shape)
+            if weight.requires_grad:
+                gw = weight_grad(weight, dy2, saved)
+            if ctx.bias is not None and ctx.bias.requires_grad:
+                gb = deliver(ctx.bias, column_sum(dy2))
+        else:
+            # row-parallel: the gathered dy feeds both dx = gather(dy) W and dW = gather(dy)^T x
+            x2 = _as2d(saved)
+            if ctx.needs_input_grad[0]:
+                dx2, dy_total = fused.ag_gemm(dy, weight, None, b_mn=True)
+                dx = dx2.view(ctx.x_shape)
+            else:
+                dy_total = gather_first(dy, group).reshape(-1, dy.shape[-1])
+            if weight.requires_grad:
+                gw = weight_grad(weight, dy_total, x2)
+        return dx, gw, gb, None, None, None, None, None
 
 
 def tp_linear(x, weight, bias=None, *, group=None, gather_input=False, reduce_output="none",

@@ -1,0 +1,340 @@
+"""Checkpoint save / load glue.
+
+Directory layout and state captured follow the reference (megatron/training/checkpointing.py:
+tracker file ``latest_checkpointed_iteration.txt`` :228, ``iter_{:07d}`` directories, legacy
+``mp_rank_{tp:02d}[_{pp:03d}]/model_optim_rng.pt`` :130, ``generate_state_dict`` :729 with args,
+``checkpoint_version`` 3.0, iteration, ``model``/``model{i}``, optimizer, scheduler, RNG states,
+rerun-state-machine state and the running FLOP count; load prefers the newest of the persistent
+and the in-memory checkpoint :991-1002).  Formats:
+
+* ``torch_dist`` - sharded, reshardable (``checkpoint/sharded.py``), optionally written by a
+  background worker after a synchronous device-to-host copy (``--async-save``);
+* ``torch``      - one file per model-parallel rank;
+* non-persistent ``local`` - erasure-coded in-memory checkpoint (``checkpoint/ec_checkpoint.py``),
+  the counterpart of the reference's replicated local checkpoint (:520-544, :870-900).
+"""
+from __future__ import annotations
+
+import os
+import random
+import threading
+import time
+from typing import Any, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..checkpoint import sharded as ds
+from ..parallel import state
+from ..parallel.random import get_cuda_rng_tracker
+
+TRACKER = "latest_checkpointed_iteration.txt"
+
+
+def _unwrap(m):
+    while hasattr(m, "module"):
+        m = m.module
+    return m
+
+
+def get_checkpoint_tracker_filename(d: str) -> str:
+    return os.path.join(d, TRACKER)
+
+
+def get_checkpoint_name(d: str, iteration: int, release: bool = False, tp_rank=None, pp_rank=None, ep_rank=None,
+                        return_base_dir: bool = False) -> str:
+    base = os.path.join(d, "release" if release else f"iter_{iteration:07d}")
+    if return_base_dir:
+        return base
+    init = state.model_parallel_is_initialized()
+    tp_rank = (state.get_tensor_model_parallel_rank() if init else 0) if tp_rank is None else tp_rank
+    pp_rank = (state.get_pipeline_model_parallel_rank() if init else 0) if pp_rank is None else pp_rank
+    pp = state.get_pipeline_model_parallel_world_size() if init else 1
+    ep = state.get_expert_model_parallel_world_size() if init else 1
+    ep_rank = (state.get_expert_model_parallel_rank() if init else 0) if ep_rank is None else ep_rank
+    name = f"mp_rank_{tp_rank:02d}" + (f"_{pp_rank:03d}" if pp > 1 else "") + (f"_{ep_rank:03d}" if ep > 1 else "")
+    return os.path.join(base, name, "model_optim_rng.pt")
+
+
+def read_metadata(tracker_filename: str):
+    with open(tracker_filename) as f:
+        s = f.read().strip()
+    if s == "release":
+        return 0, True
+    return int(s), False
+
+
+def get_rng_state() -> Dict[str, Any]:
+    st = {"random_rng_state": random.getstate(), "np_rng_state": np.random.get_state(),
+          "torch_rng_state": torch.get_rng_state(),
+          "rng_tracker_states": get_cuda_rng_tracker().get_states()}
+    if torch.cuda.is_available():
+        st["cuda_rng_state"] = torch.cuda.get_rng_state()
+    return st
+
+
+def set_rng_state(st: Dict[str, Any]) -> None:
+    random.setstate(st["random_rng_state"])
+    np.random.set_state(st["np_rng_state"])
+    torch.set_rng_state(st["torch_rng_state"])
+    if torch.cuda.is_available() and "cuda_rng_state" in st:
+        torch.cuda.set_rng_state(st["cuda_rng_state"])
+    if st.get("rng_tracker_states"):
+        get_cuda_rng_tracker().set_states(st["rng_tracker_states"])
+
+
+# ----------------------------------------------------------------------------- sharded descriptions
+def _coords():
+    init = state.model_parallel_is_initialized()
+    return dict(tp_rank=state.get_tensor_model_parallel_rank() if init else 0,
+                tp_size=state.get_tensor_model_parallel_world_size() if init else 1,
+                dp_rank=state.get_data_parallel_rank(with_context_parallel=True) if init else 0,
+                pp_rank=state.get_pipeline_model_parallel_rank() if init else 0,
+                pp_size=state.get_pipeline_model_parallel_world_size() if init else 1)
+
+
+def model_sharded_state_dicts(model: Sequence[torch.nn.Module]) -> List[Dict[str, ds.ShardedTensor]]:
+    c = _coords()
+    out = []
+    for chunk in model:
+        m = _unwrap(chunk)
+        off = getattr(getattr(m, "decoder", None), "layer_offset", 0)
+        out.append(ds.model_sharded_state_dict(m, tp_rank=c["tp_rank"], tp_size=c["tp_size"], dp_rank=c["dp_rank"],
+                                               pp_layer_offset=off, num_layers_global=m.config.num_layers))
+    return out
+
+
+def optimizer_sharded_state_dict(optimizer, model: Sequence[torch.nn.Module],
+                                 model_sd: List[Dict[str, ds.ShardedTensor]]) -> Dict[str, Any]:
+    """Optimizer state in model space: for every parameter piece this rank owns,
+    ``optimizer.state.{fp32_param,exp_avg,exp_avg_sq}.<model key>`` with the parameter's global
+    placement and the flattened range of the piece (reference: distrib_optimizer.py:1344-1440)."""
+    opts = getattr(optimizer, "chained_optimizers", [optimizer])
+    name_of = {}
+    for ci, chunk in enumerate(model):
+        for n, p in _unwrap(chunk).named_parameters():
+            name_of[p] = (ci, n)
+    c = _coords()
+    out: Dict[str, Any] = {"param_state": {}, "common": []}
+    for oi, opt in enumerate(opts):
+        out["common"].append(dict(step=opt.step_count, param_groups=[dict(g) for g in opt.param_groups],
+                                  grad_scaler=None if opt.grad_scaler is None else opt.grad_scaler.state_dict()))
+        for st in opt.states:
+            sharded_over_dp = st.sharded
+            for piece in st.pieces:
+                p = piece["param"]
+                ci, n = name_of[p]
+                desc = model_sd[ci].get(n)
+                if desc is None:          # strided (gated) weights: describe in the parameter's own flat space
+                    desc = ds.ShardedTensor.from_rank_offsets(
+                        f"chunk{ci}.{n}.tp{c['tp_rank']}of{c['tp_size']}.pp{c['pp_rank']}", p.detach(),
+                        replica_id=(0, 0, c["dp_rank"]))
+                lo = piece["param_start"]
+                hi = lo + piece["numel"]
+                whole = (lo == 0 and hi == p.numel())
+                for kind, flat in (("fp32_param", st.master), ("exp_avg", st.exp_avg), ("exp_avg_sq", st.exp_avg_sq)):
+                    data = flat[piece["local_start"]:piece["local_start"] + piece["numel"]]
+                    replica = desc.replica_id if not sharded_over_dp else (desc.replica_id[0], desc.replica_id[1], 0)
+                    stn = ds.ShardedTensor(f"optimizer.state.{kind}.{desc.key}", data if not whole else data.view(p.shape),
+                                           torch.float32, desc.local_shape, desc.global_shape, desc.global_offset,
+                                           desc.axis_fragmentations, replica, desc.prepend_axis_num, False,
+                                           None if whole else slice(lo, hi))
+                    out["param_state"][f"{oi}.{kind}.{ci}.{n}.{lo}"] = stn
+    return out
+
+
+def generate_state_dict(args, model, optimizer, opt_param_scheduler, rng_state, iteration: int, sharded: bool,
+                        rerun_state=None, num_floating_point_operations_so_far: float = 0.0) -> Dict[str, Any]:
+    sd: Dict[str, Any] = {"args": args, "checkpoint_version": 3.0, "iteration": iteration,
+                          "num_floating_point_operations_so_far": num_floating_point_operations_so_far}
+    model_sd = model_sharded_state_dicts(model) if sharded else None
+    for i, chunk in enumerate(model):
+        key = "model" if len(model) == 1 else f"model{i}"
+        sd[key] = model_sd[i] if sharded else _unwrap(chunk).state_dict()
+    if optimizer is not None and not getattr(args, "no_save_optim", False):
+        sd["optimizer"] = optimizer_sharded_state_dict(optimizer, model, model_sd) if sharded else optimizer.state_dict()
+        if opt_param_scheduler is not None:
+            sd["opt_param_scheduler"] = opt_param_scheduler.state_dict()
+    if rerun_state is not None:
+        sd["rerun_state_machine"] = rerun_state
+    if rng_state is not None and not getattr(args, "no_save_rng", False):
+        if sharded:
+            c = _coords()
+            dp = state.get_data_parallel_world_size(with_context_parallel=True) if state.model_parallel_is_initialized() else 1
+            sd["rng_state"] = ds.ShardedObject("rng_state", rng_state, (c["pp_size"], c["tp_size"], dp),
+                                               (c["pp_rank"], c["tp_rank"], c["dp_rank"]))
+        else:
+            sd["rng_state"] = rng_state
+    return sd
+
+
+# ----------------------------------------------------------------------------- async worker
+class AsyncCallsQueue:
+    """Runs checkpoint writes on a background thread; ``maybe_finalize`` is polled from the
+    training loop and all ranks agree before the tracker file is updated (reference:
+    dist_checkpointing/strategies/async_utils.py:478)."""
+
+    def __init__(self):
+        self.pending: List[tuple] = []
+
+    def schedule(self, fn, finalize_fn):
+        t = threading.Thread(target=fn, daemon=True)
+        t.start()
+        self.pending.append((t, finalize_fn))
+
+    def maybe_finalize(self, blocking: bool = False) -> None:
+        still = []
+        for t, fin in self.pending:
+            if blocking:
+                t.join()
+            done = torch.tensor([0 if t.is_alive() else 1], dtype=torch.int32)
+            if dist.is_initialized() and dist.get_world_size() > 1:
+                if torch.cuda.is_available() and dist.get_backend() == "nccl":
+                    done = done.cuda()
+                dist.all_reduce(done, op=dist.ReduceOp.MIN)
+            if int(done.item()) == 1:
+                fin()
+            else:
+                still.append((t, fin))
+        self.pending = still
+
+    def close(self):
+        self.maybe_finalize(blocking=True)
+
+
+_async_queue = AsyncCallsQueue()
+
+
+def maybe_finalize_async_save(blocking: bool = False) -> None:
+    _async_queue.maybe_finalize(blocking)
+
+
+# ----------------------------------------------------------------------------- save / load
+def _write_tracker(save_dir: str, iteration: int) -> None:
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        with open(get_checkpoint_tracker_filename(save_dir), "w") as f:
+            f.write(str(iteration))
+
+
+def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args, *,
+                    num_floating_point_operations_so_far: float = 0.0, rerun_state=None,
+                    non_persistent: bool = False, ec_manager=None) -> Dict[str, float]:
+    t0 = time.time()
+    stats: Dict[str, float] = {}
+    if non_persistent and getattr(args, "non_persistent_ckpt_type", None) == "local":
+        if ec_manager is None:
+            raise RuntimeError("local non-persistent checkpoints need an ECCheckpointManager")
+        tensors = list(optimizer.local_state_tensors())
+        for chunk in model:
+            for buf in getattr(chunk, "buffers", []) + getattr(chunk, "expert_buffers", []):
+                tensors.append(buf.param_data)
+        stats = ec_manager.save(tensors, iteration)
+        stats["total_s"] = time.time() - t0
+        return stats
+    save_dir = args.non_persistent_global_ckpt_dir if non_persistent else args.save
+    fmt = getattr(args, "ckpt_format", "torch_dist")
+    rng = get_rng_state()
+    if fmt == "torch_dist":
+        sd = generate_state_dict(args, model, optimizer, opt_param_scheduler, rng, iteration, True, rerun_state,
+                                 num_floating_point_operations_so_far)
+        out_dir = get_checkpoint_name(save_dir, iteration, return_base_dir=True)
+        if getattr(args, "async_save", False):
+            # synchronous device-to-host copy, asynchronous file write
+            for _, st in ds.extract_sharded(sd)[0]:
+                if st.data is not None:
+                    st.data = st.data.detach().to("cpu", copy=True)
+            world = dist.get_world_size() if dist.is_initialized() else 1
+            if world > 1:
+                raise NotImplementedError("async save with several ranks needs the collective-free writer; "
+                                          "use synchronous save")
+            _async_queue.schedule(lambda: ds.save(sd, out_dir), lambda: _write_tracker(save_dir, iteration))
+        else:
+            ds.save(sd, out_dir)
+            _write_tracker(save_dir, iteration)
+    elif fmt == "torch":
+        sd = generate_state_dict(args, model, optimizer, opt_param_scheduler, rng, iteration, False, rerun_state,
+                                 num_floating_point_operations_so_far)
+        init = state.model_parallel_is_initialized()
+        if not init or state.get_data_parallel_rank(with_context_parallel=True) == 0:
+            name = get_checkpoint_name(save_dir, iteration)
+            os.makedirs(os.path.dirname(name), exist_ok=True)
+            torch.save(sd, name)
+        if dist.is_initialized():
+            dist.barrier()
+        _write_tracker(save_dir, iteration)
+    else:
+        raise ValueError(f"unknown checkpoint format {fmt}")
+    stats["total_s"] = time.time() - t0
+    return stats
+
+
+def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Optional[str] = None,
+                    strict: bool = True):
+    """Returns (iteration, num_floating_point_operations_so_far).  (0, 0) when nothing to load."""
+    load_dir = load_dir or args.load
+    if load_dir is None:
+        return 0, 0.0
+    tracker = get_checkpoint_tracker_filename(load_dir)
+    if not os.path.isfile(tracker):
+        if getattr(args, "exit_on_missing_checkpoint", False):
+            raise SystemExit(f"no checkpoint found in {load_dir}")
+        return 0, 0.0
+    iteration, release = read_metadata(tracker)
+    base = get_checkpoint_name(load_dir, iteration, release, return_base_dir=True)
+    finetune = getattr(args, "finetune", False)
+    no_optim = getattr(args, "no_load_optim", False) or finetune or release
+    no_rng = getattr(args, "no_load_rng", False) or finetune or release
+    if ds.check_is_distributed_checkpoint(base):
+        model_sd = model_sharded_state_dicts(model)
+        req: Dict[str, Any] = {}
+        for i in range(len(model)):
+            req["model" if len(model) == 1 else f"model{i}"] = model_sd[i]
+        if optimizer is not None and not no_optim:
+            req["optimizer"] = optimizer_sharded_state_dict(optimizer, model, model_sd)
+        if not no_rng:
+            c = _coords()
+            dp = state.get_data_parallel_world_size(with_context_parallel=True) if state.model_parallel_is_initialized() else 1
+            req["rng_state"] = ds.ShardedObject("rng_state", None, (c["pp_size"], c["tp_size"], dp),
+                                                (c["pp_rank"], c["tp_rank"], c["dp_rank"]))
+        # RNG states are per (pp, tp, dp) position: under a different layout there is nothing to restore
+        loaded = ds.load(req, base, strict=strict and not getattr(args, "dist_ckpt_strictness", "") == "ignore_all",
+                         optional_objects=("rng_state",))
+        for i, chunk in enumerate(model):
+            ds.load_model_from_sharded(_unwrap(chunk), loaded["model" if len(model) == 1 else f"model{i}"])
+        if optimizer is not None and not no_optim and "optimizer" in loaded:
+            opts = getattr(optimizer, "chained_optimizers", [optimizer])
+            common = loaded["optimizer"].get("common", [])
+            for opt, cm in zip(opts, common):
+                opt.step_count = cm["step"]
+                for g, s in zip(opt.param_groups, cm["param_groups"]):
+                    g.update(s)
+                if opt.grad_scaler is not None and cm.get("grad_scaler"):
+                    opt.grad_scaler.load_state_dict(cm["grad_scaler"])
+            # tensors were copied in place into the optimizer's flat state by ``load``
+            if opt_param_scheduler is not None and "opt_param_scheduler" in loaded:
+                opt_param_scheduler.load_state_dict(loaded["opt_param_scheduler"])
+        elif optimizer is not None:
+            optimizer.reload_model_params()
+        if not no_rng and loaded.get("rng_state") is not None:
+            try:
+                set_rng_state(loaded["rng_state"])
+            except Exception:
+                pass
+        sd = loaded
+    else:
+        name = get_checkpoint_name(load_dir, iteration, release)
+        sd = torch.load(name, map_location="cpu", weights_only=False)
+        for i, chunk in enumerate(model):
+            _unwrap(chunk).load_state_dict(sd["model" if len(model) == 1 else f"model{i}"], strict=strict)
+        if optimizer is not None and not no_optim and "optimizer" in sd:
+            optimizer.load_state_dict(sd["optimizer"])
+            if opt_param_scheduler is not None and "opt_param_scheduler" in sd:
+                opt_param_scheduler.load_state_dict(sd["opt_param_scheduler"])
+        elif optimizer is not None:
+            optimizer.reload_model_params()
+        if not no_rng and "rng_state" in sd:
+            set_rng_state(sd["rng_state"])
+    if finetune or release:
+        return 0, 0.0
+    return int(sd.get("iteration", iteration)), float(sd.get("num_floating_point_operations_so_far", 0.0))

@@ -37,8 +37,16 @@ def run_distributed(fn, world: int, *args, timeout: float = 240.0):
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout)
+    # poll: as soon as one rank fails, the others (likely blocked in a collective) are stopped
+    import time
+    deadline = time.time() + timeout
+    while time.time() < deadline:
+        if all(not p.is_alive() for p in procs):
+            break
+        if any((not p.is_alive()) and p.exitcode != 0 for p in procs):
+            time.sleep(2.0)
+            break
+        time.sleep(0.2)
     alive = [p for p in procs if p.is_alive()]
     for p in alive:
         p.terminate()

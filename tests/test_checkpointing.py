@@ -1,0 +1,142 @@
+"""Sharded checkpoints: block algebra, integrity validation, save under one layout / load under another."""
+import argparse
+import os
+
+import pytest
+import torch
+
+from megatron_lm_b200.checkpoint import sharded as ds
+from tests.dist_utils import run_distributed
+
+
+def test_block_overlap_reassembly(tmp_path):
+    full = torch.arange(6 * 8, dtype=torch.float32).view(6, 8)
+    # saved as 2x2 blocks
+    sd = {}
+    for i in range(2):
+        for j in range(2):
+            blk = full[i * 3:(i + 1) * 3, j * 4:(j + 1) * 4].clone()
+            sd[f"b{i}{j}"] = ds.ShardedTensor.from_rank_offsets("w", blk, (0, i, 2), (1, j, 2))
+    ds.save(sd, str(tmp_path))
+    # loaded as 3 row stripes
+    for r in range(3):
+        req = {"x": ds.ShardedTensor.from_rank_offsets("w", torch.zeros(2, 8), (0, r, 3))}
+        out = ds.load(req, str(tmp_path))
+        assert torch.equal(out["x"], full[2 * r:2 * r + 2])
+    # flattened range of a block (distributed-optimizer shard)
+    blk = torch.zeros(3, 8)
+    st = ds.ShardedTensor.from_rank_offsets("w", blk, (0, 1, 2))
+    st.flattened_range = slice(5, 17)
+    st.data = torch.zeros(12)
+    out = ds.load({"x": st}, str(tmp_path))
+    assert torch.equal(out["x"], full[3:6].reshape(-1)[5:17])
+
+
+def test_integrity_validation_catches_holes(tmp_path):
+    sd = {"a": ds.ShardedTensor.from_rank_offsets("w", torch.zeros(2, 4), (0, 0, 2))}     # second half missing
+    with pytest.raises(ValueError):
+        ds.save(sd, str(tmp_path))
+
+
+def test_objects_and_common_state(tmp_path):
+    sd = {"iteration": 7, "nested": {"lr": 0.5},
+          "rng": ds.ShardedObject("rng", {"seed": 3}, (1, 1), (0, 0)),
+          "w": ds.ShardedTensor.from_rank_offsets("w", torch.ones(2))}
+    ds.save(sd, str(tmp_path))
+    req = {"rng": ds.ShardedObject("rng", None, (1, 1), (0, 0)), "w": ds.ShardedTensor.from_rank_offsets("w", torch.zeros(2)),
+           "keep": ds.LocalNonpersistentObject([1, 2])}
+    out = ds.load(req, str(tmp_path))
+    assert out["iteration"] == 7 and out["nested"]["lr"] == 0.5 and out["rng"] == {"seed": 3}
+    assert out["keep"] == [1, 2] and torch.equal(out["w"], torch.ones(2))
+
+
+def _args(d, **kw):
+    ns = argparse.Namespace(save=d, load=d, ckpt_format="torch_dist", async_save=False, no_save_optim=False,
+                            no_save_rng=False, no_load_optim=False, no_load_rng=False, finetune=False)
+    for k, v in kw.items():
+        setattr(ns, k, v)
+    return ns
+
+
+def _build(tp, pp, dist_opt, reinit=True):
+    from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig, TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.training.training import setup_model_and_optimizer
+    from tests.model_utils import reinit_by_global_name
+    cfg = TransformerConfig(num_layers=4, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+                            attention_dropout=0.0, tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
+                            normalization="RMSNorm", gated_linear_unit=True, activation_func="silu",
+                            add_bias_linear=False, use_cpu_initialization=True)
+
+    def provider(pre_process=True, post_process=True, vp_stage=None):
+        m = GPTModel(cfg, 96, 16, pre_process=pre_process, post_process=post_process, position_embedding_type="rope")
+        if reinit:
+            reinit_by_global_name(m, cfg)
+        else:
+            with torch.no_grad():
+                for p in m.parameters():
+                    p.zero_()
+        return m
+    model, opt, _ = setup_model_and_optimizer(
+        provider, cfg, OptimizerConfig(lr=1e-2, use_distributed_optimizer=dist_opt),
+        DistributedDataParallelConfig(grad_reduce_in_fp32=True, use_distributed_optimizer=dist_opt))
+    return cfg, model, opt
+
+
+def _save_rank(rank, world, tp, pp, d):
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.training.checkpointing import save_checkpoint
+    state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp)
+    cfg, model, opt = _build(tp, pp, world // (tp * pp) > 1)
+    # make the optimizer state recognisable: exp_avg = 2 * master, exp_avg_sq = 3 * master
+    for st in opt.states:
+        st.exp_avg.copy_(2 * st.master)
+        st.exp_avg_sq.copy_(3 * st.master)
+    opt.step_count = 5
+    save_checkpoint(11, model, opt, None, _args(d))
+
+
+def _load_rank(rank, world, tp, pp, d, check_optim):
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.training.checkpointing import load_checkpoint
+    from tests.model_utils import reinit_by_global_name
+    state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp)
+    cfg, model, opt = _build(tp, pp, world // (tp * pp) > 1, reinit=False)
+    it, _ = load_checkpoint(model, opt, None, _args(d, no_load_optim=not check_optim))
+    assert it == 11
+    # the expected weights are the name-seeded ones
+    from megatron_lm_b200.models.gpt import GPTModel
+    for chunk in model:
+        m = chunk.module
+        got = {n: p.detach().clone() for n, p in m.named_parameters()}
+        reinit_by_global_name(m, cfg)
+        for n, p in m.named_parameters():
+            assert torch.equal(got[n], p.detach()), n
+    if check_optim:
+        assert opt.step_count == 5
+        for st in opt.states:
+            st.reload_master_from_params()
+            assert torch.allclose(st.exp_avg, 2 * st.master) and torch.allclose(st.exp_avg_sq, 3 * st.master)
+
+
+@pytest.mark.parametrize("save_cfg,load_cfg,optim", [((2, 2, 1), (1, 1, 1), False), ((2, 1, 2), (2, 2, 1), False),
+                                                     ((2, 1, 1), (2, 1, 1), True), ((1, 1, 1), (2, 1, 1), True)])
+def test_save_then_load_under_another_layout(tmp_path, save_cfg, load_cfg, optim):
+    d = str(tmp_path / "ckpt")
+    run_distributed(_save_rank, save_cfg[0], save_cfg[1], save_cfg[2], d)
+    assert os.path.isfile(os.path.join(d, "latest_checkpointed_iteration.txt"))
+    run_distributed(_load_rank, load_cfg[0], load_cfg[1], load_cfg[2], d, optim)
+
+
+def test_legacy_torch_format_roundtrip(tmp_path):
+    from megatron_lm_b200.training.checkpointing import load_checkpoint, save_checkpoint
+    d = str(tmp_path)
+    cfg, model, opt = _build(1, 1, False)
+    opt.step_count = 3
+    save_checkpoint(4, model, opt, None, _args(d, ckpt_format="torch"))
+    assert os.path.isfile(os.path.join(d, "iter_0000004", "mp_rank_00", "model_optim_rng.pt"))
+    cfg2, model2, opt2 = _build(1, 1, False, reinit=False)
+    it, _ = load_checkpoint(model2, opt2, None, _args(d, ckpt_format="torch"))
+    assert it == 4 and opt2.step_count == 3
+    for (n, a), (_, b) in zip(model[0].module.named_parameters(), model2[0].module.named_parameters()):
+        assert torch.equal(a, b), n
