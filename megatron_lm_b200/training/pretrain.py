@@ -1,0 +1,289 @@
+"""The training program: initialise, build model/optimizer/data, run the loop, log, checkpoint.
+
+Counterpart of the reference's ``pretrain`` / ``train`` / ``training_log`` (megatron/training/
+training.py:706, :2070, :1531) and ``initialize_megatron`` (initialize.py:38).  Scalar names in the
+log and on TensorBoard match the reference (``lm loss``, ``iteration-time``, ``learning-rate``,
+``grad-norm``, ``throughput`` in TFLOP/s/GPU by the reference's FLOP formula), so its result
+parsers keep working.
+"""
+from __future__ import annotations
+
+import os
+import signal
+import sys
+import time
+from datetime import timedelta
+from typing import Callable, Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..checkpoint.ec_checkpoint import ECCheckpointManager
+from ..data.tokenizer import build_tokenizer
+from ..parallel import state
+from ..parallel.random import model_parallel_cuda_manual_seed
+from ..utils.timers import Timers
+from . import checkpointing
+from .arguments import (core_transformer_config_from_args, ddp_config_from_args, optimizer_config_from_args,
+                        parse_args, set_args, validate_args)
+from .flops import flops_from_config
+from .resilience import DistributedSignalHandler, RerunStateMachine, StragglerDetector
+from .training import (evaluate, get_model, get_optimizer_param_scheduler, install_callbacks, train_step)
+from ..optimizer import get_megatron_optimizer
+
+_TIMERS: Optional[Timers] = None
+_WRITER = None
+
+
+def print_rank_0(msg: str) -> None:
+    if not dist.is_initialized() or dist.get_rank() == 0:
+        print(msg, flush=True)
+
+
+def print_rank_last(msg: str) -> None:
+    if not dist.is_initialized() or dist.get_rank() == dist.get_world_size() - 1:
+        print(msg, flush=True)
+
+
+def get_timers() -> Timers:
+    return _TIMERS
+
+
+def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unknown_args=False, argv=None):
+    """Parse arguments, start torch.distributed, build the parallel groups, seed the RNG streams."""
+    global _TIMERS, _WRITER
+    args = parse_args(extra_args_provider, ignore_unknown_args, argv)
+    if getattr(args, "yaml_cfg", None):
+        from .arguments import load_yaml_args
+        args = load_yaml_args(args.yaml_cfg, args)
+    validate_args(args, args_defaults)
+    set_args(args)
+    use_cuda = torch.cuda.is_available() and args.distributed_backend == "nccl"
+    if use_cuda:
+        torch.cuda.set_device(args.local_rank)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        kw = dict(backend=args.distributed_backend if use_cuda else "gloo", world_size=args.world_size, rank=args.rank,
+                  timeout=timedelta(minutes=args.distributed_timeout_minutes))
+        if use_cuda:
+            kw["device_id"] = torch.device("cuda", args.local_rank)
+        dist.init_process_group(**kw)
+    state.initialize_model_parallel(
+        tensor_model_parallel_size=args.tensor_model_parallel_size,
+        pipeline_model_parallel_size=args.pipeline_model_parallel_size,
+        virtual_pipeline_model_parallel_size=args.virtual_pipeline_model_parallel_size,
+        context_parallel_size=args.context_parallel_size,
+        hierarchical_context_parallel_sizes=getattr(args, "hierarchical_context_parallel_sizes", None),
+        expert_model_parallel_size=args.expert_model_parallel_size,
+        expert_tensor_parallel_size=args.expert_tensor_parallel_size,
+        num_distributed_optimizer_instances=getattr(args, "num_distributed_optimizer_instances", 1),
+        nccl_communicator_config_path=getattr(args, "nccl_communicator_config_path", None),
+        distributed_timeout_minutes=args.distributed_timeout_minutes,
+        order="tp-cp-ep-dp-pp" if not getattr(args, "use_tp_pp_dp_mapping", False) else "tp-cp-ep-pp-dp",
+        create_gloo_process_groups=getattr(args, "enable_gloo_process_groups", True),
+        high_priority_stream_groups=getattr(args, "high_priority_stream_groups", None) or ())
+    seed = args.seed + 100 * state.get_pipeline_model_parallel_rank()
+    if getattr(args, "data_parallel_random_init", False):
+        seed += 10 * state.get_data_parallel_rank()
+    import random
+    import numpy as np
+    random.seed(seed)
+    np.random.seed(seed)
+    model_parallel_cuda_manual_seed(seed)
+    _TIMERS = Timers(args.timing_log_level, args.timing_log_option)
+    if getattr(args, "tensorboard_dir", None) and args.rank == args.world_size - 1:
+        try:
+            from torch.utils.tensorboard import SummaryWriter
+            _WRITER = SummaryWriter(log_dir=args.tensorboard_dir, max_queue=args.tensorboard_queue_size)
+        except Exception:
+            _WRITER = None
+    args.tokenizer = None
+    if getattr(args, "tokenizer_type", None):
+        args.tokenizer = build_tokenizer(args)
+    return args
+
+
+def cyclic_iter(it):
+    while True:
+        for x in it:
+            yield x
+
+
+def build_train_valid_test_data_iterators(provider: Callable, args):
+    """Only the first tensor-parallel rank reads data; the others receive it by broadcast."""
+    from ..data.gpt_dataset import build_pretraining_data_loader
+    train_iters = args.train_iters
+    eval_iters = (train_iters // args.eval_interval + 1) * args.eval_iters if args.eval_interval else 0
+    sizes = [train_iters * args.global_batch_size, eval_iters * args.global_batch_size,
+             args.eval_iters * args.global_batch_size]
+    train_it = valid_it = test_it = None
+    if state.get_tensor_model_parallel_rank() == 0:
+        train_ds, valid_ds, test_ds = provider(sizes)
+        dp_rank, dp_size = state.get_data_parallel_rank(), state.get_data_parallel_world_size()
+        mk = lambda ds, consumed: build_pretraining_data_loader(ds, consumed, args.micro_batch_size, dp_rank, dp_size,
+                                                                args.dataloader_type or "single", args.num_workers,
+                                                                args.seed)
+        tl, vl, sl = mk(train_ds, args.consumed_train_samples), mk(valid_ds, 0), mk(test_ds, 0)
+        train_it = iter(tl) if tl is not None else None
+        valid_it = cyclic_iter(vl) if vl is not None else None
+        test_it = cyclic_iter(sl) if sl is not None else None
+    return train_it, valid_it, test_it
+
+
+def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: int, loss_scale: float, skipped: int,
+                 grad_norm, num_zeros, args, elapsed_per_iter: float, config, tokens_per_iter: int):
+    for k, v in loss_dict.items():
+        total_loss_dict[k] = total_loss_dict.get(k, 0.0) + float(v)
+    total_loss_dict["_n"] = total_loss_dict.get("_n", 0) + 1
+    total_loss_dict["_skipped"] = total_loss_dict.get("_skipped", 0) + skipped
+    if iteration % args.log_interval != 0:
+        return
+    n = max(total_loss_dict.pop("_n", 1) - total_loss_dict.get("_skipped", 0), 1)
+    skipped_tot = total_loss_dict.pop("_skipped", 0)
+    fl = flops_from_config(config, args.global_batch_size, args.seq_length, args.padded_vocab_size or 0)
+    throughput = fl / (elapsed_per_iter * 1e12 * args.world_size)
+    line = (f" iteration {iteration:8d}/{args.train_iters:8d} | consumed samples: {args.consumed_train_samples:12d} |"
+            f" elapsed time per iteration (ms): {elapsed_per_iter * 1000.0:.1f} |"
+            f" throughput per GPU (TFLOP/s/GPU): {throughput:.1f} |"
+            f" tokens/s/GPU: {tokens_per_iter / elapsed_per_iter / args.world_size:.1f} |"
+            f" learning rate: {lr:.6E} | global batch size: {args.global_batch_size:5d} |")
+    for k in list(total_loss_dict.keys()):
+        line += f" {k}: {total_loss_dict[k] / n:.6E} |"
+        if _WRITER is not None:
+            _WRITER.add_scalar(k, total_loss_dict[k] / n, iteration)
+        total_loss_dict[k] = 0.0
+    line += f" loss scale: {loss_scale:.1f} |"
+    if grad_norm is not None:
+        line += f" grad norm: {float(grad_norm):.3f} |"
+    if num_zeros is not None:
+        line += f" num zeros: {int(num_zeros)} |"
+    line += f" number of skipped iterations: {skipped_tot:3d} |"
+    if _WRITER is not None:
+        _WRITER.add_scalar("iteration-time", elapsed_per_iter, iteration)
+        _WRITER.add_scalar("learning-rate", lr, iteration)
+        _WRITER.add_scalar("throughput", throughput, iteration)
+        if grad_norm is not None:
+            _WRITER.add_scalar("grad-norm", float(grad_norm), iteration)
+        if torch.cuda.is_available():
+            _WRITER.add_scalar("mem-allocated-bytes", torch.cuda.memory_allocated(), iteration)
+            _WRITER.add_scalar("mem-max-allocated-bytes", torch.cuda.max_memory_allocated(), iteration)
+    print_rank_last(line)
+    if _TIMERS is not None:
+        _TIMERS.log(normalizer=args.log_interval)
+
+
+def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Callable, forward_step_func: Callable,
+             extra_args_provider=None, args_defaults=None, argv=None):
+    """Full program.  ``model_provider(pre_process, post_process, vp_stage=None)`` builds a model chunk;
+    ``forward_step_func(data_iterator, model)`` returns ``(output, loss_func)``."""
+    args = initialize_megatron(extra_args_provider, args_defaults, argv=argv)
+    timers = get_timers()
+    config = core_transformer_config_from_args(args)
+    ocfg, dcfg = optimizer_config_from_args(args), ddp_config_from_args(args)
+    timers("model-and-optimizer-setup", 0).start(barrier=True)
+    model = get_model(lambda **kw: model_provider(config=config, **kw), config, dcfg)
+    optimizer = get_megatron_optimizer(ocfg, model)
+    scheduler = get_optimizer_param_scheduler(
+        optimizer, lr=args.lr, min_lr=args.min_lr, lr_decay_style=args.lr_decay_style, train_iters=args.train_iters,
+        global_batch_size=args.global_batch_size, lr_decay_iters=args.lr_decay_iters,
+        lr_warmup_iters=args.lr_warmup_iters, lr_warmup_fraction=args.lr_warmup_fraction,
+        lr_warmup_init=args.lr_warmup_init, weight_decay=args.weight_decay,
+        start_weight_decay=args.start_weight_decay, end_weight_decay=args.end_weight_decay,
+        weight_decay_incr_style=args.weight_decay_incr_style, lr_wsd_decay_style=args.lr_wsd_decay_style,
+        lr_wsd_decay_iters=args.lr_wsd_decay_iters)
+    install_callbacks(config, model, optimizer)
+    if config.tp_comm_overlap and torch.cuda.is_available():
+        from ..ops.tp_fused import attach_fused_tp
+        attach_fused_tp(model, config, args.seq_length, args.micro_batch_size)
+    iteration, flops_so_far = 0, 0.0
+    if args.load is not None:
+        iteration, flops_so_far = checkpointing.load_checkpoint(model, optimizer, scheduler, args)
+        args.consumed_train_samples = iteration * args.global_batch_size
+    timers("model-and-optimizer-setup").stop()
+    ec_manager = None
+    if getattr(args, "non_persistent_ckpt_type", None) == "local":
+        grp = state.get_data_parallel_group(with_context_parallel=True)
+        ec_manager = ECCheckpointManager(grp, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes)
+    timers("train/valid/test-data-iterators-setup", 0).start(barrier=True)
+    train_it, valid_it, test_it = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args)
+    timers("train/valid/test-data-iterators-setup").stop()
+    timers.log(["model-and-optimizer-setup", "train/valid/test-data-iterators-setup"], barrier=True)
+    rerun = RerunStateMachine(mode=getattr(args, "rerun_mode", "disabled")) if getattr(args, "rerun_mode", "disabled") \
+        != "disabled" else None
+    sig = DistributedSignalHandler().__enter__() if getattr(args, "exit_signal_handler", False) else None
+    straggler = StragglerDetector() if getattr(args, "log_straggler", False) else None
+    dp = state.get_data_parallel_world_size()
+    nmb = args.global_batch_size // (args.micro_batch_size * dp)
+    total_loss: Dict = {}
+    start_time = time.time()
+    for m in model:
+        m.train()
+    t_last = time.time()
+    its = [train_it] * len(model) if len(model) > 1 else train_it
+    while iteration < args.train_iters:
+        checkpointing.maybe_finalize_async_save(blocking=False)
+        if getattr(args, "profile", False) and iteration == args.profile_step_start and torch.cuda.is_available() \
+                and args.rank in (args.profile_ranks or [0]):
+            torch.cuda.cudart().cudaProfilerStart()
+        loss_dict, skipped, grad_norm, zeros = train_step(
+            forward_step_func, its, model, optimizer, scheduler, config, num_microbatches=nmb,
+            seq_length=args.seq_length, micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size,
+            rerun_state_machine=rerun)
+        iteration += 1
+        args.iteration = iteration
+        args.consumed_train_samples += args.global_batch_size
+        flops_so_far += flops_from_config(config, args.global_batch_size, args.seq_length, args.padded_vocab_size or 0)
+        if iteration % args.log_interval == 0:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            now = time.time()
+            elapsed = (now - t_last) / args.log_interval
+            t_last = now
+        else:
+            elapsed = 0.0
+        lr = optimizer.param_groups[0]["lr"]
+        training_log(loss_dict, total_loss, lr, iteration, float(optimizer.get_loss_scale()), skipped, grad_norm, zeros,
+                     args, max(elapsed, 1e-9), config, args.global_batch_size * args.seq_length)
+        if straggler is not None and iteration % args.log_interval == 0:
+            straggler.report(iteration)
+        if getattr(args, "profile", False) and iteration == args.profile_step_end and torch.cuda.is_available():
+            torch.cuda.cudart().cudaProfilerStop()
+        if args.eval_interval and iteration % args.eval_interval == 0 and valid_it is not None:
+            res = evaluate(forward_step_func, valid_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
+                           seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
+            print_rank_last(f" validation loss at iteration {iteration} | " +
+                            " | ".join(f"{k} value: {v:.6E}" for k, v in res.items()))
+        if ec_manager is not None and args.non_persistent_save_interval and \
+                iteration % args.non_persistent_save_interval == 0:
+            st = checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args, non_persistent=True,
+                                               ec_manager=ec_manager)
+            print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: "
+                         f"{st.get('encode_GBps', 0.0):.2f} GB/s encode, {st.get('total_s', 0.0):.3f} s")
+        exiting = False
+        if sig is not None and any(sig.signals_received()):
+            exiting = True
+        if getattr(args, "exit_interval", None) and iteration % args.exit_interval == 0:
+            exiting = True
+        if getattr(args, "exit_duration_in_mins", None) and (time.time() - start_time) / 60.0 > args.exit_duration_in_mins:
+            exiting = True
+        if args.save and ((args.save_interval and iteration % args.save_interval == 0) or exiting):
+            timers("save-checkpoint", 0).start(barrier=True)
+            checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args,
+                                          num_floating_point_operations_so_far=flops_so_far)
+            timers("save-checkpoint").stop(barrier=True)
+            timers.log(["save-checkpoint"])
+        if exiting:
+            print_rank_0(f"exiting program at iteration {iteration}")
+            break
+    checkpointing.maybe_finalize_async_save(blocking=True)
+    if args.save and iteration % max(args.save_interval or 1, 1) != 0 and iteration > 0:
+        checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args,
+                                      num_floating_point_operations_so_far=flops_so_far)
+    if test_it is not None and args.eval_iters:
+        res = evaluate(forward_step_func, test_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
+                       seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
+        print_rank_last(" test loss | " + " | ".join(f"{k} value: {v:.6E}" for k, v in res.items()))
+    if _WRITER is not None:
+        _WRITER.flush()
+    return model, optimizer, scheduler

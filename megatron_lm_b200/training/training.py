@@ -112,18 +112,23 @@ def train_step(forward_step_func, data_iterator, model: Sequence[torch.nn.Module
                global_batch_size: Optional[int] = None, rerun_state_machine=None):
     """One optimizer step.  Returns (loss dict, skipped_iter, grad_norm, num_zeros_in_grad)."""
     fb = get_forward_backward_func()
-    while True:
+
+    def run_once():
         for m in model:
             if hasattr(m, "zero_grad_buffer"):
                 m.zero_grad_buffer()
         optimizer.zero_grad()
-        if rerun_state_machine is not None and not rerun_state_machine.should_run_forward_backward(data_iterator):
-            break
-        losses = fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=list(model),
-                    num_microbatches=num_microbatches, seq_length=seq_length, micro_batch_size=micro_batch_size,
-                    forward_only=False)
-        if rerun_state_machine is None:
-            break
+        return fb(forward_step_func=forward_step_func, data_iterator=data_iterator, model=list(model),
+                  num_microbatches=num_microbatches, seq_length=seq_length, micro_batch_size=micro_batch_size,
+                  forward_only=False)
+
+    if rerun_state_machine is None:
+        losses = run_once()
+    else:
+        # normally one pass; a suspicious result makes every rank replay the step
+        losses = []
+        while rerun_state_machine.should_run_forward_backward(data_iterator):
+            losses = run_once()
     ok, grad_norm, zeros = optimizer.step()
     skipped = 0 if ok else 1
     if ok and opt_param_scheduler is not None:

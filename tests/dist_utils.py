@@ -34,7 +34,7 @@ def run_distributed(fn, world: int, *args, timeout: float = 240.0):
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     # poll: as soon as one rank fails, the others (likely blocked in a collective) are stopped
@@ -50,6 +50,10 @@ def run_distributed(fn, world: int, *args, timeout: float = 240.0):
     alive = [p for p in procs if p.is_alive()]
     for p in alive:
         p.terminate()
+    for p in alive:
+        p.join(10)
+        if p.is_alive():
+            p.kill()
     msgs = []
     while not errq.empty():
         msgs.append(errq.get())

@@ -31,11 +31,11 @@ def _entry(rank, world, port, fn, args, errq):
         raise
 
 
-def run_on_gpus(fn, world: int, *args, timeout: float = 600.0):
+def run_on_gpus(fn, world: int, *args, timeout: float = 180.0):
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq), daemon=True) for r in range(world)]
     for p in procs:
         p.start()
     # poll: as soon as one rank fails, the others (likely blocked in a collective) are stopped
@@ -51,6 +51,10 @@ def run_on_gpus(fn, world: int, *args, timeout: float = 600.0):
     alive = [p for p in procs if p.is_alive()]
     for p in alive:
         p.terminate()
+    for p in alive:
+        p.join(10)
+        if p.is_alive():
+            p.kill()
     msgs = []
     while not errq.empty():
         msgs.append(errq.get())
