@@ -1,0 +1,87 @@
+// Erasure-code parity over GF(2^8) (polynomial 0x11d) as a multiply-XOR reduction over up to 16
+// source buffers that may live on this GPU or on peers (plain loads through peer-mapped pointers):
+//     dst_i = XOR_j coef[i][j] * src_j        i < m <= 4,  j < k <= 16
+// Encoding uses the generator rows, decoding the rows of the inverted survivor matrix - same kernel.
+// Bytes are processed four to a 32-bit word: multiplication by the constant 2 ("xtime") is
+//     ((x & 0x7f7f7f7f) << 1) ^ (((x >> 7) & 0x01010101) * 0x1d)
+// and a product by c is the XOR of the x * 2^b for the set bits b of c; the chain of doublings of a
+// source word is computed once and shared by all m outputs.  Coefficients are launch parameters,
+// so every branch on them is uniform.  The reference has no erasure coding (its in-memory
+// checkpoint replicates: megatron/training/checkpointing.py:520-544); this is new functionality.
+#include "common.cuh"
+
+namespace mlb {
+
+constexpr int kEcMaxK = 16, kEcMaxM = 4;
+
+struct EcParams {
+  const uint4* src[kEcMaxK];
+  uint4* dst[kEcMaxM];
+  uint8_t coef[kEcMaxM][kEcMaxK];
+  int k, m;
+  int all_ones;            // every coefficient is 0 or 1: pure XOR, no field multiplications
+  size_t nvec;             // 16-byte vectors per buffer
+};
+
+__device__ __forceinline__ uint32_t xtime4(uint32_t x) {
+  return ((x & 0x7f7f7f7fu) << 1) ^ (((x >> 7) & 0x01010101u) * 0x1du);
+}
+
+__global__ void __launch_bounds__(256)
+ec_apply_kernel(const EcParams p) {
+  for (size_t v = blockIdx.x * (size_t)blockDim.x + threadIdx.x; v < p.nvec; v += (size_t)gridDim.x * blockDim.x) {
+    uint32_t acc[kEcMaxM][4];
+#pragma unroll
+    for (int i = 0; i < kEcMaxM; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0u; }
+    for (int j = 0; j < p.k; ++j) {
+      const uint4 raw = p.src[j][v];
+      uint32_t x[4] = {raw.x, raw.y, raw.z, raw.w};
+      if (p.all_ones) {
+#pragma unroll
+        for (int i = 0; i < kEcMaxM; ++i)
+          if (i < p.m && p.coef[i][j]) { acc[i][0] ^= x[0]; acc[i][1] ^= x[1]; acc[i][2] ^= x[2]; acc[i][3] ^= x[3]; }
+      } else {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+#pragma unroll
+          for (int i = 0; i < kEcMaxM; ++i)
+            if (i < p.m && ((p.coef[i][j] >> b) & 1)) {
+              acc[i][0] ^= x[0]; acc[i][1] ^= x[1]; acc[i][2] ^= x[2]; acc[i][3] ^= x[3];
+            }
+          x[0] = xtime4(x[0]); x[1] = xtime4(x[1]); x[2] = xtime4(x[2]); x[3] = xtime4(x[3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kEcMaxM; ++i)
+      if (i < p.m) p.dst[i][v] = make_uint4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+  }
+}
+
+}  // namespace mlb
+
+using namespace mlb;
+
+// src: host array of k device addresses (16-byte aligned; local or peer-mapped); dst: host array of m local
+// addresses; coef: host array [m][k] row-major; nbytes: multiple of 16.
+MLB_API int mlb_ec_apply(const void* const* src, void* const* dst, const uint8_t* coef, int k, int m, long nbytes,
+                         int max_blocks, cudaStream_t st) {
+  if (k < 1 || k > kEcMaxK || m < 1 || m > kEcMaxM || nbytes <= 0 || (nbytes % 16)) return -3;
+  EcParams p = {};
+  p.k = k; p.m = m; p.nvec = (size_t)nbytes / 16; p.all_ones = 1;
+  for (int j = 0; j < k; ++j) {
+    if (reinterpret_cast<uintptr_t>(src[j]) & 15) return -3;
+    p.src[j] = reinterpret_cast<const uint4*>(src[j]);
+  }
+  for (int i = 0; i < m; ++i) {
+    if (reinterpret_cast<uintptr_t>(dst[i]) & 15) return -3;
+    p.dst[i] = reinterpret_cast<uint4*>(dst[i]);
+    for (int j = 0; j < k; ++j) { p.coef[i][j] = coef[i * k + j]; if (coef[i * k + j] > 1) p.all_ones = 0; }
+  }
+  size_t blocks = (p.nvec + 255) / 256;
+  size_t cap = max_blocks > 0 ? (size_t)max_blocks : (size_t)148 * 8;
+  if (blocks > cap) blocks = cap;
+  ec_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+  MLB_CHECK_LAUNCH();
+  return 0;
+}

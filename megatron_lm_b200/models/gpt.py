@@ -207,6 +207,8 @@ class GPTModel(nn.Module):
                 seq = ref.shape[0]
                 if cfg.sequence_parallel:
                     seq *= self.tp_size
+                if state.model_parallel_is_initialized():
+                    seq *= state.get_context_parallel_world_size()     # tables are built for the full sequence
                 off = 0
             dev = input_ids.device if input_ids is not None else ref.device
             rotary = self.rotary_pos_emb(seq, dev, off)

@@ -160,6 +160,9 @@ class SelfAttention(nn.Module):
         scale = config.softmax_scale if config.softmax_scale is not None else 1.0 / math.sqrt(self.hn)
         self.softmax_scale = scale
         self.recompute_core = config.recompute_granularity == "selective" and "core_attn" in config.recompute_modules
+        self.cp_size = state.get_context_parallel_world_size() if state.model_parallel_is_initialized() else 1
+        ct = config.cp_comm_type
+        self.cp_comm_type = (ct[(layer_number - 1) % len(ct)] if isinstance(ct, (list, tuple)) else ct) or "p2p"
 
     def _core(self, qkv5, cos=None, sin=None):
         rope = None if cos is None else (cos, sin)
@@ -175,6 +178,20 @@ class SelfAttention(nn.Module):
             k = self.k_layernorm(qkv5[:, :, :, self.qpg:self.qpg + 1].contiguous())
             qkv5 = torch.cat((q, k, qkv5[:, :, :, self.qpg + 1:]), dim=3)
         cos, sin = rotary if rotary is not None else (None, None)
+        if self.cp_size > 1 and inference_context is None:
+            # context parallel: q/k/v leave the fused buffer (K/V travel between ranks)
+            from ..parallel.context_parallel import context_parallel_attention
+            q = qkv5[:, :, :, :self.qpg].reshape(s, b, self.ng_local * self.qpg, self.hn)
+            k = qkv5[:, :, :, self.qpg]
+            v = qkv5[:, :, :, self.qpg + 1]
+            if cos is not None:
+                q = ops.apply_rope(q, cos, sin, self.config.rotary_interleaved)
+                k = ops.apply_rope(k, cos, sin, self.config.rotary_interleaved)
+            ctx_out = context_parallel_attention(q.reshape(s, b, self.ng_local, self.qpg, self.hn), k.contiguous(),
+                                                 v.contiguous(), self.cp_comm_type, scale=self.softmax_scale,
+                                                 causal=self.causal)
+            out, bias = self.linear_proj(ctx_out.reshape(s, b, self.np_local * self.hn))
+            return out, bias
         if inference_context is not None:
             if cos is not None:
                 qkv5 = _rope_copy(qkv5, cos, sin, self.config.rotary_interleaved) if qkv5.is_cuda else \

@@ -147,6 +147,75 @@ class _FusedQKVAttnFn(torch.autograd.Function):
         return dqkv, None, None, None, None, None
 
 
+# ----------------------------------------------------------------------------- raw forward / backward
+def attention_fwd_raw(q, k, v, causal: bool, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(o [sq, b, ng, qpg, d], lse [b, ng, qpg, sq] natural log) without autograd - the building block
+    of ring attention, which merges partial results by their log-sum-exp."""
+    sq, b, ng, qpg, d = q.shape
+    sk = k.shape[0]
+    if not q.is_cuda:
+        qf = q.float().permute(1, 2, 3, 0, 4)
+        kf = k.float().permute(1, 2, 0, 3).unsqueeze(2)
+        vf = v.float().permute(1, 2, 0, 3).unsqueeze(2)
+        s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        if causal:
+            i = torch.arange(sq).unsqueeze(1) + (sk - sq)
+            s = s.masked_fill(torch.arange(sk).unsqueeze(0) > i, float("-inf"))
+        lse = torch.logsumexp(s, dim=-1)
+        o = torch.matmul(torch.exp(s - lse.unsqueeze(-1)), vf)
+        return o.permute(3, 0, 1, 2, 4).to(q.dtype).contiguous(), lse
+    o = torch.empty(sq, b, ng, qpg, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, ng, qpg, sq, dtype=torch.float32, device=q.device)
+    st = _lib.status_word()
+    qs, ks, vs, os_ = q.stride(), k.stride(), v.stride(), o.stride()
+    _lib.check(_lib.lib().mlb_attn_fwd(
+        1 if q.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+        sq, sk, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2],
+        os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), st.data_ptr(), _lib.stream()), "attn_fwd")
+    return o, lse
+
+
+def attention_bwd_raw(q, k, v, o, do, lse, causal: bool, scale: float):
+    """(dq, dk, dv) of one attention block given the *final* output ``o`` and log-sum-exp ``lse`` of
+    the rows (which may come from a merge over several blocks)."""
+    sq, b, ng, qpg, d = q.shape
+    sk = k.shape[0]
+    if not q.is_cuda:
+        qf = q.float().permute(1, 2, 3, 0, 4)
+        kf = k.float().permute(1, 2, 0, 3).unsqueeze(2)
+        vf = v.float().permute(1, 2, 0, 3).unsqueeze(2)
+        dof = do.float().permute(1, 2, 3, 0, 4)
+        of = o.float().permute(1, 2, 3, 0, 4)
+        s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        if causal:
+            i = torch.arange(sq).unsqueeze(1) + (sk - sq)
+            s = s.masked_fill(torch.arange(sk).unsqueeze(0) > i, float("-inf"))
+        p = torch.exp(s - lse.unsqueeze(-1))
+        delta = (dof * of).sum(-1, keepdim=True)
+        dv = torch.matmul(p.transpose(-1, -2), dof).sum(2)                 # sum over q heads of the group
+        dp = torch.matmul(dof, vf.transpose(-1, -2))
+        ds = p * (dp - delta) * scale
+        dq = torch.matmul(ds, kf)
+        dk = torch.matmul(ds.transpose(-1, -2), qf).sum(2)
+        return (dq.permute(3, 0, 1, 2, 4).to(q.dtype).contiguous(), dk.permute(2, 0, 1, 3).to(q.dtype).contiguous(),
+                dv.permute(2, 0, 1, 3).to(q.dtype).contiguous())
+    do = do if do.stride(-1) == 1 else do.contiguous()
+    dq = torch.empty(sq, b, ng, qpg, d, dtype=q.dtype, device=q.device)
+    dk = torch.empty(sk, b, ng, d, dtype=q.dtype, device=q.device)
+    dv = torch.empty(sk, b, ng, d, dtype=q.dtype, device=q.device)
+    delta = torch.empty(b, ng, qpg, sq, dtype=torch.float32, device=q.device)
+    st = _lib.status_word()
+    qs, ks, vs, os_, dos = q.stride(), k.stride(), v.stride(), o.stride(), do.stride()
+    dqs, dks, dvs = dq.stride(), dk.stride(), dv.stride()
+    _lib.check(_lib.lib().mlb_attn_bwd(
+        1 if q.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+        lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), sq, sk, b, ng, qpg, d,
+        qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3],
+        dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3], dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2],
+        float(scale), int(causal), st.data_ptr(), _lib.stream()), "attn_bwd")
+    return dq, dk, dv
+
+
 def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
     """q [sq, b, ng, qpg, d], k/v [sk, b, ng, d] -> [sq, b, ng*qpg, d].  With ``causal`` the last
     query row attends to the last key (sq <= sk)."""

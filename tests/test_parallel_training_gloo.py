@@ -128,3 +128,57 @@ def test_data_parallel_matches(tmp_path, baseline, dist_opt):
 
 def test_tp2_pp2_sp_distopt(tmp_path, baseline):
     _close(_trajectory(tmp_path, 4, tp=2, pp=2, sp=True), baseline["llama"])
+
+
+def _run_cp(rank, world, cp, comm, out_path):
+    """Context-parallel training: every rank holds its zig-zag slice of each sequence."""
+    from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.parallel.context_parallel import zigzag_indices
+    from megatron_lm_b200.training.training import setup_model_and_optimizer, train_step
+    from tests.model_utils import reinit_by_global_name
+    state.initialize_model_parallel(context_parallel_size=cp)
+    cfg = _make_cfg(1, 1, None, False, "llama")
+    cfg.context_parallel_size = cp
+    cfg.cp_comm_type = comm
+
+    def provider(pre_process=True, post_process=True, vp_stage=None):
+        m = GPTModel(cfg, V, S, position_embedding_type="rope")
+        reinit_by_global_name(m, cfg)
+        return m
+    model, opt, _ = setup_model_and_optimizer(provider, cfg, OptimizerConfig(lr=5e-3, weight_decay=0.01, clip_grad=1.0),
+                                              DistributedDataParallelConfig(grad_reduce_in_fp32=True))
+    gen = torch.Generator().manual_seed(5)
+    data = torch.randint(0, V, (STEPS, NMB * B, S + 1), generator=gen)
+    idx = zigzag_indices(S, cp, state.get_context_parallel_rank())
+    losses = []
+    for step in range(STEPS):
+        def gen_it():
+            for i in range(NMB):
+                r = data[step][i * B:(i + 1) * B]
+                yield r[:, :-1][:, idx], r[:, 1:][:, idx]
+        it = gen_it()
+
+        def fwd(it_, m):
+            tok, lab = next(it_)
+            out = m(tok, labels=lab)
+
+            def lf(o):
+                tot = torch.stack([o.float().sum(), torch.tensor(float(o.numel()))])
+                torch.distributed.all_reduce(tot, group=state.get_context_parallel_group())
+                # the gradient of the cp-summed loss w.r.t. local tokens is that of the local sum
+                loss = o.float().sum() / tot[1]
+                return loss * cp, {"lm loss": (tot[0] / tot[1]).detach()}
+            return out, lf
+        l, _, gn, _ = train_step(fwd, it, model, opt, None, cfg, num_microbatches=NMB, seq_length=S, micro_batch_size=B)
+        losses.append((float(l["lm loss"]), float(gn)))
+    if rank == 0:
+        torch.save(losses, out_path)
+
+
+@pytest.mark.parametrize("comm", ["p2p", "a2a", "all_gather"])
+def test_context_parallel_matches(tmp_path, baseline, comm):
+    out = str(tmp_path / f"cp_{comm}.pt")
+    run_distributed(_run_cp, 2, 2, comm, out)
+    _close(torch.load(out), baseline["llama"])
