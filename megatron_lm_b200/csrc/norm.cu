@@ -246,3 +246,60 @@ MLB_API int mlb_norm_bwd(int dtype, int rms, const void* dy, const void* x, cons
   MLB_CHECK_LAUNCH();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in norm_noalloc.h).
+#include "norm_noalloc.h"
+#include <mutex>
+
+namespace mlb {
+constexpr int kNoAllocBlocks = 148;
+constexpr int kNoAllocMaxH = 8192;
+// Partial sums [kNoAllocBlocks][2][h].  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels are given the resolved device pointer.
+static __device__ __align__(256) float g_norm_noalloc_scratch[kNoAllocBlocks * 2 * kNoAllocMaxH];
+
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_ptr[kMaxDevices] = {};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device (resolved on first use per device).
+static int noalloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return MLB_NOALLOC_NO_SYMBOL;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return MLB_NOALLOC_NO_SYMBOL;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace mlb
+
+MLB_API int mlb_norm_bwd_noalloc_max_h(void) { return mlb::kNoAllocMaxH; }
+
+MLB_API int mlb_norm_bwd_noalloc(int dtype, int rms, const void* dy, const void* x, const void* gamma,
+                                 const float* mean, const float* rstd, void* dx, float* dgamma, float* dbeta,
+                                 int rows, int h, int zero_centered, int accumulate, cudaStream_t st) {
+  if (rows < 1 || h < 8 || (h % 8) != 0 || h > mlb::kNoAllocMaxH) return MLB_NOALLOC_BAD_SIZE;
+  if (dtype != MLB_F32 && dtype != MLB_BF16 && dtype != MLB_F16) return MLB_NOALLOC_BAD_DTYPE;
+  float* scratch = nullptr;
+  int rc = mlb::noalloc_scratch(&scratch);
+  if (rc) return rc;
+  const int grid = rows < mlb::kNoAllocBlocks ? rows : mlb::kNoAllocBlocks;
+  MLB_DISPATCH_ACT(dtype, T, {
+    rc = rms ? mlb::launch_bwd<T, true>(dy, x, gamma, mean, rstd, dx, scratch, rows, h, zero_centered, grid, st)
+             : mlb::launch_bwd<T, false>(dy, x, gamma, mean, rstd, dx, scratch, rows, h, zero_centered, grid, st);
+  });
+  if (rc) return rc;
+  mlb::norm_bwd_reduce_kernel<<<(h + 31) / 32, 256, 0, st>>>(scratch, grid, h, dgamma, rms ? nullptr : dbeta,
+                                                             accumulate);
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
