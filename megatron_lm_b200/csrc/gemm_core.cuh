@@ -14,11 +14,12 @@
 // * Communication modes (tensor parallelism with sequence parallelism, one launch per product):
 //     AG : the A operand is the all-gather of per-rank row shards.  The first ``n_comm`` CTAs pull the
 //          peers' shards over NVLink with bulk async copies (peer global -> shared -> local gathered
-//          buffer) and publish a flag per 128-row block; the GEMM CTAs walk row blocks in arrival order
-//          (own shard first) and their TMA producer waits on the block's flag.
+//          buffer) and publish a flag per 128-row block; the GEMM CTAs start on this rank's own rows (read
+//          in place through a second tensor map), then walk the peers' row blocks in arrival order, their
+//          TMA producer waiting on each block's flag.
 //     RS : D is reduce-scattered over ranks.  Row blocks owned by other ranks are computed first; the
-//          epilogue stores each partial tile straight into the owner's receive slot (peer stores) and
-//          bumps the owner's arrival counter; when a CTA runs out of tiles it sums the arrived slots of
+//          epilogue stages each partial tile in shared memory and TMA-stores it into the owner's receive
+//          slot (over NVLink for a peer), then bumps the owner's arrival counter; when a CTA runs out of tiles it sums the arrived slots of
 //          this rank's row blocks (+ optional residual) into the output.
 //   Every cross-rank wait is bounded and reports through the status word.
 //
@@ -59,6 +60,7 @@ struct CommParams {
   uint32_t* chunk_flags;            // local, one per row block
   uint32_t* peer_sig[kMaxPeers];    // every rank's signal words: ready[tp] then done[tp]
   uint32_t* comm_counter;           // local
+  uint32_t comm_target;             // cumulative worker completions that mean "this call's copies are all done"
   long shard_bytes;                 // rows_per_rank * K * 2
   // RS
   void* peer_recv[kMaxPeers];       // every rank's receive buffer [tp][rows_per_rank][N]
@@ -106,6 +108,11 @@ __device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
 }
 
+// Extra tensor maps of the communication modes.  AG: m[0] covers this rank's own [rows_per_rank, K] shard, so its
+// rows are multiplied straight from where they are.  RS: m[q] covers, inside rank q's receive buffer, the slot
+// [rows_per_rank, N] that belongs to this rank (32-row x 128-byte boxes, stored by the epilogue).
+struct ExtraMaps { CUtensorMap m[kMaxPeers]; };
+
 struct TileCoord { int m_blk, n_blk, owner, m_local; };
 __device__ __forceinline__ TileCoord map_tile(int tile, const GemmParams& p, const CommParams& c) {
   TileCoord t;
@@ -138,7 +145,8 @@ __device__ void ag_comm_cta(uint8_t* smem, uint64_t* bars, const GemmParams& p, 
   uint32_t base = 0;                     // pieces moved so far in this call (ring position / barrier parity)
   bool ok = true;
   for (int it = blockIdx.x; it < items && ok; it += c.n_comm) {
-    const int d = it / c.bpr, j = it % c.bpr;            // peers in arrival order: own shard first
+    // peers in the order the GEMM CTAs want them; the own shard (which the GEMM reads in place) goes last
+    const int d = (it / c.bpr + 1) % c.tp, j = it % c.bpr;
     const int q = (c.rank + d) % c.tp;
     if (q != c.rank && !wait_ge<true>(my_sig + q, c.seq, p.status, 41)) { ok = false; break; }
     const uint8_t* src = reinterpret_cast<const uint8_t*>(c.peer_x[q]) + (long)j * block_bytes;
@@ -174,7 +182,7 @@ __device__ void ag_comm_cta(uint8_t* smem, uint64_t* bars, const GemmParams& p, 
   // when every worker of this rank is done, tell the peers they may overwrite their shards
   __threadfence();
   const uint32_t prev = atomicAdd(c.comm_counter, 1u);
-  if (prev + 1u == c.seq * (uint32_t)c.n_comm)
+  if (prev + 1u == c.comm_target)
     for (int q = 0; q < c.tp; ++q) if (q != c.rank) st_release_sys(c.peer_sig[q] + c.tp + c.rank, c.seq);
   if (blockIdx.x == 0)
     for (int q = 0; q < c.tp; ++q) if (q != c.rank) wait_ge<true>(my_sig + c.tp + q, c.seq, p.status, 43);
@@ -202,7 +210,8 @@ template <int BN> struct GemmSmem {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmD, const GemmParams p, const CommParams cp) {
+            const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p,
+            const CommParams cp) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -253,7 +262,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
         const TileCoord tc = map_tile(tile, p, cp);
         const int m0 = tc.m_blk * BM, n0 = tc.n_blk * BN;
-        if (cp.mode == COMM_AG && tc.m_blk != ready_blk) {
+        const bool own_rows = cp.mode == COMM_AG && tc.owner == cp.rank;
+        if (cp.mode == COMM_AG && !own_rows && tc.m_blk != ready_blk) {
           // rows of this block arrive from a peer: wait for the worker's flag, then order the
           // async-proxy (TMA) reads after the acquired writes
           if (!wait_ge<false>(cp.chunk_flags + tc.m_blk, cp.seq, p.status, 5)) { *abort_flag = 1; ok = false; break; }
@@ -266,7 +276,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tma_load_2d(a_dst, &tmA, full(stage), k0, m0);                 // box [64 k, 128 rows]
+            if (own_rows) tma_load_2d(a_dst, &xm.m[0], full(stage), k0, tc.m_local * BM);
+            else tma_load_2d(a_dst, &tmA, full(stage), k0, m0);            // box [64 k, 128 rows]
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, full(stage), m0 + 64 * j, k0);
@@ -330,37 +341,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       fence_after_sync();
       const int row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-      if (cp.mode == COMM_RS) {
-        // ---- reduce-scatter epilogue: the partial tile goes to slot `rank` of the owner's receive buffer
-        // (a peer store over NVLink unless this rank owns the rows), then the owner's counter is bumped.
-        const int rows_per_rank = cp.bpr * BM;
-        uint16_t* recv = reinterpret_cast<uint16_t*>(cp.peer_recv[tc.owner]) +
-                         ((size_t)cp.rank * rows_per_rank + (size_t)tc.m_local * BM + quad * 32 + lane) * p.N;
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(t_row + (uint32_t)c, r);
-          tmem_wait_ld();
-          const int col = n0 + c;
-          if (col + 32 <= p.N) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              reinterpret_cast<uint4*>(recv + col)[q] =
-                  make_uint4(pack2(__uint_as_float(r[8 * q]), __uint_as_float(r[8 * q + 1]), p.lp_fmt),
-                             pack2(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]), p.lp_fmt),
-                             pack2(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]), p.lp_fmt),
-                             pack2(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]), p.lp_fmt));
-          }
-        }
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(cp.peer_cnt[tc.owner] + tc.m_local, 1u);
-      } else if (p.tma_out) {
+      if (p.tma_out) {
         // ---- staged epilogue: registers -> 128B-swizzled shared tile -> TMA store / add-reduce.
         // Each warp owns rows [quad*32, quad*32+32) of the tile and two private 4 KB buffers, so no
         // cross-warp synchronisation is needed; out-of-range rows/columns are clipped by the TMA.
+        // Reduce-scatter: the destination is this rank's slot in the row owner's receive buffer (a TMA store
+        // over NVLink unless this rank owns the rows); the owner's arrival counter is bumped once the
+        // warp's stores have completed.
         const int cw = (p.out_mode == OUT_LP) ? 64 : 32;          // columns per 128-byte staged row
         uint8_t* my_stage = sEpi + (warp - 2) * 8192;
+        const CUtensorMap* dmap = (cp.mode == COMM_RS) ? &xm.m[tc.owner] : &tmD;
+        const int drow = (cp.mode == COMM_RS) ? tc.m_local * BM + quad * 32 : m0 + quad * 32;
 #pragma unroll 1
         for (int c = 0; c < BN; c += cw) {
           uint32_t r0[32], r1[32];
@@ -399,11 +390,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           fence_async_smem();
           __syncwarp();
           if (lane == 0 && col < p.N && (m0 + quad * 32) < p.M) {
-            if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(&tmD, smem_u32(stage), col, m0 + quad * 32);
-            else tma_store_2d(&tmD, smem_u32(stage), col, m0 + quad * 32);
+            if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(dmap, smem_u32(stage), col, drow);
+            else tma_store_2d(dmap, smem_u32(stage), col, drow);
             bulk_commit();
           }
           epi_buf ^= 1;
+        }
+        if (cp.mode == COMM_RS && lane == 0) {
+          bulk_wait<0>();                      // this warp's 32 rows of the tile have landed in the owner's slot
+          fence_proxy_async_all();
+          __threadfence_system();
+          red_release_sys_add(cp.peer_cnt[tc.owner] + tc.m_local, 1u);
         }
       } else {
 #pragma unroll 1
@@ -470,42 +467,88 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (p.tma_out && warp >= 2 && lane == 0) bulk_wait<0>();     // staged stores have landed
   if (cp.mode == COMM_RS && warp >= 2) {
     // ---- reduce phase: sum the tp arrived slots of this rank's rows (+ residual) into the output.
-    // Work item = (row block, 256-column strip); the 128 epilogue threads move 16-byte vectors.
+    // The [rows_per_rank, N] output is cut into equal contiguous runs of 16-byte vectors, one run per CTA;
+    // a run waits for the arrival counter of each 128-row block as it enters it.
     const int rows_per_rank = cp.bpr * BM;
-    const int strips = (p.N + 255) / 256;
     const int et = threadIdx.x - 64;
     const uint16_t* recv = reinterpret_cast<const uint16_t*>(cp.peer_recv[cp.rank]);
-    for (int item = cta; item < cp.bpr * strips; item += n_cta) {
-      const int mb = item / strips, c0 = (item % strips) * 256;
-      if (!wait_ge<true>(cp.peer_cnt[cp.rank] + mb, cp.cnt_target, p.status, 6)) break;
-      const int cols = (p.N - c0) < 256 ? (p.N - c0) : 256;
-      const int vec_per_row = cols >> 3;
-      for (int v = et; v < BM * vec_per_row; v += 128) {
-        const int r = mb * BM + v / vec_per_row, cc = c0 + (v % vec_per_row) * 8;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < cp.tp; ++s) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(recv + ((size_t)s * rows_per_rank + r) * p.N + cc);
-          const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+    {
+      const int vec_per_row = p.N >> 3;
+      const long all_vec = (long)rows_per_rank * vec_per_row;
+      constexpr int U = 8;                     // vectors per thread per pass: U x 2 slot loads in flight
+      long per = (all_vec + n_cta - 1) / n_cta;
+      per = (per + 128 * U - 1) / (128 * U) * (128 * U);
+      const long run0 = (long)cta * per;
+      const long total = run0 + per < all_vec ? run0 + per : all_vec;
+      const int c0 = 0;
+      int ready_mb = run0 < all_vec ? (int)(run0 / vec_per_row / BM) - 1 : 0;
+      bool alive = true;
+      auto addv = [&](float* a, const uint4& raw) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            float2 f = p.lp_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]))
-                                : __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
-            acc[2 * k] += f.x; acc[2 * k + 1] += f.y;
+        for (int k = 0; k < 4; ++k) {
+          float2 f = p.lp_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]))
+                              : __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+          a[2 * k] += f.x; a[2 * k + 1] += f.y;
+        }
+      };
+      const int mb = 0;
+      for (long v0 = run0 + et; v0 - et < total && alive; v0 += 128 * U) {
+        {
+          const long last = (v0 - et + 128 * U - 1 < total - 1) ? v0 - et + 128 * U - 1 : total - 1;
+          const int mb_hi = (int)(last / vec_per_row / BM);
+          while (ready_mb < mb_hi) {
+            ++ready_mb;
+            if (!wait_ge<true>(cp.peer_cnt[cp.rank] + ready_mb, cp.cnt_target, p.status, 6)) { alive = false; break; }
           }
+          if (!alive) break;
+        }
+        float acc[U][8];
+        size_t off[U]; int rr[U], cc[U]; bool on[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long v = v0 + u * 128;
+          on[u] = v < total;
+          const long vv = on[u] ? v : run0;
+          rr[u] = mb * BM + (int)(vv / vec_per_row); cc[u] = c0 + (int)(vv % vec_per_row) * 8;
+          off[u] = (size_t)rr[u] * p.N + cc[u];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+        }
+        const size_t slot_stride = (size_t)rows_per_rank * p.N;
+        int s = 0;
+        for (; s + 1 < cp.tp; s += 2) {
+          uint4 r0[U], r1[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            r0[u] = *reinterpret_cast<const uint4*>(recv + (size_t)s * slot_stride + off[u]);
+            r1[u] = *reinterpret_cast<const uint4*>(recv + (size_t)(s + 1) * slot_stride + off[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) { addv(acc[u], r0[u]); addv(acc[u], r1[u]); }
+        }
+        if (s < cp.tp) {
+          uint4 r0[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) r0[u] = *reinterpret_cast<const uint4*>(recv + (size_t)s * slot_stride + off[u]);
+#pragma unroll
+          for (int u = 0; u < U; ++u) addv(acc[u], r0[u]);
         }
         if (cp.residual != nullptr) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(cp.residual) + (size_t)r * cp.ld_res + cc);
-          const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+          uint4 r0[U];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            float2 f = p.lp_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]))
-                                : __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
-            acc[2 * k] += f.x; acc[2 * k + 1] += f.y;
-          }
+          for (int u = 0; u < U; ++u)
+            r0[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(cp.residual) + (size_t)rr[u] * cp.ld_res + cc[u]);
+#pragma unroll
+          for (int u = 0; u < U; ++u) addv(acc[u], r0[u]);
         }
-        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cp.out) + (size_t)r * cp.ld_out + cc) =
-            make_uint4(pack2(acc[0], acc[1], p.lp_fmt), pack2(acc[2], acc[3], p.lp_fmt),
-                       pack2(acc[4], acc[5], p.lp_fmt), pack2(acc[6], acc[7], p.lp_fmt));
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (!on[u]) continue;
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cp.out) + (size_t)rr[u] * cp.ld_out + cc[u]) =
+              make_uint4(pack2(acc[u][0], acc[u][1], p.lp_fmt), pack2(acc[u][2], acc[u][3], p.lp_fmt),
+                         pack2(acc[u][4], acc[u][5], p.lp_fmt), pack2(acc[u][6], acc[u][7], p.lp_fmt));
+        }
       }
     }
   }
@@ -516,8 +559,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 template <int BN, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, GemmParams p,
-                       const CommParams& cp, int sm_count, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const ExtraMaps& xm,
+                       GemmParams p, const CommParams& cp, int sm_count, cudaStream_t st) {
   using S = GemmSmem<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
@@ -531,7 +574,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = tiles < sm_count ? tiles : sm_count;
   if (cp.mode == COMM_AG) grid = sm_count;          // workers + GEMM CTAs, all co-resident
-  kern<<<grid, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, p, cp);
+  kern<<<grid, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, xm, p, cp);
   MLB_CHECK_LAUNCH();
   return 0;
 }
@@ -539,7 +582,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 // Tensor maps for A (K- or MN-major), B and, when aligned, the output; then launch.
 static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B, long ldb, int b_mn, void* D,
                     long ldd, int out_mode, const void* bias, int M, int N, int K, int sms, int* status,
-                    const CommParams& cp, cudaStream_t st);
+                    const CommParams& cp, cudaStream_t st, const ExtraMaps* xm_in = nullptr);
 
 static int sm_count_cached() {
   static int n = 0;
@@ -554,7 +597,9 @@ static int sm_count_cached() {
 
 static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B, long ldb, int b_mn, void* D,
                     long ldd, int out_mode, const void* bias, int M, int N, int K, int sms, int* status,
-                    const CommParams& cp, cudaStream_t st) {
+                    const CommParams& cp, cudaStream_t st, const ExtraMaps* xm_in) {
+  static const ExtraMaps kNoMaps = {};
+  const ExtraMaps& xm = xm_in ? *xm_in : kNoMaps;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
   const int bn = (N > 128) ? 256 : 128;
   CUtensorMap tmA, tmB, tmD;
@@ -571,8 +616,11 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
     if ((rc = make_tmap(&tmB, B, 2, dims, strides, box))) return rc;
   }
   const int esz = (out_mode == OUT_LP) ? 2 : 4;
-  int tma_out = cp.mode != COMM_RS && (((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
-  if (tma_out) {
+  int tma_out = (((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
+  if (cp.mode == COMM_RS) {
+    tma_out = 1;                 // the epilogue stores through xm; tmD is unused
+    tmD = tmA;
+  } else if (tma_out) {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)ldd * esz};
     uint32_t box[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
     if (make_tmap(&tmD, D, 2, dims, strides, box, esz)) tma_out = 0;
@@ -582,7 +630,7 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
   p.tma_out = tma_out;
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
-#define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, tmD, p, cp, sms, st)
+#define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, tmD, xm, p, cp, sms, st)
   if (bn == 256) {
     if (!a_mn && !b_mn) GO(256, false, false);
     if (!a_mn && b_mn) GO(256, false, true);

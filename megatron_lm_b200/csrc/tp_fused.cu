@@ -11,9 +11,10 @@ using namespace mlb;
 // peer_x / peer_sig: host arrays of tp device addresses (symmetric-memory mappings, this rank's own included).
 // gathered: local [tp*rows_per_rank, K]; chunk_flags: local uint32[tp*rows_per_rank/128]; comm_counter: local uint32.
 // seq: 1, 2, 3, ... per call on this buffer set (flags and signals are monotonic, never reset).
+// comm_target: the sum of n_comm over all calls on this buffer set so far, this one included.
 MLB_API int mlb_ag_gemm(int lp_fmt, const void* const* peer_x, uint32_t* const* peer_sig, void* gathered,
                         uint32_t* chunk_flags, uint32_t* comm_counter, int rank, int tp, int rows_per_rank,
-                        unsigned seq, int n_comm, const void* B, long ldb, int b_mn, void* D, long ldd, int out_mode,
+                        unsigned seq, unsigned comm_target, int n_comm, const void* B, long ldb, int b_mn, void* D, long ldd, int out_mode,
                         const void* bias, int N, int K, int* status, cudaStream_t st) {
   if (tp < 2 || tp > kMaxPeers || rows_per_rank % BM || K % 8) return -7;
   const int sms = sm_count_cached();
@@ -21,10 +22,17 @@ MLB_API int mlb_ag_gemm(int lp_fmt, const void* const* peer_x, uint32_t* const* 
   CommParams cp = {};
   cp.mode = COMM_AG; cp.rank = rank; cp.tp = tp; cp.n_comm = n_comm; cp.bpr = rows_per_rank / BM; cp.seq = seq;
   for (int i = 0; i < tp; ++i) { cp.peer_x[i] = peer_x[i]; cp.peer_sig[i] = peer_sig[i]; }
-  cp.gathered = gathered; cp.chunk_flags = chunk_flags; cp.comm_counter = comm_counter;
+  cp.gathered = gathered; cp.chunk_flags = chunk_flags; cp.comm_counter = comm_counter; cp.comm_target = comm_target;
   cp.shard_bytes = (long)rows_per_rank * K * 2;
+  ExtraMaps xm = {};
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows_per_rank}, strides[1] = {(uint64_t)K * 2};
+    uint32_t box[2] = {BK, BM};
+    int rc = make_tmap(&xm.m[0], peer_x[rank], 2, dims, strides, box);
+    if (rc) return rc;
+  }
   return run_gemm(lp_fmt, gathered, K, 0, B, ldb, b_mn, D, ldd, out_mode, bias, tp * rows_per_rank, N, K, sms, status,
-                  cp, st);
+                  cp, st, &xm);
 }
 
 // A: local [tp*rows_per_rank, K] (a_mn = 0).  peer_recv[i]: rank i's receive buffer [tp][rows_per_rank][N];
@@ -39,8 +47,16 @@ MLB_API int mlb_gemm_rs(int lp_fmt, const void* A, long lda, const void* B, long
   cp.mode = COMM_RS; cp.rank = rank; cp.tp = tp; cp.bpr = rows_per_rank / BM; cp.cnt_target = cnt_target;
   for (int i = 0; i < tp; ++i) { cp.peer_recv[i] = peer_recv[i]; cp.peer_cnt[i] = peer_cnt[i]; }
   cp.residual = residual; cp.ld_res = ld_res; cp.out = out; cp.ld_out = ld_out;
+  ExtraMaps xm = {};
+  for (int q = 0; q < tp; ++q) {
+    const uint8_t* slot = reinterpret_cast<const uint8_t*>(peer_recv[q]) + (size_t)rank * rows_per_rank * N * 2;
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)rows_per_rank}, strides[1] = {(uint64_t)N * 2};
+    uint32_t box[2] = {64, 32};
+    int rc = make_tmap(&xm.m[q], slot, 2, dims, strides, box);
+    if (rc) return rc;
+  }
   return run_gemm(lp_fmt, A, lda, 0, B, ldb, b_mn, out /*unused*/, ld_out, OUT_LP, nullptr, tp * rows_per_rank, N, K,
-                  sm_count_cached(), status, cp, st);
+                  sm_count_cached(), status, cp, st, &xm);
 }
 
 // Arrivals one mlb_gemm_rs call adds to each row-block counter.

@@ -1,0 +1,484 @@
+"""Text generation: KV-cache contexts, sampling, a static-batch engine and a dynamic
+(continuous-batching) engine with a paged KV cache.
+
+Counterparts in the reference (megatron/core/inference/): ``StaticInferenceContext`` and
+``DynamicInferenceContext`` with its ``ChunkAllocator`` (contexts/dynamic_context.py:72,
+dynamic_chunk_allocator.py:9), ``Scheduler`` (scheduler.py:17), ``TextGenerationController``
+sampling (text_generation_controllers/text_generation_controller.py:168-310),
+``StaticInferenceEngine`` (engines/static_engine.py:30) and ``DynamicInferenceEngine``
+(engines/dynamic_engine.py:37: ``add_request`` :157, ``step`` :386).
+
+The model's ``SelfAttention`` hands its fused, already rotated QKV activation to
+``context.attend``; the context appends K/V to its cache and runs either the flash-attention
+kernel (prefill, several query positions) or the single-query decode kernel over the cache.
+"""
+from __future__ import annotations
+
+import math
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import _lib
+from ..ops.attention import attention
+
+_lib.register_signatures({
+    "mlb_attn_decode": "ippppppiiiiliifp",
+    "mlb_kv_append": "ppppppplilii" "ip",
+})
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 0.0
+    return_log_probs: bool = False
+    return_segments: bool = False
+    num_tokens_to_generate: int = 30
+    top_n_logprobs: int = 0
+    return_prompt_top_n_logprobs: bool = False
+
+
+def sample_from_logits(logits: torch.Tensor, params: SamplingParams, vocab_size: Optional[int] = None,
+                       generator=None) -> torch.Tensor:
+    """logits [b, v] -> token ids [b].  top_k == 1 is greedy; top-k and top-p (nucleus) filter before
+    the temperature-scaled multinomial draw."""
+    if params.top_k == 1:
+        out = torch.argmax(logits, dim=-1)
+    else:
+        x = logits.float().clone()
+        if params.temperature != 1.0:
+            x.div_(params.temperature)
+        if params.top_k > 1:
+            if params.top_k > x.size(-1):
+                raise ValueError("top-k is larger than the vocabulary")
+            kth = torch.topk(x, params.top_k, dim=-1)[0][..., -1, None]
+            x.masked_fill_(x < kth, float("-inf"))
+        elif params.top_p > 0.0:
+            if params.top_p > 1.0:
+                raise ValueError("top-p must be at most 1")
+            srt, idx = torch.sort(x, descending=True, dim=-1)
+            cum = srt.softmax(dim=-1).cumsum(dim=-1)
+            remove = cum > params.top_p
+            remove[..., 1:] = remove[..., :-1].clone()
+            remove[..., 0] = False
+            x.masked_fill_(remove.scatter(-1, idx, remove), float("-inf"))
+        out = torch.multinomial(x.softmax(dim=-1), num_samples=1, generator=generator).view(-1)
+    if vocab_size is not None:
+        out = torch.clamp(out, min=0, max=vocab_size - 1)
+    return out
+
+
+# ----------------------------------------------------------------------------- contexts
+class _ContextBase:
+    def rope_span(self, input_ids) -> Tuple[int, int]:
+        """(number of positions the rotary table must cover from ``offset``, offset) for this step."""
+        raise NotImplementedError
+
+
+class StaticInferenceContext(_ContextBase):
+    """Contiguous KV cache [max_batch, max_len, ng, hn] per layer; all sequences advance together."""
+
+    def __init__(self, max_batch_size: int, max_sequence_length: int):
+        self.max_batch, self.max_len = max_batch_size, max_sequence_length
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        self.offset = 0                 # tokens already cached
+        self.step_len = 0
+
+    def reset(self):
+        self.offset = 0
+
+    def rope_span(self, input_ids):
+        self.step_len = input_ids.shape[1]
+        return self.step_len, self.offset
+
+    def advance(self):
+        self.offset += self.step_len
+
+    def attend(self, layer_number: int, qkv5: torch.Tensor, scale: float) -> torch.Tensor:
+        s, b, ng, tot, d = qkv5.shape
+        qpg = tot - 2
+        if layer_number not in self.k:
+            shape = (self.max_batch, self.max_len, ng, d)
+            self.k[layer_number] = torch.zeros(shape, dtype=qkv5.dtype, device=qkv5.device)
+            self.v[layer_number] = torch.zeros(shape, dtype=qkv5.dtype, device=qkv5.device)
+        kc, vc = self.k[layer_number], self.v[layer_number]
+        o0, o1 = self.offset, self.offset + s
+        if o1 > self.max_len:
+            raise RuntimeError("sequence exceeds the KV cache")
+        kc[:b, o0:o1] = qkv5[:, :, :, qpg].transpose(0, 1)
+        vc[:b, o0:o1] = qkv5[:, :, :, qpg + 1].transpose(0, 1)
+        q = qkv5[:, :, :, :qpg]
+        if s == 1 and qkv5.is_cuda:
+            qd = q[0].contiguous()                                         # [b, ng, qpg, d]
+            out = torch.empty_like(qd)
+            lens = torch.full((b,), o1, dtype=torch.int32, device=qkv5.device)
+            _lib.check(_lib.lib().mlb_attn_decode(_lib.dt(qd), qd.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                  lens.data_ptr(), None, out.data_ptr(), b, ng, qpg, d, self.max_len,
+                                                  0, 0, float(scale), _lib.stream()), "attn_decode")
+            return out.view(1, b, ng * qpg * d)
+        kk = kc[:b, :o1].transpose(0, 1)                                    # [sk, b, ng, d] views of the cache
+        vv = vc[:b, :o1].transpose(0, 1)
+        o = attention(q.contiguous() if not q.is_cuda else q, kk, vv, causal=True, scale=scale)
+        return o.reshape(s, b, ng * qpg * d)
+
+
+class ChunkAllocator:
+    """Free-list of fixed-size KV chunks."""
+
+    def __init__(self, num_chunks: int):
+        self.total = num_chunks
+        self.free: List[int] = list(range(num_chunks - 1, -1, -1))
+
+    def allocate(self, n: int) -> Optional[List[int]]:
+        if n > len(self.free):
+            return None
+        return [self.free.pop() for _ in range(n)]
+
+    def release(self, chunks: Sequence[int]) -> None:
+        self.free.extend(chunks)
+
+    @property
+    def available(self) -> int:
+        return len(self.free)
+
+
+class DynamicInferenceContext(_ContextBase):
+    """Paged KV cache shared by requests of different lengths.  A step carries a flat list of tokens
+    (``seq_of[i]``, ``pos_of[i]``): whole prompts of newly admitted requests and one token of each
+    request that is decoding."""
+
+    def __init__(self, max_requests: int, max_sequence_length: int, chunk_size: int = 256,
+                 buffer_size_gb: Optional[float] = None, num_chunks: Optional[int] = None):
+        self.max_requests, self.max_len, self.chunk = max_requests, max_sequence_length, chunk_size
+        self.max_chunks = (max_sequence_length + chunk_size - 1) // chunk_size
+        self.num_chunks = num_chunks
+        self.buffer_gb = buffer_size_gb
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        self.alloc: Optional[ChunkAllocator] = None
+        self.block_table = None
+        self.lens = [0] * max_requests                      # cached tokens per slot
+        self.slot_chunks: Dict[int, List[int]] = {}
+        self.free_slots = list(range(max_requests - 1, -1, -1))
+        self.step_tokens: List[Tuple[int, int]] = []        # (slot, position) of each token of the step
+        self.step_groups: List[Tuple[int, int, int]] = []   # (slot, first token index, count)
+        self._step_no = 0
+        self._reserved_step = -1
+
+    def _ensure(self, layer, ng, d, dtype, device):
+        if self.alloc is None:
+            if self.num_chunks is None:
+                if self.buffer_gb is not None:
+                    per_chunk = 2 * self.chunk * ng * d * torch.empty((), dtype=dtype).element_size()
+                    self.num_chunks = max(int(self.buffer_gb * 2 ** 30 // max(per_chunk, 1)), self.max_chunks)
+                else:
+                    self.num_chunks = self.max_requests * self.max_chunks
+            self.alloc = ChunkAllocator(self.num_chunks)
+            self.block_table = torch.zeros(self.max_requests, self.max_chunks, dtype=torch.int32, device=device)
+        if layer not in self.k:
+            shape = (self.num_chunks, self.chunk, ng, d)
+            self.k[layer] = torch.zeros(shape, dtype=dtype, device=device)
+            self.v[layer] = torch.zeros(shape, dtype=dtype, device=device)
+
+    # -- request bookkeeping (host) ------------------------------------------------
+    def chunks_needed(self, slot_len: int, extra: int) -> int:
+        have = (slot_len + self.chunk - 1) // self.chunk
+        need = (slot_len + extra + self.chunk - 1) // self.chunk
+        return need - have
+
+    def can_admit(self, prompt_len: int, reserve: int = 0) -> bool:
+        if not self.free_slots:
+            return False
+        free = self.alloc.available if self.alloc is not None else (self.num_chunks or self.max_requests * self.max_chunks)
+        return self.chunks_needed(0, prompt_len + reserve) <= free
+
+    def admit(self) -> int:
+        slot = self.free_slots.pop()
+        self.lens[slot] = 0
+        self.slot_chunks[slot] = []
+        return slot
+
+    def release(self, slot: int) -> None:
+        if self.alloc is not None:
+            self.alloc.release(self.slot_chunks.get(slot, []))
+        self.slot_chunks.pop(slot, None)
+        self.lens[slot] = 0
+        self.free_slots.append(slot)
+
+    def begin_step(self, groups: List[Tuple[int, int]]):
+        """groups: (slot, number of new tokens).  Returns position ids of the step's flat token list."""
+        self.step_tokens, self.step_groups = [], []
+        self._step_no += 1
+        for slot, n in groups:
+            self.step_groups.append((slot, len(self.step_tokens), n))
+            for i in range(n):
+                self.step_tokens.append((slot, self.lens[slot] + i))
+        return [p for _, p in self.step_tokens]
+
+    def _reserve_chunks(self):
+        for slot, _, n in self.step_groups:
+            need = self.chunks_needed(self.lens[slot], n)
+            if need:
+                got = self.alloc.allocate(need)
+                if got is None:
+                    raise RuntimeError("KV cache exhausted")
+                base = len(self.slot_chunks[slot])
+                self.slot_chunks[slot].extend(got)
+                self.block_table[slot, base:base + need] = torch.tensor(got, dtype=torch.int32,
+                                                                        device=self.block_table.device)
+
+    def end_step(self):
+        for slot, _, n in self.step_groups:
+            self.lens[slot] += n
+
+    def rope_span(self, input_ids):
+        return self.max_len, 0          # positions differ per token: select_rope picks each token's row
+
+    def select_rope(self, rotary, position_ids):
+        cos, sin = rotary
+        pos = position_ids.reshape(-1)
+        return cos[pos].contiguous(), sin[pos].contiguous()
+
+    # -- device side ------------------------------------------------------------------
+    def attend(self, layer_number: int, qkv5: torch.Tensor, scale: float) -> torch.Tensor:
+        n_tok, one, ng, tot, d = qkv5.shape                   # tokens along dim 0, "batch" of 1
+        qpg = tot - 2
+        dev = qkv5.device
+        self._ensure(layer_number, ng, d, qkv5.dtype, dev)
+        if self._reserved_step != self._step_no:            # first layer of this step: chunks and index vectors
+            self._reserve_chunks()
+            self._reserved_step = self._step_no
+            self._seq_of = torch.tensor([s for s, _ in self.step_tokens], dtype=torch.int32, device=dev)
+            self._pos_of = torch.tensor([p for _, p in self.step_tokens], dtype=torch.int32, device=dev)
+        kc, vc = self.k[layer_number], self.v[layer_number]
+        k_new = qkv5[:, 0, :, qpg]                             # [n_tok, ng, d] strided
+        v_new = qkv5[:, 0, :, qpg + 1]
+        if qkv5.is_cuda and qkv5.element_size() == 2 and qpg + 2 == tot and k_new.stride(1) == (qpg + 2) * d:
+            kk, vv = k_new.contiguous(), v_new.contiguous()
+            _lib.check(_lib.lib().mlb_kv_append(kk.data_ptr(), vv.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                self._seq_of.data_ptr(), self._pos_of.data_ptr(),
+                                                self.block_table.data_ptr(), ng * d, ng * d, 0, self.chunk,
+                                                self.max_chunks, n_tok, _lib.stream()), "kv_append")
+        else:
+            for i, (slot, pos) in enumerate(self.step_tokens):
+                c = self.slot_chunks[slot][pos // self.chunk]
+                kc[c, pos % self.chunk] = k_new[i]
+                vc[c, pos % self.chunk] = v_new[i]
+        out = torch.empty(n_tok, ng, qpg, d, dtype=qkv5.dtype, device=dev)
+        decode_rows, decode_slots = [], []
+        for slot, start, n in self.step_groups:
+            total = self.lens[slot] + n
+            if n == 1 and qkv5.is_cuda:
+                decode_rows.append(start)
+                decode_slots.append(slot)
+                continue
+            # prefill (or CPU): gather this request's cache and run causal attention with sq <= sk
+            chunks = self.slot_chunks[slot]
+            kk = kc[chunks].reshape(-1, ng, d)[:total].unsqueeze(1)
+            vv = vc[chunks].reshape(-1, ng, d)[:total].unsqueeze(1)
+            q = qkv5[start:start + n, :, :, :qpg]
+            o = attention(q.contiguous(), kk.contiguous(), vv.contiguous(), causal=True, scale=scale)
+            out[start:start + n] = o.reshape(n, ng, qpg, d)
+        if decode_rows:
+            rows = torch.tensor(decode_rows, device=dev)
+            qd = qkv5[rows, 0, :, :qpg].contiguous()
+            od = torch.empty_like(qd)
+            # the decode kernel indexes the block table by sequence number: give it the rows of these slots
+            bt = self.block_table[torch.tensor(decode_slots, device=dev)].contiguous()
+            lens = torch.tensor([self.lens[s] + 1 for s in decode_slots], dtype=torch.int32, device=dev)
+            _lib.check(_lib.lib().mlb_attn_decode(_lib.dt(qd), qd.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                                  lens.data_ptr(), bt.data_ptr(), od.data_ptr(), len(decode_rows), ng,
+                                                  qpg, d, 0, self.chunk, self.max_chunks, float(scale), _lib.stream()),
+                       "attn_decode")
+            out[rows] = od
+        return out.view(n_tok, 1, ng * qpg * d)
+
+
+# ----------------------------------------------------------------------------- requests / scheduler
+@dataclass
+class InferenceRequest:
+    request_id: int
+    prompt_tokens: List[int]
+    sampling_params: SamplingParams
+    generated_tokens: List[int] = field(default_factory=list)
+    generated_log_probs: List[float] = field(default_factory=list)
+    status: str = "waiting"            # waiting -> active -> completed
+    slot: int = -1
+    prompt: Optional[str] = None
+    generated_text: Optional[str] = None
+
+
+class Scheduler:
+    """Waiting / active / completed pools with a cap on concurrently active requests."""
+
+    def __init__(self, max_batch_size: int):
+        self.max_batch_size = max_batch_size
+        self.waiting: Deque[InferenceRequest] = deque()
+        self.active: Dict[int, InferenceRequest] = {}
+        self.completed: Dict[int, InferenceRequest] = {}
+        self._next_id = 0
+
+    def add_request(self, prompt_tokens: List[int], params: SamplingParams, prompt: Optional[str] = None) -> int:
+        rid = self._next_id
+        self._next_id += 1
+        self.waiting.append(InferenceRequest(rid, list(prompt_tokens), params, prompt=prompt))
+        return rid
+
+    def have_requests_pending(self) -> bool:
+        return bool(self.waiting or self.active)
+
+    def activate(self, req: InferenceRequest):
+        req.status = "active"
+        self.active[req.request_id] = req
+
+    def complete(self, req: InferenceRequest):
+        req.status = "completed"
+        self.active.pop(req.request_id, None)
+        self.completed[req.request_id] = req
+
+
+# ----------------------------------------------------------------------------- engines
+class StaticInferenceEngine:
+    """Generates for a fixed batch: prompts are right-padded, decoding starts at the shortest prompt
+    length, and positions still inside a longer prompt are forced to the prompt's token."""
+
+    def __init__(self, model, tokenizer=None, max_batch_size: int = 8, max_sequence_length: int = 2048,
+                 eod_id: Optional[int] = None, pad_id: int = 0):
+        self.model, self.tokenizer = model, tokenizer
+        self.max_batch, self.max_len = max_batch_size, max_sequence_length
+        self.eod = eod_id if eod_id is not None else (tokenizer.eod if tokenizer is not None else None)
+        self.pad = pad_id
+
+    @torch.no_grad()
+    def generate(self, prompts: Sequence, sampling_params: Optional[SamplingParams] = None, generator=None):
+        sp = sampling_params or SamplingParams()
+        toks = [self.tokenizer.tokenize(p) if isinstance(p, str) else list(p) for p in prompts]
+        if len(toks) > self.max_batch:
+            raise ValueError("more prompts than max_batch_size")
+        dev = next(self.model.parameters()).device
+        lens = [len(t) for t in toks]
+        min_len, max_prompt = min(lens), max(lens)
+        total = min(max_prompt + sp.num_tokens_to_generate, self.max_len)
+        b = len(toks)
+        ids = torch.full((b, total), self.pad, dtype=torch.long, device=dev)
+        for i, t in enumerate(toks):
+            ids[i, :len(t)] = torch.tensor(t, device=dev)
+        lens_t = torch.tensor(lens, device=dev)
+        ctx = StaticInferenceContext(b, total)
+        was_training = self.model.training
+        self.model.eval()
+        done = torch.zeros(b, dtype=torch.bool, device=dev)
+        log_probs = [[] for _ in range(b)]
+        prev = 0
+        for pos in range(min_len, total):
+            logits = self.model(ids[:, prev:pos], inference_context=ctx)            # [b, pos-prev, v]
+            ctx.advance()
+            last = logits[:, -1].float()
+            new = sample_from_logits(last, sp, None, generator)
+            in_prompt = lens_t > pos
+            new = torch.where(in_prompt, ids[:, pos], new)
+            if self.eod is not None:
+                new = torch.where(done, torch.full_like(new, self.eod), new)
+            if sp.return_log_probs:
+                lp = torch.log_softmax(last, dim=-1).gather(1, new[:, None]).squeeze(1)
+                for i in range(b):
+                    if not bool(in_prompt[i]) and not bool(done[i]):
+                        log_probs[i].append(float(lp[i]))
+            ids[:, pos] = new
+            if self.eod is not None:
+                done |= (new == self.eod) & ~in_prompt
+                if bool(done.all()):
+                    total = pos + 1
+                    break
+            prev = pos
+        self.model.train(was_training)
+        out = []
+        for i in range(b):
+            seq = ids[i, :total].tolist()
+            gen = seq[lens[i]:]
+            if self.eod is not None and self.eod in gen:
+                gen = gen[:gen.index(self.eod) + 1]
+            req = InferenceRequest(i, toks[i], sp, gen, log_probs[i], "completed")
+            if self.tokenizer is not None:
+                req.generated_text = self.tokenizer.detokenize(gen)
+            out.append(req)
+        return out
+
+
+class DynamicInferenceEngine:
+    """Continuous batching: each ``step`` admits waiting requests while the paged cache has room,
+    runs one forward over the new prompts' tokens plus one token per decoding request, samples, and
+    retires finished requests (their chunks return to the allocator)."""
+
+    def __init__(self, model, max_requests: int = 16, max_sequence_length: int = 2048, chunk_size: int = 256,
+                 buffer_size_gb: Optional[float] = None, tokenizer=None, eod_id: Optional[int] = None,
+                 num_chunks: Optional[int] = None):
+        self.model, self.tokenizer = model, tokenizer
+        self.context = DynamicInferenceContext(max_requests, max_sequence_length, chunk_size, buffer_size_gb, num_chunks)
+        self.scheduler = Scheduler(max_requests)
+        self.eod = eod_id if eod_id is not None else (tokenizer.eod if tokenizer is not None else None)
+        self.max_len = max_sequence_length
+
+    def add_request(self, prompt, sampling_params: Optional[SamplingParams] = None) -> int:
+        toks = self.tokenizer.tokenize(prompt) if isinstance(prompt, str) else list(prompt)
+        if len(toks) >= self.max_len:
+            raise ValueError("prompt longer than max_sequence_length")
+        return self.scheduler.add_request(toks, sampling_params or SamplingParams(), prompt if isinstance(prompt, str) else None)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.have_requests_pending()
+
+    @torch.no_grad()
+    def step(self, generator=None) -> List[InferenceRequest]:
+        sch, ctx = self.scheduler, self.context
+        groups, feed, owners = [], [], []
+        for req in sch.active.values():                         # one token each for decoding requests
+            groups.append((req.slot, 1))
+            feed.append([req.generated_tokens[-1]])
+            owners.append(req)
+        while sch.waiting and ctx.can_admit(len(sch.waiting[0].prompt_tokens), 1) and \
+                len(sch.active) < sch.max_batch_size:
+            req = sch.waiting.popleft()
+            req.slot = ctx.admit()
+            sch.activate(req)
+            groups.append((req.slot, len(req.prompt_tokens)))
+            feed.append(req.prompt_tokens)
+            owners.append(req)
+        if not groups:
+            return []
+        dev = next(self.model.parameters()).device
+        positions = ctx.begin_step(groups)
+        ids = torch.tensor([t for f in feed for t in f], dtype=torch.long, device=dev).unsqueeze(0)     # [1, n_tok]
+        pos = torch.tensor(positions, dtype=torch.long, device=dev).unsqueeze(0)
+        was_training = self.model.training
+        self.model.eval()
+        logits = self.model(ids, position_ids=pos, inference_context=ctx)[0]                       # [n_tok, v]
+        self.model.train(was_training)
+        ctx.end_step()
+        finished = []
+        for (slot, start, n), req in zip(ctx.step_groups, owners):
+            last = logits[start + n - 1].float().unsqueeze(0)
+            tok = int(sample_from_logits(last, req.sampling_params, None, generator)[0])
+            req.generated_tokens.append(tok)
+            if req.sampling_params.return_log_probs:
+                req.generated_log_probs.append(float(torch.log_softmax(last, -1)[0, tok]))
+            total = len(req.prompt_tokens) + len(req.generated_tokens)
+            if (self.eod is not None and tok == self.eod) or total >= self.max_len or \
+                    len(req.generated_tokens) >= req.sampling_params.num_tokens_to_generate:
+                ctx.release(req.slot)
+                sch.complete(req)
+                if self.tokenizer is not None:
+                    req.generated_text = self.tokenizer.detokenize(req.generated_tokens)
+                finished.append(req)
+        return finished
+
+    def generate(self, prompts: Sequence, sampling_params: Optional[SamplingParams] = None, generator=None):
+        ids = [self.add_request(p, sampling_params) for p in prompts]
+        while self.has_unfinished_requests():
+            self.step(generator)
+        return [self.scheduler.completed[i] for i in ids]

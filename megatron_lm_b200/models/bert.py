@@ -1,0 +1,134 @@
+"""BERT: bidirectional encoder with masked-LM head and optional next-sentence (binary) head.
+
+Reference: megatron/core/models/bert/bert_model.py (``BertModel`` :36, extended mask :188, forward
+:262), ``BertLMHead`` bert_lm_head.py, ``Pooler`` models/bert/pooler.py.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..config import TransformerConfig
+from ..ops import core as ops
+from ..parallel import state
+from ..parallel.layers import ColumnParallelLinear, _device
+from .gpt import LanguageModelEmbedding
+from .transformer import Norm, TransformerBlock
+
+
+def bert_extended_attention_mask(attention_mask: torch.Tensor) -> torch.Tensor:
+    """[b, s] of 1 = real token -> [b, 1, s, s] bool with True = may NOT attend."""
+    m = attention_mask.unsqueeze(1) * attention_mask.unsqueeze(2)       # [b, s, s]
+    return (m.unsqueeze(1) < 0.5)
+
+
+class BertLMHead(nn.Module):
+    def __init__(self, config: TransformerConfig):
+        super().__init__()
+        self.dense = nn.Linear(config.hidden_size, config.hidden_size, device=_device(config), dtype=config.params_dtype)
+        if config.perform_initialization:
+            config.init_method(self.dense.weight)
+            nn.init.zeros_(self.dense.bias)
+        self.layer_norm = Norm(config, config.hidden_size)
+        for p in self.dense.parameters():
+            p.sequence_parallel = config.sequence_parallel
+
+    def forward(self, h):
+        return self.layer_norm(torch.nn.functional.gelu(self.dense(h)))
+
+
+class Pooler(nn.Module):
+    """tanh(W h[0]) of the first token (sequence gathered first under sequence parallelism)."""
+
+    def __init__(self, config: TransformerConfig):
+        super().__init__()
+        self.config = config
+        self.dense = nn.Linear(config.hidden_size, config.hidden_size, device=_device(config), dtype=config.params_dtype)
+        if config.perform_initialization:
+            config.init_method(self.dense.weight)
+            nn.init.zeros_(self.dense.bias)
+
+    def forward(self, h, index: int = 0):
+        if self.config.sequence_parallel and state.model_parallel_is_initialized() and \
+                state.get_tensor_model_parallel_world_size() > 1:
+            from ..parallel.mappings import gather_from_sequence_parallel_region
+            h = gather_from_sequence_parallel_region(h, tensor_parallel_output_grad=False)
+        return torch.tanh(self.dense(h[index]))
+
+
+class BertModel(nn.Module):
+    def __init__(self, config: TransformerConfig, num_tokentypes: int, vocab_size: int, max_sequence_length: int,
+                 pre_process: bool = True, post_process: bool = True, fp16_lm_cross_entropy: bool = False,
+                 parallel_output: bool = True, share_embeddings_and_output_weights: bool = False,
+                 position_embedding_type: str = "learned_absolute", add_binary_head: bool = True,
+                 return_embeddings: bool = False, vp_stage: Optional[int] = None, transformer_layer_spec=None):
+        super().__init__()
+        if return_embeddings and not (post_process and add_binary_head):
+            raise ValueError("return_embeddings needs the pooler of the last stage")
+        self.config, self.vocab_size = config, vocab_size
+        self.pre_process, self.post_process = pre_process, post_process
+        self.add_binary_head, self.return_embeddings = add_binary_head, return_embeddings
+        self.parallel_output = parallel_output
+        self.share_embeddings_and_output_weights = share_embeddings_and_output_weights
+        tp = state.get_tensor_model_parallel_world_size() if state.model_parallel_is_initialized() else 1
+        self.tp_size = tp
+        self.tp_rank = state.get_tensor_model_parallel_rank() if tp > 1 else 0
+        if pre_process:
+            self.embedding = LanguageModelEmbedding(config, vocab_size, max_sequence_length, position_embedding_type,
+                                                    num_tokentypes)
+        self.encoder = TransformerBlock(config, pre_process, post_process, vp_stage, causal=False)
+        if post_process:
+            self.lm_head = BertLMHead(config)
+            skip = pre_process and share_embeddings_and_output_weights
+            self.output_layer = ColumnParallelLinear(config.hidden_size, vocab_size, config=config,
+                                                     init_method=config.init_method, bias=True,
+                                                     skip_weight_param_allocation=skip)
+            if add_binary_head:
+                self.pooler = Pooler(config)
+                self.binary_head = nn.Linear(config.hidden_size, 2, device=_device(config), dtype=config.params_dtype)
+                if config.perform_initialization:
+                    config.init_method(self.binary_head.weight)
+                    nn.init.zeros_(self.binary_head.bias)
+        if share_embeddings_and_output_weights and pre_process and post_process:
+            self.embedding.word_embeddings.weight.expected_grad_signals = 2
+
+    def set_input_tensor(self, t):
+        if isinstance(t, (list, tuple)):
+            t = t[0]
+        self.encoder.set_input_tensor(t)
+
+    def forward(self, input_ids, attention_mask, tokentype_ids=None, lm_labels=None, inference_context=None):
+        ext = bert_extended_attention_mask(attention_mask)
+        x = None
+        if self.pre_process:
+            pos = torch.arange(input_ids.shape[1], device=input_ids.device).unsqueeze(0).expand_as(input_ids)
+            x = self.embedding(input_ids, pos, tokentype_ids)
+        h = self.encoder(x, attention_mask=ext)
+        if not self.post_process:
+            return h
+        binary_logits = None
+        if self.add_binary_head:
+            pooled = self.pooler(h, 0)
+            if self.return_embeddings:
+                # mean of the real tokens between [CLS] and [SEP]
+                hb = h.transpose(0, 1)
+                out = torch.zeros(hb.shape[0], hb.shape[2], dtype=torch.float32, device=hb.device)
+                lens = attention_mask.sum(dim=1).long()
+                for i in range(hb.shape[0]):
+                    out[i] = hb[i, 1:max(int(lens[i]) - 1, 2)].float().mean(dim=0)
+                return out
+            binary_logits = self.binary_head(pooled)
+        weight = self.embedding.word_embeddings.weight if (self.share_embeddings_and_output_weights
+                                                           and self.pre_process) else None
+        logits, _ = self.output_layer(self.lm_head(h), weight=weight)          # [s, b, v/tp]
+        if lm_labels is None:
+            return logits.transpose(0, 1).contiguous(), binary_logits
+        tgt = lm_labels.transpose(0, 1).contiguous()
+        group = state.get_tensor_model_parallel_group() if self.tp_size > 1 else None
+        if not logits.is_cuda:
+            logits = logits.float()
+        loss = ops.cross_entropy(logits, tgt, vocab_start=self.tp_rank * logits.shape[-1], vocab_total=self.vocab_size,
+                                 group=group)
+        return loss.transpose(0, 1).contiguous(), binary_logits

@@ -136,9 +136,19 @@ class GPTModel(nn.Module):
         self.tp_rank = state.get_tensor_model_parallel_rank() if state.model_parallel_is_initialized() else 0
         if vocab_size % tp:
             raise ValueError("vocab_size must be padded to a multiple of the tensor-parallel size")
-        if pre_process:
+        # multi-token prediction embeds shifted tokens on the last stage, so that stage holds the table too
+        if pre_process or (post_process and config.mtp_num_layers):
             self.embedding = LanguageModelEmbedding(config, vocab_size, max_sequence_length, position_embedding_type)
-        if position_embedding_type == "rope":
+        if position_embedding_type == "rope" and getattr(config, "multi_latent_attention", False):
+            from .mla import YarnRotaryEmbedding
+            if config.rope_type == "yarn":
+                self.rotary_pos_emb = YarnRotaryEmbedding(
+                    config.qk_pos_emb_head_dim, config.rotary_base, config.rotary_scaling_factor,
+                    config.original_max_position_embeddings, config.beta_fast, config.beta_slow, config.mscale,
+                    config.mscale_all_dim)
+            else:
+                self.rotary_pos_emb = RotaryEmbedding(config.qk_pos_emb_head_dim, rotary_percent, config.rotary_base)
+        elif position_embedding_type == "rope":
             self.rotary_pos_emb = RotaryEmbedding(config.kv_channels, rotary_percent, rotary_base,
                                                   seq_len_interpolation_factor, rope_scaling, rope_scaling_factor)
         else:
@@ -196,12 +206,17 @@ class GPTModel(nn.Module):
     def forward(self, input_ids, position_ids=None, attention_mask=None, decoder_input=None, labels=None,
                 inference_context=None, loss_mask=None, runtime_gather_output: Optional[bool] = None):
         cfg = self.config
+        span = None
+        if inference_context is not None:
+            span = inference_context.rope_span(input_ids)      # (positions covered, first position) of this step
+            if position_ids is None:
+                position_ids = (torch.arange(input_ids.shape[1], device=input_ids.device) + span[1]).unsqueeze(0)
         if decoder_input is None and self.pre_process:
             decoder_input = self.embedding(input_ids, position_ids)
         rotary = None
         if self.rotary_pos_emb is not None:
-            if inference_context is not None:
-                seq, off = inference_context.rope_span(input_ids)
+            if span is not None:
+                seq, off = span
             else:
                 ref = decoder_input if decoder_input is not None else self.decoder.input_tensor
                 seq = ref.shape[0]
@@ -212,6 +227,8 @@ class GPTModel(nn.Module):
                 off = 0
             dev = input_ids.device if input_ids is not None else ref.device
             rotary = self.rotary_pos_emb(seq, dev, off)
+            if inference_context is not None and hasattr(inference_context, "select_rope"):
+                rotary = inference_context.select_rope(rotary, position_ids)    # one table row per token
         hidden = self.decoder(decoder_input, rotary=rotary, inference_context=inference_context,
                               attention_mask=attention_mask)
         if not self.post_process:
@@ -221,8 +238,8 @@ class GPTModel(nn.Module):
             weight = self.shared_embedding_or_output_weight()
         mtp_loss = None
         if cfg.mtp_num_layers and labels is not None and self.training:
-            mtp_loss = self.mtp(hidden, input_ids, position_ids, labels, loss_mask, rotary, self.embedding
-                                if self.pre_process else None, self.output_layer, weight)
+            mtp_loss = self.mtp(hidden, input_ids, position_ids, labels, loss_mask, rotary, self.embedding,
+                                self.output_layer, weight, self.compute_language_model_loss)
         logits, _ = self.output_layer(hidden, weight=weight)         # [s, b, v/tp]
         if labels is None:
             gather = self.parallel_output is False if runtime_gather_output is None else runtime_gather_output

@@ -134,6 +134,22 @@ def _rope_copy(qkv5, cos, sin, interleaved):
     return out
 
 
+def masked_attention(q5, k, v, attention_mask, scale, causal=False):
+    """Attention with an arbitrary mask (True = may not attend), e.g. padding masks of BERT / T5 batches.
+    q5 [sq, b, ng, qpg, d], k/v [sk, b, ng, d], mask broadcastable to [b, 1, sq, sk].  The flash kernels
+    cover the causal and full cases; arbitrary masks go through torch's scaled-dot-product attention."""
+    sq, b, ng, qpg, d = q5.shape
+    sk = k.shape[0]
+    q = q5.reshape(sq, b, ng * qpg, d).permute(1, 2, 0, 3)
+    kk = k.permute(1, 2, 0, 3).repeat_interleave(qpg, dim=1)
+    vv = v.permute(1, 2, 0, 3).repeat_interleave(qpg, dim=1)
+    allow = ~attention_mask.bool()
+    if causal:
+        allow = allow & torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(sk - sq)
+    o = torch.nn.functional.scaled_dot_product_attention(q, kk, vv, attn_mask=allow, scale=scale)
+    return o.permute(2, 0, 1, 3).reshape(sq, b, ng * qpg * d)
+
+
 class SelfAttention(nn.Module):
     def __init__(self, config: TransformerConfig, layer_number: int, causal: bool = True):
         super().__init__()
@@ -192,7 +208,13 @@ class SelfAttention(nn.Module):
                                                  causal=self.causal)
             out, bias = self.linear_proj(ctx_out.reshape(s, b, self.np_local * self.hn))
             return out, bias
-        if inference_context is not None:
+        if attention_mask is not None and inference_context is None:
+            if cos is not None:
+                qkv5 = ops.apply_rope_qkv_(qkv5.clone() if qkv5.is_cuda else qkv5, cos, sin,
+                                           self.config.rotary_interleaved)
+            ctx_out = masked_attention(qkv5[:, :, :, :self.qpg], qkv5[:, :, :, self.qpg], qkv5[:, :, :, self.qpg + 1],
+                                       attention_mask, self.softmax_scale, self.causal)
+        elif inference_context is not None:
             if cos is not None:
                 qkv5 = _rope_copy(qkv5, cos, sin, self.config.rotary_interleaved) if qkv5.is_cuda else \
                     ops.apply_rope_qkv_(qkv5, cos, sin, self.config.rotary_interleaved)
@@ -225,14 +247,17 @@ class CrossAttention(nn.Module):
                                              init_method=config.output_layer_init_method,
                                              bias=config.add_bias_linear, skip_bias_add=True)
 
-    def forward(self, hidden_states, key_value_states):
+    def forward(self, hidden_states, key_value_states, attention_mask=None):
         q, _ = self.linear_q(hidden_states)
         kv, _ = self.linear_kv(key_value_states)
         sq, b = q.shape[0], q.shape[1]
         sk = kv.shape[0]
         q5 = q.view(sq, b, self.np_local, 1, self.hn)
         kv5 = kv.view(sk, b, self.np_local, 2, self.hn)
-        o = attention(q5, kv5[:, :, :, 0], kv5[:, :, :, 1], causal=False)
+        if attention_mask is not None:
+            o = masked_attention(q5, kv5[:, :, :, 0], kv5[:, :, :, 1], attention_mask, 1.0 / math.sqrt(self.hn))
+        else:
+            o = attention(q5, kv5[:, :, :, 0], kv5[:, :, :, 1], causal=False)
         return self.linear_proj(o.reshape(sq, b, self.np_local * self.hn))
 
 
@@ -291,7 +316,11 @@ class TransformerLayer(nn.Module):
         super().__init__()
         self.config, self.layer_number = config, layer_number
         self.input_layernorm = Norm(config, config.hidden_size)
-        self.self_attention = SelfAttention(config, layer_number, causal=causal)
+        if getattr(config, "multi_latent_attention", False):
+            from .mla import MLASelfAttention
+            self.self_attention = MLASelfAttention(config, layer_number, causal=causal)
+        else:
+            self.self_attention = SelfAttention(config, layer_number, causal=causal)
         if cross_attention:
             self.pre_cross_attn_layernorm = Norm(config, config.hidden_size)
             self.cross_attention = CrossAttention(config, layer_number)
@@ -318,7 +347,7 @@ class TransformerLayer(nn.Module):
         return ops.bias_dropout_add(x, bias, residual, p, self.training)
 
     def forward(self, hidden_states, rotary=None, inference_context=None, encoder_output=None,
-                attention_mask=None):
+                attention_mask=None, enc_dec_attn_mask=None):
         residual = hidden_states
         if self.recompute_input_ln and self.training:
             ck = CheckpointWithoutOutput()
@@ -333,7 +362,7 @@ class TransformerLayer(nn.Module):
         if self.cross_attention is not None:
             residual = hidden_states
             ln = self.pre_cross_attn_layernorm(hidden_states)
-            x_out, x_bias = self.cross_attention(ln, encoder_output)
+            x_out, x_bias = self.cross_attention(ln, encoder_output, enc_dec_attn_mask)
             hidden_states = self._bda(x_out, x_bias, residual)
         residual = hidden_states
         if self.recompute_input_ln and self.training and not self.is_moe:
@@ -381,7 +410,7 @@ class TransformerBlock(nn.Module):
         return fn
 
     def forward(self, hidden_states, rotary=None, inference_context=None, encoder_output=None,
-                attention_mask=None):
+                attention_mask=None, enc_dec_attn_mask=None):
         if not self.pre_process and self.input_tensor is not None:
             hidden_states = self.input_tensor
         cfg = self.config
@@ -404,7 +433,8 @@ class TransformerBlock(nn.Module):
         else:
             for layer in self.layers:
                 hidden_states = layer(hidden_states, rotary=rotary, inference_context=inference_context,
-                                      encoder_output=encoder_output, attention_mask=attention_mask)
+                                      encoder_output=encoder_output, attention_mask=attention_mask,
+                                      enc_dec_attn_mask=enc_dec_attn_mask)
         if self.final_layernorm is not None:
             hidden_states = self.final_layernorm(hidden_states)
         return hidden_states

@@ -33,7 +33,7 @@ from . import _lib
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 _lib.register_signatures({
-    "mlb_ag_gemm": "ipppppiiiiipliplipiipp",
+    "mlb_ag_gemm": "ipppppiiiiiipliplipiipp",
     "mlb_gemm_rs": "iplplippiiiiplpliipp",
     "mlb_gemm_rs_arrivals": "ii",
 })
@@ -79,6 +79,7 @@ class FusedTP:
         self.chunk_flags = torch.zeros(self.tp * bpr, dtype=torch.int32, device=dev)
         self.comm_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.ag_seq = 0
+        self.comm_total = 0
         self.rs_calls = 0
         self.cnt_expected = [0, 0]
         self.hdl.barrier()
@@ -97,13 +98,14 @@ class FusedTP:
         gathered = torch.empty(self.tp * rows, K, dtype=self.dtype, device=x.device)
         y = torch.empty(self.tp * rows, N, dtype=out_dtype or self.dtype, device=x.device)
         self.ag_seq += 1
+        self.comm_total += self.n_comm
         st = _lib.status_word()
         mode = 0 if y.dtype != torch.float32 else 1
         bias_c = None if bias is None else bias.to(self.dtype).contiguous()
         _lib.check(_lib.lib().mlb_ag_gemm(
             1 if self.dtype == torch.bfloat16 else 0, _ptr_array(self.x_ptrs), _ptr_array(self.sig_ptrs),
             gathered.data_ptr(), self.chunk_flags.data_ptr(), self.comm_counter.data_ptr(), self.rank, self.tp,
-            rows, self.ag_seq, self.n_comm, weight.data_ptr(), weight.stride(0), int(b_mn), y.data_ptr(),
+            rows, self.ag_seq, self.comm_total, self.n_comm, weight.data_ptr(), weight.stride(0), int(b_mn), y.data_ptr(),
             y.stride(0), mode, _lib.ptr(bias_c), N, K, st.data_ptr(), _lib.stream()), "ag_gemm")
         return y, gathered
 

@@ -146,6 +146,9 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
         scale = config.grad_scale_func(torch.ones(1, device=loss.device)) if config.grad_scale_func is not None \
             else torch.ones(1, device=loss.device)
         MoEAuxLossAutoScaler.set_loss_scale(scale if config.calculate_per_token_loss else scale / num_microbatches)
+        if getattr(config, "mtp_num_layers", None):
+            from ..models.mtp import MTPLossAutoScaler
+            MTPLossAutoScaler.set_loss_scale(scale if config.calculate_per_token_loss else scale / num_microbatches)
         return loss, num_tokens
     return output, num_tokens
 

@@ -1,0 +1,103 @@
+"""Generation engines against a plain full-sequence forward (greedy), sampling filters, chunk allocator."""
+import pytest
+import torch
+
+from megatron_lm_b200.config import TransformerConfig
+from megatron_lm_b200.inference import (ChunkAllocator, DynamicInferenceEngine, SamplingParams, StaticInferenceEngine,
+                                        sample_from_logits)
+from megatron_lm_b200.models.gpt import GPTModel
+
+
+def _model(device="cpu", dtype=torch.float32, hn=16, pos="rope"):
+    torch.manual_seed(7)
+    cfg = TransformerConfig(num_layers=2, hidden_size=4 * hn, num_attention_heads=4, num_query_groups=2,
+                            ffn_hidden_size=8 * hn, normalization="RMSNorm", gated_linear_unit=True,
+                            add_bias_linear=False, params_dtype=dtype,
+                            bf16=dtype == torch.bfloat16, hidden_dropout=0.0, attention_dropout=0.0)
+    m = GPTModel(cfg, vocab_size=128, max_sequence_length=64, parallel_output=False,
+                 share_embeddings_and_output_weights=False, position_embedding_type=pos).to(device)
+    return m.eval()
+
+
+def _greedy_reference(model, prompt, n):
+    toks = list(prompt)
+    dev = next(model.parameters()).device
+    with torch.no_grad():
+        for _ in range(n):
+            logits = model(torch.tensor([toks], device=dev))
+            toks.append(int(logits[0, -1].float().argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("pos", ["rope", "learned_absolute"])
+def test_static_engine_matches_full_forward(pos):
+    model = _model(pos=pos)
+    prompts = [[5, 9, 2, 33, 7], [11, 4, 6]]
+    eng = StaticInferenceEngine(model, max_batch_size=4, max_sequence_length=32)
+    out = eng.generate(prompts, SamplingParams(top_k=1, num_tokens_to_generate=6, return_log_probs=True))
+    for req, p in zip(out, prompts):
+        ref = _greedy_reference(model, p, 6 + (5 - len(p)))
+        assert req.generated_tokens[:len(ref)] == ref[:len(req.generated_tokens)]
+        assert len(req.generated_log_probs) == len(req.generated_tokens)
+
+
+def test_dynamic_engine_matches_full_forward_and_recycles_chunks():
+    model = _model()
+    prompts = [[5, 9, 2, 33, 7], [11, 4, 6], [1, 2, 3, 4, 5, 6, 7, 8, 9]]
+    eng = DynamicInferenceEngine(model, max_requests=2, max_sequence_length=32, chunk_size=4, num_chunks=16)
+    out = eng.generate(prompts, SamplingParams(top_k=1, num_tokens_to_generate=5))
+    for req, p in zip(out, prompts):
+        assert req.generated_tokens == _greedy_reference(model, p, 5)
+    assert eng.context.alloc.available == 16 and len(eng.context.free_slots) == 2
+
+
+def test_sampling_filters():
+    g = torch.Generator().manual_seed(0)
+    logits = torch.tensor([[0.0, 5.0, 4.0, -2.0, 1.0]]).repeat(200, 1)
+    tk = sample_from_logits(logits, SamplingParams(top_k=2), generator=g)
+    assert set(tk.tolist()) <= {1, 2}
+    tp = sample_from_logits(logits, SamplingParams(top_p=0.7), generator=g)
+    assert set(tp.tolist()) <= {1, 2}
+    assert sample_from_logits(logits, SamplingParams(top_k=1)).tolist() == [1] * 200
+    with pytest.raises(ValueError):
+        sample_from_logits(logits, SamplingParams(top_k=9))
+
+
+def test_chunk_allocator():
+    a = ChunkAllocator(4)
+    x = a.allocate(3)
+    assert len(set(x)) == 3 and a.available == 1
+    assert a.allocate(2) is None
+    a.release(x)
+    assert a.available == 4
+
+
+@pytest.mark.gpu
+def test_engines_gpu_decode_kernel():
+    model = _model("cuda", torch.bfloat16, hn=64)
+    prompts = [[5, 9, 2, 33, 7, 8, 1], [11, 4, 6]]
+    # logits of the incremental path (prefill + decode kernel over the cache) against a full forward
+    from megatron_lm_b200.inference import StaticInferenceContext
+    ids = torch.tensor([prompts[0] + [3, 4, 5]], device="cuda")
+    with torch.no_grad():
+        full = model(ids).float()
+        ctx = StaticInferenceContext(1, 32)
+        a = model(ids[:, :7], inference_context=ctx).float(); ctx.advance()
+        outs = [a]
+        for i in range(7, 10):
+            outs.append(model(ids[:, i:i + 1], inference_context=ctx).float()); ctx.advance()
+    inc = torch.cat(outs, dim=1)
+    assert torch.allclose(inc, full, atol=5e-2, rtol=5e-2), (inc - full).abs().max()
+    st = StaticInferenceEngine(model, max_batch_size=4, max_sequence_length=48)
+    dy = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=48, chunk_size=16)
+    sp = SamplingParams(top_k=1, num_tokens_to_generate=8)
+    o_dy = dy.generate(prompts, sp)
+    for req, p in zip(o_dy, prompts):
+        # paged decode against full-forward logits, token by token (teacher-forced on the engine's tokens)
+        seq = torch.tensor([p + req.generated_tokens], device="cuda")
+        with torch.no_grad():
+            lg = model(seq).float()[0]
+        for i, t in enumerate(req.generated_tokens):
+            row = lg[len(p) + i - 1]
+            assert row[t] >= row.max() - 0.15
+    assert len(st.generate(prompts, sp)) == 2
