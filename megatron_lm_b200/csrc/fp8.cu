@@ -1,0 +1,164 @@
+// FP8 quantisation kernels.
+//   mlb_amax            : max |x| of a tensor into a device float (atomic max on the bit pattern)
+//   mlb_fp8_cast_transpose : per-tensor ("current") scaling cast to e4m3 / e5m2, producing the row-major copy and,
+//                         optionally, its transpose in the same pass (the FP8 GEMM takes K-major operands only,
+//                         so dgrad / wgrad read the transposed copies)
+//   mlb_mxfp8_quantize  : microscaling format - 32-element blocks along the row (or along the column) share one
+//                         power-of-two scale stored as an E8M0 byte
+// They cover what the reference obtains from Transformer Engine through megatron/core/fp8_utils.py:413-532
+// (recipes "tensorwise" and "mxfp8") and the parameter cast of :394.
+#include "common.cuh"
+#include <cuda_fp8.h>
+
+namespace mlb {
+
+template <typename T>
+__global__ void amax_kernel(const T* __restrict__ x, size_t n, float* __restrict__ amax) {
+  __shared__ float sh[32];
+  float m = 0.f;
+  const size_t stride = (size_t)gridDim.x * blockDim.x * 8;
+  for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    if (i + 8 <= n) {
+      float v[8]; load8(x + i, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) m = fmaxf(m, fabsf(v[k]));
+    } else {
+      for (size_t k = i; k < n; ++k) m = fmaxf(m, fabsf(to_f(x[k])));
+    }
+  }
+  m = block_max(m, sh);
+  if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(amax), __float_as_int(m));
+}
+
+__device__ __forceinline__ uint8_t to_fp8(float v, int e5m2) {
+  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, e5m2 ? __NV_E5M2 : __NV_E4M3);
+}
+
+// 64 x 64 tile per block of 256 threads
+template <typename T>
+__global__ void cast_transpose_kernel(const T* __restrict__ x, const float* __restrict__ amax, uint8_t* __restrict__ q,
+                                      uint8_t* __restrict__ qt, float* __restrict__ scale_inv, int rows, int cols,
+                                      int e5m2) {
+  __shared__ uint8_t tile[64][64 + 16];
+  const float fmax = e5m2 ? 57344.f : 448.f;
+  const float a = *amax;
+  const float scale = (a > 0.f && isfinite(a)) ? fmax / a : 1.f;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale_inv = 1.f / scale;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int tr = threadIdx.x >> 2, tc = (threadIdx.x & 3) * 16;
+  const int r = r0 + tr, c = c0 + tc;
+  uint4 packed = make_uint4(0, 0, 0, 0);
+  if (r < rows && c < cols) {
+    float v[16];
+    load8(x + (size_t)r * cols + c, *reinterpret_cast<float(*)[8]>(v));
+    load8(x + (size_t)r * cols + c + 8, *reinterpret_cast<float(*)[8]>(v + 8));
+    uint8_t* b = reinterpret_cast<uint8_t*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) b[i] = to_fp8(v[i] * scale, e5m2);
+    *reinterpret_cast<uint4*>(q + (size_t)r * cols + c) = packed;
+  }
+  if (qt == nullptr) return;
+  *reinterpret_cast<uint4*>(&tile[tr][tc]) = packed;
+  __syncthreads();
+  const int oc = c0 + tr;                  // source column = destination row
+  const int orow = r0 + tc;                // first of 16 source rows = destination columns
+  if (oc < cols && orow < rows) {
+    uint4 o; uint8_t* b = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) b[i] = tile[tc + i][tr];
+    *reinterpret_cast<uint4*>(qt + (size_t)oc * rows + orow) = o;
+  }
+}
+
+__device__ __forceinline__ int e8m0_exponent(float amax) {
+  // smallest power of two s.t. amax / 2^e <= 448 (largest e4m3 magnitude)
+  if (!(amax > 0.f)) return -127;
+  int e = (int)ceilf(log2f(amax / 448.f));
+  return max(-127, min(127, e));
+}
+
+// row-wise: one thread per 32-element block
+template <typename T>
+__global__ void mxfp8_row_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sc, int rows,
+                                 int cols) {
+  const int bpr = cols / 32;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * bpr) return;
+  const size_t off = i * 32;
+  float v[32];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) load8(x + off + 8 * k, *reinterpret_cast<float(*)[8]>(v + 8 * k));
+  float m = 0.f;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(v[k]));
+  const int e = e8m0_exponent(m);
+  const float s = exp2f((float)-e);
+  uint4 o[2]; uint8_t* b = reinterpret_cast<uint8_t*>(o);
+#pragma unroll
+  for (int k = 0; k < 32; ++k) b[k] = to_fp8(v[k] * s, 0);
+  reinterpret_cast<uint4*>(q + off)[0] = o[0];
+  reinterpret_cast<uint4*>(q + off)[1] = o[1];
+  sc[i] = (uint8_t)(e + 127);
+}
+
+// column-wise: blocks of 32 consecutive rows of one column; thread per column, coalesced across the warp
+template <typename T>
+__global__ void mxfp8_col_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sc, int rows,
+                                 int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int rb = blockIdx.y;
+  if (c >= cols) return;
+  float v[32];
+  float m = 0.f;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) { v[k] = to_f(x[(size_t)(rb * 32 + k) * cols + c]); m = fmaxf(m, fabsf(v[k])); }
+  const int e = e8m0_exponent(m);
+  const float s = exp2f((float)-e);
+#pragma unroll
+  for (int k = 0; k < 32; ++k) q[(size_t)(rb * 32 + k) * cols + c] = to_fp8(v[k] * s, 0);
+  sc[(size_t)rb * cols + c] = (uint8_t)(e + 127);
+}
+
+}  // namespace mlb
+
+using namespace mlb;
+
+// amax must be zeroed by the caller (or hold a running maximum to extend)
+MLB_API int mlb_amax(int dtype, const void* x, long n, float* amax, cudaStream_t st) {
+  if (n <= 0) return 0;
+  long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  MLB_DISPATCH_ACT(dtype, T, (amax_kernel<T><<<(unsigned)blocks, 256, 0, st>>>((const T*)x, (size_t)n, amax)));
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+
+// x [rows, cols] -> q [rows, cols] (and qt [cols, rows] when non-null) as fp8 bytes; scale_inv receives 1/scale
+MLB_API int mlb_fp8_cast_transpose(int dtype, const void* x, const float* amax, void* q, void* qt, float* scale_inv,
+                                   int rows, int cols, int e5m2, cudaStream_t st) {
+  if (rows % 16 || cols % 16) return -3;
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+  MLB_DISPATCH_ACT(dtype, T, (cast_transpose_kernel<T><<<grid, 256, 0, st>>>((const T*)x, amax, (uint8_t*)q, (uint8_t*)qt,
+                                                                            scale_inv, rows, cols, e5m2)));
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+
+// along_rows = 1: scales [rows, cols/32]; 0: blocks run down the columns, scales [rows/32, cols]
+MLB_API int mlb_mxfp8_quantize(int dtype, const void* x, void* q, void* scales, int rows, int cols, int along_rows,
+                               cudaStream_t st) {
+  if (along_rows) {
+    if (cols % 32) return -3;
+    const size_t nb = (size_t)rows * (cols / 32);
+    MLB_DISPATCH_ACT(dtype, T, (mxfp8_row_kernel<T><<<(unsigned)((nb + 127) / 128), 128, 0, st>>>(
+                                   (const T*)x, (uint8_t*)q, (uint8_t*)scales, rows, cols)));
+  } else {
+    if (rows % 32) return -3;
+    dim3 grid((cols + 127) / 128, rows / 32);
+    MLB_DISPATCH_ACT(dtype, T, (mxfp8_col_kernel<T><<<grid, 128, 0, st>>>((const T*)x, (uint8_t*)q, (uint8_t*)scales, rows,
+                                                                         cols)));
+  }
+  MLB_CHECK_LAUNCH();
+  return 0;
+}

@@ -45,6 +45,11 @@ struct GemmParams {
   int* status;
   int tiles_m, tiles_n;
   int tma_out;                // 1: epilogue stages tiles in shared memory and stores / add-reduces them by TMA
+  // 8-bit operands (both K-major, 128 elements per 128-byte swizzle row, 32 per MMA): the shared-memory
+  // layout in bytes is the same as for 16-bit operands, only the instruction kind and the K step differ
+  int fp8, a_fmt, b_fmt;      // formats: 0 = e4m3, 1 = e5m2
+  const float* scale_a;       // device scalars: the accumulator is multiplied by (*scale_a) * (*scale_b); may be null
+  const float* scale_b;
 };
 
 enum : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
@@ -251,7 +256,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int bk_elems = p.fp8 ? 2 * BK : BK;                        // elements per 128-byte row of a stage
+  const int num_kb = (p.K + bk_elems - 1) / bk_elems;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -274,7 +280,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
           mbar_expect_tx(full(stage), S::kABytes + S::kBBytes);
           const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
-          const int k0 = kb * BK;
+          const int k0 = kb * bk_elems;
           if constexpr (!A_MN) {
             if (own_rows) tma_load_2d(a_dst, &xm.m[0], full(stage), k0, tc.m_local * BM);
             else tma_load_2d(a_dst, &tmA, full(stage), k0, m0);            // box [64 k, 128 rows]
@@ -299,7 +305,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t idesc = p.fp8 ? make_idesc_f8(BM, BN, p.a_fmt, p.b_fmt)
+                                   : make_idesc(BM, BN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0; uint32_t phase = 0;
       int t = 0;
       bool ok = true;
@@ -318,7 +325,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // K-major: 16 elements = 32 B inside the swizzle row.  MN-major: 16 K-rows = two 1024 B groups.
             const uint64_t da = A_MN ? make_desc(a_addr + k * 2048, 8192, 1024) : make_desc(a_addr + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_desc(b_addr + k * 2048, 8192, 1024) : make_desc(b_addr + k * 32, 16, 1024);
-            mma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if (p.fp8) mma_f8(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else mma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           mma_commit(empty(stage));            // stage reusable once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -329,6 +337,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
+    const float alpha = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
     int t = 0;
     int epi_buf = 0;
     bool ok = true;
@@ -366,8 +375,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (p.out_mode == OUT_LP) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-              float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+              float a0 = __uint_as_float(r0[2 * i]) * alpha, a1 = __uint_as_float(r0[2 * i + 1]) * alpha;
+              float b0 = __uint_as_float(r1[2 * i]) * alpha, b1 = __uint_as_float(r1[2 * i + 1]) * alpha;
               if (p.bias != nullptr) {
                 a0 += load_bias(p.bias, col + 2 * i, p.N, p.lp_fmt); a1 += load_bias(p.bias, col + 2 * i + 1, p.N, p.lp_fmt);
                 b0 += load_bias(p.bias, col + 32 + 2 * i, p.N, p.lp_fmt); b1 += load_bias(p.bias, col + 33 + 2 * i, p.N, p.lp_fmt);
@@ -378,7 +387,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              float a = __uint_as_float(r0[i]);
+              float a = __uint_as_float(r0[i]) * alpha;
               if (p.bias != nullptr) a += load_bias(p.bias, col + i, p.N, p.lp_fmt);
               w[i] = __float_as_uint(a);
             }
@@ -412,7 +421,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (row < p.M && col < p.N) {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
           if (p.bias != nullptr) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -630,6 +639,7 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
   p.tma_out = tma_out;
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
+  p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr;
 #define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, tmD, xm, p, cp, sms, st)
   if (bn == 256) {
     if (!a_mn && !b_mn) GO(256, false, false);
@@ -643,6 +653,40 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
     GO(128, true, true);
   }
 #undef GO
+}
+
+// 8-bit operands: A [M, K], B [N, K] bytes, both K-major; D = (A B^T) * (*scale_a) * (*scale_b) (+ bias)
+static int run_gemm_fp8(int a_fmt, int b_fmt, const void* A, long lda, const void* B, long ldb, void* D, long ldd,
+                        int out_mode, int out_lp_fmt, const void* bias, const float* scale_a, const float* scale_b, int M,
+                        int N, int K, int sms, int* status, cudaStream_t st) {
+  if ((lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  const int bn = (N > 128) ? 256 : 128;
+  CUtensorMap tmA, tmB, tmD;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M}, strides[1] = {(uint64_t)lda};
+    uint32_t box[2] = {128, BM};
+    if ((rc = make_tmap(&tmA, A, 2, dims, strides, box, 1))) return rc;
+    dims[1] = (uint64_t)N; strides[0] = (uint64_t)ldb; box[1] = (uint32_t)bn;
+    if ((rc = make_tmap(&tmB, B, 2, dims, strides, box, 1))) return rc;
+  }
+  const int esz = (out_mode == OUT_LP) ? 2 : 4;
+  int tma_out = (((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
+  if (tma_out) {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)ldd * esz};
+    uint32_t box[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
+    if (make_tmap(&tmD, D, 2, dims, strides, box, esz)) tma_out = 0;
+  }
+  if (!tma_out) tmD = tmA;
+  GemmParams p;
+  p.tma_out = tma_out;
+  p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = out_lp_fmt;
+  p.status = status; p.tiles_m = p.tiles_n = 0;
+  p.fp8 = 1; p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.scale_a = scale_a; p.scale_b = scale_b;
+  static const ExtraMaps kNoMaps = {};
+  CommParams cp = {};
+  if (bn == 256) return launch_gemm<256, false, false>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
+  return launch_gemm<128, false, false>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
 }
 
 }  // namespace mlb

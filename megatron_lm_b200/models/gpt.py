@@ -162,6 +162,7 @@ class GPTModel(nn.Module):
             self.output_layer = ColumnParallelLinear(config.hidden_size, vocab_size, config=config,
                                                      init_method=config.init_method, bias=False,
                                                      skip_weight_param_allocation=skip)
+            self.output_layer.fp8_eligible = False          # the vocabulary projection stays in 16 bits
         self._setup_shared_embeddings()
 
     # -- tied embeddings ---------------------------------------------------

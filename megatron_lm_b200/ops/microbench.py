@@ -1,0 +1,131 @@
+"""Kernel microbenchmarks: ``python -m megatron_lm_b200.ops.microbench <op> [options]``.
+
+Each op is timed with CUDA events on the launching stream after warm-up, with a synchronize on both
+sides; operands are sized (or cycled) so that the working set exceeds the 126 MB L2.  Throughput is
+printed next to the fraction of the measured machine peaks when a ``MEASURED_PEAKS.json`` (keys
+``hbm_gbs``, ``bf16_tflops``) is found in the working directory.  ``--iters`` small (1-3) makes the run
+suitable for a profiler capture of a single kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    try:
+        with open("MEASURED_PEAKS.json") as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
+def _time(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _report(name, ms, flops=None, bytes_=None):
+    pk = _peaks()
+    msg = f"{name}: {ms * 1e3:.1f} us"
+    if flops:
+        tf = flops / ms / 1e9
+        msg += f"  {tf:.0f} TFLOP/s"
+        if pk.get("bf16_tflops"):
+            msg += f" ({tf / pk['bf16_tflops']:.2f} of measured cuBLAS burst)"
+    if bytes_:
+        gb = bytes_ / ms / 1e6
+        msg += f"  {gb:.0f} GB/s"
+        if pk.get("hbm_gbs"):
+            msg += f" ({gb / pk['hbm_gbs']:.2f} of measured copy bandwidth)"
+    print(msg, flush=True)
+
+
+def bench_gemm(a):
+    from .gemm import gemm
+    M, N, K = a.m, a.n, a.k
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * M * N * K
+    _report(f"gemm fwd {M}x{N}x{K} bf16", _time(lambda: gemm(A, B, out=out), a.iters, a.warmup), fl)
+    if a.all:
+        Bt, At = B.t().contiguous(), A.t().contiguous()
+        _report("  dgrad form (B MN-major)", _time(lambda: gemm(A, Bt, b_mn=True, out=out), a.iters, a.warmup), fl)
+        o32 = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+        _report("  wgrad form (A, B MN-major, fp32 accumulate)",
+                _time(lambda: gemm(At, Bt, a_mn=True, b_mn=True, out=o32, accumulate=True), a.iters, a.warmup), fl)
+        _report("  torch.matmul (cuBLAS)", _time(lambda: torch.matmul(A, B.t(), out=out), a.iters, a.warmup), fl)
+
+
+def bench_attention(a):
+    from .attention import attention_bwd_raw, attention_fwd_raw
+    s, b, ng, qpg, d = a.seq, a.batch, a.groups, a.heads // a.groups, a.head_dim
+    qkv = torch.randn(s, b, ng, qpg + 2, d, device="cuda", dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, :, :qpg], qkv[:, :, :, qpg], qkv[:, :, :, qpg + 1]
+    scale = d ** -0.5
+    fl = 4.0 * s * s * b * a.heads * d * (0.5 if a.causal else 1.0)
+    o, lse = attention_fwd_raw(q, k, v, a.causal, scale)
+    _report(f"attention fwd s={s} b={b} heads={a.heads} d={d} causal={a.causal}",
+            _time(lambda: attention_fwd_raw(q, k, v, a.causal, scale), a.iters, a.warmup), fl)
+    do = torch.randn_like(o)
+    _report("attention bwd", _time(lambda: attention_bwd_raw(q, k, v, o, do, lse, a.causal, scale), a.iters, a.warmup),
+            2.5 * fl)
+
+
+def bench_norm(a):
+    from . import core as ops
+    x = torch.randn(a.rows, a.hidden, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(a.hidden, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    by = x.numel() * 2 * 2
+    _report(f"rmsnorm fwd [{a.rows}, {a.hidden}]", _time(lambda: ops.rmsnorm(x, w, 1e-5, False), a.iters, a.warmup), bytes_=by)
+    y = ops.rmsnorm(x, w, 1e-5, False)
+    g = torch.randn_like(y)
+    _report("rmsnorm bwd", _time(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True), a.iters, a.warmup),
+            bytes_=x.numel() * 2 * 3)
+
+
+def bench_adam(a):
+    from . import optim as kops
+    n = a.numel
+    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    g = torch.randn(n, device="cuda")
+    lp = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    segs = [(0, n, 0)]
+    table, nc = kops.build_chunk_table(segs, p.device)
+    f = lambda: kops.adam_step(p, m, v, g, table=table, nchunks=nc, lrs=[1e-3], wds=[0.1], beta1=0.9, beta2=0.95,
+                               eps=1e-8, step=1, p_lp=lp, segments=segs)
+    _report(f"adam (fp32 p/m/v + bf16 copy) n={n}", _time(f, a.iters, a.warmup), bytes_=n * (4 * 7 + 2))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    sub = ap.add_subparsers(dest="op", required=True)
+    g = sub.add_parser("gemm"); g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=8192); g.add_argument("--all", action="store_true")
+    t = sub.add_parser("attention"); t.add_argument("--seq", type=int, default=4096); t.add_argument("--batch", type=int, default=4)
+    t.add_argument("--heads", type=int, default=32); t.add_argument("--groups", type=int, default=32)
+    t.add_argument("--head-dim", type=int, default=128); t.add_argument("--causal", type=int, default=1)
+    n = sub.add_parser("norm"); n.add_argument("--rows", type=int, default=32768); n.add_argument("--hidden", type=int, default=4096)
+    d = sub.add_parser("adam"); d.add_argument("--numel", type=int, default=1 << 28)
+    a = ap.parse_args(argv)
+    {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
+    from . import _lib
+    _lib.check_status()
+
+
+if __name__ == "__main__":
+    main()

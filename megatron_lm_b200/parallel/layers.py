@@ -206,6 +206,19 @@ def tp_linear(x, weight, bias=None, *, group=None, gather_input=False, reduce_ou
     return _TPLinear.apply(x, weight, bias, group, gather_input, reduce_output, allreduce_dgrad, fused)
 
 
+def _fp8_format(module, x, w) -> Optional[str]:
+    """'e4m3' / 'hybrid' when this call should run its GEMMs in FP8, else None.  FP8 applies to the linears
+    of transformer layers (``fp8_eligible``), with sizes the 8-bit tensor-core path accepts (multiples of 16);
+    the collectives then run outside the GEMM (the fused peer-memory kernels are 16-bit)."""
+    fmt = getattr(module.config, "fp8", None)
+    if not fmt or not getattr(module, "fp8_eligible", True) or x.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    tokens = x.numel() // x.shape[-1]
+    if tokens % 16 or w.shape[0] % 16 or w.shape[1] % 16:
+        return None
+    return "hybrid" if fmt == "hybrid" else "e4m3"
+
+
 class ColumnParallelLinear(nn.Module):
     """Y = X A^T + b with A split along its output dim: A = [A_1; ...; A_p]."""
 
@@ -251,8 +264,20 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, x, weight: Optional[torch.Tensor] = None):
         w = self.weight if weight is None else weight
         b = self.bias if not self.skip_bias_add else None
-        y = tp_linear(x, w, b, group=self.tp_group, gather_input=self.sequence_parallel,
-                      allreduce_dgrad=(self.tp_size > 1 and not self.sequence_parallel), fused=self.fused)
+        fmt = _fp8_format(self, x, w)
+        if fmt is not None:
+            from ..ops.fp8 import linear_fp8
+            from .mappings import copy_to_tensor_model_parallel_region, gather_from_sequence_parallel_region
+            if self.sequence_parallel:
+                inp = gather_from_sequence_parallel_region(x, True, self.tp_group)
+            elif self.tp_size > 1:
+                inp = copy_to_tensor_model_parallel_region(x, self.tp_group)
+            else:
+                inp = x
+            y = linear_fp8(inp, w, b, fmt)
+        else:
+            y = tp_linear(x, w, b, group=self.tp_group, gather_input=self.sequence_parallel,
+                          allreduce_dgrad=(self.tp_size > 1 and not self.sequence_parallel), fused=self.fused)
         if self.gather_output and self.tp_size > 1:
             from .mappings import gather_from_tensor_model_parallel_region
             y = gather_from_tensor_model_parallel_region(y, self.tp_group)
@@ -303,7 +328,17 @@ class RowParallelLinear(nn.Module):
             from .mappings import scatter_to_tensor_model_parallel_region
             x = scatter_to_tensor_model_parallel_region(x, self.tp_group)
         red = "none" if self.tp_size == 1 else ("reduce_scatter" if self.sequence_parallel else "all_reduce")
-        y = tp_linear(x, self.weight, None, group=self.tp_group, reduce_output=red, fused=self.fused)
+        fmt = _fp8_format(self, x, self.weight)
+        if fmt is not None:
+            from ..ops.fp8 import linear_fp8
+            from .mappings import reduce_from_tensor_model_parallel_region, reduce_scatter_to_sequence_parallel_region
+            y = linear_fp8(x, self.weight, None, fmt)
+            if red == "reduce_scatter":
+                y = reduce_scatter_to_sequence_parallel_region(y, self.tp_group)
+            elif red == "all_reduce":
+                y = reduce_from_tensor_model_parallel_region(y, self.tp_group)
+        else:
+            y = tp_linear(x, self.weight, None, group=self.tp_group, reduce_output=red, fused=self.fused)
         if self.skip_bias_add or self.bias is None:
             return y, self.bias
         return y + self.bias, None
