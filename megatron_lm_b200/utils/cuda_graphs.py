@@ -9,7 +9,9 @@ by writing ``param.main_grad`` inside the kernels, so those writes are part of t
 Python-side readiness signals that the data-parallel buckets wait for are re-issued after each replay.
 ``FullIterationGraph`` captures a whole forward-backward callable the same way.
 
-Limits: shapes and tensor addresses are frozen at capture; host-chosen scalars (dropout seeds, loss
+Limits: no autograd graph that involves the module's parameters may be alive when the capture starts
+(gradient-accumulation nodes created on another stream make the captured backward depend on uncaptured
+work); shapes and tensor addresses are frozen at capture; host-chosen scalars (dropout seeds, loss
 scale read on the host) are frozen too, so capture with dropout 0 or device-side RNG only.
 """
 from __future__ import annotations

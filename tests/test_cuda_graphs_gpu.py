@@ -25,6 +25,9 @@ def test_graphed_layer_matches_eager():
     ref_w = [p.main_grad.clone() for p in layer.parameters()]
     for p in layer.parameters():
         p.main_grad.zero_()
+    # the eager graph (and the gradient-accumulation nodes it created on this stream) must be gone before capture
+    del y
+    x.grad = None
     gl = GraphedModule(layer)
     for it in range(2):                       # second call replays
         x2 = x.detach().clone().requires_grad_()
