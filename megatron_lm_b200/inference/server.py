@@ -1,0 +1,184 @@
+"""HTTP text-generation server and its request handling.
+
+``python -m megatron_lm_b200.inference.server --port 5000 ...`` after building a model, or embed
+``MegatronServer(engine).run(host, port)``.
+
+Reference: megatron/inference/text_generation_server.py (``MegatronGenerate.put`` :35, request validation
+:40-200, ``MegatronServer`` :208) and text_generation/api.py:90 (``generate_and_post_process``), beam search
+text_generation/generation.py:334.  The wire format is kept: ``PUT /api`` with JSON
+{"prompts": [...], "tokens_to_generate": n, "temperature", "top_k", "top_p", "logprobs", "add_BOS",
+ "random_seed", "beam_width", "length_penalty", "stop_token"} -> {"text": [...], "segments", "logprobs"}.
+Implemented on the standard library's http.server (no web framework needed).
+"""
+from __future__ import annotations
+
+import json
+import threading
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import List, Optional
+
+import torch
+
+from .engine import SamplingParams, StaticInferenceContext
+
+
+def validate_request(req: dict, max_batch: int = 128):
+    """Returns (error message or None, normalised request)."""
+    if "prompts" not in req:
+        return "prompts argument required", None
+    prompts = req["prompts"]
+    if not isinstance(prompts, list) or not prompts or not all(isinstance(p, str) for p in prompts):
+        return "prompts is not a list of strings", None
+    if len(prompts) > max_batch:
+        return f"Maximum number of prompts is {max_batch}", None
+    out = {"prompts": prompts}
+    n = req.get("tokens_to_generate", 64)
+    if not isinstance(n, int) or n < 0:
+        return "tokens_to_generate must be an integer greater than or equal to 0", None
+    out["tokens_to_generate"] = n
+    lp = req.get("logprobs", False)
+    if not isinstance(lp, bool):
+        return "logprobs must be a boolean value", None
+    if n == 0 and not lp:
+        return "tokens_to_generate=0 implies logprobs should be True", None
+    out["logprobs"] = lp
+    t = req.get("temperature", 1.0)
+    if not isinstance(t, (int, float)) or not 0.0 < t <= 100.0:
+        return "temperature must be a positive number less than or equal to 100.0", None
+    out["temperature"] = float(t)
+    k = req.get("top_k", 0)
+    if not isinstance(k, int) or not 0 <= k <= 1000:
+        return "top_k must be an integer equal to or greater than 0 and less than or equal to 1000", None
+    p = req.get("top_p", 0.0)
+    if not isinstance(p, (int, float)) or not 0.0 <= p <= 1.0:
+        return "top_p must be less than or equal to 1.0", None
+    if k > 0 and p > 0.0:
+        return "cannot set both top-k and top-p samplings.", None
+    out["top_k"], out["top_p"] = k, float(p)
+    for flag in ("add_BOS", "stop_on_double_eol", "stop_on_eol", "no_log"):
+        v = req.get(flag, False)
+        if not isinstance(v, bool):
+            return f"{flag} must be a boolean value", None
+        out[flag] = v
+    seed = req.get("random_seed", -1)
+    if not isinstance(seed, int) or seed < -1:
+        return "random_seed must be a non-negative integer", None
+    out["random_seed"] = seed
+    bw = req.get("beam_width")
+    if bw is not None:
+        if not isinstance(bw, int) or bw < 1:
+            return "beam_width must be an integer > 1", None
+        if len(prompts) > 1:
+            return "When doing beam_search, batch size must be 1", None
+    out["beam_width"] = bw
+    out["stop_token"] = req.get("stop_token", None)
+    out["length_penalty"] = float(req.get("length_penalty", 1.0))
+    return None, out
+
+
+@torch.no_grad()
+def beam_search(model, prompt: List[int], beam_width: int, tokens_to_generate: int, stop_token: int,
+                length_penalty: float = 1.0, max_len: int = 2048):
+    """Length-penalised beam search for one prompt; returns (token lists, scores) best first."""
+    dev = next(model.parameters()).device
+    beams = [(list(prompt), 0.0)]
+    done = []
+    for _ in range(tokens_to_generate):
+        ids = torch.tensor([b[0] for b in beams], device=dev)
+        logits = model(ids)[:, -1].float()
+        lp = torch.log_softmax(logits, dim=-1)
+        cand = []
+        for bi, (toks, score) in enumerate(beams):
+            top = torch.topk(lp[bi], beam_width)
+            for v, t in zip(top.values.tolist(), top.indices.tolist()):
+                cand.append((toks + [t], score + v))
+        cand.sort(key=lambda c: c[1], reverse=True)
+        beams = []
+        for toks, score in cand:
+            if toks[-1] == stop_token:
+                done.append((toks, score / (len(toks) - len(prompt)) ** length_penalty))
+            else:
+                beams.append((toks, score))
+            if len(beams) == beam_width:
+                break
+        if len(done) >= beam_width or not beams or len(beams[0][0]) >= max_len:
+            break
+    done.extend((t, s / max(len(t) - len(prompt), 1) ** length_penalty) for t, s in beams)
+    done.sort(key=lambda c: c[1], reverse=True)
+    done = done[:beam_width]
+    return [d[0] for d in done], [d[1] for d in done]
+
+
+def generate_and_post_process(engine, req: dict):
+    """Run a validated request through a generation engine; returns the response dict."""
+    tok = engine.tokenizer
+    prompts = req["prompts"]
+    if req.get("beam_width"):
+        ids = tok.tokenize(prompts[0])
+        stop = req["stop_token"] if req.get("stop_token") is not None else tok.eod
+        seqs, scores = beam_search(engine.model, ids, req["beam_width"], req["tokens_to_generate"], stop,
+                                   req["length_penalty"])
+        return {"text": [tok.detokenize(s) for s in seqs], "segments": [[tok.detokenize([t]) for t in s] for s in seqs],
+                "scores": scores}
+    gen = None
+    if req.get("random_seed", -1) >= 0:
+        dev = next(engine.model.parameters()).device
+        gen = torch.Generator(device=dev).manual_seed(req["random_seed"])
+    sp = SamplingParams(temperature=req["temperature"], top_k=req["top_k"] or (0 if req["top_p"] > 0 else 1),
+                        top_p=req["top_p"], return_log_probs=req["logprobs"],
+                        num_tokens_to_generate=req["tokens_to_generate"])
+    toks = []
+    for p in prompts:
+        t = tok.tokenize(p)
+        if req.get("add_BOS") and getattr(tok, "bos", None) is not None:
+            t = [tok.bos] + t
+        toks.append(t)
+    outs = engine.generate(toks, sp, generator=gen)
+    text = [p + tok.detokenize(o.generated_tokens) for p, o in zip(prompts, outs)]
+    resp = {"text": text, "segments": [[tok.detokenize([t]) for t in (tk + o.generated_tokens)] for tk, o in zip(toks, outs)]}
+    if req["logprobs"]:
+        resp["logprobs"] = [o.generated_log_probs for o in outs]
+    return resp
+
+
+class MegatronServer:
+    def __init__(self, engine, max_batch: int = 128):
+        self.engine, self.max_batch = engine, max_batch
+        self.lock = threading.Lock()
+
+    def handle(self, body: bytes):
+        try:
+            req = json.loads(body)
+        except json.JSONDecodeError:
+            return 400, {"message": "request body is not JSON"}
+        err, norm = validate_request(req, self.max_batch)
+        if err:
+            return 400, {"message": err}
+        with self.lock:                       # one generation at a time, like the reference
+            try:
+                return 200, generate_and_post_process(self.engine, norm)
+            except ValueError as e:
+                return 400, {"message": str(e)}
+
+    def run(self, host: str = "0.0.0.0", port: int = 5000):
+        server = self
+
+        class Handler(BaseHTTPRequestHandler):
+            def do_PUT(self):
+                if self.path.rstrip("/") != "/api":
+                    self.send_error(404)
+                    return
+                n = int(self.headers.get("Content-Length", 0))
+                code, payload = server.handle(self.rfile.read(n))
+                data = json.dumps(payload).encode()
+                self.send_response(code)
+                self.send_header("Content-Type", "application/json")
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                self.wfile.write(data)
+            do_POST = do_PUT
+
+            def log_message(self, *a):
+                pass
+        self.httpd = ThreadingHTTPServer((host, port), Handler)
+        self.httpd.serve_forever()

@@ -1,0 +1,41 @@
+"""Request validation, beam search and the request -> response path of the generation server."""
+import json
+
+import torch
+
+from megatron_lm_b200.inference import StaticInferenceEngine
+from megatron_lm_b200.inference.server import MegatronServer, beam_search, validate_request
+from tests.test_inference import _model
+
+
+class _Tok:
+    eod, bos = 0, 1
+    def tokenize(self, s): return [int(x) for x in s.split()]
+    def detokenize(self, ids): return " " + " ".join(str(i) for i in ids) if ids else ""
+
+
+def test_validation_messages():
+    assert validate_request({})[0] == "prompts argument required"
+    assert validate_request({"prompts": ["a"], "top_k": 3, "top_p": 0.5})[0].startswith("cannot set both")
+    assert validate_request({"prompts": ["a"], "tokens_to_generate": 0})[0].startswith("tokens_to_generate=0")
+    assert validate_request({"prompts": ["a", "b"], "beam_width": 2})[0].startswith("When doing beam_search")
+    err, req = validate_request({"prompts": ["a"], "temperature": 0.7, "top_k": 5})
+    assert err is None and req["top_k"] == 5 and req["tokens_to_generate"] == 64
+
+
+def test_server_roundtrip_and_beam():
+    model = _model()
+    eng = StaticInferenceEngine(model, tokenizer=_Tok(), max_batch_size=4, max_sequence_length=32)
+    srv = MegatronServer(eng)
+    code, resp = srv.handle(json.dumps({"prompts": ["5 9 2", "7 7"], "tokens_to_generate": 4, "top_k": 1,
+                                        "logprobs": True}).encode())
+    assert code == 200 and len(resp["text"]) == 2 and len(resp["logprobs"][0]) >= 1
+    assert resp["text"][0].startswith("5 9 2")
+    code, resp = srv.handle(b"{not json")
+    assert code == 400
+    seqs, scores = beam_search(model, [5, 9, 2], 3, 4, stop_token=0)
+    assert len(seqs) == 3 and scores == sorted(scores, reverse=True)
+    # beam 1 equals greedy
+    g, _ = beam_search(model, [5, 9, 2], 1, 4, stop_token=-1)
+    from tests.test_inference import _greedy_reference
+    assert g[0][3:] == _greedy_reference(model, [5, 9, 2], 4)
