@@ -58,9 +58,82 @@ ec_apply_kernel(const EcParams p) {
   }
 }
 
+// Batched form: a table of jobs in device memory, each with its own sources (local or peer), destinations (local or
+// peer: a parity owner may compute all parities of a stripe and store the others' straight into their memory) and
+// coefficient rows.  Every job covers `nvec` vectors and is cut into `parts` block-sized pieces.
+struct EcJob {
+  unsigned long long src[kEcMaxK];
+  unsigned long long dst[kEcMaxM];
+  uint8_t coef[kEcMaxM][kEcMaxK];
+  int k, m, pad0, pad1;
+};
+
+__global__ void __launch_bounds__(256)
+ec_batch_kernel(const EcJob* __restrict__ jobs, int n_jobs, size_t nvec, int parts) {
+  __shared__ EcJob job;
+  const size_t per_part = (nvec + parts - 1) / parts;
+  for (long w = blockIdx.x; w < (long)n_jobs * parts; w += gridDim.x) {
+    __syncthreads();
+    if (threadIdx.x < sizeof(EcJob) / 4)
+      reinterpret_cast<uint32_t*>(&job)[threadIdx.x] = reinterpret_cast<const uint32_t*>(jobs + w / parts)[threadIdx.x];
+    __syncthreads();
+    const size_t v0 = (size_t)(w % parts) * per_part;
+    const size_t v1 = v0 + per_part < nvec ? v0 + per_part : nvec;
+    const int k = job.k, m = job.m;
+    for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+      uint4 raw[kEcMaxK];
+#pragma unroll
+      for (int j = 0; j < kEcMaxK; ++j)
+        if (j < k) raw[j] = reinterpret_cast<const uint4*>(job.src[j])[v];       // all loads in flight together
+      uint32_t acc[kEcMaxM][4];
+#pragma unroll
+      for (int i = 0; i < kEcMaxM; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0u; }
+#pragma unroll
+      for (int j = 0; j < kEcMaxK; ++j) {
+        if (j >= k) break;
+        uint32_t x[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+        uint32_t any = 0;
+#pragma unroll
+        for (int i = 0; i < kEcMaxM; ++i) any |= (i < m) ? job.coef[i][j] : 0;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          if ((any >> b) == 0) break;
+#pragma unroll
+          for (int i = 0; i < kEcMaxM; ++i)
+            if (i < m && ((job.coef[i][j] >> b) & 1)) {
+              acc[i][0] ^= x[0]; acc[i][1] ^= x[1]; acc[i][2] ^= x[2]; acc[i][3] ^= x[3];
+            }
+          x[0] = xtime4(x[0]); x[1] = xtime4(x[1]); x[2] = xtime4(x[2]); x[3] = xtime4(x[3]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kEcMaxM; ++i)
+        if (i < m) reinterpret_cast<uint4*>(job.dst[i])[v] = make_uint4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    }
+  }
+}
+
 }  // namespace mlb
 
 using namespace mlb;
+
+MLB_API int mlb_ec_job_bytes() { return (int)sizeof(EcJob); }
+
+// jobs: device array of n_jobs EcJob records (layout: 16 x u64 src, 4 x u64 dst, 4 x 16 coefficient bytes, k, m, 2 pad
+// ints); every buffer holds nbytes (multiple of 16).  grid_blocks bounds the SMs used (0 = whole GPU).
+MLB_API int mlb_ec_apply_batch(const void* jobs, int n_jobs, long nbytes, int grid_blocks, cudaStream_t st) {
+  if (n_jobs <= 0) return 0;
+  if (nbytes <= 0 || (nbytes % 16)) return -3;
+  const size_t nvec = (size_t)nbytes / 16;
+  int parts = (int)((nvec + 256 * 16 - 1) / (256 * 16));      // ~16 vectors per thread per piece
+  if (parts < 1) parts = 1;
+  long total = (long)n_jobs * parts;
+  long cap = grid_blocks > 0 ? grid_blocks : 148L * 8;
+  unsigned grid = (unsigned)(total < cap ? total : cap);
+  ec_batch_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const EcJob*>(jobs), n_jobs, nvec, parts);
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
 
 // src: host array of k device addresses (16-byte aligned; local or peer-mapped); dst: host array of m local
 // addresses; coef: host array [m][k] row-major; nbytes: multiple of 16.
