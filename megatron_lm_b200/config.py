@@ -472,6 +472,9 @@ class DistributedDataParallelConfig:
     preserve_fp32_weights: bool = True
     keep_fp8_transpose_cache_when_using_custom_fsdp: bool = False
     nccl_ub: bool = False
+    # gradient reduce-scatter and parameter all-gather of the distributed optimizer as peer-memory kernels (pull-
+    # reduce fused with scaling and norm; AdamW storing its result into every rank's parameter buffer)
+    peer_memory_collectives: bool = False
     fsdp_double_buffer: bool = False
 
     def __post_init__(self):

@@ -68,7 +68,7 @@ struct EcJob {
   int k, m, pad0, pad1;
 };
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 ec_batch_kernel(const EcJob* __restrict__ jobs, int n_jobs, size_t nvec, int parts) {
   __shared__ EcJob job;
   const size_t per_part = (nvec + parts - 1) / parts;
@@ -81,29 +81,33 @@ ec_batch_kernel(const EcJob* __restrict__ jobs, int n_jobs, size_t nvec, int par
     const size_t v1 = v0 + per_part < nvec ? v0 + per_part : nvec;
     const int k = job.k, m = job.m;
     for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-      uint4 raw[kEcMaxK];
-#pragma unroll
-      for (int j = 0; j < kEcMaxK; ++j)
-        if (j < k) raw[j] = reinterpret_cast<const uint4*>(job.src[j])[v];       // all loads in flight together
       uint32_t acc[kEcMaxM][4];
 #pragma unroll
       for (int i = 0; i < kEcMaxM; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0u; }
+      // sources four at a time: four 16-byte loads in flight per thread, few enough registers for 4 blocks per SM
+      for (int j0 = 0; j0 < k; j0 += 4) {
+        uint4 raw[4];
 #pragma unroll
-      for (int j = 0; j < kEcMaxK; ++j) {
-        if (j >= k) break;
-        uint32_t x[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
-        uint32_t any = 0;
+        for (int jj = 0; jj < 4; ++jj)
+          if (j0 + jj < k) raw[jj] = reinterpret_cast<const uint4*>(job.src[j0 + jj])[v];
 #pragma unroll
-        for (int i = 0; i < kEcMaxM; ++i) any |= (i < m) ? job.coef[i][j] : 0;
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = j0 + jj;
+          if (j >= k) break;
+          uint32_t x[4] = {raw[jj].x, raw[jj].y, raw[jj].z, raw[jj].w};
+          uint32_t any = 0;
 #pragma unroll
-        for (int b = 0; b < 8; ++b) {
-          if ((any >> b) == 0) break;
+          for (int i = 0; i < kEcMaxM; ++i) any |= (i < m) ? job.coef[i][j] : 0;
 #pragma unroll
-          for (int i = 0; i < kEcMaxM; ++i)
-            if (i < m && ((job.coef[i][j] >> b) & 1)) {
-              acc[i][0] ^= x[0]; acc[i][1] ^= x[1]; acc[i][2] ^= x[2]; acc[i][3] ^= x[3];
-            }
-          x[0] = xtime4(x[0]); x[1] = xtime4(x[1]); x[2] = xtime4(x[2]); x[3] = xtime4(x[3]);
+          for (int b = 0; b < 8; ++b) {
+            if ((any >> b) == 0) break;
+#pragma unroll
+            for (int i = 0; i < kEcMaxM; ++i)
+              if (i < m && ((job.coef[i][j] >> b) & 1)) {
+                acc[i][0] ^= x[0]; acc[i][1] ^= x[1]; acc[i][2] ^= x[2]; acc[i][3] ^= x[3];
+              }
+            x[0] = xtime4(x[0]); x[1] = xtime4(x[1]); x[2] = xtime4(x[2]); x[3] = xtime4(x[3]);
+          }
         }
       }
 #pragma unroll

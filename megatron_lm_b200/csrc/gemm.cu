@@ -29,3 +29,14 @@ MLB_API int mlb_gemm_fp8(int a_fmt, int b_fmt, const void* A, long lda, const vo
   return run_gemm_fp8(a_fmt, b_fmt, A, lda, B, ldb, D, ldd, out_mode, out_lp_fmt, bias, scale_a, scale_b, M, N, K,
                       sm_count_cached(), status, st);
 }
+
+// Grouped (mixture-of-experts) product in one launch: rows of A [T, K] are sorted by expert, `tiles` is a device
+// array of n_tiles records {row_begin, row_end, expert, 0} (each at most 128 rows of one expert), B stacks the
+// experts' matrices: b_mn == 0 -> [E * N, K] (forward, y = x W_e^T); b_mn == 1 -> [E * K, N] (data gradient,
+// dx = dy W_e with W_e stored [K, N]; K a multiple of 64).  D [T, N] gets only the rows the tiles cover.
+MLB_API int mlb_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B, long ldb, int b_mn, void* D, long ldd,
+                             const void* tiles, int n_tiles, int E, int T, int N, int K, int* status, cudaStream_t st) {
+  if (n_tiles <= 0 || N <= 0 || K <= 0) return 0;
+  return run_gemm_grouped(lp_fmt, A, lda, B, ldb, b_mn, D, ldd, reinterpret_cast<const int4*>(tiles), n_tiles, E, T, N,
+                          K, sm_count_cached(), status, st);
+}

@@ -19,8 +19,9 @@
 //          TMA producer waiting on each block's flag.
 //     RS : D is reduce-scattered over ranks.  Row blocks owned by other ranks are computed first; the
 //          epilogue stages each partial tile in shared memory and TMA-stores it into the owner's receive
-//          slot (over NVLink for a peer), then bumps the owner's arrival counter; when a CTA runs out of tiles it sums the arrived slots of
-//          this rank's row blocks (+ optional residual) into the output.
+//          slot (over NVLink), then bumps the owner's arrival counter.  This rank's own row blocks come last:
+//          their epilogue adds the peers' arrived partial rows (+ optional residual) to the accumulator and
+//          stores the finished sum, so there is no separate reduction pass.
 //   Every cross-rank wait is bounded and reports through the status word.
 //
 // Covers the GEMM call sites of the reference at megatron/core/tensor_parallel/layers.py:480
@@ -50,6 +51,12 @@ struct GemmParams {
   int fp8, a_fmt, b_fmt;      // formats: 0 = e4m3, 1 = e5m2
   const float* scale_a;       // device scalars: the accumulator is multiplied by (*scale_a) * (*scale_b); may be null
   const float* scale_b;
+  // Grouped (ragged) mode for mixture-of-experts: rows of A are sorted by expert; row-tile t covers rows
+  // [group_tiles[t].x, group_tiles[t].y) of expert group_tiles[t].z (at most 128 rows, never across two experts).
+  // B holds all experts stacked: K-major [E * N, K] or MN-major [E * K, N].  Output rows outside the tile's range
+  // are not written, so a short tile may read rows of the next expert without harm.
+  const int4* group_tiles;    // device array [tiles_m], or null
+  int raster_m;               // row blocks per rasterisation group (plain mode)
 };
 
 enum : int { COMM_NONE = 0, COMM_AG = 1, COMM_RS = 2 };
@@ -122,7 +129,14 @@ struct TileCoord { int m_blk, n_blk, owner, m_local; };
 __device__ __forceinline__ TileCoord map_tile(int tile, const GemmParams& p, const CommParams& c) {
   TileCoord t;
   if (c.mode == COMM_NONE) {
-    t.m_blk = tile % p.tiles_m; t.n_blk = tile / p.tiles_m; t.owner = 0; t.m_local = t.m_blk;
+    // Row-block groups of `raster_m`: the ~148 tiles in flight at any time then cover a squarish patch of the
+    // output (raster_m row blocks x ~148/raster_m column blocks), so the A and B panels they share stay in L2.
+    const int gm = p.raster_m;
+    const int per_group = gm * p.tiles_n;
+    const int grp = tile / per_group, in_grp = tile % per_group;
+    const int first_m = grp * gm;
+    const int size_m = (p.tiles_m - first_m) < gm ? (p.tiles_m - first_m) : gm;
+    t.m_blk = first_m + in_grp % size_m; t.n_blk = in_grp / size_m; t.owner = 0; t.m_local = t.m_blk;
   } else {
     const int per_group = c.bpr * p.tiles_n;
     const int g = tile / per_group, idx = tile % per_group;
@@ -212,7 +226,9 @@ template <int BN> struct GemmSmem {
   static constexpr int kBytes = kStages * (kABytes + kBBytes) + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN, bool A_MN, bool B_MN>
+// FP8 is a compile-time switch: a run-time choice of the MMA kind inside the issue loop costs the 16-bit path
+// more than 15 % (measured), so 8-bit operands get their own instantiations.
+template <int BN, bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p,
@@ -256,7 +272,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int bk_elems = p.fp8 ? 2 * BK : BK;                        // elements per 128-byte row of a stage
+  constexpr int bk_elems = FP8 ? 2 * BK : BK;                        // elements per 128-byte row of a stage
   const int num_kb = (p.K + bk_elems - 1) / bk_elems;
 
   if (warp == 0) {
@@ -269,6 +285,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const TileCoord tc = map_tile(tile, p, cp);
         const int m0 = tc.m_blk * BM, n0 = tc.n_blk * BN;
         const bool own_rows = cp.mode == COMM_AG && tc.owner == cp.rank;
+        int a_row = m0, b_row0 = n0, b_k0 = 0;
+        if (p.group_tiles != nullptr) {
+          const int4 g = p.group_tiles[tc.m_blk];
+          a_row = g.x;
+          if (B_MN) b_k0 = g.z * p.K; else b_row0 = g.z * p.N + n0;
+        }
         if (cp.mode == COMM_AG && !own_rows && tc.m_blk != ready_blk) {
           // rows of this block arrive from a peer: wait for the worker's flag, then order the
           // async-proxy (TMA) reads after the acquired writes
@@ -283,16 +305,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int k0 = kb * bk_elems;
           if constexpr (!A_MN) {
             if (own_rows) tma_load_2d(a_dst, &xm.m[0], full(stage), k0, tc.m_local * BM);
-            else tma_load_2d(a_dst, &tmA, full(stage), k0, m0);            // box [64 k, 128 rows]
+            else tma_load_2d(a_dst, &tmA, full(stage), k0, a_row);         // box [64 k, 128 rows]
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, full(stage), m0 + 64 * j, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(b_dst, &tmB, full(stage), k0, n0);                 // box [64 k, BN rows]
+            tma_load_2d(b_dst, &tmB, full(stage), k0, b_row0);             // box [64 k, BN rows]
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, full(stage), n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, full(stage), n0 + 64 * j, b_k0 + k0);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -305,8 +327,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = p.fp8 ? make_idesc_f8(BM, BN, p.a_fmt, p.b_fmt)
-                                   : make_idesc(BM, BN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t idesc = FP8 ? make_idesc_f8(BM, BN, p.a_fmt, p.b_fmt)
+                                 : make_idesc(BM, BN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0; uint32_t phase = 0;
       int t = 0;
       bool ok = true;
@@ -325,7 +347,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             // K-major: 16 elements = 32 B inside the swizzle row.  MN-major: 16 K-rows = two 1024 B groups.
             const uint64_t da = A_MN ? make_desc(a_addr + k * 2048, 8192, 1024) : make_desc(a_addr + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_desc(b_addr + k * 2048, 8192, 1024) : make_desc(b_addr + k * 32, 16, 1024);
-            if (p.fp8) mma_f8(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (FP8) mma_f8(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             else mma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           mma_commit(empty(stage));            // stage reusable once these MMAs have read it
@@ -348,7 +370,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int m0 = tc.m_blk * BM, n0 = tc.n_blk * BN;
       if (!mbar_wait(tfull(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       fence_after_sync();
-      const int row = m0 + quad * 32 + lane;
+      int row = m0 + quad * 32 + lane, row_end = p.M;
+      if (p.group_tiles != nullptr) {
+        const int4 g = p.group_tiles[tc.m_blk];
+        row = g.x + quad * 32 + lane; row_end = g.y;
+      }
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
       if (p.tma_out) {
         // ---- staged epilogue: registers -> 128B-swizzled shared tile -> TMA store / add-reduce.
@@ -359,8 +385,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // warp's stores have completed.
         const int cw = (p.out_mode == OUT_LP) ? 64 : 32;          // columns per 128-byte staged row
         uint8_t* my_stage = sEpi + (warp - 2) * 8192;
-        const CUtensorMap* dmap = (cp.mode == COMM_RS) ? &xm.m[tc.owner] : &tmD;
+        // Rows this rank owns are finished here: once the peers' partial tiles of the row block have arrived
+        // (they were computed first on every rank), each thread adds their rows and the residual to its
+        // accumulator row and the sum goes straight to the output - the own partial never touches memory.
+        const bool rs_own = cp.mode == COMM_RS && tc.owner == cp.rank;
+        const CUtensorMap* dmap = (cp.mode == COMM_RS && !rs_own) ? &xm.m[tc.owner] : &tmD;
         const int drow = (cp.mode == COMM_RS) ? tc.m_local * BM + quad * 32 : m0 + quad * 32;
+        if (rs_own) {
+          if (lane == 0 && !wait_ge<true>(cp.peer_cnt[cp.rank] + tc.m_local, cp.cnt_target, p.status, 6)) ok = false;
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) { *abort_flag = 1; break; }
+          __threadfence_system();              // every lane's loads below are ordered after the acquired counter
+        }
 #pragma unroll 1
         for (int c = 0; c < BN; c += cw) {
           uint32_t r0[32], r1[32];
@@ -381,8 +417,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 a0 += load_bias(p.bias, col + 2 * i, p.N, p.lp_fmt); a1 += load_bias(p.bias, col + 2 * i + 1, p.N, p.lp_fmt);
                 b0 += load_bias(p.bias, col + 32 + 2 * i, p.N, p.lp_fmt); b1 += load_bias(p.bias, col + 33 + 2 * i, p.N, p.lp_fmt);
               }
-              w[i] = pack2(a0, a1, p.lp_fmt);
-              w[16 + i] = pack2(b0, b1, p.lp_fmt);
+              r0[2 * i] = __float_as_uint(a0); r0[2 * i + 1] = __float_as_uint(a1);
+              r1[2 * i] = __float_as_uint(b0); r1[2 * i + 1] = __float_as_uint(b1);
+            }
+            if (rs_own && col < p.N) {
+              // 64 columns = 128 bytes of this thread's row in every peer's slot and in the residual
+              const size_t rrow = (size_t)(drow + lane);
+              auto add_row = [&](const uint16_t* src) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * q);
+                  const uint32_t* ww = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+                  for (int k2 = 0; k2 < 4; ++k2) {
+                    const float2 f = p.lp_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[k2]))
+                                              : __half22float2(*reinterpret_cast<const __half2*>(&ww[k2]));
+                    uint32_t* dst = (q < 4) ? &r0[8 * q + 2 * k2] : &r1[8 * (q - 4) + 2 * k2];
+                    dst[0] = __float_as_uint(__uint_as_float(dst[0]) + f.x);
+                    dst[1] = __float_as_uint(__uint_as_float(dst[1]) + f.y);
+                  }
+                }
+              };
+              const uint16_t* recv = reinterpret_cast<const uint16_t*>(cp.peer_recv[cp.rank]);
+              const size_t slot_stride = (size_t)cp.bpr * BM * p.N;
+              for (int sl = 0; sl < cp.tp; ++sl)
+                if (sl != cp.rank) add_row(recv + (size_t)sl * slot_stride + rrow * p.N + col);
+              if (cp.residual != nullptr)
+                add_row(reinterpret_cast<const uint16_t*>(cp.residual) + rrow * cp.ld_res + col);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              w[i] = pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]), p.lp_fmt);
+              w[16 + i] = pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]), p.lp_fmt);
             }
           } else {
 #pragma unroll
@@ -405,7 +471,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           epi_buf ^= 1;
         }
-        if (cp.mode == COMM_RS && lane == 0) {
+        if (cp.mode == COMM_RS && !rs_own && lane == 0) {
           bulk_wait<0>();                      // this warp's 32 rows of the tile have landed in the owner's slot
           fence_proxy_async_all();
           __threadfence_system();
@@ -418,7 +484,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld32(t_row + (uint32_t)c, r);
         tmem_wait_ld();
         const int col = n0 + c;
-        if (row < p.M && col < p.N) {
+        if (row < row_end && col < p.N) {
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
@@ -474,112 +540,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   }
   if (p.tma_out && warp >= 2 && lane == 0) bulk_wait<0>();     // staged stores have landed
-  if (cp.mode == COMM_RS && warp >= 2) {
-    // ---- reduce phase: sum the tp arrived slots of this rank's rows (+ residual) into the output.
-    // The [rows_per_rank, N] output is cut into equal contiguous runs of 16-byte vectors, one run per CTA;
-    // a run waits for the arrival counter of each 128-row block as it enters it.
-    const int rows_per_rank = cp.bpr * BM;
-    const int et = threadIdx.x - 64;
-    const uint16_t* recv = reinterpret_cast<const uint16_t*>(cp.peer_recv[cp.rank]);
-    {
-      const int vec_per_row = p.N >> 3;
-      const long all_vec = (long)rows_per_rank * vec_per_row;
-      constexpr int U = 8;                     // vectors per thread per pass: U x 2 slot loads in flight
-      long per = (all_vec + n_cta - 1) / n_cta;
-      per = (per + 128 * U - 1) / (128 * U) * (128 * U);
-      const long run0 = (long)cta * per;
-      const long total = run0 + per < all_vec ? run0 + per : all_vec;
-      const int c0 = 0;
-      int ready_mb = run0 < all_vec ? (int)(run0 / vec_per_row / BM) - 1 : 0;
-      bool alive = true;
-      auto addv = [&](float* a, const uint4& raw) {
-        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float2 f = p.lp_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]))
-                              : __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
-          a[2 * k] += f.x; a[2 * k + 1] += f.y;
-        }
-      };
-      const int mb = 0;
-      for (long v0 = run0 + et; v0 - et < total && alive; v0 += 128 * U) {
-        {
-          const long last = (v0 - et + 128 * U - 1 < total - 1) ? v0 - et + 128 * U - 1 : total - 1;
-          const int mb_hi = (int)(last / vec_per_row / BM);
-          while (ready_mb < mb_hi) {
-            ++ready_mb;
-            if (!wait_ge<true>(cp.peer_cnt[cp.rank] + ready_mb, cp.cnt_target, p.status, 6)) { alive = false; break; }
-          }
-          if (!alive) break;
-        }
-        float acc[U][8];
-        size_t off[U]; int rr[U], cc[U]; bool on[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long v = v0 + u * 128;
-          on[u] = v < total;
-          const long vv = on[u] ? v : run0;
-          rr[u] = mb * BM + (int)(vv / vec_per_row); cc[u] = c0 + (int)(vv % vec_per_row) * 8;
-          off[u] = (size_t)rr[u] * p.N + cc[u];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
-        }
-        const size_t slot_stride = (size_t)rows_per_rank * p.N;
-        int s = 0;
-        for (; s + 1 < cp.tp; s += 2) {
-          uint4 r0[U], r1[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            r0[u] = *reinterpret_cast<const uint4*>(recv + (size_t)s * slot_stride + off[u]);
-            r1[u] = *reinterpret_cast<const uint4*>(recv + (size_t)(s + 1) * slot_stride + off[u]);
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) { addv(acc[u], r0[u]); addv(acc[u], r1[u]); }
-        }
-        if (s < cp.tp) {
-          uint4 r0[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) r0[u] = *reinterpret_cast<const uint4*>(recv + (size_t)s * slot_stride + off[u]);
-#pragma unroll
-          for (int u = 0; u < U; ++u) addv(acc[u], r0[u]);
-        }
-        if (cp.residual != nullptr) {
-          uint4 r0[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u)
-            r0[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(cp.residual) + (size_t)rr[u] * cp.ld_res + cc[u]);
-#pragma unroll
-          for (int u = 0; u < U; ++u) addv(acc[u], r0[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (!on[u]) continue;
-          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cp.out) + (size_t)rr[u] * cp.ld_out + cc[u]) =
-              make_uint4(pack2(acc[u][0], acc[u][1], p.lp_fmt), pack2(acc[u][2], acc[u][3], p.lp_fmt),
-                         pack2(acc[u][4], acc[u][5], p.lp_fmt), pack2(acc[u][6], acc[u][7], p.lp_fmt));
-        }
-      }
-    }
-  }
   // ---------------------------------------------------------------- teardown
   fence_before_sync();
   __syncthreads();
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem_base, 2 * BN >= 32 ? 2 * BN : 32); }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool FP8 = false>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const ExtraMaps& xm,
                        GemmParams p, const CommParams& cp, int sm_count, cudaStream_t st) {
   using S = GemmSmem<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  p.tiles_m = (p.M + BM - 1) / BM;
+  if (p.group_tiles == nullptr) p.tiles_m = (p.M + BM - 1) / BM;     // grouped mode: set by the caller
   p.tiles_n = (p.N + BN - 1) / BN;
+  {
+    static int env_gm = -1;
+    if (env_gm < 0) { const char* e = getenv("MLB_GEMM_RASTER_M"); env_gm = e ? atoi(e) : 0; }
+    p.raster_m = env_gm > 0 ? env_gm : 8;
+    if (p.raster_m > p.tiles_m) p.raster_m = p.tiles_m;
+    if (p.raster_m < 1) p.raster_m = 1;
+  }
   const int tiles = p.tiles_m * p.tiles_n;
   int grid = tiles < sm_count ? tiles : sm_count;
   if (cp.mode == COMM_AG) grid = sm_count;          // workers + GEMM CTAs, all co-resident
@@ -627,8 +613,12 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
   const int esz = (out_mode == OUT_LP) ? 2 : 4;
   int tma_out = (((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0);
   if (cp.mode == COMM_RS) {
-    tma_out = 1;                 // the epilogue stores through xm; tmD is unused
-    tmD = tmA;
+    // peers' rows leave through xm; this rank's own rows are stored (already summed) into cp.out through tmD
+    tma_out = 1;
+    if ((((size_t)cp.ld_out * 2) % 16) || (reinterpret_cast<uintptr_t>(cp.out) & 15)) return -3;
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)(cp.bpr * BM)}, strides[1] = {(uint64_t)cp.ld_out * 2};
+    uint32_t box[2] = {64, 32};
+    if ((rc = make_tmap(&tmD, cp.out, 2, dims, strides, box, 2))) return rc;
   } else if (tma_out) {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)ldd * esz};
     uint32_t box[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
@@ -639,7 +629,7 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
   p.tma_out = tma_out;
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
-  p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr;
+  p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr; p.group_tiles = nullptr;
 #define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, tmD, xm, p, cp, sms, st)
   if (bn == 256) {
     if (!a_mn && !b_mn) GO(256, false, false);
@@ -682,11 +672,44 @@ static int run_gemm_fp8(int a_fmt, int b_fmt, const void* A, long lda, const voi
   p.tma_out = tma_out;
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = out_lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
-  p.fp8 = 1; p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.scale_a = scale_a; p.scale_b = scale_b;
+  p.fp8 = 1; p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.scale_a = scale_a; p.scale_b = scale_b; p.group_tiles = nullptr;
   static const ExtraMaps kNoMaps = {};
   CommParams cp = {};
-  if (bn == 256) return launch_gemm<256, false, false>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
-  return launch_gemm<128, false, false>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
+  if (bn == 256) return launch_gemm<256, false, false, true>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
+  return launch_gemm<128, false, false, true>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
+}
+
+// Grouped product over expert-sorted rows (see GemmParams::group_tiles).  A [T, K] K-major; B stacked experts.
+static int run_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B, long ldb, int b_mn, void* D, long ldd,
+                            const int4* tiles, int n_tiles, int E, int T, int N, int K, int sms, int* status,
+                            cudaStream_t st) {
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (b_mn && (K % BK)) return -3;               // the reduction may not run into the next expert's rows
+  const int bn = (N > 128) ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)T}, strides[1] = {(uint64_t)lda * 2};
+    uint32_t box[2] = {BK, BM};
+    if ((rc = make_tmap(&tmA, A, 2, dims, strides, box))) return rc;
+    if (!b_mn) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)E * N; box[0] = BK; box[1] = (uint32_t)bn; }
+    else       { dims[0] = (uint64_t)N; dims[1] = (uint64_t)E * K; box[0] = 64; box[1] = BK; }
+    strides[0] = (uint64_t)ldb * 2;
+    if ((rc = make_tmap(&tmB, B, 2, dims, strides, box))) return rc;
+  }
+  GemmParams p;
+  p.tma_out = 0;
+  p.M = T; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = nullptr; p.out_mode = OUT_LP; p.lp_fmt = lp_fmt;
+  p.status = status; p.tiles_m = n_tiles; p.tiles_n = 0;
+  p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr; p.group_tiles = tiles;
+  static const ExtraMaps kNoMaps = {};
+  CommParams cp = {};
+  if (bn == 256) {
+    if (!b_mn) return launch_gemm<256, false, false>(tmA, tmB, tmA, kNoMaps, p, cp, sms, st);
+    return launch_gemm<256, false, true>(tmA, tmB, tmA, kNoMaps, p, cp, sms, st);
+  }
+  if (!b_mn) return launch_gemm<128, false, false>(tmA, tmB, tmA, kNoMaps, p, cp, sms, st);
+  return launch_gemm<128, false, true>(tmA, tmB, tmA, kNoMaps, p, cp, sms, st);
 }
 
 }  // namespace mlb

@@ -17,13 +17,17 @@ struct OptGroups {
 
 constexpr int kOptThreads = 256;
 
+// Additional destinations of the low-precision parameter copy: the same element range of the parameter buffers of
+// the other data-parallel ranks (peer-mapped addresses), so that the update doubles as the parameter all-gather.
+struct PeerOut { __nv_bfloat16* ptr[8]; int n; };
+
 // grads are multiplied by *grad_scale (device scalar, may be null = 1); whole launch is a
 // no-op when *skip != 0 (overflow found).  p_lp (bf16, optional) receives the updated value.
 template <typename G>
 __global__ void __launch_bounds__(kOptThreads)
 adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, const G* __restrict__ g,
             __nv_bfloat16* __restrict__ p_lp, const OptChunk* __restrict__ chunks, OptGroups hp,
-            const float* __restrict__ grad_scale, const float* __restrict__ skip) {
+            const float* __restrict__ grad_scale, const float* __restrict__ skip, const PeerOut peers) {
   if (skip != nullptr && *skip != 0.f) return;
   const OptChunk c = chunks[blockIdx.x];
   const float gs = grad_scale ? *grad_scale : 1.f;
@@ -57,6 +61,7 @@ adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
 #pragma unroll
         for (int k = 0; k < 4; ++k) h[k] = __float2bfloat16_rn(P[k]);
         *reinterpret_cast<uint2*>(p_lp + o) = t;
+        for (int q = 0; q < peers.n; ++q) *reinterpret_cast<uint2*>(peers.ptr[q] + o) = t;
       }
     } else {
       for (int k = 0; k < 4 && i + k < c.len; ++k) {
@@ -66,7 +71,10 @@ adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
         const float vk = hp.beta2 * v[q] + (1.f - hp.beta2) * gr * gr;
         const float pk = p[q] * decay - step * mk / (sqrtf(vk) * rbc2 + hp.eps);
         m[q] = mk; v[q] = vk; p[q] = pk;
-        if (p_lp) p_lp[q] = __float2bfloat16_rn(pk);
+        if (p_lp) {
+          p_lp[q] = __float2bfloat16_rn(pk);
+          for (int r = 0; r < peers.n; ++r) peers.ptr[r][q] = __float2bfloat16_rn(pk);
+        }
       }
     }
   }
@@ -118,6 +126,30 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partial, int n, flo
   if (threadIdx.x == 0) out[0] = accumulate ? out[0] + acc : acc;
 }
 
+// Gradient reduce-scatter as a pull: out[i] = scale * sum_q src[q][i] over the data-parallel ranks' buffers (peer
+// loads), fused with the averaging scale and the sum of squares of the result (per-block partials).
+struct PeerIn { const float* ptr[8]; int n; };
+__global__ void __launch_bounds__(kOptThreads)
+grad_pull_kernel(const PeerIn src, float* __restrict__ out, size_t n, float scale, float* __restrict__ partial) {
+  __shared__ float sh[64];
+  float acc = 0.f;
+  const size_t nv = n >> 2;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (q >= src.n) break;
+      const float4 t = reinterpret_cast<const float4*>(src.ptr[q])[i];
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    reinterpret_cast<float4*>(out)[i] = s;
+    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+  }
+  acc = block_sum(acc, sh);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
 template <typename T>
 __global__ void scale_kernel(T* __restrict__ x, size_t n, const float* __restrict__ scale_ptr, float scale) {
   const float s = scale_ptr ? *scale_ptr * scale : scale;
@@ -140,6 +172,8 @@ __global__ void count_zeros_kernel(const T* __restrict__ x, size_t n, unsigned l
 
 using namespace mlb;
 
+MLB_API int mlb_sumsq_parts();
+
 static OptGroups make_groups(const float* lr, const float* wd, int ngroups, float b1, float b2, float eps,
                              float bc1, float bc2, float momentum) {
   OptGroups hp;
@@ -157,12 +191,43 @@ MLB_API int mlb_adam(int grad_dtype, float* p, float* m, float* v, const void* g
   OptGroups hp = make_groups(lr, wd, ngroups, beta1, beta2, eps, bc1, bc2, 0.f);
   if (grad_dtype == MLB_F32)
     adam_kernel<float><<<nchunks, kOptThreads, 0, st>>>(p, m, v, (const float*)g, (__nv_bfloat16*)p_lp,
-                                                        (const OptChunk*)chunks, hp, grad_scale, skip);
+                                                        (const OptChunk*)chunks, hp, grad_scale, skip, PeerOut{});
   else if (grad_dtype == MLB_BF16)
     adam_kernel<__nv_bfloat16><<<nchunks, kOptThreads, 0, st>>>(p, m, v, (const __nv_bfloat16*)g, (__nv_bfloat16*)p_lp,
-                                                                (const OptChunk*)chunks, hp, grad_scale, skip);
+                                                                (const OptChunk*)chunks, hp, grad_scale, skip, PeerOut{});
   else return -1;
   MLB_CHECK_LAUNCH(); return 0;
+}
+// AdamW on this rank's shard whose bf16 result is also stored into the same range of n_peers other ranks' parameter
+// buffers (peer_lp: host array of device addresses, each already offset to the shard's first element).
+MLB_API int mlb_adam_push(float* p, float* m, float* v, const float* g, void* p_lp, void* const* peer_lp, int n_peers,
+                          const void* chunks, int nchunks, const float* lr, const float* wd, int ngroups, float beta1,
+                          float beta2, float eps, float bc1, float bc2, const float* grad_scale, const float* skip,
+                          cudaStream_t st) {
+  if (nchunks <= 0) return 0;
+  if (ngroups > 16 || n_peers > 8 || p_lp == nullptr) return -4;
+  OptGroups hp = make_groups(lr, wd, ngroups, beta1, beta2, eps, bc1, bc2, 0.f);
+  PeerOut po = {};
+  po.n = n_peers;
+  for (int i = 0; i < n_peers; ++i) po.ptr[i] = reinterpret_cast<__nv_bfloat16*>(peer_lp[i]);
+  adam_kernel<float><<<nchunks, kOptThreads, 0, st>>>(p, m, v, g, (__nv_bfloat16*)p_lp, (const OptChunk*)chunks, hp,
+                                                      grad_scale, skip, po);
+  MLB_CHECK_LAUNCH(); return 0;
+}
+// out[0:n] = scale * sum over n_src buffers (local and peer addresses, fp32, 16-byte aligned, n % 4 == 0);
+// sumsq_out[0] (+)= sum of squares of the result.  workspace: fp32 [mlb_sumsq_parts()].
+MLB_API int mlb_grad_pull(const void* const* src, int n_src, float* out, long n, float scale, float* sumsq_out,
+                          float* workspace, int accumulate, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n_src < 1 || n_src > 8 || (n % 4)) return -3;
+  PeerIn pi = {};
+  pi.n = n_src;
+  for (int i = 0; i < n_src; ++i) pi.ptr[i] = reinterpret_cast<const float*>(src[i]);
+  const int parts = mlb_sumsq_parts();
+  grad_pull_kernel<<<parts, kOptThreads, 0, st>>>(pi, out, (size_t)n, scale, workspace);
+  MLB_CHECK_LAUNCH();
+  if (sumsq_out) { sumsq_final_kernel<<<1, 256, 0, st>>>(workspace, parts, sumsq_out, accumulate); MLB_CHECK_LAUNCH(); }
+  return 0;
 }
 MLB_API int mlb_sgd(int grad_dtype, float* p, float* mom, const void* g, void* p_lp, const void* chunks, int nchunks,
                     const float* lr, const float* wd, int ngroups, float momentum, int first_step,

@@ -37,12 +37,13 @@ MLB_API int mlb_ag_gemm(int lp_fmt, const void* const* peer_x, uint32_t* const* 
 
 // A: local [tp*rows_per_rank, K] (a_mn = 0).  peer_recv[i]: rank i's receive buffer [tp][rows_per_rank][N];
 // peer_cnt[i]: rank i's uint32[rows_per_rank/128] arrival counters.  cnt_target: cumulative arrivals expected on
-// this counter set once this call is complete (each call adds tp * ceil(N/BN) * 4 per row block).
+// this counter set once this call is complete (each call adds (tp - 1) * ceil(N/BN) * 4 per row block: one per
+// epilogue warp per tile from every peer; the owner's own tiles are summed in registers and do not count).
 MLB_API int mlb_gemm_rs(int lp_fmt, const void* A, long lda, const void* B, long ldb, int b_mn, void* const* peer_recv,
                         uint32_t* const* peer_cnt, unsigned cnt_target, int rank, int tp, int rows_per_rank,
                         const void* residual, long ld_res, void* out, long ld_out, int N, int K, int* status,
                         cudaStream_t st) {
-  if (tp < 2 || tp > kMaxPeers || rows_per_rank % BM || N % 32) return -7;
+  if (tp < 2 || tp > kMaxPeers || rows_per_rank % BM || N % 64) return -7;
   CommParams cp = {};
   cp.mode = COMM_RS; cp.rank = rank; cp.tp = tp; cp.bpr = rows_per_rank / BM; cp.cnt_target = cnt_target;
   for (int i = 0; i < tp; ++i) { cp.peer_recv[i] = peer_recv[i]; cp.peer_cnt[i] = peer_cnt[i]; }
@@ -60,4 +61,4 @@ MLB_API int mlb_gemm_rs(int lp_fmt, const void* A, long lda, const void* B, long
 }
 
 // Arrivals one mlb_gemm_rs call adds to each row-block counter.
-MLB_API int mlb_gemm_rs_arrivals(int tp, int N) { return tp * ((N + ((N > 128) ? 256 : 128) - 1) / ((N > 128) ? 256 : 128)) * 4; }
+MLB_API int mlb_gemm_rs_arrivals(int tp, int N) { return (tp - 1) * ((N + ((N > 128) ? 256 : 128) - 1) / ((N > 128) ? 256 : 128)) * 4; }

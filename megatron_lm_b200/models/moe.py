@@ -416,6 +416,49 @@ class MoEAlltoAllTokenDispatcher:
         return out.view(self.shape)
 
 
+_FUSED_COMM = {}
+
+
+class MoEFusedPeerDispatcher(MoEAlltoAllTokenDispatcher):
+    """Dispatch / combine as single kernels over NVLink peer memory (``ops/moe_fused.py``): permute + all-to-all
+    and all-to-all + un-permute + prob weighting, each one launch.  Used for CUDA tensors with expert
+    parallelism and a dropless router; otherwise behaves like the all-to-all dispatcher."""
+
+    def _comm(self, T, hdim, dtype):
+        from ..ops.moe_fused import FusedMoEComm
+        key = (id(self.ep_group), T, hdim, dtype, self.config.moe_router_topk)
+        if key not in _FUSED_COMM:
+            _FUSED_COMM[key] = FusedMoEComm(self.ep_group, T, self.config.moe_router_topk, hdim, self.E, dtype)
+        return _FUSED_COMM[key]
+
+    def _use_fused(self, h):
+        return h.is_cuda and self.ep > 1 and self.config.moe_expert_capacity_factor is None and \
+            h.dtype in (torch.bfloat16, torch.float16)
+
+    def dispatch(self, hidden, probs, routing_map):
+        h = hidden.reshape(-1, hidden.shape[-1])
+        self.fused = self._use_fused(h)
+        if not self.fused:
+            return super().dispatch(hidden, probs, routing_map)
+        from ..ops.moe_fused import fused_dispatch
+        self.shape, self.T = hidden.shape, h.shape[0]
+        rm = routing_map.t().contiguous()
+        token_idx = torch.arange(self.T, device=h.device).unsqueeze(0).expand(self.E, -1)
+        sorted_indices = token_idx.masked_select(rm)
+        self.comm = self._comm(self.T, h.shape[1], h.dtype)
+        self.plan = self.comm.plan(routing_map, sorted_indices)
+        self.copy_probs = probs.t().contiguous().masked_select(rm)
+        recv = fused_dispatch(h, self.comm, self.plan)
+        return recv, self.plan["tokens_per_local_expert"]
+
+    def combine(self, expert_out):
+        if not self.fused:
+            return super().combine(expert_out)
+        from ..ops.moe_fused import fused_combine
+        out = fused_combine(expert_out, self.copy_probs, self.comm, self.plan, self.T)
+        return out.view(self.shape)
+
+
 class MoEAllGatherTokenDispatcher:
     """Gather every rank's tokens, run the local experts on the ones routed here, reduce-scatter
     the outputs back (reference: token_dispatcher.py:196)."""
@@ -458,7 +501,9 @@ class MoELayer(nn.Module):
         self.router = TopKRouter(config, layer_number)
         self.experts = GroupedMLP(self.E_local, config)
         kind = config.moe_token_dispatcher_type
-        if kind in ("alltoall", "alltoall_seq", "flex"):
+        if kind == "flex":
+            self.token_dispatcher = MoEFusedPeerDispatcher(self.E_local, config)
+        elif kind in ("alltoall", "alltoall_seq"):
             self.token_dispatcher = MoEAlltoAllTokenDispatcher(self.E_local, config)
         elif kind == "allgather":
             self.token_dispatcher = MoEAllGatherTokenDispatcher(self.E_local, config)

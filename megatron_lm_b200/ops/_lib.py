@@ -49,6 +49,8 @@ _SIGS: Dict[str, str] = {
     "mlb_ce_fwd": "ipppppp" "lilqp",
     "mlb_ce_bwd": "ippppp" "p" "lilqfip",
     "mlb_adam": "ippppppi" "ppi" "fffff" "ppp",
+    "mlb_adam_push": "pppppp" "i" "pi" "ppi" "fffff" "ppp",
+    "mlb_grad_pull": "pipl" "f" "pp" "i" "p",
     "mlb_sgd": "ipppppi" "ppi" "fi" "ppp",
     "mlb_sumsq_parts": "",
     "mlb_sumsq": "iplppip",

@@ -42,10 +42,11 @@ def _farr(vals: Sequence[float]):
 def adam_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tensor, *, table, nchunks: int,
               lrs: Sequence[float], wds: Sequence[float], beta1: float, beta2: float, eps: float, step: int,
               p_lp: Optional[torch.Tensor] = None, grad_scale: Optional[torch.Tensor] = None,
-              skip: Optional[torch.Tensor] = None, segments=None) -> None:
+              skip: Optional[torch.Tensor] = None, segments=None, peer_lp: Optional[Sequence[int]] = None) -> None:
     """In-place AdamW (decoupled weight decay) on flat fp32 p/m/v with grads g (fp32 or bf16).
     ``grad_scale`` and ``skip`` are 1-element fp32 device tensors read by the kernel, so the
-    host never waits for the clip coefficient or the overflow flag."""
+    host never waits for the clip coefficient or the overflow flag.  ``peer_lp``: device addresses (peer-mapped)
+    that receive the low-precision result as well - the update then doubles as the parameter all-gather."""
     bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
     if not p.is_cuda:
         if skip is not None and float(skip) != 0.0:
@@ -60,6 +61,15 @@ def adam_step(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tensor
             p[sl].mul_(1 - lrs[group] * wds[group]).addcdiv_(m[sl], denom, value=-lrs[group] / bc1)
             if p_lp is not None:
                 p_lp[sl].copy_(p[sl])
+        return
+    if peer_lp:
+        if g.dtype != torch.float32 or p_lp is None:
+            raise ValueError("the peer-push update needs fp32 gradients and a low-precision parameter copy")
+        arr = (ctypes.c_void_p * len(peer_lp))(*[int(a) for a in peer_lp])
+        _lib.check(_lib.lib().mlb_adam_push(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), p_lp.data_ptr(), arr,
+                                            len(peer_lp), table.data_ptr(), nchunks, _farr(lrs), _farr(wds), len(lrs),
+                                            beta1, beta2, eps, bc1, bc2, _lib.ptr(grad_scale), _lib.ptr(skip),
+                                            _lib.stream()), "adam_push")
         return
     _lib.check(_lib.lib().mlb_adam(_lib.dt(g), p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(),
                                    _lib.ptr(p_lp), table.data_ptr(), nchunks, _farr(lrs), _farr(wds), len(lrs),
@@ -89,6 +99,17 @@ def sgd_step(p, mom, g, *, table, nchunks, lrs, wds, momentum: float, first_step
     _lib.check(_lib.lib().mlb_sgd(_lib.dt(g), p.data_ptr(), _lib.ptr(mom), g.data_ptr(), _lib.ptr(p_lp),
                                   table.data_ptr(), nchunks, _farr(lrs), _farr(wds), len(lrs), momentum,
                                   int(first_step), _lib.ptr(grad_scale), _lib.ptr(skip), _lib.stream()), "sgd")
+
+
+def grad_pull(src_addrs: Sequence[int], out: torch.Tensor, scale: float, sumsq: Optional[torch.Tensor] = None,
+              accumulate: bool = True) -> None:
+    """out = scale * sum of the fp32 buffers at ``src_addrs`` (this rank's and its peers' gradient slices), and
+    optionally sumsq (+)= |out|^2 - the reduce-scatter of the distributed optimizer as one pull kernel."""
+    L = _lib.lib()
+    ws = workspace((L.mlb_sumsq_parts(),), torch.float32, "sumsq", out.device)
+    arr = (ctypes.c_void_p * len(src_addrs))(*[int(a) for a in src_addrs])
+    _lib.check(L.mlb_grad_pull(arr, len(src_addrs), out.data_ptr(), out.numel(), float(scale), _lib.ptr(sumsq),
+                               ws.data_ptr(), int(accumulate), _lib.stream()), "grad_pull")
 
 
 def sum_squares(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:

@@ -232,16 +232,22 @@ class MixedPrecisionOptimizer:
                     continue
                 master = st.master[l0:l0 + n]
                 if cfg.optimizer == "adam":
+                    peer_lp = None
+                    if getattr(buf, "peer", None) is not None and lp is not None:
+                        peer_lp = [base + 2 * s for q, base in enumerate(buf.peer["param"]) if q != buf.dp_rank]
                     K.adam_step(master, st.exp_avg[l0:l0 + n], st.exp_avg_sq[l0:l0 + n], g, table=table,
                                 nchunks=nchunks, lrs=lrs, wds=wds, beta1=cfg.adam_beta1, beta2=cfg.adam_beta2,
                                 eps=cfg.adam_eps, step=self.step_count, p_lp=lp, grad_scale=self.grad_scale,
-                                skip=self.found_inf, segments=segs)
+                                skip=self.found_inf, segments=segs, peer_lp=peer_lp)
                 else:
                     K.sgd_step(master, st.exp_avg[l0:l0 + n], g, table=table, nchunks=nchunks, lrs=lrs, wds=wds,
                                momentum=cfg.sgd_momentum, first_step=self.step_count == 1, p_lp=lp,
                                grad_scale=self.grad_scale, skip=self.found_inf, segments=segs)
                 if lp is None:
                     buf.param_data[s:e].copy_(master)
+        for st in self.states:
+            if getattr(st.buf, "peer", None) is not None:
+                st.buf.peer_barrier()            # every rank's pushed weights have landed before the next forward
         for chunk in self.model_chunks:
             chunk.start_param_sync()
 

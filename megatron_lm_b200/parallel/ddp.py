@@ -89,8 +89,29 @@ class ParamAndGradBuffer:
             off = close(off)
         self.numel = off
         dev = params[0].device
-        self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=dev)
-        self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+        # Peer-memory collectives: both buffers live in one symmetric allocation that every rank of the data-
+        # parallel group can address, so the gradient reduce-scatter becomes a pull kernel and the optimizer
+        # stores updated weights straight into the peers' parameter buffers.
+        self.peer = None
+        want_peer = getattr(ddp_config, "peer_memory_collectives", False) and self.use_dist_opt and dp_size > 1 \
+            and dp_size <= 8 and dev.type == "cuda" and grad_dtype == torch.float32 and param_dtype == torch.bfloat16
+        if want_peer:
+            import os
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+            gbytes = self.numel * 4
+            pbytes = _pad(self.numel * 2, 16)
+            raw = symm_mem.empty(gbytes + pbytes, dtype=torch.uint8, device=dev)
+            raw.zero_()
+            torch.cuda.synchronize()
+            hdl = symm_mem.rendezvous(raw, dp_group)
+            base = [int(x) for x in hdl.buffer_ptrs]
+            self.grad_data = raw[:gbytes].view(torch.float32)
+            self.param_data = raw[gbytes:gbytes + self.numel * 2].view(torch.bfloat16)
+            self.peer = {"raw": raw, "hdl": hdl, "grad": base, "param": [b + gbytes for b in base], "pulled": False}
+        else:
+            self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=dev)
+            self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
         self.params = list(params)
         for p in params:
             s, e, _ = self.param_index_map[p]
@@ -107,7 +128,14 @@ class ParamAndGradBuffer:
         return bucket.start + r * n, bucket.start + (r + 1) * n
 
     def zero_grads(self):
+        if self.peer is not None:
+            self.peer["hdl"].barrier()          # peers may still be pulling last step's gradients from this buffer
+            self.peer["pulled"] = False
         self.grad_data.zero_()
+
+    def peer_barrier(self):
+        if self.peer is not None:
+            self.peer["hdl"].barrier()
 
 
 class BucketGroup:
@@ -152,6 +180,10 @@ class BucketGroup:
         if buf.ddp_config.check_for_nan_in_grad:
             if not torch.isfinite(g.float().sum()):
                 raise RuntimeError(f"non-finite gradient in bucket {b.index} before the data-parallel reduction")
+        if buf.peer is not None:
+            # nothing leaves now: finish_grad_sync pulls this rank's shard from every peer (scaling included)
+            self.grad_handle = "peer"
+            return
         if buf.gradient_scaling_factor != 1.0:
             scale_(g, buf.gradient_scaling_factor)
         if buf.dp_size == 1 or buf.dp_group is None:
@@ -169,7 +201,16 @@ class BucketGroup:
     def finish_grad_sync(self):
         if self.grad_handle is None:
             self.start_grad_sync()
-        if self.grad_handle is not True and self.grad_handle is not None:
+        if self.grad_handle == "peer":
+            buf, b = self.buf, self.bucket
+            if not buf.peer["pulled"]:
+                buf.peer["hdl"].barrier()        # every rank has finished its backward pass
+                buf.peer["pulled"] = True
+            s, e = buf.shard_range(b)
+            scale = buf.gradient_scaling_factor * ((1.0 / buf.dp_size) if buf.ddp_config.average_in_collective else 1.0)
+            from ..ops.optim import grad_pull
+            grad_pull([base + 4 * s for base in buf.peer["grad"]], buf.grad_data[s:e], scale)
+        elif self.grad_handle is not True and self.grad_handle is not None:
             self.grad_handle.wait()
         self.grad_handle = None
         self.ready.clear()
@@ -180,6 +221,8 @@ class BucketGroup:
         buf, b = self.buf, self.bucket
         if not buf.use_dist_opt or buf.dp_size == 1:
             return
+        if buf.peer is not None:
+            return                               # the optimizer already stored the new weights into every rank
         if self.param_handle is not None:
             return
         s, e = buf.shard_range(b)
