@@ -1,5 +1,6 @@
 // Plain (single-GPU) entry point of the tcgen05 GEMM; the kernel lives in gemm_core.cuh.
 #include "gemm_core.cuh"
+#include "gemm2.cuh"
 
 using namespace mlb;
 
@@ -39,4 +40,14 @@ MLB_API int mlb_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B,
   if (n_tiles <= 0 || N <= 0 || K <= 0) return 0;
   return run_gemm_grouped(lp_fmt, A, lda, B, ldb, b_mn, D, ldd, reinterpret_cast<const int4*>(tiles), n_tiles, E, T, N,
                           K, sm_count_cached(), status, st);
+}
+
+// CTA-pair (cta_group::2) variant of mlb_gemm for plain products whose output rows are 16-byte aligned.
+MLB_API int mlb_gemm_pair(int lp_fmt, const void* A, long lda, int a_mn, const void* B, long ldb, int b_mn, void* D,
+                          long ldd, int out_mode, const void* bias, int M, int N, int K, int max_ctas, int* status,
+                          cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  int sms = sm_count_cached();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  return run_gemm2(lp_fmt, A, lda, a_mn, B, ldb, b_mn, D, ldd, out_mode, bias, M, N, K, sms, status, st);
 }

@@ -1,0 +1,306 @@
+// CTA-pair variant of the bf16/fp16 GEMM (plain mode): two CTAs of one cluster (one TPC) compute a 256 x 256 output
+// tile with `tcgen05.mma.cta_group::2`.  Each CTA stages 128 rows of A and 128 of the 256 B rows per K step, so a
+// stage is 32 KB per SM instead of 48 KB - the L2 -> shared traffic per flop drops by a third, which is what
+// limits the single-CTA kernel - and six stages fit.  The accumulator rows [128 r, 128 r + 128) live in CTA r's
+// tensor memory; each CTA drains its own half.
+//   * full[s]   lives in the leader (even) CTA: its producer posts the 64 KB expectation, both CTAs' TMA loads
+//               complete on it (plain per-CTA loads, the barrier is addressed through the cluster window);
+//   * empty[s], tfull[a] exist in both CTAs and are signalled by the leader's commit with a 2-CTA mask;
+//   * tempty[a] lives in the leader: the eight epilogue warps of the pair arrive on it.
+// Every wait is bounded (status word), like in the single-CTA kernel.
+#pragma once
+#include "gemm_core.cuh"
+
+namespace mlb {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// one arrival on the barrier at this shared-memory offset in every CTA of `mask`, once the MMAs issued so far are done
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask) : "memory");
+}
+
+struct Gemm2Smem {
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = 128 * BK * 2;          // this CTA's 128 rows of A
+  static constexpr int kBBytes = 128 * BK * 2;          // this CTA's 128 of the tile's 256 B rows
+  static constexpr int kEpiBytes = 4 * 2 * 4096;
+  static constexpr int kBytes = kStages * (kABytes + kBBytes) + kEpiBytes + 1024 + 256;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+             const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  using S = Gemm2Smem;
+  constexpr int kStages = S::kStages;
+  constexpr int TN = 256;                                // tile columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + kStages * S::kABytes;
+  uint8_t* sEpi = smem + kStages * (S::kABytes + S::kBBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + S::kEpiBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto tfull = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
+  auto tempty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();               // 0 = leader
+  const bool leader = rank == 0;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 8); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmD);
+  }
+  if (warp == 1) { tmem_alloc2(smem_u32(tmem_slot), 512); tmem_relinquish2(); }
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                    // the peer's barriers exist before anything signals them
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+  const int gm = p.raster_m < tiles_m ? (p.raster_m > 0 ? p.raster_m : 1) : tiles_m;
+  auto tile_mn = [&](int tile, int& m_blk, int& n_blk) {
+    const int per_group = gm * tiles_n;
+    const int grp = tile / per_group, in_grp = tile % per_group;
+    const int first_m = grp * gm;
+    const int size_m = (tiles_m - first_m) < gm ? (tiles_m - first_m) : gm;
+    m_blk = first_m + in_grp % size_m; n_blk = in_grp / size_m;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        int mb, nb; tile_mn(tile, mb, nb);
+        const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN + 128 * (int)rank;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+          if (leader) mbar_expect_tx(full(stage), 2 * (S::kABytes + S::kBBytes));
+          const uint32_t fbar = map_to_cta(full(stage), 0);
+          const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(a_dst, &tmA, fbar, k0, m0);                   // box [64 k, 128 rows]
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, fbar, m0 + 64 * j, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(b_dst, &tmB, fbar, k0, n0);                   // box [64 k, 128 rows]
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, fbar, n0 + 64 * j, k0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) { const long long t0 = clock64(); while (clock64() - t0 < 2000000LL) { __nanosleep(1000); } }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc(256, TN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0; uint32_t phase = 0;
+      int t = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
+        const int acc = t & 1;
+        const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + stage * S::kABytes), b_addr = smem_u32(sB + stage * S::kBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t da = A_MN ? make_desc(a_addr + k * 2048, 8192, 1024) : make_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_desc(b_addr + k * 2048, 8192, 1024) : make_desc(b_addr + k * 32, 16, 1024);
+            mma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(empty(stage), 3);      // both CTAs may refill this stage once the MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) mma_commit_pair(tfull(acc), 3);  // accumulator complete: wake both CTAs' epilogue warps
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int quad = warp & 3;
+    int t = 0, epi_buf = 0;
+    bool ok = true;
+    const uint32_t tempty_leader0 = map_to_cta(tempty(0), 0);
+    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
+      const int acc = t & 1;
+      const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+      int mb, nb; tile_mn(tile, mb, nb);
+      const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN;
+      if (!mbar_wait(tfull(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+      fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * TN);
+      const int cw = (p.out_mode == OUT_LP) ? 64 : 32;
+      uint8_t* my_stage = sEpi + (warp - 2) * 8192;
+      const int drow = m0 + quad * 32;
+#pragma unroll 1
+      for (int c = 0; c < TN; c += cw) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_row + (uint32_t)c, r0);
+        if (cw == 64) tmem_ld32(t_row + (uint32_t)c + 32, r1);
+        tmem_wait_ld();
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        uint8_t* stage = my_stage + epi_buf * 4096;
+        const int col = n0 + c;
+        uint32_t w[32];
+        if (p.out_mode == OUT_LP) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+            float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+            if (p.bias != nullptr) {
+              a0 += load_bias(p.bias, col + 2 * i, p.N, p.lp_fmt); a1 += load_bias(p.bias, col + 2 * i + 1, p.N, p.lp_fmt);
+              b0 += load_bias(p.bias, col + 32 + 2 * i, p.N, p.lp_fmt); b1 += load_bias(p.bias, col + 33 + 2 * i, p.N, p.lp_fmt);
+            }
+            w[i] = pack2(a0, a1, p.lp_fmt);
+            w[16 + i] = pack2(b0, b1, p.lp_fmt);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float a = __uint_as_float(r0[i]);
+            if (p.bias != nullptr) a += load_bias(p.bias, col + i, p.N, p.lp_fmt);
+            w[i] = __float_as_uint(a);
+          }
+        }
+        uint8_t* rowp = stage + lane * 128;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && col < p.N && drow < p.M) {
+          if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(&tmD, smem_u32(stage), col, drow);
+          else tma_store_2d(&tmD, smem_u32(stage), col, drow);
+          bulk_commit();
+        }
+        epi_buf ^= 1;
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8u * (uint32_t)acc);
+    }
+    if (lane == 0) bulk_wait<0>();
+  }
+  // ---------------------------------------------------------------- teardown: nobody leaves while the peer may
+  // still signal this CTA's barriers or read its operand tiles
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc2(tmem_base, 512); }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const GemmParams& p,
+                        int sm_count, cudaStream_t st) {
+  using S = Gemm2Smem;
+  auto kern = gemm2_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  int pairs = sm_count / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, p);
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+
+// Same contract as run_gemm (plain mode); the output must be TMA-addressable (16-byte aligned rows).
+static int run_gemm2(int lp_fmt, const void* A, long lda, int a_mn, const void* B, long ldb, int b_mn, void* D, long ldd,
+                     int out_mode, const void* bias, int M, int N, int K, int sms, int* status, cudaStream_t st) {
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  const int esz = (out_mode == OUT_LP) ? 2 : 4;
+  if ((((size_t)ldd * esz) % 16) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
+  CUtensorMap tmA, tmB, tmD;
+  int rc;
+  uint64_t dims[2], strides[1]; uint32_t box[2];
+  if (!a_mn) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = 128; }
+  else       { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK; }
+  strides[0] = (uint64_t)lda * 2;
+  if ((rc = make_tmap(&tmA, A, 2, dims, strides, box))) return rc;
+  if (!b_mn) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = 128; }
+  else       { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 64; box[1] = BK; }
+  strides[0] = (uint64_t)ldb * 2;
+  if ((rc = make_tmap(&tmB, B, 2, dims, strides, box))) return rc;
+  {
+    uint64_t dd[2] = {(uint64_t)N, (uint64_t)M}, ds[1] = {(uint64_t)ldd * esz};
+    uint32_t db[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
+    if ((rc = make_tmap(&tmD, D, 2, dd, ds, db, esz))) return rc;
+  }
+  GemmParams p = {};
+  p.tma_out = 1;
+  p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = lp_fmt;
+  p.status = status;
+  {
+    static int env_gm = -1;
+    if (env_gm < 0) { const char* e = getenv("MLB_GEMM_RASTER_M"); env_gm = e ? atoi(e) : 0; }
+    p.raster_m = env_gm > 0 ? env_gm : 16;
+  }
+  if (!a_mn && !b_mn) return launch_gemm2<false, false>(tmA, tmB, tmD, p, sms, st);
+  if (!a_mn && b_mn) return launch_gemm2<false, true>(tmA, tmB, tmD, p, sms, st);
+  if (a_mn && !b_mn) return launch_gemm2<true, false>(tmA, tmB, tmD, p, sms, st);
+  return launch_gemm2<true, true>(tmA, tmB, tmD, p, sms, st);
+}
+
+}  // namespace mlb

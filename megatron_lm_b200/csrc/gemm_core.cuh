@@ -562,7 +562,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   {
     static int env_gm = -1;
     if (env_gm < 0) { const char* e = getenv("MLB_GEMM_RASTER_M"); env_gm = e ? atoi(e) : 0; }
-    p.raster_m = env_gm > 0 ? env_gm : 8;
+    p.raster_m = env_gm > 0 ? env_gm : 32;
     if (p.raster_m > p.tiles_m) p.raster_m = p.tiles_m;
     if (p.raster_m < 1) p.raster_m = 1;
   }

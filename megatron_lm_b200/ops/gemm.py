@@ -66,10 +66,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if bias is not None:
         bias = bias.to(a.dtype).contiguous()
     st = _lib.status_word()
-    _lib.check(_lib.lib().mlb_gemm(1 if a.dtype == torch.bfloat16 else 0, a.data_ptr(), a.stride(0), int(a_mn),
-                                   b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0), mode,
-                                   _lib.ptr(bias), M, N, K, max_ctas, st.data_ptr(), _lib.stream()), "gemm")
+    fn = _lib.lib().mlb_gemm
+    if _PAIR and N >= 256 and M >= 256 and (out.stride(0) * out.element_size()) % 16 == 0 and out.data_ptr() % 16 == 0:
+        fn = _lib.lib().mlb_gemm_pair            # CTA-pair kernel: 256 x 256 tiles over two SMs
+    _lib.check(fn(1 if a.dtype == torch.bfloat16 else 0, a.data_ptr(), a.stride(0), int(a_mn),
+                  b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0), mode,
+                  _lib.ptr(bias), M, N, K, max_ctas, st.data_ptr(), _lib.stream()), "gemm")
     return out
+
+
+import os as _os
+
+_PAIR = _os.environ.get("MLB_GEMM_PAIR", "1") == "1"      # set MLB_GEMM_PAIR=0 for the single-CTA kernel
 
 
 class _LinearFn(torch.autograd.Function):

@@ -15,9 +15,9 @@ def _worker(rank, world):
     from megatron_lm_b200.parallel import state
     from megatron_lm_b200.parallel.random import model_parallel_cuda_manual_seed
     state.initialize_model_parallel(expert_model_parallel_size=world, create_gloo_process_groups=False)
-    model_parallel_cuda_manual_seed(11)
     outs = {}
     for kind in ("alltoall", "flex"):
+        model_parallel_cuda_manual_seed(11)          # same expert initialisation for both layers
         torch.manual_seed(5)
         cfg = TransformerConfig(num_layers=1, hidden_size=256, num_attention_heads=4, ffn_hidden_size=512,
                                 num_moe_experts=2 * world, moe_router_topk=2, moe_ffn_hidden_size=256,
