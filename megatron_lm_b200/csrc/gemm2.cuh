@@ -64,7 +64,8 @@ struct Gemm2Smem {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-             const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+             const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p,
+             const CommParams cp) {
   using S = Gemm2Smem;
   constexpr int kStages = S::kStages;
   constexpr int TN = 256;                                // tile columns
@@ -83,6 +84,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   auto tempty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // All-gather mode: the first n_comm CTAs (whole pairs) are copy workers and take no part in the GEMM or in any
+  // cluster-wide synchronisation.
+  if (cp.mode == COMM_AG && (int)blockIdx.x < cp.n_comm) {
+    ag_comm_cta<6>(smem, bars, p, cp);
+    return;
+  }
   const uint32_t rank = cluster_ctarank();               // 0 = leader
   const bool leader = rank == 0;
   if (threadIdx.x == 0) {
@@ -102,14 +109,25 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
+  const int first_cta = (cp.mode == COMM_AG) ? cp.n_comm : 0;
+  const int pair = ((int)blockIdx.x - first_cta) >> 1, n_pairs = ((int)gridDim.x - first_cta) >> 1;
   const int gm = p.raster_m < tiles_m ? (p.raster_m > 0 ? p.raster_m : 1) : tiles_m;
-  auto tile_mn = [&](int tile, int& m_blk, int& n_blk) {
-    const int per_group = gm * tiles_n;
-    const int grp = tile / per_group, in_grp = tile % per_group;
-    const int first_m = grp * gm;
-    const int size_m = (tiles_m - first_m) < gm ? (tiles_m - first_m) : gm;
-    m_blk = first_m + in_grp % size_m; n_blk = in_grp / size_m;
+  const int bpr2 = cp.bpr >> 1;                          // 256-row blocks per rank (communication modes)
+  // tile -> (256-row block, 256-column block, owner rank of the rows, 256-row block within the owner's rows)
+  auto tile_mn = [&](int tile, int& m_blk, int& n_blk, int& owner, int& m_loc) {
+    if (cp.mode == COMM_NONE) {
+      const int per_group = gm * tiles_n;
+      const int grp = tile / per_group, in_grp = tile % per_group;
+      const int first_m = grp * gm;
+      const int size_m = (tiles_m - first_m) < gm ? (tiles_m - first_m) : gm;
+      m_blk = first_m + in_grp % size_m; n_blk = in_grp / size_m; owner = 0; m_loc = m_blk;
+    } else {
+      const int per_group = bpr2 * tiles_n;
+      const int g = tile / per_group, idx = tile % per_group;
+      m_loc = idx % bpr2; n_blk = idx / bpr2;
+      owner = (cp.mode == COMM_AG) ? (cp.rank + g) % cp.tp : (cp.rank + 1 + g) % cp.tp;
+      m_blk = owner * bpr2 + m_loc;
+    }
   };
 
   if (warp == 0) {
@@ -117,9 +135,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      int ready_blk = -1;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-        int mb, nb; tile_mn(tile, mb, nb);
+        int mb, nb, owner, mloc; tile_mn(tile, mb, nb, owner, mloc);
         const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN + 128 * (int)rank;
+        const bool own_rows = cp.mode == COMM_AG && owner == cp.rank;
+        if (cp.mode == COMM_AG && !own_rows && (2 * mb + (int)rank) != ready_blk) {
+          // this CTA's 128 rows arrive from a peer: wait for the copy worker's flag of that row block
+          if (!wait_ge<false>(cp.chunk_flags + 2 * mb + (int)rank, cp.seq, p.status, 5)) { *abort_flag = 1; ok = false; break; }
+          fence_proxy_async_all();
+          ready_blk = 2 * mb + (int)rank;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
           if (leader) mbar_expect_tx(full(stage), 2 * (S::kABytes + S::kBBytes));
@@ -127,7 +153,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tma_load_2d_pair(a_dst, &tmA, fbar, k0, m0);                   // box [64 k, 128 rows]
+            if (own_rows) tma_load_2d_pair(a_dst, &xm.m[0], fbar, k0, mloc * 256 + 128 * (int)rank);
+            else tma_load_2d_pair(a_dst, &tmA, fbar, k0, m0);              // box [64 k, 128 rows]
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, fbar, m0 + 64 * j, k0);
@@ -181,14 +208,27 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
       const int acc = t & 1;
       const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
-      int mb, nb; tile_mn(tile, mb, nb);
+      int mb, nb, owner, mloc; tile_mn(tile, mb, nb, owner, mloc);
       const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN;
       if (!mbar_wait(tfull(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * TN);
       const int cw = (p.out_mode == OUT_LP) ? 64 : 32;
       uint8_t* my_stage = sEpi + (warp - 2) * 8192;
-      const int drow = m0 + quad * 32;
+      // reduce-scatter: rows of other ranks go to this rank's slot in their receive buffer; this rank's own rows
+      // (computed last) add the peers' arrived partial rows and the residual and are stored finished
+      const bool rs = cp.mode == COMM_RS;
+      const bool rs_own = rs && owner == cp.rank;
+      const int blk_loc = 2 * mloc + (int)rank;            // 128-row block inside the owner's rows
+      const CUtensorMap* dmap = (rs && !rs_own) ? &xm.m[owner] : &tmD;
+      const int drow = rs ? blk_loc * 128 + quad * 32 : m0 + quad * 32;
+      const float alpha = 1.f;
+      if (rs_own) {
+        if (lane == 0 && !wait_ge<true>(cp.peer_cnt[cp.rank] + blk_loc, cp.cnt_target, p.status, 6)) ok = false;
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) { *abort_flag = 1; break; }
+        __threadfence_system();
+      }
 #pragma unroll 1
       for (int c = 0; c < TN; c += cw) {
         uint32_t r0[32], r1[32];
@@ -209,8 +249,37 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
               a0 += load_bias(p.bias, col + 2 * i, p.N, p.lp_fmt); a1 += load_bias(p.bias, col + 2 * i + 1, p.N, p.lp_fmt);
               b0 += load_bias(p.bias, col + 32 + 2 * i, p.N, p.lp_fmt); b1 += load_bias(p.bias, col + 33 + 2 * i, p.N, p.lp_fmt);
             }
-            w[i] = pack2(a0, a1, p.lp_fmt);
-            w[16 + i] = pack2(b0, b1, p.lp_fmt);
+            r0[2 * i] = __float_as_uint(a0 * alpha); r0[2 * i + 1] = __float_as_uint(a1 * alpha);
+            r1[2 * i] = __float_as_uint(b0 * alpha); r1[2 * i + 1] = __float_as_uint(b1 * alpha);
+          }
+          if (rs_own && col < p.N) {
+            const size_t rrow = (size_t)(drow + lane);
+            auto add_row = [&](const uint16_t* src) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * q);
+                const uint32_t* ww = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+                for (int k2 = 0; k2 < 4; ++k2) {
+                  const float2 f = p.lp_fmt ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[k2]))
+                                            : __half22float2(*reinterpret_cast<const __half2*>(&ww[k2]));
+                  uint32_t* dst = (q < 4) ? &r0[8 * q + 2 * k2] : &r1[8 * (q - 4) + 2 * k2];
+                  dst[0] = __float_as_uint(__uint_as_float(dst[0]) + f.x);
+                  dst[1] = __float_as_uint(__uint_as_float(dst[1]) + f.y);
+                }
+              }
+            };
+            const uint16_t* recv = reinterpret_cast<const uint16_t*>(cp.peer_recv[cp.rank]);
+            const size_t slot_stride = (size_t)cp.bpr * BM * p.N;
+            for (int sl = 0; sl < cp.tp; ++sl)
+              if (sl != cp.rank) add_row(recv + (size_t)sl * slot_stride + rrow * p.N + col);
+            if (cp.residual != nullptr)
+              add_row(reinterpret_cast<const uint16_t*>(cp.residual) + rrow * cp.ld_res + col);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            w[i] = pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]), p.lp_fmt);
+            w[16 + i] = pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]), p.lp_fmt);
           }
         } else {
 #pragma unroll
@@ -226,12 +295,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
         fence_async_smem();
         __syncwarp();
-        if (lane == 0 && col < p.N && drow < p.M) {
-          if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(&tmD, smem_u32(stage), col, drow);
-          else tma_store_2d(&tmD, smem_u32(stage), col, drow);
+        if (lane == 0 && col < p.N && (rs || drow < p.M)) {
+          if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(dmap, smem_u32(stage), col, drow);
+          else tma_store_2d(dmap, smem_u32(stage), col, drow);
           bulk_commit();
         }
         epi_buf ^= 1;
+      }
+      if (rs && !rs_own && lane == 0) {
+        bulk_wait<0>();                        // this warp's 32 rows of the tile have landed in the owner's slot
+        fence_proxy_async_all();
+        __threadfence_system();
+        red_release_sys_add(cp.peer_cnt[owner] + blk_loc, 1u);
       }
       fence_before_sync();
       __syncwarp();
@@ -248,8 +323,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const GemmParams& p,
-                        int sm_count, cudaStream_t st) {
+static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const ExtraMaps& xm,
+                        const GemmParams& p, const CommParams& cp, int sm_count, cudaStream_t st) {
   using S = Gemm2Smem;
   auto kern = gemm2_kernel<A_MN, B_MN>;
   static bool attr_set = false;
@@ -260,18 +335,26 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   }
   const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
   int pairs = sm_count / 2;
-  if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, p);
+  if (tiles < pairs && cp.mode != COMM_AG) pairs = tiles;          // all-gather mode: workers + GEMM pairs, all resident
+  kern<<<2 * pairs, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, xm, p, cp);
   MLB_CHECK_LAUNCH();
   return 0;
 }
 
 // Same contract as run_gemm (plain mode); the output must be TMA-addressable (16-byte aligned rows).
 static int run_gemm2(int lp_fmt, const void* A, long lda, int a_mn, const void* B, long ldb, int b_mn, void* D, long ldd,
-                     int out_mode, const void* bias, int M, int N, int K, int sms, int* status, cudaStream_t st) {
+                     int out_mode, const void* bias, int M, int N, int K, int sms, int* status, cudaStream_t st,
+                     const CommParams* cp_in = nullptr, const ExtraMaps* xm_in = nullptr) {
+  static const ExtraMaps kNoMaps = {};
+  static const CommParams kNoComm = {};
+  const CommParams& cp = cp_in ? *cp_in : kNoComm;
+  const ExtraMaps& xm = xm_in ? *xm_in : kNoMaps;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
   const int esz = (out_mode == OUT_LP) ? 2 : 4;
+  int M_d = M;                                      // rows of the output map
+  if (cp.mode == COMM_RS) { D = cp.out; ldd = cp.ld_out; M_d = cp.bpr * BM; }   // only this rank's rows are output
   if ((((size_t)ldd * esz) % 16) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
+  if (cp.mode != COMM_NONE && ((cp.bpr & 1) || a_mn)) return -7;               // 256-row tiles must not straddle ranks
   CUtensorMap tmA, tmB, tmD;
   int rc;
   uint64_t dims[2], strides[1]; uint32_t box[2];
@@ -284,7 +367,7 @@ static int run_gemm2(int lp_fmt, const void* A, long lda, int a_mn, const void* 
   strides[0] = (uint64_t)ldb * 2;
   if ((rc = make_tmap(&tmB, B, 2, dims, strides, box))) return rc;
   {
-    uint64_t dd[2] = {(uint64_t)N, (uint64_t)M}, ds[1] = {(uint64_t)ldd * esz};
+    uint64_t dd[2] = {(uint64_t)N, (uint64_t)M_d}, ds[1] = {(uint64_t)ldd * esz};
     uint32_t db[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
     if ((rc = make_tmap(&tmD, D, 2, dd, ds, db, esz))) return rc;
   }
@@ -297,10 +380,10 @@ static int run_gemm2(int lp_fmt, const void* A, long lda, int a_mn, const void* 
     if (env_gm < 0) { const char* e = getenv("MLB_GEMM_RASTER_M"); env_gm = e ? atoi(e) : 0; }
     p.raster_m = env_gm > 0 ? env_gm : 16;
   }
-  if (!a_mn && !b_mn) return launch_gemm2<false, false>(tmA, tmB, tmD, p, sms, st);
-  if (!a_mn && b_mn) return launch_gemm2<false, true>(tmA, tmB, tmD, p, sms, st);
-  if (a_mn && !b_mn) return launch_gemm2<true, false>(tmA, tmB, tmD, p, sms, st);
-  return launch_gemm2<true, true>(tmA, tmB, tmD, p, sms, st);
+  if (!a_mn && !b_mn) return launch_gemm2<false, false>(tmA, tmB, tmD, xm, p, cp, sms, st);
+  if (!a_mn && b_mn) return launch_gemm2<false, true>(tmA, tmB, tmD, xm, p, cp, sms, st);
+  if (a_mn && !b_mn) return launch_gemm2<true, false>(tmA, tmB, tmD, xm, p, cp, sms, st);
+  return launch_gemm2<true, true>(tmA, tmB, tmD, xm, p, cp, sms, st);
 }
 
 }  // namespace mlb

@@ -5,8 +5,16 @@
 // They replace the userbuffer-overlapped GEMMs the reference configures through
 // megatron/training/initialize.py:238-294 and megatron/core/extensions/transformer_engine.py:188-221.
 #include "gemm_core.cuh"
+#include "gemm2.cuh"
 
 using namespace mlb;
+
+// MLB_GEMM_PAIR=0 selects the single-CTA kernel for the fused products too
+static bool pair_ok() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("MLB_GEMM_PAIR"); v = (e && e[0] == '0') ? 0 : 1; }
+  return v == 1;
+}
 
 // peer_x / peer_sig: host arrays of tp device addresses (symmetric-memory mappings, this rank's own included).
 // gathered: local [tp*rows_per_rank, K]; chunk_flags: local uint32[tp*rows_per_rank/128]; comm_counter: local uint32.
@@ -30,6 +38,13 @@ MLB_API int mlb_ag_gemm(int lp_fmt, const void* const* peer_x, uint32_t* const* 
     uint32_t box[2] = {BK, BM};
     int rc = make_tmap(&xm.m[0], peer_x[rank], 2, dims, strides, box);
     if (rc) return rc;
+  }
+  // CTA-pair kernel when 256-row tiles fit the rank layout and the output is TMA-addressable
+  if (pair_ok() && (cp.bpr % 2 == 0) && (n_comm % 2 == 0) && N >= 256) {
+    const int esz = out_mode == OUT_LP ? 2 : 4;
+    if ((((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0))
+      return run_gemm2(lp_fmt, gathered, K, 0, B, ldb, b_mn, D, ldd, out_mode, bias, tp * rows_per_rank, N, K, sms,
+                       status, st, &cp, &xm);
   }
   return run_gemm(lp_fmt, gathered, K, 0, B, ldb, b_mn, D, ldd, out_mode, bias, tp * rows_per_rank, N, K, sms, status,
                   cp, st, &xm);
@@ -56,6 +71,10 @@ MLB_API int mlb_gemm_rs(int lp_fmt, const void* A, long lda, const void* B, long
     int rc = make_tmap(&xm.m[q], slot, 2, dims, strides, box);
     if (rc) return rc;
   }
+  if (pair_ok() && (cp.bpr % 2 == 0) && N >= 256 && (((size_t)ld_out * 2) % 16 == 0) &&
+      ((reinterpret_cast<uintptr_t>(out) & 15) == 0))
+    return run_gemm2(lp_fmt, A, lda, 0, B, ldb, b_mn, out, ld_out, OUT_LP, nullptr, tp * rows_per_rank, N, K,
+                     sm_count_cached(), status, st, &cp, &xm);
   return run_gemm(lp_fmt, A, lda, 0, B, ldb, b_mn, out /*unused*/, ld_out, OUT_LP, nullptr, tp * rows_per_rank, N, K,
                   sm_count_cached(), status, cp, st, &xm);
 }
