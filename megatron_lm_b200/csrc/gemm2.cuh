@@ -1,12 +1,13 @@
 // CTA-pair variant of the bf16/fp16 GEMM (plain mode): two CTAs of one cluster (one TPC) compute a 256 x 256 output
 // tile with `tcgen05.mma.cta_group::2`.  Each CTA stages 128 rows of A and 128 of the 256 B rows per K step, so a
 // stage is 32 KB per SM instead of 48 KB - the L2 -> shared traffic per flop drops by a third, which is what
-// limits the single-CTA kernel - and six stages fit.  The accumulator rows [128 r, 128 r + 128) live in CTA r's
+// limits the single-CTA kernel.  Five stages and eight epilogue warps per CTA (two per TMEM lane quadrant, each
+// taking half of the tile's columns) fit in shared memory.  The accumulator rows [128 r, 128 r + 128) live in CTA r's
 // tensor memory; each CTA drains its own half.
 //   * full[s]   lives in the leader (even) CTA: its producer posts the 64 KB expectation, both CTAs' TMA loads
 //               complete on it (plain per-CTA loads, the barrier is addressed through the cluster window);
 //   * empty[s], tfull[a] exist in both CTAs and are signalled by the leader's commit with a 2-CTA mask;
-//   * tempty[a] lives in the leader: the eight epilogue warps of the pair arrive on it.
+//   * tempty[a] lives in the leader: the sixteen epilogue warps of the pair arrive on it.
 // Every wait is bounded (status word), like in the single-CTA kernel.
 #pragma once
 #include "gemm_core.cuh"
@@ -53,16 +54,18 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t mask) {
                ::"r"(bar), "h"(mask) : "memory");
 }
 
+constexpr int kGemm2Threads = 320;    // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two warps per TMEM lane quadrant)
+
 struct Gemm2Smem {
-  static constexpr int kStages = 6;
+  static constexpr int kStages = 5;
   static constexpr int kABytes = 128 * BK * 2;          // this CTA's 128 rows of A
   static constexpr int kBBytes = 128 * BK * 2;          // this CTA's 128 of the tile's 256 B rows
-  static constexpr int kEpiBytes = 4 * 2 * 4096;
+  static constexpr int kEpiBytes = 8 * 2 * 4096;        // per epilogue warp: two 32-row x 128-byte staging buffers
   static constexpr int kBytes = kStages * (kABytes + kBBytes) + kEpiBytes + 1024 + 256;
 };
 
 template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemm2Threads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p,
              const CommParams cp) {
@@ -94,7 +97,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const bool leader = rank == 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 16); }
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmD);
@@ -200,9 +203,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs): warp w drains
+    // TMEM lanes of quadrant w % 4; warps 2..5 take tile columns [0, 128), warps 6..9 columns [128, 256)
     const int quad = warp & 3;
+    const int chalf = (warp - 2) >> 2;
     int t = 0, epi_buf = 0;
+    int pend_owner = -1, pend_blk = 0;                    // reduce-scatter: tile whose arrival signal is still owed
     bool ok = true;
     const uint32_t tempty_leader0 = map_to_cta(tempty(0), 0);
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
@@ -223,6 +229,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const CUtensorMap* dmap = (rs && !rs_own) ? &xm.m[owner] : &tmD;
       const int drow = rs ? blk_loc * 128 + quad * 32 : m0 + quad * 32;
       const float alpha = 1.f;
+      int n_groups = 0;
+      if (rs_own && lane == 0 && pend_owner >= 0) {       // last tile sent to a peer: flush its signal
+        bulk_wait<0>(); fence_proxy_async_all(); __threadfence_system();
+        red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+        pend_owner = -1;
+      }
       if (rs_own) {
         if (lane == 0 && !wait_ge<true>(cp.peer_cnt[cp.rank] + blk_loc, cp.cnt_target, p.status, 6)) ok = false;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -230,7 +242,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         __threadfence_system();
       }
 #pragma unroll 1
-      for (int c = 0; c < TN; c += cw) {
+      for (int c = chalf * 128; c < chalf * 128 + 128; c += cw) {
         uint32_t r0[32], r1[32];
         tmem_ld32(t_row + (uint32_t)c, r0);
         if (cw == 64) tmem_ld32(t_row + (uint32_t)c + 32, r1);
@@ -299,20 +311,32 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(dmap, smem_u32(stage), col, drow);
           else tma_store_2d(dmap, smem_u32(stage), col, drow);
           bulk_commit();
+          ++n_groups;
         }
         epi_buf ^= 1;
       }
       if (rs && !rs_own && lane == 0) {
-        bulk_wait<0>();                        // this warp's 32 rows of the tile have landed in the owner's slot
-        fence_proxy_async_all();
-        __threadfence_system();
-        red_release_sys_add(cp.peer_cnt[owner] + blk_loc, 1u);
+        // Signal one tile late: waiting here for this tile's stores to cross NVLink would stall the warp for a
+        // round trip per tile.  Everything older than the groups just committed has completed after this wait.
+        if (pend_owner >= 0) {
+          bulk_wait_upto(n_groups);
+          fence_proxy_async_all();
+          __threadfence_system();
+          red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+        }
+        pend_owner = owner; pend_blk = blk_loc;
       }
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8u * (uint32_t)acc);
     }
-    if (lane == 0) bulk_wait<0>();
+    if (lane == 0) {
+      bulk_wait<0>();
+      if (pend_owner >= 0) {
+        fence_proxy_async_all(); __threadfence_system();
+        red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+      }
+    }
   }
   // ---------------------------------------------------------------- teardown: nobody leaves while the peer may
   // still signal this CTA's barriers or read its operand tiles
@@ -336,7 +360,7 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
   int pairs = sm_count / 2;
   if (tiles < pairs && cp.mode != COMM_AG) pairs = tiles;          // all-gather mode: workers + GEMM pairs, all resident
-  kern<<<2 * pairs, kGemmThreads, S::kBytes, st>>>(tmA, tmB, tmD, xm, p, cp);
+  kern<<<2 * pairs, kGemm2Threads, S::kBytes, st>>>(tmA, tmB, tmD, xm, p, cp);
   MLB_CHECK_LAUNCH();
   return 0;
 }

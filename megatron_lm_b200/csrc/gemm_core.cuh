@@ -362,6 +362,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const float alpha = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
     int t = 0;
     int epi_buf = 0;
+    int pend_owner = -1, pend_blk = 0;                    // reduce-scatter: tile whose arrival signal is still owed
     bool ok = true;
     for (int tile = cta; tile < num_tiles && ok; tile += n_cta, ++t) {
       const int acc = t & 1;
@@ -391,6 +392,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const bool rs_own = cp.mode == COMM_RS && tc.owner == cp.rank;
         const CUtensorMap* dmap = (cp.mode == COMM_RS && !rs_own) ? &xm.m[tc.owner] : &tmD;
         const int drow = (cp.mode == COMM_RS) ? tc.m_local * BM + quad * 32 : m0 + quad * 32;
+        int n_groups = 0;
+        if (rs_own && lane == 0 && pend_owner >= 0) {     // last tile sent to a peer: flush its signal
+          bulk_wait<0>(); fence_proxy_async_all(); __threadfence_system();
+          red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+          pend_owner = -1;
+        }
         if (rs_own) {
           if (lane == 0 && !wait_ge<true>(cp.peer_cnt[cp.rank] + tc.m_local, cp.cnt_target, p.status, 6)) ok = false;
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -468,15 +475,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (p.out_mode == OUT_F32_ACC) tma_reduce_add_2d(dmap, smem_u32(stage), col, drow);
             else tma_store_2d(dmap, smem_u32(stage), col, drow);
             bulk_commit();
+            ++n_groups;
           }
           epi_buf ^= 1;
         }
-        if (cp.mode == COMM_RS && !rs_own && lane == 0) {
-          bulk_wait<0>();                      // this warp's 32 rows of the tile have landed in the owner's slot
+      if (cp.mode == COMM_RS && !rs_own && lane == 0) {
+        // Signal one tile late: waiting here for this tile's stores to cross NVLink would stall the warp for a
+        // round trip per tile.  Everything older than the groups just committed has completed after this wait.
+        if (pend_owner >= 0) {
+          bulk_wait_upto(n_groups);
           fence_proxy_async_all();
           __threadfence_system();
-          red_release_sys_add(cp.peer_cnt[tc.owner] + tc.m_local, 1u);
+          red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
         }
+        pend_owner = tc.owner; pend_blk = tc.m_local;
+      }
       } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
@@ -538,8 +551,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty(acc));
     }
+    if (lane == 0) {
+      if (p.tma_out) bulk_wait<0>();
+      if (pend_owner >= 0) {
+        fence_proxy_async_all(); __threadfence_system();
+        red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+      }
+    }
   }
-  if (p.tma_out && warp >= 2 && lane == 0) bulk_wait<0>();     // staged stores have landed
   // ---------------------------------------------------------------- teardown
   fence_before_sync();
   __syncthreads();

@@ -104,6 +104,16 @@ template <int N> __device__ __forceinline__ void bulk_wait_read() {
 template <int N> __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+// wait until at most n (0..4) of this thread's most recent bulk groups are still pending
+__device__ __forceinline__ void bulk_wait_upto(int n) {
+  switch (n) {
+    case 0: bulk_wait<0>(); break;
+    case 1: bulk_wait<1>(); break;
+    case 2: bulk_wait<2>(); break;
+    case 3: bulk_wait<3>(); break;
+    default: bulk_wait<4>(); break;
+  }
+}
 // make generic-proxy writes to shared memory visible to the async proxy (TMA / tcgen05 operand reads)
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

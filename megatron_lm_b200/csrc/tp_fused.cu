@@ -79,5 +79,10 @@ MLB_API int mlb_gemm_rs(int lp_fmt, const void* A, long lda, const void* B, long
                   sm_count_cached(), status, cp, st, &xm);
 }
 
-// Arrivals one mlb_gemm_rs call adds to each row-block counter.
-MLB_API int mlb_gemm_rs_arrivals(int tp, int N) { return (tp - 1) * ((N + ((N > 128) ? 256 : 128) - 1) / ((N > 128) ? 256 : 128)) * 4; }
+// Arrivals one mlb_gemm_rs call adds to each 128-row block counter: one per epilogue warp per column tile from every
+// peer (4 warps in the single-CTA kernel, 8 in the CTA-pair kernel; the choice mirrors mlb_gemm_rs).
+MLB_API int mlb_gemm_rs_arrivals(int tp, int N, int rows_per_rank) {
+  const int bn = (N > 128) ? 256 : 128;
+  const bool pair = pair_ok() && ((rows_per_rank / BM) % 2 == 0) && N >= 256;
+  return (tp - 1) * ((N + bn - 1) / bn) * (pair ? 8 : 4);
+}

@@ -35,7 +35,7 @@ os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 _lib.register_signatures({
     "mlb_ag_gemm": "ipppppiiiiiipliplipiipp",
     "mlb_gemm_rs": "iplplippiiiiplpliipp",
-    "mlb_gemm_rs_arrivals": "ii",
+    "mlb_gemm_rs_arrivals": "iii",
 })
 
 
@@ -123,7 +123,7 @@ class FusedTP:
         which = self.rs_calls & 1
         self.rs_calls += 1
         L = _lib.lib()
-        self.cnt_expected[which] += L.mlb_gemm_rs_arrivals(self.tp, N)
+        self.cnt_expected[which] += L.mlb_gemm_rs_arrivals(self.tp, N, self.rows)
         out = torch.empty(self.rows, N, dtype=self.dtype, device=a.device)
         res2 = None if residual is None else residual.reshape(self.rows, N)
         st = _lib.status_word()
