@@ -418,3 +418,100 @@ def load_model_from_sharded(model: torch.nn.Module, loaded: Dict[str, torch.Tens
             if parts:
                 dim = int(getattr(p, "partition_dim", 0))
                 p.copy_(torch.cat([t.to(p.device) for t in parts], dim=dim).view(p.shape))
+
+
+# ----------------------------------------------------------------------------- factories and parallel strategies
+@dataclass
+class ShardedTensorFactory:
+    """A tensor whose on-disk form differs from its in-memory form: ``build_fn(key, data, replica_id)`` turns it
+    into a structure of ShardedTensors before saving / loading and ``merge_fn`` turns the loaded structure back
+    (reference: dist_checkpointing/mapping.py:606; used e.g. to store a fused [gate; up] weight as two tensors)."""
+    key: str
+    data: torch.Tensor
+    build_fn: Any
+    merge_fn: Any
+    replica_id: ReplicaId = 0
+
+    def build(self):
+        return self.build_fn(self.key, self.data, self.replica_id)
+
+
+def apply_factories(sharded_state_dict):
+    """Replace every factory in place by the structure it builds; returns the factories by path for ``apply_factory_merges``."""
+    found = {}
+
+    def walk(d, path=()):
+        it = d.items() if isinstance(d, dict) else enumerate(d) if isinstance(d, list) else ()
+        for k, v in list(it):
+            if isinstance(v, ShardedTensorFactory):
+                found[path + (k,)] = v
+                d[k] = v.build()
+            elif isinstance(v, (dict, list)):
+                walk(v, path + (k,))
+    walk(sharded_state_dict)
+    return found
+
+
+def apply_factory_merges(loaded_state_dict, factories):
+    for path, f in factories.items():
+        d = loaded_state_dict
+        for k in path[:-1]:
+            d = d[k]
+        d[path[-1]] = f.merge_fn(d[path[-1]])
+    return loaded_state_dict
+
+
+def distribute_main_replicas(sharded_state_dict, group=None):
+    """Fully parallel save: shards replicated over the ranks of ``group`` (data-parallel copies) are re-assigned so
+    that each is written by exactly one rank and the bytes written per rank are balanced (greedy, largest first;
+    reference: strategies/fully_parallel.py:48, exchange_utils.py:121).  Marks the chosen copy ``replica_id = 0``
+    and every other copy non-zero; returns the bytes this rank will write."""
+    if group is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return sum(st.data.numel() * st.data.element_size() for _, st in extract_sharded(sharded_state_dict)[0]
+                   if st.is_main_replica())
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    tensors, _, _ = extract_sharded(sharded_state_dict)
+    mine = {}
+    for _, st in tensors:
+        ident = (st.key, tuple(st.global_offset), None if st.flattened_range is None else
+                 (st.flattened_range.start, st.flattened_range.stop))
+        mine[ident] = st
+    sizes = {k: v.data.numel() * v.data.element_size() for k, v in mine.items()}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, sizes, group=group)
+    holders = {}
+    for r, d in enumerate(gathered):
+        for k, n in d.items():
+            holders.setdefault(k, (n, []))[1].append(r)
+    load = [0] * world
+    owner = {}
+    for k, (n, rs) in sorted(holders.items(), key=lambda kv: (-kv[1][0], str(kv[0]))):
+        r = min(rs, key=lambda x: (load[x], x))
+        owner[k] = r
+        load[r] += n
+    for k, st in mine.items():
+        st.replica_id = 0 if owner[k] == rank else 1
+    return load[rank]
+
+
+def fully_parallel_load(sharded_state_dict, checkpoint_dir: str, group=None, **kw):
+    """Fully parallel load: each shard that several ranks of ``group`` need is read from storage by one of them and
+    broadcast to the others (reference: strategies/fully_parallel.py:141)."""
+    if group is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return load(sharded_state_dict, checkpoint_dir, **kw)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    tensors, _, _ = extract_sharded(sharded_state_dict)
+    idents = []
+    for _, st in tensors:
+        idents.append((st.key, tuple(st.global_offset), tuple(st.full_local_shape()),
+                       None if st.flattened_range is None else (st.flattened_range.start, st.flattened_range.stop)))
+    gathered = [None] * world
+    dist.all_gather_object(gathered, idents, group=group)
+    same = all(g == gathered[0] for g in gathered)
+    if not same:                                    # ranks need different shards: everyone reads its own
+        return load(sharded_state_dict, checkpoint_dir, **kw)
+    loaded = load(sharded_state_dict, checkpoint_dir, **kw) if rank == 0 else None
+    # rank 0 of the group read everything once; the others receive it
+    box = [loaded]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0), group=group)
+    return box[0]
