@@ -11,11 +11,16 @@ namespace mlb {
 
 constexpr int kCeThreads = 256;
 
+// Peer-memory variant of the cross-rank combination: instead of leaving its four per-row statistics for an
+// all-reduce, each rank stores them (one 16-byte store per peer and row) into slot `rank` of every rank's
+// statistics table [tp][rows][4]; after a barrier ce_combine_kernel reads the tp slots of its own table.
+struct CePeers { float4* table[8]; int n, rank; long rows; };
+
 template <typename T>
 __global__ void __launch_bounds__(kCeThreads)
 ce_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ target, float* __restrict__ row_max,
               float* __restrict__ row_sumexp, float* __restrict__ row_tgt, float* __restrict__ row_sumx,
-              int v_local, long ld, int64_t v0) {
+              int v_local, long ld, int64_t v0, const CePeers peers) {
   __shared__ float sh[64];
   const size_t row = blockIdx.x;
   const T* x = logits + row * ld;
@@ -48,8 +53,29 @@ ce_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ target, 
     row_sumexp[row] = s;
     row_sumx[row] = sx;
     const int64_t t = target[row] - v0;
-    row_tgt[row] = (t >= 0 && t < v_local) ? to_f(x[t]) : 0.f;
+    const float tg = (t >= 0 && t < v_local) ? to_f(x[t]) : 0.f;
+    row_tgt[row] = tg;
+    for (int q = 0; q < peers.n; ++q)
+      peers.table[q][(size_t)peers.rank * peers.rows + row] = make_float4(gm, s, tg, sx);
   }
+}
+
+// loss, global max and global sum(exp(x - gmax)) per row from the tp slots of this rank's statistics table
+__global__ void ce_combine_kernel(const float4* __restrict__ table, int tp, long rows, float label_smoothing, int v_total,
+                                  float* __restrict__ loss, float* __restrict__ gmax, float* __restrict__ gsum) {
+  const long row = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float m = -INFINITY;
+  for (int q = 0; q < tp; ++q) m = fmaxf(m, table[(size_t)q * rows + row].x);
+  float s = 0.f, tg = 0.f, sx = 0.f;
+  for (int q = 0; q < tp; ++q) {
+    const float4 v = table[(size_t)q * rows + row];
+    s += v.y * __expf(v.x - m); tg += v.z; sx += v.w;
+  }
+  const float lse = logf(s) + m;
+  float l = lse - tg;
+  if (label_smoothing > 0.f) l = (1.f - label_smoothing) * l + label_smoothing * (lse - sx / (float)v_total);
+  loss[row] = l; gmax[row] = m; gsum[row] = s;
 }
 
 // grad = (softmax - onehot*(1-ls) - ls/V_total) * gscale[row]; written to dlogits (may alias logits)
@@ -93,7 +119,29 @@ MLB_API int mlb_ce_fwd(int dtype, const void* logits, const int64_t* target, flo
                        cudaStream_t st) {
   if (ld % 8 || rows <= 0) return -3;
   MLB_DISPATCH_ACT(dtype, T, (ce_fwd_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>(
-      (const T*)logits, target, row_max, row_sumexp, row_tgt, row_sumx, v_local, ld, v0)));
+      (const T*)logits, target, row_max, row_sumexp, row_tgt, row_sumx, v_local, ld, v0, CePeers{})));
+  MLB_CHECK_LAUNCH(); return 0;
+}
+// Same forward, additionally storing the row statistics into slot `rank` of every rank's table
+// (tables: host array of tp device addresses of float4 [tp][table_rows]).
+MLB_API int mlb_ce_fwd_peer(int dtype, const void* logits, const int64_t* target, float* row_max, float* row_sumexp,
+                            float* row_tgt, float* row_sumx, long rows, int v_local, long ld, int64_t v0,
+                            void* const* tables, int tp, int rank, long table_rows, cudaStream_t st) {
+  if (ld % 8 || rows <= 0 || tp > 8 || rows > table_rows) return -3;
+  CePeers pe = {};
+  pe.n = tp; pe.rank = rank; pe.rows = table_rows;
+  for (int i = 0; i < tp; ++i) pe.table[i] = reinterpret_cast<float4*>(tables[i]);
+  MLB_DISPATCH_ACT(dtype, T, (ce_fwd_kernel<T><<<(unsigned)rows, kCeThreads, 0, st>>>(
+      (const T*)logits, target, row_max, row_sumexp, row_tgt, row_sumx, v_local, ld, v0, pe)));
+  MLB_CHECK_LAUNCH(); return 0;
+}
+MLB_API int mlb_ce_combine(const void* table, int tp, long rows, long table_rows, float label_smoothing, int v_total,
+                           float* loss, float* gmax, float* gsum, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  // the table is laid out with table_rows per slot; only the first `rows` of each slot are valid
+  if (rows != table_rows) return -3;
+  ce_combine_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(reinterpret_cast<const float4*>(table), tp, rows,
+                                                                   label_smoothing, v_total, loss, gmax, gsum);
   MLB_CHECK_LAUNCH(); return 0;
 }
 MLB_API int mlb_ce_bwd(int dtype, const void* logits, const int64_t* target, const float* gmax, const float* gsum,

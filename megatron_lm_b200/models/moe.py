@@ -350,6 +350,29 @@ class GroupedMLP(nn.Module):
         return grouped_linear(a, self.weight2, tokens_per_expert), None
 
 
+class SequentialMLP(nn.Module):
+    """One ordinary MLP module per local expert, applied to that expert's slice of the sorted tokens
+    (reference: experts.py:988; parameter names ``local_experts.<e>.linear_fc{1,2}``).  Used when
+    ``moe_grouped_gemm`` is off, e.g. for checkpoints converted expert by expert."""
+
+    def __init__(self, num_local_experts: int, config: TransformerConfig):
+        super().__init__()
+        from .transformer import MLP
+        self.E = num_local_experts
+        self.local_experts = nn.ModuleList([MLP(config, ffn_hidden_size=config.moe_ffn_hidden_size, is_expert=True)
+                                            for _ in range(num_local_experts)])
+
+    def forward(self, tokens, tokens_per_expert):
+        splits = [int(v) for v in (tokens_per_expert.tolist() if torch.is_tensor(tokens_per_expert) else tokens_per_expert)]
+        outs, o = [], 0
+        for e, n in enumerate(splits):
+            x = tokens[o:o + n]
+            y, b = self.local_experts[e](x)
+            outs.append(y if b is None else y + b)
+            o += n
+        return (torch.cat(outs, dim=0) if outs else tokens.new_zeros(0, tokens.shape[-1])), None
+
+
 class SharedExpertMLP(nn.Module):
     """Dense MLP applied to every token next to the routed experts (reference: shared_experts.py:26)."""
 
@@ -499,7 +522,7 @@ class MoELayer(nn.Module):
         ep = state.get_expert_model_parallel_world_size() if state.model_parallel_is_initialized() else 1
         self.E_local = config.num_moe_experts // ep
         self.router = TopKRouter(config, layer_number)
-        self.experts = GroupedMLP(self.E_local, config)
+        self.experts = GroupedMLP(self.E_local, config) if config.moe_grouped_gemm else SequentialMLP(self.E_local, config)
         kind = config.moe_token_dispatcher_type
         if kind == "flex":
             self.token_dispatcher = MoEFusedPeerDispatcher(self.E_local, config)

@@ -47,6 +47,8 @@ _SIGS: Dict[str, str] = {
     "mlb_embedding_bwd": "ippplipp",
     "mlb_cast": "iipplfip",
     "mlb_ce_fwd": "ipppppp" "lilqp",
+    "mlb_ce_fwd_peer": "ipppppp" "lilq" "piil" "p",
+    "mlb_ce_combine": "pillfi" "ppp" "p",
     "mlb_ce_bwd": "ippppp" "p" "lilqfip",
     "mlb_adam": "ippppppi" "ppi" "fffff" "ppp",
     "mlb_adam_push": "pppppp" "i" "pi" "ppi" "fffff" "ppp",

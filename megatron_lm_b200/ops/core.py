@@ -7,6 +7,8 @@ implementation to fall back to.
 """
 from __future__ import annotations
 
+import ctypes
+
 import math
 from typing import Optional, Tuple
 
@@ -387,6 +389,39 @@ def _tp_reduce(t, op, group):
     return t
 
 
+_CE_PEER = {}
+
+
+class CrossEntropyPeerComm:
+    """Per-row statistics table in symmetric memory for the vocab-parallel cross entropy: every rank's forward kernel
+    stores its (max, sum exp, target logit, sum of logits) into all ranks' tables, a device-side barrier follows,
+    and a small kernel combines the slots - no all-reduce.  Enabled with ``MLB_CE_PEER=1`` (single node)."""
+
+    def __init__(self, group, rows: int):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.tp, self.rank, self.rows = torch.distributed.get_world_size(group), torch.distributed.get_rank(group), rows
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(self.tp * rows * 4, dtype=torch.float32, device=dev)
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = (ctypes.c_void_p * self.tp)(*[int(p) for p in self.hdl.buffer_ptrs])
+        self.hdl.barrier()
+
+    @staticmethod
+    def get(group, rows):
+        key = (id(group), rows)
+        if key not in _CE_PEER:
+            _CE_PEER[key] = CrossEntropyPeerComm(group, rows)
+        return _CE_PEER[key]
+
+
+def _ce_peer_enabled(group, lg) -> bool:
+    import os
+    return os.environ.get("MLB_CE_PEER", "0") == "1" and group is not None and torch.distributed.is_initialized() \
+        and 1 < torch.distributed.get_world_size(group) <= 8
+
+
 class _CrossEntropyFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, target, vocab_start, vocab_total, label_smoothing, group, inplace_backward):
@@ -395,6 +430,22 @@ class _CrossEntropyFn(torch.autograd.Function):
         tg = target.contiguous().view(-1)
         rows = lg.shape[0]
         stats = torch.empty(4, rows, dtype=torch.float32, device=lg.device)
+        if _ce_peer_enabled(group, lg):
+            comm = CrossEntropyPeerComm.get(group, rows)
+            L = _lib.lib()
+            comm.hdl.barrier()                   # the previous call's combine has read every slot
+            _lib.check(L.mlb_ce_fwd_peer(_lib.dt(lg), lg.data_ptr(), tg.data_ptr(), stats[0].data_ptr(),
+                                         stats[1].data_ptr(), stats[2].data_ptr(), stats[3].data_ptr(), rows, v_local,
+                                         lg.stride(0), vocab_start, comm.ptrs, comm.tp, comm.rank, comm.rows,
+                                         _lib.stream()), "ce_fwd_peer")
+            comm.hdl.barrier()                   # every rank's statistics have landed
+            out = torch.empty(3, rows, dtype=torch.float32, device=lg.device)
+            _lib.check(L.mlb_ce_combine(comm.buf.data_ptr(), comm.tp, rows, comm.rows, float(label_smoothing),
+                                        vocab_total, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+                                        _lib.stream()), "ce_combine")
+            ctx.save_for_backward(lg, tg, out[1], out[2])
+            ctx.cfg = (vocab_start, vocab_total, label_smoothing, inplace_backward, logits.shape)
+            return out[0].view(target.shape)
         _lib.check(_lib.lib().mlb_ce_fwd(_lib.dt(lg), lg.data_ptr(), tg.data_ptr(), stats[0].data_ptr(),
                                          stats[1].data_ptr(), stats[2].data_ptr(), stats[3].data_ptr(), rows,
                                          v_local, lg.stride(0), vocab_start, _lib.stream()), "ce_fwd")

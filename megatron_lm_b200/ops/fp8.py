@@ -161,3 +161,47 @@ def mxfp8_dequantize(q: torch.Tensor, scales: torch.Tensor, along_rows: bool = T
     if along_rows:
         return (v.view(rows, cols // 32, 32) * s.unsqueeze(-1)).view(rows, cols)
     return (v.view(rows // 32, 32, cols) * s.unsqueeze(1)).view(rows, cols)
+
+
+# ----------------------------------------------------------------------------- delayed scaling
+class DelayedScalingState:
+    """Scale taken from the amax history of *previous* steps (no extra pass over the tensor before the cast):
+    ``fp8_amax_history_len`` past maxima, reduced with ``max`` or ``most_recent``; scale = fp8_max / amax / 2^margin
+    (reference: the "delayed" recipe configured at megatron/core/fp8_utils.py:459-470 and its ``TEDelayedScaling``
+    wrapper, extensions/transformer_engine.py:1462)."""
+
+    def __init__(self, fmt: int = 0, history_len: int = 1, algo: str = "most_recent", margin: int = 0, device="cpu"):
+        self.fmt, self.algo, self.margin = fmt, algo, margin
+        self.history = torch.zeros(history_len, dtype=torch.float32, device=device)
+        self.scale = torch.ones(1, dtype=torch.float32, device=device)
+
+    def _update(self, amax: torch.Tensor) -> None:
+        self.history = torch.roll(self.history, 1)
+        self.history[0] = amax
+        ref = self.history.max() if self.algo == "max" else self.history[0]
+        s = _FMAX[self.fmt] / ref / (2.0 ** self.margin)
+        self.scale = torch.where((ref > 0) & torch.isfinite(s), s, self.scale).reshape(1)
+
+    def quantize(self, x: torch.Tensor, transpose: bool = False) -> Fp8Tensor:
+        """Cast with the current scale, then fold this tensor's amax into the history for the next call."""
+        x2 = x.reshape(-1, x.shape[-1])
+        scale = self.scale.to(x2.device)
+        q = (x2.float() * scale).clamp(-_FMAX[self.fmt], _FMAX[self.fmt]).to(_TORCH_FP8[self.fmt]).view(torch.uint8)
+        out = Fp8Tensor(q, q.t().contiguous() if transpose else None, (1.0 / scale).reshape(1), self.fmt)
+        self.history = self.history.to(x2.device)
+        self._update(x2.detach().float().abs().max())
+        return out
+
+
+def quantize_param_shard(master_shard: torch.Tensor, fmt: int = 0, amax_group=None) -> Fp8Tensor:
+    """FP8 copy of an fp32 master-weight shard for the parameter all-gather (``--fp8-param-gather``): the amax is
+    reduced over ``amax_group`` first so that every shard of one tensor uses the same scale
+    (reference: fp8_utils.py:394)."""
+    import torch.distributed as dist
+    a = master_shard.detach().float().abs().max().reshape(1)
+    if amax_group is not None and dist.is_initialized():
+        dist.all_reduce(a, op=dist.ReduceOp.MAX, group=amax_group)
+    scale = torch.where(a > 0, _FMAX[fmt] / a, torch.ones_like(a))
+    flat = master_shard.reshape(1, -1)
+    q = (flat.float() * scale).clamp(-_FMAX[fmt], _FMAX[fmt]).to(_TORCH_FP8[fmt]).view(torch.uint8)
+    return Fp8Tensor(q, None, 1.0 / scale, fmt)
