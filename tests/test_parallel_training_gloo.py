@@ -130,6 +130,12 @@ def test_tp2_pp2_sp_distopt(tmp_path, baseline):
     _close(_trajectory(tmp_path, 4, tp=2, pp=2, sp=True), baseline["llama"])
 
 
+def test_tp4_pp2_vpp2_eight_ranks(tmp_path, baseline):
+    """The 8-GPU layout of the headline benchmark (tensor 4 x pipeline 2 with 2 virtual stages, sequence parallel,
+    distributed optimizer) on 8 Gloo ranks."""
+    _close(baseline["gpt"], _trajectory(tmp_path, 8, tp=4, pp=2, vpp=2, sp=True, dist_opt=True, kind="gpt"))
+
+
 def _run_cp(rank, world, cp, comm, out_path):
     """Context-parallel training: every rank holds its zig-zag slice of each sequence."""
     from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig
