@@ -142,7 +142,7 @@ def run_ours(args):
         attention_dropout=0.0, bf16=True, params_dtype=torch.bfloat16, tensor_model_parallel_size=tp,
         pipeline_model_parallel_size=pp, virtual_pipeline_model_parallel_size=vpp, sequence_parallel=tp > 1,
         pipeline_dtype=torch.bfloat16, tp_comm_overlap=args.tp_comm_overlap and tp > 1, init_method_std=0.02,
-        overlap_p2p_comm=pp > 1)
+        overlap_p2p_comm=pp > 1, fp8=args.fp8, fp8_recipe="tensorwise" if args.fp8 else "delayed")
 
     def provider(pre_process=True, post_process=True, vp_stage=None):
         return GPTModel(cfg, vocab_size=M["vocab_size"], max_sequence_length=M["seq_length"], pre_process=pre_process,
@@ -237,7 +237,7 @@ def run_ours(args):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / args.gpus / BASELINE_TOKENS_PER_SEC_PER_GPU) if BASELINE_TOKENS_PER_SEC_PER_GPU else None,
-            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
+            "dtype": "fp8" if args.fp8 else "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
             "tokens_per_sec_per_gpu": value / args.gpus,
             "model_tflops_per_gpu": fl / (dev_ms / args.steps / 1e3) / 1e12 / args.gpus,
             "config": {"model": "llama2-7b (32L h4096 32 heads ffn11008 swiglu rmsnorm rope)" if not args.layers
@@ -277,6 +277,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a bench value)")
     ap.add_argument("--tp-comm-overlap", action="store_true", default=True)
     ap.add_argument("--no-tp-comm-overlap", dest="tp_comm_overlap", action="store_false")
+    ap.add_argument("--fp8", default=None, choices=["e4m3", "hybrid"],
+                    help="FP8 variant: layer linears run FP8 GEMMs with per-tensor scales (reported as dtype fp8)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
