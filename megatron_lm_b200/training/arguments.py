@@ -71,6 +71,12 @@ def build_parser(extra_args_provider: Optional[Callable] = None) -> argparse.Arg
     g.add_argument("--ec-data-shards", type=int, default=None, help="k: data members per stripe (default group size - m)")
     g.add_argument("--ec-parity-shards", type=int, default=1, help="m: parity members per stripe (losses tolerated)")
     g.add_argument("--ec-chunk-bytes", type=int, default=1 << 20)
+    g = parser.add_argument_group(title="peer-memory kernels")
+    g.add_argument("--peer-memory-collectives", action="store_true",
+                   help="distributed optimizer: gradient reduce-scatter as a pull kernel over NVLink peer memory and "
+                        "AdamW storing new weights into every rank's parameter buffer (single node)")
+    g.add_argument("--cross-entropy-peer-exchange", action="store_true",
+                   help="vocab-parallel cross entropy exchanges its row statistics through peer memory instead of all-reduces")
     if extra_args_provider is not None:
         parser = extra_args_provider(parser)
     return parser
@@ -250,6 +256,10 @@ def ddp_config_from_args(args) -> DistributedDataParallelConfig:
     kw["bucket_size"] = getattr(args, "ddp_bucket_size", None)
     kw["average_in_collective"] = getattr(args, "ddp_average_in_collective", False)
     kw["pad_buckets_for_high_nccl_busbw"] = getattr(args, "ddp_pad_buckets_for_high_nccl_busbw", False)
+    kw["peer_memory_collectives"] = getattr(args, "peer_memory_collectives", False)
+    if getattr(args, "cross_entropy_peer_exchange", False):
+        import os
+        os.environ["MLB_CE_PEER"] = "1"
     return DistributedDataParallelConfig(**kw)
 
 
