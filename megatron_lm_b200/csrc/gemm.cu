@@ -27,6 +27,14 @@ MLB_API int mlb_gemm_fp8(int a_fmt, int b_fmt, const void* A, long lda, const vo
                          int out_mode, int out_lp_fmt, const void* bias, const float* scale_a, const float* scale_b,
                          int M, int N, int K, int* status, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  {
+    static int pair = -1;
+    if (pair < 0) { const char* e = getenv("MLB_GEMM_PAIR"); pair = (e && e[0] == '0') ? 0 : 1; }
+    const int esz = out_mode == OUT_LP ? 2 : 4;
+    if (pair && M >= 256 && N >= 256 && (((size_t)ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(D) & 15) == 0))
+      return run_gemm2_fp8(a_fmt, b_fmt, A, lda, B, ldb, D, ldd, out_mode, out_lp_fmt, bias, scale_a, scale_b, M, N, K,
+                           sm_count_cached(), status, st);
+  }
   return run_gemm_fp8(a_fmt, b_fmt, A, lda, B, ldb, D, ldd, out_mode, out_lp_fmt, bias, scale_a, scale_b, M, N, K,
                       sm_count_cached(), status, st);
 }

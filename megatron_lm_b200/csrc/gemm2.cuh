@@ -48,6 +48,13 @@ __device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, u
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // one arrival on the barrier at this shared-memory offset in every CTA of `mask`, once the MMAs issued so far are done
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -64,7 +71,8 @@ struct Gemm2Smem {
   static constexpr int kBytes = kStages * (kABytes + kBBytes) + kEpiBytes + 1024 + 256;
 };
 
-template <bool A_MN, bool B_MN>
+// FP8 (both operands K-major bytes, 128 per 128-byte row, 32 per MMA) is a separate instantiation, see gemm_core.cuh.
+template <bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemm2Threads, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p,
@@ -111,7 +119,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
   const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int bk_elems = FP8 ? 2 * BK : BK;
+  const int num_kb = (p.K + bk_elems - 1) / bk_elems;
   const int first_cta = (cp.mode == COMM_AG) ? cp.n_comm : 0;
   const int pair = ((int)blockIdx.x - first_cta) >> 1, n_pairs = ((int)gridDim.x - first_cta) >> 1;
   const int gm = p.raster_m < tiles_m ? (p.raster_m > 0 ? p.raster_m : 1) : tiles_m;
@@ -154,7 +163,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           if (leader) mbar_expect_tx(full(stage), 2 * (S::kABytes + S::kBBytes));
           const uint32_t fbar = map_to_cta(full(stage), 0);
           const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
-          const int k0 = kb * BK;
+          const int k0 = kb * bk_elems;
           if constexpr (!A_MN) {
             if (own_rows) tma_load_2d_pair(a_dst, &xm.m[0], fbar, k0, mloc * 256 + 128 * (int)rank);
             else tma_load_2d_pair(a_dst, &tmA, fbar, k0, m0);              // box [64 k, 128 rows]
@@ -176,7 +185,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
-      const uint32_t idesc = make_idesc(256, TN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t idesc = FP8 ? make_idesc_f8(256, TN, p.a_fmt, p.b_fmt)
+                                 : make_idesc(256, TN, p.lp_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0; uint32_t phase = 0;
       int t = 0;
       bool ok = true;
@@ -194,7 +204,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           for (int k = 0; k < BK / UK; ++k) {
             const uint64_t da = A_MN ? make_desc(a_addr + k * 2048, 8192, 1024) : make_desc(a_addr + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_desc(b_addr + k * 2048, 8192, 1024) : make_desc(b_addr + k * 32, 16, 1024);
-            mma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (FP8) mma_f8_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else mma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           mma_commit_pair(empty(stage), 3);      // both CTAs may refill this stage once the MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -228,7 +239,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const int blk_loc = 2 * mloc + (int)rank;            // 128-row block inside the owner's rows
       const CUtensorMap* dmap = (rs && !rs_own) ? &xm.m[owner] : &tmD;
       const int drow = rs ? blk_loc * 128 + quad * 32 : m0 + quad * 32;
-      const float alpha = 1.f;
+      const float alpha = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
       int n_groups = 0;
       if (rs_own && lane == 0 && pend_owner >= 0) {       // last tile sent to a peer: flush its signal
         bulk_wait<0>(); fence_proxy_async_all(); __threadfence_system();
@@ -255,14 +266,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         if (p.out_mode == OUT_LP) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-            float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+            float a0 = __uint_as_float(r0[2 * i]) * alpha, a1 = __uint_as_float(r0[2 * i + 1]) * alpha;
+            float b0 = __uint_as_float(r1[2 * i]) * alpha, b1 = __uint_as_float(r1[2 * i + 1]) * alpha;
             if (p.bias != nullptr) {
               a0 += load_bias(p.bias, col + 2 * i, p.N, p.lp_fmt); a1 += load_bias(p.bias, col + 2 * i + 1, p.N, p.lp_fmt);
               b0 += load_bias(p.bias, col + 32 + 2 * i, p.N, p.lp_fmt); b1 += load_bias(p.bias, col + 33 + 2 * i, p.N, p.lp_fmt);
             }
-            r0[2 * i] = __float_as_uint(a0 * alpha); r0[2 * i + 1] = __float_as_uint(a1 * alpha);
-            r1[2 * i] = __float_as_uint(b0 * alpha); r1[2 * i + 1] = __float_as_uint(b1 * alpha);
+            r0[2 * i] = __float_as_uint(a0); r0[2 * i + 1] = __float_as_uint(a1);
+            r1[2 * i] = __float_as_uint(b0); r1[2 * i + 1] = __float_as_uint(b1);
           }
           if (rs_own && col < p.N) {
             const size_t rrow = (size_t)(drow + lane);
@@ -296,7 +307,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            float a = __uint_as_float(r0[i]);
+            float a = __uint_as_float(r0[i]) * alpha;
             if (p.bias != nullptr) a += load_bias(p.bias, col + i, p.N, p.lp_fmt);
             w[i] = __float_as_uint(a);
           }
@@ -346,11 +357,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   if (warp == 1) { fence_after_sync(); tmem_dealloc2(tmem_base, 512); }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FP8 = false>
 static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const ExtraMaps& xm,
                         const GemmParams& p, const CommParams& cp, int sm_count, cudaStream_t st) {
   using S = Gemm2Smem;
-  auto kern = gemm2_kernel<A_MN, B_MN>;
+  auto kern = gemm2_kernel<A_MN, B_MN, FP8>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
@@ -408,6 +419,35 @@ static int run_gemm2(int lp_fmt, const void* A, long lda, int a_mn, const void* 
   if (!a_mn && b_mn) return launch_gemm2<false, true>(tmA, tmB, tmD, xm, p, cp, sms, st);
   if (a_mn && !b_mn) return launch_gemm2<true, false>(tmA, tmB, tmD, xm, p, cp, sms, st);
   return launch_gemm2<true, true>(tmA, tmB, tmD, xm, p, cp, sms, st);
+}
+
+// 8-bit operands on the CTA-pair kernel: A [M, K], B [N, K] bytes, K-major; D = (A B^T) * (*scale_a) * (*scale_b) (+ bias)
+static int run_gemm2_fp8(int a_fmt, int b_fmt, const void* A, long lda, const void* B, long ldb, void* D, long ldd,
+                         int out_mode, int out_lp_fmt, const void* bias, const float* scale_a, const float* scale_b, int M,
+                         int N, int K, int sms, int* status, cudaStream_t st) {
+  if ((lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  const int esz = (out_mode == OUT_LP) ? 2 : 4;
+  if ((((size_t)ldd * esz) % 16) || (reinterpret_cast<uintptr_t>(D) & 15)) return -3;
+  CUtensorMap tmA, tmB, tmD;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M}, strides[1] = {(uint64_t)lda};
+    uint32_t box[2] = {128, 128};
+    if ((rc = make_tmap(&tmA, A, 2, dims, strides, box, 1))) return rc;
+    dims[1] = (uint64_t)N; strides[0] = (uint64_t)ldb;
+    if ((rc = make_tmap(&tmB, B, 2, dims, strides, box, 1))) return rc;
+    uint64_t dd[2] = {(uint64_t)N, (uint64_t)M}, ds[1] = {(uint64_t)ldd * esz};
+    uint32_t db[2] = {(uint32_t)(esz == 2 ? 64 : 32), 32};
+    if ((rc = make_tmap(&tmD, D, 2, dd, ds, db, esz))) return rc;
+  }
+  GemmParams p = {};
+  p.tma_out = 1;
+  p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = out_lp_fmt;
+  p.status = status; p.fp8 = 1; p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.scale_a = scale_a; p.scale_b = scale_b;
+  p.raster_m = 16;
+  static const ExtraMaps kNoMaps = {};
+  static const CommParams kNoComm = {};
+  return launch_gemm2<false, false, true>(tmA, tmB, tmD, kNoMaps, p, kNoComm, sms, st);
 }
 
 }  // namespace mlb
