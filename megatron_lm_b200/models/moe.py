@@ -17,6 +17,7 @@ expert MLP runs on expert-sorted tokens through the ragged grouped product of
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -26,6 +27,7 @@ import torch.nn.functional as F
 
 from ..config import TransformerConfig
 from ..ops import core as ops
+from ..ops import router as fused_router
 from ..ops.grouped_gemm import grouped_linear
 from ..parallel import state
 from ..parallel.layers import _device, _init_sharded, set_tensor_model_parallel_attributes
@@ -231,6 +233,38 @@ class TopKRouter(nn.Module):
                                    self.layer_number, cfg.num_layers)
         return MoEAuxLossAutoScaler.apply(activation, loss)
 
+    def _fused_eligible(self, logits) -> bool:
+        """One CUDA pass for scores, top-k, map and loss statistics (``ops/router.py``): GPU tensors, no capacity
+        dropping, no group-limited choice, plain or aux-loss balancing.  ``MLB_FUSED_ROUTER=0`` turns it off."""
+        cfg = self.config
+        return (logits.is_cuda and os.environ.get("MLB_FUSED_ROUTER", "1") != "0"
+                and self.routing_type in ("aux_loss", "none") and cfg.moe_expert_capacity_factor is None
+                and not cfg.moe_router_group_topk and logits.dtype == torch.float32
+                and self.num_experts <= fused_router.MAX_EXPERTS
+                and cfg.moe_router_score_function in ("softmax", "sigmoid"))
+
+    def _forward_fused(self, logits):
+        cfg = self.config
+        train = self.training
+        aux_c = cfg.moe_aux_loss_coeff if (train and self.routing_type == "aux_loss") else 0.0
+        z_c = cfg.moe_z_loss_coeff if (train and cfg.moe_z_loss_coeff is not None) else 0.0
+        group = None
+        if aux_c and state.model_parallel_is_initialized() and dist.is_initialized() \
+                and state.get_group_size("tp_cp") > 1:
+            group = state.get_tensor_and_context_parallel_group()
+        probs, rmap, _tpe, aux, z = fused_router.fused_topk_router(
+            logits, self.topk, fused_router.router_mode(cfg.moe_router_score_function, cfg.moe_router_pre_softmax),
+            cfg.moe_router_topk_scaling_factor, self.expert_bias, aux_c, z_c, group,
+            lambda: MoEAuxLossAutoScaler.main_loss_backward_scale)
+        if aux_c:
+            save_to_aux_losses_tracker("load_balancing_loss", aux / aux_c, self.layer_number, cfg.num_layers)
+        if z_c:
+            save_to_aux_losses_tracker("z_loss", z / z_c, self.layer_number, cfg.num_layers)
+        if self.expert_bias is not None and train:
+            with torch.no_grad():
+                self.local_tokens_per_expert += _tpe
+        return probs, rmap
+
     def forward(self, hidden):
         cfg = self.config
         h = hidden.reshape(-1, hidden.shape[-1])
@@ -239,6 +273,8 @@ class TopKRouter(nn.Module):
             h = h * torch.empty_like(h).uniform_(1.0 - eps, 1.0 + eps)
         logits = self.gating(h)
         T = logits.shape[0]
+        if self._fused_eligible(logits):
+            return self._forward_fused(logits)
         if cfg.moe_z_loss_coeff is not None and self.training:
             z = z_loss_func(logits, cfg.moe_z_loss_coeff)
             logits = MoEAuxLossAutoScaler.apply(logits, z)
@@ -405,8 +441,9 @@ class MoEAlltoAllTokenDispatcher:
         permuted, self.sorted_indices = permute(h, routing_map)
         local_counts = routing_map.sum(dim=0).to(torch.int64)              # [E]
         if self.ep > 1:
-            all_counts = torch.empty(self.ep, self.E, dtype=torch.int64, device=h.device)
-            dist.all_gather_into_tensor(all_counts, local_counts.contiguous(), group=self.ep_group)
+            flat_counts = torch.empty(self.ep * self.E, dtype=torch.int64, device=h.device)
+            dist.all_gather_into_tensor(flat_counts, local_counts.contiguous(), group=self.ep_group)
+            all_counts = flat_counts.view(self.ep, self.E)
             r = dist.get_rank(self.ep_group)
             mine = all_counts[:, r * self.E_local:(r + 1) * self.E_local]    # [ep, E_local]: from each source rank
             # one host read per layer: split sizes are needed by the collective
