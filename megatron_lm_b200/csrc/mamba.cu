@@ -173,3 +173,167 @@ MLB_API int mlb_ssd_scan_fwd(int dtype, const void* x, const float* dt, const fl
   MLB_CHECK_LAUNCH();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Gated group RMSNorm of the Mamba-2 mixer: out = rmsnorm_g(y * silu(z)) * w, the mean square taken over each of G
+// contiguous channel groups (reference: megatron/core/ssm/mamba_mixer.py:52, the external library's RMSNormGated with
+// norm_before_gate=False).  One thread block per row (grid-stride); a thread owns channels tid*8 + it*2048 so its
+// weight-gradient partial sums stay in registers across the rows it sees.  y, z and their gradients carry a row
+// stride so z can be the slice of the fused input projection it comes from.
+namespace mlb {
+
+constexpr int kGnThreads = 256;
+constexpr int kGnMaxIt = 8;                 // channels <= 8 * 256 * 8 = 16384
+constexpr int kGnMaxGroups = 64;
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(kGnThreads)
+gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const float* __restrict__ w,
+                         T* __restrict__ out, float* __restrict__ rstd, int rows, int C, int G, long long ys,
+                         long long zs, float eps) {
+  __shared__ float gsum[kGnMaxGroups];
+  const int gs = C / G;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (threadIdx.x < G) gsum[threadIdx.x] = 0.f;
+    __syncthreads();
+    float u[kGnMaxIt][8];
+#pragma unroll
+    for (int it = 0; it < kGnMaxIt; ++it) {
+      const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+      if (c < C) {
+        float a[8], b[8];
+        load8(y + (size_t)r * ys + c, a);
+        load8(z + (size_t)r * zs + c, b);
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { u[it][k] = a[k] * b[k] * sigmoidf_(b[k]); ss += u[it][k] * u[it][k]; }
+        atomicAdd(&gsum[c / gs], ss);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < kGnMaxIt; ++it) {
+      const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+      if (c < C) {
+        const float rs = rsqrtf(gsum[c / gs] / gs + eps);
+        float o[8], wv[8];
+        load8(w + c, wv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = u[it][k] * rs * wv[k];
+        store8(out + (size_t)r * C + c, o);
+      }
+    }
+    if (threadIdx.x < G) rstd[(size_t)r * G + threadIdx.x] = rsqrtf(gsum[threadIdx.x] / gs + eps);
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kGnThreads)
+gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, const T* __restrict__ z,
+                         const float* __restrict__ w, const float* __restrict__ rstd, T* __restrict__ dy,
+                         T* __restrict__ dz, float* __restrict__ dw, int rows, int C, int G, long long ys,
+                         long long zs, long long dys, long long dzs) {
+  __shared__ float gdot[kGnMaxGroups];
+  const int gs = C / G;
+  float wacc[kGnMaxIt][8];
+#pragma unroll
+  for (int it = 0; it < kGnMaxIt; ++it)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) wacc[it][k] = 0.f;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (threadIdx.x < G) gdot[threadIdx.x] = 0.f;
+    __syncthreads();
+    // pass 1: mean over the group of (dout * w) * n, n = u * rstd
+#pragma unroll
+    for (int it = 0; it < kGnMaxIt; ++it) {
+      const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+      if (c < C) {
+        float a[8], b[8], g[8], wv[8];
+        load8(y + (size_t)r * ys + c, a);
+        load8(z + (size_t)r * zs + c, b);
+        load8(dout + (size_t)r * C + c, g);
+        load8(w + c, wv);
+        const float rs = rstd[(size_t)r * G + c / gs];
+        float dot = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float n = a[k] * b[k] * sigmoidf_(b[k]) * rs;
+          dot += g[k] * wv[k] * n;
+          wacc[it][k] += g[k] * n;
+        }
+        atomicAdd(&gdot[c / gs], dot);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < kGnMaxIt; ++it) {
+      const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+      if (c < C) {
+        float a[8], b[8], g[8], wv[8], oy[8], oz[8];
+        load8(y + (size_t)r * ys + c, a);
+        load8(z + (size_t)r * zs + c, b);
+        load8(dout + (size_t)r * C + c, g);
+        load8(w + c, wv);
+        const float rs = rstd[(size_t)r * G + c / gs];
+        const float md = gdot[c / gs] / gs;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float sg = sigmoidf_(b[k]);
+          const float sl = b[k] * sg;                                  // silu(z)
+          const float n = a[k] * sl * rs;
+          const float du = rs * (g[k] * wv[k] - n * md);
+          oy[k] = du * sl;
+          oz[k] = du * a[k] * sg * (1.f + b[k] * (1.f - sg));
+        }
+        store8(dy + (size_t)r * dys + c, oy);
+        store8(dz + (size_t)r * dzs + c, oz);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int it = 0; it < kGnMaxIt; ++it) {
+    const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+    if (c < C) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) atomicAdd(dw + c + k, wacc[it][k]);
+    }
+  }
+}
+
+static bool gn_ok(int rows, int C, int G, long long ys, long long zs) {
+  return rows > 0 && C > 0 && C % 8 == 0 && C <= kGnThreads * 8 * kGnMaxIt && G >= 1 && G <= kGnMaxGroups &&
+         C % G == 0 && (C / G) % 8 == 0 && ys % 8 == 0 && zs % 8 == 0;
+}
+
+}  // namespace mlb
+
+MLB_API int mlb_gated_rmsnorm_fwd(int dtype, const void* y, const void* z, const float* w, void* out, float* rstd,
+                                  int rows, int C, int G, long long y_stride, long long z_stride, float eps,
+                                  cudaStream_t st) {
+  using namespace mlb;
+  if (!gn_ok(rows, C, G, y_stride, z_stride)) return -3;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  MLB_DISPATCH_ACT(dtype, T, (gated_rmsnorm_fwd_kernel<T><<<grid, kGnThreads, 0, st>>>(
+      (const T*)y, (const T*)z, w, (T*)out, rstd, rows, C, G, y_stride, z_stride, eps)));
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+
+// dw [C] fp32 is accumulated into: zero it (or pass the running gradient) before the call.
+MLB_API int mlb_gated_rmsnorm_bwd(int dtype, const void* dout, const void* y, const void* z, const float* w,
+                                  const float* rstd, void* dy, void* dz, float* dw, int rows, int C, int G,
+                                  long long y_stride, long long z_stride, long long dy_stride, long long dz_stride,
+                                  cudaStream_t st) {
+  using namespace mlb;
+  if (!gn_ok(rows, C, G, y_stride, z_stride) || dy_stride % 8 != 0 || dz_stride % 8 != 0) return -3;
+  const int grid = rows < 148 * 2 ? rows : 148 * 2;
+  MLB_DISPATCH_ACT(dtype, T, (gated_rmsnorm_bwd_kernel<T><<<grid, kGnThreads, 0, st>>>(
+      (const T*)dout, (const T*)y, (const T*)z, w, rstd, (T*)dy, (T*)dz, dw, rows, C, G, y_stride, z_stride,
+      dy_stride, dz_stride)));
+  MLB_CHECK_LAUNCH();
+  return 0;
+}

@@ -23,6 +23,7 @@ import torch
 
 from ..ops import _lib
 from ..ops.attention import attention
+from ..ops.sampling import sample as fused_sample
 
 _lib.register_signatures({
     "mlb_attn_decode": "ippppppiiiiliifp",
@@ -46,20 +47,24 @@ def sample_from_logits(logits: torch.Tensor, params: SamplingParams, vocab_size:
                        generator=None) -> torch.Tensor:
     """logits [b, v] -> token ids [b].  top_k == 1 is greedy; top-k and top-p (nucleus) filter before
     the temperature-scaled multinomial draw."""
-    if params.top_k == 1:
+    if params.top_k > logits.size(-1):
+        raise ValueError("top-k is larger than the vocabulary")
+    if params.top_p > 1.0:
+        raise ValueError("top-p must be at most 1")
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16, torch.float16):
+        # one kernel: filter + inverse-CDF draw from uniforms of the caller's generator
+        u = torch.rand(logits.shape[0], device=logits.device, generator=generator)
+        out = fused_sample(logits, u, params.temperature, params.top_k, params.top_p)
+    elif params.top_k == 1:
         out = torch.argmax(logits, dim=-1)
     else:
         x = logits.float().clone()
         if params.temperature != 1.0:
             x.div_(params.temperature)
         if params.top_k > 1:
-            if params.top_k > x.size(-1):
-                raise ValueError("top-k is larger than the vocabulary")
             kth = torch.topk(x, params.top_k, dim=-1)[0][..., -1, None]
             x.masked_fill_(x < kth, float("-inf"))
         elif params.top_p > 0.0:
-            if params.top_p > 1.0:
-                raise ValueError("top-p must be at most 1")
             srt, idx = torch.sort(x, descending=True, dim=-1)
             cum = srt.softmax(dim=-1).cumsum(dim=-1)
             remove = cum > params.top_p

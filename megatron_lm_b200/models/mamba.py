@@ -17,7 +17,7 @@ import torch.nn.functional as F
 
 from ..config import TransformerConfig
 from ..ops import core as ops
-from ..ops.mamba import causal_conv1d, causal_conv1d_update, ssd_scan
+from ..ops.mamba import causal_conv1d, causal_conv1d_update, gated_rmsnorm, ssd_scan
 from ..parallel import state
 from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, _device
 from .gpt import LanguageModelEmbedding, RotaryEmbedding
@@ -96,12 +96,7 @@ class MambaMixer(nn.Module):
 
     def _gated_norm(self, y, z):
         """RMSNorm(y * silu(z)) per tensor-parallel group of channels (reference: ssm/mamba_mixer.py:52)."""
-        y = y * F.silu(z.float()).to(y.dtype)
-        group = self.di_loc // self.g_loc
-        shp = y.shape
-        yf = y.float().view(*shp[:-1], self.g_loc, group)
-        yf = yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + self.eps)
-        return (yf.view(shp) * self.norm_weight.float()).to(y.dtype)
+        return gated_rmsnorm(y, z, self.norm_weight, self.g_loc, self.eps)
 
     def forward(self, hidden_states, inference_context=None):
         """hidden_states [s, b, h] -> ([s, b, h], None)."""

@@ -20,6 +20,8 @@ _lib.register_signatures({
     "mlb_causal_conv1d_fwd": "ippppp" "iiiii" "p",
     "mlb_causal_conv1d_bwd": "ippppp" "ppp" "iiiii" "p",
     "mlb_ssd_scan_fwd": "ippppp" "pppp" "iiiiii" "i" "p",
+    "mlb_gated_rmsnorm_fwd": "ippppp" "iii" "qq" "f" "p",
+    "mlb_gated_rmsnorm_bwd": "ippppp" "ppp" "iii" "qqqq" "p",
 })
 
 
@@ -173,3 +175,65 @@ def ssd_reference(x, dt, A, Bm, Cm, D=None, initial_state=None):
             yt = yt + x[:, t].float() * D.float().view(1, H, 1)
         ys.append(yt)
     return torch.stack(ys, dim=1), h
+
+
+# ----------------------------------------------------------------------------- gated group RMSNorm
+def _gated_rmsnorm_ref(y, z, w, groups, eps):
+    u = y.float() * F.silu(z.float())
+    shp = u.shape
+    ug = u.view(*shp[:-1], groups, shp[-1] // groups)
+    ug = ug * torch.rsqrt(ug.pow(2).mean(-1, keepdim=True) + eps)
+    return (ug.view(shp) * w.float()).to(y.dtype)
+
+
+def _rows_view(t, C):
+    """[.., C] -> ([rows, C] sharing storage when the rows are evenly strided, else a copy; row stride)."""
+    t2 = t.reshape(-1, C)                      # a view whenever the leading dims collapse
+    if t2.stride(1) != 1 or t2.stride(0) % 8 != 0 or t2.data_ptr() % 16 != 0:
+        t2 = t2.contiguous()
+    return t2, t2.stride(0)
+
+
+class _GatedNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, z, w, groups, eps):
+        C = y.shape[-1]
+        y2, ys = _rows_view(y, C)
+        z2, zs = _rows_view(z, C)
+        rows = y2.shape[0]
+        wf = w.float().contiguous()
+        out = torch.empty(rows, C, dtype=y.dtype, device=y.device)
+        rstd = torch.empty(rows, groups, dtype=torch.float32, device=y.device)
+        _lib.check(_lib.lib().mlb_gated_rmsnorm_fwd(_lib.dt(y2), y2.data_ptr(), z2.data_ptr(), wf.data_ptr(),
+                                                    out.data_ptr(), rstd.data_ptr(), rows, C, groups, ys, zs,
+                                                    float(eps), _lib.stream()), "gated_rmsnorm_fwd")
+        ctx.save_for_backward(y2, z2, wf, rstd)
+        ctx.meta = (groups, y.shape, z.shape, w.dtype)
+        return out.view(y.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y2, z2, wf, rstd = ctx.saved_tensors
+        groups, yshape, zshape, wdt = ctx.meta
+        rows, C = y2.shape
+        do = dout.reshape(rows, C).contiguous()
+        dy = torch.empty(rows, C, dtype=y2.dtype, device=y2.device)
+        dz = torch.empty(rows, C, dtype=y2.dtype, device=y2.device)
+        dw = torch.zeros(C, dtype=torch.float32, device=y2.device)
+        _lib.check(_lib.lib().mlb_gated_rmsnorm_bwd(_lib.dt(y2), do.data_ptr(), y2.data_ptr(), z2.data_ptr(),
+                                                    wf.data_ptr(), rstd.data_ptr(), dy.data_ptr(), dz.data_ptr(),
+                                                    dw.data_ptr(), rows, C, groups, y2.stride(0), z2.stride(0), C, C,
+                                                    _lib.stream()), "gated_rmsnorm_bwd")
+        return dy.view(yshape), dz.view(zshape), dw.to(wdt), None, None
+
+
+def gated_rmsnorm(y, z, w, groups: int = 1, eps: float = 1e-5):
+    """rmsnorm(y * silu(z)) * w with the mean square over each of ``groups`` contiguous channel groups.
+    ``z`` may be a strided slice (same dtype as ``y``).  CUDA kernel for up to 16384 channels and 64 groups with
+    group size a multiple of 8; other shapes and CPU tensors use the PyTorch body."""
+    C = y.shape[-1]
+    ok = (y.is_cuda and z.dtype == y.dtype and y.dtype in (torch.float32, torch.bfloat16, torch.float16)
+          and C % 8 == 0 and C <= 16384 and 1 <= groups <= 64 and C % groups == 0 and (C // groups) % 8 == 0)
+    if not ok:
+        return _gated_rmsnorm_ref(y, z, w, groups, eps)
+    return _GatedNormFn.apply(y, z, w, groups, eps)

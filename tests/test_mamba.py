@@ -87,3 +87,25 @@ def test_mamba_kernels_gpu():
         assert torch.allclose(xc.grad.float(), x2.grad, atol=tol * 10, rtol=tol * 2)
         assert torch.allclose(w.grad.float(), w2.grad, atol=tol * 60, rtol=tol * 2)
         assert torch.allclose(bias.grad.float(), b2.grad, atol=tol * 60, rtol=tol * 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("C,G", [(256, 1), (1024, 8), (4096, 2), (2560, 5)])
+def test_gated_rmsnorm_gpu(C, G):
+    from megatron_lm_b200.ops.mamba import _gated_rmsnorm_ref, gated_rmsnorm
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        torch.manual_seed(C + G)
+        big = torch.randn(3, 70, 2 * C + 64, device="cuda", dtype=dtype)
+        z = big[..., :C].detach().requires_grad_()                  # strided slice, as in the mixer
+        y = torch.randn(3, 70, C, device="cuda", dtype=dtype, requires_grad=True)
+        w = (1 + 0.1 * torch.randn(C, device="cuda")).requires_grad_()
+        out = gated_rmsnorm(y, z, w, G, 1e-5)
+        g = torch.randn_like(out)
+        out.backward(g)
+        y2, z2, w2 = (t.detach().float().requires_grad_() for t in (y, z, w))
+        ref = _gated_rmsnorm_ref(y2, z2, w2, G, 1e-5)
+        ref.backward(g.float())
+        assert torch.allclose(out.float(), ref, atol=tol * 4, rtol=tol)
+        assert torch.allclose(y.grad.float(), y2.grad, atol=tol * 8, rtol=tol * 2)
+        assert torch.allclose(z.grad.float(), z2.grad, atol=tol * 8, rtol=tol * 2)
+        assert torch.allclose(w.grad.float(), w2.grad, atol=tol * 200, rtol=tol * 4)
