@@ -7,6 +7,12 @@ offers four primitives - post a receive from the previous / next stage, send to
 the next / previous stage - all non-blocking; the schedule executor decides when
 to wait.  Sends are kept alive until complete and drained at the end of the step.
 Variable sequence lengths exchange a 3-element shape tensor first (:21).
+
+Each of the four message streams of a stage (activations in from the previous stage, activations out to the next,
+gradients in from the next, gradients out to the previous) runs on a communicator of its own
+(``state.get_pipeline_channel``), so every communicator is a one-way FIFO.  The reference instead batches the sends
+and receives of one schedule step into one NCCL group (``batch_isend_irecv``); un-batched transfers of both
+directions on one communicator can block each other, because NCCL runs them in issue order on one stream.
 """
 from __future__ import annotations
 
@@ -14,6 +20,8 @@ from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+from . import state
 
 
 class _Pending:
@@ -34,24 +42,33 @@ class P2PCommunicator:
         self._sends: List[_Pending] = []
         backend = dist.get_backend(group) if group is not None else "gloo"
         self.device = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+        prev_stage = (pp_rank - 1) % pp_size
+
+        def channel(kind, sender_stage):
+            ch = state.get_pipeline_channel(kind, sender_stage) if state.model_parallel_is_initialized() else None
+            return ch if ch is not None else group
+        self.ch_fwd_out = channel("F", pp_rank)        # activations to the next stage
+        self.ch_fwd_in = channel("F", prev_stage)      # activations from the previous stage
+        self.ch_bwd_in = channel("B", pp_rank)         # gradients from the next stage
+        self.ch_bwd_out = channel("B", prev_stage)     # gradients to the previous stage
 
     # -- receives ------------------------------------------------------------
-    def _irecv(self, src: int) -> _Pending:
+    def _irecv(self, src: int, ch) -> _Pending:
         shape = self.shape
         if self.variable:
             sh = torch.empty(3, dtype=torch.int64, device=self.device)
-            dist.recv(sh, src=src, group=self.group)
+            dist.recv(sh, src=src, group=ch)
             shape = tuple(int(x) for x in sh.tolist())
         buf = torch.empty(shape, dtype=self.dtype, device=self.device)
-        return _Pending(buf, dist.irecv(buf, src=src, group=self.group))
+        return _Pending(buf, dist.irecv(buf, src=src, group=ch))
 
     def irecv_forward(self) -> _Pending:
         """Activation from the previous stage (the last stage's sender for rank 0 of a later chunk)."""
-        return self._irecv(self.prev)
+        return self._irecv(self.prev, self.ch_fwd_in)
 
     def irecv_backward(self) -> _Pending:
         """Output gradient from the next stage."""
-        return self._irecv(self.next)
+        return self._irecv(self.next, self.ch_bwd_in)
 
     def wait(self, pending: Optional[_Pending]) -> Optional[torch.Tensor]:
         if pending is None:
@@ -60,21 +77,35 @@ class P2PCommunicator:
         return pending.tensor
 
     # -- sends -----------------------------------------------------------------
-    def _isend(self, t: torch.Tensor, dst: int) -> None:
+    def _isend(self, t: torch.Tensor, dst: int, ch) -> None:
         t = t.detach().contiguous()
         if t.dtype != self.dtype:
             t = t.to(self.dtype)
         if self.variable:
             sh = torch.tensor(list(t.shape) + [1] * (3 - t.dim()), dtype=torch.int64, device=self.device)
-            dist.send(sh, dst=dst, group=self.group)
-        self._sends.append(_Pending(t, dist.isend(t, dst=dst, group=self.group)))
+            dist.send(sh, dst=dst, group=ch)
+        self._sends.append(_Pending(t, dist.isend(t, dst=dst, group=ch)))
         self._reap()
 
     def send_forward(self, t: torch.Tensor) -> None:
-        self._isend(t, self.next)
+        self._isend(t, self.next, self.ch_fwd_out)
 
     def send_backward(self, t: torch.Tensor) -> None:
-        self._isend(t, self.prev)
+        self._isend(t, self.prev, self.ch_bwd_out)
+
+    def warmup(self) -> None:
+        """One tiny message over each channel, so the communicators exist before the first timed or
+        latency-sensitive step (NCCL builds a communicator at its first use, which can take seconds)."""
+        one = torch.ones(1, dtype=torch.float32, device=self.device)
+        bufs = [torch.empty_like(one) for _ in range(2)]
+        works = [dist.isend(one, dst=self.next, group=self.ch_fwd_out),
+                 dist.irecv(bufs[0], src=self.prev, group=self.ch_fwd_in),
+                 dist.isend(one, dst=self.prev, group=self.ch_bwd_out),
+                 dist.irecv(bufs[1], src=self.next, group=self.ch_bwd_in)]
+        for w in works:
+            w.wait()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
 
     def _reap(self) -> None:
         self._sends = [p for p in self._sends if not p.work.is_completed()]

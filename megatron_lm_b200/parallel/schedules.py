@@ -25,6 +25,9 @@ from . import p2p, state
 
 
 # ----------------------------------------------------------------------------- plan
+_WARM_PIPELINE_GROUPS = set()
+
+
 def get_pp_rank_microbatches(num_microbatches: int, num_model_chunks: int, microbatch_group_size: int,
                              pp_size: int, pp_rank: int, forward_only: bool = False):
     """(total virtual microbatches, all_warmup, warm-up count, remaining)
@@ -248,7 +251,14 @@ def forward_backward_pipelining(*, forward_step_func, data_iterator, model, num_
                                forward_only)
     shape = get_tensor_shapes(seq_length, micro_batch_size, config)
     dtype = config.pipeline_dtype or config.params_dtype
-    comm = p2p.P2PCommunicator(state.get_pipeline_model_parallel_group(), pp_rank, pp_size, shape, dtype, config)
+    pp_group = state.get_pipeline_model_parallel_group()
+    comm = p2p.P2PCommunicator(pp_group, pp_rank, pp_size, shape, dtype, config)
+    if pp_group is not None and id(pp_group) not in _WARM_PIPELINE_GROUPS:
+        # build the channel communicators before the first step, then line the ranks up again: the ranks of one
+        # stage must enter their first step within the wait limit of the fused tensor-parallel kernels
+        _WARM_PIPELINE_GROUPS.add(id(pp_group))
+        comm.warmup()
+        torch.distributed.barrier()
 
     def first_virtual(c): return pp_rank == 0 and c == 0
     def last_virtual(c): return pp_rank == pp_size - 1 and c == v - 1

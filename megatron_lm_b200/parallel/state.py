@@ -118,6 +118,7 @@ class _State:
     position_embedding_ranks: List[int] = field(default_factory=list)
     memory_buffer: Optional[object] = None
     nccl_cfg: Optional[dict] = None
+    pp_channels: Optional[dict] = None
 
 
 _S = _State()
@@ -270,6 +271,23 @@ def initialize_model_parallel(
     mk("tp", "tp")
     pp_backend = pipeline_model_parallel_comm_backend or backend
     _make("pp", dense.get_ranks("pp"), backend=pp_backend if not virtual else None, timeout=timeout)
+    # one-directional pipeline channels.  Every (sender stage -> receiver stage, activation or gradient) stream of
+    # messages gets a communicator of its own, so each communicator carries a strict FIFO from one sender to one
+    # receiver.  NCCL runs the point-to-point kernels of one communicator in issue order on one stream; with sends
+    # and receives of both directions mixed on one communicator, two stages that each post a receive before their
+    # send (or two sends first) would wait on each other for ever.  With one channel per direction and kind that
+    # cannot happen, whatever order the schedule posts its transfers in.
+    _S.pp_channels = {}
+    if pp > 1:
+        for ranks in dense.get_ranks("pp"):
+            for s in range(len(ranks)):
+                pair = sorted({ranks[s], ranks[(s + 1) % len(ranks)]})
+                for kind in ("F", "B"):
+                    pg = None
+                    if not virtual and dist.is_initialized():
+                        pg = dist.new_group(pair, backend=pp_backend, timeout=timeout)
+                    if rank in ranks and rank in pair:
+                        _S.pp_channels[(kind, s)] = pg
     # embedding groups: first and last pipeline stage (tied embeddings)
     emb, pos = [], []
     for ranks in dense.get_ranks("pp"):
@@ -323,6 +341,12 @@ def destroy_model_parallel() -> None:
                         dist.destroy_process_group(pg)
                     except Exception:
                         pass
+        for pg in (_S.pp_channels or {}).values():
+            if pg is not None:
+                try:
+                    dist.destroy_process_group(pg)
+                except Exception:
+                    pass
     _S = _State()
 
 
@@ -361,6 +385,15 @@ def get_tensor_model_parallel_world_size(): return get_group_size("tp")
 def get_tensor_model_parallel_rank(): return get_group_rank("tp")
 def get_tensor_model_parallel_src_rank(): return _g("tp").ranks[0]
 def get_pipeline_model_parallel_group(): return _g("pp").pg
+
+
+def get_pipeline_channel(kind: str, sender_stage: int):
+    """Communicator of one one-directional pipeline channel: ``("F", s)`` carries activations from stage ``s`` to
+    stage ``s + 1`` (wrapping), ``("B", s)`` carries gradients from stage ``s + 1`` back to stage ``s``.  None when
+    this rank is on neither end (or pipeline parallelism is off)."""
+    return (_S.pp_channels or {}).get((kind, sender_stage))
+
+
 def get_pipeline_model_parallel_world_size(): return get_group_size("pp")
 def get_pipeline_model_parallel_rank(): return get_group_rank("pp")
 def get_model_parallel_group(): return _g("mp").pg
