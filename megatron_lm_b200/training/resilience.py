@@ -131,6 +131,7 @@ class RerunStateMachine:
         self.diagnostics: List[tuple] = []
         self.saved_rng = None
         self.stats: Dict[str, List[float]] = {}
+        self._resume_pending = False
 
     # -- consensus ------------------------------------------------------------
     def _any(self, flag: bool) -> bool:
@@ -178,6 +179,12 @@ class RerunStateMachine:
                 self.exit_code = EXIT_CODE_RESUME_TO_DISAMBIGUATE
             return self._finish(its)
         if self.state in (RerunState.RERUNNING_FROM_CHECKPOINT, RerunState.RERUNNING_AGAIN_FROM_CHECKPOINT):
+            if self._resume_pending:
+                # first call after a resume: replay the saved step (on possibly different hardware)
+                self._resume_pending = False
+                for i in its:
+                    i.rewind()
+                return True
             return self._finish(its)
         return self._finish(its)
 
@@ -191,8 +198,10 @@ class RerunStateMachine:
             i.rewind()
 
     def _finish(self, its) -> bool:
-        if self.state != RerunState.WILL_RERUN_FROM_CHECKPOINT:
-            self.state = RerunState.NOT_RUNNING_YET
+        if self.state == RerunState.WILL_RERUN_FROM_CHECKPOINT:
+            # the step is not over: the checkpoint written now carries its first result for the replay
+            return False
+        self.state = RerunState.NOT_RUNNING_YET
         self.step += 1
         self.first_result = None
         return False
