@@ -53,7 +53,7 @@ router_fwd_kernel(const RouterFwdArgs a) {
     for (int j = 0; j < VPT; ++j) se += (lane + 32 * j < a.E) ? __expf(l[j] - m) : 0.f;
     se = warp_sum(se);
     const float lse = m + __logf(se);
-    zacc += lse * lse;
+    if (lane == 0) zacc += lse * lse;
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int e = lane + 32 * j;
@@ -110,7 +110,6 @@ router_fwd_kernel(const RouterFwdArgs a) {
       atomicAdd(&sh_score[e], s[j]);
     }
   }
-  zacc = warp_sum(zacc);
   __syncthreads();
   for (int i = threadIdx.x; i < a.E; i += blockDim.x) {
     if (sh_cnt[i]) atomicAdd(a.tokens_per_expert + i, sh_cnt[i]);
