@@ -1,0 +1,228 @@
+"""Command line surface and small runtime utilities: argument parsing / validation / config objects, YAML overlay,
+timers, the microbatch calculator with batch-size ramp-up, FLOP and memory models, energy monitor (fake NVML),
+config logger.  Mirrors the reference's tests/unit_tests/test_num_microbatches_calculator.py, test_utilities,
+test_training.py and the argument checks of megatron/training/arguments.py."""
+import json
+import time
+
+import pytest
+import torch
+
+from megatron_lm_b200.training import arguments as A
+
+BASE = ["--num-layers", "4", "--hidden-size", "64", "--num-attention-heads", "4", "--seq-length", "128",
+        "--micro-batch-size", "2", "--train-iters", "10", "--lr", "1e-3"]
+
+
+def _args(extra=(), world=1, monkeypatch=None):
+    if monkeypatch is not None:
+        monkeypatch.setenv("WORLD_SIZE", str(world))
+    return A.parse_args(argv=BASE + list(extra))
+
+
+def test_flag_surface_matches_the_reference_count():
+    from megatron_lm_b200.training.flag_table import FLAGS
+    assert len(FLAGS) >= 498
+    parser = A.build_parser()
+    dests = {a.dest for a in parser._actions}
+    for must in ("tensor_model_parallel_size", "pipeline_model_parallel_size", "use_distributed_optimizer",
+                 "sequence_parallel", "num_experts", "moe_router_topk", "fp8", "recompute_granularity",
+                 "rampup_batch_size", "rerun_mode", "ckpt_format", "tp_comm_overlap", "context_parallel_size"):
+        assert must in dests, must
+
+
+def test_defaults_are_derived(monkeypatch):
+    a = A.validate_args(_args(["--swiglu", "--bf16"], world=4, monkeypatch=monkeypatch))
+    assert a.data_parallel_size == 4 and a.global_batch_size == 8
+    assert a.ffn_hidden_size == int((4 * 64 * 2 / 3) / 64) * 64
+    assert a.kv_channels == 16 and a.num_query_groups == 4 and a.max_position_embeddings == 128
+    assert a.params_dtype == torch.bfloat16 and a.accumulate_allreduce_grads_in_fp32
+    assert a.virtual_pipeline_model_parallel_size is None
+
+
+def test_virtual_pipeline_and_parallel_sizes(monkeypatch):
+    a = A.validate_args(_args(["--tensor-model-parallel-size", "2", "--pipeline-model-parallel-size", "2",
+                               "--num-layers-per-virtual-pipeline-stage", "1", "--sequence-parallel",
+                               "--global-batch-size", "16"], world=8, monkeypatch=monkeypatch))
+    assert a.data_parallel_size == 2 and a.virtual_pipeline_model_parallel_size == 2 and a.sequence_parallel
+    a = A.validate_args(_args(["--sequence-parallel"], world=1, monkeypatch=monkeypatch))
+    assert not a.sequence_parallel                          # meaningless without tensor parallelism
+
+
+@pytest.mark.parametrize("extra,world,msg", [
+    (["--tensor-model-parallel-size", "3"], 4, "divisible"),
+    (["--fp16", "--bf16"], 1, "mutually exclusive"),
+    (["--global-batch-size", "3"], 1, "multiple"),
+    (["--num-layers-per-virtual-pipeline-stage", "1"], 1, "pipeline"),
+    (["--tp-comm-overlap"], 1, "sequence-parallel"),
+    (["--overlap-param-gather"], 1, "distributed-optimizer"),
+    (["--expert-model-parallel-size", "2"], 2, "num-experts"),
+    (["--num-experts", "3", "--expert-model-parallel-size", "2"], 2, "divisible"),
+    (["--min-lr", "1.0"], 1, "min-lr"),
+    (["--save", "/tmp/x"], 1, "save-interval"),
+    (["--train-samples", "100"], 1, "either"),
+    (["--context-parallel-size", "2", "--seq-length", "6"], 2, "seq-length"),
+])
+def test_inconsistent_arguments_are_rejected(extra, world, msg, monkeypatch):
+    with pytest.raises(ValueError, match=msg):
+        A.validate_args(_args(extra, world=world, monkeypatch=monkeypatch))
+
+
+def test_config_objects_from_args(monkeypatch):
+    a = A.validate_args(_args(["--swiglu", "--normalization", "RMSNorm", "--disable-bias-linear", "--bf16",
+                               "--use-distributed-optimizer", "--overlap-grad-reduce", "--clip-grad", "0.5",
+                               "--num-experts", "4", "--moe-router-topk", "2", "--group-query-attention",
+                               "--num-query-groups", "2", "--position-embedding-type", "rope"],
+                              monkeypatch=monkeypatch))
+    cfg = A.core_transformer_config_from_args(a)
+    assert cfg.num_layers == 4 and cfg.gated_linear_unit and cfg.normalization == "RMSNorm" and not cfg.add_bias_linear
+    assert cfg.num_moe_experts == 4 and cfg.moe_router_topk == 2 and cfg.num_query_groups == 2 and cfg.bf16
+    oc = A.optimizer_config_from_args(a)
+    assert oc.lr == 1e-3 and oc.clip_grad == 0.5 and oc.use_distributed_optimizer and oc.bf16
+    dc = A.ddp_config_from_args(a)
+    assert dc.use_distributed_optimizer and dc.overlap_grad_reduce and dc.grad_reduce_in_fp32
+
+
+def test_yaml_overlay_and_global_args(tmp_path, monkeypatch):
+    p = tmp_path / "cfg.yaml"
+    p.write_text("model:\n  hidden_size: 96\n  num_attention_heads: 6\ntraining:\n  micro_batch_size: 3\n")
+    a = A.load_yaml_args(str(p), _args(monkeypatch=monkeypatch))
+    a = A.validate_args(a)
+    assert a.hidden_size == 96 and a.kv_channels == 16 and a.micro_batch_size == 3
+    A.set_args(a)
+    assert A.get_args() is a
+
+
+# ------------------------------------------------------------------------------------------------ timers
+def test_timers_levels_and_report():
+    from megatron_lm_b200.utils.timers import Timers
+    t = Timers(log_level=1, log_option="minmax")
+    t("step", log_level=0).start()
+    time.sleep(0.02)
+    t("step").stop()
+    t("detail", log_level=2).start()                     # above the configured level: a no-op
+    t("detail", log_level=2).stop()
+    with pytest.raises(RuntimeError):
+        t("step").stop()
+    with pytest.raises(ValueError):
+        t("step", log_level=1)
+    with pytest.raises(ValueError):
+        t("x", log_level=5)
+    s = t.get_all_timers_string(reset=False)
+    assert "step" in s and "detail" not in s and "(min, max)" in s
+    e = t("step").elapsed(reset=True)
+    assert 0.015 < e < 0.5 and t("step").elapsed() == 0.0
+
+    class W:
+        def __init__(self): self.rows = []
+        def add_scalar(self, k, v, it): self.rows.append((k, v, it))
+    t("step").start(); t("step").stop()
+    w = W()
+    t.write(["step", "missing"], w, 7)
+    assert w.rows and w.rows[0][0] == "step-time" and w.rows[0][2] == 7
+
+
+# ------------------------------------------------------------------------------------------------ microbatches
+def test_constant_microbatch_calculator():
+    from megatron_lm_b200.utils import num_microbatches_calculator as M
+    M.init_num_microbatches_calculator(0, None, 32, 2, 4)
+    assert M.get_num_microbatches() == 4 and M.get_current_global_batch_size() == 32 and M.get_micro_batch_size() == 2
+    M.update_num_microbatches(1000)
+    assert M.get_num_microbatches() == 4
+    with pytest.raises(ValueError):
+        M.init_num_microbatches_calculator(0, None, 30, 4, 4)
+    M.init_num_microbatches_calculator(0, None, 30, 4, 4, decrease_batch_size_if_needed=True)
+    assert M.get_current_running_global_batch_size() == 16 and M.get_num_microbatches() == 1
+    M.destroy_num_microbatches_calculator()
+
+
+def test_rampup_microbatch_calculator():
+    from megatron_lm_b200.utils import num_microbatches_calculator as M
+    # 16 -> 48 in steps of 16 over 96 samples: 2 increments, 48 samples each
+    M.init_num_microbatches_calculator(0, [16, 16, 96], 48, 2, 2)
+    assert M.get_current_global_batch_size() == 16 and M.get_num_microbatches() == 4
+    M.update_num_microbatches(47)
+    assert M.get_current_global_batch_size() == 16
+    M.update_num_microbatches(48)
+    assert M.get_current_global_batch_size() == 32 and M.get_num_microbatches() == 8
+    M.update_num_microbatches(97)
+    assert M.get_current_global_batch_size() == 48 and M.get_num_microbatches() == 12
+    with pytest.raises(ValueError):
+        M.init_num_microbatches_calculator(0, [16, 10, 96], 48, 2, 2)
+    with pytest.raises(ValueError):
+        M.init_num_microbatches_calculator(0, [16, 16], 48, 2, 2)
+    M.destroy_num_microbatches_calculator()
+
+
+# ------------------------------------------------------------------------------------------------ models of cost
+def test_flops_model_matches_hand_count():
+    from megatron_lm_b200.training.flops import num_floating_point_operations
+    # Llama-2-7B at 4096: 42.86 GFLOP per token (fwd+bwd), GPT-3 1.3B at 2048: 8.47
+    f = num_floating_point_operations(batch_size=1, seq_length=4096, num_layers=32, hidden_size=4096,
+                                      num_attention_heads=32, ffn_hidden_size=11008, padded_vocab_size=32000, swiglu=True)
+    assert f / 4096 / 1e9 == pytest.approx(42.86, abs=0.02)
+    g = num_floating_point_operations(batch_size=1, seq_length=2048, num_layers=24, hidden_size=2048,
+                                      num_attention_heads=16, ffn_hidden_size=8192, padded_vocab_size=50304)
+    assert g / 2048 / 1e9 == pytest.approx(8.47, abs=0.02)
+    h, s, v, L = 64, 32, 100, 2
+    hand = 3 * 2 * s * (L * (4 * h * h + 2 * s * h / 2 * 1 + 2 * h * 4 * h) + h * v)
+    got = num_floating_point_operations(batch_size=1, seq_length=s, num_layers=L, hidden_size=h, num_attention_heads=4,
+                                        padded_vocab_size=v)
+    assert got == pytest.approx(hand, rel=1e-9)
+    moe = num_floating_point_operations(batch_size=1, seq_length=s, num_layers=L, hidden_size=h, num_attention_heads=4,
+                                        padded_vocab_size=v, num_experts=8, moe_router_topk=2)
+    assert moe > got                                           # two experts per token cost twice the MLP
+
+
+def test_theoretical_memory_scales_with_sharding(monkeypatch):
+    from megatron_lm_b200.training.theoretical_memory_usage import report_theoretical_memory
+    a = A.validate_args(_args(["--swiglu", "--bf16", "--vocab-size", "1000"], monkeypatch=monkeypatch))
+    a.padded_vocab_size = 1024
+    r1 = report_theoretical_memory(a, num_microbatches=4)
+    a8 = A.validate_args(_args(["--swiglu", "--bf16", "--use-distributed-optimizer", "--vocab-size", "1000"],
+                               world=8, monkeypatch=monkeypatch))
+    a8.padded_vocab_size = 1024
+    r8 = report_theoretical_memory(a8, num_microbatches=4)
+    k = [x for x in r1 if "weight" in x][0]
+    assert r8[k] < r1[k]                                       # optimizer state sharded 8 ways
+    assert all(v > 0 for v in r1.values() if isinstance(v, (int, float)))
+
+
+# ------------------------------------------------------------------------------------------------ energy / config log
+class _FakeNvml:
+    def __init__(self): self.mj, self.inited, self.down = 1_000_000, False, False
+    def nvmlInit(self): self.inited = True
+    def nvmlShutdown(self): self.down = True
+    def nvmlDeviceGetHandleByIndex(self, i): return ("h", i)
+    def nvmlDeviceGetTotalEnergyConsumption(self, h): return self.mj
+
+
+def test_energy_monitor_reads_only_the_counter():
+    from megatron_lm_b200.utils.energy_monitor import EnergyMonitor
+    nv = _FakeNvml()
+    m = EnergyMonitor(nvml=nv, device_index=0)
+    m.setup()
+    m.resume()
+    nv.mj += 5000
+    assert m.lap() == pytest.approx(5.0)
+    nv.mj += 2000
+    m.pause()
+    nv.mj += 100000                                            # paused: not counted
+    m.resume()
+    nv.mj += 1000
+    assert m.lap() == pytest.approx(3.0) and m.get_total() == pytest.approx(8.0)
+    m.shutdown()
+    assert nv.inited and nv.down
+    assert not [n for n in dir(nv) if "Set" in n]              # nothing on the device is ever written
+
+
+def test_config_logger_writes_json(tmp_path):
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.utils.config_logger import has_config_logger_enabled, log_config_to_disk
+    cfg = TransformerConfig(num_layers=2, hidden_size=32, num_attention_heads=4, config_logger_dir=str(tmp_path))
+    assert has_config_logger_enabled(cfg)
+    p1 = log_config_to_disk(cfg, {"config": cfg, "dtype": torch.bfloat16, "fn": test_config_logger_writes_json}, "gpt")
+    p2 = log_config_to_disk(cfg, {"x": [1, (2, 3)]}, "gpt")
+    assert p1 != p2
+    d = json.load(open(p1))
+    assert d["config"]["hidden_size"] == 32 and d["dtype"] == "torch.bfloat16" and d["fn"] == "test_config_logger_writes_json"
