@@ -1,0 +1,118 @@
+"""Small structural components: explicit pipeline layer layouts, the N-dimensional communicator grid, module specs,
+process-wide globals and writers, the half-precision module wrapper.
+Mirrors the reference's tests/unit_tests/test_hyper_comm_grid.py, pipeline_parallel/test_pipeline_layout.py,
+transformer/test_spec_customization.py and test_global_vars."""
+import json
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+
+def test_pipeline_layout_string_expansion_and_queries():
+    from megatron_lm_b200.models.pp_layout import PipelineParallelLayerLayout as L
+    one = L("Et*3|(tt|)*2,m|L", pipeline_model_parallel_size=1)
+    assert ["".join(s) for s in one.stages] == ["Ettt", "tt", "tt", "m", "L"] and one.vpp == 5
+    one.validate_layer_layout(7, mtp_num_layers=1)
+    with pytest.raises(ValueError):
+        one.validate_layer_layout(8)
+    lay = L("Ett|tt|tt|ttL", pipeline_model_parallel_size=2)            # stage index = v * pp + rank
+    assert lay.vpp == 2
+    assert lay.get_num_layers_to_build(0, 0) == 2 and lay.get_num_layers_to_build(1, 1) == 2
+    assert lay.get_layer_offset(1, 0) == 2 and lay.get_layer_offset(0, 1) == 4 and lay.get_layer_offset(1, 1) == 6
+    assert lay.get_layer_id_list(0, 1) == [4, 5]
+    assert lay.get_num_layers_to_build(0, 0, kind="E") == 1 and lay.get_num_layers_to_build(1, 1, kind="L") == 1
+    uneven = L([["E", "t"], ["t", "t", "t", "L"]], 2)
+    assert uneven.get_num_layers_to_build(0) == 1 and uneven.get_num_layers_to_build(1) == 3
+    for bad in ("Ett|ttL|tt", "tt|ttL", "Ett|tt"):
+        with pytest.raises(ValueError):
+            L(bad, 2)
+
+
+def test_hyper_comm_grid_enumerations_match_reference_order():
+    from megatron_lm_b200.parallel.hyper_comm_grid import HyperCommGrid
+    g = HyperCommGrid([2, 2, 2], ["tp", "dp", "pp"])                  # tp fastest
+    assert g.get_rank_enum("tp") == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert g.get_rank_enum("dp") == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert g.get_rank_enum("pp") == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert g.get_rank_enum(["tp", "dp"]) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert g.get_rank_enum("dp-tp") == g.get_rank_enum("tp-dp")      # dims are taken in grid order
+    off = HyperCommGrid([2, 2], ["tp", "dp"], rank_offset=4)
+    assert off.get_rank_enum("tp") == [[4, 5], [6, 7]]
+    mine = g.create_pg("tp")                                          # no process group backend: the rank tuple
+    assert mine == (0, 1) and g.get_pg("tp") == (0, 1)
+    with pytest.raises(KeyError):
+        g.create_pg("tp")
+    with pytest.raises(KeyError):
+        g.get_pg("dp")
+    with pytest.raises(KeyError):
+        g.get_rank_enum("xx")
+    with pytest.raises(ValueError):
+        HyperCommGrid([2, 2], ["tp"])
+
+
+def test_module_spec_builds_nested_modules():
+    from megatron_lm_b200.models.spec_utils import ModuleSpec, build_module, get_module, import_module
+    spec = ModuleSpec(module=("torch.nn", "Linear"), params={"bias": False})
+    lin = build_module(spec, 4, 3)
+    assert isinstance(lin, torch.nn.Linear) and lin.bias is None and lin.weight.shape == (3, 4)
+    assert get_module(spec) is torch.nn.Linear and import_module(("torch.nn", "ReLU")) is torch.nn.ReLU
+    assert isinstance(build_module(torch.nn.ReLU), torch.nn.ReLU)
+    fn = lambda x: x                                                  # noqa: E731
+    assert build_module(fn) is fn and build_module(ModuleSpec(module=fn)) is fn
+
+    class Block(torch.nn.Module):
+        def __init__(self, width, submodules=None):
+            super().__init__()
+            self.inner = build_module(submodules["inner"], width, width)
+    blk = build_module(ModuleSpec(module=Block, params={"width": 5}, submodules={"inner": spec}))
+    assert blk.inner.weight.shape == (5, 5) and blk.inner.bias is None
+
+
+def test_global_variables_and_fallback_writers(tmp_path):
+    from megatron_lm_b200.training import global_vars as G
+    G.unset_global_variables()
+    with pytest.raises(Exception):
+        G.get_args()
+    args = SimpleNamespace(rank=0, world_size=1, timing_log_level=1, timing_log_option="max",
+                           tensorboard_dir=str(tmp_path / "tb"), wandb_project=None, enable_one_logger=True,
+                           exit_signal_handler=False, log_energy=False, tokenizer_type=None)
+    G.set_global_variables(args, build_tokenizer=False)
+    assert G.get_args() is args and G.get_timers() is not None
+    w = G.get_tensorboard_writer()
+    w.add_scalar("loss", 1.5, 3)
+    w.flush()
+    one = G.get_one_logger()
+    one.on_train_start(train_iterations_start=0)
+    one.log_metrics({"a": 1})
+    assert one.store_has_key("train_iterations_start")
+    jw = G._JsonlWriter(str(tmp_path / "m" / "x.jsonl"))
+    jw.add_scalar("lr", 0.1, 2)
+    jw.log({"loss": 2.0}, step=3)
+    jw.close()
+    rows = [json.loads(l) for l in open(tmp_path / "m" / "x.jsonl")]
+    assert rows[0]["tag"] == "lr" and rows[0]["value"] == 0.1 and rows[1]["tag"] == "loss" and rows[1]["value"] == 2.0 and rows[1]["step"] == 3
+    G.unset_global_variables()
+
+
+def test_float16_module_casts_inputs_and_outputs():
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.module import Float16Module, MegatronModule
+
+    class Inner(MegatronModule):
+        def __init__(self, cfg):
+            super().__init__(cfg)
+            self.lin = torch.nn.Linear(4, 4)
+            self.seen = None
+
+        def forward(self, x):
+            self.seen = x.dtype
+            return self.lin(x)
+    cfg = TransformerConfig(num_layers=1, hidden_size=4, num_attention_heads=1, bf16=True, params_dtype=torch.bfloat16)
+    m = Float16Module(cfg, Inner(cfg))
+    assert m.module.lin.weight.dtype == torch.bfloat16
+    out = m(torch.randn(2, 4))
+    assert m.module.seen == torch.bfloat16 and out.dtype == torch.float32
+    sd = m.state_dict()
+    m.load_state_dict(sd)
+    assert any(k.endswith("lin.weight") for k in sd)
