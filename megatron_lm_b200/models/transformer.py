@@ -125,6 +125,57 @@ class Norm(nn.Module):
         return ops.layernorm(x, self.weight, self.bias, self.eps, self.zero_centered)
 
 
+class L2Norm(nn.Module):
+    """x / sqrt(mean(x^2) + eps) over the last dim, no parameters (reference: transformer/torch_norm.py:54);
+    the q/k normalisation of ``qk_l2_norm`` models."""
+
+    def __init__(self, hidden_size: int = 0, eps: float = 1e-6, **_):
+        super().__init__()
+        self.eps = eps
+
+    def forward(self, x):
+        return (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + self.eps)).type_as(x)
+
+
+class WrappedTorchNorm(nn.Module):
+    """The plain-PyTorch norm of the reference's local spec (transformer/torch_norm.py:9), for configurations the
+    fused kernels do not cover (hidden size not a multiple of 8) and as their numerical reference."""
+
+    def __init__(self, config: TransformerConfig, hidden_size: int, eps: float = 1e-5, **_):
+        super().__init__()
+        if config.layernorm_zero_centered_gamma:
+            raise ValueError("zero-centred gamma needs the fused norm")
+        if config.normalization == "LayerNorm":
+            self.norm = nn.LayerNorm(hidden_size, eps=eps)
+        elif config.normalization == "RMSNorm":
+            self.norm = nn.RMSNorm(hidden_size, eps=eps)
+        else:
+            raise ValueError(f"unknown normalization {config.normalization}")
+        for p in self.norm.parameters():
+            p.sequence_parallel = config.sequence_parallel
+
+    def forward(self, x):
+        return self.norm(x)
+
+
+class IdentityOp(nn.Module):
+    """Returns its first argument (reference: transformer/identity_op.py:5): the placeholder a layer spec uses for
+    a sub-module it leaves out."""
+
+    def __init__(self, *a, **k):
+        super().__init__()
+
+    def forward(self, x, *a, **k):
+        return x
+
+
+class IdentityFuncOp(IdentityOp):
+    """Returns a function that returns its argument (the bias-dropout-add slot of a spec)."""
+
+    def forward(self, *a, **k):
+        return super().forward
+
+
 # --------------------------------------------------------------------------- attention
 def _rope_copy(qkv5, cos, sin, interleaved):
     """Out-of-place RoPE on q and k of a fused QKV tensor (inference path, no autograd)."""
