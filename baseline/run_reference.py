@@ -41,7 +41,7 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29512")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    tp, pp, vpp = layout_for(args.gpus)
+    tp, pp, vpp = layout_for(args.gpus)[:3]
     parallel_state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
                                              virtual_pipeline_model_parallel_size=vpp)
     model_parallel_cuda_manual_seed(1234)

@@ -35,11 +35,24 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 
 LLAMA7B = dict(num_layers=32, hidden_size=4096, num_attention_heads=32, ffn_hidden_size=11008, seq_length=4096,
                vocab_size=32000, micro_batch_size=1, global_batch_size=64)
+GPT3_1P3B = dict(num_layers=24, hidden_size=2048, num_attention_heads=16, ffn_hidden_size=8192, seq_length=2048,
+                 vocab_size=50304, micro_batch_size=4, global_batch_size=256)
+MIXTRAL = dict(num_layers=16, hidden_size=4096, num_attention_heads=32, num_query_groups=8, ffn_hidden_size=14336,
+               seq_length=4096, vocab_size=32000, micro_batch_size=1, global_batch_size=64, num_experts=8, topk=2)
+MODELS = {"llama7b": LLAMA7B, "gpt3-1.3b": GPT3_1P3B, "mixtral": MIXTRAL}
 BASELINE_TOKENS_PER_SEC_PER_GPU = None      # the reference publishes no B200 number
 
 
-def layout_for(n: int):
-    return {1: (1, 1, None), 2: (2, 1, None), 4: (4, 1, None), 8: (4, 2, 2)}[n]
+def layout_for(n: int, config: str = "llama7b"):
+    """(tp, pp, virtual stages, ep) for ``n`` GPUs.  llama7b (the headline): tp up to 4, then pp 2 with two
+    virtual stages; gpt3-1.3b: tp 2 and the rest data parallel; mixtral: expert parallel over all GPUs."""
+    if config == "gpt3-1.3b":
+        return (2 if n >= 2 else 1, 1, None, 1)
+    if config == "mixtral":
+        if n < 4:
+            raise SystemExit("the mixtral config holds 22.5 B parameters: it needs at least 4 GPUs (expert parallel)")
+        return (1, 1, None, n)
+    return {1: (1, 1, None, 1), 2: (2, 1, None, 1), 4: (4, 1, None, 1), 8: (4, 2, 2, 1)}[n]
 
 
 class ClockSampler:
@@ -127,27 +140,44 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    tp, pp, vpp = layout_for(args.gpus)
+    tp, pp, vpp, ep = layout_for(args.gpus, args.config)
     state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
-                                    virtual_pipeline_model_parallel_size=vpp, create_gloo_process_groups=False)
+                                    virtual_pipeline_model_parallel_size=vpp, expert_model_parallel_size=ep,
+                                    create_gloo_process_groups=False)
     model_parallel_cuda_manual_seed(1234 + 100 * state.get_pipeline_model_parallel_rank())
-    M = dict(LLAMA7B)
+    M = dict(MODELS[args.config])
     if args.layers:
         M["num_layers"] = args.layers
     dp = world // (tp * pp)
-    cfg = TransformerConfig(
+    common = dict(
         num_layers=M["num_layers"], hidden_size=M["hidden_size"], num_attention_heads=M["num_attention_heads"],
-        ffn_hidden_size=M["ffn_hidden_size"], normalization="RMSNorm", layernorm_epsilon=1e-5,
-        gated_linear_unit=True, activation_func="silu", add_bias_linear=False, hidden_dropout=0.0,
+        ffn_hidden_size=M["ffn_hidden_size"], hidden_dropout=0.0,
         attention_dropout=0.0, bf16=True, params_dtype=torch.bfloat16, tensor_model_parallel_size=tp,
         pipeline_model_parallel_size=pp, virtual_pipeline_model_parallel_size=vpp, sequence_parallel=tp > 1,
         pipeline_dtype=torch.bfloat16, tp_comm_overlap=args.tp_comm_overlap and tp > 1, init_method_std=0.02,
         overlap_p2p_comm=pp > 1, fp8=args.fp8, fp8_recipe="tensorwise" if args.fp8 else "delayed")
+    if args.config == "gpt3-1.3b":
+        cfg = TransformerConfig(normalization="LayerNorm", layernorm_epsilon=1e-5, gated_linear_unit=False,
+                                activation_func="gelu", add_bias_linear=True, **common)
+        model_kw = dict(position_embedding_type="learned_absolute", share_embeddings_and_output_weights=True)
+    elif args.config == "mixtral":
+        cfg = TransformerConfig(normalization="RMSNorm", layernorm_epsilon=1e-5, gated_linear_unit=True,
+                                activation_func="silu", add_bias_linear=False, num_query_groups=M["num_query_groups"],
+                                num_moe_experts=M["num_experts"], moe_router_topk=M["topk"],
+                                moe_ffn_hidden_size=M["ffn_hidden_size"], moe_aux_loss_coeff=1e-2,
+                                moe_router_load_balancing_type="aux_loss", moe_grouped_gemm=True,
+                                moe_token_dispatcher_type="flex" if ep > 1 else "alltoall",
+                                expert_model_parallel_size=ep, **common)
+        model_kw = dict(position_embedding_type="rope", rotary_base=1000000.0,
+                        share_embeddings_and_output_weights=False)
+    else:
+        cfg = TransformerConfig(normalization="RMSNorm", layernorm_epsilon=1e-5, gated_linear_unit=True,
+                                activation_func="silu", add_bias_linear=False, **common)
+        model_kw = dict(position_embedding_type="rope", rotary_base=10000.0, share_embeddings_and_output_weights=False)
 
     def provider(pre_process=True, post_process=True, vp_stage=None):
         return GPTModel(cfg, vocab_size=M["vocab_size"], max_sequence_length=M["seq_length"], pre_process=pre_process,
-                        post_process=post_process, position_embedding_type="rope", rotary_base=10000.0,
-                        share_embeddings_and_output_weights=False, vp_stage=vp_stage)
+                        post_process=post_process, vp_stage=vp_stage, **model_kw)
 
     ocfg = OptimizerConfig(optimizer="adam", lr=3e-4, min_lr=3e-5, weight_decay=0.1, adam_beta1=0.9, adam_beta2=0.95,
                            adam_eps=1e-8, clip_grad=1.0, bf16=True, params_dtype=torch.bfloat16,
@@ -231,17 +261,22 @@ def run_ours(args):
     if rank == 0:
         from megatron_lm_b200.training.flops import flops_from_config
         fl = flops_from_config(cfg, GB, S, M["vocab_size"])
-        par = f"tp{tp}pp{pp}" + (f"vpp{vpp}" if vpp else "") + f"dp{dp}" + ("-sp" if tp > 1 else "")
+        par = f"tp{tp}pp{pp}" + (f"vpp{vpp}" if vpp else "") + f"dp{dp}" + (f"ep{ep}" if ep > 1 else "") + \
+            ("-sp" if tp > 1 else "")
+        names = {"llama7b": ("Llama-7B", "llama2-7b (32L h4096 32 heads ffn11008 swiglu rmsnorm rope)"),
+                 "gpt3-1.3b": ("GPT-3 1.3B", "gpt3-1.3b (24L h2048 16 heads ffn8192 gelu layernorm learned positions)"),
+                 "mixtral": ("Mixtral-style 8-expert MoE", "mixtral-style (16L h4096 32q/8kv heads, 8 experts top-2 "
+                             "ffn14336 swiglu rmsnorm rope 1e6, aux loss 1e-2, dropless)")}[args.config]
         out = {
-            "metric": "tokens/sec (whole job) Llama-7B pre-training step", "value": value, "unit": "tokens/s",
+            "metric": f"tokens/sec (whole job) {names[0]} pre-training step", "value": value, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / args.gpus / BASELINE_TOKENS_PER_SEC_PER_GPU) if BASELINE_TOKENS_PER_SEC_PER_GPU else None,
             "dtype": "fp8" if args.fp8 else "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
             "tokens_per_sec_per_gpu": value / args.gpus,
             "model_tflops_per_gpu": fl / (dev_ms / args.steps / 1e3) / 1e12 / args.gpus,
-            "config": {"model": "llama2-7b (32L h4096 32 heads ffn11008 swiglu rmsnorm rope)" if not args.layers
-                       else f"llama2-7b truncated to {args.layers} layers (debug only)",
+            "config": {"model": names[1] if not args.layers
+                       else f"{args.config} truncated to {args.layers} layers (debug only)",
                        "global_batch": GB, "seq_len": S, "micro_batch": B, "parallelism": par,
                        "l2_note": "inputs and weights (>13 GB) far exceed the 126 MB L2 every step"},
             "clocks": clocks,
@@ -274,6 +309,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="llama7b", choices=sorted(MODELS),
+                    help="llama7b is the headline benchmark; the others are the secondary configurations")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a bench value)")
     ap.add_argument("--tp-comm-overlap", action="store_true", default=True)
     ap.add_argument("--no-tp-comm-overlap", dest="tp_comm_overlap", action="store_false")
