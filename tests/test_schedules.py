@@ -87,3 +87,94 @@ def test_cross_rank_dependencies_are_satisfiable():
 def test_forward_only_plan():
     plan = build_pipeline_plan(4, 2, 0, 2, 2, forward_only=True)
     assert all(s.kind == "F" for s in plan) and len(plan) == 8
+
+
+# ------------------------------------------------------------------ NCCL issue-order model of the p2p transfers
+def _simulate(pp, v, nmb, one_way_channels, overlap):
+    """Replays the executor's transfers under NCCL's rules: the point-to-point operations of one communicator run
+    in issue order (one stream per communicator per rank), and a send and its receive complete together, only
+    when each is at the head of its rank's queue for that communicator and the send's data is computed.
+    Returns True when every rank finishes its plan."""
+    from collections import defaultdict, deque
+    from megatron_lm_b200.parallel.schedules import build_pipeline_plan
+    plans = [build_pipeline_plan(nmb, pp, r, v) for r in range(pp)]
+
+    def comm_key(kind, sender_stage):
+        if one_way_channels:
+            return (kind, sender_stage)
+        return frozenset((sender_stage, (sender_stage + 1) % pp))       # one communicator per neighbour pair
+
+    def first_virtual(r, c): return r == 0 and c == 0
+    def last_virtual(r, c): return r == pp - 1 and c == v - 1
+
+    # issue order per rank: [(op, comm key, message id, step index that must be computed first or None)]
+    queues = [defaultdict(deque) for _ in range(pp)]
+    recv_of_step = [dict() for _ in range(pp)]
+    for r, plan in enumerate(plans):
+        posted = set()
+
+        def post(idx):
+            if idx >= len(plan) or idx in posted:
+                return
+            posted.add(idx)
+            st = plan[idx]
+            if st.kind == "F" and not first_virtual(r, st.chunk):
+                key, msg = comm_key("F", (r - 1) % pp), ("F", (r - 1) % pp, st.chunk if r else st.chunk - 1, st.microbatch)
+            elif st.kind == "B" and not last_virtual(r, st.chunk):
+                key, msg = comm_key("B", r), ("B", r, st.chunk, st.microbatch)
+            else:
+                return
+            queues[r][key].append(("recv", msg, None))
+            recv_of_step[r][idx] = msg
+        post(0)
+        for idx, st in enumerate(plan):
+            if overlap:
+                post(idx + 1)
+            post(idx)
+            if st.kind == "F" and not last_virtual(r, st.chunk):
+                queues[r][comm_key("F", r)].append(("send", ("F", r, st.chunk, st.microbatch), idx))
+            if st.kind == "B" and not first_virtual(r, st.chunk):
+                # the gradient of chunk c's input belongs to the sender's chunk (c on the previous stage, c-1 on wrap)
+                sender = (r - 1) % pp
+                queues[r][comm_key("B", sender)].append(("send", ("B", sender, st.chunk if r else st.chunk - 1,
+                                                                  st.microbatch), idx))
+    done_step = [-1] * pp                       # last computed step per rank
+    received = [set() for _ in range(pp)]
+    progress = True
+    while progress:
+        progress = False
+        for r in range(pp):                    # compute as far as the received inputs allow
+            while done_step[r] + 1 < len(plans[r]):
+                nxt = done_step[r] + 1
+                need = recv_of_step[r].get(nxt)
+                if need is not None and need not in received[r]:
+                    break
+                done_step[r] = nxt
+                progress = True
+        for r in range(pp):                    # complete matching heads
+            for key, q in queues[r].items():
+                if not q or q[0][0] != "send":
+                    continue
+                _, msg, dep = q[0]
+                if dep > done_step[r]:
+                    continue
+                dst = (r + 1) % pp if msg[0] == "F" else (r - 1) % pp
+                dq = queues[dst].get(key)
+                if dq and dq[0][0] == "recv" and dq[0][1] == msg:
+                    q.popleft(); dq.popleft()
+                    received[dst].add(msg)
+                    progress = True
+    return all(done_step[r] == len(plans[r]) - 1 for r in range(pp)) and \
+        all(not q for r in range(pp) for q in queues[r].values())
+
+
+@pytest.mark.parametrize("pp,v,nmb", [(2, 1, 4), (2, 2, 8), (4, 1, 8), (4, 2, 8), (4, 3, 12), (8, 2, 16), (2, 2, 64)])
+@pytest.mark.parametrize("overlap", [False, True])
+def test_one_way_channels_cannot_deadlock_under_nccl_ordering(pp, v, nmb, overlap):
+    assert _simulate(pp, v, nmb, one_way_channels=True, overlap=overlap)
+
+
+def test_shared_pair_communicator_would_deadlock():
+    # the reason for the channels: with one communicator per neighbour pair the same transfers block each other
+    assert not _simulate(2, 1, 4, one_way_channels=False, overlap=False)
+    assert not _simulate(2, 2, 8, one_way_channels=False, overlap=True)
