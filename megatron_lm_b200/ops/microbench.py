@@ -109,6 +109,52 @@ def bench_adam(a):
     _report(f"adam (fp32 p/m/v + bf16 copy) n={n}", _time(f, a.iters, a.warmup), bytes_=n * (4 * 7 + 2))
 
 
+def bench_router(a):
+    from .router import fused_topk_router
+    lg = torch.randn(a.tokens, a.experts, device="cuda", requires_grad=True)
+    by = a.tokens * a.experts * (4 + 4 + 1)
+    f = lambda: fused_topk_router(lg, a.topk, "softmax_post", None, None, 1e-2, 1e-3)
+    _report(f"router fwd T={a.tokens} E={a.experts} k={a.topk}", _time(f, a.iters, a.warmup), bytes_=by)
+    probs = f()[0]
+    g = torch.randn_like(probs)
+    _report("router bwd", _time(lambda: torch.autograd.grad(probs, lg, g, retain_graph=True), a.iters, a.warmup),
+            bytes_=a.tokens * a.experts * (4 + 1 + 4 + 4))
+
+    def unfused():
+        p = torch.softmax(lg, -1)
+        v, i = torch.topk(lg, a.topk, dim=1)
+        w = torch.softmax(v, -1)
+        dense = torch.zeros_like(lg).scatter(1, i, w)
+        m = torch.zeros_like(lg, dtype=torch.bool).scatter(1, i, True)
+        return dense, m, m.sum(0), p.sum(0), torch.logsumexp(lg, -1).square().sum()
+    _report("router fwd, op-by-op PyTorch", _time(unfused, a.iters, a.warmup))
+
+
+def bench_sampling(a):
+    from .sampling import sample, sample_reference
+    lg = torch.randn(a.rows, a.vocab, device="cuda", dtype=torch.bfloat16) * 3
+    u = torch.rand(a.rows, device="cuda")
+    for name, kw in (("greedy", dict(top_k=1)), ("top-k 50", dict(top_k=50)), ("top-p 0.9", dict(top_p=0.9)),
+                     ("multinomial", dict())):
+        ms = _time(lambda: sample(lg, u, 0.8, **kw), a.iters, a.warmup)
+        ref = _time(lambda: sample_reference(lg, u, 0.8, **kw), max(a.iters // 4, 1), 1)
+        _report(f"sample {name} [{a.rows}, {a.vocab}] (sort-based PyTorch: {ref * 1e3:.0f} us)", ms,
+                bytes_=lg.numel() * 2)
+
+
+def bench_gated_norm(a):
+    from .mamba import gated_rmsnorm
+    y = torch.randn(a.rows, a.hidden, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    z = torch.randn(a.rows, a.hidden, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(a.hidden, device="cuda", requires_grad=True)
+    _report(f"gated rmsnorm fwd [{a.rows}, {a.hidden}] groups={a.groups}",
+            _time(lambda: gated_rmsnorm(y, z, w, a.groups, 1e-5), a.iters, a.warmup), bytes_=y.numel() * 2 * 3)
+    out = gated_rmsnorm(y, z, w, a.groups, 1e-5)
+    g = torch.randn_like(out)
+    _report("gated rmsnorm bwd", _time(lambda: torch.autograd.grad(out, (y, z, w), g, retain_graph=True), a.iters, a.warmup),
+            bytes_=y.numel() * 2 * 5)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--iters", type=int, default=20)
@@ -121,8 +167,15 @@ def main(argv=None):
     t.add_argument("--head-dim", type=int, default=128); t.add_argument("--causal", type=int, default=1)
     n = sub.add_parser("norm"); n.add_argument("--rows", type=int, default=32768); n.add_argument("--hidden", type=int, default=4096)
     d = sub.add_parser("adam"); d.add_argument("--numel", type=int, default=1 << 28)
+    r = sub.add_parser("router"); r.add_argument("--tokens", type=int, default=1 << 20)
+    r.add_argument("--experts", type=int, default=64); r.add_argument("--topk", type=int, default=6)
+    sp = sub.add_parser("sampling"); sp.add_argument("--rows", type=int, default=512)
+    sp.add_argument("--vocab", type=int, default=131072)
+    gn = sub.add_parser("gated-norm"); gn.add_argument("--rows", type=int, default=32768)
+    gn.add_argument("--hidden", type=int, default=4096); gn.add_argument("--groups", type=int, default=8)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam}[a.op](a)
+    {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam, "router": bench_router,
+     "sampling": bench_sampling, "gated-norm": bench_gated_norm}[a.op](a)
     from . import _lib
     _lib.check_status()
 
