@@ -134,6 +134,9 @@ def run_ours(args):
 
     rank, world, local = dist_env()
     assert world == args.gpus, f"launched with {world} ranks for --gpus {args.gpus}"
+    if os.environ.get("MLB_BENCH_STACK_DUMP_S"):      # debug aid: print every thread's Python stack after N seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ["MLB_BENCH_STACK_DUMP_S"]), exit=False)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if not dist.is_initialized():
@@ -141,6 +144,9 @@ def run_ours(args):
         os.environ.setdefault("MASTER_PORT", "29511")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     tp, pp, vpp, ep = layout_for(args.gpus, args.config)
+    if args.layout:                                   # debug only: "tp,pp,vpp" (vpp 0 = none)
+        tp, pp, vpp = (int(x) for x in args.layout.split(","))
+        vpp = vpp or None
     state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
                                     virtual_pipeline_model_parallel_size=vpp, expert_model_parallel_size=ep,
                                     create_gloo_process_groups=False)
@@ -154,7 +160,7 @@ def run_ours(args):
         ffn_hidden_size=M["ffn_hidden_size"], hidden_dropout=0.0,
         attention_dropout=0.0, bf16=True, params_dtype=torch.bfloat16, tensor_model_parallel_size=tp,
         pipeline_model_parallel_size=pp, virtual_pipeline_model_parallel_size=vpp, sequence_parallel=tp > 1,
-        pipeline_dtype=torch.bfloat16, tp_comm_overlap=args.tp_comm_overlap and tp > 1, init_method_std=0.02,
+        pipeline_dtype=torch.bfloat16, tp_comm_overlap=args.tp_comm_overlap and tp > 1 and pp == 1, init_method_std=0.02,
         overlap_p2p_comm=pp > 1, fp8=args.fp8, fp8_recipe="tensorwise" if args.fp8 else "delayed")
     if args.config == "gpt3-1.3b":
         cfg = TransformerConfig(normalization="LayerNorm", layernorm_epsilon=1e-5, gated_linear_unit=False,
@@ -312,6 +318,7 @@ def main():
     ap.add_argument("--config", default="llama7b", choices=sorted(MODELS),
                     help="llama7b is the headline benchmark; the others are the secondary configurations")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a bench value)")
+    ap.add_argument("--layout", default=None, help="debug only: override the parallel layout as tp,pp,vpp")
     ap.add_argument("--tp-comm-overlap", action="store_true", default=True)
     ap.add_argument("--no-tp-comm-overlap", dest="tp_comm_overlap", action="store_false")
     ap.add_argument("--fp8", default=None, choices=["e4m3", "hybrid"],

@@ -20,8 +20,9 @@ import torch.distributed as dist
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--state-gb", type=float, default=2.0)
-    ap.add_argument("--k", type=int, default=None)
-    ap.add_argument("--m", type=int, default=2)
+    # long names: a launcher that parses abbreviations (torchrun -m ...) must not mistake them for its own flags
+    ap.add_argument("--data-shards", "--k", dest="k", type=int, default=None)
+    ap.add_argument("--parity-shards", "--m", dest="m", type=int, default=2)
     ap.add_argument("--chunk-mib", type=float, default=1.0)
     ap.add_argument("--lose", type=int, default=2)
     ap.add_argument("--iters", type=int, default=3)

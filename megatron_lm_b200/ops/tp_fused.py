@@ -142,6 +142,13 @@ def attach_fused_tp(model_chunks, config, seq_length: int, micro_batch_size: int
     tp = state.get_tensor_model_parallel_world_size()
     if tp == 1 or not config.sequence_parallel:
         return None
+    if state.get_pipeline_model_parallel_world_size() > 1:
+        # The fused kernels need all of their thread blocks resident at once: consumer blocks wait on flags that
+        # worker blocks (or the peers' blocks) set.  A pipeline stage has NCCL send / receive kernels spinning on
+        # some SMs for as long as the neighbouring stage computes, and those kernels wait, transitively, on this
+        # GPU's progress; blocks of a fused kernel that find no SM would then never run.  With pipeline
+        # parallelism the layers therefore keep the NCCL collectives and the plain (dependency-free) GEMM kernels.
+        return None
     rows = seq_length * micro_batch_size // config.context_parallel_size // tp
     if rows % 128:
         return None

@@ -97,11 +97,20 @@ class P2PCommunicator:
         """One tiny message over each channel, so the communicators exist before the first timed or
         latency-sensitive step (NCCL builds a communicator at its first use, which can take seconds)."""
         one = torch.ones(1, dtype=torch.float32, device=self.device)
-        bufs = [torch.empty_like(one) for _ in range(2)]
-        works = [dist.isend(one, dst=self.next, group=self.ch_fwd_out),
-                 dist.irecv(bufs[0], src=self.prev, group=self.ch_fwd_in),
-                 dist.isend(one, dst=self.prev, group=self.ch_bwd_out),
-                 dist.irecv(bufs[1], src=self.next, group=self.ch_bwd_in)]
+        prev_stage = (self.rank - 1) % self.size
+        # every rank touches its channels in one global order, (kind, sender stage): a communicator that is built
+        # at first use blocks the host until both members arrive, and a common order rules out a cycle of waits
+        mine = {("F", self.rank): ("send", self.next, self.ch_fwd_out), ("F", prev_stage): ("recv", self.prev, self.ch_fwd_in),
+                ("B", self.rank): ("recv", self.next, self.ch_bwd_in), ("B", prev_stage): ("send", self.prev, self.ch_bwd_out)}
+        works, keep = [], []
+        for key in sorted(mine):
+            op, peer, ch = mine[key]
+            if op == "send":
+                works.append(dist.isend(one, dst=peer, group=ch))
+            else:
+                buf = torch.empty_like(one)
+                keep.append(buf)
+                works.append(dist.irecv(buf, src=peer, group=ch))
         for w in works:
             w.wait()
         if self.device.type == "cuda":
