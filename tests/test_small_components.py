@@ -116,3 +116,49 @@ def test_float16_module_casts_inputs_and_outputs():
     sd = m.state_dict()
     m.load_state_dict(sd)
     assert any(k.endswith("lin.weight") for k in sd)
+
+
+def test_huggingface_adapters_wrap_transformers_modules():
+    transformers = pytest.importorskip("transformers")
+    from megatron_lm_b200.models.huggingface import AutoHuggingFaceModel, ClipHuggingFaceModel, QwenHuggingFaceModel
+    cfg = SimpleNamespace(huggingface_model_name_or_path=None)
+    clip_cfg = transformers.CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                                             num_attention_heads=2, image_size=16, patch_size=8)
+    clip = ClipHuggingFaceModel(cfg, clip_cfg)
+    out = clip(torch.randn(2, 3, 16, 16))
+    assert out.shape == (2, 5, 32)                                    # 4 patches + class token
+    assert all(p.tensor_model_parallel is False for p in clip.parameters())
+    q_cfg = transformers.Qwen2Config(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                     num_key_value_heads=2, vocab_size=50, max_position_embeddings=32)
+    qwen = QwenHuggingFaceModel(cfg, q_cfg)
+    ids = torch.randint(0, 50, (2, 7))
+    emb = qwen.embedding(ids)
+    assert emb.shape == (7, 2, 32)                                    # [s, b, h], the layout of this framework
+    a = qwen(input_ids=ids)
+    b = qwen(decoder_input=emb)
+    assert a.shape == (2, 7, 32) and torch.allclose(a, b, atol=1e-5)
+    auto = AutoHuggingFaceModel(cfg, q_cfg)
+    assert auto(input_ids=ids)["last_hidden_state"].shape == (2, 7, 32)
+    auto.set_input_tensor(None)
+
+
+def _pg_bundles(rank, world):
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.parallel.process_groups_config import GradCommProcessGroups, ModelCommProcessGroups
+    import torch.distributed as dist
+    state.initialize_model_parallel(tensor_model_parallel_size=2)
+    m = ModelCommProcessGroups.use_mpu_process_groups(["tp", "pp", "cp"])
+    assert m.tp is state.get_tensor_model_parallel_group() and m.ep is None
+    assert dist.get_world_size(m.tp) == 2 and dist.get_world_size(m.pp) == 1
+    with pytest.raises(ValueError):
+        ModelCommProcessGroups.use_mpu_process_groups(["nope"])
+    every = ModelCommProcessGroups.use_mpu_process_groups()
+    assert every.tp_cp is not None and every.mp is not None
+    g = GradCommProcessGroups.use_mpu_process_groups()
+    assert dist.get_world_size(g.dp) == 1 and g.expt_dp is not None
+    state.destroy_model_parallel()
+
+
+def test_process_group_bundles_from_global_state():
+    from tests.dist_utils import run_distributed
+    run_distributed(_pg_bundles, 2)
