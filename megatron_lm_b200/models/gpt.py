@@ -123,7 +123,10 @@ class GPTModel(nn.Module):
                  seq_len_interpolation_factor: Optional[float] = None, vp_stage: Optional[int] = None,
                  transformer_layer_spec=None, scatter_embedding_sequence_parallel: bool = True):
         super().__init__()
-        del transformer_layer_spec      # accepted for call-site compatibility; modules are fixed
+        if not isinstance(vocab_size, int):
+            # the reference's positional order: (config, transformer_layer_spec, vocab_size, max_sequence_length)
+            transformer_layer_spec, vocab_size, max_sequence_length, pre_process = \
+                vocab_size, max_sequence_length, pre_process, True
         self.config = config
         self.vocab_size, self.max_sequence_length = vocab_size, max_sequence_length
         self.pre_process, self.post_process, self.vp_stage = pre_process, post_process, vp_stage
@@ -153,7 +156,7 @@ class GPTModel(nn.Module):
                                                   seq_len_interpolation_factor, rope_scaling, rope_scaling_factor)
         else:
             self.rotary_pos_emb = None
-        self.decoder = TransformerBlock(config, pre_process, post_process, vp_stage)
+        self.decoder = TransformerBlock(config, pre_process, post_process, vp_stage, spec=transformer_layer_spec)
         if post_process:
             if config.mtp_num_layers:
                 from .mtp import MultiTokenPredictionBlock

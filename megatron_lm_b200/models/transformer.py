@@ -359,31 +359,65 @@ class MLP(nn.Module):
 
 
 # --------------------------------------------------------------------------- layer / block
+def _build_slot(spec, **pool):
+    """Instantiate the class a layer spec names for one slot.  The class receives those of ``pool`` (config,
+    layer_number, hidden_size, causal) that its constructor names, plus the spec's own ``params`` where the
+    constructor accepts them; identity placeholders take nothing."""
+    import inspect
+    from .spec_utils import ModuleSpec, get_module
+    cls = get_module(spec) if isinstance(spec, ModuleSpec) else spec
+    params = dict(spec.params) if isinstance(spec, ModuleSpec) else {}
+    if isinstance(cls, type) and issubclass(cls, IdentityOp):
+        return cls()
+    sig = inspect.signature(cls.__init__ if isinstance(cls, type) else cls)
+    names = set(sig.parameters)
+    takes_kw = any(p.kind is inspect.Parameter.VAR_KEYWORD for p in sig.parameters.values())
+    kw = {k: v for k, v in pool.items() if k in names}
+    kw.update({k: v for k, v in params.items() if k in names or takes_kw})
+    return cls(**kw)
+
+
 class TransformerLayer(nn.Module):
     """Pre-norm residual block: x + drop(attn(norm(x)) + b); x + drop(mlp(norm(x)) + b)."""
 
     def __init__(self, config: TransformerConfig, layer_number: int, is_moe: bool = False, causal: bool = True,
-                 cross_attention: bool = False):
+                 cross_attention: bool = False, submodules=None):
+        """``submodules`` (a ``TransformerLayerSubmodules``) names the class of each slot; slots it leaves empty,
+        and all slots without it, take this library's modules as the config describes them."""
         super().__init__()
         self.config, self.layer_number = config, layer_number
-        self.input_layernorm = Norm(config, config.hidden_size)
-        if getattr(config, "multi_latent_attention", False):
-            from .mla import MLASelfAttention
-            self.self_attention = MLASelfAttention(config, layer_number, causal=causal)
-        else:
-            self.self_attention = SelfAttention(config, layer_number, causal=causal)
+        sub = submodules
+
+        def slot(name, default):
+            spec = getattr(sub, name, None) if sub is not None else None
+            if spec is None or isinstance(spec, str):
+                return default()
+            return _build_slot(spec, config=config, layer_number=layer_number, hidden_size=config.hidden_size,
+                               causal=causal)
+
+        def default_attention():
+            if getattr(config, "multi_latent_attention", False):
+                from .mla import MLASelfAttention
+                return MLASelfAttention(config, layer_number, causal=causal)
+            return SelfAttention(config, layer_number, causal=causal)
+
+        def default_mlp():
+            if is_moe:
+                from .moe import MoELayer
+                return MoELayer(config, layer_number)
+            return MLP(config)
+
+        self.input_layernorm = slot("input_layernorm", lambda: Norm(config, config.hidden_size))
+        self.self_attention = slot("self_attention", default_attention)
         if cross_attention:
-            self.pre_cross_attn_layernorm = Norm(config, config.hidden_size)
-            self.cross_attention = CrossAttention(config, layer_number)
+            self.pre_cross_attn_layernorm = slot("pre_cross_attn_layernorm", lambda: Norm(config, config.hidden_size))
+            self.cross_attention = slot("cross_attention", lambda: CrossAttention(config, layer_number))
         else:
             self.cross_attention = None
-        self.pre_mlp_layernorm = Norm(config, config.hidden_size)
-        if is_moe:
-            from .moe import MoELayer
-            self.mlp = MoELayer(config, layer_number)
-        else:
-            self.mlp = MLP(config)
-        self.is_moe = is_moe
+        self.pre_mlp_layernorm = slot("pre_mlp_layernorm", lambda: Norm(config, config.hidden_size))
+        self.mlp = slot("mlp", default_mlp)
+        from .moe import MoELayer as _MoE
+        self.is_moe = isinstance(self.mlp, _MoE)
         self.hidden_dropout = config.hidden_dropout
         mods = config.recompute_modules if config.recompute_granularity == "selective" else []
         self.recompute_input_ln = "layernorm" in mods
@@ -435,17 +469,48 @@ class TransformerBlock(nn.Module):
 
     def __init__(self, config: TransformerConfig, pre_process: bool = True, post_process: bool = True,
                  vp_stage: Optional[int] = None, causal: bool = True, cross_attention: bool = False,
-                 post_layer_norm: bool = True):
+                 post_layer_norm: bool = True, spec=None):
+        """``spec``: None, one layer ``ModuleSpec`` (used for every layer) or a ``TransformerBlockSubmodules`` whose
+        ``layer_specs`` list covers the whole model (this stage takes its slice) or just this stage."""
         super().__init__()
+        from .gpt_layer_specs import TransformerBlockSubmodules, layer_spec_is_moe
+        from .spec_utils import ModuleSpec, get_module
         self.config, self.pre_process, self.post_process, self.vp_stage = config, pre_process, post_process, vp_stage
         n = get_num_layers_to_build(config, vp_stage)
         self.layer_offset = get_transformer_layer_offset(config, vp_stage)
         pattern = config.moe_layer_pattern()
-        self.layers = nn.ModuleList([
-            TransformerLayer(config, self.layer_offset + i + 1, is_moe=bool(pattern[self.layer_offset + i]),
-                             causal=causal, cross_attention=cross_attention)
-            for i in range(n)])
-        self.final_layernorm = Norm(config, config.hidden_size) if (post_process and post_layer_norm) else None
+
+        def layer_spec(i):
+            if spec is None:
+                return None
+            if isinstance(spec, TransformerBlockSubmodules):
+                specs = spec.layer_specs or []
+                if len(specs) == n:
+                    return specs[i]
+                if len(specs) == config.num_layers:
+                    return specs[self.layer_offset + i]
+                raise ValueError(f"block spec lists {len(specs)} layers; the stage builds {n} of {config.num_layers}")
+            if isinstance(spec, ModuleSpec):
+                return spec
+            raise TypeError(f"unsupported transformer layer spec {type(spec).__name__}")
+
+        layers = []
+        for i in range(n):
+            ls = layer_spec(i)
+            cls = get_module(ls) if ls is not None else TransformerLayer
+            moe = layer_spec_is_moe(ls)
+            kw = dict(is_moe=bool(pattern[self.layer_offset + i]) if moe is None else moe, causal=causal,
+                      cross_attention=cross_attention)
+            if ls is not None and ls.submodules is not None:
+                kw["submodules"] = ls.submodules
+            layers.append(cls(config, self.layer_offset + i + 1, **kw))
+        self.layers = nn.ModuleList(layers)
+        norm_cls = getattr(spec, "layer_norm", None) if isinstance(spec, TransformerBlockSubmodules) else None
+        if post_process and post_layer_norm:
+            self.final_layernorm = _build_slot(norm_cls, config=config, hidden_size=config.hidden_size) \
+                if norm_cls is not None else Norm(config, config.hidden_size)
+        else:
+            self.final_layernorm = None
         self.input_tensor = None
 
     def set_input_tensor(self, t):
