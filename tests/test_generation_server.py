@@ -39,3 +39,35 @@ def test_server_roundtrip_and_beam():
     g, _ = beam_search(model, [5, 9, 2], 1, 4, stop_token=-1)
     from tests.test_inference import _greedy_reference
     assert g[0][3:] == _greedy_reference(model, [5, 9, 2], 4)
+
+
+def test_server_program_builds_from_training_flags_and_serves_http():
+    import http.client
+    import socket
+    import threading
+    from megatron_lm_b200.inference.run_server import main
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    srv = main(["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
+                "--max-position-embeddings", "32", "--vocab-size", "64", "--position-embedding-type", "rope",
+                "--untie-embeddings-and-output-weights", "--port", str(port), "--host", "127.0.0.1"],
+               serve=False, tokenizer=_Tok())
+    t = threading.Thread(target=srv.run, args=("127.0.0.1", port), daemon=True)
+    t.start()
+    for _ in range(50):
+        try:
+            conn = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
+            conn.request("PUT", "/api", body=json.dumps({"prompts": ["3 4 5"], "tokens_to_generate": 3, "top_k": 1}),
+                         headers={"Content-Type": "application/json"})
+            resp = conn.getresponse()
+            break
+        except ConnectionRefusedError:
+            import time
+            time.sleep(0.1)
+    body = json.loads(resp.read())
+    assert resp.status == 200 and body["text"][0].startswith("3 4 5") and len(body["text"][0].split()) == 6
+    conn = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
+    conn.request("PUT", "/api", body=json.dumps({"prompts": []}), headers={"Content-Type": "application/json"})
+    assert conn.getresponse().status == 400
+    srv.httpd.shutdown()
