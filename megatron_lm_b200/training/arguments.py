@@ -164,6 +164,10 @@ def validate_args(args, defaults: Optional[dict] = None):
         raise ValueError("--min-lr exceeds --lr")
     if args.save is not None and args.save_interval is None:
         raise ValueError("--save needs --save-interval")
+    # one corpus (or mock data) without an explicit split: the customary 969 / 30 / 1 parts
+    if getattr(args, "split", None) is None and (getattr(args, "mock_data", False) or getattr(args, "data_path", None)) \
+            and not getattr(args, "train_data_path", None):
+        args.split = "969,30,1"
     # iteration-based vs sample-based
     if args.train_iters is not None and args.train_samples is not None:
         raise ValueError("give either --train-iters or --train-samples")

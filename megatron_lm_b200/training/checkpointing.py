@@ -74,7 +74,12 @@ def get_rng_state() -> Dict[str, Any]:
     return st
 
 
+LAST_LOADED_RNG_STATE: Optional[Dict[str, Any]] = None     # what the latest load_checkpoint restored, if anything
+
+
 def set_rng_state(st: Dict[str, Any]) -> None:
+    global LAST_LOADED_RNG_STATE
+    LAST_LOADED_RNG_STATE = st
     random.setstate(st["random_rng_state"])
     np.random.set_state(st["np_rng_state"])
     torch.set_rng_state(st["torch_rng_state"])

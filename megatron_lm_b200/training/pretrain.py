@@ -208,6 +208,10 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     timers("train/valid/test-data-iterators-setup", 0).start(barrier=True)
     train_it, valid_it, test_it = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args)
     timers("train/valid/test-data-iterators-setup").stop()
+    if args.load is not None and checkpointing.LAST_LOADED_RNG_STATE is not None:
+        # building the data loaders draws from the host generators (worker base seeds); put the checkpoint's
+        # generator states back so that a resumed run continues exactly like the uninterrupted one
+        checkpointing.set_rng_state(checkpointing.LAST_LOADED_RNG_STATE)
     timers.log(["model-and-optimizer-setup", "train/valid/test-data-iterators-setup"], barrier=True)
     rerun = RerunStateMachine(mode=getattr(args, "rerun_mode", "disabled")) if getattr(args, "rerun_mode", "disabled") \
         != "disabled" else None
