@@ -128,6 +128,17 @@ def build_train_valid_test_data_iterators(provider: Callable, args):
         train_it = iter(tl) if tl is not None else None
         valid_it = cyclic_iter(vl) if vl is not None else None
         test_it = cyclic_iter(sl) if sl is not None else None
+    # every rank of a tensor-parallel group must agree on whether a phase runs: the ranks that do not read data
+    # learn it from the one that does (reference: training.py:2857 broadcasts do_train / do_valid / do_test)
+    flags = torch.tensor([int(train_it is not None), int(valid_it is not None and args.eval_iters > 0),
+                          int(test_it is not None and args.eval_iters > 0)], dtype=torch.int64)
+    if state.get_tensor_model_parallel_world_size() > 1:
+        import torch.distributed as dist
+        backend = dist.get_backend(state.get_tensor_model_parallel_group())
+        dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+        flags = flags.to(dev)
+        dist.broadcast(flags, state.get_tensor_model_parallel_src_rank(), group=state.get_tensor_model_parallel_group())
+    args.do_train, args.do_valid, args.do_test = (bool(x) for x in flags.tolist())
     return train_it, valid_it, test_it
 
 
@@ -253,7 +264,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             straggler.report(iteration)
         if getattr(args, "profile", False) and iteration == args.profile_step_end and torch.cuda.is_available():
             torch.cuda.cudart().cudaProfilerStop()
-        if args.eval_interval and iteration % args.eval_interval == 0 and valid_it is not None:
+        if args.eval_interval and iteration % args.eval_interval == 0 and args.do_valid:
             res = evaluate(forward_step_func, valid_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
                            seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
             print_rank_last(f" validation loss at iteration {iteration} | " +
@@ -284,7 +295,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     if args.save and iteration % max(args.save_interval or 1, 1) != 0 and iteration > 0:
         checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args,
                                       num_floating_point_operations_so_far=flops_so_far)
-    if test_it is not None and args.eval_iters:
+    if args.do_test:
         res = evaluate(forward_step_func, test_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
                        seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
         print_rank_last(" test loss | " + " | ".join(f"{k} value: {v:.6E}" for k, v in res.items()))

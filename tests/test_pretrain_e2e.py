@@ -44,3 +44,26 @@ def test_train_exit_resume(tmp_path):
     # an uninterrupted run reaches the same loss at iteration 8 (same data order, same weights after resume)
     whole = _iters(_run([]))
     assert abs(whole[8][1] - b[8][1]) < 1e-4 and abs(whole[3][1] - a[3][1]) < 1e-6
+
+
+def test_four_rank_tp2_pp2_program_trains_evaluates_and_saves(tmp_path):
+    """torchrun, 4 Gloo ranks, TP2 x PP2 with two virtual stages, sequence parallel, distributed optimizer: the ranks
+    that read no data must still take part in evaluation, and every rank writes its checkpoint shard."""
+    ck = str(tmp_path / "ckpt")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr",
+           "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "pretrain_gpt.py"),
+           "--tensor-model-parallel-size", "2", "--pipeline-model-parallel-size", "2",
+           "--num-layers-per-virtual-pipeline-stage", "1", "--sequence-parallel", "--use-distributed-optimizer",
+           "--distributed-backend", "gloo", "--num-layers", "4", "--hidden-size", "32", "--num-attention-heads", "4",
+           "--seq-length", "32", "--max-position-embeddings", "32", "--micro-batch-size", "1", "--global-batch-size", "4",
+           "--train-iters", "4", "--lr", "1e-3", "--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64",
+           "--log-interval", "1", "--eval-interval", "2", "--eval-iters", "1", "--save", ck, "--save-interval", "4",
+           "--use-cpu-initialization", "--attention-dropout", "0", "--hidden-dropout", "0"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=280, cwd=ROOT, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert sorted(_iters(out)) == [1, 2, 3, 4]
+    assert "validation loss at iteration 2" in out and "validation loss at iteration 4" in out and "test loss" in out
+    assert open(os.path.join(ck, "latest_checkpointed_iteration.txt")).read().strip() == "4"
+    assert len(os.listdir(os.path.join(ck, "iter_0000004"))) >= 4
