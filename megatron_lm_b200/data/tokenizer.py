@@ -414,6 +414,15 @@ class BertWordPieceTokenizer(MegatronTokenizer):
     def eos(self):
         return self.vocab_["[EOS]"]
 
+    @property
+    def additional_special_tokens_ids(self):
+        """The sentinel ids ``<extra_id_i>`` added by ``vocab_extra_ids`` (T5 span corruption)."""
+        return [i for t, i in self.vocab_.items() if t.startswith("<extra_id_")]
+
+    @property
+    def eos(self):
+        return self.vocab_["[EOS]"]
+
 
 def build_tokenizer(args):
     """Instantiate the tokenizer named by ``args.tokenizer_type`` and set ``args.padded_vocab_size``."""

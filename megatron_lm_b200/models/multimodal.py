@@ -33,6 +33,7 @@ class LLaVAModel(nn.Module):
                  language_transformer_layer_spec=None, vision_transformer_layer_spec=None,
                  vision_projection_layer_spec=None, allow_missing_vision_projection_checkpoint: bool = False):
         super().__init__()
+        self.config = language_transformer_config      # the training loop reads the model's config from here
         self.pre_process, self.post_process = pre_process, post_process
         self.add_encoder, self.add_decoder = add_encoder, add_decoder
         self.image_token_index = image_token_index

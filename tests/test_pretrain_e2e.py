@@ -67,3 +67,50 @@ def test_four_rank_tp2_pp2_program_trains_evaluates_and_saves(tmp_path):
     assert "validation loss at iteration 2" in out and "validation loss at iteration 4" in out and "test loss" in out
     assert open(os.path.join(ck, "latest_checkpointed_iteration.txt")).read().strip() == "4"
     assert len(os.listdir(os.path.join(ck, "iter_0000004"))) >= 4
+
+
+def _sentence_corpus(tmp_path):
+    import numpy as np
+    from megatron_lm_b200.data.indexed_dataset import IndexedDatasetBuilder, get_bin_path, get_idx_path
+    prefix = str(tmp_path / "sents")
+    b = IndexedDatasetBuilder(get_bin_path(prefix), dtype=np.int32)
+    rng = np.random.RandomState(0)
+    for _ in range(200):
+        for _ in range(rng.randint(3, 7)):
+            b.add_item(rng.randint(10, 50, size=rng.randint(4, 12)).tolist())
+        b.end_document()
+    b.finalize(get_idx_path(prefix))
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("\n".join(["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"] + [f"w{i}" for i in range(60)]) + "\n")
+    return prefix, str(vocab)
+
+
+def _run_script(script, extra):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29618")
+    common = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
+              "--max-position-embeddings", "64", "--micro-batch-size", "2", "--global-batch-size", "4", "--train-iters",
+              "3", "--lr", "1e-3", "--log-interval", "1", "--eval-interval", "2", "--eval-iters", "1",
+              "--use-cpu-initialization"]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, script)] + common + extra, capture_output=True, text=True,
+                       timeout=300, cwd=ROOT, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-2500:]
+    rows = _iters(out)
+    assert sorted(rows) == [1, 2, 3] and all(0.5 < v[1] < 10 for v in rows.values()), rows
+    assert "validation loss at iteration 2" in out and "test loss" in out
+    return out
+
+
+def test_bert_and_t5_programs_on_a_sentence_corpus(tmp_path):
+    prefix, vocab = _sentence_corpus(tmp_path)
+    data = ["--data-path", prefix, "--split", "90,5,5", "--tokenizer-type", "BertWordPieceLowerCase", "--vocab-file", vocab]
+    out = _run_script("pretrain_bert.py", data)
+    assert "sop loss" in out
+    _run_script("pretrain_t5.py", data + ["--encoder-seq-length", "32", "--decoder-seq-length", "16",
+                                          "--vocab-extra-ids", "10"])
+
+
+def test_mamba_and_vlm_programs_on_mock_data():
+    mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64"]
+    _run_script("pretrain_mamba.py", mock + ["--mamba-head-dim", "16", "--mamba-num-groups", "2", "--mamba-state-dim", "16"])
+    _run_script("pretrain_vlm.py", mock + ["--img-h", "28", "--img-w", "28", "--patch-dim", "14"])
