@@ -152,6 +152,8 @@ class Timers:
                 lines.append(f"  {n}:")
                 for r in range(t.shape[0]):
                     lines.append(f"     rank {r:2d}: {t[r, i]:.2f}")
+        if len(lines) <= 1:
+            return None                      # nothing was timed since the last report: no bare heading
         return "\n".join(lines)
 
     def log(self, names=None, rank=None, normalizer: float = 1.0, reset: bool = True, barrier: bool = False):
