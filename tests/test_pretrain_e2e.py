@@ -114,3 +114,27 @@ def test_mamba_and_vlm_programs_on_mock_data():
     mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64"]
     _run_script("pretrain_mamba.py", mock + ["--mamba-head-dim", "16", "--mamba-num-groups", "2", "--mamba-state-dim", "16"])
     _run_script("pretrain_vlm.py", mock + ["--img-h", "28", "--img-w", "28", "--patch-dim", "14"])
+
+
+def _torchrun(nproc, port, extra):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "pretrain_gpt.py"), "--distributed-backend", "gloo",
+           "--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
+           "--max-position-embeddings", "32", "--micro-batch-size", "1", "--train-iters", "3", "--lr", "1e-3",
+           "--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--log-interval", "1",
+           "--eval-interval", "2", "--eval-iters", "1", "--use-cpu-initialization", "--attention-dropout", "0",
+           "--hidden-dropout", "0"] + extra
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=280, cwd=ROOT, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert sorted(_iters(out)) == [1, 2, 3] and "validation loss at iteration 2" in out and "test loss" in out
+    return out
+
+
+def test_expert_parallel_and_context_parallel_programs():
+    _torchrun(2, 29642, ["--global-batch-size", "4", "--expert-model-parallel-size", "2", "--num-experts", "4",
+                         "--moe-router-topk", "2", "--moe-aux-loss-coeff", "0.01", "--moe-router-load-balancing-type",
+                         "aux_loss", "--moe-grouped-gemm", "--moe-token-dispatcher-type", "alltoall",
+                         "--use-distributed-optimizer"])
+    _torchrun(2, 29643, ["--global-batch-size", "2", "--context-parallel-size", "2", "--position-embedding-type", "rope"])
