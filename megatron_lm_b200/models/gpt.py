@@ -167,6 +167,13 @@ class GPTModel(nn.Module):
                                                      skip_weight_param_allocation=skip)
             self.output_layer.fp8_eligible = False          # the vocabulary projection stays in 16 bits
         self._setup_shared_embeddings()
+        if post_process and config.mtp_num_layers:
+            # the prediction heads reuse the embedding and the output layer: several gradients per microbatch
+            shared = list(self.embedding.parameters())
+            if self.output_layer.weight is not None:
+                shared.append(self.output_layer.weight)
+            for p in shared:
+                p.expected_grad_signals = max(2, getattr(p, "expected_grad_signals", 1))
 
     # -- tied embeddings ---------------------------------------------------
     def _setup_shared_embeddings(self):

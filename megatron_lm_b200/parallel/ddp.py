@@ -159,13 +159,13 @@ class BucketGroup:
     def register_grad_ready(self, p):
         if not self.is_last_microbatch:
             return
-        # a parameter used at several places (tied embedding / output weight on one stage)
-        # is ready once every use has delivered its gradient
-        need = getattr(p, "expected_grad_signals", 1)
-        if need > 1:
+        # a parameter used at several places (tied embedding / output weight on one stage, modules shared with
+        # the multi-token-prediction heads) delivers several partial gradients per microbatch, and how many
+        # signals that makes depends on which uses run custom kernels and which plain autograd.  Its bucket is
+        # therefore not released early: finish_grad_sync reduces it once the backward pass is over.
+        if getattr(p, "expected_grad_signals", 1) > 1:
             self.counts[p] = self.counts.get(p, 0) + 1
-            if self.counts[p] < need:
-                return
+            return
         if p in self.ready:
             raise RuntimeError("gradient of a parameter signalled ready twice in one microbatch")
         self.ready.add(p)

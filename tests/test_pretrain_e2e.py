@@ -138,3 +138,12 @@ def test_expert_parallel_and_context_parallel_programs():
                          "aux_loss", "--moe-grouped-gemm", "--moe-token-dispatcher-type", "alltoall",
                          "--use-distributed-optimizer"])
     _torchrun(2, 29643, ["--global-batch-size", "2", "--context-parallel-size", "2", "--position-embedding-type", "rope"])
+
+
+def test_feature_flags_run_in_the_program():
+    """Options that change the step's structure: multi-token prediction (modules shared between the main model and
+    the prediction heads deliver several gradients per microbatch), full recomputation, the rerun state machine."""
+    mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64"]
+    _run_script("pretrain_gpt.py", mock + ["--mtp-num-layers", "1"])
+    _run_script("pretrain_gpt.py", mock + ["--recompute-granularity", "full", "--recompute-method", "uniform",
+                                           "--recompute-num-layers", "1", "--rerun-mode", "validate_results"])
