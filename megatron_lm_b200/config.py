@@ -466,6 +466,7 @@ class DistributedDataParallelConfig:
     fp8_param_gather: bool = False
     reuse_grad_buf_for_mxfp8_param_ag: bool = False
     use_custom_fsdp: bool = False
+    use_torch_fsdp2: bool = False
     data_parallel_sharding_strategy: str = "no_shard"
     gradient_reduce_div_fusion: bool = True
     suggested_communication_unit_size: Optional[int] = None

@@ -386,6 +386,9 @@ class ShardedAdam:
     def scale_loss(self, loss):
         return loss
 
+    def get_loss_scale(self) -> torch.Tensor:
+        return torch.ones(1, dtype=torch.float32, device=self.state[0]["unit"].device if self.state else "cpu")
+
     def get_grad_norm(self) -> torch.Tensor:
         dev = self.state[0]["unit"].device
         tot = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -489,3 +492,73 @@ class TorchFullyShardedDataParallel(nn.Module):
             if p.grad is not None:
                 p.grad.mul_(factor)
     def broadcast_params(self): pass
+
+
+class TorchOptimizerAdapter:
+    """A ``torch.optim`` optimizer behind the method surface the training loop uses (``step`` returning
+    ``(update_successful, grad_norm, num_zeros)``, ``scale_loss``, ``get_loss_scale``, ``param_groups`` written by
+    the scheduler).  Used with torch FSDP2, whose parameters are DTensors that the flat-buffer optimizers of this
+    library do not own."""
+
+    def __init__(self, params, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 clip_grad: float = 0.0, optimizer: str = "adam", momentum: float = 0.0):
+        params = [p for p in params if p.requires_grad]
+        decay = [p for p in params if p.dim() > 1]
+        no_decay = [p for p in params if p.dim() <= 1]
+        groups = [dict(params=decay, weight_decay=weight_decay, wd_mult=1.0, lr_mult=1.0, max_lr=lr, min_lr=0.0),
+                  dict(params=no_decay, weight_decay=0.0, wd_mult=0.0, lr_mult=1.0, max_lr=lr, min_lr=0.0)]
+        groups = [g for g in groups if g["params"]]
+        if optimizer == "adam":
+            self.opt = torch.optim.AdamW(groups, lr=lr, betas=betas, eps=eps)
+        elif optimizer == "sgd":
+            self.opt = torch.optim.SGD(groups, lr=lr, momentum=momentum)
+        else:
+            raise ValueError(f"unknown optimizer {optimizer}")
+        self.clip = clip_grad
+        self.params = params
+
+    @property
+    def param_groups(self):
+        return self.opt.param_groups
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.opt.zero_grad(set_to_none=set_to_none)
+
+    def scale_loss(self, loss):
+        return loss
+
+    def get_loss_scale(self) -> torch.Tensor:
+        return torch.ones(1, dtype=torch.float32)
+
+    def step(self):
+        for g in self.opt.param_groups:                 # the scheduler writes one decay value; groups scale it
+            g["weight_decay"] = g["weight_decay"] * g.get("wd_mult", 1.0) if g.get("wd_mult", 1.0) == 0.0 \
+                else g["weight_decay"]
+        with_grad = [p for p in self.params if p.grad is not None]
+        norm = torch.nn.utils.clip_grad_norm_(with_grad, self.clip if self.clip > 0 else float("inf"))
+        if hasattr(norm, "full_tensor"):
+            norm = norm.full_tensor()
+        self.opt.step()
+        return True, float(norm), None
+
+    def materialize_state(self):
+        """Create the optimizer's per-parameter slots (torch builds them at the first step) without moving the
+        weights: one step with zero gradients at learning rate 0.  Needed before a checkpoint's state is copied in."""
+        saved = [(g["lr"], g["weight_decay"]) for g in self.opt.param_groups]
+        for g in self.opt.param_groups:
+            g["lr"], g["weight_decay"] = 0.0, 0.0
+        for p in self.params:
+            p.grad = torch.zeros_like(p)
+        self.opt.step()
+        self.opt.zero_grad(set_to_none=True)
+        for g, (lr, wd) in zip(self.opt.param_groups, saved):
+            g["lr"], g["weight_decay"] = lr, wd
+
+    def state_dict(self):
+        return self.opt.state_dict()
+
+    def load_state_dict(self, sd):
+        self.opt.load_state_dict(sd)
+
+    def reload_model_params(self):
+        pass

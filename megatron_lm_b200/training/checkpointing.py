@@ -222,6 +222,73 @@ def _write_tracker(save_dir: str, iteration: int) -> None:
             f.write(str(iteration))
 
 
+# ----------------------------------------------------------------------------- sharded data parallel (FSDP) models
+def _is_fsdp_optimizer(optimizer) -> bool:
+    from ..parallel.fsdp import ShardedAdam, TorchOptimizerAdapter
+    return isinstance(optimizer, (ShardedAdam, TorchOptimizerAdapter))
+
+
+def _fsdp_rank_file(base: str) -> str:
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    return os.path.join(base, f"fsdp_rank_{rank:05d}.pt")
+
+
+def _save_fsdp(iteration, model, optimizer, scheduler, save_dir, rng, flops):
+    """Every rank writes the slices it owns (``fsdp_rank_<r>.pt``): with the custom FSDP units the optimizer's fp32
+    master shards are the weights; with torch FSDP2 the local parts of the DTensor parameters and of the torch
+    optimizer state.  The layout is tied to the world size it was written with."""
+    from ..parallel.fsdp import ShardedAdam
+    base = get_checkpoint_name(save_dir, iteration, return_base_dir=True)
+    os.makedirs(base, exist_ok=True)
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    sd = {"iteration": iteration, "world_size": world, "rng_state": rng,
+          "num_floating_point_operations_so_far": flops,
+          "opt_param_scheduler": scheduler.state_dict() if scheduler is not None else None}
+    if isinstance(optimizer, ShardedAdam):
+        sd["kind"], sd["optimizer"] = "custom_fsdp", optimizer.state_dict()
+    else:
+        local = lambda t: t.to_local() if hasattr(t, "to_local") else t
+        sd["kind"] = "torch_fsdp2"
+        sd["model"] = [{n: local(p.detach()).clone() for n, p in m.module.named_parameters()} for m in model]
+        osd = optimizer.state_dict()
+        sd["optimizer"] = {"param_groups": osd["param_groups"],
+                           "state": {k: {kk: (local(vv).clone() if torch.is_tensor(vv) else vv) for kk, vv in v.items()}
+                                     for k, v in osd["state"].items()}}
+    torch.save(sd, _fsdp_rank_file(base))
+    if dist.is_initialized():
+        dist.barrier()
+    _write_tracker(save_dir, iteration)
+
+
+def _load_fsdp(model, optimizer, scheduler, base: str, no_optim: bool, no_rng: bool):
+    from ..parallel.fsdp import ShardedAdam
+    sd = torch.load(_fsdp_rank_file(base), map_location="cpu", weights_only=False)
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if sd["world_size"] != world:
+        raise RuntimeError(f"this FSDP checkpoint was written by {sd['world_size']} ranks; {world} are loading it")
+    if isinstance(optimizer, ShardedAdam):
+        optimizer.load_state_dict(sd["optimizer"])       # master shards -> parameter shards -> re-gather
+    else:
+        with torch.no_grad():
+            for m, saved in zip(model, sd["model"]):
+                for n, p in m.module.named_parameters():
+                    (p.to_local() if hasattr(p, "to_local") else p).copy_(saved[n])
+        if not no_optim:
+            if not optimizer.state_dict()["state"]:
+                optimizer.materialize_state()
+            cur = optimizer.state_dict()
+            for k, v in sd["optimizer"]["state"].items():
+                for kk, vv in v.items():
+                    if torch.is_tensor(vv) and k in cur["state"]:
+                        tgt = cur["state"][k][kk]
+                        (tgt.to_local() if hasattr(tgt, "to_local") else tgt).copy_(vv)
+    if scheduler is not None and sd.get("opt_param_scheduler") is not None and not no_optim:
+        scheduler.load_state_dict(sd["opt_param_scheduler"])
+    if not no_rng and sd.get("rng_state") is not None:
+        set_rng_state(sd["rng_state"])
+    return int(sd["iteration"]), float(sd.get("num_floating_point_operations_so_far", 0.0))
+
+
 def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args, *,
                     num_floating_point_operations_so_far: float = 0.0, rerun_state=None,
                     non_persistent: bool = False, ec_manager=None) -> Dict[str, float]:
@@ -240,6 +307,11 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
     save_dir = args.non_persistent_global_ckpt_dir if non_persistent else args.save
     fmt = getattr(args, "ckpt_format", "torch_dist")
     rng = get_rng_state()
+    if _is_fsdp_optimizer(optimizer):
+        _save_fsdp(iteration, model, optimizer, opt_param_scheduler, save_dir, rng,
+                   num_floating_point_operations_so_far)
+        stats["total_s"] = time.time() - t0
+        return stats
     if fmt == "torch_dist":
         sd = generate_state_dict(args, model, optimizer, opt_param_scheduler, rng, iteration, True, rerun_state,
                                  num_floating_point_operations_so_far)
@@ -287,6 +359,9 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Op
         return 0, 0.0
     iteration, release = read_metadata(tracker)
     base = get_checkpoint_name(load_dir, iteration, release, return_base_dir=True)
+    if optimizer is not None and _is_fsdp_optimizer(optimizer):
+        return _load_fsdp(model, optimizer, opt_param_scheduler, base, getattr(args, "no_load_optim", False),
+                          getattr(args, "no_load_rng", False))
     finetune = getattr(args, "finetune", False)
     no_optim = getattr(args, "no_load_optim", False) or finetune or release
     no_rng = getattr(args, "no_load_rng", False) or finetune or release

@@ -28,7 +28,8 @@ from .arguments import (core_transformer_config_from_args, ddp_config_from_args,
                         parse_args, set_args, validate_args)
 from .flops import flops_from_config
 from .resilience import DistributedSignalHandler, RerunStateMachine, StragglerDetector
-from .training import (evaluate, get_model, get_optimizer_param_scheduler, install_callbacks, train_step)
+from .training import (build_optimizer, evaluate, get_model, get_optimizer_param_scheduler, install_callbacks,
+                       train_step)
 from ..optimizer import get_megatron_optimizer
 
 _TIMERS: Optional[Timers] = None
@@ -194,7 +195,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     ocfg, dcfg = optimizer_config_from_args(args), ddp_config_from_args(args)
     timers("model-and-optimizer-setup", 0).start(barrier=True)
     model = get_model(lambda **kw: model_provider(config=config, **kw), config, dcfg)
-    optimizer = get_megatron_optimizer(ocfg, model)
+    optimizer = build_optimizer(ocfg, model)
     scheduler = get_optimizer_param_scheduler(
         optimizer, lr=args.lr, min_lr=args.min_lr, lr_decay_style=args.lr_decay_style, train_iters=args.train_iters,
         global_batch_size=args.global_batch_size, lr_decay_iters=args.lr_decay_iters,

@@ -50,6 +50,11 @@ def get_model(model_provider: Callable, config: TransformerConfig, ddp_config: O
         return chunks
     ddp_config = ddp_config or DistributedDataParallelConfig()
     wrapped = []
+    if getattr(ddp_config, "use_custom_fsdp", False) or getattr(ddp_config, "use_torch_fsdp2", False):
+        # sharded data parallelism (ZeRO-1/2/3 units or torch FSDP2) instead of the replicated buffers
+        from ..parallel.fsdp import FullyShardedDataParallel, TorchFullyShardedDataParallel
+        cls = FullyShardedDataParallel if getattr(ddp_config, "use_custom_fsdp", False) else TorchFullyShardedDataParallel
+        return [cls(config, ddp_config, m) for m in chunks]
     for i, m in enumerate(chunks):
         # bucketing only helps overlap on the first chunk; later chunks sync as one bucket
         wrapped.append(DistributedDataParallel(config, ddp_config, m, disable_bucketing=(i > 0) or
@@ -85,11 +90,38 @@ def get_optimizer_param_scheduler(optimizer, *, lr: float, min_lr: float = 0.0, 
                                    lr_wsd_decay_style=lr_wsd_decay_style, use_checkpoint_opt_param_scheduler=False)
 
 
+def build_optimizer(optimizer_config: OptimizerConfig, model, no_wd_decay_cond=None, scale_lr_cond=None,
+                    lr_mult: float = 1.0, cpu_offload: bool = False, offload_fraction: float = 1.0):
+    """The optimizer that fits how ``model`` is wrapped: sharded AdamW for FSDP chunks, the host-resident hybrid
+    optimizer when offloading is asked for, else the flat mixed-precision (optionally ZeRO-1) optimizer."""
+    from ..parallel.fsdp import FullyShardedDataParallel
+    if model and isinstance(model[0], FullyShardedDataParallel):
+        from ..parallel.fsdp import ShardedAdam
+        if optimizer_config.optimizer != "adam":
+            raise ValueError("the sharded (FSDP) data-parallel path implements AdamW only")
+        mp = state.get_model_parallel_group() if state.model_parallel_is_initialized() and \
+            state.get_group_size("mp") > 1 else None
+        return ShardedAdam(model, lr=optimizer_config.lr or 0.0,
+                           betas=(optimizer_config.adam_beta1, optimizer_config.adam_beta2),
+                           eps=optimizer_config.adam_eps, weight_decay=optimizer_config.weight_decay,
+                           clip_grad=optimizer_config.clip_grad or 0.0, model_parallel_group=mp)
+    from ..parallel.fsdp import TorchFullyShardedDataParallel
+    if model and isinstance(model[0], TorchFullyShardedDataParallel):
+        from ..parallel.fsdp import TorchOptimizerAdapter
+        params = [p for m in model for p in m.parameters()]
+        return TorchOptimizerAdapter(params, lr=optimizer_config.lr or 0.0,
+                                     betas=(optimizer_config.adam_beta1, optimizer_config.adam_beta2),
+                                     eps=optimizer_config.adam_eps, weight_decay=optimizer_config.weight_decay,
+                                     clip_grad=optimizer_config.clip_grad or 0.0, optimizer=optimizer_config.optimizer,
+                                     momentum=optimizer_config.sgd_momentum)
+    return get_megatron_optimizer(optimizer_config, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
+
+
 def setup_model_and_optimizer(model_provider, config: TransformerConfig, optimizer_config: OptimizerConfig,
                               ddp_config: Optional[DistributedDataParallelConfig] = None, scheduler_kwargs=None,
                               no_wd_decay_cond=None, scale_lr_cond=None, lr_mult: float = 1.0):
     model = get_model(model_provider, config, ddp_config)
-    optimizer = get_megatron_optimizer(optimizer_config, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
+    optimizer = build_optimizer(optimizer_config, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
     scheduler = None
     if scheduler_kwargs is not None:
         scheduler = get_optimizer_param_scheduler(optimizer, **scheduler_kwargs)

@@ -147,3 +147,37 @@ def test_feature_flags_run_in_the_program():
     _run_script("pretrain_gpt.py", mock + ["--mtp-num-layers", "1"])
     _run_script("pretrain_gpt.py", mock + ["--recompute-granularity", "full", "--recompute-method", "uniform",
                                            "--recompute-num-layers", "1", "--rerun-mode", "validate_results"])
+
+
+def test_sharded_data_parallel_programs_match_replicated_and_resume(tmp_path):
+    """--use-custom-fsdp (ZeRO-3 units + sharded AdamW) and --use-torch-fsdp2 train to the same losses as the
+    replicated data-parallel path on two ranks, and a custom-FSDP run resumes from its per-rank shard files."""
+    base = ["--global-batch-size", "4"]
+    ref = _iters(_torchrun(2, 29644, base))
+    z3 = _iters(_torchrun(2, 29645, base + ["--use-custom-fsdp", "--data-parallel-sharding-strategy",
+                                            "optim_grads_params"]))
+    f2 = _iters(_torchrun(2, 29646, base + ["--use-torch-fsdp2"]))
+    for it in (1, 2, 3):
+        assert abs(ref[it][1] - z3[it][1]) < 1e-5 and abs(ref[it][1] - f2[it][1]) < 1e-5
+    ck = str(tmp_path / "ck")
+    fs = base + ["--use-custom-fsdp", "--data-parallel-sharding-strategy", "optim_grads_params", "--save", ck,
+                 "--save-interval", "2"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    _torchrun(2, 29647, fs)                                      # saves at iteration 2 (and stops at 3)
+    assert sorted(os.listdir(os.path.join(ck, "iter_0000002"))) == ["fsdp_rank_00000.pt", "fsdp_rank_00001.pt"]
+    with open(os.path.join(ck, "latest_checkpointed_iteration.txt"), "w") as f:
+        f.write("2")                                               # resume from the mid-run checkpoint
+    cmd_tail = fs + ["--load", ck]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29648", os.path.join(ROOT, "pretrain_gpt.py"),
+                        "--distributed-backend", "gloo", "--num-layers", "2", "--hidden-size", "32",
+                        "--num-attention-heads", "4", "--seq-length", "32", "--max-position-embeddings", "32",
+                        "--micro-batch-size", "1", "--train-iters", "3", "--lr", "1e-3", "--mock-data",
+                        "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--log-interval", "1",
+                        "--eval-interval", "2", "--eval-iters", "1", "--use-cpu-initialization", "--attention-dropout",
+                        "0", "--hidden-dropout", "0"] + cmd_tail, capture_output=True, text=True, timeout=280, cwd=ROOT,
+                       env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-2500:]
+    resumed = _iters(out)
+    assert sorted(resumed) == [3] and abs(resumed[3][1] - z3[3][1]) < 1e-5
