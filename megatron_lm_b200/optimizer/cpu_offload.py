@@ -43,8 +43,9 @@ class HybridDeviceOptimizer(torch.optim.Optimizer):
         self.gpu_master: Dict[torch.nn.Parameter, torch.Tensor] = {}
         cpu_groups, gpu_groups = [], []
         used = 0
-        for g in self.param_groups:
+        for gi, g in enumerate(self.param_groups):
             opts = {k: v for k, v in g.items() if k != "params"}
+            opts["outer_group"] = gi                      # which of this optimizer's groups an inner group mirrors
             cg, gg = dict(opts, params=[]), dict(opts, params=[])
             for p in g["params"]:
                 if used + p.numel() <= budget:
@@ -77,11 +78,10 @@ class HybridDeviceOptimizer(torch.optim.Optimizer):
         """lr / weight decay set on this optimizer's groups by a scheduler reach the inner optimizers."""
         for inner in self.sub_optimizers:
             for ig in inner.param_groups:
-                for g in self.param_groups:
-                    for k in ("lr", "weight_decay", "betas", "eps"):
-                        if k in g:
-                            ig[k] = g[k]
-                    break
+                g = self.param_groups[ig.get("outer_group", 0)]
+                for k in ("lr", "weight_decay", "betas", "eps"):
+                    if k in g:
+                        ig[k] = g[k]
 
     def _grad_of(self, p):
         g = getattr(p, "main_grad", None)
@@ -106,7 +106,18 @@ class HybridDeviceOptimizer(torch.optim.Optimizer):
                 g = self._grad_of(p)
                 if g is not None:
                     m.grad.copy_(g.detach().float().reshape(m.shape))
+            # parameters the device optimizer updates in place take their gradient from main_grad when the
+            # model keeps gradients in the data-parallel buffers (``.grad`` is then empty)
+            masters = {id(m) for m in self.gpu_master.values()}
+            direct = [p for g in self.gpu_optimizer.param_groups for p in g["params"] if id(p) not in masters]
+            for p in direct:
+                mg = getattr(p, "main_grad", None)
+                if mg is not None:
+                    p.grad = mg.to(p.dtype).reshape(p.shape)
             self.gpu_optimizer.step()
+            for p in direct:
+                if getattr(p, "main_grad", None) is not None:
+                    p.grad = None
             for p, m in self.gpu_master.items():
                 p.data.copy_(m.to(p.dtype))
         # 3. host update, then weights return
@@ -146,3 +157,79 @@ class HybridDeviceOptimizer(torch.optim.Optimizer):
 class _null:
     def __enter__(self): return self
     def __exit__(self, *a): return False
+
+
+class OffloadedOptimizer:
+    """``HybridDeviceOptimizer`` behind the training loop's optimizer surface, for models wrapped in the replicated
+    data-parallel buffers: gradients are read from ``main_grad`` after the data-parallel reduction, the global norm
+    (over the model-parallel group) clips them, weight-decay groups follow the usual bias / 1-d rule.
+    Selected by ``--optimizer-cpu-offload`` with ``--optimizer-offload-fraction`` (reference:
+    megatron/core/optimizer/__init__.py:330-370 building HybridDeviceOptimizer)."""
+
+    def __init__(self, model_chunks, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 clip_grad: float = 0.0, offload_fraction: float = 1.0, model_parallel_group=None):
+        named = [(n, p) for m in model_chunks for n, p in m.named_parameters() if p.requires_grad]
+        decay = [p for n, p in named if not (n.endswith(".bias") or p.dim() == 1)]
+        no_decay = [p for n, p in named if (n.endswith(".bias") or p.dim() == 1)]
+        groups = [g for g in (dict(params=decay, weight_decay=weight_decay, wd_mult=1.0),
+                              dict(params=no_decay, weight_decay=0.0, wd_mult=0.0)) if g["params"]]
+        self.opt = HybridDeviceOptimizer(groups, offload_fraction=offload_fraction, lr=lr, betas=betas, eps=eps,
+                                         weight_decay=weight_decay)
+        for g in self.opt.param_groups:
+            g.setdefault("max_lr", lr)
+            g.setdefault("min_lr", 0.0)
+        self.params = [p for _, p in named]
+        self.clip, self.mp_group = clip_grad, model_parallel_group
+
+    @property
+    def param_groups(self):
+        return self.opt.param_groups
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.opt.zero_grad(set_to_none)
+
+    def scale_loss(self, loss):
+        return loss
+
+    def get_loss_scale(self) -> torch.Tensor:
+        return torch.ones(1, dtype=torch.float32)
+
+    @torch.no_grad()
+    def step(self):
+        import torch.distributed as dist
+        from ..parallel import state
+        for g in self.opt.param_groups:                       # the scheduler writes one decay for all groups
+            g["weight_decay"] = g["weight_decay"] * g.get("wd_mult", 1.0)
+        tp0 = (not state.model_parallel_is_initialized()) or state.get_tensor_model_parallel_rank() == 0
+        dev = self.params[0].device
+        tot = torch.zeros(1, dtype=torch.float32, device=dev)
+        grads = []
+        for p in self.params:
+            g = getattr(p, "main_grad", None)
+            g = g if g is not None else p.grad
+            if g is None:
+                continue
+            grads.append(g)
+            if getattr(p, "tensor_model_parallel", False) or tp0:
+                tot += g.float().pow(2).sum()
+        if self.mp_group is not None:
+            dist.all_reduce(tot, group=self.mp_group)
+        norm = tot.sqrt()
+        if self.clip > 0:
+            coef = torch.clamp(self.clip / (norm + 1e-6), max=1.0)
+            for g in grads:
+                g.mul_(coef.to(g.dtype))
+        self.opt.step()
+        return True, float(norm), None
+
+    def state_dict(self):
+        return self.opt.state_dict()
+
+    def load_state_dict(self, sd):
+        self.opt.load_state_dict(sd)
+
+    def reload_model_params(self):
+        for p, host in self.opt.cpu_copy.items():
+            host.copy_(p.detach().float().cpu().reshape(host.shape))
+        for p, m in self.opt.gpu_master.items():
+            m.copy_(p.detach().float())

@@ -114,6 +114,18 @@ def build_optimizer(optimizer_config: OptimizerConfig, model, no_wd_decay_cond=N
                                      eps=optimizer_config.adam_eps, weight_decay=optimizer_config.weight_decay,
                                      clip_grad=optimizer_config.clip_grad or 0.0, optimizer=optimizer_config.optimizer,
                                      momentum=optimizer_config.sgd_momentum)
+    if getattr(optimizer_config, "optimizer_cpu_offload", False):
+        from ..optimizer.cpu_offload import OffloadedOptimizer
+        if optimizer_config.use_distributed_optimizer or optimizer_config.optimizer != "adam":
+            raise ValueError("--optimizer-cpu-offload here covers AdamW without the distributed optimizer")
+        mp = state.get_model_parallel_group() if state.model_parallel_is_initialized() and \
+            state.get_group_size("mp") > 1 else None
+        return OffloadedOptimizer([m.module for m in model], lr=optimizer_config.lr or 0.0,
+                                  betas=(optimizer_config.adam_beta1, optimizer_config.adam_beta2),
+                                  eps=optimizer_config.adam_eps, weight_decay=optimizer_config.weight_decay,
+                                  clip_grad=optimizer_config.clip_grad or 0.0,
+                                  offload_fraction=optimizer_config.optimizer_offload_fraction,
+                                  model_parallel_group=mp)
     return get_megatron_optimizer(optimizer_config, model, no_wd_decay_cond, scale_lr_cond, lr_mult)
 
 

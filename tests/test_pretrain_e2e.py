@@ -181,3 +181,12 @@ def test_sharded_data_parallel_programs_match_replicated_and_resume(tmp_path):
     assert r.returncode == 0, out[-2500:]
     resumed = _iters(out)
     assert sorted(resumed) == [3] and abs(resumed[3][1] - z3[3][1]) < 1e-5
+
+
+def test_optimizer_cpu_offload_program_matches_the_device_optimizer():
+    mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--attention-dropout", "0",
+            "--hidden-dropout", "0"]
+    ref = _iters(_run_script("pretrain_gpt.py", mock))
+    for frac in ("1.0", "0.5"):
+        got = _iters(_run_script("pretrain_gpt.py", mock + ["--optimizer-cpu-offload", "--optimizer-offload-fraction", frac]))
+        assert all(abs(ref[i][1] - got[i][1]) < 1e-5 for i in (1, 2, 3)), (frac, ref, got)
