@@ -11,6 +11,7 @@ from __future__ import annotations
 import os
 import signal
 import sys
+import math
 import time
 from datetime import timedelta
 from typing import Callable, Dict, Optional
@@ -177,10 +178,18 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
         _WRITER.add_scalar("throughput", throughput, iteration)
         if grad_norm is not None:
             _WRITER.add_scalar("grad-norm", float(grad_norm), iteration)
+        if getattr(args, "log_loss_scale_to_tensorboard", False):
+            _WRITER.add_scalar("loss-scale", loss_scale, iteration)
+        if getattr(args, "log_world_size_to_tensorboard", False):
+            _WRITER.add_scalar("world-size", args.world_size, iteration)
         if torch.cuda.is_available():
             _WRITER.add_scalar("mem-allocated-bytes", torch.cuda.memory_allocated(), iteration)
             _WRITER.add_scalar("mem-max-allocated-bytes", torch.cuda.max_memory_allocated(), iteration)
     print_rank_last(line)
+    if getattr(args, "log_timers_to_tensorboard", False) and _TIMERS is not None:
+        # a collective over all ranks: outside the writer-only branch
+        _TIMERS.write(["forward-backward", "optimizer", "save-checkpoint"], _WRITER, iteration,
+                      normalizer=args.log_interval, reset=False)
     if _TIMERS is not None:
         _TIMERS.log(normalizer=args.log_interval)
 
@@ -237,6 +246,30 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         m.train()
     t_last = time.time()
     its = [train_it] * len(model) if len(model) > 1 else train_it
+    if getattr(args, "manual_gc", False):
+        import gc
+        gc.disable()                     # collections happen at chosen iterations, on every rank at once
+        gc.collect()
+    energy = None
+    if getattr(args, "log_energy", False):
+        from ..utils.energy_monitor import EnergyMonitor
+        try:
+            energy = EnergyMonitor()
+            energy.setup()
+            energy.resume()
+        except Exception as e:           # no NVML on this host
+            print_rank_0(f"energy monitor unavailable: {e}")
+            energy = None
+    heart = None
+    if getattr(args, "enable_ft_package", False):
+        from .resilience import HeartbeatMonitor
+        heart = HeartbeatMonitor(on_timeout=lambda sec, dt: print(
+            f"[rank {args.rank}] no heartbeat for {dt:.0f} s in section '{sec}'", flush=True))
+        heart.start_section("step")
+    if getattr(args, "record_memory_history", False) and torch.cuda.is_available():
+        torch.cuda.memory._record_memory_history(max_entries=100000)
+    if getattr(args, "skip_train", False):
+        iteration = max(iteration, args.train_iters)
     while iteration < args.train_iters:
         checkpointing.maybe_finalize_async_save(blocking=False)
         if getattr(args, "profile", False) and iteration == args.profile_step_start and torch.cuda.is_available() \
@@ -263,13 +296,39 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
                      args, max(elapsed, 1e-9), config, args.global_batch_size * args.seq_length)
         if straggler is not None and iteration % args.log_interval == 0:
             straggler.report(iteration)
+        if heart is not None:
+            heart.heartbeat()
+        if energy is not None and iteration % args.log_interval == 0:
+            joules = energy.lap()
+            print_rank_last(f" energy since the last report: {joules:.1f} J "
+                            f"({joules / max(args.log_interval * args.global_batch_size * args.seq_length, 1):.4f} J/token)")
+            if _WRITER is not None:
+                _WRITER.add_scalar("energy-joules", joules, iteration)
+        if getattr(args, "manual_gc", False) and getattr(args, "manual_gc_interval", 0) and \
+                iteration % args.manual_gc_interval == 0:
+            import gc
+            gc.collect()
+        hash_every = getattr(args, "check_weight_hash_across_dp_replicas_interval", None)
+        if hash_every and iteration % hash_every == 0:
+            from ..utils.common import check_param_hashes_across_dp_replicas
+            if not check_param_hashes_across_dp_replicas(model):
+                raise RuntimeError(f"data-parallel replicas hold different weights at iteration {iteration}")
         if getattr(args, "profile", False) and iteration == args.profile_step_end and torch.cuda.is_available():
             torch.cuda.cudart().cudaProfilerStop()
         if args.eval_interval and iteration % args.eval_interval == 0 and args.do_valid:
             res = evaluate(forward_step_func, valid_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
                            seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
             print_rank_last(f" validation loss at iteration {iteration} | " +
-                            " | ".join(f"{k} value: {v:.6E}" for k, v in res.items()))
+                            " | ".join(f"{k} value: {v:.6E} | {k} PPL: {math.exp(min(20.0, v)):.6E}"
+                                       for k, v in res.items()))
+            if _WRITER is not None:
+                for k, v in res.items():
+                    _WRITER.add_scalar(f"{k} validation", v, iteration)
+                    if getattr(args, "log_validation_ppl_to_tensorboard", False):
+                        _WRITER.add_scalar(f"{k} validation ppl", math.exp(min(20.0, v)), iteration)
+            if getattr(args, "manual_gc", False) and getattr(args, "manual_gc_eval", False):
+                import gc
+                gc.collect()
         if ec_manager is not None and args.non_persistent_save_interval and \
                 iteration % args.non_persistent_save_interval == 0:
             st = checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args, non_persistent=True,
@@ -300,6 +359,16 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         res = evaluate(forward_step_func, test_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
                        seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
         print_rank_last(" test loss | " + " | ".join(f"{k} value: {v:.6E}" for k, v in res.items()))
+    if heart is not None:
+        heart.end_section()
+        heart.calculate_and_persist_timeouts()
+        heart.shutdown()
+    if energy is not None:
+        print_rank_last(f" total energy: {energy.get_total():.1f} J")
+        energy.shutdown()
+    if getattr(args, "record_memory_history", False) and torch.cuda.is_available():
+        path = getattr(args, "memory_snapshot_path", None) or "snapshot.pickle"
+        torch.cuda.memory._dump_snapshot(f"{path}.rank{args.rank}")
     if _WRITER is not None:
         _WRITER.flush()
     return model, optimizer, scheduler

@@ -165,9 +165,13 @@ class Timers:
             print(s, flush=True)
 
     def write(self, names, writer, iteration: int, normalizer: float = 1.0, reset: bool = True, barrier: bool = False):
-        names = [n for n in names if n in self._timers]
-        if not names or writer is None:
+        # every rank takes part in the gather (a collective); only the rank that holds a writer records the result.
+        # The name list must therefore be the same on all ranks: timers a rank never started count as zero.
+        names = list(names)
+        if not names:
             return
         t = self._gather(names, reset, barrier) / normalizer
+        if writer is None:
+            return
         for i, n in enumerate(names):
             writer.add_scalar(n + "-time", float(t[:, i].max()), iteration)

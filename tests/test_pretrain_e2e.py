@@ -190,3 +190,20 @@ def test_optimizer_cpu_offload_program_matches_the_device_optimizer():
     for frac in ("1.0", "0.5"):
         got = _iters(_run_script("pretrain_gpt.py", mock + ["--optimizer-cpu-offload", "--optimizer-offload-fraction", frac]))
         assert all(abs(ref[i][1] - got[i][1]) < 1e-5 for i in (1, 2, 3)), (frac, ref, got)
+
+
+def test_loop_options_on_two_ranks(tmp_path):
+    """Options that add collectives or periodic work to the loop must stay in step on every rank: timers written
+    to tensorboard (a gather), replica hash checks, manual garbage collection, heartbeat sections; --skip-train
+    goes straight to evaluation."""
+    tb = str(tmp_path / "tb")
+    out = _torchrun(2, 29649, ["--global-batch-size", "4", "--manual-gc", "--manual-gc-interval", "1",
+                               "--check-weight-hash-across-dp-replicas-interval", "1", "--enable-ft-package",
+                               "--tensorboard-dir", tb, "--log-timers-to-tensorboard", "--log-world-size-to-tensorboard",
+                               "--log-validation-ppl-to-tensorboard"])
+    assert "PPL" in out and os.listdir(tb)
+    mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29619")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + BASE + ["--skip-train"],
+                       capture_output=True, text=True, timeout=200, cwd=ROOT, env=env)
+    assert r.returncode == 0 and "test loss" in r.stdout and not _iters(r.stdout)
