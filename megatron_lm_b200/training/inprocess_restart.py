@@ -102,7 +102,8 @@ def maybe_wrap_for_inprocess_restart(pretrain_fn: Callable, args=None):
     port = int(os.environ.get("MASTER_PORT", 29500)) + 1
     store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), port, world, is_master=(rank == 0),
                           timeout=timedelta(seconds=300), wait_for_workers=True)
-    wrapper = RestartWrapper(store, rank, world, max_restarts=getattr(args, "inprocess_max_iterations", None) or 3)
+    wrapper = RestartWrapper(store, rank, world, max_restarts=getattr(args, "inprocess_max_iterations", None) or 3,
+                             barrier_timeout=float(getattr(args, "inprocess_barrier_timeout", None) or 120.0))
 
     def wrapped(*a, **kw):
         return wrapper.run(lambda w, attempt: pretrain_fn(*a, inprocess_call_wrapper=w, **kw))

@@ -194,10 +194,51 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
         _TIMERS.log(normalizer=args.log_interval)
 
 
+def _teardown_attempt():
+    """Leave nothing of a failed attempt behind: parallel groups, process-wide globals, microbatch calculator."""
+    try:
+        state.destroy_model_parallel()
+    except Exception:
+        pass
+    from .global_vars import unset_global_variables
+    unset_global_variables()
+
+
+def _maybe_host_fault(args, iteration: int, attempt: int) -> None:
+    """Host-side fault injection for restart tests: ``MLB_INJECT_HOST_FAULT="<rank>:<iteration>"`` makes that rank
+    raise once, in the first attempt, after the given iteration.  Nothing on a GPU is touched."""
+    spec = os.environ.get("MLB_INJECT_HOST_FAULT")
+    if not spec or attempt != 0:
+        return
+    r, it = (int(x) for x in spec.split(":"))
+    if args.rank == r and iteration == it:
+        raise RuntimeError(f"injected host fault on rank {r} after iteration {it}")
+
+
 def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Callable, forward_step_func: Callable,
-             extra_args_provider=None, args_defaults=None, argv=None):
+             extra_args_provider=None, args_defaults=None, argv=None, inprocess_call_wrapper=None):
     """Full program.  ``model_provider(pre_process, post_process, vp_stage=None)`` builds a model chunk;
-    ``forward_step_func(data_iterator, model)`` returns ``(output, loss_func)``."""
+    ``forward_step_func(data_iterator, model)`` returns ``(output, loss_func)``.  With ``--inprocess-restart`` the
+    body runs inside a restart wrapper: a rank-local failure makes every rank abandon the attempt, tear down its
+    groups and start again in the same processes, resuming from the latest checkpoint."""
+    av = list(sys.argv[1:] if argv is None else argv)
+    if inprocess_call_wrapper is None and "--inprocess-restart" in av:
+        from types import SimpleNamespace
+        from .inprocess_restart import maybe_wrap_for_inprocess_restart
+        def opt(flag, cast, default):
+            return cast(av[av.index(flag) + 1]) if flag in av and av.index(flag) + 1 < len(av) else default
+        ns = SimpleNamespace(inprocess_restart=True, inprocess_max_iterations=opt("--inprocess-max-iterations", int, None),
+                             inprocess_barrier_timeout=opt("--inprocess-barrier-timeout", float, 120.0))
+        wrapped, _store = maybe_wrap_for_inprocess_restart(
+            lambda **kw: pretrain(train_valid_test_datasets_provider, model_provider, forward_step_func,
+                                  extra_args_provider, args_defaults, argv, **kw), ns)
+        return wrapped()
+    attempt = 0
+    if inprocess_call_wrapper is not None:
+        inprocess_call_wrapper.finalize = _teardown_attempt
+        attempt = inprocess_call_wrapper.attempt
+        if attempt:
+            print(f"[rank {os.environ.get('RANK', 0)}] in-process restart: attempt {attempt}", flush=True)
     args = initialize_megatron(extra_args_provider, args_defaults, argv=argv)
     timers = get_timers()
     config = core_transformer_config_from_args(args)
@@ -281,6 +322,9 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             rerun_state_machine=rerun)
         iteration += 1
         args.iteration = iteration
+        _maybe_host_fault(args, iteration, attempt)
+        if inprocess_call_wrapper is not None:
+            inprocess_call_wrapper.check()               # a peer failed: abandon this attempt between steps
         args.consumed_train_samples += args.global_batch_size
         flops_so_far += flops_from_config(config, args.global_batch_size, args.seq_length, args.padded_vocab_size or 0)
         if iteration % args.log_interval == 0:

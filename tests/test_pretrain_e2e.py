@@ -207,3 +207,25 @@ def test_loop_options_on_two_ranks(tmp_path):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + BASE + ["--skip-train"],
                        capture_output=True, text=True, timeout=200, cwd=ROOT, env=env)
     assert r.returncode == 0 and "test loss" in r.stdout and not _iters(r.stdout)
+
+
+def test_inprocess_restart_after_a_host_side_fault(tmp_path):
+    """Rank 1 raises on the host after iteration 3 (first attempt only).  Both ranks abandon the attempt, tear
+    their groups down, meet at the store barrier and run again in the same processes, resuming from the latest
+    checkpoint; the job still reaches the last iteration and exits 0.  No GPU is involved in the fault."""
+    ck = str(tmp_path / "ck")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MLB_INJECT_HOST_FAULT="1:3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29650", os.path.join(ROOT, "pretrain_gpt.py"), "--distributed-backend", "gloo",
+           "--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
+           "--max-position-embeddings", "32", "--micro-batch-size", "1", "--global-batch-size", "4", "--train-iters", "5",
+           "--lr", "1e-3", "--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--log-interval", "1",
+           "--eval-interval", "100", "--eval-iters", "0", "--use-cpu-initialization", "--save", ck, "--load", ck,
+           "--save-interval", "1", "--inprocess-restart", "--distributed-timeout-minutes", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=400, cwd=ROOT, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-3000:]
+    assert "injected host fault on rank 1 after iteration 3" in out
+    assert "[rank 0] in-process restart: attempt 1" in out and "[rank 1] in-process restart: attempt 1" in out
+    seen = [int(m.group(1)) for m in re.finditer(r"^ iteration\s+(\d+)/", out, flags=re.M)]
+    assert seen[:2] == [1, 2] and seen[-1] == 5 and seen.count(4) == 1
