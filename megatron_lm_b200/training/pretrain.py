@@ -51,7 +51,8 @@ def get_timers() -> Timers:
     return _TIMERS
 
 
-def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unknown_args=False, argv=None):
+def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unknown_args=False, argv=None,
+                        store=None):
     """Parse arguments, start torch.distributed, build the parallel groups, seed the RNG streams."""
     global _TIMERS, _WRITER
     args = parse_args(extra_args_provider, ignore_unknown_args, argv)
@@ -70,6 +71,8 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
                   timeout=timedelta(minutes=args.distributed_timeout_minutes))
         if use_cuda:
             kw["device_id"] = torch.device("cuda", args.local_rank)
+        if store is not None:
+            kw["store"] = store          # a rendezvous store of the caller's (fresh key space per restart attempt)
         dist.init_process_group(**kw)
     state.initialize_model_parallel(
         tensor_model_parallel_size=args.tensor_model_parallel_size,
@@ -239,7 +242,11 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         attempt = inprocess_call_wrapper.attempt
         if attempt:
             print(f"[rank {os.environ.get('RANK', 0)}] in-process restart: attempt {attempt}", flush=True)
-    args = initialize_megatron(extra_args_provider, args_defaults, argv=argv)
+    pg_store = None
+    if inprocess_call_wrapper is not None:
+        # each attempt rendezvouses under its own prefix: keys of a torn-down attempt cannot be picked up again
+        pg_store = dist.PrefixStore(f"pg_attempt_{attempt}", inprocess_call_wrapper.store)
+    args = initialize_megatron(extra_args_provider, args_defaults, argv=argv, store=pg_store)
     timers = get_timers()
     config = core_transformer_config_from_args(args)
     ocfg, dcfg = optimizer_config_from_args(args), ddp_config_from_args(args)
