@@ -73,6 +73,8 @@ class RestartWrapper:
                     raise
                 if not isinstance(e, RestartSignal):
                     last_error = traceback.format_exc()
+                    print(f"[rank {self.rank}] attempt {self.attempt} failed; asking every rank to restart\n"
+                          f"{last_error}", flush=True)
                     try:
                         self.store.add(self._key("failed"), 1)
                     except Exception:
