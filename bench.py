@@ -134,15 +134,20 @@ def run_ours(args):
 
     rank, world, local = dist_env()
     assert world == args.gpus, f"launched with {world} ranks for --gpus {args.gpus}"
-    if os.environ.get("MLB_BENCH_STACK_DUMP_S"):      # debug aid: print every thread's Python stack after N seconds
+    # diagnosis aid: if a multi-GPU run is still going after this many seconds, every thread's Python stack goes
+    # to stderr (stdout keeps the single JSON line); MLB_BENCH_STACK_DUMP_S overrides, 0 turns it off
+    dump_s = int(os.environ.get("MLB_BENCH_STACK_DUMP_S", "420" if world > 1 else "0"))
+    if dump_s > 0:
         import faulthandler
-        faulthandler.dump_traceback_later(int(os.environ["MLB_BENCH_STACK_DUMP_S"]), exit=False)
+        faulthandler.dump_traceback_later(dump_s, exit=False)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from datetime import timedelta
+        # a stuck collective ends with an error after ten minutes instead of holding the GPUs for the default thirty
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(minutes=10))
     tp, pp, vpp, ep = layout_for(args.gpus, args.config)
     if args.layout:                                   # debug only: "tp,pp,vpp" (vpp 0 = none)
         tp, pp, vpp = (int(x) for x in args.layout.split(","))
