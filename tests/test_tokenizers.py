@@ -64,3 +64,21 @@ def test_factory_pads_the_vocabulary(tmp_path):
     with pytest.raises(Exception):
         build_tokenizer(SimpleNamespace(tokenizer_type="NoSuchTokenizer", rank=0, make_vocab_size_divisible_by=128,
                                         tensor_model_parallel_size=1))
+
+
+def test_huggingface_tokenizer_from_a_local_directory(tmp_path):
+    tokenizers = pytest.importorskip("tokenizers")
+    transformers = pytest.importorskip("transformers")
+    from megatron_lm_b200.data.tokenizer import HuggingFaceTokenizer
+    vocab = {w: i for i, w in enumerate(["<unk>", "<s>", "</s>", "<pad>", "hello", "world", "again"])}
+    tk = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="<unk>"))
+    tk.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tk, unk_token="<unk>", bos_token="<s>",
+                                                eos_token="</s>", pad_token="<pad>")
+    d = tmp_path / "hf_tok"
+    fast.save_pretrained(str(d))
+    t = HuggingFaceTokenizer(str(d))
+    ids = t.tokenize("hello world again hello")
+    assert ids == [4, 5, 6, 4] and t.detokenize(ids) == "hello world again hello"
+    assert (t.bos, t.eos, t.pad, t.eod) == (1, 2, 3, 2) and t.vocab_size == 7
+    assert t.tokenize("unknownword") == [0]
