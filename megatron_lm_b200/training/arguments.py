@@ -71,6 +71,8 @@ def build_parser(extra_args_provider: Optional[Callable] = None) -> argparse.Arg
     g.add_argument("--ec-data-shards", type=int, default=None, help="k: data members per stripe (default group size - m)")
     g.add_argument("--ec-parity-shards", type=int, default=1, help="m: parity members per stripe (losses tolerated)")
     g.add_argument("--ec-chunk-bytes", type=int, default=1 << 20)
+    g.add_argument("--ec-device", default="auto", choices=["auto", "gpu", "cpu"],
+                   help="where parity is computed and held: peer GPUs' memory (auto on NCCL jobs) or host memory")
     g = parser.add_argument_group(title="peer-memory kernels")
     g.add_argument("--peer-memory-collectives", action="store_true",
                    help="distributed optimizer: gradient reduce-scatter as a pull kernel over NVLink peer memory and "

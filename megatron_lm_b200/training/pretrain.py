@@ -273,7 +273,19 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     ec_manager = None
     if getattr(args, "non_persistent_ckpt_type", None) == "local":
         grp = state.get_data_parallel_group(with_context_parallel=True)
-        ec_manager = ECCheckpointManager(grp, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes)
+        on_gpu = torch.cuda.is_available() and dist.get_backend(grp) == "nccl" and dist.get_world_size(grp) > 1
+        if on_gpu and getattr(args, "ec_device", "auto") != "cpu":
+            # parity computed by the peer-memory GF(2^8) kernel, parity held in the peers' HBM, host tier on a
+            # side stream; the state size fixes the stripe plan
+            from ..checkpoint.ec_gpu import GpuECCheckpoint
+            tensors = list(optimizer.local_state_tensors())
+            for chunk in model:
+                for buf in getattr(chunk, "buffers", []) + getattr(chunk, "expert_buffers", []):
+                    tensors.append(buf.param_data)
+            nbytes = sum(t.numel() * t.element_size() for t in tensors)
+            ec_manager = GpuECCheckpoint(grp, nbytes, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes)
+        else:
+            ec_manager = ECCheckpointManager(grp, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes)
     timers("train/valid/test-data-iterators-setup", 0).start(barrier=True)
     train_it, valid_it, test_it = build_train_valid_test_data_iterators(train_valid_test_datasets_provider, args)
     timers("train/valid/test-data-iterators-setup").stop()
@@ -384,8 +396,13 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
                 iteration % args.non_persistent_save_interval == 0:
             st = checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args, non_persistent=True,
                                                ec_manager=ec_manager)
-            print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: "
-                         f"{st.get('encode_GBps', 0.0):.2f} GB/s encode, {st.get('total_s', 0.0):.3f} s")
+            if "encode_ms" in st:        # GPU tier: device-timed snapshot and parity kernels
+                print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: snapshot "
+                             f"{st.get('snapshot_ms', 0.0):.2f} ms, encode {st['encode_ms']:.2f} ms, "
+                             f"{st.get('total_s', 0.0):.3f} s in all")
+            else:
+                print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: "
+                             f"{st.get('encode_GBps', 0.0):.2f} GB/s encode, {st.get('total_s', 0.0):.3f} s")
         exiting = False
         if sig is not None and any(sig.signals_received()):
             exiting = True
