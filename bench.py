@@ -259,7 +259,12 @@ def run_ours(args):
     for k in range(args.steps):
         b = host_batches[args.warmup + args.steps + k].to(dev, non_blocking=True)
         losses, *_ = one_step(b)
-        if losses:
+        if pp > 1:
+            # only the last pipeline stage holds the loss: every rank receives it, then reads it on the host
+            lt = losses["lm loss"].detach().float().reshape(1) if losses else torch.zeros(1, device=dev)
+            dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+            loss_val = float(lt.item())
+        elif losses:
             loss_val = float(losses["lm loss"].item())
         else:
             torch.cuda.current_stream().synchronize()
