@@ -54,7 +54,10 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
             gated_linear_unit=True, activation_func=torch.nn.functional.silu, add_bias_linear=False,
             hidden_dropout=0.0, attention_dropout=0.0, bf16=True, params_dtype=torch.bfloat16,
             pipeline_dtype=torch.bfloat16, tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
-            virtual_pipeline_model_parallel_size=vpp, sequence_parallel=tp > 1, init_method_std=0.02,
+            virtual_pipeline_model_parallel_size=vpp, sequence_parallel=False, init_method_std=0.02,
+            # sequence parallelism is off: the library's local layer spec builds torch norms, which assert
+            # against it (it needs Transformer Engine or Apex norms, neither installable offline), so its
+            # tensor-parallel runs use plain TP all-reduces - its own stock path for this spec
             # without a fused attention kernel the library keeps [b, np, s, s] scores per layer;
             # selective recompute of core attention is its own stock answer to that
             recompute_granularity="selective", gradient_accumulation_fusion=False, masked_softmax_fusion=False,
@@ -168,7 +171,7 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e = tokens_per_step * args.steps / (e2e_ms / 1e3)
     if rank == 0:
-        par = f"tp{tp}pp{pp}" + (f"vpp{vpp}" if vpp else "") + f"dp{dp}" + ("-sp" if tp > 1 else "")
+        par = f"tp{tp}pp{pp}" + (f"vpp{vpp}" if vpp else "") + f"dp{dp}" + ("-nosp (the local layer spec has no sequence-parallel norm)" if tp > 1 else "")
         print(json.dumps({
             "metric": "tokens/sec (whole job) Llama-7B pre-training step", "value": value, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
