@@ -42,6 +42,20 @@ class RestartWrapper:
         if self.store.num_keys() and self._failed():
             raise RestartSignal(f"another rank failed in attempt {self.attempt}")
 
+    def step_barrier(self, step: int, poll_s: float = 0.002) -> None:
+        """Between steps: wait until every rank has finished ``step`` or some rank has failed.  Unlike ``check``
+        this cannot miss a failure that is published a moment later - the failed rank never arrives, so the
+        healthy ranks are still here when its flag appears - at the price of one store round trip per step."""
+        key = self._key(f"step{step}")
+        self.store.add(key, 1)
+        t0 = time.time()
+        while int(self.store.add(key, 0)) < self.world:
+            if self._failed():
+                raise RestartSignal(f"another rank failed in attempt {self.attempt} (seen at step {step})")
+            if time.time() - t0 > self.barrier_timeout:
+                raise TimeoutError(f"rank {self.rank}: step barrier {step} of attempt {self.attempt} timed out")
+            time.sleep(poll_s)
+
     def _failed(self) -> bool:
         try:
             return int(self.store.add(self._key("failed"), 0)) > 0

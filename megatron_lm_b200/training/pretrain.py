@@ -343,7 +343,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         args.iteration = iteration
         _maybe_host_fault(args, iteration, attempt)
         if inprocess_call_wrapper is not None:
-            inprocess_call_wrapper.check()               # a peer failed: abandon this attempt between steps
+            inprocess_call_wrapper.step_barrier(iteration)   # a peer failed: abandon this attempt between steps
         args.consumed_train_samples += args.global_batch_size
         flops_so_far += flops_from_config(config, args.global_batch_size, args.seq_length, args.padded_vocab_size or 0)
         if iteration % args.log_interval == 0:

@@ -221,7 +221,7 @@ def test_inprocess_restart_after_a_host_side_fault(tmp_path):
            "--max-position-embeddings", "32", "--micro-batch-size", "1", "--global-batch-size", "4", "--train-iters", "5",
            "--lr", "1e-3", "--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--log-interval", "1",
            "--eval-interval", "100", "--eval-iters", "0", "--use-cpu-initialization", "--save", ck, "--load", ck,
-           "--save-interval", "1", "--inprocess-restart", "--distributed-timeout-minutes", "1"]
+           "--save-interval", "1", "--inprocess-restart"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=400, cwd=ROOT, env=env)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-3000:]
