@@ -229,3 +229,26 @@ def test_inprocess_restart_after_a_host_side_fault(tmp_path):
     assert "[rank 0] in-process restart: attempt 1" in out and "[rank 1] in-process restart: attempt 1" in out
     seen = [int(m.group(1)) for m in re.finditer(r"^ iteration\s+(\d+)/", out, flags=re.M)]
     assert seen[:2] == [1, 2] and seen[-1] == 5 and seen.count(4) == 1
+
+
+def test_retro_program_builds_its_retrieval_data_and_trains(tmp_path):
+    import numpy as np
+    from megatron_lm_b200.data.indexed_dataset import IndexedDatasetBuilder, get_bin_path, get_idx_path
+    prefix = str(tmp_path / "corpus")
+    b = IndexedDatasetBuilder(get_bin_path(prefix), dtype=np.int32)
+    rng = np.random.RandomState(0)
+    for d in range(24):
+        lo = 5 + 4 * (d // 2)
+        b.add_item(rng.randint(lo, lo + 8, size=rng.randint(60, 100)).tolist())
+        b.end_document()
+    b.finalize(get_idx_path(prefix))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29620")
+    cmd = [sys.executable, os.path.join(ROOT, "pretrain_retro.py"), "--num-layers", "6", "--hidden-size", "32",
+           "--num-attention-heads", "4", "--seq-length", "32", "--max-position-embeddings", "64", "--micro-batch-size", "2",
+           "--global-batch-size", "4", "--train-iters", "3", "--lr", "1e-3", "--data-path", prefix, "--split", "90,5,5",
+           "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--log-interval", "1", "--eval-interval", "2",
+           "--eval-iters", "1", "--use-cpu-initialization", "--retro-chunk-length", "8"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0, out[-2500:]
+    assert sorted(_iters(out)) == [1, 2, 3] and "validation loss at iteration 2" in out and "test loss" in out
