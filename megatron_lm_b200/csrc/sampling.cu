@@ -93,11 +93,26 @@ sample_kernel(const T* __restrict__ logits, const float* __restrict__ uniform, l
       const unsigned prefix = sh_prefix;
       if (tid < 256) hist[tid] = 0.f;
       __syncthreads();
-      for (int i = tid; i < V; i += kSampleThreads) {
-        const float x = to_f(row[i]) * inv_temp;
-        const unsigned k = order_key(x);
-        if ((k & mask) == prefix)
-          atomicAdd(&hist[(k >> shift) & 255u], by_count ? 1.f : __expf(x - m) * inv_z);
+      // Logits of one row crowd into a few buckets (in the first pass: the same sign and exponent), so lanes of a
+      // warp mostly hit one address.  Lanes that share a bucket are combined first: counts by a peer mask, masses
+      // by a warp sum when the whole warp agrees; only the rest falls back to one atomic per lane.
+      const int v_round = (V + kSampleThreads - 1) / kSampleThreads * kSampleThreads;
+      for (int i = tid; i < v_round; i += kSampleThreads) {
+        float x = 0.f; unsigned k = 0u; bool in = false;
+        if (i < V) { x = to_f(row[i]) * inv_temp; k = order_key(x); in = (k & mask) == prefix; }
+        const unsigned bucket = in ? ((k >> shift) & 255u) : 256u;          // 256: not a candidate
+        const unsigned peers = __match_any_sync(0xffffffffu, bucket);
+        if (by_count) {
+          if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[bucket], (float)__popc(peers));
+        } else {
+          const float w = in ? __expf(x - m) * inv_z : 0.f;
+          if (peers == 0xffffffffu) {                                        // warp-uniform bucket
+            const float sum = warp_sum(w);
+            if (in && lane == 0) atomicAdd(&hist[bucket], sum);
+          } else if (in) {
+            atomicAdd(&hist[bucket], w);
+          }
+        }
       }
       __syncthreads();
       if (tid == 0) {
