@@ -195,6 +195,7 @@ gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const
                          long long zs, float eps) {
   __shared__ float gsum[kGnMaxGroups];
   const int gs = C / G;
+  const bool warp_groups = (gs % 256) == 0;          // every warp's channel span stays inside one group
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     if (threadIdx.x < G) gsum[threadIdx.x] = 0.f;
     __syncthreads();
@@ -202,6 +203,7 @@ gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const
 #pragma unroll
     for (int it = 0; it < kGnMaxIt; ++it) {
       const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+      float part = 0.f;
       if (c < C) {
         float a[8], b[8];
         load8(y + (size_t)r * ys + c, a);
@@ -209,7 +211,13 @@ gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const
         float ss = 0.f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) { u[it][k] = a[k] * b[k] * sigmoidf_(b[k]); ss += u[it][k] * u[it][k]; }
-        atomicAdd(&gsum[c / gs], ss);
+        if (!warp_groups) atomicAdd(&gsum[c / gs], ss);
+        part = ss;
+      }
+      if (warp_groups) {
+        // a warp's 256 consecutive channels lie in one group: one shared-memory atomic per warp instead of 32
+        const float tot = warp_sum(part);
+        if ((threadIdx.x & 31) == 0 && c < C) atomicAdd(&gsum[c / gs], tot);
       }
     }
     __syncthreads();
@@ -238,6 +246,7 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
                          long long zs, long long dys, long long dzs) {
   __shared__ float gdot[kGnMaxGroups];
   const int gs = C / G;
+  const bool warp_groups = (gs % 256) == 0;
   float wacc[kGnMaxIt][8];
 #pragma unroll
   for (int it = 0; it < kGnMaxIt; ++it)
@@ -250,6 +259,7 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
 #pragma unroll
     for (int it = 0; it < kGnMaxIt; ++it) {
       const int c = threadIdx.x * 8 + it * kGnThreads * 8;
+      float part = 0.f;
       if (c < C) {
         float a[8], b[8], g[8], wv[8];
         load8(y + (size_t)r * ys + c, a);
@@ -264,7 +274,12 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
           dot += g[k] * wv[k] * n;
           wacc[it][k] += g[k] * n;
         }
-        atomicAdd(&gdot[c / gs], dot);
+        if (!warp_groups) atomicAdd(&gdot[c / gs], dot);
+        part = dot;
+      }
+      if (warp_groups) {
+        const float tot = warp_sum(part);
+        if ((threadIdx.x & 31) == 0 && c < C) atomicAdd(&gdot[c / gs], tot);
       }
     }
     __syncthreads();
