@@ -37,6 +37,10 @@ router_fwd_kernel(const RouterFwdArgs a) {
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float zacc = 0.f;
+  // a lane owns the same experts for every token of its warp: their statistics stay in registers until the end
+  float sacc[VPT]; int cacc[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) { sacc[j] = 0.f; cacc[j] = 0; }
   for (int t = blockIdx.x * kRouterWarps + warp; t < a.T; t += gridDim.x * kRouterWarps) {
     const float* row = a.logits + (size_t)t * a.E;
     float l[VPT], s[VPT], v[VPT];
@@ -103,11 +107,19 @@ router_fwd_kernel(const RouterFwdArgs a) {
         else if (a.mode == ROUTER_SOFTMAX_PRE) p = s[j];
         else p = a.topk > 1 ? s[j] / denom : s[j];
         p *= a.scale;
-        atomicAdd(&sh_cnt[e], 1);
+        cacc[j] += 1;
       }
       prow[e] = p;
       mrow[e] = c ? 1 : 0;
-      atomicAdd(&sh_score[e], s[j]);
+      sacc[j] += s[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int e = lane + 32 * j;
+    if (e < a.E) {
+      if (cacc[j]) atomicAdd(&sh_cnt[e], cacc[j]);
+      atomicAdd(&sh_score[e], sacc[j]);
     }
   }
   __syncthreads();
