@@ -109,8 +109,16 @@ sample_kernel(const T* __restrict__ logits, const float* __restrict__ uniform, l
           if (peers == 0xffffffffu) {                                        // warp-uniform bucket
             const float sum = warp_sum(w);
             if (in && lane == 0) atomicAdd(&hist[bucket], sum);
-          } else if (in) {
-            atomicAdd(&hist[bucket], w);
+          } else {
+            // mixed buckets in the warp: every lane adds up the weights of the lanes that share its bucket (all
+            // lanes run the same 32 shuffles), and the lowest lane of each group issues the one atomic
+            float sum = 0.f;
+#pragma unroll
+            for (int src = 0; src < 32; ++src) {
+              const float ws = __shfl_sync(0xffffffffu, w, src);
+              if ((peers >> src) & 1u) sum += ws;
+            }
+            if (in && lane == __ffs(peers) - 1) atomicAdd(&hist[bucket], sum);
           }
         }
       }
