@@ -330,15 +330,33 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         torch.cuda.memory._record_memory_history(max_entries=100000)
     if getattr(args, "skip_train", False):
         iteration = max(iteration, args.train_iters)
+    prof = None
+    if getattr(args, "profile", False) and getattr(args, "use_pytorch_profiler", False) and \
+            args.rank in (args.profile_ranks or [0]):
+        # the torch profiler instead of an external one: idle until the start step, one warm-up step, active to
+        # the end step; traces land beside the tensorboard logs (reference: training.py:2219-2236)
+        start = max(args.profile_step_start - iteration, 0)
+        prof = torch.profiler.profile(
+            schedule=torch.profiler.schedule(wait=max(start - 1, 0), warmup=1 if start > 0 else 0,
+                                             active=max(args.profile_step_end - args.profile_step_start, 1), repeat=1),
+            on_trace_ready=torch.profiler.tensorboard_trace_handler(getattr(args, "tensorboard_dir", None) or "profile"),
+            record_shapes=True, with_stack=True)
+        prof.start()
+    from ..utils.common import configure_nvtx_profiling, nvtx_range_pop, nvtx_range_push
+    configure_nvtx_profiling(bool(getattr(args, "profile", False)))
     while iteration < args.train_iters:
         checkpointing.maybe_finalize_async_save(blocking=False)
         if getattr(args, "profile", False) and iteration == args.profile_step_start and torch.cuda.is_available() \
-                and args.rank in (args.profile_ranks or [0]):
+                and args.rank in (args.profile_ranks or [0]) and prof is None:
             torch.cuda.cudart().cudaProfilerStart()
+        nvtx_range_push(f"iteration {iteration + 1}")
         loss_dict, skipped, grad_norm, zeros = train_step(
             forward_step_func, its, model, optimizer, scheduler, config, num_microbatches=nmb,
             seq_length=args.seq_length, micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size,
             rerun_state_machine=rerun)
+        nvtx_range_pop(f"iteration {iteration + 1}")
+        if prof is not None:
+            prof.step()
         iteration += 1
         args.iteration = iteration
         _maybe_host_fault(args, iteration, attempt)
@@ -427,6 +445,8 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         res = evaluate(forward_step_func, test_it, model, config, eval_iters=args.eval_iters, num_microbatches=nmb,
                        seq_length=args.seq_length, micro_batch_size=args.micro_batch_size)
         print_rank_last(" test loss | " + " | ".join(f"{k} value: {v:.6E}" for k, v in res.items()))
+    if prof is not None:
+        prof.stop()
     if heart is not None:
         heart.end_section()
         heart.calculate_and_persist_timeouts()

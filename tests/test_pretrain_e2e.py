@@ -252,3 +252,14 @@ def test_retro_program_builds_its_retrieval_data_and_trains(tmp_path):
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-2500:]
     assert sorted(_iters(out)) == [1, 2, 3] and "validation loss at iteration 2" in out and "test loss" in out
+
+
+def test_pytorch_profiler_window_writes_a_trace(tmp_path):
+    tb = str(tmp_path / "tb")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29621")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + BASE +
+                       ["--train-iters", "5", "--profile", "--use-pytorch-profiler", "--profile-step-start", "2",
+                        "--profile-step-end", "4", "--tensorboard-dir", tb], capture_output=True, text=True, timeout=300,
+                       cwd=ROOT, env=env)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-2000:]
+    assert any(f.endswith(".pt.trace.json") for f in os.listdir(tb))
