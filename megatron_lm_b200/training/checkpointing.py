@@ -75,6 +75,7 @@ def get_rng_state() -> Dict[str, Any]:
 
 
 LAST_LOADED_RNG_STATE: Optional[Dict[str, Any]] = None     # what the latest load_checkpoint restored, if anything
+LAST_LOADED_RERUN_STATE: Optional[Dict[str, Any]] = None   # state of the result-validation machine in that checkpoint
 
 
 def set_rng_state(st: Dict[str, Any]) -> None:
@@ -162,7 +163,12 @@ def generate_state_dict(args, model, optimizer, opt_param_scheduler, rng_state, 
         if opt_param_scheduler is not None:
             sd["opt_param_scheduler"] = opt_param_scheduler.state_dict()
     if rerun_state is not None:
-        sd["rerun_state_machine"] = rerun_state
+        # every rank keeps its own first result of the step under replay
+        if sharded and dist.is_initialized():
+            sd["rerun_state_machine"] = ds.ShardedObject("rerun_state_machine", rerun_state, (dist.get_world_size(),),
+                                                         (dist.get_rank(),))
+        else:
+            sd["rerun_state_machine"] = rerun_state
     if rng_state is not None and not getattr(args, "no_save_rng", False):
         if sharded:
             c = _coords()
@@ -377,9 +383,12 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Op
             dp = state.get_data_parallel_world_size(with_context_parallel=True) if state.model_parallel_is_initialized() else 1
             req["rng_state"] = ds.ShardedObject("rng_state", None, (c["pp_size"], c["tp_size"], dp),
                                                 (c["pp_rank"], c["tp_rank"], c["dp_rank"]))
+        if dist.is_initialized():
+            req["rerun_state_machine"] = ds.ShardedObject("rerun_state_machine", None, (dist.get_world_size(),),
+                                                          (dist.get_rank(),))
         # RNG states are per (pp, tp, dp) position: under a different layout there is nothing to restore
         loaded = ds.load(req, base, strict=strict and not getattr(args, "dist_ckpt_strictness", "") == "ignore_all",
-                         optional_objects=("rng_state",))
+                         optional_objects=("rng_state", "rerun_state_machine"))
         for i, chunk in enumerate(model):
             ds.load_model_from_sharded(_unwrap(chunk), loaded["model" if len(model) == 1 else f"model{i}"])
         if optimizer is not None and not no_optim and "optimizer" in loaded:
@@ -417,4 +426,6 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Op
             set_rng_state(sd["rng_state"])
     if finetune or release:
         return 0, 0.0
+    global LAST_LOADED_RERUN_STATE
+    LAST_LOADED_RERUN_STATE = sd.get("rerun_state_machine")
     return int(sd.get("iteration", iteration)), float(sd.get("num_floating_point_operations_so_far", 0.0))

@@ -294,8 +294,12 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         # generator states back so that a resumed run continues exactly like the uninterrupted one
         checkpointing.set_rng_state(checkpointing.LAST_LOADED_RNG_STATE)
     timers.log(["model-and-optimizer-setup", "train/valid/test-data-iterators-setup"], barrier=True)
-    rerun = RerunStateMachine(mode=getattr(args, "rerun_mode", "disabled")) if getattr(args, "rerun_mode", "disabled") \
-        != "disabled" else None
+    # always present (disabled when --rerun-mode says so): loss functions validate their result through it
+    from .resilience import RerunErrorInjector, set_rerun_state_machine
+    inj = RerunErrorInjector(getattr(args, "error_injection_rate", 0) or 0,
+                             getattr(args, "error_injection_type", None) or "transient_error")
+    rerun = RerunStateMachine(mode=getattr(args, "rerun_mode", None) or "disabled", error_injector=inj)
+    set_rerun_state_machine(rerun)
     sig = DistributedSignalHandler().__enter__() if getattr(args, "exit_signal_handler", False) else None
     straggler = StragglerDetector() if getattr(args, "log_straggler", False) else None
     dp = state.get_data_parallel_world_size()
@@ -305,6 +309,12 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     for m in model:
         m.train()
     t_last = time.time()
+    if rerun.mode.value != "disabled" and train_it is not None:
+        from .resilience import RerunDataIterator
+        train_it = RerunDataIterator(train_it)            # a replayed step sees the same batches again
+    if args.load is not None and checkpointing.LAST_LOADED_RERUN_STATE is not None and rerun.mode.value != "disabled":
+        rerun.load_state_dict(checkpointing.LAST_LOADED_RERUN_STATE)
+    reported = 0
     its = [train_it] * len(model) if len(model) > 1 else train_it
     if getattr(args, "manual_gc", False):
         import gc
@@ -355,6 +365,25 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             seq_length=args.seq_length, micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size,
             rerun_state_machine=rerun)
         nvtx_range_pop(f"iteration {iteration + 1}")
+        for step_no, diag, what in rerun.diagnostics[reported:]:
+            print(f" [rank {args.rank}] result validation, iteration {iteration + 1}: {diag.value} ({what})", flush=True)
+        reported = len(rerun.diagnostics)
+        stop, code = rerun.should_checkpoint_and_exit()
+        if stop:
+            # the step reproduced a rejected result here: keep the state from before the step, so that a restart
+            # (on other hardware) replays it and tells a faulty device from a real divergence
+            if args.save:
+                checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args,
+                                              num_floating_point_operations_so_far=flops_so_far,
+                                              rerun_state=rerun.state_dict())
+            checkpointing.maybe_finalize_async_save(blocking=True)
+            print_rank_0(f"exiting at iteration {iteration} with code {code} to replay the step from the checkpoint")
+            if dist.is_initialized():
+                dist.barrier()
+            sys.exit(code or 0)
+        if rerun.exit_code is not None:
+            print_rank_0(f"result validation failed again after the restart: exiting with code {rerun.exit_code}")
+            sys.exit(rerun.exit_code)
         if prof is not None:
             prof.step()
         iteration += 1

@@ -117,7 +117,7 @@ class RerunErrorInjector:
 class RerunStateMachine:
     def __init__(self, mode: str = "validate_results", error_injector: Optional[RerunErrorInjector] = None,
                  cpu_group=None, state_save_func: Optional[Callable] = None, state_restore_func: Optional[Callable] = None):
-        self.mode = RerunMode(mode)
+        self.mode = RerunMode({"report_stats": "report_determinism_stats"}.get(mode, mode))
         self.state = RerunState.NOT_RUNNING_YET
         self.injector = error_injector or RerunErrorInjector()
         self.cpu_group = cpu_group
@@ -132,6 +132,11 @@ class RerunStateMachine:
         self.saved_rng = None
         self.stats: Dict[str, List[float]] = {}
         self._resume_pending = False
+        self._spike_stats: Dict[str, "QuickStats"] = {}
+        # a step validates once per microbatch: calls are told apart by their position within the pass
+        self._call_idx = 0
+        self._first_results: Dict[int, float] = {}
+        self._suspect_idx: Optional[int] = None
 
     # -- consensus ------------------------------------------------------------
     def _any(self, flag: bool) -> bool:
@@ -150,6 +155,7 @@ class RerunStateMachine:
         """Call in ``while machine.should_run_forward_backward(it): fwd_bwd()``."""
         its = data_iterator if isinstance(data_iterator, (list, tuple)) else [data_iterator]
         its = [i for i in its if isinstance(i, RerunDataIterator)]
+        self._call_idx = 0
         if self.mode == RerunMode.DISABLED:
             if self.state == RerunState.NOT_RUNNING_YET:
                 self.state = RerunState.INITIAL_RUN
@@ -159,7 +165,7 @@ class RerunStateMachine:
         if self.state == RerunState.NOT_RUNNING_YET:
             self.state = RerunState.INITIAL_RUN
             self.rerun_requested = False
-            self.saved_rng = (torch.get_rng_state(), torch.cuda.get_rng_state() if torch.cuda.is_available() else None)
+            self.saved_rng = self._rng_snapshot()
             if self.save_fn:
                 self.save_fn()
             for i in its:
@@ -182,16 +188,32 @@ class RerunStateMachine:
             if self._resume_pending:
                 # first call after a resume: replay the saved step (on possibly different hardware)
                 self._resume_pending = False
+                if self.saved_rng is not None:
+                    self._rng_apply(self.saved_rng)      # the generators as they were when the step first ran
                 for i in its:
                     i.rewind()
                 return True
             return self._finish(its)
         return self._finish(its)
 
+    @staticmethod
+    def _rng_snapshot():
+        """Default CPU / CUDA generators and the named model-parallel generators at the start of a step."""
+        from ..parallel.random import get_cuda_rng_tracker
+        return (torch.get_rng_state(), torch.cuda.get_rng_state() if torch.cuda.is_available() else None,
+                get_cuda_rng_tracker().get_states())
+
+    @staticmethod
+    def _rng_apply(snap):
+        from ..parallel.random import get_cuda_rng_tracker
+        torch.set_rng_state(snap[0])
+        if snap[1] is not None and torch.cuda.is_available():
+            torch.cuda.set_rng_state(snap[1])
+        if len(snap) > 2 and snap[2]:
+            get_cuda_rng_tracker().set_states(snap[2])
+
     def _restore(self, its):
-        torch.set_rng_state(self.saved_rng[0])
-        if self.saved_rng[1] is not None:
-            torch.cuda.set_rng_state(self.saved_rng[1])
+        self._rng_apply(self.saved_rng)
         if self.restore_fn:
             self.restore_fn()
         for i in its:
@@ -211,22 +233,36 @@ class RerunStateMachine:
                         tolerance: float = 0.0, fatal: bool = True) -> None:
         """Call from the loss function with the value to check (e.g. the loss)."""
         if self.mode == RerunMode.DISABLED:
+            # no replay machinery, but a rejected result is still an error (reference: rerun_state_machine.py:470)
+            if fatal and rejection_func(result if torch.is_tensor(result) else torch.tensor(float(result))):
+                raise RuntimeError(f"result validation failed: {message} (value {float(result)})")
             return
         val = float(result.item()) if torch.is_tensor(result) else float(result)
+        idx = self._call_idx
+        self._call_idx += 1
         rerun = self.state != RerunState.INITIAL_RUN
-        if self.injector.maybe_inject(self.step, rerun):
+        injected = self.injector.maybe_inject(self.step, rerun)
+        if injected:
             val = self.injector.corrupt(val)
         if self.state == RerunState.INITIAL_RUN:
-            self.first_result = val
-            if self.mode == RerunMode.VALIDATE_RESULTS and rejection_func(torch.tensor(val)):
+            if idx == 0:
+                self._first_results, self._suspect_idx = {}, None
+            self._first_results[idx] = val
+            if not self.rerun_requested:
+                self.first_result = val
+            # an injected fault counts as rejected whatever the test is: it exercises the replay path
+            if (self.mode == RerunMode.VALIDATE_RESULTS and not self.rerun_requested
+                    and (injected or rejection_func(torch.tensor(val)))):
                 self.rerun_requested = True
+                self._suspect_idx = idx
                 self.suspicious_device = f"rank {dist.get_rank() if dist.is_initialized() else 0}"
         elif self.state == RerunState.RERUNNING_IN_PLACE:
             if self.mode == RerunMode.REPORT_DETERMINISM_STATS:
-                rel = abs(val - self.first_result) / max(abs(self.first_result), 1e-30)
+                first = self._first_results.get(idx, self.first_result)
+                rel = abs(val - first) / max(abs(first), 1e-30)
                 self.stats.setdefault(message, []).append(rel)
                 return
-            if self.first_result is None:
+            if self.first_result is None or idx != (self._suspect_idx or 0):
                 return
             same = self._same(val, self.first_result, tolerance)
             if not same:
@@ -235,11 +271,25 @@ class RerunStateMachine:
                 # reproducible on this device: replay elsewhere to tell a real spike from a bad device
                 self.checkpoint_and_exit = True
         elif self.state == RerunState.RERUNNING_FROM_CHECKPOINT:
+            if idx != (self._suspect_idx or 0):
+                return
             same = self.first_result is None or self._same(val, self.first_result, tolerance)
             self.diagnostics.append((self.step, RerunDiagnostic.CORRECT_RESULT if same
                                      else RerunDiagnostic.PERSISTENT_ERROR, message))
             if same and fatal and rejection_func(torch.tensor(val)):
                 self.exit_code = EXIT_CODE_FAILED_ON_RESULT_VALIDATION
+
+    def is_unexpectedly_large(self, result, threshold: float, context: str, num_samples: int = 100) -> bool:
+        """Spike test for ``validate_result``: True when ``result`` exceeds ``threshold`` times the largest value seen
+        so far in this ``context``, once ``num_samples`` values have been seen (reference:
+        rerun_state_machine.py:559).  Values that pass are added to the history."""
+        val = float(result.item()) if torch.is_tensor(result) else float(result)
+        st = self._spike_stats.setdefault(context, QuickStats())
+        if st.n >= num_samples and val > threshold * st.max:
+            return True
+        if self.state in (RerunState.NOT_RUNNING_YET, RerunState.INITIAL_RUN) or self.mode == RerunMode.DISABLED:
+            st.record(val)
+        return False
 
     @staticmethod
     def _same(a: float, b: float, tol: float) -> bool:
@@ -255,12 +305,15 @@ class RerunStateMachine:
 
     def state_dict(self, data_iterator=None):
         return {"mode": self.mode.value, "state": self.state.name, "step": self.step,
-                "first_result": self.first_result, "suspicious_device": self.suspicious_device,
+                "first_result": self.first_result, "suspect_idx": self._suspect_idx, "saved_rng": self.saved_rng,
+                "suspicious_device": self.suspicious_device,
                 "diagnostics": [(s, d.value, m) for s, d, m in self.diagnostics]}
 
     def load_state_dict(self, sd):
         self.step = sd["step"]
         self.first_result = sd.get("first_result")
+        self._suspect_idx = sd.get("suspect_idx")
+        self.saved_rng = sd.get("saved_rng")
         self.suspicious_device = sd.get("suspicious_device")
         if sd.get("state") == RerunState.WILL_RERUN_FROM_CHECKPOINT.name:
             self.state = RerunState.RERUNNING_FROM_CHECKPOINT
@@ -449,3 +502,21 @@ def maybe_setup_simulated_fault(rank: Optional[int] = None, world_size: Optional
     t.daemon = True
     t.start()
     return t
+
+
+# ----------------------------------------------------------------------------- process-wide state machine
+_RERUN_MACHINE: Optional[RerunStateMachine] = None
+
+
+def set_rerun_state_machine(machine: Optional[RerunStateMachine]) -> None:
+    global _RERUN_MACHINE
+    _RERUN_MACHINE = machine
+
+
+def get_rerun_state_machine() -> RerunStateMachine:
+    """The machine of this process (a disabled one when the program did not configure any), for loss functions
+    that validate their result (reference: rerun_state_machine.py:1196 get_rerun_state_machine)."""
+    global _RERUN_MACHINE
+    if _RERUN_MACHINE is None:
+        _RERUN_MACHINE = RerunStateMachine("disabled")
+    return _RERUN_MACHINE

@@ -173,6 +173,9 @@ def train_step(forward_step_func, data_iterator, model: Sequence[torch.nn.Module
         losses = []
         while rerun_state_machine.should_run_forward_backward(data_iterator):
             losses = run_once()
+        if rerun_state_machine.should_checkpoint_and_exit()[0]:
+            # the caller saves the state from before this step and exits: no update is applied
+            return {}, 1, None, None
     ok, grad_norm, zeros = optimizer.step()
     skipped = 0 if ok else 1
     if ok and opt_param_scheduler is not None:

@@ -263,3 +263,25 @@ def test_pytorch_profiler_window_writes_a_trace(tmp_path):
                        cwd=ROOT, env=env)
     assert r.returncode == 0, (r.stdout + r.stderr)[-2000:]
     assert any(f.endswith(".pt.trace.json") for f in os.listdir(tb))
+
+
+def test_injected_result_faults_are_replayed_and_triaged(tmp_path):
+    """--error-injection-rate 1 corrupts the first validated loss.  A transient fault is replayed in place and the
+    run matches a clean one; a reproducible fault saves the state from before the step and exits with the
+    "resume to disambiguate" code, and the restart replays the step and blames the first device."""
+    clean = _iters(_run([]))
+    out = _run(["--error-injection-rate", "1", "--error-injection-type", "transient_error"])
+    assert "result validation, iteration 1: transient_error" in out
+    got = _iters(out)
+    assert sorted(got) == sorted(clean) and all(abs(got[i][1] - clean[i][1]) < 1e-6 for i in clean)
+    ck = str(tmp_path / "ckpt")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29617")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + BASE +
+                       ["--save", ck, "--error-injection-rate", "1", "--error-injection-type", "persistent_error"],
+                       capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert r.returncode == 16, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "to replay the step from the checkpoint" in r.stdout and not _iters(r.stdout)
+    again = _run(["--save", ck, "--load", ck])
+    assert "result validation, iteration 1: persistent_error" in again
+    b = _iters(again)
+    assert sorted(b) == sorted(clean) and abs(b[8][1] - clean[8][1]) < 1e-4

@@ -47,8 +47,31 @@ def test_data_iterator_replays_a_step():
 def test_disabled_mode_runs_once():
     m = RerunStateMachine("disabled")
     it = RerunDataIterator(iter(range(5)))
-    assert _run_step(m, it, lambda b: 1e9) == [0]
-    assert _run_step(m, it, lambda b: 1.0) == [1]
+    assert _run_step(m, it, lambda b: 1.0) == [0]
+    assert _run_step(m, it, lambda b: 2.0) == [1]
+    # nothing is replayed, but a rejected result is still fatal; a non-fatal one passes
+    with pytest.raises(RuntimeError, match="validation failed"):
+        m.validate_result(1e9, _too_big, "loss")
+    m.validate_result(1e9, _too_big, "loss", fatal=False)
+
+
+def test_spike_detector_needs_history():
+    m = RerunStateMachine("disabled")
+    for v in range(10):
+        assert not m.is_unexpectedly_large(1.0 + 0.01 * v, threshold=10, context="loss", num_samples=10)
+    assert not m.is_unexpectedly_large(5.0, threshold=10, context="loss", num_samples=10)
+    assert m.is_unexpectedly_large(500.0, threshold=10, context="loss", num_samples=10)
+    assert not m.is_unexpectedly_large(500.0, threshold=10, context="other", num_samples=10)   # own history
+
+
+def test_process_wide_machine():
+    from megatron_lm_b200.training.resilience import get_rerun_state_machine, set_rerun_state_machine
+    set_rerun_state_machine(None)
+    assert get_rerun_state_machine().mode.value == "disabled"
+    m = RerunStateMachine("report_stats")
+    set_rerun_state_machine(m)
+    assert get_rerun_state_machine() is m and m.mode.value == "report_determinism_stats"
+    set_rerun_state_machine(None)
 
 
 def test_clean_step_is_not_replayed():
@@ -235,3 +258,24 @@ def test_simulated_fault_picks_one_victim_and_uses_the_kill_hook(monkeypatch):
     assert calls == [(os.getpid(), signal.SIGKILL)]
     monkeypatch.delenv("FT_SIM_FAULT_DESC")
     assert maybe_setup_simulated_fault(rank=0, world_size=4) is None
+
+
+def test_several_validations_per_step_are_matched_by_position():
+    """Three microbatches per step, the second one glitches once: only that call is compared on the replay."""
+    m = RerunStateMachine("validate_results")
+    it = RerunDataIterator(iter(range(20)))
+    passes = []
+    glitch = {"armed": True}
+    while m.should_run_forward_backward(it):
+        vals = []
+        for mb in range(3):
+            b = next(it)
+            v = 1.0 + b
+            if mb == 1 and glitch["armed"]:
+                v, glitch["armed"] = 1e9, False
+            vals.append(v)
+            m.validate_result(v, _too_big, "loss")
+        passes.append(vals)
+    assert len(passes) == 2 and passes[1] == [1.0, 2.0, 3.0]
+    assert m.diagnostics == [(0, RerunDiagnostic.TRANSIENT_ERROR, "loss")]
+    assert m.should_checkpoint_and_exit() == (False, None)
