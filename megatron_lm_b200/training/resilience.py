@@ -520,3 +520,27 @@ def get_rerun_state_machine() -> RerunStateMachine:
     if _RERUN_MACHINE is None:
         _RERUN_MACHINE = RerunStateMachine("disabled")
     return _RERUN_MACHINE
+
+
+SPIKY_LOSS_FACTOR = 10      # a loss this many times the largest seen so far is replayed (reference: pretrain_gpt.py:56)
+
+
+def validate_loss(loss, args) -> None:
+    """NaN / Inf / spike tests of one microbatch's loss through the process-wide machine, under the flags
+    ``--check-for-nan-in-loss-and-grad`` and ``--check-for-spiky-loss`` (reference: pretrain_gpt.py:248-278).  Costs
+    one host read of the loss."""
+    check_nan = getattr(args, "check_for_nan_in_loss_and_grad", False)
+    check_spike = getattr(args, "check_for_spiky_loss", False)
+    if not (check_nan or check_spike):
+        return
+    machine = get_rerun_state_machine()
+    value = float(loss)
+    if check_nan:
+        machine.validate_result(value, lambda x: bool(torch.isnan(x)), "found NaN in local forward loss calculation",
+                                tolerance=0.0, fatal=True)
+        machine.validate_result(value, lambda x: bool(torch.isinf(x)), "found Inf in local forward loss calculation",
+                                tolerance=0.0, fatal=True)
+    if check_spike:
+        def spiky(x):
+            return machine.is_unexpectedly_large(x, threshold=SPIKY_LOSS_FACTOR, context="loss")
+        machine.validate_result(value, spiky, "Spiky loss", tolerance=0.0, fatal=False)

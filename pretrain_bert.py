@@ -21,6 +21,7 @@ from megatron_lm_b200.parallel import state  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.batch import broadcast_data  # noqa: E402
 from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E402
+from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 
 
 def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
@@ -43,6 +44,7 @@ def get_batch(data_iterator):
 def loss_func(loss_mask, sentence_order, output_tensor):
     lm_loss_, sop_logits = output_tensor
     lm_loss = torch.sum(lm_loss_.float().view(-1) * loss_mask.reshape(-1)) / loss_mask.sum().clamp(min=1)
+    validate_loss(lm_loss, get_args())
     if sop_logits is not None:
         sop_loss = F.cross_entropy(sop_logits.view(-1, 2).float(), sentence_order.view(-1), ignore_index=-1)
         return lm_loss + sop_loss, {"lm loss": lm_loss.detach(), "sop loss": sop_loss.detach()}

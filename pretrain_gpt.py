@@ -22,9 +22,7 @@ from megatron_lm_b200.parallel import state  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.batch import get_batch_on_this_cp_rank, get_batch_on_this_tp_rank  # noqa: E402
 from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E402
-from megatron_lm_b200.training.resilience import get_rerun_state_machine  # noqa: E402
-
-SPIKY_LOSS_FACTOR = 10      # a loss this many times the largest seen so far is replayed (reference: pretrain_gpt.py:56)
+from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 
 
 def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
@@ -54,22 +52,7 @@ def loss_func(loss_mask, output_tensor):
     total = torch.stack([torch.sum(losses * mask), mask.sum()])
     if state.get_context_parallel_world_size() > 1:
         torch.distributed.all_reduce(total, group=state.get_context_parallel_group())
-    args = get_args()
-    check_nan = getattr(args, "check_for_nan_in_loss_and_grad", False)
-    check_spike = getattr(args, "check_for_spiky_loss", False)
-    if check_nan or check_spike:
-        # one host read per microbatch; the machine replays the step to tell a glitch from a real divergence
-        machine = get_rerun_state_machine()
-        value = float(total[0])
-        if check_nan:
-            machine.validate_result(value, lambda x: bool(torch.isnan(x)), "found NaN in local forward loss calculation",
-                                    tolerance=0.0, fatal=True)
-            machine.validate_result(value, lambda x: bool(torch.isinf(x)), "found Inf in local forward loss calculation",
-                                    tolerance=0.0, fatal=True)
-        if check_spike:
-            machine.validate_result(
-                value, partial(machine.is_unexpectedly_large, threshold=SPIKY_LOSS_FACTOR, context="loss"),
-                "Spiky loss", tolerance=0.0, fatal=False)
+    validate_loss(total[0], get_args())
     return total[0], total[1].to(torch.int64), {"lm loss": total.detach().clone()}
 
 

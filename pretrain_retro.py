@@ -23,6 +23,7 @@ from megatron_lm_b200.data.indexed_dataset import IndexedDataset  # noqa: E402
 from megatron_lm_b200.models.retro import RetroConfig, RetroModel  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E402
+from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 
 
 def add_retro_args(parser):
@@ -93,6 +94,7 @@ def loss_func(loss_mask, output_tensor):
     losses = output_tensor.float().view(-1)
     mask = loss_mask.reshape(-1).float()
     loss = torch.sum(losses * mask) / mask.sum().clamp(min=1)
+    validate_loss(loss, get_args())
     return loss, {"lm loss": loss.detach()}
 
 

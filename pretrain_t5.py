@@ -18,6 +18,7 @@ from megatron_lm_b200.models.t5 import T5Model  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.batch import broadcast_data  # noqa: E402
 from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E402
+from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 
 
 def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
@@ -43,6 +44,7 @@ def get_batch(data_iterator):
 def loss_func(loss_mask, output_tensor):
     lm = output_tensor.float()
     loss = torch.sum(lm.view(-1) * loss_mask.reshape(-1)) / loss_mask.sum().clamp(min=1)
+    validate_loss(loss, get_args())
     return loss, {"lm loss": loss.detach()}
 
 

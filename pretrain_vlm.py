@@ -15,6 +15,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from megatron_lm_b200.models.multimodal import DEFAULT_IMAGE_TOKEN_INDEX, LLaVAModel  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E402
+from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 
 
 def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
@@ -60,6 +61,7 @@ def loss_func(loss_mask, output_tensor):
     losses = output_tensor.float().view(-1)
     mask = loss_mask.reshape(-1).float()
     total = torch.stack([torch.sum(losses * mask), mask.sum()])
+    validate_loss(total[0], get_args())
     return total[0], total[1].to(torch.int64), {"lm loss": total.detach().clone()}
 
 
