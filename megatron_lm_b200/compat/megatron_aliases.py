@@ -84,6 +84,9 @@ _MAP: Dict[str, Union[str, List[Tuple[str, List[str]]]]] = {
     "megatron.core.datasets.indexed_dataset": f"{P}.data.indexed_dataset",
     "megatron.core.datasets.gpt_dataset": f"{P}.data.gpt_dataset",
     "megatron.core.rerun_state_machine": f"{P}.training.resilience",
+    "megatron.core.packed_seq_params": f"{P}.packed_seq_params",
+    "megatron.core.fp8_utils": f"{P}.fp8_utils",
+    "megatron.core.activations": f"{P}.activations",
     "megatron.core.timers": f"{P}.utils.timers",
     "megatron.core.energy_monitor": f"{P}.utils.energy_monitor",
     "megatron.core.config_logger": f"{P}.utils.config_logger",

@@ -215,9 +215,24 @@ class GPTModel(nn.Module):
 
     # -- forward ---------------------------------------------------------------
     def forward(self, input_ids, position_ids=None, attention_mask=None, decoder_input=None, labels=None,
-                inference_context=None, loss_mask=None, runtime_gather_output: Optional[bool] = None):
+                inference_context=None, loss_mask=None, runtime_gather_output: Optional[bool] = None,
+                packed_seq_params=None):
         cfg = self.config
         span = None
+        if packed_seq_params is not None:
+            # one row of documents laid end to end: attention stays inside a document, positions restart
+            if inference_context is not None:
+                raise ValueError("packed sequences are a training-time layout")
+            if state.model_parallel_is_initialized() and state.get_context_parallel_world_size() > 1:
+                raise NotImplementedError("packed sequences with context parallelism")
+            ref_ids = input_ids if input_ids is not None else position_ids
+            if ref_ids is None or ref_ids.shape[0] != 1:
+                raise ValueError("packed sequences come as one row of tokens, [1, total]")
+            total = ref_ids.shape[1]
+            seg_mask = packed_seq_params.block_mask(total, ref_ids.device)
+            attention_mask = seg_mask if attention_mask is None else (attention_mask.bool() | seg_mask)
+            if position_ids is None:
+                position_ids = packed_seq_params.positions(total, ref_ids.device).unsqueeze(0)
         if inference_context is not None:
             span = inference_context.rope_span(input_ids)      # (positions covered, first position) of this step
             if position_ids is None:
@@ -240,6 +255,9 @@ class GPTModel(nn.Module):
             rotary = self.rotary_pos_emb(seq, dev, off)
             if inference_context is not None and hasattr(inference_context, "select_rope"):
                 rotary = inference_context.select_rope(rotary, position_ids)    # one table row per token
+            if packed_seq_params is not None:
+                pos = packed_seq_params.positions(rotary[0].shape[0], rotary[0].device)
+                rotary = (rotary[0][pos].contiguous(), rotary[1][pos].contiguous())
         hidden = self.decoder(decoder_input, rotary=rotary, inference_context=inference_context,
                               attention_mask=attention_mask)
         if not self.post_process:

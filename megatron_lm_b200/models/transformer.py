@@ -323,6 +323,11 @@ class MLP(nn.Module):
             config.activation_func, "__name__", "gelu")
         self.act = {"silu": "silu", "swiglu": "silu", "gelu": "gelu", "relu": "relu",
                     "squared_relu": "squared_relu"}.get(act, act)
+        from ..activations import BY_NAME
+        # anything else: a named elementwise function, or the callable itself
+        self.act_fn = BY_NAME.get(self.act) or (config.activation_func if callable(config.activation_func) else None)
+        if self.act_fn is None:
+            raise ValueError(f"unsupported activation {act}")
         self.linear_fc1 = ColumnParallelLinear(config.hidden_size, ffn * (2 if self.gated else 1), config=config,
                                                init_method=config.init_method, bias=config.add_bias_linear,
                                                skip_bias_add=True, is_expert=is_expert,
@@ -338,8 +343,7 @@ class MLP(nn.Module):
             if self.act == "silu":
                 return ops.swiglu(x)
             a, b = x.chunk(2, dim=-1)
-            f = torch.nn.functional.gelu if self.act == "gelu" else torch.relu
-            return f(a) * b
+            return self.act_fn(a) * b
         if self.act == "gelu":
             return ops.bias_gelu(x, bias)
         if bias is not None:
@@ -348,9 +352,7 @@ class MLP(nn.Module):
             return torch.relu(x)
         if self.act == "squared_relu":
             return torch.relu(x).pow(2)
-        if self.act == "silu":
-            return torch.nn.functional.silu(x)
-        raise ValueError(f"unsupported activation {self.act}")
+        return self.act_fn(x)
 
     def forward(self, hidden_states):
         h, b1 = self.linear_fc1(hidden_states)
@@ -422,6 +424,9 @@ class TransformerLayer(nn.Module):
         mods = config.recompute_modules if config.recompute_granularity == "selective" else []
         self.recompute_input_ln = "layernorm" in mods
         self.recompute_mlp = "mlp" in mods
+        if config.fp8:
+            from ..fp8_utils import mark_layer_precision
+            mark_layer_precision(self, config, layer_number - 1)       # first / last layers may stay in 16 bits
 
     def _bda(self, x, bias, residual):
         p = self.hidden_dropout

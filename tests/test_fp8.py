@@ -108,3 +108,25 @@ def test_model_with_fp8_config_cpu():
     l8.backward()
     g = m8.decoder.layers[0].mlp.linear_fc1.weight.grad
     assert g is not None and torch.isfinite(g.float()).all()
+
+
+def test_first_and_last_layers_can_stay_in_16_bits():
+    import torch
+    from megatron_lm_b200 import fp8_utils as F8
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.transformer import TransformerBlock
+    cfg = TransformerConfig(num_layers=4, hidden_size=32, num_attention_heads=4, fp8="hybrid", first_last_layers_bf16=True,
+                            num_layers_at_start_in_bf16=1, num_layers_at_end_in_bf16=2)
+    assert [F8.layer_runs_in_fp8(cfg, i) for i in range(4)] == [False, True, False, False]
+    blk = TransformerBlock(cfg)
+    marks = [getattr(l.mlp.linear_fc1, "fp8_eligible", True) for l in blk.layers]
+    assert marks == [False, True, False, False]
+    assert all(getattr(l.self_attention.linear_qkv, "fp8_eligible", True) == m for l, m in zip(blk.layers, marks))
+    with F8.get_fp8_context(cfg, 0):
+        assert cfg.fp8 is None
+    with F8.get_fp8_context(cfg, 1):
+        assert cfg.fp8 == "hybrid"
+    assert cfg.fp8 == "hybrid"
+    assert F8.get_fp8_align_size("mxfp8") == 32 and F8.get_fp8_align_size("delayed") == 16
+    t = torch.zeros(2, dtype=torch.float8_e4m3fn)
+    assert F8.is_float8tensor(t) and not F8.is_float8tensor(torch.zeros(2))

@@ -162,3 +162,50 @@ def _pg_bundles(rank, world):
 def test_process_group_bundles_from_global_state():
     from tests.dist_utils import run_distributed
     run_distributed(_pg_bundles, 2)
+
+
+def test_packed_sequences_match_the_documents_run_one_by_one():
+    """Two documents packed in one row (thd): logits equal those of each document run alone, for rotary positions
+    (restart per document) and attention (no look across the boundary)."""
+    import torch
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.packed_seq_params import PackedSeqParams
+    torch.manual_seed(3)
+    cfg = TransformerConfig(num_layers=2, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64,
+                            hidden_dropout=0.0, attention_dropout=0.0, normalization="RMSNorm", gated_linear_unit=True,
+                            activation_func="silu", add_bias_linear=False)
+    m = GPTModel(cfg, vocab_size=50, max_sequence_length=32, position_embedding_type="rope").eval()
+    a, b = torch.randint(0, 50, (1, 5)), torch.randint(0, 50, (1, 7))
+    packed = PackedSeqParams.from_lengths([5, 7])
+    assert packed.positions(12).tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 3, 4, 5, 6]
+    with torch.no_grad():
+        both = m(torch.cat((a, b), dim=1), packed_seq_params=packed)
+        la, lb = m(a), m(b)
+    assert torch.allclose(both[:, :5], la, atol=1e-5) and torch.allclose(both[:, 5:], lb, atol=1e-5)
+    # without the boundary the second document sees the first: a different result
+    with torch.no_grad():
+        plain = m(torch.cat((a, b), dim=1))
+    assert not torch.allclose(plain[:, 5:], lb, atol=1e-4)
+
+
+def test_named_and_callable_activations():
+    import torch
+    from megatron_lm_b200 import activations as A
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.transformer import MLP
+    x = torch.linspace(-3, 3, 25)
+    assert torch.allclose(A.squared_relu(x), torch.relu(x) ** 2)
+    assert torch.allclose(A.fast_gelu(x), torch.nn.functional.gelu(x, approximate="tanh"), atol=1e-6)
+    assert (A.quick_gelu(x) - torch.nn.functional.gelu(x)).abs().max() < 0.03
+    for act, gated in (("quick_gelu", False), ("fast_gelu", True), (A.quick_gelu, True)):
+        cfg = TransformerConfig(num_layers=1, hidden_size=16, num_attention_heads=2, ffn_hidden_size=32,
+                                activation_func=act, gated_linear_unit=gated, add_bias_linear=False)
+        mlp = MLP(cfg)
+        h = torch.randn(3, 2, 16)
+        out, _ = mlp(h)
+        w1, w2 = mlp.linear_fc1.weight, mlp.linear_fc2.weight
+        z = h @ w1.t()
+        f = act if callable(act) else A.BY_NAME[act]
+        z = f(z[..., :32]) * z[..., 32:] if gated else f(z)
+        assert torch.allclose(out, z @ w2.t(), atol=1e-5)
