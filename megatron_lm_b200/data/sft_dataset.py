@@ -41,6 +41,14 @@ def default_chat_template(role: str, content: str) -> str:
     return f"<|{role}|>\n{content}\n"
 
 
+def identity_template(role: str, content: str) -> str:
+    """The turn's text as it is (pre-formatted or pre-tokenised conversations)."""
+    return content
+
+
+TEMPLATES = {"identity": identity_template}
+
+
 class SFTDataset(torch.utils.data.Dataset):
     def __init__(self, dataset, tokenizer, sequence_length: int, num_samples: Optional[int] = None,
                  template=default_chat_template, pad_id: Optional[int] = None, seed: int = 1234):

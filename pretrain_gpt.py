@@ -76,6 +76,16 @@ def train_valid_test_datasets_provider(num_samples):
                            tokenizer=args.tokenizer, reset_position_ids=args.reset_position_ids,
                            reset_attention_mask=args.reset_attention_mask, eod_mask_loss=args.eod_mask_loss,
                            create_attention_mask=args.create_attention_mask_in_dataloader)
+    if getattr(args, "sft", False):
+        # supervised fine-tuning: --data-path names a JSONL file of conversations; loss on the assistant turns only
+        from megatron_lm_b200.data.sft_dataset import TEMPLATES, SFTDataset, default_chat_template
+        template = TEMPLATES.get(getattr(args, "sft_tokenizer_prompt_format", None), default_chat_template)
+
+        def make(n, seed):
+            return SFTDataset(args.data_path[-1], args.tokenizer, args.seq_length, n, template=template,
+                              seed=seed) if n else None
+        print_rank_0("building train, validation and test datasets for supervised fine-tuning ...")
+        return make(num_samples[0], args.seed), make(num_samples[1], args.seed + 1), make(num_samples[2], args.seed + 2)
     cls = MockGPTDataset if cfg.mock else GPTDataset
     print_rank_0("building train, validation and test datasets for GPT ...")
     return BlendedMegatronDatasetBuilder(cls, num_samples, lambda: True, cfg).build()

@@ -285,3 +285,25 @@ def test_injected_result_faults_are_replayed_and_triaged(tmp_path):
     assert "result validation, iteration 1: persistent_error" in again
     b = _iters(again)
     assert sorted(b) == sorted(clean) and abs(b[8][1] - clean[8][1]) < 1e-4
+
+
+def test_supervised_finetuning_program_on_a_conversation_file(tmp_path):
+    import json
+    import random
+    rng = random.Random(0)
+    path = tmp_path / "chat.jsonl"
+    with open(path, "w") as f:
+        for _ in range(24):
+            turns = []
+            for role in ("user", "assistant", "user", "assistant"):
+                turns.append({"role": role, "content": " ".join(str(rng.randint(1, 60)) for _ in range(rng.randint(2, 6)))})
+            f.write(json.dumps({"messages": turns}) + "\n")
+    base = [a for a in BASE if a != "--mock-data"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29617")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + base +
+                       ["--sft", "--sft-tokenizer-prompt-format", "identity", "--data-path", str(path)],
+                       capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    rows = _iters(r.stdout)
+    assert sorted(rows) == list(range(1, 9)) and rows[8][1] < rows[1][1]
+    assert "supervised fine-tuning" in r.stdout and "validation loss at iteration 8" in r.stdout
