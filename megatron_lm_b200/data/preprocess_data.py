@@ -43,7 +43,11 @@ class Encoder:
         return lambda text: [s for s in (pat.split(text) if not keep_nl else re.split(r"(?<=[.!?\n])\s*", text)) if s]
 
     def encode(self, line: str):
-        data = json.loads(line)
+        if self.args.plain_text:
+            # one sentence per line, no JSON (parallel corpora for translation; reference: tools/preprocess_data_nmt.py)
+            data = {k: line.rstrip("\n") for k in self.args.json_keys}
+        else:
+            data = json.loads(line)
         ids, lens = {}, {}
         for key in self.args.json_keys:
             text = data[key]
@@ -110,6 +114,7 @@ def get_args(argv=None):
     g.add_argument("--input", required=True, help="JSON-lines file, or a glob when --partitions > 1")
     g.add_argument("--json-keys", nargs="+", default=["text"])
     g.add_argument("--split-sentences", action="store_true")
+    g.add_argument("--plain-text", action="store_true", help="input lines are sentences of text, not JSON records")
     g.add_argument("--keep-newlines", action="store_true")
     g = p.add_argument_group("tokenizer")
     g.add_argument("--tokenizer-type", required=True)

@@ -56,3 +56,13 @@ def test_sft_masks_only_assistant(tmp_path):
     # labels are next tokens; only assistant tokens (4, 5) and the closing eod count
     assert s["loss_mask"].tolist() == [0, 0, 1, 1, 1, 0, 0, 0]
     assert s["labels"][2:5].tolist() == [4, 5, 999]
+
+
+def test_preprocess_plain_text_lines(tmp_path):
+    src = tmp_path / "sents.txt"
+    src.write_text("1 2 3\n4 5\n\n6 7 8 9\n")
+    out = str(tmp_path / "nmt")
+    preprocess_data.main(["--input", str(src), "--output-prefix", out, "--tokenizer-type", "NullTokenizer",
+                          "--vocab-size", "100", "--plain-text"])
+    ds = IndexedDataset(out + "_text_document")
+    assert [ds[i].tolist() for i in range(len(ds))] == [[1, 2, 3], [4, 5], [6, 7, 8, 9]]

@@ -70,4 +70,14 @@ def test_server_program_builds_from_training_flags_and_serves_http():
     conn = http.client.HTTPConnection("127.0.0.1", port, timeout=10)
     conn.request("PUT", "/api", body=json.dumps({"prompts": []}), headers={"Content-Type": "application/json"})
     assert conn.getresponse().status == 400
+    # the command-line client against the same server: a completion, and the server's message for a bad request
+    import contextlib
+    import io
+    from megatron_lm_b200.inference import cli
+    out = io.StringIO()
+    with contextlib.redirect_stdout(out):
+        cli.main([f"127.0.0.1:{port}", "--prompt", "3 4 5", "--tokens-to-generate", "3", "--top-k", "1"])
+    assert out.getvalue().strip() == body["text"][0]
+    bad = cli.request(f"http://127.0.0.1:{port}/api", [], 3)
+    assert bad["error"] == 400 and bad["message"]
     srv.httpd.shutdown()
