@@ -53,6 +53,8 @@ class Encoder:
             text = data[key]
             doc_ids, sent_lens = [], []
             for sent in _ENC.splitter(text):
+                if not sent.strip():
+                    continue
                 t = _ENC.tokenizer.tokenize(sent)
                 if t:
                     doc_ids.extend(t)
