@@ -66,3 +66,23 @@ def test_preprocess_plain_text_lines(tmp_path):
                           "--vocab-size", "100", "--plain-text"])
     ds = IndexedDataset(out + "_text_document")
     assert [ds[i].tolist() for i in range(len(ds))] == [[1, 2, 3], [4, 5], [6, 7, 8, 9]]
+
+
+def test_preprocess_multimodal_pairs(tmp_path):
+    from megatron_lm_b200.data import preprocess_mmdata as M
+    imgs = tmp_path / "img"
+    imgs.mkdir()
+    blobs = [bytes(range(7)), bytes(range(50, 62))]
+    for i, b in enumerate(blobs):
+        (imgs / f"{i:03d}.bin").write_bytes(b)
+    src = tmp_path / "cap.jsonl"
+    _write(src, ["1 2 3", "4 5"])
+    out = str(tmp_path / "mm")
+    M.main(["--input", str(src), "--input-image", str(imgs), "--output-prefix", out, "--tokenizer-type", "NullTokenizer",
+            "--vocab-size", "100", "--pad-length", "5", "--append-eod"])
+    ds = IndexedDataset(out, multimodal=True)
+    assert len(ds) == 4
+    (t0, m0), (i0, mi0), (t1, m1), (i1, mi1) = (ds[i] for i in range(4))
+    assert (m0, mi0, m1, mi1) == (0, 1, 0, 1)
+    assert t0.tolist() == [1, 2, 3, 100, 100] and t1.tolist() == [4, 5, 100, 100, 100]
+    assert M.decode_image_bytes(i0) == blobs[0] and M.decode_image_bytes(i1) == blobs[1]
