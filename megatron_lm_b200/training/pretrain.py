@@ -61,6 +61,8 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
         args = load_yaml_args(args.yaml_cfg, args)
     validate_args(args, args_defaults)
     set_args(args)
+    from ..utils.log_handler import setup_logging
+    setup_logging(getattr(args, "logging_level", None))
     use_cuda = torch.cuda.is_available() and args.distributed_backend == "nccl"
     if use_cuda:
         torch.cuda.set_device(args.local_rank)

@@ -226,3 +226,19 @@ def test_config_logger_writes_json(tmp_path):
     assert p1 != p2
     d = json.load(open(p1))
     assert d["config"]["hidden_size"] == 32 and d["dtype"] == "torch.bfloat16" and d["fn"] == "test_config_logger_writes_json"
+
+
+def test_logging_setup_filters_quiet_loggers(capsys):
+    import logging
+    from megatron_lm_b200.utils.log_handler import StdoutHandler, setup_logging
+    root = logging.getLogger()
+    before = list(root.handlers)
+    try:
+        assert setup_logging(logging.WARNING) == logging.WARNING and root.level == logging.WARNING
+        setup_logging(logging.INFO)
+        assert sum(isinstance(h, StdoutHandler) for h in root.handlers) == 1          # installed once
+        h = next(h for h in root.handlers if isinstance(h, StdoutHandler))
+        mk = lambda name: logging.LogRecord(name, logging.INFO, __file__, 1, "m", None, None)
+        assert h.filter(mk("megatron_lm_b200.training")) and not h.filter(mk("torch.distributed.elastic"))
+    finally:
+        root.handlers[:] = before
