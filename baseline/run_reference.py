@@ -42,6 +42,9 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
     os.environ.setdefault("MASTER_PORT", "29512")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     tp, pp, vpp = layout_for(args.gpus)[:3]
+    if getattr(args, "layout", None):                 # debug only: "tp,pp,vpp" (vpp 0 = none)
+        tp, pp, vpp = (int(x) for x in args.layout.split(","))
+        vpp = vpp or None
     parallel_state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
                                              virtual_pipeline_model_parallel_size=vpp)
     model_parallel_cuda_manual_seed(1234)
@@ -69,8 +72,11 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
         for v in vps:
             if v is not None:
                 parallel_state.set_virtual_pipeline_model_parallel_rank(v)
-            pre = parallel_state.is_pipeline_first_stage(ignore_virtual=False) if v is not None else parallel_state.is_pipeline_first_stage()
-            post = parallel_state.is_pipeline_last_stage(ignore_virtual=False) if v is not None else parallel_state.is_pipeline_last_stage()
+            # this library version wants the virtual stage named when it is asked about a chunk's position
+            pre = parallel_state.is_pipeline_first_stage(ignore_virtual=False, vp_stage=v) if v is not None \
+                else parallel_state.is_pipeline_first_stage()
+            post = parallel_state.is_pipeline_last_stage(ignore_virtual=False, vp_stage=v) if v is not None \
+                else parallel_state.is_pipeline_last_stage()
             kw = dict(vp_stage=v) if v is not None else {}
             m = GPTModel(config=cfg, transformer_layer_spec=spec, vocab_size=M["vocab_size"],
                          max_sequence_length=M["seq_length"], pre_process=pre, post_process=post,
@@ -139,30 +145,33 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
         dev_batches = [b.to(dev) for b in host_batches]
         for w in range(args.warmup):
             one_step(dev_batches[w % 2])
+        # One loop of K steps carries both clocks (the same structure as the other arm): every step copies its
+        # batch from pinned host memory, runs, and reads the loss back; the device time of a step is a pair of
+        # CUDA events around the step alone, the end-to-end time is the wall clock of the whole loop.
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        barrier_sync()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for k in range(args.steps):
-            one_step(dev_batches[k % 2])
-        e1.record()
-        barrier_sync()
-        dev_ms = max_over_ranks(e0.elapsed_time(e1), dev)
-        clocks = sampler.stop() if rank == 0 else None
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
         barrier_sync()
         t0 = time.perf_counter()
         loss_val = 0.0
         for k in range(args.steps):
             b = host_batches[k % 2].to(dev, non_blocking=True)
+            ev[k][0].record()
             losses = one_step(b)
-            if losses:
+            ev[k][1].record()
+            if pp > 1:
+                lt = torch.stack([d["lm loss"] for d in losses]).mean().reshape(1) if losses else torch.zeros(1, device=dev)
+                dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+                loss_val = float(lt.item())
+            elif losses:
                 loss_val = float(torch.stack([d["lm loss"] for d in losses]).mean().item())
             else:
                 torch.cuda.current_stream().synchronize()
         barrier_sync()
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, dev)
+        dev_ms = max_over_ranks(sum(a.elapsed_time(b_) for a, b_ in ev), dev)
+        clocks = sampler.stop() if rank == 0 else None
     except Exception as e:
         if rank == 0:
             print(json.dumps({"impl": "reference", "unavailable": f"training step failed: {type(e).__name__}: {e}"[:300]}))
@@ -185,7 +194,11 @@ def run(args, ref_path, M, layout_for, ClockSampler, max_over_ranks, barrier_syn
                                   "recompute of core attention"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
-                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": loss_val},
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "last_loss": loss_val,
+                    "loss_note": "this arm cycles two fixed batches, so its loss falls by memorisation; it is not "
+                                 "comparable with the other arm's loss on fresh batches"},
+            "timing": "one loop of K steps: device time = sum of per-step CUDA-event intervals (max over ranks), "
+                      "e2e = wall clock of the same loop incl. the pinned-host batch copy and the loss read",
         }), flush=True)
     dist.barrier()
     dist.destroy_process_group()

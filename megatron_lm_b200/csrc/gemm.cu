@@ -51,11 +51,19 @@ MLB_API int mlb_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B,
 }
 
 // CTA-pair (cta_group::2) variant of mlb_gemm for plain products whose output rows are 16-byte aligned.
+// sched: null for the static tile schedule, or two zeroed device words for the dynamic one (tiles are drawn from a
+// counter by the blocks that are running, so the product does not take a second wave when another stream's
+// long-running kernel holds some SMs); launches that share the words must be ordered on one stream.
 MLB_API int mlb_gemm_pair(int lp_fmt, const void* A, long lda, int a_mn, const void* B, long ldb, int b_mn, void* D,
                           long ldd, int out_mode, const void* bias, int M, int N, int K, int max_ctas, int* status,
-                          cudaStream_t st) {
+                          cudaStream_t st, uint32_t* sched) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   int sms = sm_count_cached();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  return run_gemm2(lp_fmt, A, lda, a_mn, B, ldb, b_mn, D, ldd, out_mode, bias, M, N, K, sms, status, st);
+  if (sched == nullptr)
+    return run_gemm2(lp_fmt, A, lda, a_mn, B, ldb, b_mn, D, ldd, out_mode, bias, M, N, K, sms, status, st);
+  CommParams cp = {};
+  cp.mode = COMM_NONE;
+  cp.sched = sched;
+  return run_gemm2(lp_fmt, A, lda, a_mn, B, ldb, b_mn, D, ldd, out_mode, bias, M, N, K, sms, status, st, &cp);
 }

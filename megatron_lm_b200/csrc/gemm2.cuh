@@ -27,6 +27,17 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// cluster-scope acquire: pairs with a release.cluster arrive made by the other CTA after it stored data here
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\tselp.u32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -86,13 +97,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   uint8_t* sB = smem + kStages * S::kABytes;
   uint8_t* sEpi = smem + kStages * (S::kABytes + S::kBBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + S::kEpiBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  constexpr int kSched = 4;                              // depth of the tile-announcement ring (dynamic schedule)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4 + 2 * kSched);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);     // [kSched]
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
   auto tempty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+  auto sfull = [&](int s) { return bar0 + 8u * (2 * kStages + 4 + s); };              // one per CTA
+  auto sempty = [&](int s) { return bar0 + 8u * (2 * kStages + 4 + kSched + s); };    // used in the leader only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // All-gather mode: the first n_comm CTAs (whole pairs) are copy workers and take no part in the GEMM or in any
@@ -106,7 +121,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 16); }
-    *abort_flag = 0;
+    // a tile announcement is read by 18 parties: the leader's MMA thread, the partner's producer and the
+    // 16 epilogue warps of the pair
+    for (int q = 0; q < kSched; ++q) { mbar_init(sfull(q), 1); mbar_init(sempty(q), 18); }
+    // a wait that ran out earlier on this GPU (this step is lost anyway): drain at once instead of waiting again
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmD);
   }
@@ -142,13 +161,66 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
   };
 
+  // Tile schedule.  Static (plain products): pair q takes tiles q, q + n_pairs, ...  Dynamic (cp.sched set; the
+  // communication modes): the leader's producer thread draws tile numbers from a global counter and announces
+  // them to both CTAs through a small ring, so tiles only ever belong to pairs that are running.  A pair that
+  // has not been given an SM yet (other kernels hold it) then owns nothing that a peer GPU or a later tile could
+  // wait for: the fused kernels stay deadlock-free whatever share of the grid is resident.
+  const bool dyn = cp.sched != nullptr;
+  const uint32_t sempty_leader0 = map_to_cta(sempty(0), 0);
+  // i-th tile of this pair for a consumer role (-1: no more tiles, -2: a wait ran out)
+  auto consumer_tile = [&](int i) -> int {
+    if (!dyn) { const int t = pair + i * n_pairs; return t < num_tiles ? t : -1; }
+    const int q = i % kSched;
+    const uint32_t par = (uint32_t)(i / kSched) & 1u;
+    if (!mbar_try_wait_cluster(sfull(q), par)) {
+      const long long t0 = clock64();
+      uint32_t it = 0;
+      while (!mbar_try_wait_cluster(sfull(q), par)) {
+        if ((++it & 63u) == 0u) {
+          if (*abort_flag) return -2;
+          if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, 7); return -2; }
+        }
+      }
+    }
+    return tile_ring[q];
+  };
+  auto consumer_release = [&](int i) { mbar_arrive_cluster(sempty_leader0 + 8u * (uint32_t)(i % kSched)); };
+  auto draw_tile = [&]() -> int {
+    const int t = (int)atomicAdd(cp.sched, 1u);
+    return t < num_tiles ? t : -1;
+  };
+  // leader's producer: publish the i-th tile number (or -1) in both CTAs
+  auto announce = [&](int i, int tile) -> bool {
+    const int q = i % kSched;
+    if (!mbar_wait(sempty(q), ((uint32_t)(i / kSched) & 1u) ^ 1u, abort_flag, p.status, 8)) return false;
+    tile_ring[q] = tile;
+    st_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(tile_ring + q)), 1), (uint32_t)tile);
+    mbar_arrive_cluster(map_to_cta(sfull(q), 0));
+    mbar_arrive_cluster(map_to_cta(sfull(q), 1));
+    return true;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       int ready_blk = -1;
-      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+      const bool scheduler = dyn && leader;
+      int drawn = scheduler ? draw_tile() : 0;           // the next draw is always in flight behind the current tile
+      for (int i = 0; ok; ++i) {
+        int tile;
+        if (scheduler) {
+          tile = drawn;
+          if (!announce(i, tile)) { ok = false; break; }
+          if (tile >= 0) drawn = draw_tile();
+        } else {
+          tile = consumer_tile(i);
+          if (tile == -2) { ok = false; break; }
+          if (dyn) consumer_release(i);
+        }
+        if (tile < 0) break;
         int mb, nb, owner, mloc; tile_mn(tile, mb, nb, owner, mloc);
         const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN + 128 * (int)rank;
         const bool own_rows = cp.mode == COMM_AG && owner == cp.rank;
@@ -190,7 +262,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       int stage = 0; uint32_t phase = 0;
       int t = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
+      for (; ok; ++t) {
+        const int tile = consumer_tile(t);
+        if (tile == -2) { ok = false; break; }
+        if (dyn) consumer_release(t);
+        if (tile < 0) break;
         const int acc = t & 1;
         const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
@@ -222,7 +298,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     int pend_owner = -1, pend_blk = 0;                    // reduce-scatter: tile whose arrival signal is still owed
     bool ok = true;
     const uint32_t tempty_leader0 = map_to_cta(tempty(0), 0);
-    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
+    for (; ok; ++t) {
+      const int tile = consumer_tile(t);                  // every lane reads the announcement
+      if (tile == -2) { ok = false; break; }
+      if (dyn) { __syncwarp(); if (lane == 0) consumer_release(t); }
+      if (tile < 0) break;
       const int acc = t & 1;
       const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
       int mb, nb, owner, mloc; tile_mn(tile, mb, nb, owner, mloc);
@@ -355,6 +435,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   __syncthreads();
   cluster_sync_all();
   if (warp == 1) { fence_after_sync(); tmem_dealloc2(tmem_base, 512); }
+  if (dyn && leader && threadIdx.x == 0) {
+    // the last pair to leave puts the counters back to zero for the next launch on this buffer set (launches
+    // that share a counter pair are ordered on one stream)
+    __threadfence();
+    if (atomicAdd(cp.sched + 1, 1u) + 1u == (uint32_t)n_pairs) { cp.sched[0] = 0u; cp.sched[1] = 0u; __threadfence(); }
+  }
 }
 
 template <bool A_MN, bool B_MN, bool FP8 = false>

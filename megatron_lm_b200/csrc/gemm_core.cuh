@@ -80,6 +80,9 @@ struct CommParams {
   uint32_t cnt_target;              // cumulative arrivals that mean "this call's partials are all here"
   const void* residual; long ld_res;
   void* out; long ld_out;
+  // dynamic tile schedule (CTA-pair kernel): two local words, {next tile, pairs that have left}; both are zero
+  // between launches.  Null selects the static schedule.
+  uint32_t* sched;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -108,6 +111,8 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, int*
     if ((int32_t)(v - target) >= 0) return true;
     if ((++it & 31u) == 0u) {
       if (clock64() - t0 > kWaitCycles) { if (status) atomicCAS(status, 0, code); return false; }
+      // a wait that already ran out on this GPU means the step is lost: do not sit through the limit again
+      if ((it & 1023u) == 0u && status && *reinterpret_cast<volatile int*>(status) != 0) return false;
       __nanosleep(64);
     }
   }

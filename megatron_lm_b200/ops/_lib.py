@@ -59,7 +59,7 @@ _SIGS: Dict[str, str] = {
     "mlb_scale": "iplpfp",
     "mlb_count_zeros": "iplpp",
     "mlb_gemm": "iplipliplipiiiipp",
-    "mlb_gemm_pair": "iplipliplipiiiipp",
+    "mlb_gemm_pair": "iplipliplipiiiippp",
     "mlb_set_device": "i",
     "mlb_device_sm_count": "i",
 }

@@ -66,18 +66,45 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if bias is not None:
         bias = bias.to(a.dtype).contiguous()
     st = _lib.status_word()
-    fn = _lib.lib().mlb_gemm
+    args = (1 if a.dtype == torch.bfloat16 else 0, a.data_ptr(), a.stride(0), int(a_mn),
+            b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0), mode,
+            _lib.ptr(bias), M, N, K, max_ctas, st.data_ptr(), _lib.stream())
     if _PAIR and N >= 256 and M >= 256 and (out.stride(0) * out.element_size()) % 16 == 0 and out.data_ptr() % 16 == 0:
-        fn = _lib.lib().mlb_gemm_pair            # CTA-pair kernel: 256 x 256 tiles over two SMs
-    _lib.check(fn(1 if a.dtype == torch.bfloat16 else 0, a.data_ptr(), a.stride(0), int(a_mn),
-                  b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0), mode,
-                  _lib.ptr(bias), M, N, K, max_ctas, st.data_ptr(), _lib.stream()), "gemm")
+        # CTA-pair kernel: 256 x 256 tiles over two SMs
+        dyn = _DYNAMIC and not torch.cuda.is_current_stream_capturing()
+        _lib.check(_lib.lib().mlb_gemm_pair(*args, _sched_words() if dyn else None), "gemm")
+    else:
+        _lib.check(_lib.lib().mlb_gemm(*args), "gemm")
     return out
 
 
 import os as _os
 
 _PAIR = _os.environ.get("MLB_GEMM_PAIR", "1") == "1"      # set MLB_GEMM_PAIR=0 for the single-CTA kernel
+# Dynamic tile schedule of the CTA-pair kernel (tiles drawn from a device counter by whichever blocks are running).
+# With the static schedule a persistent grid needs a second wave whenever another stream's long-running kernel
+# (pipeline send / receive, gradient reduction) holds a few SMs: the blocks that found no SM still own their share
+# of the tiles.  The training set-up turns this on when such kernels exist; MLB_GEMM_DYNAMIC=0/1 forces it.
+_DYNAMIC = _os.environ.get("MLB_GEMM_DYNAMIC", "0") == "1"
+_sched = {}
+
+
+def set_dynamic_schedule(on: bool) -> None:
+    global _DYNAMIC
+    env = _os.environ.get("MLB_GEMM_DYNAMIC")
+    _DYNAMIC = (env == "1") if env in ("0", "1") else bool(on)
+
+
+def _sched_words() -> int:
+    """Two zeroed words per (device, stream): launches on one stream are ordered, so they can share them."""
+    key = (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+    t = _sched.get(key)
+    if t is None:
+        with torch.cuda.stream(torch.cuda.default_stream()):
+            t = torch.zeros(2, dtype=torch.int32, device="cuda")
+        torch.cuda.default_stream().synchronize()
+        _sched[key] = t
+    return t.data_ptr()
 
 
 class _LinearFn(torch.autograd.Function):

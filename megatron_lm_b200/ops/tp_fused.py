@@ -33,9 +33,11 @@ from . import _lib
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 _lib.register_signatures({
-    "mlb_ag_gemm": "ipppppiiiiiipliplipiipp",
-    "mlb_gemm_rs": "iplplippiiiiplpliipp",
+    "mlb_ag_gemm": "ipppppiiiiiipliplipiippp",
+    "mlb_gemm_rs": "iplplippiiiiplpliippp",
     "mlb_gemm_rs_arrivals": "iii",
+    "mlb_tp_fused_uses_pair": "iii",
+    "mlb_occupy_sms": "iiip",
 })
 
 
@@ -44,7 +46,8 @@ def _ptr_array(ptrs: List[int]):
 
 
 class FusedTP:
-    def __init__(self, group, rows_per_rank: int, max_k: int, max_n: int, dtype=torch.bfloat16, n_comm: int = 8):
+    def __init__(self, group, rows_per_rank: int, max_k: int, max_n: int, dtype=torch.bfloat16, n_comm: int = 8,
+                 dynamic_schedule: bool = True):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.tp = dist.get_world_size(group)
@@ -78,6 +81,8 @@ class FusedTP:
         self.x_local = self.buf[self._offs[0]:self._offs[0] + x_bytes].view(dtype)
         self.chunk_flags = torch.zeros(self.tp * bpr, dtype=torch.int32, device=dev)
         self.comm_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        # {next tile, pairs that have left} of the dynamic tile schedule; the kernel leaves both at zero
+        self.sched = torch.zeros(2, dtype=torch.int32, device=dev) if dynamic_schedule else None
         self.ag_seq = 0
         self.comm_total = 0
         self.rs_calls = 0
@@ -106,7 +111,7 @@ class FusedTP:
             1 if self.dtype == torch.bfloat16 else 0, _ptr_array(self.x_ptrs), _ptr_array(self.sig_ptrs),
             gathered.data_ptr(), self.chunk_flags.data_ptr(), self.comm_counter.data_ptr(), self.rank, self.tp,
             rows, self.ag_seq, self.comm_total, self.n_comm, weight.data_ptr(), weight.stride(0), int(b_mn), y.data_ptr(),
-            y.stride(0), mode, _lib.ptr(bias_c), N, K, st.data_ptr(), _lib.stream()), "ag_gemm")
+            y.stride(0), mode, _lib.ptr(bias_c), N, K, st.data_ptr(), _lib.stream(), _lib.ptr(self.sched)), "ag_gemm")
         return y, gathered
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
@@ -131,8 +136,16 @@ class FusedTP:
             1 if self.dtype == torch.bfloat16 else 0, a2.data_ptr(), a2.stride(0), weight.data_ptr(), weight.stride(0),
             int(b_mn), _ptr_array(self.recv_ptrs[which]), _ptr_array(self.cnt_ptrs[which]), self.cnt_expected[which],
             self.rank, self.tp, self.rows, _lib.ptr(res2), 0 if res2 is None else res2.stride(0), out.data_ptr(),
-            out.stride(0), N, K, st.data_ptr(), _lib.stream()), "gemm_rs")
+            out.stride(0), N, K, st.data_ptr(), _lib.stream(), _lib.ptr(self.sched)), "gemm_rs")
         return out
+
+
+def occupy_sms(n_ctas: int, smem_bytes: int, usec: int, stream=None) -> None:
+    """Test aid: hold ``n_ctas`` SMs' worth of shared memory on ``stream`` for ``usec`` microseconds (capped at
+    0.5 s) - a stand-in for long-running kernels of other streams that keep SMs away from a fused kernel."""
+    st = (stream or torch.cuda.current_stream()).cuda_stream
+    _lib.stream()
+    _lib.check(_lib.lib().mlb_occupy_sms(n_ctas, smem_bytes, usec, st), "occupy_sms")
 
 
 def attach_fused_tp(model_chunks, config, seq_length: int, micro_batch_size: int) -> Optional[FusedTP]:
@@ -142,15 +155,15 @@ def attach_fused_tp(model_chunks, config, seq_length: int, micro_batch_size: int
     tp = state.get_tensor_model_parallel_world_size()
     if tp == 1 or not config.sequence_parallel:
         return None
-    if state.get_pipeline_model_parallel_world_size() > 1:
-        # The fused kernels need all of their thread blocks resident at once: consumer blocks wait on flags that
-        # worker blocks (or the peers' blocks) set.  A pipeline stage has NCCL send / receive kernels spinning on
-        # some SMs for as long as the neighbouring stage computes, and those kernels wait, transitively, on this
-        # GPU's progress; blocks of a fused kernel that find no SM would then never run.  With pipeline
-        # parallelism the layers therefore keep the NCCL collectives and the plain (dependency-free) GEMM kernels.
-        return None
     rows = seq_length * micro_batch_size // config.context_parallel_size // tp
     if rows % 128:
+        return None
+    # Other kernels may hold SMs for a long time while these run (NCCL send / receive kernels of a pipeline stage,
+    # gradient reductions of a data-parallel group), so part of a fused kernel's grid can be waiting for an SM.
+    # The CTA-pair kernel hands tiles to running blocks only (dynamic schedule) and tolerates that; the single-CTA
+    # kernel assigns tiles to block numbers up front and is used only when nothing else competes for SMs.
+    shared_sms = state.get_pipeline_model_parallel_world_size() > 1 or state.get_data_parallel_world_size() > 1
+    if shared_sms and not _lib.lib().mlb_tp_fused_uses_pair(rows, 256, 8):
         return None
     max_k = max_n = 0
     lins = []
@@ -172,3 +185,11 @@ def attach_fused_tp(model_chunks, config, seq_length: int, micro_batch_size: int
     for m in lins:
         m.fused = fused
     return fused
+
+
+def detach_fused_tp(model_chunks) -> None:
+    """Take the fused communicator off every layer again: they go back to NCCL collectives around plain GEMMs."""
+    for chunk in model_chunks:
+        for m in chunk.modules():
+            if getattr(m, "fused", None) is not None:
+                m.fused = None

@@ -278,6 +278,14 @@ def initialize_model_parallel(
     # send (or two sends first) would wait on each other for ever.  With one channel per direction and kind that
     # cannot happen, whatever order the schedule posts its transfers in.
     _S.pp_channels = {}
+    # A posted receive is a kernel that spins until the neighbour stage sends, i.e. for as long as that stage
+    # computes; it holds one SM per NCCL channel all that time.  Activations of one microbatch are a few MB, so two
+    # channels are plenty and leave the SMs to the GEMMs ("pp_channel" in the NCCL config overrides this).
+    ch_opts = None
+    if is_nccl and pp_backend == "nccl":
+        cfg_ch = dict(_S.nccl_cfg or {})
+        cfg_ch.setdefault("pp_channel", {"max_ctas": 2, "min_ctas": 1})
+        ch_opts = _nccl_options("pp_channel", cfg_ch)
     if pp > 1:
         for ranks in dense.get_ranks("pp"):
             for s in range(len(ranks)):
@@ -285,7 +293,8 @@ def initialize_model_parallel(
                 for kind in ("F", "B"):
                     pg = None
                     if not virtual and dist.is_initialized():
-                        pg = dist.new_group(pair, backend=pp_backend, timeout=timeout)
+                        pg = dist.new_group(pair, backend=pp_backend, timeout=timeout,
+                                            **({"pg_options": ch_opts} if ch_opts is not None else {}))
                     if rank in ranks and rank in pair:
                         _S.pp_channels[(kind, s)] = pg
     # embedding groups: first and last pipeline stage (tied embeddings)

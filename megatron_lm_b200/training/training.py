@@ -30,6 +30,11 @@ def get_model(model_provider: Callable, config: TransformerConfig, ddp_config: O
     init = state.model_parallel_is_initialized()
     pp = state.get_pipeline_model_parallel_world_size() if init else 1
     vpp = state.get_virtual_pipeline_model_parallel_world_size() if init else None
+    if init and torch.cuda.is_available():
+        # pipeline transfers and data-parallel reductions are long-running kernels on other streams: let the
+        # persistent GEMM hand its tiles to whichever blocks are running instead of to block numbers
+        from ..ops.gemm import set_dynamic_schedule
+        set_dynamic_schedule(pp > 1 or state.get_data_parallel_world_size(with_context_parallel=True) > 1)
     chunks = []
     if pp > 1 and vpp is not None and vpp > 1:
         for i in range(vpp):

@@ -32,6 +32,60 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert torch.allclose(out.float(), ref, atol=0.5, rtol=5e-2)
 
 
+@pytest.mark.parametrize("dynamic", [False, True])
+@pytest.mark.parametrize("M,N,K", [(300, 520, 200), (257, 264, 72), (512, 300, 136), (1000, 32000, 256),
+                                   (4096, 11008, 4096), (4096, 4096, 11008), (4096, 32000, 4096)])
+def test_gemm_pair_kernel_ragged_and_model_shapes(M, N, K, dynamic):
+    """Shapes that reach the CTA-pair kernel (M, N >= 256): ragged edges, the vocabulary projection, the MLP
+    products of the 7B model; with the static and with the dynamic (counter-drawn) tile schedule."""
+    from megatron_lm_b200.ops import gemm as G
+    torch.manual_seed(5)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    old = G._DYNAMIC
+    G._DYNAMIC = dynamic
+    try:
+        for _ in range(2):                      # the second launch finds the schedule words back at zero
+            out = gemm(A, B)
+        wg = gemm(A, B.t().contiguous(), b_mn=True, out_dtype=torch.float32)
+    finally:
+        G._DYNAMIC = old
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(out, ref) < 1e-2
+    assert torch.allclose(out.float(), ref, atol=0.05 * K ** 0.5, rtol=5e-2)
+    assert _rel(wg, ref) < 1e-4 * K ** 0.5
+
+
+def test_gemm_dynamic_schedule_with_part_of_the_gpu_held():
+    """Another stream holds 40 SMs for 0.2 s; the dynamic schedule finishes the product meanwhile."""
+    from megatron_lm_b200.ops import gemm as G
+    from megatron_lm_b200.ops.tp_fused import occupy_sms
+    torch.manual_seed(6)
+    A = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    old = G._DYNAMIC
+    G._DYNAMIC = True
+    try:
+        gemm(A, B)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        occupy_sms(40, 200 * 1024, 200000, side)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(4):
+            out = gemm(A, B)
+        e1.record()
+        torch.cuda.synchronize()
+    finally:
+        G._DYNAMIC = old
+    _lib.check_status()
+    assert e0.elapsed_time(e1) < 100.0, e0.elapsed_time(e1)
+    assert _rel(out, ref) < 1e-2
+
+
 def test_gemm_fp32_out_and_accumulate():
     torch.manual_seed(1)
     M, N, K = 512, 768, 320

@@ -60,8 +60,54 @@ def test_fused_kernels_2gpu(rows, K, N):
 
 
 @pytest.mark.skipif(_n_gpus() < 4, reason="needs 4 GPUs")
-def test_fused_kernels_4gpu():
-    run_on_gpus(_kernels, 4, 256, 1024, 1024)
+@pytest.mark.parametrize("rows,K,N", [(256, 1024, 1024), (1024, 4096, 1024), (1024, 2752, 4096)])
+def test_fused_kernels_4gpu(rows, K, N):
+    # 256-row multiples per rank: the CTA-pair kernel in both communication modes at tp 4
+    run_on_gpus(_kernels, 4, rows, K, N)
+
+
+def _kernels_partly_resident(rank, world, rows, K, N):
+    """Part of the GPU is held by another stream's long-running kernel while the fused kernels run: with tiles
+    handed to running blocks only, they finish (correctly) long before the holder leaves."""
+    import torch.distributed as dist
+    from megatron_lm_b200.ops import _lib
+    from megatron_lm_b200.ops.tp_fused import FusedTP, occupy_sms
+    f = FusedTP(dist.group.WORLD, rows, max(K, N), max(K, N))
+    assert f.sched is not None
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(3)
+    W = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+    torch.manual_seed(50 + rank)
+    x = torch.randn(rows, K, device=dev).to(torch.bfloat16)
+    A = torch.randn(world * rows, K, device=dev).to(torch.bfloat16)
+    full = torch.empty(world * rows, K, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(full, x)
+    ref_full = A.float() @ W.float().t()
+    dist.all_reduce(ref_full)
+    f.ag_gemm(x, W); f.gemm_rs(A, W)                       # warm-up (module load, first-touch)
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream()
+    hold_us = 300000
+    # a different number of held SMs on every rank, each too full of shared memory to take a GEMM block
+    occupy_sms(24 + 20 * rank, 200 * 1024, hold_us, side)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        y, gathered = f.ag_gemm(x, W)
+        out = f.gemm_rs(A, W)
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert e0.elapsed_time(e1) < hold_us / 1e3 * 0.5, e0.elapsed_time(e1)      # did not wait for the holders
+    assert torch.equal(gathered, full)
+    assert _rel(y, full.float() @ W.float().t()) < 1e-2
+    assert _rel(out, ref_full[rank * rows:(rank + 1) * rows]) < 1.5e-2
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs 2 GPUs")
+def test_fused_kernels_with_part_of_the_gpu_held():
+    run_on_gpus(_kernels_partly_resident, min(_n_gpus(), 4), 1024, 2048, 2048)
 
 
 def _model(rank, world, fused, out_path):
