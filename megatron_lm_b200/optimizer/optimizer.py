@@ -248,8 +248,11 @@ class MixedPrecisionOptimizer:
         for st in self.states:
             if getattr(st.buf, "peer", None) is not None:
                 st.buf.peer_barrier()            # every rank's pushed weights have landed before the next forward
+        mine = {id(st.buf) for st in self.states}
         for chunk in self.model_chunks:
-            chunk.start_param_sync()
+            bufs = [b for b in chunk.buffers + chunk.expert_buffers if id(b) in mine]
+            chunk.mark_params_updated(bufs)
+            chunk.start_param_sync(buffers=bufs)
 
     def step(self):
         """Returns (update_successful, grad_norm, num_zeros_in_grad).  ``update_successful`` is

@@ -147,6 +147,8 @@ class BucketGroup:
         self.counts = {}
         self.grad_handle = None
         self.param_handle = None
+        # True from the optimizer step until this bucket's updated shards have been gathered
+        self.params_stale = False
         self.is_last_microbatch = True
         self.next_group: Optional["BucketGroup"] = None
 
@@ -216,27 +218,45 @@ class BucketGroup:
         self.ready.clear()
         self.counts.clear()
 
+    def gathers_params(self) -> bool:
+        buf = self.buf
+        # with peer-memory collectives the optimizer already stored the new weights into every rank
+        return buf.use_dist_opt and buf.dp_size > 1 and buf.peer is None
+
     def start_param_sync(self, force_sync: bool = False):
-        """All-gather the updated low-precision shard into the parameter buffer."""
+        """All-gather the updated low-precision shard into the parameter buffer (once per optimizer step)."""
         buf, b = self.buf, self.bucket
-        if not buf.use_dist_opt or buf.dp_size == 1:
+        if not self.gathers_params() or not self.params_stale:
             return
-        if buf.peer is not None:
-            return                               # the optimizer already stored the new weights into every rank
         if self.param_handle is not None:
+            if force_sync:
+                self.param_handle.wait()
+                self.param_handle = None
+                self.params_stale = False
             return
         s, e = buf.shard_range(b)
         async_op = buf.ddp_config.overlap_param_gather and not force_sync
         h = dist.all_gather_into_tensor(buf.param_data[b.start:b.end], buf.param_data[s:e], group=buf.dp_group,
                                         async_op=async_op)
-        self.param_handle = h if async_op else None
+        if async_op:
+            self.param_handle = h
+        else:
+            self.params_stale = False
 
     def finish_param_sync(self):
+        """Called before the bucket's weights are used.  Waits for the gather in flight, or runs it now when the
+        chain has not reached this bucket yet (a module used out of bucket order, evaluation right after a
+        step), then starts the next bucket's gather."""
         if self.param_handle is not None:
             self.param_handle.wait()
             self.param_handle = None
-            if self.next_group is not None:        # chain: the gather of the next bucket starts now
-                self.next_group.start_param_sync()
+            self.params_stale = False
+        elif self.params_stale:
+            self.start_param_sync(force_sync=True)
+        else:
+            return
+        if self.next_group is not None:            # chain: the gather of the next bucket starts now
+            self.next_group.start_param_sync()
 
 
 class DistributedDataParallel(nn.Module):
@@ -292,11 +312,16 @@ class DistributedDataParallel(nn.Module):
                 self.bucket_groups.append(bg)
                 for p in b.params:
                     self.param_to_group[p] = bg
-        # parameter gathers are chained in forward order = reverse bucket order
+        # parameter gathers are chained in forward order = reverse bucket order, inside each buffer (buffers belong
+        # to different optimizers and groups: a chain must not run from the dense weights into the expert weights)
+        self.groups_of_buffer: Dict[int, List[BucketGroup]] = {}
+        for bg in self.bucket_groups:
+            self.groups_of_buffer.setdefault(id(bg.buf), []).append(bg)
         if ddp_config.use_distributed_optimizer and ddp_config.overlap_param_gather:
-            ordered = list(reversed(self.bucket_groups))
-            for a, b in zip(ordered[:-1], ordered[1:]):
-                a.next_group = b
+            for groups in self.groups_of_buffer.values():
+                ordered = list(reversed(groups))
+                for a, b in zip(ordered[:-1], ordered[1:]):
+                    a.next_group = b
         self._install_hooks()
         self._fwd_hooks = []
         if ddp_config.use_distributed_optimizer and ddp_config.overlap_param_gather:
@@ -350,14 +375,30 @@ class DistributedDataParallel(nn.Module):
         for bg in self.bucket_groups:
             bg.finish_grad_sync()
 
-    def start_param_sync(self, *unused, force_sync: bool = False, force_dispatch: bool = False):
-        if self.ddp_config.overlap_param_gather and not force_sync:
-            # only the first (forward-order) bucket is dispatched; the rest chain from it
-            if self.bucket_groups:
-                self.bucket_groups[-1].start_param_sync()
-            return
-        for bg in self.bucket_groups:
-            bg.start_param_sync(force_sync=True)
+    def mark_params_updated(self, buffers=None):
+        """The optimizer has written new weights into its shards of ``buffers`` (default: all): the other ranks'
+        shards in this rank's parameter buffers are out of date until gathered."""
+        for buf in (buffers if buffers is not None else self.buffers + self.expert_buffers):
+            for bg in self.groups_of_buffer.get(id(buf), []):
+                if bg.gathers_params():
+                    bg.params_stale = True
+
+    def start_param_sync(self, *unused, force_sync: bool = False, force_dispatch: bool = False, buffers=None):
+        """Gather updated weights.  With ``overlap_param_gather`` only the first bucket (in forward order) of each
+        buffer is dispatched here; the forward pre-hooks wait for it and chain the rest.  ``force_sync`` gathers
+        everything now and waits (before a checkpoint or an evaluation)."""
+        for buf in (buffers if buffers is not None else self.buffers + self.expert_buffers):
+            groups = self.groups_of_buffer.get(id(buf), [])
+            if self.ddp_config.overlap_param_gather and not force_sync:
+                if groups:
+                    groups[-1].start_param_sync()
+            else:
+                for bg in groups:
+                    bg.start_param_sync(force_sync=True)
+
+    def force_param_sync(self):
+        """Every parameter buffer holds the current weights of all ranks when this returns."""
+        self.start_param_sync(force_sync=True)
 
     def scale_gradients(self, factor: float):
         for buf in self.buffers + self.expert_buffers:

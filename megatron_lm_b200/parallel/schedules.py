@@ -127,6 +127,20 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
     with ctx:
         output, loss_func = forward_step_func(data_iterator, model)
     num_tokens = torch.zeros((), dtype=torch.int64)
+    # Auxiliary losses (MoE load balance / z-loss, MTP) inject their gradient on whichever pipeline stage holds the
+    # layer, so their scale (loss scale, divided by the microbatch count) is set on every stage, not only where
+    # the main loss is formed (reference: pipeline_parallel/schedules.py:224-238).
+    if getattr(config, "num_moe_experts", None) or getattr(config, "mtp_num_layers", None):
+        dev = output.device if torch.is_tensor(output) else None
+        one = torch.ones(1, device=dev)
+        scale = config.grad_scale_func(one) if config.grad_scale_func is not None else one
+        scale = scale if config.calculate_per_token_loss else scale / num_microbatches
+        if getattr(config, "num_moe_experts", None):
+            from ..models.moe import MoEAuxLossAutoScaler
+            MoEAuxLossAutoScaler.set_loss_scale(scale)
+        if getattr(config, "mtp_num_layers", None):
+            from ..models.mtp import MTPLossAutoScaler
+            MTPLossAutoScaler.set_loss_scale(scale)
     if is_last_stage:
         if collect_non_loss_data:
             forward_data_store.append(loss_func(output, non_loss_data=True))
@@ -144,14 +158,6 @@ def forward_step(forward_step_func, data_iterator, model, num_microbatches, inpu
         forward_data_store.append(report)
         if config.grad_scale_func is not None:
             loss = config.grad_scale_func(loss)
-        # auxiliary losses (MoE balance, MTP) inject their gradient with this scale
-        from ..models.moe import MoEAuxLossAutoScaler
-        scale = config.grad_scale_func(torch.ones(1, device=loss.device)) if config.grad_scale_func is not None \
-            else torch.ones(1, device=loss.device)
-        MoEAuxLossAutoScaler.set_loss_scale(scale if config.calculate_per_token_loss else scale / num_microbatches)
-        if getattr(config, "mtp_num_layers", None):
-            from ..models.mtp import MTPLossAutoScaler
-            MTPLossAutoScaler.set_loss_scale(scale if config.calculate_per_token_loss else scale / num_microbatches)
         return loss, num_tokens
     return output, num_tokens
 

@@ -180,6 +180,39 @@ def generate_state_dict(args, model, optimizer, opt_param_scheduler, rng_state, 
     return sd
 
 
+# ----------------------------------------------------------------------------- torch (legacy layout) helpers
+def _dp_coords():
+    if not state.model_parallel_is_initialized():
+        return 0, 1
+    return (state.get_data_parallel_rank(with_context_parallel=True),
+            state.get_data_parallel_world_size(with_context_parallel=True))
+
+
+def _optimizer_is_dp_sharded(optimizer) -> bool:
+    opts = getattr(optimizer, "chained_optimizers", [optimizer])
+    return any(getattr(st, "sharded", False) for o in opts for st in getattr(o, "states", []))
+
+
+def _distrib_optim_name(model_file: str) -> str:
+    return os.path.join(os.path.dirname(model_file), f"distrib_optim_dp{_dp_coords()[0]:03d}.pt")
+
+
+def _strip_optimizer_tensors(opt_sd):
+    if isinstance(opt_sd, list):
+        return [_strip_optimizer_tensors(x) for x in opt_sd]
+    return {k: v for k, v in opt_sd.items() if k != "state"}
+
+
+def _writes_model_file() -> bool:
+    """One writer per file name: the file is named after (tp, pp, ep) ranks, so with expert parallelism every
+    expert-parallel rank of the first expert-data-parallel replica writes (its experts exist nowhere else)."""
+    if not state.model_parallel_is_initialized():
+        return True
+    if state.get_expert_model_parallel_world_size() > 1:
+        return state.get_expert_data_parallel_rank() == 0
+    return state.get_data_parallel_rank(with_context_parallel=True) == 0
+
+
 # ----------------------------------------------------------------------------- async worker
 class AsyncCallsQueue:
     """Runs checkpoint writes on a background thread; ``maybe_finalize`` is polled from the
@@ -300,6 +333,12 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
                     non_persistent: bool = False, ec_manager=None) -> Dict[str, float]:
     t0 = time.time()
     stats: Dict[str, float] = {}
+    # with overlapped parameter gathers the buffers hold the other ranks' new weights only once the next forward
+    # pass has walked through them: finish every gather before the weights are read
+    for chunk in model:
+        sync = getattr(chunk, "force_param_sync", None)
+        if sync is not None:
+            sync()
     if non_persistent and getattr(args, "non_persistent_ckpt_type", None) == "local":
         if ec_manager is None:
             raise RuntimeError("local non-persistent checkpoints need an ECCheckpointManager")
@@ -338,9 +377,17 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
     elif fmt == "torch":
         sd = generate_state_dict(args, model, optimizer, opt_param_scheduler, rng, iteration, False, rerun_state,
                                  num_floating_point_operations_so_far)
-        init = state.model_parallel_is_initialized()
-        if not init or state.get_data_parallel_rank(with_context_parallel=True) == 0:
-            name = get_checkpoint_name(save_dir, iteration)
+        name = get_checkpoint_name(save_dir, iteration)
+        opt_sd = sd.get("optimizer")
+        if opt_sd is not None and _optimizer_is_dp_sharded(optimizer):
+            # The distributed optimizer holds 1/dp of master weights and moments on every data-parallel rank, so
+            # every rank writes its own shard next to the model file (the reference gathers the shards to rank 0
+            # into distrib_optim.pt: megatron/training/checkpointing.py:520-560); the model file keeps the step
+            # count and the parameter groups only.
+            os.makedirs(os.path.dirname(name), exist_ok=True)
+            torch.save({"optimizer": opt_sd, "dp_size": _dp_coords()[1]}, _distrib_optim_name(name))
+            sd["optimizer"] = _strip_optimizer_tensors(opt_sd)
+        if _writes_model_file():
             os.makedirs(os.path.dirname(name), exist_ok=True)
             torch.save(sd, name)
         if dist.is_initialized():
@@ -417,7 +464,19 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Op
         for i, chunk in enumerate(model):
             _unwrap(chunk).load_state_dict(sd["model" if len(model) == 1 else f"model{i}"], strict=strict)
         if optimizer is not None and not no_optim and "optimizer" in sd:
-            optimizer.load_state_dict(sd["optimizer"])
+            opt_sd = sd["optimizer"]
+            if _optimizer_is_dp_sharded(optimizer):
+                shard_file = _distrib_optim_name(name)
+                if not os.path.isfile(shard_file):
+                    raise FileNotFoundError(
+                        f"{shard_file}: the distributed optimizer's shard of this data-parallel rank is missing "
+                        "(the torch format cannot change the data-parallel size; use --ckpt-format torch_dist)")
+                shard = torch.load(shard_file, map_location="cpu", weights_only=False)
+                if shard.get("dp_size") != _dp_coords()[1]:
+                    raise RuntimeError("torch-format optimizer shards were written with data-parallel size "
+                                       f"{shard.get('dp_size')}, this run has {_dp_coords()[1]}; use torch_dist")
+                opt_sd = shard["optimizer"]
+            optimizer.load_state_dict(opt_sd)
             if opt_param_scheduler is not None and "opt_param_scheduler" in sd:
                 opt_param_scheduler.load_state_dict(sd["opt_param_scheduler"])
         elif optimizer is not None:

@@ -220,6 +220,9 @@ def evaluate(forward_step_func, data_iterator, model, config, *, eval_iters: int
              seq_length: int, micro_batch_size: int) -> Dict[str, float]:
     """Forward-only passes averaged over ``eval_iters`` (reference: training.py:2413)."""
     for m in model:
+        sync = getattr(m, "force_param_sync", None)
+        if sync is not None:
+            sync()                       # evaluation must see this step's weights from every data-parallel rank
         m.eval()
     fb = get_forward_backward_func()
     totals: Dict[str, float] = {}

@@ -140,3 +140,36 @@ def test_legacy_torch_format_roundtrip(tmp_path):
     assert it == 4 and opt2.step_count == 3
     for (n, a), (_, b) in zip(model[0].module.named_parameters(), model2[0].module.named_parameters()):
         assert torch.equal(a, b), n
+
+
+def _torch_fmt_rank(rank, world, d, phase):
+    """Legacy (torch) layout with the distributed optimizer on two data-parallel ranks: every rank writes and
+    reads back *its own* shard of master weights and moments."""
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.training.checkpointing import load_checkpoint, save_checkpoint
+    state.initialize_model_parallel()
+    cfg, model, opt = _build(1, 1, True, reinit=(phase == "save"))
+    if phase == "save":
+        for st in opt.states:
+            assert st.sharded
+            st.exp_avg.copy_((rank + 2) * st.master)         # rank-dependent, so a mixed-up shard is noticed
+            st.exp_avg_sq.copy_((rank + 5) * st.master)
+        opt.step_count = 7
+        save_checkpoint(3, model, opt, None, _args(d, ckpt_format="torch"))
+        base = os.path.join(d, "iter_0000003", "mp_rank_00")
+        assert os.path.isfile(os.path.join(base, f"distrib_optim_dp{rank:03d}.pt"))
+    else:
+        it, _ = load_checkpoint(model, opt, None, _args(d, ckpt_format="torch"))
+        assert it == 3 and opt.step_count == 7
+        for st in opt.states:
+            st2_master = st.master.clone()
+            st.reload_master_from_params()                    # weights came from the model file
+            assert torch.allclose(st.master, st2_master)
+            assert torch.allclose(st.exp_avg, (rank + 2) * st.master)
+            assert torch.allclose(st.exp_avg_sq, (rank + 5) * st.master)
+
+
+def test_legacy_torch_format_with_distributed_optimizer(tmp_path):
+    d = str(tmp_path / "ckpt")
+    run_distributed(_torch_fmt_rank, 2, d, "save")
+    run_distributed(_torch_fmt_rank, 2, d, "load")

@@ -48,14 +48,16 @@ def test_gemm_pair_kernel_ragged_and_model_shapes(M, N, K, dynamic):
     try:
         for _ in range(2):                      # the second launch finds the schedule words back at zero
             out = gemm(A, B)
-        wg = gemm(A, B.t().contiguous(), b_mn=True, out_dtype=torch.float32)
+        # MN-major operands need their contiguous dim to be a multiple of 8
+        wg = gemm(A, B.t().contiguous(), b_mn=True, out_dtype=torch.float32) if N % 8 == 0 else None
     finally:
         G._DYNAMIC = old
     torch.cuda.synchronize()
     _lib.check_status()
     assert _rel(out, ref) < 1e-2
     assert torch.allclose(out.float(), ref, atol=0.05 * K ** 0.5, rtol=5e-2)
-    assert _rel(wg, ref) < 1e-4 * K ** 0.5
+    if wg is not None:
+        assert _rel(wg, ref) < 1e-4 * K ** 0.5
 
 
 def test_gemm_dynamic_schedule_with_part_of_the_gpu_held():
