@@ -109,6 +109,7 @@ class MixedPrecisionOptimizer:
         self.config = config
         self.model_chunks = list(model_chunks)
         self.sharded = config.use_distributed_optimizer
+        self.expert_only = expert is True
         self.step_count = 0
         self.groups: List[Tuple[float, float]] = []
 
@@ -192,10 +193,19 @@ class MixedPrecisionOptimizer:
                                       accumulate=True)
         total = self._norm_sq - self._excl_sq
         if state.model_parallel_is_initialized() and dist.is_initialized():
-            if state.get_group_size("mp") > 1:
-                dist.all_reduce(total, group=state.get_model_parallel_group())
-            if self.sharded and state.get_data_parallel_world_size(with_context_parallel=True) > 1:
-                dist.all_reduce(total, group=state.get_data_parallel_group(with_context_parallel=True))
+            if self.expert_only:
+                # expert parameters differ across expert-parallel ranks: their norm is summed over the expert
+                # model-parallel group (tp x ep x pp), and over the expert data-parallel group when sharded
+                # (reference: optimizer/clip_grads.py with the tp-ep-pp group of expert optimizers)
+                if state.get_group_size("tp_ep_pp") > 1:
+                    dist.all_reduce(total, group=state.get_expert_tensor_model_pipeline_parallel_group())
+                if self.sharded and state.get_expert_data_parallel_world_size() > 1:
+                    dist.all_reduce(total, group=state.get_expert_data_parallel_group())
+            else:
+                if state.get_group_size("mp") > 1:
+                    dist.all_reduce(total, group=state.get_model_parallel_group())
+                if self.sharded and state.get_data_parallel_world_size(with_context_parallel=True) > 1:
+                    dist.all_reduce(total, group=state.get_data_parallel_group(with_context_parallel=True))
         return total
 
     # -- step ---------------------------------------------------------------------

@@ -374,6 +374,13 @@ class DistributedDataParallel(nn.Module):
     def finish_grad_sync(self):
         for bg in self.bucket_groups:
             bg.finish_grad_sync()
+        # Peer-memory mode: the pulls read the other ranks' gradient buffers in place.  What follows a gradient
+        # sync (tensor-parallel all-reduce of sequence-parallel gradients with copy-back, tied-embedding
+        # all-reduce, per-token scaling) rewrites those buffers, so nobody may go on before every rank's pulls
+        # are done.
+        for buf in self.buffers + self.expert_buffers:
+            if buf.peer is not None and buf.peer["pulled"]:
+                buf.peer["hdl"].barrier()
 
     def mark_params_updated(self, buffers=None):
         """The optimizer has written new weights into its shards of ``buffers`` (default: all): the other ranks'

@@ -256,3 +256,64 @@ def test_moe_gpt_learns_and_tracks_aux_loss():
     assert losses[-1] < losses[0] - 0.5
     m = track_moe_metrics(1.0, 1)
     assert m["load_balancing_loss"] > 0 and m["z_loss"] > 0
+
+
+def _ep_training_rank(rank, world, ep, out_path):
+    """GPT with experts trained for a few steps with clipping active; returns losses and gradient norms."""
+    from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.training.training import setup_model_and_optimizer, train_step
+    from tests.model_utils import reinit_by_global_name
+    state.initialize_model_parallel(expert_model_parallel_size=ep)
+    cfg = _cfg(num_layers=2, num_moe_experts=4, moe_router_topk=2, expert_model_parallel_size=ep,
+               moe_ffn_hidden_size=32, moe_token_dispatcher_type="alltoall", moe_aux_loss_coeff=0.0,
+               use_cpu_initialization=True)
+    V, S, B, NMB = 64, 16, 2, 2
+
+    def provider(pre_process=True, post_process=True, vp_stage=None):
+        m = GPTModel(cfg, V, S, position_embedding_type="rope", share_embeddings_and_output_weights=False)
+        reinit_by_global_name(m, cfg, std=0.3)                # large weights: the clip coefficient is < 1
+        if ep > 1:
+            # the two expert-parallel ranks must hold different experts for the test to mean anything
+            with torch.no_grad():
+                for name, p in m.named_parameters():
+                    if not getattr(p, "allreduce", True):
+                        p.mul_(1.0 + 0.5 * state.get_expert_model_parallel_rank())
+        return m
+    model, opt, _ = setup_model_and_optimizer(
+        provider, cfg, OptimizerConfig(lr=1e-2, weight_decay=0.0, clip_grad=0.5),
+        DistributedDataParallelConfig(grad_reduce_in_fp32=True))
+    gen = torch.Generator().manual_seed(5)
+    data = torch.randint(0, V, (3, NMB * B, S + 1), generator=gen)
+    dp = state.get_data_parallel_world_size()
+    dpr = state.get_data_parallel_rank()
+    nmb = NMB // dp
+    out = []
+    for step in range(3):
+        rows = data[step][dpr * nmb * B:(dpr + 1) * nmb * B]
+
+        def it():
+            for i in range(nmb):
+                r = rows[i * B:(i + 1) * B]
+                yield r[:, :-1], r[:, 1:]
+
+        def fwd(itr, m):
+            tok, lab = next(itr)
+            o = m(tok, labels=lab)
+            return o, (lambda x: (x.float().mean(), {"lm loss": x.float().mean().detach()}))
+        l, _, gn, _ = train_step(fwd, it(), model, opt, None, cfg, num_microbatches=nmb, seq_length=S,
+                                 micro_batch_size=B)
+        out.append((float(l["lm loss"]), float(gn)))
+    torch.save(out, f"{out_path}.{rank}")
+
+
+def test_expert_parallel_grad_norm_is_global(tmp_path):
+    """Without the distributed optimizer the expert gradients' squared norm must still be summed over the
+    expert-parallel ranks: every rank then clips with the same coefficient and reports the same norm."""
+    p = str(tmp_path / "ep2")
+    run_distributed(_ep_training_rank, 2, 2, p)
+    a, b = torch.load(p + ".0"), torch.load(p + ".1")
+    for (la, ga), (lb, gb) in zip(a, b):
+        assert ga == pytest.approx(gb, rel=1e-6), (a, b)     # one global norm on both expert-parallel ranks
+    assert a[0][1] > 0.5                                       # clipping was active
