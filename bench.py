@@ -168,7 +168,7 @@ def run_ours(args):
         attention_dropout=0.0, bf16=True, params_dtype=torch.bfloat16, tensor_model_parallel_size=tp,
         pipeline_model_parallel_size=pp, virtual_pipeline_model_parallel_size=vpp, sequence_parallel=tp > 1,
         pipeline_dtype=torch.bfloat16, tp_comm_overlap=args.tp_comm_overlap and tp > 1, init_method_std=0.02,
-        overlap_p2p_comm=pp > 1, fp8=args.fp8, fp8_recipe="tensorwise" if args.fp8 else "delayed")
+        overlap_p2p_comm=pp > 1, fp8=args.fp8, fp8_recipe=(args.fp8_recipe if args.fp8 else "delayed"))
     if args.config == "gpt3-1.3b":
         cfg = TransformerConfig(normalization="LayerNorm", layernorm_epsilon=1e-5, gated_linear_unit=False,
                                 activation_func="gelu", add_bias_linear=True, **common)
@@ -310,7 +310,7 @@ def run_ours(args):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
             "higher_is_better": True, "scaling": "strong",
             "vs_baseline": (value / args.gpus / BASELINE_TOKENS_PER_SEC_PER_GPU) if BASELINE_TOKENS_PER_SEC_PER_GPU else None,
-            "dtype": "fp8" if args.fp8 else "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
+            "dtype": (("mxfp8" if args.fp8_recipe == "mxfp8" else "fp8") if args.fp8 else "bf16"), "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
             "tokens_per_sec_per_gpu": value / args.gpus,
             "model_tflops_per_gpu": fl / (dev_ms / args.steps / 1e3) / 1e12 / args.gpus,
             "config": {"model": names[1] if not args.layers
@@ -361,6 +361,8 @@ def main():
     ap.add_argument("--no-tp-comm-overlap", dest="tp_comm_overlap", action="store_false")
     ap.add_argument("--fp8", default=None, choices=["e4m3", "hybrid"],
                     help="FP8 variant: layer linears run FP8 GEMMs with per-tensor scales (reported as dtype fp8)")
+    ap.add_argument("--fp8-recipe", default="tensorwise", choices=["tensorwise", "mxfp8"],
+                    help="with --fp8: per-tensor current scaling, or block-scaled MXFP8 (1x32 blocks, E8M0 scales)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -27,6 +27,9 @@ namespace mlb {
 using namespace tc05;
 
 constexpr int kAttnThreads = 192;
+// backward kernels: warp 0 TMA, warp 1 MMA, warps 2-9 compute - two warps per TMEM lane quadrant, each taking
+// one half (32) of the 64 columns of a step, so eight warps instead of four hide the exp2 / TMEM-load latency
+constexpr int kAttnBwdThreads = 320;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -75,7 +78,16 @@ __device__ __forceinline__ void store_chunk_global(void* dst, const float (&v)[3
     d[q] = make_uint4(pack_lp(v[q * 8], v[q * 8 + 1], bf), pack_lp(v[q * 8 + 2], v[q * 8 + 3], bf),
                       pack_lp(v[q * 8 + 4], v[q * 8 + 5], bf), pack_lp(v[q * 8 + 6], v[q * 8 + 7], bf));
 }
-__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// half a row (32 values as 16 packed words, columns [32 half, 32 half + 32)) of a [rows x 64] K-major swizzled tile
+__device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int row, int half, const uint32_t (&w)[16]) {
+  uint8_t* base = tile + row * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 v = make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
+    *reinterpret_cast<uint4*>(base + (((half * 4 + c) ^ (row & 7)) << 4)) = v;
+  }
+}
 
 // K-major operand inside a [rows x D] tile stored as D/64 column chunks of [rows x 128 B]
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile, int kk, int chunk_bytes) {
@@ -309,7 +321,7 @@ __global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t
 
 // ============================================================================ backward: dQ
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const AttnParams p) {
@@ -343,7 +355,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(B(0), 1);
     mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
-    mbar_init(B(5), 1); mbar_init(B(6), 4); mbar_init(B(7), 4); mbar_init(B(8), 1);
+    mbar_init(B(5), 1); mbar_init(B(6), 8); mbar_init(B(7), 8); mbar_init(B(8), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -411,6 +423,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (n_kv > 0) {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                 // which 32 of a step's 64 key columns this warp takes
     const int row = quad * 32 + lane;
     const int qrow = s0 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
@@ -422,13 +435,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int n0 = t * BN;
       if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 27)) { ok = false; break; }
       fence_after_sync();
-      uint32_t w[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tS + lane_base + half * 32, rs);
-        tmem_ld32(tdP + lane_base + half * 32, rp);
-        tmem_wait_ld();
+      uint32_t w[16];
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS + lane_base + half * 32, rs);
+      tmem_ld32(tdP + lane_base + half * 32, rp);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(6));               // S / dP are in registers: the next step's products may start
+      // only tiles that touch the diagonal, the end of the keys or the end of the queries need per-element masks
+      const bool need_mask = (p.causal && (n0 + BN - 1 > s0 + p.off)) || (n0 + BN > p.sk) || (s0 + BM > p.sq);
+      if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
           float ds[2];
@@ -436,19 +453,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int e = 0; e < 2; ++e) {
             const int kv = n0 + half * 32 + 2 * c + e;
             const bool masked = (p.causal && kv > qrow + p.off) || kv >= p.sk || qrow >= p.sq;
-            const float pr = masked ? 0.f : fast_exp2(__uint_as_float(rs[2 * c + e]) * p.scale_log2 - lse2);
+            const float pr = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[2 * c + e]), p.scale_log2, -lse2));
             ds[e] = pr * (__uint_as_float(rp[2 * c + e]) - dlt) * p.scale;
           }
-          w[half * 16 + c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+          w[c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[2 * c]), p.scale_log2, -lse2));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[2 * c + 1]), p.scale_log2, -lse2));
+          w[c] = pack_lp(p0 * (__uint_as_float(rp[2 * c]) - dlt) * p.scale,
+                         p1 * (__uint_as_float(rp[2 * c + 1]) - dlt) * p.scale, p.lp_fmt);
         }
       }
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(B(6));
       if (t > 0) {
         if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 28)) { ok = false; break; }
       }
-      store_row_sw128(sdS, row, w);
+      store_half_row_sw128(sdS, row, half, w);
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(B(7));
@@ -458,7 +480,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       uint8_t* drow = reinterpret_cast<uint8_t*>(p.dq) +
                       2 * ((long)qrow * p.dq_s + (long)bb * p.dq_b + (long)g * p.dq_g + (long)j * p.dq_j);
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
+      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
         uint32_t o[32];
         tmem_ld32(tdQ + lane_base + c, o);
         tmem_wait_ld();
@@ -478,7 +500,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
 // ============================================================================ backward: dK, dV
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const AttnParams p) {
@@ -518,7 +540,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(B(0), 1);
     mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
-    mbar_init(B(5), 1); mbar_init(B(6), 4); mbar_init(B(7), 4); mbar_init(B(8), 1);
+    mbar_init(B(5), 1); mbar_init(B(6), 8); mbar_init(B(7), 8); mbar_init(B(8), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -591,8 +613,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (n_steps > 0) {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                 // which 32 of a step's 64 query columns this warp takes
     const int row = quad * 32 + lane;
-    const int ct = threadIdx.x - 64;                 // 0..127 among the compute threads
+    const int ct = threadIdx.x - 64;                 // 0..255 among the compute threads
     const int krow = n0 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     bool ok = true;
@@ -601,46 +624,58 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // stage this step's per-query statistics (64 lse2 + 64 delta) in shared memory
       {
         float* dst = sStat + (t & 1) * 128;
-        const int qi = q0 + (ct & 63);
-        const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
-        float v = 0.f;
-        if (qi < p.sq) v = (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
-        dst[ct] = v;
+        if (ct < 128) {
+          const int qi = q0 + (ct & 63);
+          const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
+          float v = 0.f;
+          if (qi < p.sq) v = (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
+          dst[ct] = v;
+        }
         bar_sync_compute();
       }
-      const float* stat = sStat + (t & 1) * 128;
+      const float* stat = sStat + (t & 1) * 128 + half * 32;
       if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 37)) { ok = false; break; }
       fence_after_sync();
-      uint32_t wp[32], wd[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tS + lane_base + half * 32, rs);
-        tmem_ld32(tdP + lane_base + half * 32, rp);
-        tmem_wait_ld();
+      uint32_t wp[16], wd[16];
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS + lane_base + half * 32, rs);
+      tmem_ld32(tdP + lane_base + half * 32, rp);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(6));
+      // per-element masks only where the step touches the diagonal or the ends of the sequences
+      const bool need_mask = (p.causal && (n0 + BM - 1 > q0 + p.off)) || (q0 + BN > p.sq) || (n0 + BM > p.sk);
+      if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
           float pr[2], ds[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = half * 32 + 2 * c + e;
-            const int qi = q0 + col;
+            const int col = 2 * c + e;
+            const int qi = q0 + half * 32 + col;
             const bool masked = (p.causal && krow > qi + p.off) || qi >= p.sq || krow >= p.sk;
-            pr[e] = masked ? 0.f : fast_exp2(__uint_as_float(rs[2 * c + e]) * p.scale_log2 - stat[col]);
-            ds[e] = pr[e] * (__uint_as_float(rp[2 * c + e]) - stat[64 + col]) * p.scale;
+            pr[e] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[col]), p.scale_log2, -stat[col]));
+            ds[e] = pr[e] * (__uint_as_float(rp[col]) - stat[64 + col]) * p.scale;
           }
-          wp[half * 16 + c] = pack_lp(pr[0], pr[1], p.lp_fmt);
-          wd[half * 16 + c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+          wp[c] = pack_lp(pr[0], pr[1], p.lp_fmt);
+          wd[c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[2 * c]), p.scale_log2, -stat[2 * c]));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[2 * c + 1]), p.scale_log2, -stat[2 * c + 1]));
+          wp[c] = pack_lp(p0, p1, p.lp_fmt);
+          wd[c] = pack_lp(p0 * (__uint_as_float(rp[2 * c]) - stat[64 + 2 * c]) * p.scale,
+                          p1 * (__uint_as_float(rp[2 * c + 1]) - stat[64 + 2 * c + 1]) * p.scale, p.lp_fmt);
         }
       }
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(B(6));
       if (t > 0) {
         if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
       }
-      store_row_sw128(sP, row, wp);
-      store_row_sw128(sdS, row, wd);
+      store_half_row_sw128(sP, row, half, wp);
+      store_half_row_sw128(sdS, row, half, wd);
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(B(7));
@@ -650,7 +685,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
       uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
+      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
         uint32_t o[32];
         float v[32];
         tmem_ld32(tdV + lane_base + c, o);
@@ -672,7 +707,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else {
     // no query can see this key tile: its gradients are zero
     const int ct = threadIdx.x - 64;
-    if (ct >= 0) {
+    if (ct >= 0 && ct < 128) {
       const int krow = n0 + ct;
       if (krow < p.sk) {
         uint4 z = make_uint4(0, 0, 0, 0);
@@ -778,11 +813,11 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     if (D == 128) {
       static bool set = false;
       if (!set) { if ((rc = set_smem(attn_bwd_dq_kernel<128>, smem))) return rc; set = true; }
-      attn_bwd_dq_kernel<128><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      attn_bwd_dq_kernel<128><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
     } else {
       static bool set = false;
       if (!set) { if ((rc = set_smem(attn_bwd_dq_kernel<64>, smem))) return rc; set = true; }
-      attn_bwd_dq_kernel<64><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      attn_bwd_dq_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
     }
     MLB_CHECK_LAUNCH();
   }
@@ -797,11 +832,11 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     if (D == 128) {
       static bool set = false;
       if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, smem))) return rc; set = true; }
-      attn_bwd_dkv_kernel<128><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      attn_bwd_dkv_kernel<128><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
     } else {
       static bool set = false;
       if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<64>, smem))) return rc; set = true; }
-      attn_bwd_dkv_kernel<64><<<grid, kAttnThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      attn_bwd_dkv_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
     }
     MLB_CHECK_LAUNCH();
   }

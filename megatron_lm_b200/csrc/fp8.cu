@@ -119,9 +119,96 @@ __global__ void mxfp8_col_kernel(const T* __restrict__ x, uint8_t* __restrict__ 
   sc[(size_t)rb * cols + c] = (uint8_t)(e + 127);
 }
 
+// Scale byte of (row r, K block kb) of a [rows, K] matrix in the "atom" layout the block-scaled GEMM copies to
+// tensor memory (gemm_mx.cu): atoms of 128 rows x 4 K blocks, 512 bytes each, row-block major.
+__device__ __forceinline__ size_t mx_sf_offset(int r, int kb, int kb4_per_row) {
+  return ((size_t)(r >> 7) * kb4_per_row + (kb >> 2)) * 512 + (size_t)(r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3);
+}
+__device__ __forceinline__ int e8m0_exponent_for(float amax, float fmax) {
+  if (!(amax > 0.f)) return -127;
+  int e = (int)ceilf(log2f(amax / fmax));
+  return max(-127, min(127, e));
+}
+
+// One pass over x [rows, cols] for both MXFP8 copies a training GEMM needs:
+//   q_row  [rows, cols] : 32-element blocks along the row share a scale (operand with `cols` as reduction dim)
+//   q_colT [cols, rows] : x transposed, 32-element blocks along the *source column* share a scale (operand with
+//                         `rows` as reduction dim: data gradient of a weight, both weight-gradient operands)
+// with their scales in the atom layout.  64 x 64 tile per block of 256 threads: threads 0..127 quantise the tile's
+// 128 row blocks, threads 128..255 its 128 column blocks.
+template <typename T>
+__global__ void mxfp8_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
+                                  uint8_t* __restrict__ q_colT, uint8_t* __restrict__ sf_col, int rows, int cols,
+                                  int e5m2) {
+  __shared__ float tile[64][65];
+  const float fmax = e5m2 ? 57344.f : 448.f;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  {
+    const int tr = threadIdx.x >> 2, tc = (threadIdx.x & 3) * 16;
+    float v[16];
+    if (r0 + tr < rows && c0 + tc < cols) {
+      load8(x + (size_t)(r0 + tr) * cols + c0 + tc, *reinterpret_cast<float(*)[8]>(v));
+      load8(x + (size_t)(r0 + tr) * cols + c0 + tc + 8, *reinterpret_cast<float(*)[8]>(v + 8));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tile[tr][tc + i] = v[i];
+  }
+  __syncthreads();
+  const int t = threadIdx.x & 127;
+  if (threadIdx.x < 128) {
+    if (q_row == nullptr) return;
+    const int lr = t >> 1, blk = t & 1;                 // row of the tile, which 32-column block
+    const int r = r0 + lr, c = c0 + blk * 32;
+    if (r >= rows || c >= cols) return;
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(tile[lr][blk * 32 + k]));
+    const int e = e8m0_exponent_for(m, fmax);
+    const float sc = exp2f((float)-e);
+    uint4 o[2]; uint8_t* b = reinterpret_cast<uint8_t*>(o);
+#pragma unroll
+    for (int k = 0; k < 32; ++k) b[k] = to_fp8(tile[lr][blk * 32 + k] * sc, e5m2);
+    uint4* dst = reinterpret_cast<uint4*>(q_row + (size_t)r * cols + c);
+    dst[0] = o[0]; dst[1] = o[1];
+    sf_row[mx_sf_offset(r, c >> 5, (cols + 127) >> 7)] = (uint8_t)(e + 127);
+  } else {
+    if (q_colT == nullptr) return;
+    const int lc = t & 63, blk = t >> 6;                // column of the tile, which 32-row block
+    const int c = c0 + lc, r = r0 + blk * 32;
+    if (c >= cols || r >= rows) return;
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(tile[blk * 32 + k][lc]));
+    const int e = e8m0_exponent_for(m, fmax);
+    const float sc = exp2f((float)-e);
+    uint4 o[2]; uint8_t* b = reinterpret_cast<uint8_t*>(o);
+#pragma unroll
+    for (int k = 0; k < 32; ++k) b[k] = to_fp8(tile[blk * 32 + k][lc] * sc, e5m2);
+    uint4* dst = reinterpret_cast<uint4*>(q_colT + (size_t)c * rows + r);
+    dst[0] = o[0]; dst[1] = o[1];
+    sf_col[mx_sf_offset(c, r >> 5, (rows + 127) >> 7)] = (uint8_t)(e + 127);
+  }
+}
+
 }  // namespace mlb
 
 using namespace mlb;
+
+// x [rows, cols] -> q_row [rows, cols] + sf_row and/or q_colT [cols, rows] + sf_col (either pair may be null);
+// rows and cols multiples of 32; the scale buffers hold mlb_mx_sf_bytes(rows, cols) resp. (cols, rows) bytes.
+MLB_API int mlb_mxfp8_quantize_dual(int dtype, const void* x, void* q_row, void* sf_row, void* q_colT, void* sf_col,
+                                    int rows, int cols, int e5m2, cudaStream_t st) {
+  if ((rows % 32) || (cols % 32)) return -3;
+  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+  MLB_DISPATCH_ACT(dtype, T, (mxfp8_dual_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)q_row, (uint8_t*)sf_row,
+                                                                        (uint8_t*)q_colT, (uint8_t*)sf_col, rows, cols,
+                                                                        e5m2)));
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
 
 // amax must be zeroed by the caller (or hold a running maximum to extend)
 MLB_API int mlb_amax(int dtype, const void* x, long n, float* amax, cudaStream_t st) {

@@ -22,6 +22,9 @@ _lib.register_signatures({
     "mlb_fp8_cast_transpose": "ipppppiiip",
     "mlb_mxfp8_quantize": "ipppiiip",
     "mlb_gemm_fp8": "iiplplpliipppiiipp",
+    "mlb_mxfp8_quantize_dual": "ippppp" "iiip",
+    "mlb_mx_sf_bytes": "ll",
+    "mlb_gemm_mx": "iiplpplppliipiiipp",
 })
 
 _TORCH_FP8 = {0: torch.float8_e4m3fn, 1: torch.float8_e5m2}
@@ -161,6 +164,141 @@ def mxfp8_dequantize(q: torch.Tensor, scales: torch.Tensor, along_rows: bool = T
     if along_rows:
         return (v.view(rows, cols // 32, 32) * s.unsqueeze(-1)).view(rows, cols)
     return (v.view(rows // 32, 32, cols) * s.unsqueeze(1)).view(rows, cols)
+
+
+# ----------------------------------------------------------------------------- MXFP8 training GEMMs
+def mx_sf_bytes(rows: int, k: int) -> int:
+    """Size of the scale buffer of a quantised [rows, k] operand: atoms of 128 rows x 128 K elements, 512 B each."""
+    return ((rows + 127) // 128) * ((k + 127) // 128) * 512
+
+
+def mx_sf_index(rows: int, k: int, device="cpu") -> torch.Tensor:
+    """[rows, k/32] int64: byte position of each (row, K block) scale in the atom layout the block-scaled GEMM
+    copies to tensor memory (``csrc/gemm_mx.cu``)."""
+    r = torch.arange(rows, device=device).unsqueeze(1)
+    kb = torch.arange(k // 32, device=device).unsqueeze(0)
+    kb4 = (k + 127) // 128
+    return ((r // 128) * kb4 + kb // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + kb % 4
+
+
+@dataclass
+class MxTensor:
+    """MXFP8 operand: ``data`` uint8 [rows, k] (K-major), ``sf`` uint8 scale bytes in the atom layout."""
+    data: torch.Tensor
+    sf: torch.Tensor
+    fmt: int
+
+    def dequantize(self) -> torch.Tensor:
+        rows, k = self.data.shape
+        e = self.sf.to("cpu")[mx_sf_index(rows, k)].float() - 127.0
+        v = self.data.to("cpu").view(_TORCH_FP8[self.fmt]).float().view(rows, k // 32, 32)
+        return (v * torch.exp2(e).unsqueeze(-1)).view(rows, k).to(self.data.device)
+
+
+def mxfp8_quantize_dual(x: torch.Tensor, fmt: int = 0, rowwise: bool = True, colwise: bool = True
+                        ) -> Tuple[Optional[MxTensor], Optional[MxTensor]]:
+    """One pass over ``x`` [rows, cols] -> (row-wise copy [rows, cols] scaled along cols, column-wise copy
+    transposed to [cols, rows] and scaled along rows).  The first feeds a GEMM that reduces over ``cols``, the
+    second one that reduces over ``rows`` (reference: the two usages of an MXFP8 tensor,
+    megatron/core/fp8_utils.py:459-485)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    rows, cols = x2.shape
+    if rows % 32 or cols % 32:
+        raise ValueError("MXFP8 blocks need both sizes to be multiples of 32")
+    dev = x.device
+    if not x2.is_cuda:
+        def one(m):      # m [R, K] float -> MxTensor, scaled along K
+            R, K = m.shape
+            blk = m.view(R, K // 32, 32)
+            amax = blk.abs().amax(dim=-1)
+            e = torch.where(amax > 0, torch.ceil(torch.log2(amax / _FMAX[fmt])),
+                            torch.full_like(amax, -127.0)).clamp(-127, 127)
+            q = (blk * torch.exp2(-e).unsqueeze(-1)).clamp(-_FMAX[fmt], _FMAX[fmt]).to(_TORCH_FP8[fmt]).view(torch.uint8)
+            sf = torch.zeros(mx_sf_bytes(R, K), dtype=torch.uint8)
+            sf[mx_sf_index(R, K).reshape(-1)] = (e + 127).to(torch.uint8).reshape(-1)
+            return MxTensor(q.view(R, K).contiguous(), sf, fmt)
+        xf = x2.float()
+        return (one(xf) if rowwise else None), (one(xf.t().contiguous()) if colwise else None)
+    x2 = x2.contiguous()
+    qr = sr = qc = sc = None
+    if rowwise:
+        qr = torch.empty(rows, cols, dtype=torch.uint8, device=dev)
+        sr = torch.zeros(mx_sf_bytes(rows, cols), dtype=torch.uint8, device=dev)
+    if colwise:
+        qc = torch.empty(cols, rows, dtype=torch.uint8, device=dev)
+        sc = torch.zeros(mx_sf_bytes(cols, rows), dtype=torch.uint8, device=dev)
+    _lib.check(_lib.lib().mlb_mxfp8_quantize_dual(_lib.dt(x2), x2.data_ptr(), _lib.ptr(qr), _lib.ptr(sr), _lib.ptr(qc),
+                                                  _lib.ptr(sc), rows, cols, fmt, _lib.stream()), "mxfp8 quantize")
+    return (MxTensor(qr, sr, fmt) if rowwise else None), (MxTensor(qc, sc, fmt) if colwise else None)
+
+
+def gemm_mx(a: MxTensor, b: MxTensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+            accumulate: bool = False, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M, K], b [N, K] MXFP8 -> a b^T (+ bias) as [M, N] on the block-scaled tensor-core path."""
+    M, K = a.data.shape
+    N = b.data.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.data.device)
+    if not a.data.is_cuda:
+        r = a.dequantize() @ b.dequantize().t()
+        if bias is not None:
+            r = r + bias.float()
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r.to(out.dtype))
+        return out
+    mode = 0 if out.dtype in (torch.bfloat16, torch.float16) else (2 if accumulate else 1)
+    if accumulate and mode == 0:
+        raise ValueError("accumulation needs an fp32 output")
+    lp = 0 if (out.dtype == torch.float16 or (bias is not None and bias.dtype == torch.float16)) else 1
+    st = _lib.status_word()
+    _lib.check(_lib.lib().mlb_gemm_mx(a.fmt, b.fmt, a.data.data_ptr(), a.data.stride(0), a.sf.data_ptr(),
+                                      b.data.data_ptr(), b.data.stride(0), b.sf.data_ptr(), out.data_ptr(),
+                                      out.stride(0), mode, lp, _lib.ptr(bias), M, N, K, st.data_ptr(), _lib.stream()),
+               "gemm_mx")
+    return out
+
+
+class _MxLinearFn(torch.autograd.Function):
+    """y = x W^T (+ bias) with MXFP8 operands (1 x 32 blocks, power-of-two scales): activations and weights e4m3,
+    gradients ``grad_fmt``.  Every tensor is quantised once into the two copies its GEMMs need."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, grad_fmt):
+        x2 = x.reshape(-1, x.shape[-1])
+        xr, xc = mxfp8_quantize_dual(x2, 0, colwise=weight.requires_grad)
+        wr, wc = mxfp8_quantize_dual(weight, 0, colwise=x.requires_grad)
+        y = gemm_mx(xr, wr, out_dtype=x.dtype, bias=None if bias is None else bias.to(x.dtype))
+        ctx.xc, ctx.wc = xc, wc
+        ctx.weight, ctx.bias, ctx.grad_fmt, ctx.x_shape, ctx.x_dtype = weight, bias, grad_fmt, x.shape, x.dtype
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        weight, bias = ctx.weight, ctx.bias
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dr, dc = mxfp8_quantize_dual(dy2, ctx.grad_fmt, rowwise=ctx.needs_input_grad[0], colwise=weight.requires_grad)
+        dx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            # dx [T, K] = dy [T, N] (W^T [K, N])^T: reduction over N
+            dx = gemm_mx(dr, ctx.wc, out_dtype=ctx.x_dtype).view(ctx.x_shape)
+        if weight.requires_grad:
+            # dW [N, K] = dy^T [N, T] (x^T [K, T])^T: reduction over tokens
+            if has_main_grad(weight) and weight.main_grad.dtype == torch.float32:
+                gemm_mx(dc, ctx.xc, out=weight.main_grad, accumulate=True)
+                notify_ready(weight)
+            else:
+                gw = deliver(weight, gemm_mx(dc, ctx.xc, out_dtype=torch.float32))
+        if bias is not None and bias.requires_grad:
+            gb = deliver(bias, dy2.float().sum(dim=0))
+        ctx.xc = ctx.wc = None
+        return dx, gw, gb, None
+
+
+def linear_mxfp8(x, weight, bias=None, fp8_format: str = "hybrid"):
+    """Drop-in linear with block-scaled FP8 GEMMs.  Token count and both feature sizes must be multiples of 32."""
+    return _MxLinearFn.apply(x, weight, bias, 1 if fp8_format == "hybrid" else 0)
 
 
 # ----------------------------------------------------------------------------- delayed scaling

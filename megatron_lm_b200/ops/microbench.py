@@ -67,6 +67,16 @@ def bench_gemm(a):
         _report("  wgrad form (A, B MN-major, fp32 accumulate)",
                 _time(lambda: gemm(At, Bt, a_mn=True, b_mn=True, out=o32, accumulate=True), a.iters, a.warmup), fl)
         _report("  torch.matmul (cuBLAS)", _time(lambda: torch.matmul(A, B.t(), out=out), a.iters, a.warmup), fl)
+    if a.fp8:
+        from . import fp8
+        qa, qb = fp8.quantize(A, 0, transpose=False), fp8.quantize(B, 0, transpose=False)
+        _report("  fp8 e4m3, per-tensor scales", _time(lambda: fp8.gemm_fp8(qa.data, 0, qa.scale_inv, qb.data, 0, qb.scale_inv,
+                                                                         out=out), a.iters, a.warmup), fl)
+        ma, _ = fp8.mxfp8_quantize_dual(A, colwise=False)
+        mb, _ = fp8.mxfp8_quantize_dual(B, colwise=False)
+        _report("  mxfp8 (1x32 block scales in the tensor core)", _time(lambda: fp8.gemm_mx(ma, mb, out=out), a.iters, a.warmup), fl)
+        _report("  mxfp8 dual quantiser (row-wise + transposed column-wise copy)",
+                _time(lambda: fp8.mxfp8_quantize_dual(A), a.iters, a.warmup), bytes_=A.numel() * 4)
 
 
 def bench_attention(a):
@@ -82,6 +92,25 @@ def bench_attention(a):
     do = torch.randn_like(o)
     _report("attention bwd", _time(lambda: attention_bwd_raw(q, k, v, o, do, lse, a.causal, scale), a.iters, a.warmup),
             2.5 * fl)
+    if a.library:
+        # same-box library bar: torch SDPA on the cuDNN backend (falls back to its flash backend), [b, h, s, d] views
+        import torch.nn.functional as F
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        ql = q.reshape(s, b, a.heads, d).permute(1, 2, 0, 3).detach().requires_grad_(True)
+        kl = k.unsqueeze(3).expand(s, b, ng, qpg, d).reshape(s, b, a.heads, d).permute(1, 2, 0, 3).detach().requires_grad_(True)
+        vl = v.unsqueeze(3).expand(s, b, ng, qpg, d).reshape(s, b, a.heads, d).permute(1, 2, 0, 3).detach().requires_grad_(True)
+        for name, be in (("cuDNN", SDPBackend.CUDNN_ATTENTION), ("flash", SDPBackend.FLASH_ATTENTION)):
+            try:
+                with sdpa_kernel([be]):
+                    f = lambda: F.scaled_dot_product_attention(ql, kl, vl, is_causal=bool(a.causal), scale=scale)
+                    out = f()
+                    _report(f"  torch SDPA ({name}) fwd", _time(f, a.iters, a.warmup), fl)
+                    gl = torch.randn_like(out)
+                    _report(f"  torch SDPA ({name}) bwd",
+                            _time(lambda: torch.autograd.grad(out, (ql, kl, vl), gl, retain_graph=True), a.iters, a.warmup),
+                            2.5 * fl)
+            except Exception as e:       # backend not built into this torch
+                print(f"  torch SDPA ({name}): unavailable ({type(e).__name__})", flush=True)
 
 
 def bench_norm(a):
@@ -162,9 +191,11 @@ def main(argv=None):
     sub = ap.add_subparsers(dest="op", required=True)
     g = sub.add_parser("gemm"); g.add_argument("--m", type=int, default=8192); g.add_argument("--n", type=int, default=8192)
     g.add_argument("--k", type=int, default=8192); g.add_argument("--all", action="store_true")
+    g.add_argument("--fp8", action="store_true", help="also time the per-tensor FP8 and the block-scaled MXFP8 kernels")
     t = sub.add_parser("attention"); t.add_argument("--seq", type=int, default=4096); t.add_argument("--batch", type=int, default=4)
     t.add_argument("--heads", type=int, default=32); t.add_argument("--groups", type=int, default=32)
     t.add_argument("--head-dim", type=int, default=128); t.add_argument("--causal", type=int, default=1)
+    t.add_argument("--library", action="store_true", help="also time torch SDPA (cuDNN / flash backends) on the same shapes")
     n = sub.add_parser("norm"); n.add_argument("--rows", type=int, default=32768); n.add_argument("--hidden", type=int, default=4096)
     d = sub.add_parser("adam"); d.add_argument("--numel", type=int, default=1 << 28)
     r = sub.add_parser("router"); r.add_argument("--tokens", type=int, default=1 << 20)

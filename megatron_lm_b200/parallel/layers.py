@@ -214,9 +214,17 @@ def _fp8_format(module, x, w) -> Optional[str]:
     if not fmt or not getattr(module, "fp8_eligible", True) or x.dtype not in (torch.bfloat16, torch.float16):
         return None
     tokens = x.numel() // x.shape[-1]
-    if tokens % 16 or w.shape[0] % 16 or w.shape[1] % 16:
+    need = 32 if getattr(module.config, "fp8_recipe", None) == "mxfp8" else 16
+    if tokens % need or w.shape[0] % need or w.shape[1] % need:
         return None
     return "hybrid" if fmt == "hybrid" else "e4m3"
+
+
+def _fp8_linear(module):
+    """The FP8 linear of the configured recipe: block-scaled MXFP8 (1 x 32 blocks, power-of-two scales in the
+    tensor core) or per-tensor current scaling."""
+    from ..ops.fp8 import linear_fp8, linear_mxfp8
+    return linear_mxfp8 if getattr(module.config, "fp8_recipe", None) == "mxfp8" else linear_fp8
 
 
 class ColumnParallelLinear(nn.Module):
@@ -266,7 +274,7 @@ class ColumnParallelLinear(nn.Module):
         b = self.bias if not self.skip_bias_add else None
         fmt = _fp8_format(self, x, w)
         if fmt is not None:
-            from ..ops.fp8 import linear_fp8
+            linear_fp8 = _fp8_linear(self)
             from .mappings import copy_to_tensor_model_parallel_region, gather_from_sequence_parallel_region
             if self.sequence_parallel:
                 inp = gather_from_sequence_parallel_region(x, True, self.tp_group)
@@ -330,7 +338,7 @@ class RowParallelLinear(nn.Module):
         red = "none" if self.tp_size == 1 else ("reduce_scatter" if self.sequence_parallel else "all_reduce")
         fmt = _fp8_format(self, x, self.weight)
         if fmt is not None:
-            from ..ops.fp8 import linear_fp8
+            linear_fp8 = _fp8_linear(self)
             from .mappings import reduce_from_tensor_model_parallel_region, reduce_scatter_to_sequence_parallel_region
             y = linear_fp8(x, self.weight, None, fmt)
             if red == "reduce_scatter":

@@ -130,3 +130,80 @@ def test_first_and_last_layers_can_stay_in_16_bits():
     assert F8.get_fp8_align_size("mxfp8") == 32 and F8.get_fp8_align_size("delayed") == 16
     t = torch.zeros(2, dtype=torch.float8_e4m3fn)
     assert F8.is_float8tensor(t) and not F8.is_float8tensor(torch.zeros(2))
+
+
+# ----------------------------------------------------------------------------- block-scaled (MXFP8) tensor-core GEMM
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+def _mx_ref(a, b):
+    return a.dequantize().float() @ b.dequantize().float().t()
+
+
+def test_mx_dual_quantiser_cpu_roundtrip():
+    from megatron_lm_b200.ops import fp8
+    torch.manual_seed(0)
+    x = torch.randn(96, 160) * 3
+    r, c = fp8.mxfp8_quantize_dual(x)
+    assert r.data.shape == (96, 160) and c.data.shape == (160, 96)
+    assert r.sf.numel() == fp8.mx_sf_bytes(96, 160) and c.sf.numel() == fp8.mx_sf_bytes(160, 96)
+    # e4m3 keeps 3 mantissa bits: relative error of a block-scaled value stays under 2^-3 of the block maximum
+    assert (r.dequantize() - x).abs().max() <= 0.0625 * x.abs().max()
+    assert (c.dequantize() - x.t()).abs().max() <= 0.0625 * x.abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(64, 128), (256, 384), (4096, 1024), (96, 160)])
+def test_mx_dual_quantiser_matches_cpu(rows, cols):
+    from megatron_lm_b200.ops import fp8
+    torch.manual_seed(1)
+    x = (torch.randn(rows, cols) * 2).to(torch.bfloat16)
+    rc, cc = fp8.mxfp8_quantize_dual(x)
+    rg, cg = fp8.mxfp8_quantize_dual(x.cuda())
+    assert torch.equal(rg.data.cpu(), rc.data) and torch.equal(cg.data.cpu(), cc.data)
+    idx_r = fp8.mx_sf_index(rows, cols).reshape(-1)
+    idx_c = fp8.mx_sf_index(cols, rows).reshape(-1)
+    assert torch.equal(rg.sf.cpu()[idx_r], rc.sf[idx_r]) and torch.equal(cg.sf.cpu()[idx_c], cc.sf[idx_c])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(256, 192, 128), (256, 384, 256), (512, 256, 512), (300, 200, 96), (1024, 1000, 4096),
+                                   (4096, 4096, 1024)])
+def test_mx_gemm_matches_dequantised_product(M, N, K):
+    """The tensor core applies the 1 x 32 scales itself: the result must equal the fp32 product of the dequantised
+    operands (same quantised inputs on both sides, so only accumulation order differs)."""
+    from megatron_lm_b200.ops import _lib, fp8
+    torch.manual_seed(2)
+    # rows with very different magnitudes, so a wrong scale byte (row or K-block mix-up) shows at once
+    A = (torch.randn(M, K, device="cuda") * torch.logspace(-2, 2, M, device="cuda").unsqueeze(1)).to(torch.bfloat16)
+    B = (torch.randn(N, K, device="cuda") * (1 + torch.arange(K, device="cuda") // 32 % 7).unsqueeze(0)).to(torch.bfloat16)
+    a, _ = fp8.mxfp8_quantize_dual(A, colwise=False)
+    b, _ = fp8.mxfp8_quantize_dual(B, colwise=False)
+    ref = _mx_ref(a, b)
+    out32 = fp8.gemm_mx(a, b, out_dtype=torch.float32)
+    out16 = fp8.gemm_mx(a, b, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(out32, ref) < 1e-5 * K ** 0.5
+    assert torch.allclose(out32, ref, rtol=1e-3, atol=1e-3 * ref.abs().max().item())
+    assert _rel(out16, ref) < 1e-2
+    acc = torch.ones(M, N, device="cuda")
+    fp8.gemm_mx(a, b, out=acc, accumulate=True)
+    assert _rel(acc, ref + 1) < 1e-5 * K ** 0.5
+
+
+@pytest.mark.gpu
+def test_mx_linear_gradients_close_to_bf16():
+    from megatron_lm_b200.ops import _lib, fp8
+    torch.manual_seed(3)
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.nn.Parameter(torch.randn(384, 256, device="cuda", dtype=torch.bfloat16) * 0.1)
+    y = fp8.linear_mxfp8(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(dy.float())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(y, yr) < 6e-2 and _rel(x.grad, xr.grad) < 8e-2 and _rel(w.grad, wr.grad) < 8e-2
