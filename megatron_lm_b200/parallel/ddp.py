@@ -269,6 +269,10 @@ class DistributedDataParallel(nn.Module):
         if ddp_config.bucket_size is None:
             ddp_config.bucket_size = max(40_000_000, 1_000_000 * dp)
         bucket_size = ddp_config.bucket_size if (ddp_config.overlap_grad_reduce or ddp_config.use_distributed_optimizer) else None
+        if getattr(ddp_config, "num_buckets", None):
+            # --ddp-num-buckets: a bucket count instead of a bucket size
+            total = sum(p.numel() for p in module.parameters() if p.requires_grad)
+            bucket_size = max(1, -(-total // int(ddp_config.num_buckets)))
         if disable_bucketing:
             bucket_size = None
         self.bucket_size = bucket_size

@@ -108,11 +108,27 @@ def build_pipeline_plan(num_microbatches: int, pp_size: int, pp_rank: int, num_m
 
 # ----------------------------------------------------------------------------- step helpers
 def deallocate_output_tensor(out, deallocate: bool = False):
-    """Free an activation's storage once it has been sent downstream; only its grad_fn is
-    needed for backward (reference: schedules.py:126)."""
+    """Drop an activation's data once it has been sent downstream: only its ``grad_fn`` is needed for this stage's
+    backward.  ``.data`` is swapped for a one-element tensor (the send keeps its own reference to the storage until
+    it completes); backward then goes through :func:`custom_backward`, which does not compare shapes
+    (reference: pipeline_parallel/schedules.py:126-143)."""
     if out is None or not deallocate:
         return
-    out.untyped_storage().resize_(0)
+    assert isinstance(out, torch.Tensor) and out._base is None, "only a stage output that is no view can be dropped"
+    out.data = torch.empty((1,), device=out.device, dtype=out.dtype)
+
+
+def custom_backward(output: torch.Tensor, grad_output: Optional[torch.Tensor]) -> None:
+    """Run the autograd engine from ``output`` with ``grad_output`` without the shape check of
+    ``torch.autograd.backward`` - the output's data has been dropped by :func:`deallocate_output_tensor`
+    (reference: pipeline_parallel/schedules.py:146-176)."""
+    assert output.numel() == 1, "custom_backward is for outputs whose data was dropped"
+    if grad_output is None:
+        grad_output = torch.ones_like(output, memory_format=torch.preserve_format)
+    from torch.autograd import Variable
+    Variable._execution_engine.run_backward(tensors=(output,), grad_tensors=(grad_output,), keep_graph=False,
+                                            create_graph=False, inputs=tuple(), allow_unreachable=True,
+                                            accumulate_grad=True)
 
 
 def forward_step(forward_step_func, data_iterator, model, num_microbatches, input_tensor, forward_data_store,
@@ -168,12 +184,25 @@ def backward_step(input_tensor, output_tensor, output_tensor_grad, config):
         input_tensor.retain_grad()
     if output_tensor_grad is None:
         torch.autograd.backward(output_tensor)
+    elif config.deallocate_pipeline_outputs and output_tensor.numel() == 1 and output_tensor_grad.numel() != 1:
+        custom_backward(output_tensor, output_tensor_grad)
     else:
         torch.autograd.backward(output_tensor, output_tensor_grad)
     g = None
     if input_tensor is not None:
         g = input_tensor.grad
     return g
+
+
+def _call_chunk_hook(hook, chunk: int) -> None:
+    """``hook`` is None, one callable (single chunk) or a list with one callable per model chunk."""
+    if hook is None:
+        return
+    if isinstance(hook, (list, tuple)):
+        if chunk < len(hook) and hook[chunk] is not None:
+            hook[chunk]()
+    elif chunk == 0:
+        hook()
 
 
 def _as_list(x):
@@ -333,27 +362,31 @@ def forward_backward_pipelining(*, forward_step_func, data_iterator, model, num_
                                      config, collect_non_loss_data, is_last, st.microbatch, fwd_count[c] == 0)
             fwd_count[c] += 1
             total_tokens = total_tokens + ntok.to(total_tokens.device)
+            if fwd_count[c] == 1 and c + 1 < v:
+                # first microbatch of this chunk: start gathering the next chunk's updated weights behind it
+                _call_chunk_hook(config.param_sync_func, c + 1)
             if not is_last:
                 comm.send_forward(out)
             if not forward_only:
                 inputs[c].append((tensor_in, out))
-                if not is_last and config.deallocate_pipeline_outputs:
-                    pass   # the output is kept: its grad_fn owns the graph; storage is small next to activations
+                if not is_last:
+                    deallocate_output_tensor(out, config.deallocate_pipeline_outputs)
         else:
             tensor_in_f, out = inputs[c].pop(0)
             bwd_count[c] += 1
             # the last backward of a chunk is the one that syncs that chunk's gradients
             if bwd_count[c] == num_microbatches:
                 exit_no_sync()
-                if config.grad_sync_func is not None and v > 1:
-                    pass
             grad_in = backward_step(tensor_in_f, out, tensor_in, config)
-            if bwd_count[c] == num_microbatches and sum(bwd_count) < num_microbatches * v:
-                enter_no_sync()
+            if bwd_count[c] == num_microbatches:
+                # this chunk's gradients are complete: launch whatever part of its data-parallel reduction the
+                # per-bucket triggers have not started yet, so it overlaps the other chunks' remaining backward
+                # passes (reference: pipeline_parallel/schedules.py:1106-1116)
+                _call_chunk_hook(config.grad_sync_func, c)
+                if sum(bwd_count) < num_microbatches * v:
+                    enter_no_sync()
             if not first_virtual(c):
                 comm.send_backward(grad_in)
-        if not config.overlap_p2p_comm:
-            pass
     comm.drain()
     exit_no_sync()
     if v > 1:

@@ -198,11 +198,192 @@ def validate_args(args, defaults: Optional[dict] = None):
         if args.world_size > 1 and not any(a in algo for a in ("Tree", "Ring", "CollnetDirect", "CollnetChain", "^NVLS")):
             raise ValueError("deterministic mode needs NCCL_ALGO set to a deterministic algorithm")
         torch.use_deterministic_algorithms(True, warn_only=True)
+    # aliases and derived values of flags that only rename or refine another setting
+    if getattr(args, "use_rotary_position_embeddings", False):
+        args.position_embedding_type = "rope"
+    if getattr(args, "grad_reduce_in_bf16", False):
+        args.accumulate_allreduce_grads_in_fp32 = False
+    for flag, field in (("decoder_first_pipeline_num_layers", "num_layers_in_first_pipeline_stage"),
+                        ("decoder_last_pipeline_num_layers", "num_layers_in_last_pipeline_stage")):
+        v = getattr(args, flag, None)
+        if v is not None:
+            if pp <= 1:
+                raise ValueError(f"--{flag.replace('_', '-')} needs pipeline parallelism")
+            setattr(args, field, v)
+    # sample-based learning-rate schedule
+    if getattr(args, "lr_decay_samples", None) is not None and args.lr_decay_iters is not None:
+        raise ValueError("give either --lr-decay-iters or --lr-decay-samples")
+    if getattr(args, "lr_warmup_samples", 0) and args.lr_warmup_iters not in (0, None):
+        raise ValueError("give either --lr-warmup-iters or --lr-warmup-samples")
+    check_unused_flags(args)
     args.padded_vocab_size = getattr(args, "padded_vocab_size", None)
     args.consumed_train_samples = 0
     args.consumed_valid_samples = 0
     args.iteration = 0
     return args
+
+
+# Flags of the reference's command line that this framework parses (so launch scripts carry over) but does not act
+# on.  "warn": setting it changes nothing that affects results; a warning says so.  "refuse": it would change
+# numerics, the parallel layout or what a checkpoint contains, so a run that asks for it stops instead of silently
+# training something else.  Every flag of the table in flag_table.py that no module reads must be listed here
+# (tests/test_arguments_and_utils.py enumerates them).
+_W, _R = "warn", "refuse"
+UNUSED_FLAGS = {
+    # kernel / implementation selectors whose one implementation here is always on
+    "transformer_impl": (_W, "one implementation: the native sm_100a kernels"),
+    "te_rng_tracker": (_W, "the native RNG tracker is always used"),
+    "use_flash_attn": (_W, "flash attention is the only attention kernel"),
+    "no_persist_layer_norm": (_W, "one norm kernel"),
+    "bias_swiglu_fusion": (_W, "SwiGLU is always a fused kernel"),
+    "deprecated_use_mcore_models": (_W, "deprecated in the reference"),
+    "use_legacy_models": (_R, "the legacy model classes are not built"),
+    "checkpoint_activations": (_R, "deprecated: use --recompute-granularity full --recompute-method uniform"),
+    "openai_gelu": (_R, "the tanh-approximated GELU variant is not built"),
+    "onnx_safe": (_W, "no ONNX export path"),
+    "nccl_all_reduce_for_prefill": (_W, "inference prefill uses the same collectives as training"),
+    "scatter_gather_tensors_in_pipeline": (_W, "pipeline transfers always carry the sequence-parallel shard"),
+    "lazy_mpu_init": (_R, "external model-parallel initialisation is not supported"),
+    "model_parallel_size": (_R, "old name of --tensor-model-parallel-size"),
+    "align_grad_reduce": (_W, "gradient reductions of pipeline stages are launched per chunk as they complete"),
+    "tp_comm_overlap_cfg": (_W, "the fused tensor-parallel kernels take no user-buffer configuration"),
+    "enable_experimental": (_W, "no experimental-API gate"),
+    "disable_mamba_mem_eff_path": (_W, "one Mamba forward path"),
+    "enable_msc": (_W, "the multi-storage client is not built; paths are local"),
+    "kitchen_config_file": (_R, "the Kitchen quantisation back end is not built"),
+    "kitchen_recipe_number": (_R, "the Kitchen quantisation back end is not built"),
+    # inference engine knobs read by the engines' own constructors, not from the training arguments
+    "inference_batch_times_seqlen_threshold": (_W, "inference uses no pipelined micro-batching threshold"),
+    "max_tokens_to_oom": (_W, "the engines size their buffers from the context they are given"),
+    "output_bert_embeddings": (_R, "BERT embedding extraction is not built"),
+    "bert_embedder_type": (_W, "only used with --output-bert-embeddings"),
+    "inference_max_batch_size": (_W, "pass max_requests to the engine"),
+    "inference_max_seq_length": (_W, "pass max_sequence_length to the engine"),
+    "inference_dynamic_batching": (_W, "choose DynamicInferenceEngine in the serving program"),
+    "inference_dynamic_batching_buffer_size_gb": (_W, "pass buffer_size_gb to DynamicInferenceContext"),
+    "inference_dynamic_batching_chunk_size": (_W, "pass chunk_size_tokens to DynamicInferenceContext"),
+    "inference_dynamic_batching_buffer_guaranteed_fraction": (_W, "pass it to DynamicInferenceContext"),
+    "inference_dynamic_batching_buffer_overflow_factor": (_W, "pass it to DynamicInferenceContext"),
+    "inference_dynamic_batching_max_requests_override": (_W, "pass it to DynamicInferenceContext"),
+    "inference_dynamic_batching_max_tokens_override": (_W, "pass it to DynamicInferenceContext"),
+    "inference_dynamic_batching_num_cuda_graphs": (_W, "the dynamic engine captures no graphs"),
+    # Retro / biencoder / vision programs that are not (fully) built
+    "retro_add_retriever": (_W, "pretrain_retro.py always builds the retriever"),
+    "retro_cyclic_train_iters": (_R, "cyclic Retro training is not built"),
+    "retro_attention_gate": (_R, "the Retro attention gate is fixed at 1"),
+    "decoder_num_layers": (_R, "encoder-decoder layer split flags are not wired; use --num-layers"),
+    "retriever_seq_length": (_W, "biencoder programs are not built"), "sample_rate": (_W, "biencoder programs are not built"),
+    "ict_head_size": (_R, "pretrain_ict is not built"), "biencoder_projection_dim": (_R, "pretrain_ict is not built"),
+    "biencoder_shared_query_context_model": (_R, "pretrain_ict is not built"), "ict_load": (_R, "pretrain_ict is not built"),
+    "bert_load": (_R, "pretrain_ict is not built"), "titles_data_path": (_R, "pretrain_ict is not built"),
+    "query_in_block_prob": (_W, "pretrain_ict is not built"), "use_one_sent_docs": (_W, "pretrain_ict is not built"),
+    "evidence_data_path": (_R, "pretrain_ict is not built"), "retriever_report_topk_accuracies": (_W, "pretrain_ict is not built"),
+    "retriever_score_scaling": (_W, "pretrain_ict is not built"), "block_data_path": (_R, "pretrain_ict is not built"),
+    "embedding_path": (_R, "pretrain_ict is not built"), "indexer_batch_size": (_W, "pretrain_ict is not built"),
+    "indexer_log_interval": (_W, "pretrain_ict is not built"),
+    "num_classes": (_W, "vision pre-training programs are not built"), "num_channels": (_W, "vision pre-training programs are not built"),
+    "classes_fraction": (_W, "vision pre-training programs are not built"),
+    "data_per_class_fraction": (_W, "vision pre-training programs are not built"),
+    "data_sharding": (_W, "vision pre-training programs are not built"), "head_lr_mult": (_W, "vision pre-training programs are not built"),
+    "vision_pretraining": (_R, "vision pre-training programs are not built"),
+    "vision_pretraining_type": (_W, "vision pre-training programs are not built"),
+    "vision_backbone_type": (_W, "vision pre-training programs are not built"),
+    "swin_backbone_type": (_W, "vision pre-training programs are not built"), "mask_type": (_W, "vision pre-training programs are not built"),
+    "mask_factor": (_W, "vision pre-training programs are not built"), "iter_per_epoch": (_W, "vision pre-training programs are not built"),
+    "dino_local_img_size": (_W, "vision pre-training programs are not built"),
+    "dino_local_crops_number": (_W, "vision pre-training programs are not built"),
+    "dino_head_hidden_size": (_W, "vision pre-training programs are not built"),
+    "dino_bottleneck_size": (_W, "vision pre-training programs are not built"),
+    "dino_freeze_last_layer": (_W, "vision pre-training programs are not built"),
+    "dino_norm_last_layer": (_W, "vision pre-training programs are not built"),
+    "dino_warmup_teacher_temp": (_W, "vision pre-training programs are not built"),
+    "dino_teacher_temp": (_W, "vision pre-training programs are not built"),
+    "dino_warmup_teacher_temp_epochs": (_W, "vision pre-training programs are not built"),
+    # resilience / logging services that run with fixed settings here
+    "disable_straggler_on_startup": (_W, "the straggler detector has no remote toggle"),
+    "straggler_ctrlr_port": (_W, "the straggler detector has no remote toggle"),
+    "straggler_minmax_count": (_W, "the straggler report lists every rank"),
+    "run_workload_inspector_server": (_W, "no workload-inspector server"),
+    "inprocess_monitor_thread_interval": (_W, "the restart wrapper polls once per step"),
+    "inprocess_monitor_process_interval": (_W, "the restart wrapper polls once per step"),
+    "inprocess_progress_watchdog_interval": (_W, "the restart wrapper polls once per step"),
+    "inprocess_heartbeat_interval": (_W, "the restart wrapper polls once per step"),
+    "inprocess_soft_timeout": (_W, "one timeout: --inprocess-barrier-timeout"),
+    "inprocess_hard_timeout": (_W, "one timeout: --inprocess-barrier-timeout"),
+    "inprocess_heartbeat_timeout": (_W, "one timeout: --inprocess-barrier-timeout"),
+    "inprocess_completion_timeout": (_W, "one timeout: --inprocess-barrier-timeout"),
+    "inprocess_last_call_wait": (_W, "no last-call phase"), "inprocess_termination_grace_time": (_W, "no external monitor process"),
+    "inprocess_granularity": (_W, "restarts are per rank"), "inprocess_active_world_size": (_R, "spare ranks are not built"),
+    "inprocess_empty_cuda_cache": (_W, "the cache is kept across attempts"),
+    "one_logger_project": (_W, "the one-logger adapter records locally"), "one_logger_run_name": (_W, "the one-logger adapter records locally"),
+    "one_logger_async": (_W, "the one-logger adapter records locally"), "app_tag_run_name": (_W, "the one-logger adapter records locally"),
+    "app_tag_run_version": (_W, "the one-logger adapter records locally"),
+    "calc_ft_timeouts": (_W, "heartbeat timeouts are fixed"),
+    "log_throughput": (_W, "throughput is part of every log line"),
+    "log_progress": (_W, "no progress.txt file"), "tensorboard_log_interval": (_W, "scalars are written every --log-interval"),
+    "log_memory_to_tensorboard": (_W, "memory is reported on the console (--log-memory-interval)"),
+    "result_rejected_tracker_filename": (_W, "rejections are reported on the console"),
+    "adlr_autoresume_interval": (_W, "no cluster auto-resume service"),
+    # checkpoint options
+    "save_retain_interval": (_W, "no checkpoint is deleted"),
+    "load_main_params_from_ckpt": (_R, "loading fp32 main parameters separately is not built"),
+    "non_persistent_local_ckpt_dir": (_W, "local checkpoints live in memory (erasure-coded), not in a directory"),
+    "non_persistent_local_ckpt_algo": (_W, "the in-memory checkpoint has one algorithm (erasure coding)"),
+    "use_checkpoint_args": (_R, "arguments are not read back from checkpoints"),
+    "use_mp_args_from_checkpoint_args": (_R, "arguments are not read back from checkpoints"),
+    "use_tokenizer_model_from_checkpoint_args": (_W, "arguments are not read back from checkpoints"),
+    "use_dist_ckpt_deprecated": (_W, "deprecated in the reference"), "dist_ckpt_format_deprecated": (_W, "deprecated in the reference"),
+    "use_persistent_ckpt_worker": (_W, "asynchronous saves use one background thread"),
+    "auto_detect_ckpt_format": (_W, "the format of a checkpoint is always detected at load"),
+    "ckpt_convert_format": (_R, "convert with python -m megatron_lm_b200.checkpoint.convert"),
+    "ckpt_convert_save": (_R, "convert with python -m megatron_lm_b200.checkpoint.convert"),
+    "ckpt_convert_update_legacy_dist_opt_format": (_R, "the legacy distributed-optimizer format is not read"),
+    "ckpt_fully_parallel_save_deprecated": (_W, "sharded saves are always spread over the data-parallel ranks"),
+    "ckpt_fully_parallel_save": (_W, "sharded saves are always spread over the data-parallel ranks"),
+    "ckpt_fully_parallel_load": (_W, "sharded loads read each piece once per data-parallel group"),
+    "ckpt_assume_constant_structure": (_W, "no save-plan cache"),
+    "load_model_opt_format": (_R, "ModelOpt checkpoints are not read"),
+    "torch_fsdp2_reshard_after_forward": (_W, "FSDP2 keeps its default resharding"),
+    "replication_jump": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
+    "replication_factor": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
+    "data_args_path": (_R, "give the data paths on the command line"), "per_split_data_args_path": (_R, "give the data paths on the command line"),
+    "moe_use_upcycling": (_R, "upcycle offline with models.upcycling"), "moe_upcycling_granularity": (_W, "upcycle offline with models.upcycling"),
+    "heterogeneous_layers_config_path": (_R, "build heterogeneous models through models.heterogeneous"),
+    "heterogeneous_layers_config_encoded_json": (_R, "build heterogeneous models through models.heterogeneous"),
+}
+
+
+def check_unused_flags(args, defaults: Optional[dict] = None) -> List[str]:
+    """Warn about (or refuse) every flag that was given a non-default value but that nothing here acts on.
+    Returns the warnings (also sent to ``warnings.warn``)."""
+    import warnings
+    if defaults is None:
+        defaults = _parser_defaults()
+    out = []
+    for dest, (kind, why) in UNUSED_FLAGS.items():
+        if not hasattr(args, dest):
+            continue
+        v = getattr(args, dest)
+        if v == defaults.get(dest) or (v in (None, False, [], 0) and defaults.get(dest) in (None, False, [], 0)):
+            continue
+        flag = "--" + dest.replace("_", "-")
+        if kind == _R:
+            raise ValueError(f"{flag} (= {v!r}) is not supported: {why}")
+        msg = f"{flag} (= {v!r}) has no effect here: {why}"
+        warnings.warn(msg)
+        out.append(msg)
+    return out
+
+
+_DEFAULTS_CACHE: Optional[dict] = None
+
+
+def _parser_defaults() -> dict:
+    global _DEFAULTS_CACHE
+    if _DEFAULTS_CACHE is None:
+        p = build_parser()
+        _DEFAULTS_CACHE = {a.dest: a.default for a in p._actions}
+    return _DEFAULTS_CACHE
 
 
 def _copy_fields(cls, args, overrides=None):
@@ -263,6 +444,7 @@ def ddp_config_from_args(args) -> DistributedDataParallelConfig:
     kw["average_in_collective"] = getattr(args, "ddp_average_in_collective", False)
     kw["pad_buckets_for_high_nccl_busbw"] = getattr(args, "ddp_pad_buckets_for_high_nccl_busbw", False)
     kw["peer_memory_collectives"] = getattr(args, "peer_memory_collectives", False)
+    kw["num_buckets"] = getattr(args, "ddp_num_buckets", None)
     if getattr(args, "cross_entropy_peer_exchange", False):
         import os
         os.environ["MLB_CE_PEER"] = "1"

@@ -411,6 +411,8 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Op
             raise SystemExit(f"no checkpoint found in {load_dir}")
         return 0, 0.0
     iteration, release = read_metadata(tracker)
+    if getattr(args, "ckpt_step", None) is not None:
+        iteration, release = int(args.ckpt_step), False          # --ckpt-step: a named iteration, not the latest
     base = get_checkpoint_name(load_dir, iteration, release, return_base_dir=True)
     if optimizer is not None and _is_fsdp_optimizer(optimizer):
         return _load_fsdp(model, optimizer, opt_param_scheduler, base, getattr(args, "no_load_optim", False),

@@ -199,6 +199,33 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
         _TIMERS.log(normalizer=args.log_interval)
 
 
+def argparse_namespace_copy(args, **overrides):
+    import copy
+    ns = copy.copy(args)
+    for k, v in overrides.items():
+        setattr(ns, k, v)
+    return ns
+
+
+def params_l2_norm(model) -> torch.Tensor:
+    """L2 norm of all parameters of the whole (model-parallel) model: tensor-parallel duplicates and tied copies
+    are counted once, the squares are summed over the model-parallel group (reference: training/utils.py
+    calc_params_l2_norm)."""
+    tp_rank = state.get_tensor_model_parallel_rank() if state.model_parallel_is_initialized() else 0
+    sq = None
+    for chunk in model:
+        for p in chunk.parameters():
+            if getattr(p, "shared", False) or not (getattr(p, "tensor_model_parallel", False) or tp_rank == 0):
+                continue
+            v = p.detach().float().pow(2).sum()
+            sq = v if sq is None else sq + v
+    if sq is None:
+        return torch.zeros(())
+    if dist.is_initialized() and state.model_parallel_is_initialized() and state.get_group_size("mp") > 1:
+        dist.all_reduce(sq, group=state.get_model_parallel_group())
+    return sq.sqrt()
+
+
 def _teardown_attempt():
     """Leave nothing of a failed attempt behind: parallel groups, process-wide globals, microbatch calculator."""
     try:
@@ -262,7 +289,9 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         lr_warmup_init=args.lr_warmup_init, weight_decay=args.weight_decay,
         start_weight_decay=args.start_weight_decay, end_weight_decay=args.end_weight_decay,
         weight_decay_incr_style=args.weight_decay_incr_style, lr_wsd_decay_style=args.lr_wsd_decay_style,
-        lr_wsd_decay_iters=args.lr_wsd_decay_iters)
+        lr_wsd_decay_iters=args.lr_wsd_decay_iters, lr_decay_samples=getattr(args, "lr_decay_samples", None),
+        lr_warmup_samples=getattr(args, "lr_warmup_samples", 0) or 0,
+        lr_wsd_decay_samples=getattr(args, "lr_wsd_decay_samples", None))
     install_callbacks(config, model, optimizer)
     if config.tp_comm_overlap and torch.cuda.is_available():
         from ..ops.tp_fused import attach_fused_tp
@@ -271,6 +300,11 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     if args.load is not None:
         iteration, flops_so_far = checkpointing.load_checkpoint(model, optimizer, scheduler, args)
         args.consumed_train_samples = iteration * args.global_batch_size
+    if iteration == 0 and getattr(args, "pretrained_checkpoint", None):
+        # nothing to resume from: start from the weights of a pre-trained checkpoint (no optimizer state, no
+        # iteration count), as --finetune does (reference: training/checkpointing.py load of pretrained_checkpoint)
+        ft = argparse_namespace_copy(args, finetune=True, no_load_optim=True, no_load_rng=True)
+        checkpointing.load_checkpoint(model, optimizer, scheduler, ft, load_dir=args.pretrained_checkpoint)
     timers("model-and-optimizer-setup").stop()
     ec_manager = None
     if getattr(args, "non_persistent_ckpt_type", None) == "local":
@@ -356,8 +390,20 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         prof.start()
     from ..utils.common import configure_nvtx_profiling, nvtx_range_pop, nvtx_range_push
     configure_nvtx_profiling(bool(getattr(args, "profile", False)))
+    skip_set = set(getattr(args, "iterations_to_skip", None) or [])
     while iteration < args.train_iters:
         checkpointing.maybe_finalize_async_save(blocking=False)
+        if (iteration + 1) in skip_set:
+            # --iterations-to-skip: the batches of the step are drawn (so the data order of later steps is
+            # unchanged) but no forward / backward / update happens (reference: training.py dummy_train_step)
+            if train_it is not None:
+                for _ in range(nmb):
+                    next(train_it)
+            iteration += 1
+            args.iteration = iteration
+            args.consumed_train_samples += args.global_batch_size
+            print_rank_0(f" iteration {iteration}: skipped on request")
+            continue
         if getattr(args, "profile", False) and iteration == args.profile_step_start and torch.cuda.is_available() \
                 and args.rank in (args.profile_ranks or [0]) and prof is None:
             torch.cuda.cudart().cudaProfilerStart()
@@ -403,6 +449,13 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             t_last = now
         else:
             elapsed = 0.0
+        if getattr(args, "train_sync_interval", None) and iteration % args.train_sync_interval == 0 \
+                and torch.cuda.is_available():
+            torch.cuda.synchronize()      # keeps the host from running far ahead of the device
+        if getattr(args, "empty_unused_memory_level", 0) and torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        if getattr(args, "log_params_norm", False) and iteration % args.log_interval == 0:
+            print_rank_last(f" iteration {iteration}: params norm: {float(params_l2_norm(model)):.4f}")
         lr = optimizer.param_groups[0]["lr"]
         training_log(loss_dict, total_loss, lr, iteration, float(optimizer.get_loss_scale()), skipped, grad_norm, zeros,
                      args, max(elapsed, 1e-9), config, args.global_batch_size * args.seq_length)

@@ -76,7 +76,8 @@ def get_optimizer_param_scheduler(optimizer, *, lr: float, min_lr: float = 0.0, 
                                   lr_warmup_fraction: Optional[float] = None, lr_warmup_init: float = 0.0,
                                   weight_decay: float = 0.01, start_weight_decay: Optional[float] = None,
                                   end_weight_decay: Optional[float] = None, weight_decay_incr_style: str = "constant",
-                                  lr_wsd_decay_style=None, lr_wsd_decay_iters=None, **kw) -> OptimizerParamScheduler:
+                                  lr_wsd_decay_style=None, lr_wsd_decay_iters=None, lr_decay_samples=None,
+                                  lr_warmup_samples: int = 0, lr_wsd_decay_samples=None, **kw) -> OptimizerParamScheduler:
     """Schedules are stepped in samples, so iteration counts are multiplied by the global batch
     (reference: training.py:1167-1221)."""
     decay_iters = lr_decay_iters or train_iters or 1
@@ -86,12 +87,19 @@ def get_optimizer_param_scheduler(optimizer, *, lr: float, min_lr: float = 0.0, 
         warm = int(lr_warmup_fraction * decay_steps)
     else:
         warm = lr_warmup_iters * global_batch_size
+    # sample-based forms of the same settings (--lr-decay-samples, --lr-warmup-samples, --lr-wsd-decay-samples)
+    if lr_decay_samples is not None:
+        decay_steps = lr_decay_samples
+    if lr_warmup_samples:
+        warm = lr_warmup_samples
+    wsd_steps = lr_wsd_decay_samples if lr_wsd_decay_samples is not None else \
+        (lr_wsd_decay_iters * global_batch_size if lr_wsd_decay_iters else None)
     sw = weight_decay if start_weight_decay is None else start_weight_decay
     ew = weight_decay if end_weight_decay is None else end_weight_decay
     return OptimizerParamScheduler(optimizer, init_lr=lr_warmup_init, max_lr=lr, min_lr=min_lr, lr_warmup_steps=warm,
                                    lr_decay_steps=decay_steps, lr_decay_style=lr_decay_style, start_wd=sw, end_wd=ew,
                                    wd_incr_steps=wd_steps, wd_incr_style=weight_decay_incr_style,
-                                   wsd_decay_steps=(lr_wsd_decay_iters * global_batch_size if lr_wsd_decay_iters else None),
+                                   wsd_decay_steps=wsd_steps,
                                    lr_wsd_decay_style=lr_wsd_decay_style, use_checkpoint_opt_param_scheduler=False)
 
 

@@ -64,14 +64,21 @@ def forward_step(data_iterator, model):
 
 def train_valid_test_datasets_provider(num_samples):
     args = get_args()
-    blend = None
-    if args.data_path:
-        paths = args.data_path
+    def as_blend(paths):
+        if not paths:
+            return None
         if len(paths) == 1:
-            blend = ([paths[0]], None)
-        else:
-            blend = ([paths[i] for i in range(1, len(paths), 2)], [float(paths[i]) for i in range(0, len(paths), 2)])
-    cfg = GPTDatasetConfig(random_seed=args.seed, sequence_length=args.seq_length, blend=blend, split=args.split,
+            return ([paths[0]], None)
+        return ([paths[i] for i in range(1, len(paths), 2)], [float(paths[i]) for i in range(0, len(paths), 2)])
+    blend = as_blend(args.data_path)
+    # --train-data-path / --valid-data-path / --test-data-path: one corpus (or blend) per split instead of one
+    # corpus cut by --split
+    per_split = [as_blend(getattr(args, k, None)) for k in ("train_data_path", "valid_data_path", "test_data_path")]
+    per_split = per_split if any(b is not None for b in per_split) else None
+    if per_split is not None:
+        blend = None
+    cfg = GPTDatasetConfig(random_seed=args.seed, sequence_length=args.seq_length, blend=blend,
+                           blend_per_split=per_split, split=None if per_split is not None else args.split,
                            path_to_cache=args.data_cache_path, mmap_bin_files=args.mmap_bin_files, mock=args.mock_data,
                            tokenizer=args.tokenizer, reset_position_ids=args.reset_position_ids,
                            reset_attention_mask=args.reset_attention_mask, eod_mask_loss=args.eod_mask_loss,

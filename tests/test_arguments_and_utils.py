@@ -242,3 +242,84 @@ def test_logging_setup_filters_quiet_loggers(capsys):
         assert h.filter(mk("megatron_lm_b200.training")) and not h.filter(mk("torch.distributed.elastic"))
     finally:
         root.handlers[:] = before
+
+
+# ----------------------------------------------------------------------------- flags that nothing acts on
+def _flags_nobody_reads():
+    """Destinations of the flag table that appear nowhere in the package sources (the table of unused flags in
+    arguments.py itself is cut out of the scan)."""
+    import os
+    import re
+    from megatron_lm_b200.training.flag_table import FLAGS
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    texts = []
+    for base, _, files in os.walk(os.path.join(root, "megatron_lm_b200")):
+        for f in files:
+            if not f.endswith(".py") or f == "flag_table.py":
+                continue
+            t = open(os.path.join(base, f)).read()
+            if f == "arguments.py":
+                a = t.index("UNUSED_FLAGS = {")
+                t = t[:a] + t[t.index("\n}\n", a):]
+            texts.append(t)
+    for f in os.listdir(root):
+        if f.startswith("pretrain_") and f.endswith(".py"):
+            texts.append(open(os.path.join(root, f)).read())
+    text = "\n".join(texts)
+    out = set()
+    for _, flags, kw in FLAGS:
+        dest = kw.get("dest") or flags[0].lstrip("-").replace("-", "_")
+        if not re.search(r"\b" + re.escape(dest) + r"\b", text):
+            out.add(dest)
+    return out
+
+
+def test_every_flag_is_read_or_declared_unused():
+    from megatron_lm_b200.training.arguments import UNUSED_FLAGS
+    unread = _flags_nobody_reads()
+    assert unread - set(UNUSED_FLAGS) == set(), f"parsed but silently ignored: {sorted(unread - set(UNUSED_FLAGS))}"
+    assert set(UNUSED_FLAGS) - unread == set(), f"listed as unused but read somewhere: {sorted(set(UNUSED_FLAGS) - unread)}"
+    assert all(kind in ("warn", "refuse") and why for kind, why in UNUSED_FLAGS.values())
+
+
+def test_unused_flags_warn_or_refuse():
+    import warnings
+    from megatron_lm_b200.training.arguments import parse_args, validate_args
+    base = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "16",
+            "--max-position-embeddings", "16", "--micro-batch-size", "1", "--train-iters", "1", "--lr", "1e-3"]
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        args = parse_args(argv=base + ["--use-flash-attn", "--save-retain-interval", "10"])
+        args.world_size, args.rank = 1, 0
+        validate_args(args)
+    msgs = [str(x.message) for x in w]
+    assert any("--use-flash-attn" in m for m in msgs) and any("--save-retain-interval" in m for m in msgs)
+    # defaults do not warn
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        args = parse_args(argv=base)
+        args.world_size, args.rank = 1, 0
+        validate_args(args)
+    assert not [x for x in w if "has no effect here" in str(x.message)]
+    # a flag that would change the layout or the numerics stops the run
+    for extra in (["--use-legacy-models"], ["--openai-gelu"], ["--moe-use-upcycling"]):
+        args = parse_args(argv=base + extra)
+        args.world_size, args.rank = 1, 0
+        with pytest.raises(ValueError, match="not supported"):
+            validate_args(args)
+
+
+def test_renaming_flags_are_plumbed():
+    from megatron_lm_b200.training.arguments import (core_transformer_config_from_args, ddp_config_from_args, parse_args,
+                                                      validate_args)
+    base = ["--num-layers", "6", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "16",
+            "--max-position-embeddings", "16", "--micro-batch-size", "1", "--train-iters", "1", "--lr", "1e-3",
+            "--pipeline-model-parallel-size", "2", "--decoder-first-pipeline-num-layers", "2",
+            "--use-rotary-position-embeddings", "--bf16", "--grad-reduce-in-bf16", "--ddp-num-buckets", "3"]
+    args = parse_args(argv=base)
+    args.world_size, args.rank = 2, 0
+    validate_args(args)
+    cfg = core_transformer_config_from_args(args)
+    assert cfg.num_layers_in_first_pipeline_stage == 2 and args.position_embedding_type == "rope"
+    d = ddp_config_from_args(args)
+    assert d.grad_reduce_in_fp32 is False and d.num_buckets == 3

@@ -13,6 +13,10 @@ def _make_cfg(tp, pp, vpp, sp, kind):
     kw = dict(num_layers=4, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
               attention_dropout=0.0, tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
               virtual_pipeline_model_parallel_size=vpp, sequence_parallel=sp, use_cpu_initialization=True)
+    if kind == "llama-dealloc":
+        # stage outputs are dropped right after they are sent; backward runs from their grad_fn alone
+        kind = "llama"
+        kw.update(deallocate_pipeline_outputs=True)
     if kind == "moe":
         # a large balance-loss coefficient: a wrong scale of its gradient on an early stage moves the trajectory
         kw.update(normalization="RMSNorm", gated_linear_unit=True, activation_func="silu", add_bias_linear=False,
@@ -38,7 +42,7 @@ def _run(rank, world, tp, pp, vpp, sp, dist_opt, kind, out_path):
 
     def provider(pre_process=True, post_process=True, vp_stage=None):
         m = GPTModel(cfg, V, S, pre_process=pre_process, post_process=post_process, vp_stage=vp_stage,
-                     position_embedding_type="rope" if kind in ("llama", "moe") else "learned_absolute",
+                     position_embedding_type="rope" if kind in ("llama", "moe", "llama-dealloc") else "learned_absolute",
                      share_embeddings_and_output_weights=tied)
         reinit_by_global_name(m, cfg)
         if tied and post_process and not pre_process:
@@ -124,6 +128,10 @@ def test_pipeline_tied_embeddings_match(tmp_path, baseline):
 
 def test_interleaved_pipeline_matches(tmp_path, baseline):
     _close(_trajectory(tmp_path, 2, pp=2, vpp=2), baseline["llama"])
+
+
+def test_interleaved_pipeline_with_deallocated_outputs(tmp_path, baseline):
+    _close(_trajectory(tmp_path, 2, pp=2, vpp=2, kind="llama-dealloc"), baseline["llama"])
 
 
 def test_pipeline_parallel_moe_aux_loss_scale(tmp_path):
