@@ -71,6 +71,11 @@ def build_parser(extra_args_provider: Optional[Callable] = None) -> argparse.Arg
     g.add_argument("--ec-data-shards", type=int, default=None, help="k: data members per stripe (default group size - m)")
     g.add_argument("--ec-parity-shards", type=int, default=1, help="m: parity members per stripe (losses tolerated)")
     g.add_argument("--ec-chunk-bytes", type=int, default=1 << 20)
+    g.add_argument("--ec-group", default="auto", choices=["auto", "data-parallel", "world"],
+                   help="ranks that protect one another: the data-parallel group (replicas of one model shard), or "
+                        "every rank of the job - each rank's state is a stripe member whatever it holds, so tensor- and "
+                        "pipeline-parallel layouts without data parallelism are protected too.  auto: the data-parallel "
+                        "group when it has at least k + m ranks, else the world")
     g.add_argument("--ec-device", default="auto", choices=["auto", "gpu", "cpu"],
                    help="where parity is computed and held: peer GPUs' memory (auto on NCCL jobs) or host memory")
     g = parser.add_argument_group(title="peer-memory kernels")

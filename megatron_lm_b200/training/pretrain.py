@@ -199,6 +199,21 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
         _TIMERS.log(normalizer=args.log_interval)
 
 
+def ec_protection_group(args):
+    """The ranks whose states form the stripes of the erasure-coded in-memory checkpoint.  Members need not hold
+    replicas of anything: parity is computed over whatever bytes each rank contributes, so a tensor x pipeline
+    parallel job with a single data-parallel replica is protected by striping over the whole job."""
+    choice = getattr(args, "ec_group", "auto")
+    dp_group = state.get_data_parallel_group(with_context_parallel=True)
+    dp = dist.get_world_size(dp_group) if dist.is_initialized() and dp_group is not None else 1
+    m = args.ec_parity_shards
+    k = args.ec_data_shards
+    need = (k + m) if k is not None else (m + 1)
+    if choice == "data-parallel" or (choice == "auto" and dp >= max(need, 2)):
+        return dp_group
+    return dist.group.WORLD if dist.is_initialized() else dp_group
+
+
 def argparse_namespace_copy(args, **overrides):
     import copy
     ns = copy.copy(args)
@@ -308,7 +323,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     timers("model-and-optimizer-setup").stop()
     ec_manager = None
     if getattr(args, "non_persistent_ckpt_type", None) == "local":
-        grp = state.get_data_parallel_group(with_context_parallel=True)
+        grp = ec_protection_group(args)
         on_gpu = torch.cuda.is_available() and dist.get_backend(grp) == "nccl" and dist.get_world_size(grp) > 1
         if on_gpu and getattr(args, "ec_device", "auto") != "cpu":
             # parity computed by the peer-memory GF(2^8) kernel, parity held in the peers' HBM, host tier on a

@@ -63,6 +63,8 @@ def _save_lose_recover(rank, world, k, m, lost, chunk):
         assert torch.equal(a, b), f"rank {rank} did not get back its bytes"
 
 
-@pytest.mark.parametrize("world,k,m,lost", [(2, 2, 1, [1]), (4, 3, 1, [2]), (4, 2, 2, [0, 3]), (4, 2, 1, [1])])
+# the last case is the 8-rank Reed-Solomon k=6, m=2 layout with two ranks lost at once
+@pytest.mark.parametrize("world,k,m,lost", [(2, 2, 1, [1]), (4, 3, 1, [2]), (4, 2, 2, [0, 3]), (4, 2, 1, [1]),
+                                            (8, 6, 2, [2, 5])])
 def test_save_lose_recover_gloo(world, k, m, lost):
     run_distributed(_save_lose_recover, world, k, m, lost, 4096)

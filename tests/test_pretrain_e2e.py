@@ -307,3 +307,12 @@ def test_supervised_finetuning_program_on_a_conversation_file(tmp_path):
     rows = _iters(r.stdout)
     assert sorted(rows) == list(range(1, 9)) and rows[8][1] < rows[1][1]
     assert "supervised fine-tuning" in r.stdout and "validation loss at iteration 8" in r.stdout
+
+
+def test_erasure_coded_checkpoint_over_the_whole_job_without_data_parallelism():
+    """TP2 x PP2 on four ranks has one data-parallel replica: the in-memory checkpoint then stripes over all four
+    ranks (each contributes its own, different, state) with two parity members per stripe."""
+    out = _torchrun(4, 29653, ["--tensor-model-parallel-size", "2", "--pipeline-model-parallel-size", "2",
+                               "--global-batch-size", "2", "--non-persistent-ckpt-type", "local",
+                               "--non-persistent-save-interval", "2", "--ec-data-shards", "2", "--ec-parity-shards", "2"])
+    assert "in-memory erasure-coded checkpoint at iteration 2" in out
