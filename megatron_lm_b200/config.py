@@ -476,6 +476,8 @@ class DistributedDataParallelConfig:
     # gradient reduce-scatter and parameter all-gather of the distributed optimizer as peer-memory kernels (pull-
     # reduce fused with scaling and norm; AdamW storing its result into every rank's parameter buffer)
     peer_memory_collectives: bool = False
+    # thread blocks of one peer-memory gradient pull (it overlaps the backward pass, so it gets a small grid)
+    peer_pull_blocks: int = 64
     # --ddp-num-buckets: split each buffer into this many buckets (overrides bucket_size)
     num_buckets: Optional[int] = None
     fsdp_double_buffer: bool = False

@@ -128,10 +128,41 @@ __global__ void sumsq_final_kernel(const float* __restrict__ partial, int n, flo
 
 // Gradient reduce-scatter as a pull: out[i] = scale * sum_q src[q][i] over the data-parallel ranks' buffers (peer
 // loads), fused with the averaging scale and the sum of squares of the result (per-block partials).
+// With `flags` set the kernel first waits (bounded) until every peer has published, in this rank's flag words, that
+// its part of the bucket is complete for this step (flags[q] >= target): the pull can then be launched on a side
+// stream as soon as the *local* bucket is complete, while the backward pass goes on.
 struct PeerIn { const float* ptr[8]; int n; };
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
 __global__ void __launch_bounds__(kOptThreads)
-grad_pull_kernel(const PeerIn src, float* __restrict__ out, size_t n, float scale, float* __restrict__ partial) {
+grad_pull_kernel(const PeerIn src, float* __restrict__ out, size_t n, float scale, float* __restrict__ partial,
+                 const uint32_t* __restrict__ flags, int n_flags, uint32_t target, int* status) {
   __shared__ float sh[64];
+  __shared__ int give_up;
+  if (flags != nullptr) {
+    if (threadIdx.x == 0) {
+      give_up = 0;
+      const long long t0 = clock64();
+      for (int q = 0; q < n_flags && !give_up; ++q) {
+        uint32_t it = 0;
+        while ((int32_t)(ld_acquire_sys_u32(flags + q) - target) < 0) {
+          if ((++it & 63u) == 0u) {
+            // about twenty seconds: data-parallel ranks may be further apart than tensor-parallel ones
+            if (clock64() - t0 > 40000000000LL || (status && *reinterpret_cast<volatile int*>(status) != 0)) {
+              if (status) atomicCAS(status, 0, 61);
+              give_up = 1;
+              break;
+            }
+            __nanosleep(256);
+          }
+        }
+      }
+      __threadfence_system();
+    }
+    __syncthreads();
+    if (give_up) { if (threadIdx.x == 0) partial[blockIdx.x] = 0.f; return; }
+  }
   float acc = 0.f;
   const size_t nv = n >> 2;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
@@ -148,6 +179,13 @@ grad_pull_kernel(const PeerIn src, float* __restrict__ out, size_t n, float scal
   }
   acc = block_sum(acc, sh);
   if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+// one thread publishes `value` in a word of every peer (after everything earlier on the stream has completed)
+struct PeerFlags { uint32_t* ptr[8]; int n; };
+__global__ void peer_signal_kernel(const PeerFlags f, uint32_t value) {
+  __threadfence_system();
+  for (int q = 0; q < f.n; ++q) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.ptr[q]), "r"(value) : "memory");
 }
 
 template <typename T>
@@ -224,9 +262,38 @@ MLB_API int mlb_grad_pull(const void* const* src, int n_src, float* out, long n,
   pi.n = n_src;
   for (int i = 0; i < n_src; ++i) pi.ptr[i] = reinterpret_cast<const float*>(src[i]);
   const int parts = mlb_sumsq_parts();
-  grad_pull_kernel<<<parts, kOptThreads, 0, st>>>(pi, out, (size_t)n, scale, workspace);
+  grad_pull_kernel<<<parts, kOptThreads, 0, st>>>(pi, out, (size_t)n, scale, workspace, nullptr, 0, 0u, nullptr);
   MLB_CHECK_LAUNCH();
   if (sumsq_out) { sumsq_final_kernel<<<1, 256, 0, st>>>(workspace, parts, sumsq_out, accumulate); MLB_CHECK_LAUNCH(); }
+  return 0;
+}
+// The same pull behind a wait on `n_flags` local flag words (each >= target), on at most `max_blocks` blocks
+// (0 = the usual grid; a small grid leaves the SMs to the backward pass it overlaps).  workspace: fp32
+// [mlb_sumsq_parts()], private to the stream the call runs on.
+MLB_API int mlb_grad_pull_when_ready(const void* const* src, int n_src, float* out, long n, float scale,
+                                     float* workspace, const void* flags, int n_flags, unsigned target, int max_blocks,
+                                     int* status, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n_src < 1 || n_src > 8 || (n % 4) || n_flags < 0 || n_flags > 8) return -3;
+  PeerIn pi = {};
+  pi.n = n_src;
+  for (int i = 0; i < n_src; ++i) pi.ptr[i] = reinterpret_cast<const float*>(src[i]);
+  int parts = mlb_sumsq_parts();
+  if (max_blocks > 0 && max_blocks < parts) parts = max_blocks;
+  grad_pull_kernel<<<parts, kOptThreads, 0, st>>>(pi, out, (size_t)n, scale, workspace,
+                                                  reinterpret_cast<const uint32_t*>(flags), n_flags, target, status);
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+// *dst[q] = value for q < n (peer-mapped addresses of 32-bit words), ordered after all earlier work of the stream
+MLB_API int mlb_peer_signal(void* const* dst, int n, unsigned value, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n > 8) return -3;
+  PeerFlags f = {};
+  f.n = n;
+  for (int i = 0; i < n; ++i) f.ptr[i] = reinterpret_cast<uint32_t*>(dst[i]);
+  peer_signal_kernel<<<1, 1, 0, st>>>(f, value);
+  MLB_CHECK_LAUNCH();
   return 0;
 }
 MLB_API int mlb_sgd(int grad_dtype, float* p, float* mom, const void* g, void* p_lp, const void* chunks, int nchunks,

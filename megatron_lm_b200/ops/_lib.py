@@ -53,6 +53,8 @@ _SIGS: Dict[str, str] = {
     "mlb_adam": "ippppppi" "ppi" "fffff" "ppp",
     "mlb_adam_push": "pppppp" "i" "pi" "ppi" "fffff" "ppp",
     "mlb_grad_pull": "pipl" "f" "pp" "i" "p",
+    "mlb_grad_pull_when_ready": "pipl" "f" "p" "pi" "i" "i" "pp",
+    "mlb_peer_signal": "piip",
     "mlb_sgd": "ipppppi" "ppi" "fi" "ppp",
     "mlb_sumsq_parts": "",
     "mlb_sumsq": "iplppip",

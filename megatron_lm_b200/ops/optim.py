@@ -112,6 +112,25 @@ def grad_pull(src_addrs: Sequence[int], out: torch.Tensor, scale: float, sumsq: 
                                ws.data_ptr(), int(accumulate), _lib.stream()), "grad_pull")
 
 
+def grad_pull_when_ready(src_addrs: Sequence[int], out: torch.Tensor, scale: float, flags: torch.Tensor,
+                         target: int, max_blocks: int = 0, workspace_tag: str = "pull-side") -> None:
+    """:func:`grad_pull` behind an in-kernel wait until every word of ``flags`` (written by the peers) has reached
+    ``target``.  Meant for a side stream: it gets a workspace of its own."""
+    L = _lib.lib()
+    ws = workspace((L.mlb_sumsq_parts(),), torch.float32, workspace_tag, out.device)
+    arr = (ctypes.c_void_p * len(src_addrs))(*[int(a) for a in src_addrs])
+    st = _lib.status_word()
+    _lib.check(L.mlb_grad_pull_when_ready(arr, len(src_addrs), out.data_ptr(), out.numel(), float(scale), ws.data_ptr(),
+                                          flags.data_ptr(), flags.numel(), int(target) & 0xFFFFFFFF, int(max_blocks),
+                                          st.data_ptr(), _lib.stream()), "grad_pull")
+
+
+def peer_signal(dst_addrs: Sequence[int], value: int) -> None:
+    """Store ``value`` into the 32-bit word at each (peer-mapped) address, after all earlier work of the stream."""
+    arr = (ctypes.c_void_p * len(dst_addrs))(*[int(a) for a in dst_addrs])
+    _lib.check(_lib.lib().mlb_peer_signal(arr, len(dst_addrs), int(value) & 0xFFFFFFFF, _lib.stream()), "peer_signal")
+
+
 def sum_squares(x: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
     """fp32 1-element tensor with sum(x^2) (deterministic two-stage reduction)."""
     if out is None:

@@ -204,8 +204,12 @@ class MixedPrecisionOptimizer:
             else:
                 if state.get_group_size("mp") > 1:
                     dist.all_reduce(total, group=state.get_model_parallel_group())
-                if self.sharded and state.get_data_parallel_world_size(with_context_parallel=True) > 1:
-                    dist.all_reduce(total, group=state.get_data_parallel_group(with_context_parallel=True))
+                # shards live inside one optimizer instance (the whole data-parallel group unless several
+                # instances were asked for): other instances hold copies of the same shards
+                if self.sharded and state.get_data_parallel_world_size(with_context_parallel=True,
+                                                                       partial_data_parallel=True) > 1:
+                    dist.all_reduce(total, group=state.get_data_parallel_group(with_context_parallel=True,
+                                                                               partial_data_parallel=True))
         return total
 
     # -- step ---------------------------------------------------------------------

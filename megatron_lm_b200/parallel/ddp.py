@@ -49,11 +49,14 @@ class ParamAndGradBuffer:
 
     def __init__(self, ddp_config: DistributedDataParallelConfig, params: List[nn.Parameter], param_dtype,
                  grad_dtype, dp_group, dp_size: int, dp_rank: int, bucket_size: Optional[int],
-                 gradient_scaling_factor: float, is_expert: bool = False):
+                 gradient_scaling_factor: float, is_expert: bool = False, inter_group=None):
         self.ddp_config, self.param_dtype, self.grad_dtype = ddp_config, param_dtype, grad_dtype
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.gradient_scaling_factor = gradient_scaling_factor
         self.is_expert = is_expert
+        # several distributed-optimizer instances: dp_group is one instance (shards live inside it); the reduced
+        # shards are then summed across instances over inter_group
+        self.inter_group = inter_group
         self.use_dist_opt = ddp_config.use_distributed_optimizer
         pad_to = 1
         if self.use_dist_opt:
@@ -101,14 +104,20 @@ class ParamAndGradBuffer:
             import torch.distributed._symmetric_memory as symm_mem
             gbytes = self.numel * 4
             pbytes = _pad(self.numel * 2, 16)
-            raw = symm_mem.empty(gbytes + pbytes, dtype=torch.uint8, device=dev)
+            # one readiness word per (bucket, source rank): rank q stores the step number into word [b][q] of every
+            # peer once its bucket b holds this step's complete gradients
+            fbytes = _pad(len(self.buckets) * dp_size * 4, 16)
+            raw = symm_mem.empty(gbytes + pbytes + fbytes, dtype=torch.uint8, device=dev)
             raw.zero_()
             torch.cuda.synchronize()
             hdl = symm_mem.rendezvous(raw, dp_group)
             base = [int(x) for x in hdl.buffer_ptrs]
             self.grad_data = raw[:gbytes].view(torch.float32)
             self.param_data = raw[gbytes:gbytes + self.numel * 2].view(torch.bfloat16)
-            self.peer = {"raw": raw, "hdl": hdl, "grad": base, "param": [b + gbytes for b in base], "pulled": False}
+            self.peer = {"raw": raw, "hdl": hdl, "grad": base, "param": [b + gbytes for b in base], "pulled": False,
+                         "flags": raw[gbytes + pbytes:gbytes + pbytes + len(self.buckets) * dp_size * 4].view(torch.int32),
+                         "flag_addr": [b + gbytes + pbytes for b in base], "step": 0, "side": torch.cuda.Stream(),
+                         "pending": False}
         else:
             self.param_data = torch.zeros(self.numel, dtype=param_dtype, device=dev)
             self.grad_data = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
@@ -149,6 +158,7 @@ class BucketGroup:
         self.param_handle = None
         # True from the optimizer step until this bucket's updated shards have been gathered
         self.params_stale = False
+        self.pull_count = 0
         self.is_last_microbatch = True
         self.next_group: Optional["BucketGroup"] = None
 
@@ -183,7 +193,7 @@ class BucketGroup:
             if not torch.isfinite(g.float().sum()):
                 raise RuntimeError(f"non-finite gradient in bucket {b.index} before the data-parallel reduction")
         if buf.peer is not None:
-            # nothing leaves now: finish_grad_sync pulls this rank's shard from every peer (scaling included)
+            self._peer_pull()
             self.grad_handle = "peer"
             return
         if buf.gradient_scaling_factor != 1.0:
@@ -196,6 +206,7 @@ class BucketGroup:
         if buf.use_dist_opt:
             s, e = buf.shard_range(b)
             h = dist.reduce_scatter_tensor(buf.grad_data[s:e], g, op=op, group=buf.dp_group, async_op=async_op)
+            self.inter_pending = buf.inter_group is not None
         else:
             h = dist.all_reduce(g, op=op, group=buf.dp_group, async_op=async_op)
         self.grad_handle = h if async_op else True
@@ -204,16 +215,22 @@ class BucketGroup:
         if self.grad_handle is None:
             self.start_grad_sync()
         if self.grad_handle == "peer":
-            buf, b = self.buf, self.bucket
-            if not buf.peer["pulled"]:
-                buf.peer["hdl"].barrier()        # every rank has finished its backward pass
-                buf.peer["pulled"] = True
-            s, e = buf.shard_range(b)
-            scale = buf.gradient_scaling_factor * ((1.0 / buf.dp_size) if buf.ddp_config.average_in_collective else 1.0)
-            from ..ops.optim import grad_pull
-            grad_pull([base + 4 * s for base in buf.peer["grad"]], buf.grad_data[s:e], scale)
+            peer = self.buf.peer
+            if peer["pending"]:
+                # the pulls were launched bucket by bucket on the side stream while backward went on: join them
+                torch.cuda.current_stream().wait_stream(peer["side"])
+                peer["pending"] = False
+            peer["pulled"] = True
         elif self.grad_handle is not True and self.grad_handle is not None:
             self.grad_handle.wait()
+        if getattr(self, "inter_pending", False):
+            # second level: this rank's shard, reduced inside its optimizer instance, is summed across the
+            # instances (reference: param_and_grad_buffer.py:405-431)
+            buf, b = self.buf, self.bucket
+            s, e = buf.shard_range(b)
+            op = dist.ReduceOp.AVG if buf.ddp_config.average_in_collective else dist.ReduceOp.SUM
+            dist.all_reduce(buf.grad_data[s:e], op=op, group=buf.inter_group)
+            self.inter_pending = False
         self.grad_handle = None
         self.ready.clear()
         self.counts.clear()
@@ -222,6 +239,35 @@ class BucketGroup:
         buf = self.buf
         # with peer-memory collectives the optimizer already stored the new weights into every rank
         return buf.use_dist_opt and buf.dp_size > 1 and buf.peer is None
+
+    def _peer_pull(self):
+        """Reduce-scatter of this bucket over peer memory, started as soon as the *local* bucket is complete:
+        (1) a one-thread kernel on the compute stream tells every peer (a word per bucket and source rank in their
+        memory) that this rank's part holds the step's gradients; (2) the pull kernel goes to a side stream behind
+        an event, waits in the kernel for the peers' words and then sums the peers' slices of this rank's shard
+        (averaging scale fused) on a small grid, while the backward pass keeps the rest of the GPU
+        (reference behaviour it replaces: the bucket's asynchronous reduce-scatter,
+        megatron/core/distributed/param_and_grad_buffer.py:319-441)."""
+        from ..ops.optim import grad_pull_when_ready, peer_signal
+        buf, b = self.buf, self.bucket
+        peer = buf.peer
+        # every rank starts the pull of a bucket exactly once per step, so the count is the same on all of them
+        self.pull_count += 1
+        dp, me, step = buf.dp_size, buf.dp_rank, self.pull_count
+        word = 4 * (b.index * dp + me)
+        peer_signal([peer["flag_addr"][q] + word for q in range(dp) if q != me], step)
+        # this rank's own word is set on the host side of the same stream (no peer needs to see it)
+        peer["flags"][b.index * dp + me:b.index * dp + me + 1].fill_(step)
+        cur = torch.cuda.current_stream()
+        side = peer["side"]
+        side.wait_stream(cur)
+        s, e = buf.shard_range(b)
+        scale = buf.gradient_scaling_factor * ((1.0 / dp) if buf.ddp_config.average_in_collective else 1.0)
+        with torch.cuda.stream(side):
+            grad_pull_when_ready([base + 4 * s for base in peer["grad"]], buf.grad_data[s:e], scale,
+                                 peer["flags"][b.index * dp:(b.index + 1) * dp], step,
+                                 max_blocks=getattr(buf.ddp_config, "peer_pull_blocks", 64))
+        peer["pending"] = True
 
     def start_param_sync(self, force_sync: bool = False):
         """All-gather the updated low-precision shard into the parameter buffer (once per optimizer step)."""
@@ -306,7 +352,15 @@ class DistributedDataParallel(nn.Module):
                 else:
                     g = state.get_data_parallel_group(with_context_parallel=True) if init else None
                     n, r = dp, (state.get_data_parallel_rank(with_context_parallel=True) if init else 0)
-                buf = ParamAndGradBuffer(ddp_config, ps, pd, gd, g, n, r, bucket_size, scaling(n, is_expert), is_expert)
+                inter = None
+                if not is_expert and init and ddp_config.use_distributed_optimizer and \
+                        getattr(ddp_config, "num_distributed_optimizer_instances", 1) > 1:
+                    g = state.get_data_parallel_group(with_context_parallel=True, partial_data_parallel=True)
+                    n = state.get_data_parallel_world_size(with_context_parallel=True, partial_data_parallel=True)
+                    r = state.get_data_parallel_rank(with_context_parallel=True, partial_data_parallel=True)
+                    inter = state.get_inter_distributed_optimizer_instance_group()
+                buf = ParamAndGradBuffer(ddp_config, ps, pd, gd, g, n, r, bucket_size, scaling(n, is_expert), is_expert,
+                                         inter_group=inter)
                 (self.expert_buffers if is_expert else self.buffers).append(buf)
         self.bucket_groups: List[BucketGroup] = []
         self.param_to_group: Dict[nn.Parameter, BucketGroup] = {}

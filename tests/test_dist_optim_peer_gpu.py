@@ -8,7 +8,7 @@ from tests.gpu_dist_utils import run_on_gpus
 pytestmark = pytest.mark.gpu
 
 
-def _train(rank, world, peer, out_path):
+def _train(rank, world, peer, out_path, overlap=False):
     from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig, TransformerConfig
     from megatron_lm_b200.models.gpt import GPTModel
     from megatron_lm_b200.ops import _lib
@@ -27,7 +27,8 @@ def _train(rank, world, peer, out_path):
         reinit_by_global_name(m, cfg, std=0.02)
         return m
     dcfg = DistributedDataParallelConfig(grad_reduce_in_fp32=True, use_distributed_optimizer=True,
-                                         peer_memory_collectives=peer, bucket_size=200000)
+                                         peer_memory_collectives=peer, bucket_size=200000,
+                                         overlap_grad_reduce=overlap)
     model, opt, _ = setup_model_and_optimizer(provider, cfg, OptimizerConfig(lr=1e-3, clip_grad=1.0, bf16=True,
                                                                              use_distributed_optimizer=True), dcfg)
     assert (model[0].buffers[0].peer is not None) == peer
@@ -47,12 +48,15 @@ def _train(rank, world, peer, out_path):
                    out_path)
 
 
-def test_peer_collectives_match_nccl(tmp_path):
+@pytest.mark.parametrize("overlap", [False, True])
+def test_peer_collectives_match_nccl(tmp_path, overlap):
+    """``overlap``: every bucket's pull is launched on the side stream as soon as the bucket is complete locally and
+    waits in the kernel for the peers' readiness words, while the backward pass goes on."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     a, b = str(tmp_path / "nccl.pt"), str(tmp_path / "peer.pt")
-    run_on_gpus(_train, 2, False, a)
-    run_on_gpus(_train, 2, True, b)
+    run_on_gpus(_train, 2, False, a, overlap)
+    run_on_gpus(_train, 2, True, b, overlap)
     ra, rb = torch.load(a), torch.load(b)
     for (la, ga), (lb, gb) in zip(ra["losses"], rb["losses"]):
         assert abs(la - lb) < 2e-3 and abs(ga - gb) < 2e-3 * max(1.0, ga), (ra["losses"], rb["losses"])

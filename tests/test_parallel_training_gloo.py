@@ -208,3 +208,52 @@ def test_context_parallel_matches(tmp_path, baseline, comm):
     out = str(tmp_path / f"cp_{comm}.pt")
     run_distributed(_run_cp, 2, 2, comm, out)
     _close(torch.load(out), baseline["llama"])
+
+
+def _run_multi_instance(rank, world, instances, out_path):
+    """Distributed optimizer with several instances: reduce-scatter inside an instance, all-reduce across."""
+    from megatron_lm_b200.config import DistributedDataParallelConfig, OptimizerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.parallel import state
+    from megatron_lm_b200.training.training import setup_model_and_optimizer, train_step
+    from tests.model_utils import reinit_by_global_name
+    state.initialize_model_parallel(num_distributed_optimizer_instances=instances)
+    cfg = _make_cfg(1, 1, None, False, "llama")
+
+    def provider(pre_process=True, post_process=True, vp_stage=None):
+        m = GPTModel(cfg, V, S, position_embedding_type="rope")
+        reinit_by_global_name(m, cfg)
+        return m
+    model, opt, _ = setup_model_and_optimizer(
+        provider, cfg, OptimizerConfig(lr=5e-3, weight_decay=0.01, clip_grad=1.0, use_distributed_optimizer=True),
+        DistributedDataParallelConfig(grad_reduce_in_fp32=True, use_distributed_optimizer=True, overlap_grad_reduce=True,
+                                      num_distributed_optimizer_instances=instances, bucket_size=5000))
+    if instances > 1:
+        assert model[0].buffers[0].dp_size == world // instances and model[0].buffers[0].inter_group is not None
+    gen = torch.Generator().manual_seed(5)
+    data = torch.randint(0, V, (STEPS, NMB * B, S + 1), generator=gen)
+    nmb_local = NMB // world
+    losses = []
+    for step in range(STEPS):
+        rows = data[step][rank * nmb_local * B:(rank + 1) * nmb_local * B]
+
+        def gen_it():
+            for i in range(nmb_local):
+                r = rows[i * B:(i + 1) * B]
+                yield r[:, :-1], r[:, 1:]
+
+        def fwd(it, m):
+            tok, lab = next(it)
+            out = m(tok, labels=lab)
+            return out, (lambda o: (o.float().mean(), {"lm loss": o.float().mean().detach()}))
+        l, _, gnorm, _ = train_step(fwd, gen_it(), model, opt, None, cfg, num_microbatches=nmb_local, seq_length=S,
+                                    micro_batch_size=B)
+        losses.append((float(l["lm loss"]), float(gnorm)))
+    if rank == 0:
+        torch.save(losses, out_path)
+
+
+def test_two_distributed_optimizer_instances_match(tmp_path, baseline):
+    out = str(tmp_path / "inst2.pt")
+    run_distributed(_run_multi_instance, 4, 2, out)
+    _close(torch.load(out), baseline["llama"])
