@@ -56,6 +56,14 @@ struct GemmParams {
   // B holds all experts stacked: K-major [E * N, K] or MN-major [E * K, N].  Output rows outside the tile's range
   // are not written, so a short tile may read rows of the next expert without harm.
   const int4* group_tiles;    // device array [tiles_m], or null
+  const int* group_count;     // device scalar: number of valid records in group_tiles (tiles_m is then an upper
+                              // bound used to size the grid); null = all tiles_m records are valid
+  // Grouped weight gradient (one launch for all experts): dW_e [N_out, K_in] (=|+=) dy_e^T x_e, both operands
+  // MN-major views of [T, *] activations whose rows are sorted by expert.  Output row blocks are numbered
+  // e * wg_mblocks + i; the reduction of expert e runs over rows [group_offsets[e], group_offsets[e + 1]) in steps of
+  // BK, and the rows of the last step that belong to the next expert are zeroed in shared memory before the MMA.
+  const int* group_offsets;   // device int32 [E + 1], or null
+  int wg_mblocks;             // 128-row output blocks per expert (N_out / 128)
   int raster_m;               // row blocks per rasterisation group (plain mode)
 };
 
@@ -236,9 +244,15 @@ template <int BN> struct GemmSmem {
 template <int BN, bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p,
+            const __grid_constant__ CUtensorMap tmD, const __grid_constant__ ExtraMaps xm, const GemmParams p_in,
             const CommParams cp) {
   using S = GemmSmem<BN>;
+  GemmParams p = p_in;
+  if (p.group_count != nullptr) {                        // the number of row tiles is decided on the device
+    p.tiles_m = *p.group_count;
+    if (p.raster_m > p.tiles_m) p.raster_m = p.tiles_m > 0 ? p.tiles_m : 1;
+  }
+  const bool gw = p.group_offsets != nullptr;            // grouped weight gradient
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -246,14 +260,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* sB = smem + kStages * S::kABytes;
   uint8_t* sEpi = smem + kStages * (S::kABytes + S::kBBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + S::kEpiBytes);
-  // bars: full[kStages], empty[kStages], tfull[2], tempty[2]; then tmem slot + abort flag
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  // bars: full[kStages], empty[kStages], tfull[2], tempty[2], tail; then tmem slot + abort flag
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
   auto tempty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+  const uint32_t tail_bar = bar0 + 8u * (2 * kStages + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (cp.mode == COMM_AG && (int)blockIdx.x < cp.n_comm) {        // communication CTAs take no part in the GEMM
@@ -265,6 +280,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
+    mbar_init(tail_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
@@ -279,10 +295,63 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int num_tiles = p.tiles_m * p.tiles_n;
   constexpr int bk_elems = FP8 ? 2 * BK : BK;                        // elements per 128-byte row of a stage
   const int num_kb = (p.K + bk_elems - 1) / bk_elems;
+  // grouped weight gradient: reduction range of the expert that output row block m_blk belongs to
+  auto wg_range = [&](int m_blk, int& r0, int& r1) {
+    const int e = m_blk / p.wg_mblocks;
+    r0 = p.group_offsets[e]; r1 = p.group_offsets[e + 1];
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (gw) {
+      // Grouped weight gradient: the whole warp walks the tiles (lane 0 issues the copies); in an expert's last
+      // reduction step the rows that belong to the next expert are zeroed by all lanes before the stage is
+      // handed to the MMA warp.
+      int stage = 0; uint32_t phase = 0, tail_phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += n_cta) {
+        const TileCoord tc = map_tile(tile, p, cp);
+        const int n0 = tc.n_blk * BN;
+        const int a_col = (tc.m_blk % p.wg_mblocks) * BM;          // first output row of the block inside its expert
+        int r0, r1; wg_range(tc.m_blk, r0, r1);
+        const int nkb = (r1 - r0 + BK - 1) / BK;
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const int k0 = r0 + kb * BK;
+          const int valid = (r1 - k0) < BK ? (r1 - k0) : BK;       // rows of this step that belong to the expert
+          const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
+          int w_ok = 1;
+          if (lane == 0) {
+            w_ok = mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.status, 1) ? 1 : 0;
+            if (w_ok) {
+              const uint32_t bar = valid < BK ? tail_bar : full(stage);
+              mbar_expect_tx(bar, S::kABytes + S::kBBytes);
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, bar, a_col + 64 * j, k0);
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, bar, n0 + 64 * j, k0);
+              if (valid < BK) w_ok = mbar_wait(tail_bar, tail_phase, abort_flag, p.status, 9) ? 1 : 0;
+            }
+          }
+          w_ok = __shfl_sync(0xffffffffu, w_ok, 0);
+          if (!w_ok) { ok = false; break; }
+          if (valid < BK) {
+            tail_phase ^= 1u;
+            // every 64-element chunk of an MN-major tile is BK rows of 128 bytes: rows [valid, BK) are contiguous
+            const int n16 = (BK - valid) * 8;                      // 16-byte pieces to clear per chunk
+            for (int ch = 0; ch < BM / 64 + BN / 64; ++ch) {
+              uint8_t* base = (ch < BM / 64 ? sA + stage * S::kABytes + ch * 8192
+                                            : sB + stage * S::kBBytes + (ch - BM / 64) * 8192) + valid * 128;
+              for (int i = lane; i < n16; i += 32) reinterpret_cast<uint4*>(base)[i] = make_uint4(0, 0, 0, 0);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full(stage));
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && lane == 0) { const long long t0 = clock64(); while (clock64() - t0 < 2000000LL) { __nanosleep(1000); } }
+    } else if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       int ready_blk = -1;
@@ -343,7 +412,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int nkb = num_kb;
+        if (gw) { int r0, r1; wg_range(map_tile(tile, p, cp).m_blk, r0, r1); nkb = (r1 - r0 + BK - 1) / BK; }
+        for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
           fence_after_sync();
           const uint32_t a_addr = smem_u32(sA + stage * S::kABytes), b_addr = smem_u32(sB + stage * S::kBBytes);
@@ -377,6 +448,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (!mbar_wait(tfull(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       fence_after_sync();
       int row = m0 + quad * 32 + lane, row_end = p.M;
+      bool wg_empty = false;                     // expert without tokens: its gradient tile is zero (no MMA ran)
+      if (gw) { int r0, r1; wg_range(tc.m_blk, r0, r1); wg_empty = r1 <= r0; }
       if (p.group_tiles != nullptr) {
         const int4 g = p.group_tiles[tc.m_blk];
         row = g.x + quad * 32 + lane; row_end = g.y;
@@ -415,6 +488,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tmem_ld32(t_row + (uint32_t)c, r0);
           if (cw == 64) tmem_ld32(t_row + (uint32_t)c + 32, r1);
           tmem_wait_ld();
+          if (wg_empty) {
+            if (p.out_mode == OUT_F32_ACC) continue;               // += 0
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { r0[i] = 0u; r1[i] = 0u; }
+          }
           if (lane == 0) bulk_wait_read<1>();                      // the buffer used two chunks ago is free
           __syncwarp();
           uint8_t* stage = my_stage + epi_buf * 4096;
@@ -654,6 +732,7 @@ static int run_gemm(int lp_fmt, const void* A, long lda, int a_mn, const void* B
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
   p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr; p.group_tiles = nullptr;
+  p.group_count = nullptr; p.group_offsets = nullptr; p.wg_mblocks = 0;
 #define GO(BNv, AM, BMj) return launch_gemm<BNv, AM, BMj>(tmA, tmB, tmD, xm, p, cp, sms, st)
   if (bn == 256) {
     if (!a_mn && !b_mn) GO(256, false, false);
@@ -697,6 +776,7 @@ static int run_gemm_fp8(int a_fmt, int b_fmt, const void* A, long lda, const voi
   p.M = M; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = bias; p.out_mode = out_mode; p.lp_fmt = out_lp_fmt;
   p.status = status; p.tiles_m = p.tiles_n = 0;
   p.fp8 = 1; p.a_fmt = a_fmt; p.b_fmt = b_fmt; p.scale_a = scale_a; p.scale_b = scale_b; p.group_tiles = nullptr;
+  p.group_count = nullptr; p.group_offsets = nullptr; p.wg_mblocks = 0;
   static const ExtraMaps kNoMaps = {};
   CommParams cp = {};
   if (bn == 256) return launch_gemm<256, false, false, true>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
@@ -706,7 +786,7 @@ static int run_gemm_fp8(int a_fmt, int b_fmt, const void* A, long lda, const voi
 // Grouped product over expert-sorted rows (see GemmParams::group_tiles).  A [T, K] K-major; B stacked experts.
 static int run_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B, long ldb, int b_mn, void* D, long ldd,
                             const int4* tiles, int n_tiles, int E, int T, int N, int K, int sms, int* status,
-                            cudaStream_t st) {
+                            cudaStream_t st, const int* tile_count = nullptr) {
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
   if (b_mn && (K % BK)) return -3;               // the reduction may not run into the next expert's rows
   const int bn = (N > 128) ? 256 : 128;
@@ -726,6 +806,7 @@ static int run_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B, 
   p.M = T; p.N = N; p.K = K; p.D = D; p.ldd = ldd; p.bias = nullptr; p.out_mode = OUT_LP; p.lp_fmt = lp_fmt;
   p.status = status; p.tiles_m = n_tiles; p.tiles_n = 0;
   p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr; p.group_tiles = tiles;
+  p.group_count = tile_count; p.group_offsets = nullptr; p.wg_mblocks = 0;
   static const ExtraMaps kNoMaps = {};
   CommParams cp = {};
   if (bn == 256) {
@@ -734,6 +815,39 @@ static int run_gemm_grouped(int lp_fmt, const void* A, long lda, const void* B, 
   }
   if (!b_mn) return launch_gemm<128, false, false>(tmA, tmB, tmA, kNoMaps, p, cp, sms, st);
   return launch_gemm<128, false, true>(tmA, tmB, tmA, kNoMaps, p, cp, sms, st);
+}
+
+// Weight gradients of all experts in one launch: dW [E, N_out, K_in] fp32 (=|+=) dy_e^T x_e with dy [T, N_out] and
+// x [T, K_in] (rows sorted by expert, expert e = rows [offsets[e], offsets[e + 1])).  N_out a multiple of 128.
+static int run_gemm_grouped_wgrad(int lp_fmt, const void* dy, long ld_dy, const void* x, long ld_x, float* dW,
+                                  const int* offsets, int E, int T, int N_out, int K_in, int accumulate, int sms,
+                                  int* status, cudaStream_t st) {
+  if ((ld_dy % 8) || (ld_x % 8) || (reinterpret_cast<uintptr_t>(dy) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
+  if ((N_out % BM) || (K_in % 4) || (reinterpret_cast<uintptr_t>(dW) & 15)) return -3;
+  const int bn = (K_in > 128) ? 256 : 128;
+  CUtensorMap tmA, tmB, tmD;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)N_out, (uint64_t)T}, strides[1] = {(uint64_t)ld_dy * 2};
+    uint32_t box[2] = {64, BK};
+    if ((rc = make_tmap(&tmA, dy, 2, dims, strides, box))) return rc;
+    dims[0] = (uint64_t)K_in; strides[0] = (uint64_t)ld_x * 2;
+    if ((rc = make_tmap(&tmB, x, 2, dims, strides, box))) return rc;
+    uint64_t dd[2] = {(uint64_t)K_in, (uint64_t)E * N_out}, ds[1] = {(uint64_t)K_in * 4};
+    uint32_t db[2] = {32, 32};
+    if ((rc = make_tmap(&tmD, dW, 2, dd, ds, db, 4))) return rc;
+  }
+  GemmParams p;
+  p.tma_out = 1;
+  p.M = E * N_out; p.N = K_in; p.K = T; p.D = dW; p.ldd = K_in; p.bias = nullptr;
+  p.out_mode = accumulate ? OUT_F32_ACC : OUT_F32; p.lp_fmt = lp_fmt;
+  p.status = status; p.tiles_m = 0; p.tiles_n = 0;
+  p.fp8 = 0; p.a_fmt = p.b_fmt = 0; p.scale_a = p.scale_b = nullptr; p.group_tiles = nullptr;
+  p.group_count = nullptr; p.group_offsets = offsets; p.wg_mblocks = N_out / BM;
+  static const ExtraMaps kNoMaps = {};
+  CommParams cp = {};
+  if (bn == 256) return launch_gemm<256, true, true>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
+  return launch_gemm<128, true, true>(tmA, tmB, tmD, kNoMaps, p, cp, sms, st);
 }
 
 }  // namespace mlb
