@@ -112,8 +112,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sV = sK + 2 * KVB;
   uint8_t* sP = sV + 2 * KVB;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 16384);
-  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 s_full | 6 s_empty | 7 p_full | 8 o_done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  // 0 q_full | 1,2 k_full | 3,4 k_empty | 5 s_full | 6 s_empty | 7 p_full | 8 o_done | 9,10 v_full | 11,12 v_empty
+  // K and V tiles have rings of their own: a K tile is free as soon as S = Q K^T of its step has run (early in
+  // the step), so the K tile two steps ahead is requested a whole step before it is needed; with one ring for
+  // both, the request waited for P V at the end of the step and every step stalled on the copy's latency.
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto B = [&](int i) { return bar0 + 8u * i; };
@@ -133,6 +136,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(B(0), 1);
     mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
     mbar_init(B(5), 1); mbar_init(B(6), 4); mbar_init(B(7), 4); mbar_init(B(8), 1);
+    mbar_init(B(9), 1); mbar_init(B(10), 1); mbar_init(B(11), 1); mbar_init(B(12), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
@@ -151,13 +155,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int c = 0; c < D / 64; ++c) tma_load_5d(smem_u32(sQ) + c * QC, &tmQ, B(0), c * 64, j, g, bb, s0);
       for (int t = 0; t < n_kv; ++t) {
         const int st = t & 1;
-        if (!mbar_wait(B(3 + st), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag, p.status, 11)) break;
-        mbar_expect_tx(B(1 + st), 2 * KVB);
+        const uint32_t ph = (((uint32_t)t >> 1) & 1u) ^ 1u;
+        if (!mbar_wait(B(3 + st), ph, abort_flag, p.status, 11)) break;
+        mbar_expect_tx(B(1 + st), KVB);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
+        for (int c = 0; c < D / 64; ++c)
           tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(1 + st), c * 64, 0, g, bb, t * BN);
-          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(1 + st), c * 64, 0, g, bb, t * BN);
-        }
+        if (!mbar_wait(B(11 + st), ph, abort_flag, p.status, 11)) break;
+        mbar_expect_tx(B(9 + st), KVB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(9 + st), c * 64, 0, g, bb, t * BN);
       }
     }
   } else if (warp == 1) {
@@ -170,6 +178,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           mma_f16(tS, kmajor_desc(aQ, kk, QC), kmajor_desc(kb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(3 + (t & 1)));            // this K tile may be overwritten once S has been computed
         mma_commit(B(5));
       };
       bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 12) && mbar_wait(B(1), 0, abort_flag, p.status, 13);
@@ -182,13 +191,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           fence_after_sync();
           issue_s(t + 1);
         }
+        if (!mbar_wait(B(9 + (t & 1)), ((uint32_t)t >> 1) & 1u, abort_flag, p.status, 16)) { ok = false; break; }
         if (!mbar_wait(B(7), (uint32_t)t & 1u, abort_flag, p.status, 16)) { ok = false; break; }
         fence_after_sync();
         const uint32_t vb = aV + (t & 1) * KVB;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
           mma_f16(tO, kmajor_desc(aP, kk, 0), mnmajor_desc(vb, kk, KC), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(B(3 + (t & 1)));
+        mma_commit(B(11 + (t & 1)));
         mma_commit(B(8));
       }
     }
@@ -331,12 +341,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + QB;
+  // Four K/V stages: a K tile is held until dQ += dS K at the end of its step, so with two stages the tile two
+  // steps ahead was requested only when it was already needed and every step waited for the copy.
+  constexpr int NST = 4;
   uint8_t* sK = sdO + QB;
-  uint8_t* sV = sK + 2 * KVB;
-  uint8_t* sdS = sV + 2 * KVB;
+  uint8_t* sV = sK + NST * KVB;
+  uint8_t* sdS = sV + NST * KVB;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 16384);
-  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 sdp_full | 6 sdp_empty | 7 ds_full | 8 dq_done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  // 0 q_full | 1..4 kv_full | 5..8 kv_empty | 9 sdp_full | 10 sdp_empty | 11 ds_full | 12 dq_done
+  constexpr int KF = 1, KE = 1 + NST, SF = 1 + 2 * NST, SE = SF + 1, DF = SF + 2, DD = SF + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DD + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto B = [&](int i) { return bar0 + 8u * i; };
@@ -354,8 +368,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(B(0), 1);
-    mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
-    mbar_init(B(5), 1); mbar_init(B(6), 8); mbar_init(B(7), 8); mbar_init(B(8), 1);
+    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(1 + i), 1);
+    mbar_init(B(SF), 1); mbar_init(B(SE), 8); mbar_init(B(DF), 8); mbar_init(B(DD), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -376,13 +390,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_5d(smem_u32(sdO) + c * QC, &tmdO, B(0), c * 64, j, g, bb, s0);
       }
       for (int t = 0; t < n_kv; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(B(3 + st), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
-        mbar_expect_tx(B(1 + st), 2 * KVB);
+        const int st = t % NST;
+        if (!mbar_wait(B(KE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(KF + st), 2 * KVB);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(1 + st), c * 64, 0, g, bb, t * BN);
-          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(1 + st), c * 64, 0, g, bb, t * BN);
+          tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(KF + st), c * 64, 0, g, bb, t * BN);
+          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(KF + st), c * 64, 0, g, bb, t * BN);
         }
       }
     }
@@ -392,33 +406,33 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t idesc_q = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dQ = dS (K-major) x K (MN-major)
       const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), adS = smem_u32(sdS);
       auto issue_sdp = [&](int t) {
-        const uint32_t kb = aK + (t & 1) * KVB, vb = aV + (t & 1) * KVB;
+        const uint32_t kb = aK + (t % NST) * KVB, vb = aV + (t % NST) * KVB;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           mma_f16(tS, kmajor_desc(aQ, kk, QC), kmajor_desc(kb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           mma_f16(tdP, kmajor_desc(adO, kk, QC), kmajor_desc(vb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(B(5));
+        mma_commit(B(SF));
       };
-      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 22) && mbar_wait(B(1), 0, abort_flag, p.status, 23);
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 22) && mbar_wait(B(KF), 0, abort_flag, p.status, 23);
       if (ok) { fence_after_sync(); issue_sdp(0); }
       for (int t = 0; t < n_kv && ok; ++t) {
         if (t + 1 < n_kv) {
-          const int st1 = (t + 1) & 1;
-          if (!mbar_wait(B(1 + st1), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.status, 24)) { ok = false; break; }
-          if (!mbar_wait(B(6), (uint32_t)t & 1u, abort_flag, p.status, 25)) { ok = false; break; }
+          const int st1 = (t + 1) % NST;
+          if (!mbar_wait(B(KF + st1), ((uint32_t)((t + 1) / NST)) & 1u, abort_flag, p.status, 24)) { ok = false; break; }
+          if (!mbar_wait(B(SE), (uint32_t)t & 1u, abort_flag, p.status, 25)) { ok = false; break; }
           fence_after_sync();
           issue_sdp(t + 1);
         }
-        if (!mbar_wait(B(7), (uint32_t)t & 1u, abort_flag, p.status, 26)) { ok = false; break; }
+        if (!mbar_wait(B(DF), (uint32_t)t & 1u, abort_flag, p.status, 26)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t kb = aK + (t & 1) * KVB;
+        const uint32_t kb = aK + (t % NST) * KVB;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
           mma_f16(tdQ, kmajor_desc(adS, kk, 0), mnmajor_desc(kb, kk, KC), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(B(3 + (t & 1)));
-        mma_commit(B(8));
+        mma_commit(B(KE + (t % NST)));
+        mma_commit(B(DD));
       }
     }
   } else if (n_kv > 0) {
@@ -433,7 +447,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     bool ok = true;
     for (int t = 0; t < n_kv; ++t) {
       const int n0 = t * BN;
-      if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 27)) { ok = false; break; }
+      if (!mbar_wait(B(SF), (uint32_t)t & 1u, abort_flag, p.status, 27)) { ok = false; break; }
       fence_after_sync();
       uint32_t w[16];
       uint32_t rs[32], rp[32];
@@ -442,7 +456,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_wait_ld();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(6));               // S / dP are in registers: the next step's products may start
+      if (lane == 0) mbar_arrive(B(SE));              // S / dP are in registers: the next step's products may start
       // only tiles that touch the diagonal, the end of the keys or the end of the queries need per-element masks
       const bool need_mask = (p.causal && (n0 + BN - 1 > s0 + p.off)) || (n0 + BN > p.sk) || (s0 + BM > p.sq);
       if (need_mask) {
@@ -468,14 +482,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       if (t > 0) {
-        if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 28)) { ok = false; break; }
+        if (!mbar_wait(B(DD), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 28)) { ok = false; break; }
       }
       store_half_row_sw128(sdS, row, half, w);
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(7));
+      if (lane == 0) mbar_arrive(B(DF));
     }
-    if (ok && mbar_wait(B(8), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 29)) {
+    if (ok && mbar_wait(B(DD), (uint32_t)(n_kv - 1) & 1u, abort_flag, p.status, 29)) {
       fence_after_sync();
       uint8_t* drow = reinterpret_cast<uint8_t*>(p.dq) +
                       2 * ((long)qrow * p.dq_s + (long)bb * p.dq_b + (long)g * p.dq_g + (long)j * p.dq_j);
@@ -510,14 +524,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = sK + KB;
+  // Three Q / dO stages: a stage is held until dK += dS^T Q at the end of its step; with two, the tile two steps
+  // ahead was requested only when it was already needed.
+  constexpr int NST = 3;
   uint8_t* sQ = sV + KB;
-  uint8_t* sdO = sQ + 2 * QB;
-  uint8_t* sP = sdO + 2 * QB;
+  uint8_t* sdO = sQ + NST * QB;
+  uint8_t* sP = sdO + NST * QB;
   uint8_t* sdS = sP + 16384;
   float* sStat = reinterpret_cast<float*>(sdS + 16384);       // [2][2][64] lse2 / delta per step parity
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 256);
-  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5 sdp_full | 6 sdp_empty | 7 pds_full | 8 pds_done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  // 0 kv_full | 1..3 q_full | 4..6 q_empty | 7 sdp_full | 8 sdp_empty | 9 pds_full | 10 pds_done
+  constexpr int QF = 1, QE = 1 + NST, SF = 1 + 2 * NST, SE = SF + 1, PF = SF + 2, PD = SF + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PD + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto B = [&](int i) { return bar0 + 8u * i; };
@@ -539,8 +557,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(B(0), 1);
-    mbar_init(B(1), 1); mbar_init(B(2), 1); mbar_init(B(3), 1); mbar_init(B(4), 1);
-    mbar_init(B(5), 1); mbar_init(B(6), 8); mbar_init(B(7), 8); mbar_init(B(8), 1);
+    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(1 + i), 1);
+    mbar_init(B(SF), 1); mbar_init(B(SE), 8); mbar_init(B(PF), 8); mbar_init(B(PD), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -561,14 +579,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_5d(smem_u32(sV) + c * KC, &tmV, B(0), c * 64, 0, g, bb, n0);
       }
       for (int t = 0; t < n_steps; ++t) {
-        const int st = t & 1;
+        const int st = t % NST;
         const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
-        if (!mbar_wait(B(3 + st), (((uint32_t)t >> 1) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
-        mbar_expect_tx(B(1 + st), 2 * QB);
+        if (!mbar_wait(B(QE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
+        mbar_expect_tx(B(QF + st), 2 * QB);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_5d(smem_u32(sQ) + st * QB + c * QC, &tmQ, B(1 + st), c * 64, j, g, bb, q0);
-          tma_load_5d(smem_u32(sdO) + st * QB + c * QC, &tmdO, B(1 + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sQ) + st * QB + c * QC, &tmQ, B(QF + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sdO) + st * QB + c * QC, &tmdO, B(QF + st), c * 64, j, g, bb, q0);
         }
       }
     }
@@ -579,36 +597,36 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
       const uint32_t aP = smem_u32(sP), adS = smem_u32(sdS);
       auto issue_sdp = [&](int t) {
-        const uint32_t qb = aQ + (t & 1) * QB, ob = adO + (t & 1) * QB;
+        const uint32_t qb = aQ + (t % NST) * QB, ob = adO + (t % NST) * QB;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           mma_f16(tS, kmajor_desc(aK, kk, KC), kmajor_desc(qb, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           mma_f16(tdP, kmajor_desc(aV, kk, KC), kmajor_desc(ob, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(B(5));
+        mma_commit(B(SF));
       };
-      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 32) && mbar_wait(B(1), 0, abort_flag, p.status, 33);
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 32) && mbar_wait(B(QF), 0, abort_flag, p.status, 33);
       if (ok) { fence_after_sync(); issue_sdp(0); }
       for (int t = 0; t < n_steps && ok; ++t) {
         if (t + 1 < n_steps) {
-          const int st1 = (t + 1) & 1;
-          if (!mbar_wait(B(1 + st1), ((uint32_t)(t + 1) >> 1) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
-          if (!mbar_wait(B(6), (uint32_t)t & 1u, abort_flag, p.status, 35)) { ok = false; break; }
+          const int st1 = (t + 1) % NST;
+          if (!mbar_wait(B(QF + st1), ((uint32_t)((t + 1) / NST)) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
+          if (!mbar_wait(B(SE), (uint32_t)t & 1u, abort_flag, p.status, 35)) { ok = false; break; }
           fence_after_sync();
           issue_sdp(t + 1);
         }
-        if (!mbar_wait(B(7), (uint32_t)t & 1u, abort_flag, p.status, 36)) { ok = false; break; }
+        if (!mbar_wait(B(PF), (uint32_t)t & 1u, abort_flag, p.status, 36)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t qb = aQ + (t & 1) * QB, ob = adO + (t & 1) * QB;
+        const uint32_t qb = aQ + (t % NST) * QB, ob = adO + (t % NST) * QB;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
           mma_f16(tdV, kmajor_desc(aP, kk, 0), mnmajor_desc(ob, kk, QC), idesc_g, (t > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
           mma_f16(tdK, kmajor_desc(adS, kk, 0), mnmajor_desc(qb, kk, QC), idesc_g, (t > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(B(3 + (t & 1)));
-        mma_commit(B(8));
+        mma_commit(B(QE + (t % NST)));
+        mma_commit(B(PD));
       }
     }
   } else if (n_steps > 0) {
@@ -634,7 +652,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bar_sync_compute();
       }
       const float* stat = sStat + (t & 1) * 128 + half * 32;
-      if (!mbar_wait(B(5), (uint32_t)t & 1u, abort_flag, p.status, 37)) { ok = false; break; }
+      if (!mbar_wait(B(SF), (uint32_t)t & 1u, abort_flag, p.status, 37)) { ok = false; break; }
       fence_after_sync();
       uint32_t wp[16], wd[16];
       uint32_t rs[32], rp[32];
@@ -643,7 +661,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_wait_ld();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(6));
+      if (lane == 0) mbar_arrive(B(SE));
       // per-element masks only where the step touches the diagonal or the ends of the sequences
       const bool need_mask = (p.causal && (n0 + BM - 1 > q0 + p.off)) || (q0 + BN > p.sq) || (n0 + BM > p.sk);
       if (need_mask) {
@@ -672,15 +690,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       if (t > 0) {
-        if (!mbar_wait(B(8), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
+        if (!mbar_wait(B(PD), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
       }
       store_half_row_sw128(sP, row, half, wp);
       store_half_row_sw128(sdS, row, half, wd);
       fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(7));
+      if (lane == 0) mbar_arrive(B(PF));
     }
-    if (ok && mbar_wait(B(8), (uint32_t)(n_steps - 1) & 1u, abort_flag, p.status, 39)) {
+    if (ok && mbar_wait(B(PD), (uint32_t)(n_steps - 1) & 1u, abort_flag, p.status, 39)) {
       fence_after_sync();
       uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
       uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
@@ -809,7 +827,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
     if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
     const int grid = ((sq + 127) / 128) * ng * qpg * b;
-    const int smem = 2 * D * 256 + 4 * D * 128 + 16384 + 128;
+    const int smem = 2 * D * 256 + 8 * D * 128 + 16384 + 128;         // Q, dO, four K/V stages, dS
     if (D == 128) {
       static bool set = false;
       if (!set) { if ((rc = set_smem(attn_bwd_dq_kernel<128>, smem))) return rc; set = true; }
@@ -828,7 +846,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
     if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
     const int grid = ((sk + 127) / 128) * ng * b;
-    const int smem = 2 * D * 256 + 4 * D * 128 + 2 * 16384 + 1024 + 128;
+    const int smem = 2 * D * 256 + 6 * D * 128 + 2 * 16384 + 1024 + 128;  // K, V, three Q/dO stages, P, dS, stats
     if (D == 128) {
       static bool set = false;
       if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, smem))) return rc; set = true; }

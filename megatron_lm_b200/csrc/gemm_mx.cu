@@ -83,9 +83,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + kStages * S::kABytes;
-  uint8_t* sSF = smem + kStages * (S::kABytes + S::kBBytes);
-  uint8_t* sEpi = sSF + kStages * S::kSfBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sEpi + S::kEpiBytes);
+  // the epilogue's staging buffers are 128B-swizzled like the operand tiles and must sit on 1024-byte boundaries:
+  // they come right after the operand stages, the (un-swizzled) scale-factor stages after them
+  uint8_t* sEpi = smem + kStages * (S::kABytes + S::kBBytes);
+  uint8_t* sSF = sEpi + S::kEpiBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + kStages * S::kSfBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
@@ -133,7 +135,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         int mb, nb; tile_mn(tile, mb, nb);
         const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN;
-        const int sfa_row = ((m0 >> 7) * num_kb) * 32;           // first of the 32 rows of atom (m0 / 128, kb)
+        const int sfa_atom = (m0 >> 7) * num_kb;                  // atom (m0 / 128, 0)
         const int sfb_atom0 = n0 >> 7;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
@@ -143,10 +145,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sf_dst = smem_u32(sSF + stage * S::kSfBytes);
           tma_load_2d_pair(a_dst, &tmA, fbar, kb * 128, m0);                          // box [128 B, 128 rows]
           tma_load_2d_pair(b_dst, &tmB, fbar, kb * 128, n0 + 96 * (int)rank);         // box [128 B, 96 rows]
-          tma_load_2d_pair(sf_dst, &tmSFA, fbar, 0, sfa_row + kb * 32);               // box [16 B, 32 rows]
-          tma_load_2d_pair(sf_dst + 512, &tmSFB, fbar, 0, (sfb_atom0 * num_kb + kb) * 32);
+          tma_load_2d_pair(sf_dst, &tmSFA, fbar, 0, sfa_atom + kb);                   // one atom = one 512-byte row
+          tma_load_2d_pair(sf_dst + 512, &tmSFB, fbar, 0, sfb_atom0 * num_kb + kb);
           // the second B atom may lie past the end of the matrix: the copy is then zero-filled (and still counted)
-          tma_load_2d_pair(sf_dst + 1024, &tmSFB, fbar, 0, ((sfb_atom0 + 1) * num_kb + kb) * 32);
+          tma_load_2d_pair(sf_dst + 1024, &tmSFB, fbar, 0, (sfb_atom0 + 1) * num_kb + kb);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -265,15 +267,16 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) { fence_after_sync(); tmem_dealloc2(tmem_base, 512); }
 }
 
-// tensor map without swizzle over rows of 16 bytes (the scale-factor atoms: 32 consecutive rows per atom)
+// tensor map without swizzle over the scale-factor atoms: one row of 128 32-bit words (512 bytes) per atom, so an
+// atom is a single copy request and lands in shared memory as the dense 32 x 16-byte block tcgen05.cp reads
 static int make_sf_tmap(CUtensorMap* out, const void* base, long n_atoms) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
-  cuuint64_t d[2] = {16, (cuuint64_t)n_atoms * 32};
-  cuuint64_t s[1] = {16};
-  cuuint32_t b[2] = {16, 32};
+  cuuint64_t d[2] = {128, (cuuint64_t)n_atoms};
+  cuuint64_t s[1] = {512};
+  cuuint32_t b[2] = {128, 1};
   cuuint32_t e[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), d, s, b, e,
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), d, s, b, e,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(1000 + (int)r);
