@@ -13,9 +13,10 @@ fully_parallel.py:48 spreading replicated shards over data-parallel ranks):
 * ``load`` fills each requested block from every saved block that overlaps it, so the saved and
   the loading layouts need not match.
 
-On-disk layout: ``<dir>/metadata.json``, ``<dir>/common.pt``, ``<dir>/shard_<rank>.pt``.  (The
-reference stores the same logical content through torch.distributed.checkpoint files; the
-logical model - keys, global shapes, offsets - is the same, the container format is not.)
+Two on-disk containers hold the same logical content (keys, global shapes, offsets): the reference's
+``torch_dist`` layout (``.metadata`` + ``__<rank>_0.distcp`` + ``common.pt``, written and read by
+``checkpoint/torch_dist.py``; the default, so checkpoints interchange with the reference) and a native
+one (``metadata.json`` index + ``common.pt`` + one ``shard_<rank>.pt`` per rank).
 """
 from __future__ import annotations
 
@@ -196,7 +197,17 @@ def validate_sharding_integrity(index: List[dict]) -> None:
             raise ValueError(f"{key}: main replicas cover {covered} of {total} elements")
 
 
-def save(sharded_state_dict, checkpoint_dir: str, validate_access_integrity: bool = True, group=None) -> None:
+# Container written by :func:`save`: "torch_dist" = the reference's layout (``.metadata``, ``__<rank>_0.distcp``,
+# ``common.pt``; see checkpoint/torch_dist.py), "native" = one ``shard_<rank>.pt`` per rank with a JSON index.
+# :func:`load` recognises both.
+DEFAULT_CONTAINER = os.environ.get("MLB_CKPT_CONTAINER", "torch_dist")
+
+
+def save(sharded_state_dict, checkpoint_dir: str, validate_access_integrity: bool = True, group=None,
+         container: Optional[str] = None) -> None:
+    if (container or DEFAULT_CONTAINER) == "torch_dist":
+        from . import torch_dist
+        return torch_dist.save(sharded_state_dict, checkpoint_dir, validate_access_integrity, group)
     rank = dist.get_rank() if dist.is_initialized() else 0
     world = dist.get_world_size() if dist.is_initialized() else 1
     os.makedirs(checkpoint_dir, exist_ok=True)
@@ -254,15 +265,19 @@ class _ShardFiles:
         return self.cache[fname]
 
 
-def _fill(st: ShardedTensor, entries: List[dict], files: _ShardFiles, strict: bool) -> torch.Tensor:
-    """Assemble the block described by ``st`` from the saved blocks overlapping it."""
+def _fill(st: ShardedTensor, entries: List[dict], files: Optional[_ShardFiles], strict: bool,
+          read_blob=None) -> torch.Tensor:
+    """Assemble the block described by ``st`` from the saved blocks overlapping it.  ``read_blob(entry)`` returns
+    the saved block of an index entry (default: out of the native shard files)."""
+    if read_blob is None:
+        read_blob = lambda e: files.get(e["file"])["tensors"][e["blob"]]      # noqa: E731
     full_local = st.full_local_shape()
     want = _slices(st.global_offset, full_local)
     n_want = int(np.prod(full_local)) if full_local else 1
     fr = st.flattened_range
     out = torch.zeros(n_want if fr is None else fr.stop - fr.start, dtype=st.dtype)
     got = 0
-    for e in sorted(entries, key=lambda e: e["file"]):
+    for e in sorted(entries, key=lambda e: e.get("file", "")):
         if tuple(e["global_shape"]) != tuple(st.global_shape) and not st.allow_shape_mismatch:
             raise ValueError(f"{st.key}: checkpoint global shape {e['global_shape']} != requested {st.global_shape}")
         have = _slices(e["global_offset"], e["local_shape_full"])
@@ -275,7 +290,7 @@ def _fill(st: ShardedTensor, entries: List[dict], files: _ShardFiles, strict: bo
             inter.append((lo, hi))
         if inter is None:
             continue
-        blob = files.get(e["file"])["tensors"][e["blob"]]
+        blob = read_blob(e)
         src_shape = tuple(e["local_shape_full"])
         n_src = int(np.prod(src_shape)) if src_shape else 1
         # positions (in the flattened source block) of the intersection, and where they land in the target
@@ -283,7 +298,7 @@ def _fill(st: ShardedTensor, entries: List[dict], files: _ShardFiles, strict: bo
                                                             for (lo, hi), h in zip(inter, have))].reshape(-1)
         dst_idx = torch.arange(n_want).view(full_local)[tuple(slice(lo - w.start, hi - w.start)
                                                               for (lo, hi), w in zip(inter, want))].reshape(-1)
-        if e["flattened_range"] is not None:
+        if e.get("flattened_range") is not None:
             s0, s1 = e["flattened_range"]
             keep = (src_idx >= s0) & (src_idx < s1)
             src_idx, dst_idx = src_idx[keep] - s0, dst_idx[keep]
@@ -304,6 +319,9 @@ def load(sharded_state_dict, checkpoint_dir: str, strict: bool = True, optional_
     common (non-sharded) leaves taken from the checkpoint."""
     with open(os.path.join(checkpoint_dir, "metadata.json")) as f:
         meta = json.load(f)
+    if meta.get("sharded_backend") == "torch_dist":
+        from . import torch_dist
+        return torch_dist.load(sharded_state_dict, checkpoint_dir, strict, optional_objects)
     by_key: Dict[str, List[dict]] = {}
     for e in meta["tensors"]:
         by_key.setdefault(e["key"], []).append(e)
@@ -354,6 +372,9 @@ def load_common_state_dict(checkpoint_dir: str):
 def load_tensors_metadata(checkpoint_dir: str) -> Dict[str, dict]:
     with open(os.path.join(checkpoint_dir, "metadata.json")) as f:
         meta = json.load(f)
+    if meta.get("sharded_backend") == "torch_dist":
+        from . import torch_dist
+        return torch_dist.load_tensors_metadata(checkpoint_dir)
     return {e["key"]: dict(global_shape=e["global_shape"], dtype=e["dtype"]) for e in meta["tensors"]}
 
 

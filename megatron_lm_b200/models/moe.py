@@ -503,11 +503,13 @@ class MoEFusedPeerDispatcher(MoEAlltoAllTokenDispatcher):
         from ..ops.moe_fused import fused_dispatch
         self.shape, self.T = hidden.shape, h.shape[0]
         rm = routing_map.t().contiguous()
-        token_idx = torch.arange(self.T, device=h.device).unsqueeze(0).expand(self.E, -1)
-        sorted_indices = token_idx.masked_select(rm)
+        # dropless top-k routing: exactly T * topk copies, so the (expert, token) pairs can be listed without the
+        # host learning a data-dependent size (row-major order of the [E, T] map = expert-major copy order)
+        pairs = rm.nonzero_static(size=self.T * self.config.moe_router_topk)
+        sorted_indices = pairs[:, 1].contiguous()
         self.comm = self._comm(self.T, h.shape[1], h.dtype)
         self.plan = self.comm.plan(routing_map, sorted_indices)
-        self.copy_probs = probs.t().contiguous().masked_select(rm)
+        self.copy_probs = probs.t()[pairs[:, 0], pairs[:, 1]]
         recv = fused_dispatch(h, self.comm, self.plan)
         return recv, self.plan["tokens_per_local_expert"]
 

@@ -71,10 +71,8 @@ class FusedMoEComm:
         flat = blk.reshape(self.ep, -1)
         offs = torch.cumsum(flat, dim=1) - flat                                    # [dst, e_local * ep]
         my_base = offs.view(self.ep, self.E_local, self.ep)[:, :, self.rank].reshape(-1)   # [E]: base row of my block
-        host = torch.cat((local_counts, blk[self.rank].reshape(-1))).tolist()       # one host read
-        counts = [int(v) for v in host[:self.E]]
-        recv_blocks = [int(v) for v in host[self.E:]]                                # [e_local][src]
-        n_copies = sum(counts)
+        # every token has exactly top-k copies (dropless routing): the number of copies leaving this rank is static
+        n_copies = sorted_indices.numel()
         expert_of = torch.repeat_interleave(torch.arange(self.E, device=dev), local_counts, output_size=n_copies)
         start = torch.cumsum(local_counts, 0) - local_counts
         j = torch.arange(n_copies, device=dev) - start[expert_of]
@@ -82,9 +80,12 @@ class FusedMoEComm:
         dst_rank = (expert_of // self.E_local).to(torch.int32)
         # copies of token t: positions in the expert-major order, grouped by token
         order = torch.argsort(sorted_indices, stable=True)                         # [T * topk]
-        tpe_local = [sum(recv_blocks[e * self.ep:(e + 1) * self.ep]) for e in range(self.E_local)]
+        # rows per local expert stay on the device (the grouped GEMM builds its tile table there); the only value
+        # the host needs is how many rows arrive, to size the activations of the expert MLP: one scalar read
+        tpe_local = blk[self.rank].sum(dim=-1)                                       # [E_local] int64, device
+        n_recv = int(tpe_local.sum().item())
         return {"dst_rank": dst_rank, "dst_row": dst_row, "order": order.to(torch.int32), "n_copies": n_copies,
-                "n_recv": sum(recv_blocks), "tokens_per_local_expert": tpe_local,
+                "n_recv": n_recv, "tokens_per_local_expert": tpe_local,
                 "src_row": sorted_indices.to(torch.int32)}
 
     # -- raw kernels ------------------------------------------------------------------------

@@ -173,3 +173,47 @@ def test_legacy_torch_format_with_distributed_optimizer(tmp_path):
     d = str(tmp_path / "ckpt")
     run_distributed(_torch_fmt_rank, 2, d, "save")
     run_distributed(_torch_fmt_rank, 2, d, "load")
+
+
+def test_torch_dist_layout_is_readable_by_torch_dcp_and_back(tmp_path):
+    """The default container is the reference's ``torch_dist`` layout: what we write, torch.distributed.checkpoint
+    reads with its own reader; what it writes, our loader reads (and re-blocks)."""
+    import json
+    import torch.distributed.checkpoint as dcp
+    d = str(tmp_path / "ours")
+    full = torch.arange(8 * 6, dtype=torch.float32).view(8, 6)
+    sd = {"w_top": ds.ShardedTensor.from_rank_offsets("layer.w", full[:4].clone(), (0, 0, 2)),
+          "w_bot": ds.ShardedTensor.from_rank_offsets("layer.w", full[4:].clone(), (0, 1, 2)),
+          "b": ds.ShardedTensor.from_rank_offsets("layer.b", torch.ones(3)),
+          "rng": ds.ShardedObject("rng_state", {"seed": 5}, (1,), (0,)), "iteration": 9}
+    ds.save(sd, d)
+    names = set(os.listdir(d))
+    assert {".metadata", "__0_0.distcp", "common.pt", "metadata.json"} <= names
+    assert json.load(open(os.path.join(d, "metadata.json")))["sharded_backend"] == "torch_dist"
+    # torch's own reader
+    target = {"layer.w": torch.zeros(8, 6), "layer.b": torch.zeros(3)}
+    dcp.load(target, storage_reader=dcp.FileSystemReader(d), no_dist=True)
+    assert torch.equal(target["layer.w"], full) and torch.equal(target["layer.b"], torch.ones(3))
+    # a checkpoint written by torch.distributed.checkpoint, read here as three row stripes
+    d2 = str(tmp_path / "theirs")
+    dcp.save({"layer.w": full.clone(), "layer.b": torch.full((3,), 2.0)}, storage_writer=dcp.FileSystemWriter(d2),
+             no_dist=True)
+    torch.save({"iteration": 4}, os.path.join(d2, "common.pt"))
+    with open(os.path.join(d2, "metadata.json"), "w") as f:
+        json.dump({"sharded_backend": "torch_dist", "sharded_backend_version": 1, "common_backend": "torch",
+                   "common_backend_version": 1}, f)
+    for r in range(2):
+        req = {"x": ds.ShardedTensor.from_rank_offsets("layer.w", torch.zeros(4, 6), (0, r, 2)),
+               "b": ds.ShardedTensor.from_rank_offsets("layer.b", torch.zeros(3))}
+        out = ds.load(req, d2)
+        assert torch.equal(out["x"], full[4 * r:4 * r + 4]) and out["iteration"] == 4
+        assert torch.equal(out["b"], torch.full((3,), 2.0))
+
+
+def test_native_container_still_round_trips(tmp_path):
+    d = str(tmp_path)
+    sd = {"w": ds.ShardedTensor.from_rank_offsets("w", torch.arange(6.0).view(2, 3)), "it": 3}
+    ds.save(sd, d, container="native")
+    assert os.path.isfile(os.path.join(d, "shard_0.pt"))
+    out = ds.load({"w": ds.ShardedTensor.from_rank_offsets("w", torch.zeros(2, 3))}, d)
+    assert torch.equal(out["w"], torch.arange(6.0).view(2, 3)) and out["it"] == 3
