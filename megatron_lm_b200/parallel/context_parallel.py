@@ -12,6 +12,12 @@ schemes are written on top of this library's flash-attention kernels:
                  queries x its first chunk; block of a later rank -> second query chunk x all keys.
 * ``all_gather`` gather K/V once (cheap for GQA), two causal calls per rank with sq < sk.
 * ``a2a``        Ulysses: all-to-all to [full sequence, heads / cp], local attention, all-to-all back.
+* ``a2a+p2p``    hierarchical: Ulysses inside the inner sub-group (consecutive ranks, e.g. one NVLink island),
+                 ring attention between the sub-groups.  After the inner all-to-all a rank holds, for its share
+                 of the heads, the early chunks of its whole sub-group and their mirror late chunks - again a
+                 zig-zag layout, of the sub-groups - so the ring step logic is reused unchanged
+                 (reference: megatron/core/parallel_state.py:305-364 builds the groups,
+                 extensions/transformer_engine.py:876-930 passes them to the attention).
 """
 from __future__ import annotations
 
@@ -212,6 +218,39 @@ def ulysses_attention(q, k, v, group=None, scale: Optional[float] = None, causal
     return out.reshape(s_local, b, ng * qpg, d)
 
 
+def hierarchical_attention(q, k, v, inner_group, outer_group, scale: Optional[float] = None, causal: bool = True):
+    """``a2a+p2p``: q [s_local, b, ng, qpg, d], k/v [s_local, b, ng, d] in the zig-zag layout of the whole
+    context-parallel group (size = inner x outer, inner ranks consecutive) -> [s_local, b, ng*qpg, d]."""
+    A = dist.get_world_size(inner_group)
+    if A == 1:
+        return ring_attention(q, k, v, outer_group, scale, causal)
+    s_local, b, ng, qpg, d = q.shape
+    if ng % A != 0:
+        raise ValueError("a2a+p2p needs the number of KV groups to be divisible by the inner (a2a) group size")
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    c = s_local // 2
+    # gathered order is (source rank j, [early chunk, late chunk]); wanted: early chunks by rank, then late chunks by
+    # falling rank - natural order inside both halves, which is what the ring's zig-zag steps assume
+    pos = torch.arange(A * s_local, device=q.device).view(A, 2, c)
+    order = torch.cat((pos[:, 0].reshape(-1), pos[:, 1].flip(0).reshape(-1)))
+    inv = torch.argsort(order)
+
+    def seq_to_heads(t):          # [s_local, b, ng, ...] -> [A * s_local, b, ng / A, ...]
+        rest = t.shape[3:]
+        x = t.reshape(s_local, b, A, ng // A, *rest).permute(2, 0, 1, 3, *range(4, 4 + len(rest))).contiguous()
+        x = all_to_all(inner_group, x.reshape(A * s_local, b, ng // A, *rest))
+        return x.index_select(0, order)
+
+    def heads_to_seq(t):          # [A * s_local, b, ng / A, qpg, d] -> [s_local, b, ng, qpg, d]
+        x = all_to_all(inner_group, t.index_select(0, inv).contiguous())
+        x = x.reshape(A, s_local, b, ng // A, qpg, d).permute(1, 2, 0, 3, 4, 5)
+        return x.reshape(s_local, b, ng, qpg, d)
+
+    o = ring_attention(seq_to_heads(q), seq_to_heads(k), seq_to_heads(v), outer_group, scale, causal)
+    out = heads_to_seq(o.reshape(A * s_local, b, ng // A, qpg, d))
+    return out.reshape(s_local, b, ng * qpg, d)
+
+
 def context_parallel_attention(q, k, v, comm_type: str = "p2p", group=None, scale=None, causal=True):
     if comm_type == "p2p":
         return ring_attention(q, k, v, group, scale, causal)
@@ -223,5 +262,6 @@ def context_parallel_attention(q, k, v, comm_type: str = "p2p", group=None, scal
         groups = state.get_hierarchical_context_parallel_groups()
         if len(groups) < 2:
             return ring_attention(q, k, v, group, scale, causal)
-        raise NotImplementedError("hierarchical a2a+p2p context parallelism: use p2p, a2a or all_gather")
+        # level 0 is the innermost (fastest varying) sub-group: all-to-all there, ring across
+        return hierarchical_attention(q, k, v, groups[0], groups[1], scale, causal)
     raise ValueError(f"unknown cp_comm_type {comm_type}")

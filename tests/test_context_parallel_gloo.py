@@ -12,7 +12,8 @@ def _run(rank, world, kind, ng, qpg):
     from megatron_lm_b200.ops.attention import _ref_attention
     from megatron_lm_b200.parallel import state
     from megatron_lm_b200.parallel.context_parallel import context_parallel_attention, zigzag_indices
-    state.initialize_model_parallel(context_parallel_size=world)
+    state.initialize_model_parallel(context_parallel_size=world,
+                                    hierarchical_context_parallel_sizes=[2, world // 2] if kind == "a2a+p2p" else None)
     torch.manual_seed(3)
     S, b, d = 16 * world, 2, 8
     q = torch.randn(S, b, ng, qpg, d, dtype=torch.float64)
@@ -36,3 +37,8 @@ def _run(rank, world, kind, ng, qpg):
 @pytest.mark.parametrize("world", [2, 4])
 def test_cp_attention_matches_full(kind, world):
     run_distributed(_run, world, kind, 4, 2)
+
+
+def test_hierarchical_a2a_p2p_matches_full():
+    """cp = 4 as 2 (all-to-all inside a pair of ranks) x 2 (ring between the pairs)."""
+    run_distributed(_run, 4, "a2a+p2p", 4, 2)
