@@ -28,6 +28,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--encode-blocks", type=int, default=0)
     ap.add_argument("--no-host-tier", action="store_true")
+    ap.add_argument("--direct-loads", action="store_true",
+                    help="parity kernel with plain peer loads instead of bulk copies staged through shared memory")
     a = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
@@ -39,7 +41,7 @@ def main(argv=None):
     m = min(a.m, world - 1)
     k = a.k if a.k is not None else world - m
     mgr = GpuECCheckpoint(dist.group.WORLD, nbytes, k=k, m=m, chunk_bytes=int(a.chunk_mib * 2 ** 20),
-                          host_tier=not a.no_host_tier, encode_blocks=a.encode_blocks)
+                          host_tier=not a.no_host_tier, encode_blocks=a.encode_blocks, staged=not a.direct_loads)
 
     def mx(v):
         t = torch.tensor([v], device="cuda", dtype=torch.float64)
@@ -77,7 +79,10 @@ def main(argv=None):
                           "snapshot_ms": min(snap), "encode_ms": best, "encode_GBps_aggregate": total / best / 1e6,
                           "nvlink_bytes_per_rank": nbytes * (k + m - 1) / k if world > 1 else 0,
                           "host_tier_ms": min(host), "lost_ranks": lost, "recovery_s": rec_ms / 1e3,
-                          "byte_exact": bool(ok.item()), "stripes": len(mgr.plan.stripes)}), flush=True)
+                          "byte_exact": bool(ok.item()), "stripes": len(mgr.plan.stripes),
+                          "kernel": "direct peer loads" if a.direct_loads else "bulk copies staged through shared memory",
+                          "encode_fraction_of_nvlink_roofline": (nbytes / 770e9) / (best / 1e3) if world > 1 else None}),
+              flush=True)
     dist.destroy_process_group()
 
 

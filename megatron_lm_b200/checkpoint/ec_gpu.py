@@ -30,7 +30,8 @@ from .ec_plan import StripePlan, plan_stripes
 
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
-_lib.register_signatures({"mlb_ec_apply_batch": "pilip", "mlb_ec_job_bytes": ""})
+_lib.register_signatures({"mlb_ec_apply_batch": "pilip", "mlb_ec_job_bytes": "",
+                          "mlb_ec_apply_batch_staged": "piliipp"})
 
 _JOB = np.dtype([("src", "<u8", 16), ("dst", "<u8", 4), ("coef", "u1", (4, 16)), ("k", "<i4"), ("m", "<i4"),
                  ("pad", "<i4", 2)])
@@ -38,7 +39,7 @@ _JOB = np.dtype([("src", "<u8", 16), ("dst", "<u8", 4), ("coef", "u1", (4, 16)),
 
 class GpuECCheckpoint:
     def __init__(self, group, state_bytes: int, k: Optional[int] = None, m: int = 2, chunk_bytes: int = 1 << 20,
-                 host_tier: bool = True, encode_blocks: int = 0):
+                 host_tier: bool = True, encode_blocks: int = 0, staged: bool = True):
         import torch.distributed._symmetric_memory as symm_mem
         assert _JOB.itemsize == _lib.lib().mlb_ec_job_bytes()
         self.group = group
@@ -49,6 +50,7 @@ class GpuECCheckpoint:
             raise ValueError("the GPU tier needs k + m <= group size")
         self.chunk = int(chunk_bytes)
         self.encode_blocks = encode_blocks
+        self.staged = staged
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
         n = torch.tensor([(state_bytes + self.chunk - 1) // self.chunk], dtype=torch.int64, device=dev)
@@ -107,9 +109,15 @@ class GpuECCheckpoint:
 
     def _launch(self, jobs):
         tbl, n = jobs
-        if n:
-            _lib.check(_lib.lib().mlb_ec_apply_batch(tbl.data_ptr(), n, self.chunk, self.encode_blocks,
-                                                     torch.cuda.current_stream().cuda_stream), "ec batch")
+        if not n:
+            return
+        st = torch.cuda.current_stream().cuda_stream
+        if self.staged and self.chunk % 4096 == 0:
+            # sources staged through shared memory by bulk copies (large NVLink requests, several in flight per SM)
+            _lib.check(_lib.lib().mlb_ec_apply_batch_staged(tbl.data_ptr(), n, self.chunk, max(self.k, 1), self.encode_blocks,
+                                                            _lib.status_word().data_ptr(), st), "ec batch")
+        else:
+            _lib.check(_lib.lib().mlb_ec_apply_batch(tbl.data_ptr(), n, self.chunk, self.encode_blocks, st), "ec batch")
 
     # -- save ---------------------------------------------------------------------------
     def save(self, tensors: Sequence[torch.Tensor], iteration: int, overlap: bool = False) -> Dict[str, float]:

@@ -9,6 +9,7 @@
 // so every branch on them is uniform.  The reference has no erasure coding (its in-memory
 // checkpoint replicates: megatron/training/checkpointing.py:520-544); this is new functionality.
 #include "common.cuh"
+#include "tc05.cuh"
 
 namespace mlb {
 
@@ -117,6 +118,90 @@ ec_batch_kernel(const EcJob* __restrict__ jobs, int n_jobs, size_t nvec, int par
   }
 }
 
+// Staged form of the batched kernel: the sources (mostly peers' memory) are brought into shared memory by bulk
+// asynchronous copies - one thread keeps several 4 KB pieces per source in flight, so the NVLink reads are large
+// requests that do not depend on how many warps are resident - and the multiply-XOR runs out of shared memory.
+// Work item = (job, 4 KB piece); a ring of `stages` stages of k_max pieces each.  Every wait is bounded.
+constexpr int kEcPiece = 4096;
+__device__ __forceinline__ void ec_bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(288, 2)
+ec_staged_kernel(const EcJob* __restrict__ jobs, int n_jobs, size_t nbytes, int k_max, int stages, int* status) {
+  using namespace tc05;
+  extern __shared__ __align__(128) uint8_t ec_smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ec_smem);          // full[stages], empty[stages]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 16);
+  uint8_t* data = ec_smem + 256;
+  const uint32_t bar0 = smem_u32(bars);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(bar0 + 8u * s, 1); mbar_init(bar0 + 8u * (8 + s), 8); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const long pieces = (long)(nbytes / kEcPiece);
+  const long total = (long)n_jobs * pieces;
+  const size_t stage_bytes = (size_t)k_max * kEcPiece;
+  if (warp == 8) {
+    // ---------------------------------------------------------------- producer (one thread)
+    if (lane == 0) {
+      int st = 0; uint32_t ph = 0;
+      for (long w = blockIdx.x; w < total; w += gridDim.x) {
+        const EcJob* job = jobs + w / pieces;
+        const size_t off = (size_t)(w % pieces) * kEcPiece;
+        if (!mbar_wait(bar0 + 8u * (8 + st), ph ^ 1u, abort_flag, status, 71)) break;
+        const int k = job->k;
+        mbar_expect_tx(bar0 + 8u * st, (uint32_t)k * kEcPiece);
+        for (int j = 0; j < k; ++j)
+          ec_bulk_g2s(smem_u32(data + st * stage_bytes + (size_t)j * kEcPiece),
+                      reinterpret_cast<const uint8_t*>(job->src[j]) + off, kEcPiece, bar0 + 8u * st);
+        if (++st == stages) { st = 0; ph ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- 256 consumers: one 16-byte vector each
+    int st = 0; uint32_t ph = 0;
+    const int v = threadIdx.x;                                       // vector index inside the piece
+    for (long w = blockIdx.x; w < total; w += gridDim.x) {
+      const EcJob* job = jobs + w / pieces;
+      const size_t off = (size_t)(w % pieces) * kEcPiece;
+      const int k = job->k, m = job->m;
+      if (!mbar_wait(bar0 + 8u * st, ph, abort_flag, status, 72)) break;
+      uint32_t acc[kEcMaxM][4];
+#pragma unroll
+      for (int i = 0; i < kEcMaxM; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0u; }
+      const uint8_t* base = data + st * stage_bytes;
+      for (int j = 0; j < k; ++j) {
+        const uint4 raw = reinterpret_cast<const uint4*>(base + (size_t)j * kEcPiece)[v];
+        uint32_t x[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t c[kEcMaxM];
+        uint32_t any = 0;
+#pragma unroll
+        for (int i = 0; i < kEcMaxM; ++i) { c[i] = (i < m) ? job->coef[i][j] : 0u; any |= c[i]; }
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          if ((any >> b) == 0) break;
+#pragma unroll
+          for (int i = 0; i < kEcMaxM; ++i)
+            if ((c[i] >> b) & 1u) { acc[i][0] ^= x[0]; acc[i][1] ^= x[1]; acc[i][2] ^= x[2]; acc[i][3] ^= x[3]; }
+          x[0] = xtime4(x[0]); x[1] = xtime4(x[1]); x[2] = xtime4(x[2]); x[3] = xtime4(x[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar0 + 8u * (8 + st));              // this warp has read the stage
+#pragma unroll
+      for (int i = 0; i < kEcMaxM; ++i)
+        if (i < m) reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(job->dst[i]) + off)[v] =
+            make_uint4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+      if (++st == stages) { st = 0; ph ^= 1u; }
+    }
+  }
+}
+
 }  // namespace mlb
 
 using namespace mlb;
@@ -125,6 +210,31 @@ MLB_API int mlb_ec_job_bytes() { return (int)sizeof(EcJob); }
 
 // jobs: device array of n_jobs EcJob records (layout: 16 x u64 src, 4 x u64 dst, 4 x 16 coefficient bytes, k, m, 2 pad
 // ints); every buffer holds nbytes (multiple of 16).  grid_blocks bounds the SMs used (0 = whole GPU).
+// Staged variant (sources through shared memory by bulk copies); nbytes a multiple of 4096, k_max = the largest
+// number of sources of any job.  status: optional device word that receives a code if a bounded wait runs out.
+MLB_API int mlb_ec_apply_batch_staged(const void* jobs, int n_jobs, long nbytes, int k_max, int grid_blocks,
+                                      int* status, cudaStream_t st) {
+  if (n_jobs <= 0) return 0;
+  if (nbytes <= 0 || (nbytes % kEcPiece) || k_max < 1 || k_max > kEcMaxK) return -3;
+  int stages = (96 * 1024) / (k_max * kEcPiece);                     // two blocks per SM when the ring fits 96 KB
+  if (stages > 8) stages = 8;
+  if (stages < 2) stages = 2;
+  const int smem = 256 + stages * k_max * kEcPiece;
+  static int smem_set = 0;
+  if (smem > smem_set) {
+    cudaError_t e = cudaFuncSetAttribute(ec_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    smem_set = smem;
+  }
+  const long total = (long)n_jobs * (nbytes / kEcPiece);
+  long cap = grid_blocks > 0 ? grid_blocks : 148L * 2;
+  unsigned grid = (unsigned)(total < cap ? total : cap);
+  ec_staged_kernel<<<grid, 288, smem, st>>>(reinterpret_cast<const EcJob*>(jobs), n_jobs, (size_t)nbytes, k_max, stages,
+                                            status);
+  MLB_CHECK_LAUNCH();
+  return 0;
+}
+
 MLB_API int mlb_ec_apply_batch(const void* jobs, int n_jobs, long nbytes, int grid_blocks, cudaStream_t st) {
   if (n_jobs <= 0) return 0;
   if (nbytes <= 0 || (nbytes % 16)) return -3;

@@ -184,6 +184,72 @@ def bench_gated_norm(a):
             bytes_=y.numel() * 2 * 5)
 
 
+def bench_tp_fused(a):
+    """Launch with torchrun on tp GPUs of one node.  For the four tensor-parallel products of a transformer layer
+    (sizes of the 7B model by default): the GEMM alone, NCCL collective + GEMM as two launches, and the fused
+    all-gather->GEMM / GEMM->reduce-scatter kernel; device-timed, max over ranks, against the roofline
+    max(FLOPs / GEMM peak, NVLink bytes / 770 GB/s per direction)."""
+    import torch.distributed as dist
+    from .gemm import gemm
+    from .tp_fused import FusedTP
+    rank, tp = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    h, f, S = a.hidden, a.ffn, a.seq
+    rows = S // tp
+    fused = FusedTP(dist.group.WORLD, rows, max(h, 2 * f // tp), max(h, 2 * f // tp))
+    pk = _peaks()
+    gemm_peak = pk.get("bf16_tflops", 1590.0) * 1e12
+    link = 770e9
+
+    def mx(v):
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    def line(name, ms, flops, nv_bytes):
+        ms = mx(ms)
+        roof = max(flops / gemm_peak, nv_bytes / link) * 1e3
+        if rank == 0:
+            print(f"  {name}: {ms * 1e3:.1f} us  {flops / ms / 1e9:.0f} TFLOP/s  roofline {roof * 1e3:.1f} us "
+                  f"-> {roof / ms:.2f} of roofline", flush=True)
+    cases = [("qkv  (all-gather -> GEMM)", "ag", h, 3 * h // tp), ("fc1  (all-gather -> GEMM)", "ag", h, 2 * f // tp),
+             ("proj (GEMM -> reduce-scatter)", "rs", h // tp, h), ("fc2  (GEMM -> reduce-scatter)", "rs", f // tp, h)]
+    for name, kind, K, N in cases:
+        W = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+        flops = 2.0 * S * N * K
+        if rank == 0:
+            print(f"{name}: M={S} N={N} K={K} tp={tp}", flush=True)
+        if kind == "ag":
+            x = torch.randn(rows, K, device="cuda").to(torch.bfloat16)
+            full = torch.empty(S, K, device="cuda", dtype=torch.bfloat16)
+            out = torch.empty(S, N, device="cuda", dtype=torch.bfloat16)
+            line("GEMM alone          ", _time(lambda: gemm(full, W, out=out), a.iters, a.warmup), flops, 0)
+
+            def nccl():
+                dist.all_gather_into_tensor(full, x)
+                gemm(full, W, out=out)
+            line("NCCL all-gather+GEMM", _time(nccl, a.iters, a.warmup), flops, (tp - 1) * rows * K * 2)
+            line("fused               ", _time(lambda: fused.ag_gemm(x, W), a.iters, a.warmup), flops, (tp - 1) * rows * K * 2)
+        else:
+            A = torch.randn(S, K, device="cuda").to(torch.bfloat16)
+            full = torch.empty(S, N, device="cuda", dtype=torch.bfloat16)
+            out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+            line("GEMM alone          ", _time(lambda: gemm(A, W, out=full), a.iters, a.warmup), flops, 0)
+
+            def nccl():
+                gemm(A, W, out=full)
+                dist.reduce_scatter_tensor(out, full)
+            nv = (tp - 1) * rows * N * 2
+            line("GEMM+NCCL red-scat. ", _time(nccl, a.iters, a.warmup), flops, nv)
+            line("fused               ", _time(lambda: fused.gemm_rs(A, W), a.iters, a.warmup), flops, nv)
+    torch.cuda.synchronize()
+    from . import _lib
+    _lib.check_status()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--iters", type=int, default=20)
@@ -204,8 +270,11 @@ def main(argv=None):
     sp.add_argument("--vocab", type=int, default=131072)
     gn = sub.add_parser("gated-norm"); gn.add_argument("--rows", type=int, default=32768)
     gn.add_argument("--hidden", type=int, default=4096); gn.add_argument("--groups", type=int, default=8)
+    tf = sub.add_parser("tp-fused", help="torchrun --nproc-per-node TP -m megatron_lm_b200.ops.microbench tp-fused")
+    tf.add_argument("--hidden", type=int, default=4096); tf.add_argument("--ffn", type=int, default=11008)
+    tf.add_argument("--seq", type=int, default=4096)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam, "router": bench_router,
+    {"tp-fused": bench_tp_fused, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam, "router": bench_router,
      "sampling": bench_sampling, "gated-norm": bench_gated_norm}[a.op](a)
     from . import _lib
     _lib.check_status()

@@ -50,7 +50,9 @@ def test_noalloc_matches_regular_entry_point_twice(rms, dtype, code, tol):
     assert lib.mlb_set_device(torch.cuda.current_device()) == 0
     stream = torch.cuda.current_stream().cuda_stream
     torch.manual_seed(0)
-    for call, (rows, h) in enumerate([(300, 4096), (77, 1024)]):     # second call reuses the dirty scratch array
+    # later calls reuse the dirty scratch array; the last two are the widest row the array supports, once with
+    # fewer rows than the kernel has blocks (most blocks only write zeros) and once with many
+    for call, (rows, h) in enumerate([(300, 4096), (77, 1024), (5, 8192), (1500, 8192)]):
         x = (torch.randn(rows, h, device="cuda") * 2 + 0.3).to(dtype)
         dy = torch.randn(rows, h, device="cuda").to(dtype)
         gamma = (torch.rand(h, device="cuda") + 0.5).to(dtype)
