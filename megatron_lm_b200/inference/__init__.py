@@ -1,6 +1,8 @@
 """Text generation engines, KV-cache contexts and sampling."""
-from .engine import (ChunkAllocator, DynamicInferenceContext, DynamicInferenceEngine, InferenceRequest, SamplingParams,
-                     Scheduler, StaticInferenceContext, StaticInferenceEngine, sample_from_logits)
+from .engine import (ChunkAllocator, DynamicInferenceContext, DynamicInferenceEngine, EncoderDecoderInferenceEngine,
+                     InferenceRequest, SamplingParams, Scheduler, StaticInferenceContext, StaticInferenceEngine,
+                     VLMInferenceEngine, sample_from_logits)
 
-__all__ = ["ChunkAllocator", "DynamicInferenceContext", "DynamicInferenceEngine", "InferenceRequest", "SamplingParams",
-           "Scheduler", "StaticInferenceContext", "StaticInferenceEngine", "sample_from_logits"]
+__all__ = ["ChunkAllocator", "DynamicInferenceContext", "DynamicInferenceEngine", "EncoderDecoderInferenceEngine",
+           "InferenceRequest", "SamplingParams", "Scheduler", "StaticInferenceContext", "StaticInferenceEngine",
+           "VLMInferenceEngine", "sample_from_logits"]

@@ -487,3 +487,125 @@ class DynamicInferenceEngine:
         while self.has_unfinished_requests():
             self.step(generator)
         return [self.scheduler.completed[i] for i in ids]
+
+    def stream(self, prompts: Sequence, sampling_params: Optional[SamplingParams] = None, generator=None):
+        """Generator form of :meth:`generate`: after every engine step yields, for each request that produced a
+        token in that step, ``(request_id, token, text_delta, finished)`` - ``text_delta`` is the newly decoded
+        text when the engine has a tokenizer (detokenised incrementally, so multi-token characters come out whole),
+        else None (reference: text_generation_controller.py:1032 ``stream_tokens``)."""
+        ids = [self.add_request(p, sampling_params) for p in prompts]
+        mine = set(ids)
+        seen = {i: 0 for i in ids}
+        text = {i: "" for i in ids}
+        while any(i in self.scheduler.active or any(r.request_id == i for r in self.scheduler.waiting) for i in mine):
+            finished = {r.request_id for r in self.step(generator)}
+            for i in ids:
+                req = self.scheduler.active.get(i) or self.scheduler.completed.get(i)
+                if req is None:
+                    continue
+                while seen[i] < len(req.generated_tokens):
+                    tok = req.generated_tokens[seen[i]]
+                    seen[i] += 1
+                    delta = None
+                    if self.tokenizer is not None:
+                        full = self.tokenizer.detokenize(req.generated_tokens[:seen[i]])
+                        delta, text[i] = full[len(text[i]):], full
+                    yield i, tok, delta, (i in finished and seen[i] == len(req.generated_tokens))
+
+
+class EncoderDecoderInferenceEngine:
+    """Greedy / sampled decoding for encoder-decoder models (T5): the encoder runs once per batch, the decoder is
+    re-run on the growing target prefix (no KV cache: targets are short next to the encoder input).
+    ``model(encoder_ids, decoder_ids, ...)`` must return logits [b, t, v]
+    (reference: inference/model_inference_wrappers/t5/t5_inference_wrapper.py)."""
+
+    def __init__(self, model, bos_id: int, eod_id: Optional[int] = None, pad_id: int = 0, max_target_length: int = 128):
+        self.model, self.bos, self.eod, self.pad, self.max_t = model, bos_id, eod_id, pad_id, max_target_length
+
+    @torch.no_grad()
+    def generate(self, encoder_inputs: Sequence[Sequence[int]], sampling_params: Optional[SamplingParams] = None,
+                 generator=None):
+        sp = sampling_params or SamplingParams()
+        dev = next(self.model.parameters()).device
+        b = len(encoder_inputs)
+        L = max(len(x) for x in encoder_inputs)
+        enc = torch.full((b, L), self.pad, dtype=torch.long, device=dev)
+        for i, x in enumerate(encoder_inputs):
+            enc[i, :len(x)] = torch.tensor(list(x), device=dev)
+        enc_mask = enc != self.pad
+        dec = torch.full((b, 1), self.bos, dtype=torch.long, device=dev)
+        done = torch.zeros(b, dtype=torch.bool, device=dev)
+        was_training = self.model.training
+        self.model.eval()
+        steps = min(sp.num_tokens_to_generate, self.max_t)
+        for _ in range(steps):
+            if bool((~enc_mask).any()) and _accepts(self.model, "encoder_attn_mask"):
+                logits = self.model(enc, dec, encoder_attn_mask=enc_mask)      # padded batch: mask the padding
+            else:
+                logits = self.model(enc, dec)
+            new = sample_from_logits(logits[:, -1].float(), sp, None, generator)
+            if self.eod is not None:
+                new = torch.where(done, torch.full_like(new, self.eod), new)
+                done |= new == self.eod
+            dec = torch.cat((dec, new[:, None]), dim=1)
+            if self.eod is not None and bool(done.all()):
+                break
+        self.model.train(was_training)
+        out = []
+        for i in range(b):
+            gen = dec[i, 1:].tolist()
+            if self.eod is not None and self.eod in gen:
+                gen = gen[:gen.index(self.eod) + 1]
+            out.append(InferenceRequest(i, list(encoder_inputs[i]), sp, gen, [], "completed"))
+        return out
+
+
+def _accepts(model, name: str) -> bool:
+    import inspect
+    try:
+        return name in inspect.signature(model.forward).parameters
+    except (TypeError, ValueError):
+        return False
+
+
+class VLMInferenceEngine(StaticInferenceEngine):
+    """Text generation conditioned on images for LLaVA-style models: the first forward carries the image tensor
+    (the model splices the projected image embeddings into the prompt and fills the KV cache), later steps are
+    text-only (reference: inference/model_inference_wrappers/multimodal/vlm_inference_wrapper.py)."""
+
+    @torch.no_grad()
+    def generate_with_images(self, prompts: Sequence, images: torch.Tensor,
+                             sampling_params: Optional[SamplingParams] = None, generator=None):
+        sp = sampling_params or SamplingParams()
+        toks = [self.tokenizer.tokenize(p) if isinstance(p, str) else list(p) for p in prompts]
+        if len({len(t) for t in toks}) != 1:
+            raise ValueError("image-conditioned generation takes prompts of one length (pad them first)")
+        dev = next(self.model.parameters()).device
+        ids = torch.tensor(toks, dtype=torch.long, device=dev)
+        was_training = self.model.training
+        self.model.eval()
+        gen = []
+        done = torch.zeros(len(toks), dtype=torch.bool, device=dev)
+        for step in range(sp.num_tokens_to_generate):
+            # no cache across the image splice: the sequence is short and the model decides where the image goes
+            logits = self.model(images, ids)
+            new = sample_from_logits(logits[:, -1].float(), sp, None, generator)
+            if self.eod is not None:
+                new = torch.where(done, torch.full_like(new, self.eod), new)
+                done |= new == self.eod
+            gen.append(new)
+            ids = torch.cat((ids, new[:, None]), dim=1)
+            if self.eod is not None and bool(done.all()):
+                break
+        self.model.train(was_training)
+        g = torch.stack(gen, dim=1).tolist() if gen else [[] for _ in toks]
+        out = []
+        for i, t in enumerate(toks):
+            seq = g[i]
+            if self.eod is not None and self.eod in seq:
+                seq = seq[:seq.index(self.eod) + 1]
+            req = InferenceRequest(i, t, sp, seq, [], "completed")
+            if self.tokenizer is not None:
+                req.generated_text = self.tokenizer.detokenize(seq)
+            out.append(req)
+        return out

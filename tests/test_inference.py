@@ -101,3 +101,60 @@ def test_engines_gpu_decode_kernel():
             row = lg[len(p) + i - 1]
             assert row[t] >= row.max() - 0.15
     assert len(st.generate(prompts, sp)) == 2
+
+
+def test_dynamic_engine_streams_tokens_as_they_are_produced():
+    model = _model()
+    prompts = [[5, 9, 2, 33, 7], [11, 4, 6]]
+    eng = DynamicInferenceEngine(model, max_requests=2, max_sequence_length=32, chunk_size=4, num_chunks=16)
+    got = {0: [], 1: []}
+    order, finished = [], set()
+    for rid, tok, delta, fin in eng.stream(prompts, SamplingParams(top_k=1, num_tokens_to_generate=4)):
+        got[rid].append(tok)
+        order.append(rid)
+        assert delta is None                      # no tokenizer attached
+        if fin:
+            finished.add(rid)
+    for rid, p in enumerate(prompts):
+        assert got[rid] == _greedy_reference(model, p, 4)
+    assert finished == {0, 1}
+    assert order[:4].count(0) == 2 and order[:4].count(1) == 2      # interleaved: both requests advance every step
+
+
+def test_encoder_decoder_engine_matches_a_manual_greedy_loop():
+    from megatron_lm_b200.inference import EncoderDecoderInferenceEngine
+    from megatron_lm_b200.models.t5 import T5Model
+    torch.manual_seed(3)
+    cfg = TransformerConfig(num_layers=2, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+                            attention_dropout=0.0)
+    m = T5Model(cfg, vocab_size=64, max_sequence_length=16).eval()
+    enc = [[3, 4, 5, 6, 7, 8]]
+    out = EncoderDecoderInferenceEngine(m, bos_id=1, max_target_length=8).generate(
+        enc, SamplingParams(top_k=1, num_tokens_to_generate=5))
+    dec = [1]
+    with torch.no_grad():
+        for _ in range(5):
+            logits = m(torch.tensor(enc), torch.tensor([dec]))
+            dec.append(int(logits[0, -1].float().argmax()))
+    assert out[0].generated_tokens == dec[1:]
+
+
+def test_vlm_engine_generates_from_an_image_and_a_prompt():
+    from megatron_lm_b200.inference import VLMInferenceEngine
+    from megatron_lm_b200.models.multimodal import LLaVAModel
+    torch.manual_seed(0)
+
+    def cfg(h=32):
+        return TransformerConfig(num_layers=1, hidden_size=h, num_attention_heads=4, ffn_hidden_size=2 * h,
+                                 hidden_dropout=0.0, attention_dropout=0.0)
+    m = LLaVAModel(cfg(), 64, 64, cfg(16), cfg(), img_h=8, img_w=8, patch_dim=4, drop_vision_class_token=True,
+                   image_token_index=-200).eval()
+    images = torch.randn(1, 3, 8, 8)
+    eng = VLMInferenceEngine(m, max_batch_size=1, max_sequence_length=32)
+    out = eng.generate_with_images([[5, -200, 7]], images, SamplingParams(top_k=1, num_tokens_to_generate=3))
+    ids = [5, -200, 7]
+    with torch.no_grad():
+        for _ in range(3):
+            logits = m(images, torch.tensor([ids]))
+            ids.append(int(logits[0, -1].float().argmax()))
+    assert out[0].generated_tokens == ids[3:]
