@@ -11,6 +11,7 @@ validation in ``__post_init__`` keeps the combination rules of the reference
 from __future__ import annotations
 
 import math
+import dataclasses
 from dataclasses import dataclass, field
 from typing import Any, Callable, List, Optional, Tuple, Union
 
@@ -109,6 +110,42 @@ class ModelParallelConfig:
             self.microbatch_group_size_per_vp_stage = self.pipeline_model_parallel_size
         if self.overlap_p2p_comm_warmup_flush and not self.overlap_p2p_comm:
             raise ValueError("overlap_p2p_comm_warmup_flush requires overlap_p2p_comm")
+
+
+# Fields of the reference's configuration that this framework accepts (so configurations carry over) but does not
+# implement, and that would change the numerics, the model or the memory plan if they were honoured: asking for one
+# of them stops the construction of the configuration instead of silently building something else.  Fields that
+# only pick between implementations of the same mathematics (fusion switches, library back ends, CUDA-graph and
+# communication-overlap tuning knobs) are accepted without effect: there is one implementation here.
+UNSUPPORTED_FIELDS = {
+    "apply_residual_connection_post_layernorm": "the residual is always taken before the norm",
+    "window_size": "sliding-window attention is not built",
+    "cpu_offloading": "activation / weight offloading to the host is not built",
+    "fp8_dot_product_attention": "attention runs in bf16 / fp16",
+    "fp8_multi_head_attention": "attention runs in bf16 / fp16",
+    "no_rope_freq": "layers without rotary embedding are not built",
+    "moe_router_force_load_balancing": "forced uniform routing is not built",
+    "moe_apply_probs_on_input": "routing weights are applied to the expert output",
+    "moe_router_topk_limited_devices": "device-limited routing is expressed with moe_router_num_groups / group_topk",
+    "moe_layer_recompute": "use recompute_granularity / recompute_modules",
+    "delay_wgrad_compute": "weight gradients are computed with their layer's backward",
+    "init_model_with_meta_device": "parameters are created on their device",
+    "use_kitchen": "the Kitchen quantisation back end is not built",
+    "quant_recipe": "per-layer quantisation recipes are not built",
+    "heterogeneous_block_specs": "build heterogeneous models through models.heterogeneous",
+}
+
+
+def check_unsupported_fields(cfg) -> None:
+    defaults = {f.name: f.default for f in dataclasses.fields(type(cfg)) if f.default is not dataclasses.MISSING}
+    for name, why in UNSUPPORTED_FIELDS.items():
+        if not hasattr(cfg, name):
+            continue
+        v = getattr(cfg, name)
+        d = defaults.get(name)
+        if v == d or (v in (None, False, 0) and d in (None, False, 0)):
+            continue
+        raise ValueError(f"TransformerConfig.{name} = {v!r} is not supported: {why}")
 
 
 def init_method_normal(sigma: float) -> Callable:
@@ -285,6 +322,7 @@ class TransformerConfig(ModelParallelConfig):
             self.params_dtype = torch.float16
         if self.num_layers <= 0 or self.hidden_size <= 0 or self.num_attention_heads <= 0:
             raise ValueError("num_layers, hidden_size and num_attention_heads must be set")
+        check_unsupported_fields(self)
         if self.num_attention_heads % self.tensor_model_parallel_size != 0:
             raise ValueError(
                 f"num_attention_heads ({self.num_attention_heads}) must be divisible by "

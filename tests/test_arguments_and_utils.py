@@ -323,3 +323,14 @@ def test_renaming_flags_are_plumbed():
     assert cfg.num_layers_in_first_pipeline_stage == 2 and args.position_embedding_type == "rope"
     d = ddp_config_from_args(args)
     assert d.grad_reduce_in_fp32 is False and d.num_buckets == 3
+
+
+def test_unsupported_config_fields_are_refused():
+    from megatron_lm_b200.config import UNSUPPORTED_FIELDS, TransformerConfig
+    base = dict(num_layers=1, hidden_size=32, num_attention_heads=4)
+    TransformerConfig(**base)                                           # defaults pass
+    for name, value in (("window_size", (128, 0)), ("apply_residual_connection_post_layernorm", True),
+                        ("cpu_offloading", True), ("fp8_dot_product_attention", True)):
+        assert name in UNSUPPORTED_FIELDS
+        with pytest.raises(ValueError, match="not supported"):
+            TransformerConfig(**base, **{name: value})
