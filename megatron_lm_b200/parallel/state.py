@@ -293,8 +293,13 @@ def initialize_model_parallel(
                 for kind in ("F", "B"):
                     pg = None
                     if not virtual and dist.is_initialized():
-                        pg = dist.new_group(pair, backend=pp_backend, timeout=timeout,
-                                            **({"pg_options": ch_opts} if ch_opts is not None else {}))
+                        try:
+                            pg = dist.new_group(pair, backend=pp_backend, timeout=timeout,
+                                                **({"pg_options": ch_opts} if ch_opts is not None else {}))
+                        except (RuntimeError, TypeError, ValueError):
+                            # a build of the collective library that does not take the channel cap: default options
+                            ch_opts = None
+                            pg = dist.new_group(pair, backend=pp_backend, timeout=timeout)
                     if rank in ranks and rank in pair:
                         _S.pp_channels[(kind, s)] = pg
     # embedding groups: first and last pipeline stage (tied embeddings)
