@@ -229,8 +229,13 @@ class GPTModel(nn.Module):
             if ref_ids is None or ref_ids.shape[0] != 1:
                 raise ValueError("packed sequences come as one row of tokens, [1, total]")
             total = ref_ids.shape[1]
-            seg_mask = packed_seq_params.block_mask(total, ref_ids.device)
-            attention_mask = seg_mask if attention_mask is None else (attention_mask.bool() | seg_mask)
+            if ref_ids.is_cuda and attention_mask is None:
+                # GPU: per-segment causal flash attention on slices of the fused QKV activation, no dense mask
+                from ..packed_seq_params import PackedSegments
+                attention_mask = PackedSegments(packed_seq_params.segment_bounds(total))
+            else:
+                seg_mask = packed_seq_params.block_mask(total, ref_ids.device)
+                attention_mask = seg_mask if attention_mask is None else (attention_mask.bool() | seg_mask)
             if position_ids is None:
                 position_ids = packed_seq_params.positions(total, ref_ids.device).unsqueeze(0)
         if inference_context is not None:

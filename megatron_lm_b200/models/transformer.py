@@ -259,7 +259,18 @@ class SelfAttention(nn.Module):
                                                  causal=self.causal)
             out, bias = self.linear_proj(ctx_out.reshape(s, b, self.np_local * self.hn))
             return out, bias
-        if attention_mask is not None and inference_context is None:
+        from ..packed_seq_params import PackedSegments
+        if isinstance(attention_mask, PackedSegments) and inference_context is None:
+            # packed row: every document is its own causal attention problem on a slice of the fused buffer
+            # (sequence parallelism has already gathered the row: qkv5 holds all tokens of this rank's heads)
+            outs = []
+            bnd = attention_mask.bounds
+            for s0, s1 in zip(bnd[:-1], bnd[1:]):
+                if s1 > s0:
+                    outs.append(self._core(qkv5[s0:s1], None if cos is None else cos[s0:s1],
+                                           None if sin is None else sin[s0:s1]))
+            ctx_out = outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
+        elif attention_mask is not None and inference_context is None:
             if cos is not None:
                 qkv5 = ops.apply_rope_qkv_(qkv5.clone() if qkv5.is_cuda else qkv5, cos, sin,
                                            self.config.rotary_interleaved)

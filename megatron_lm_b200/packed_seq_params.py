@@ -23,6 +23,9 @@ class PackedSeqParams:
     cu_seqlens_kv_padded: Optional[torch.Tensor] = None
     max_seqlen_q: Optional[int] = None
     max_seqlen_kv: Optional[int] = None
+    # the same boundaries as a host list, when the caller has them: lets the attention cut the row into segments
+    # without reading a device tensor back
+    bounds_host: Optional[list] = None
 
     def _bounds(self) -> torch.Tensor:
         b = self.cu_seqlens_q_padded if self.cu_seqlens_q_padded is not None else self.cu_seqlens_q
@@ -52,5 +55,31 @@ class PackedSeqParams:
     def from_lengths(cls, lengths, device=None) -> "PackedSeqParams":
         ln = torch.as_tensor(lengths, dtype=torch.int32, device=device)
         cu = torch.cat((ln.new_zeros(1), ln.cumsum(0).to(torch.int32)))
-        m = int(ln.max()) if ln.numel() else 0
-        return cls("thd", cu, cu.clone(), None, None, m, m)
+        host = [int(v) for v in (lengths.tolist() if torch.is_tensor(lengths) else lengths)]
+        m = max(host) if host else 0
+        bounds = [0]
+        for n in host:
+            bounds.append(bounds[-1] + n)
+        return cls("thd", cu, cu.clone(), None, None, m, m, bounds)
+
+    def segment_bounds(self, total: int) -> list:
+        """Host list [0, ..., total] of segment boundaries (tokens after the last boundary form a segment)."""
+        b = self.bounds_host if self.bounds_host is not None else [int(v) for v in self._bounds().tolist()]
+        b = [v for v in b if v <= total]
+        if not b or b[0] != 0:
+            b = [0] + b
+        if b[-1] < total:
+            b.append(total)
+        return b
+
+
+class PackedSegments:
+    """What the attention layers receive in place of a dense mask for a packed row on a GPU: the host-side
+    segment boundaries.  Every segment then runs as its own causal flash-attention call on a slice of the fused
+    QKV activation - no [total, total] mask is ever built."""
+
+    def __init__(self, bounds):
+        self.bounds = list(bounds)
+
+    def __len__(self):
+        return len(self.bounds) - 1
