@@ -78,6 +78,24 @@ __device__ __forceinline__ void store_chunk_global(void* dst, const float (&v)[3
     d[q] = make_uint4(pack_lp(v[q * 8], v[q * 8 + 1], bf), pack_lp(v[q * 8 + 2], v[q * 8 + 3], bf),
                       pack_lp(v[q * 8 + 4], v[q * 8 + 5], bf), pack_lp(v[q * 8 + 6], v[q * 8 + 7], bf));
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 rows = lanes, two 16-bit K elements per 32-bit column) comes
+// from tensor memory, where the compute warps have just written it - it never goes through shared memory
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp writes row (lane base + t)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // half a row (32 values as 16 packed words, columns [32 half, 32 half + 32)) of a [rows x 64] K-major swizzled tile
 __device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int row, int half, const uint32_t (&w)[16]) {
@@ -512,6 +530,202 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
 
+// ============================================================================ backward: dQ, dS kept in tensor memory
+// Same product as attn_bwd_dq_kernel with two changes that take shared-memory traffic and latency out of a step:
+//   * dS (bf16) is written by the compute warps into tensor memory and is the A operand of dQ += dS K straight from
+//     there (`tcgen05.mma` with A in TMEM): no 16 KB store + 16 KB re-read through shared memory per step;
+//   * S and dP are double buffered in tensor memory, so the products of step t + 1 are already complete when the
+//     compute warps finish step t, and those of step t + 2 are issued as soon as dQ of step t is.
+// Tensor memory columns: S0 | dP0 | S1 | dP1 (64 each) | dQ (D) | dS0 | dS1 (32 each).
+template <int D>
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                      const AttnParams p) {
+  constexpr int BM = 128, BN = 64;
+  constexpr int QB = D * 256, KVB = D * 128, QC = 16384, KC = 8192;
+  constexpr uint32_t TCOLS = 512;
+  constexpr int NST = 4;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + QB;
+  uint8_t* sK = sdO + QB;
+  uint8_t* sV = sK + NST * KVB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * KVB);
+  // 0 q_full | kv_full[4] | kv_empty[4] | sdp_full[2] | sdp_empty[2] | ds_full[2] | ds_free[2]
+  constexpr int KF = 1, KE = KF + NST, SF = KE + NST, SE = SF + 2, DF = SE + 2, DR = DF + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DR + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_qtiles = (p.sq + BM - 1) / BM;
+  const int heads = p.ng * p.qpg;
+  const int qt = n_qtiles - 1 - (int)(blockIdx.x / (heads * p.b));
+  const int hb = blockIdx.x % (heads * p.b);
+  const int bb = hb / heads, hh = hb % heads, g = hh / p.qpg, j = hh % p.qpg;
+  const int s0 = qt * BM;
+  int kv_end = p.sk;
+  if (p.causal) { kv_end = s0 + BM + p.off; if (kv_end > p.sk) kv_end = p.sk; }
+  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(KF + i), 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(B(SF + i), 1); mbar_init(B(SE + i), 8); mbar_init(B(DF + i), 8); mbar_init(B(DR + i), 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  auto tS = [&](int b) { return tmem + (uint32_t)(128 * b); };
+  auto tdP = [&](int b) { return tmem + (uint32_t)(128 * b + 64); };
+  const uint32_t tdQ = tmem + 256;
+  auto tdS = [&](int b) { return tmem + 256 + (uint32_t)D + (uint32_t)(32 * b); };
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(B(0), 2 * QB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_5d(smem_u32(sQ) + c * QC, &tmQ, B(0), c * 64, j, g, bb, s0);
+        tma_load_5d(smem_u32(sdO) + c * QC, &tmdO, B(0), c * 64, j, g, bb, s0);
+      }
+      for (int t = 0; t < n_kv; ++t) {
+        const int st = t % NST;
+        if (!mbar_wait(B(KE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(KF + st), 2 * KVB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(KF + st), c * 64, 0, g, bb, t * BN);
+          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(KF + st), c * 64, 0, g, bb, t * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);
+      const uint32_t idesc_q = make_idesc(BM, D, p.lp_fmt, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV);
+      bool ok = true;
+      // S and dP of step t into buffer t & 1 (its previous contents, step t - 2, are in the compute warps' registers)
+      auto issue_sdp = [&](int t) -> bool {
+        const int b = t & 1;
+        const uint32_t k = (uint32_t)(t >> 1);
+        if (!mbar_wait(B(KF + t % NST), ((uint32_t)(t / NST)) & 1u, abort_flag, p.status, 24)) return false;
+        if (!mbar_wait(B(SE + b), (k & 1u) ^ 1u, abort_flag, p.status, 25)) return false;
+        fence_after_sync();
+        const uint32_t kb = aK + (t % NST) * KVB, vb = aV + (t % NST) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS(b), kmajor_desc(aQ, kk, QC), kmajor_desc(kb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP(b), kmajor_desc(adO, kk, QC), kmajor_desc(vb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF + b));
+        return true;
+      };
+      ok = mbar_wait(B(0), 0, abort_flag, p.status, 22);
+      if (ok) ok = issue_sdp(0);
+      if (ok && n_kv > 1) ok = issue_sdp(1);
+      for (int t = 0; t < n_kv && ok; ++t) {
+        const int b = t & 1;
+        if (!mbar_wait(B(DF + b), ((uint32_t)(t >> 1)) & 1u, abort_flag, p.status, 26)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t kb = aK + (t % NST) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tdQ, tdS(b) + (uint32_t)(kk * 8), mnmajor_desc(kb, kk, KC), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(KE + (t % NST)));         // K / V of this step may be overwritten
+        mma_commit(B(DR + b));                 // and so may dS of this buffer
+        if (t + 2 < n_kv) ok = issue_sdp(t + 2);
+      }
+    }
+  } else if (n_kv > 0) {
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    const int qrow = s0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const long stat_idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qrow;
+    const float lse2 = qrow < p.sq ? p.lse[stat_idx] * kLog2e : 0.f;
+    const float dlt = qrow < p.sq ? p.delta[stat_idx] : 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_kv; ++t) {
+      const int n0 = t * BN;
+      const int b = t & 1;
+      const uint32_t k = (uint32_t)(t >> 1);
+      if (!mbar_wait(B(SF + b), k & 1u, abort_flag, p.status, 27)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t w[16];
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS(b) + lane_base + half * 32, rs);
+      tmem_ld32(tdP(b) + lane_base + half * 32, rp);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(SE + b));
+      const bool need_mask = (p.causal && (n0 + BN - 1 > s0 + p.off)) || (n0 + BN > p.sk) || (s0 + BM > p.sq);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int kv = n0 + half * 32 + 2 * c + e;
+            const bool masked = (p.causal && kv > qrow + p.off) || kv >= p.sk || qrow >= p.sq;
+            const float pr = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[2 * c + e]), p.scale_log2, -lse2));
+            ds[e] = pr * (__uint_as_float(rp[2 * c + e]) - dlt) * p.scale;
+          }
+          w[c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[2 * c]), p.scale_log2, -lse2));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[2 * c + 1]), p.scale_log2, -lse2));
+          w[c] = pack_lp(p0 * (__uint_as_float(rp[2 * c]) - dlt) * p.scale,
+                         p1 * (__uint_as_float(rp[2 * c + 1]) - dlt) * p.scale, p.lp_fmt);
+        }
+      }
+      // dS of step t - 2 (same buffer) must have been consumed by its dQ product
+      if (!mbar_wait(B(DR + b), (k & 1u) ^ 1u, abort_flag, p.status, 28)) { ok = false; break; }
+      fence_after_sync();
+      tmem_st16(tdS(b) + lane_base + half * 16, w);     // keys [32 half, 32 half + 32) = 16 packed columns
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(DF + b));
+    }
+    const int bl = (n_kv - 1) & 1;
+    if (ok && mbar_wait(B(DR + bl), ((uint32_t)((n_kv - 1) >> 1)) & 1u, abort_flag, p.status, 29)) {
+      fence_after_sync();
+      uint8_t* drow = reinterpret_cast<uint8_t*>(p.dq) +
+                      2 * ((long)qrow * p.dq_s + (long)bb * p.dq_b + (long)g * p.dq_g + (long)j * p.dq_j);
+#pragma unroll 1
+      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tdQ + lane_base + c, o);
+        tmem_wait_ld();
+        if (qrow < p.sq) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+          store_chunk_global(drow + c * 2, v, p.lp_fmt);
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
 // ============================================================================ backward: dK, dV
 template <int D>
 __global__ void __launch_bounds__(kAttnBwdThreads, 1)
@@ -827,6 +1041,21 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
     if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
     const int grid = ((sq + 127) / 128) * ng * qpg * b;
+    static int use_ts = -1;                                            // MLB_ATTN_TS=0: dS through shared memory
+    if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
+    if (use_ts) {
+      const int smem_ts = 2 * D * 256 + 8 * D * 128 + 256;             // Q, dO, four K/V stages
+      if (D == 128) {
+        static bool set = false;
+        if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<128>, smem_ts))) return rc; set = true; }
+        attn_bwd_dq_ts_kernel<128><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+      } else {
+        static bool set = false;
+        if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<64>, smem_ts))) return rc; set = true; }
+        attn_bwd_dq_ts_kernel<64><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+      }
+      MLB_CHECK_LAUNCH();
+    } else {
     const int smem = 2 * D * 256 + 8 * D * 128 + 16384 + 128;         // Q, dO, four K/V stages, dS
     if (D == 128) {
       static bool set = false;
@@ -838,6 +1067,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
       attn_bwd_dq_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
     }
     MLB_CHECK_LAUNCH();
+    }
   }
   {  // dK, dV: 128-row key tiles, 64-row query tiles
     CUtensorMap tmQ, tmK, tmV, tmdO;

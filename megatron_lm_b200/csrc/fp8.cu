@@ -134,62 +134,64 @@ __device__ __forceinline__ int e8m0_exponent_for(float amax, float fmax) {
 //   q_row  [rows, cols] : 32-element blocks along the row share a scale (operand with `cols` as reduction dim)
 //   q_colT [cols, rows] : x transposed, 32-element blocks along the *source column* share a scale (operand with
 //                         `rows` as reduction dim: data gradient of a weight, both weight-gradient operands)
-// with their scales in the atom layout.  64 x 64 tile per block of 256 threads: threads 0..127 quantise the tile's
-// 128 row blocks, threads 128..255 its 128 column blocks.
+// with their scales in the atom layout.  64 x 64 tile per block of 256 threads.  Every thread quantises 16 values
+// of a row block (two neighbouring lanes share a 32-element block and agree on its maximum by one shuffle), writes
+// them with one 16-byte store, then does the same for 16 values of a column block read out of the shared tile.
 template <typename T>
-__global__ void mxfp8_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
-                                  uint8_t* __restrict__ q_colT, uint8_t* __restrict__ sf_col, int rows, int cols,
-                                  int e5m2) {
+__global__ void __launch_bounds__(256)
+mxfp8_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
+                  uint8_t* __restrict__ q_colT, uint8_t* __restrict__ sf_col, int rows, int cols, int e5m2) {
   __shared__ float tile[64][65];
   const float fmax = e5m2 ? 57344.f : 448.f;
   const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int tr = threadIdx.x >> 2, tq = threadIdx.x & 3;          // row of the tile, 16-column quarter
+  float v[16];
   {
-    const int tr = threadIdx.x >> 2, tc = (threadIdx.x & 3) * 16;
-    float v[16];
-    if (r0 + tr < rows && c0 + tc < cols) {
-      load8(x + (size_t)(r0 + tr) * cols + c0 + tc, *reinterpret_cast<float(*)[8]>(v));
-      load8(x + (size_t)(r0 + tr) * cols + c0 + tc + 8, *reinterpret_cast<float(*)[8]>(v + 8));
+    const int r = r0 + tr, c = c0 + tq * 16;
+    if (r < rows && c < cols) {
+      load8(x + (size_t)r * cols + c, *reinterpret_cast<float(*)[8]>(v));
+      load8(x + (size_t)r * cols + c + 8, *reinterpret_cast<float(*)[8]>(v + 8));
     } else {
 #pragma unroll
       for (int i = 0; i < 16; ++i) v[i] = 0.f;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) tile[tr][tc + i] = v[i];
+    for (int i = 0; i < 16; ++i) tile[tr][tq * 16 + i] = v[i];
+  }
+  if (q_row != nullptr) {
+    // row-wise: lanes (tq = 0, 1) and (tq = 2, 3) hold the two halves of a 32-element block
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    const int e = e8m0_exponent_for(m, fmax);
+    const float sc = exp2f((float)-e);
+    const int r = r0 + tr, c = c0 + tq * 16;
+    if (r < rows && c < cols) {
+      uint4 o; uint8_t* b = reinterpret_cast<uint8_t*>(&o);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) b[i] = to_fp8(v[i] * sc, e5m2);
+      *reinterpret_cast<uint4*>(q_row + (size_t)r * cols + c) = o;
+      if ((tq & 1) == 0) sf_row[mx_sf_offset(r, c >> 5, (cols + 127) >> 7)] = (uint8_t)(e + 127);
+    }
   }
   __syncthreads();
-  const int t = threadIdx.x & 127;
-  if (threadIdx.x < 128) {
-    if (q_row == nullptr) return;
-    const int lr = t >> 1, blk = t & 1;                 // row of the tile, which 32-column block
-    const int r = r0 + lr, c = c0 + blk * 32;
-    if (r >= rows || c >= cols) return;
+  if (q_colT != nullptr) {
+    // column-wise: thread (column tr, row quarter tq) takes tile rows [16 tq, 16 tq + 16) of column tr
     float m = 0.f;
 #pragma unroll
-    for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(tile[lr][blk * 32 + k]));
+    for (int i = 0; i < 16; ++i) { v[i] = tile[tq * 16 + i][tr]; m = fmaxf(m, fabsf(v[i])); }
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
     const int e = e8m0_exponent_for(m, fmax);
     const float sc = exp2f((float)-e);
-    uint4 o[2]; uint8_t* b = reinterpret_cast<uint8_t*>(o);
+    const int c = c0 + tr, r = r0 + tq * 16;
+    if (c < cols && r < rows) {
+      uint4 o; uint8_t* b = reinterpret_cast<uint8_t*>(&o);
 #pragma unroll
-    for (int k = 0; k < 32; ++k) b[k] = to_fp8(tile[lr][blk * 32 + k] * sc, e5m2);
-    uint4* dst = reinterpret_cast<uint4*>(q_row + (size_t)r * cols + c);
-    dst[0] = o[0]; dst[1] = o[1];
-    sf_row[mx_sf_offset(r, c >> 5, (cols + 127) >> 7)] = (uint8_t)(e + 127);
-  } else {
-    if (q_colT == nullptr) return;
-    const int lc = t & 63, blk = t >> 6;                // column of the tile, which 32-row block
-    const int c = c0 + lc, r = r0 + blk * 32;
-    if (c >= cols || r >= rows) return;
-    float m = 0.f;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) m = fmaxf(m, fabsf(tile[blk * 32 + k][lc]));
-    const int e = e8m0_exponent_for(m, fmax);
-    const float sc = exp2f((float)-e);
-    uint4 o[2]; uint8_t* b = reinterpret_cast<uint8_t*>(o);
-#pragma unroll
-    for (int k = 0; k < 32; ++k) b[k] = to_fp8(tile[blk * 32 + k][lc] * sc, e5m2);
-    uint4* dst = reinterpret_cast<uint4*>(q_colT + (size_t)c * rows + r);
-    dst[0] = o[0]; dst[1] = o[1];
-    sf_col[mx_sf_offset(c, r >> 5, (rows + 127) >> 7)] = (uint8_t)(e + 127);
+      for (int i = 0; i < 16; ++i) b[i] = to_fp8(v[i] * sc, e5m2);
+      *reinterpret_cast<uint4*>(q_colT + (size_t)c * rows + r) = o;
+      if ((tq & 1) == 0) sf_col[mx_sf_offset(c, r >> 5, (rows + 127) >> 7)] = (uint8_t)(e + 127);
+    }
   }
 }
 
@@ -198,10 +200,11 @@ __global__ void mxfp8_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__
 using namespace mlb;
 
 // x [rows, cols] -> q_row [rows, cols] + sf_row and/or q_colT [cols, rows] + sf_col (either pair may be null);
-// rows and cols multiples of 32; the scale buffers hold mlb_mx_sf_bytes(rows, cols) resp. (cols, rows) bytes.
+// cols a multiple of 32 for the row-wise copy, rows a multiple of 32 for the column-wise one (both multiples of 16);
+// the scale buffers hold mlb_mx_sf_bytes(rows, cols) resp. (cols, rows) bytes.
 MLB_API int mlb_mxfp8_quantize_dual(int dtype, const void* x, void* q_row, void* sf_row, void* q_colT, void* sf_col,
                                     int rows, int cols, int e5m2, cudaStream_t st) {
-  if ((rows % 32) || (cols % 32)) return -3;
+  if ((rows % 16) || (cols % 16) || (q_row && (cols % 32)) || (q_colT && (rows % 32))) return -3;
   dim3 grid((cols + 63) / 64, (rows + 63) / 64);
   MLB_DISPATCH_ACT(dtype, T, (mxfp8_dual_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)q_row, (uint8_t*)sf_row,
                                                                         (uint8_t*)q_colT, (uint8_t*)sf_col, rows, cols,

@@ -5,7 +5,9 @@
 //
 // Tile: 256 rows (128 per CTA of the pair) x 192 columns.  Two 192-column fp32 accumulators take 384 of the 512
 // tensor-memory columns; the scale factors of the stage in flight need 12 more (4 for this CTA's 128 A rows, 8 for
-// up to 256 B rows), double buffered: 408 columns.  (A 256-column tile would leave no room for them.)
+// up to 256 B rows), in three buffers: 420 columns.  (A 256-column tile would leave no room for them.)  The scale
+// factors of the next stage are copied to tensor memory before the MMAs of the current stage are issued, so the
+// copy's latency hides behind them.
 //
 // Scale-factor layout in global memory ("atoms"): for a quantised matrix Q[rows, K] the scale of row r and K block
 // kb (32 elements) is the byte
@@ -112,7 +114,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   cluster_sync_all();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_sf = tmem_base + 2 * TN;           // 2 x 12 scale-factor columns behind the accumulators
+  const uint32_t tmem_sf = tmem_base + 2 * TN;           // 3 x 12 scale-factor columns behind the accumulators
 
   const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
@@ -162,7 +164,15 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int k = 0; k < 4; ++k) idesc[k] = make_idesc_mx(256, TN, p.a_fmt, p.b_fmt, k);
       int stage = 0; uint32_t phase = 0;
       int t = 0;
-      uint32_t n_stage = 0;
+      uint32_t g = 0;                      // stages consumed so far (over all tiles)
+      uint32_t cp_done = 0;                // stages whose scale factors have been sent to tensor memory
+      auto issue_cp = [&](uint32_t gs, int st) {
+        const uint32_t sf_addr = smem_u32(sSF + st * S::kSfBytes);
+        const uint32_t tsf = tmem_sf + (gs % 3u) * 12u;
+        sf_copy_pair(tsf, make_sf_desc(sf_addr));
+        sf_copy_pair(tsf + 4, make_sf_desc(sf_addr + 512));
+        sf_copy_pair(tsf + 8, make_sf_desc(sf_addr + 1024));
+      };
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
         int mb, nb; tile_mn(tile, mb, nb);
@@ -172,15 +182,16 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
-        for (int kb = 0; kb < num_kb; ++kb, ++n_stage) {
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
           fence_after_sync();
+          if (cp_done == g) { issue_cp(g, stage); ++cp_done; }
+          // the next stage (of this or the next tile) has usually landed already: start its scale-factor copy now
+          const int nst = (stage + 1 == kStages) ? 0 : stage + 1;
+          const uint32_t nph = (stage + 1 == kStages) ? (phase ^ 1u) : phase;
+          if (cp_done == g + 1 && mbar_try_wait(full(nst), nph)) { fence_after_sync(); issue_cp(g + 1, nst); ++cp_done; }
           const uint32_t a_addr = smem_u32(sA + stage * S::kABytes), b_addr = smem_u32(sB + stage * S::kBBytes);
-          const uint32_t sf_addr = smem_u32(sSF + stage * S::kSfBytes);
-          const uint32_t tsf = tmem_sf + (n_stage & 1u) * 12u;
-          sf_copy_pair(tsf, make_sf_desc(sf_addr));
-          sf_copy_pair(tsf + 4, make_sf_desc(sf_addr + 512));
-          sf_copy_pair(tsf + 8, make_sf_desc(sf_addr + 1024));
+          const uint32_t tsf = tmem_sf + (g % 3u) * 12u;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_mx_pair(d_tmem, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc[k],

@@ -203,8 +203,8 @@ def mxfp8_quantize_dual(x: torch.Tensor, fmt: int = 0, rowwise: bool = True, col
     megatron/core/fp8_utils.py:459-485)."""
     x2 = x.reshape(-1, x.shape[-1])
     rows, cols = x2.shape
-    if rows % 32 or cols % 32:
-        raise ValueError("MXFP8 blocks need both sizes to be multiples of 32")
+    if (rowwise and cols % 32) or (colwise and rows % 32) or rows % 16 or cols % 16:
+        raise ValueError("MXFP8 blocks of 32 need the scaled dimension to be a multiple of 32 (the other of 16)")
     dev = x.device
     if not x2.is_cuda:
         def one(m):      # m [R, K] float -> MxTensor, scaled along K
@@ -260,6 +260,26 @@ def gemm_mx(a: MxTensor, b: MxTensor, out: Optional[torch.Tensor] = None, out_dt
     return out
 
 
+# Quantised copies of a weight are reused by every microbatch of a step: the optimizer announces new weights by
+# advancing this counter (the bf16 weights are rewritten through raw pointers, which tensor version counters
+# do not see).
+_WEIGHT_EPOCH = [0]
+
+
+def weights_updated() -> None:
+    _WEIGHT_EPOCH[0] += 1
+
+
+def _quantized_weight(weight: torch.Tensor, need_col: bool):
+    c = getattr(weight, "_mx_cache", None)
+    key = (_WEIGHT_EPOCH[0], weight.data_ptr(), weight._version)
+    if c is not None and c[0] == key and (c[2] is not None or not need_col):
+        return c[1], c[2]
+    wr, wc = mxfp8_quantize_dual(weight.detach(), 0, colwise=need_col)
+    weight._mx_cache = (key, wr, wc)
+    return wr, wc
+
+
 class _MxLinearFn(torch.autograd.Function):
     """y = x W^T (+ bias) with MXFP8 operands (1 x 32 blocks, power-of-two scales): activations and weights e4m3,
     gradients ``grad_fmt``.  Every tensor is quantised once into the two copies its GEMMs need."""
@@ -268,7 +288,7 @@ class _MxLinearFn(torch.autograd.Function):
     def forward(ctx, x, weight, bias, grad_fmt):
         x2 = x.reshape(-1, x.shape[-1])
         xr, xc = mxfp8_quantize_dual(x2, 0, colwise=weight.requires_grad)
-        wr, wc = mxfp8_quantize_dual(weight, 0, colwise=x.requires_grad)
+        wr, wc = _quantized_weight(weight, x.requires_grad)
         y = gemm_mx(xr, wr, out_dtype=x.dtype, bias=None if bias is None else bias.to(x.dtype))
         ctx.xc, ctx.wc = xc, wc
         ctx.weight, ctx.bias, ctx.grad_fmt, ctx.x_shape, ctx.x_dtype = weight, bias, grad_fmt, x.shape, x.dtype

@@ -262,6 +262,8 @@ class MixedPrecisionOptimizer:
         for st in self.states:
             if getattr(st.buf, "peer", None) is not None:
                 st.buf.peer_barrier()            # every rank's pushed weights have landed before the next forward
+        from ..ops.fp8 import weights_updated
+        weights_updated()                        # cached FP8 copies of the weights are out of date
         mine = {id(st.buf) for st in self.states}
         for chunk in self.model_chunks:
             bufs = [b for b in chunk.buffers + chunk.expert_buffers if id(b) in mine]
