@@ -315,6 +315,241 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
 
+// ============================================================================ forward, two query tiles per CTA
+// One CTA per SM works on 256 query rows as two 128-row tiles that take turns on the tensor core: while the eight
+// softmax warps of one tile compute exp2, the products of the other tile run.  Per 128-key step and tile:
+//   S = Q K^T (128 x 128, fp32) into tensor memory; one thread per row reads it, writes P (16-bit) over the first
+//   64 columns of S, and O += P V takes P as the A operand straight from tensor memory.
+// Compared with attn_fwd_kernel (two independent 128-row CTAs per SM, 64-key steps, P through shared memory) a
+// K / V tile is copied into shared memory once for 256 rows instead of once per 128, the S product reads 8 KB of
+// operands per instruction of 128 x 128 x 16 instead of 6 KB per 128 x 64 x 16, and P is neither stored to nor
+// read from shared memory - shared-memory bandwidth, not the tensor core, was what bounded that kernel.
+// Tensor memory columns: S0 | S1 (128 each) | O0 | O1 (D each).  The products of one thread run in issue order,
+// which is what allows S of step t + 1 to overwrite P of step t right behind the P V product that reads it.
+constexpr int kAttnFwd2Threads = 320;
+template <int D>
+__global__ void __launch_bounds__(kAttnFwd2Threads, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  constexpr int BM = 128, BN = 128;
+  constexpr int QB = D * 256, KVB = D * 256, CH = 16384;               // tile bytes; bytes of a 64-column chunk
+  constexpr int NSLOT = 5;                                              // ring of K0 V0 K1 V1 K2 ...
+  constexpr uint32_t TCOLS = 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + 2 * QB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + NSLOT * KVB);
+  constexpr int QF = 0, KF = 2, KE = KF + NSLOT, SF = KE + NSLOT, PF = SF + 2, OD = PF + 2, NBAR = OD + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_qtiles = (p.sq + 2 * BM - 1) / (2 * BM);
+  const int heads = p.ng * p.qpg;
+  const int qt = n_qtiles - 1 - (int)(blockIdx.x / (heads * p.b));      // heavy (late) tiles first
+  const int hb = blockIdx.x % (heads * p.b);
+  const int bb = hb / heads, hh = hb % heads, g = hh / p.qpg, j = hh % p.qpg;
+  const int s0 = qt * 2 * BM;
+  auto steps_of = [&](int i) {
+    const int s0i = s0 + i * BM;
+    int kv_end = p.sk;
+    if (p.causal) { kv_end = s0i + BM + p.off; if (kv_end > p.sk) kv_end = p.sk; }
+    return (s0i < p.sq && kv_end > 0) ? (kv_end + BN - 1) / BN : 0;
+  };
+  const int n_t0 = steps_of(0), n_t1 = steps_of(1);
+  auto n_of = [&](int i) { return i ? n_t1 : n_t0; };
+  const int n_kv = n_t0 > n_t1 ? n_t0 : n_t1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(QF), 1); mbar_init(B(QF + 1), 1);
+    for (int i = 0; i < 2 * NSLOT; ++i) mbar_init(B(KF + i), 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(B(SF + i), 1); mbar_init(B(PF + i), 4); mbar_init(B(OD + i), 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  auto tS = [&](int i) { return tmem + (uint32_t)(128 * i); };
+  auto tO = [&](int i) { return tmem + 256u + (uint32_t)(D * i); };
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (n_of(i) > 0) {
+          mbar_expect_tx(B(QF + i), QB);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_5d(smem_u32(sQ) + i * QB + c * CH, &tmQ, B(QF + i), c * 64, j, g, bb, s0 + i * BM);
+        }
+      for (int u = 0; u < 2 * n_kv; ++u) {                              // u = 2 t: K of step t; 2 t + 1: V
+        const int slot = u % NSLOT;
+        if (!mbar_wait(B(KE + slot), (((uint32_t)(u / NSLOT)) & 1u) ^ 1u, abort_flag, p.status, 11)) break;
+        mbar_expect_tx(B(KF + slot), KVB);
+        const CUtensorMap* tm = (u & 1) ? &tmV : &tmK;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sKV) + slot * KVB + c * CH, tm, B(KF + slot), c * 64, 0, g, bb, (u >> 1) * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);
+      const uint32_t idesc_o = make_idesc(BM, D, p.lp_fmt, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aKV = smem_u32(sKV);
+      auto kv_ready = [&](int u) {
+        return mbar_wait(B(KF + u % NSLOT), ((uint32_t)(u / NSLOT)) & 1u, abort_flag, p.status, 13);
+      };
+      auto issue_s = [&](int i, int t) {
+        const uint32_t kb = aKV + ((2 * t) % NSLOT) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS(i), kmajor_desc(aQ + i * QB, kk, CH), kmajor_desc(kb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF + i));
+      };
+      auto issue_pv = [&](int i, int t) {
+        const uint32_t vb = aKV + ((2 * t + 1) % NSLOT) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tO(i), tS(i) + (uint32_t)(kk * 8), mnmajor_desc(vb, kk, CH), idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(OD + i));
+      };
+      bool ok = true;
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (ok && n_of(i) > 0) ok = mbar_wait(B(QF + i), 0, abort_flag, p.status, 12);
+      if (ok) ok = kv_ready(0);
+      if (ok) {
+        fence_after_sync();
+        if (n_t0 > 0) issue_s(0, 0);
+        if (n_t1 > 0) issue_s(1, 0);
+        mma_commit(B(KE + 0));
+      }
+      for (int t = 0; t < n_kv && ok; ++t) {
+        bool k_next_ready = false;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (t < n_of(i)) {
+            if (i == 0 || !(t < n_t0)) { if (!kv_ready(2 * t + 1)) { ok = false; break; } }
+            if (!mbar_wait(B(PF + i), (uint32_t)t & 1u, abort_flag, p.status, 16)) { ok = false; break; }
+            fence_after_sync();
+            issue_pv(i, t);
+          }
+          if (t + 1 < n_of(i)) {
+            if (!k_next_ready) { if (!kv_ready(2 * t + 2)) { ok = false; break; } k_next_ready = true; fence_after_sync(); }
+            issue_s(i, t + 1);
+          }
+        }
+        if (!ok) break;
+        mma_commit(B(KE + (2 * t + 1) % NSLOT));                      // V of this step
+        if (t + 1 < n_kv) mma_commit(B(KE + (2 * t + 2) % NSLOT));    // K of the next
+      }
+    }
+  } else {
+    const int i = (warp - 2) >> 2;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int s0i = s0 + i * BM;
+    const int qrow = s0i + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const int n_mine = n_of(i);
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_mine; ++t) {
+      const int n0 = t * BN;
+      if (!mbar_wait(B(SF + i), (uint32_t)t & 1u, abort_flag, p.status, 17)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS(i) + lane_base + c * 32, r[c]);
+      tmem_wait_ld();
+      const bool need_mask = (p.causal && (n0 + BN - 1 > s0i + p.off)) || (n0 + BN > p.sk);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kv = n0 + c * 32 + e;
+            if ((p.causal && kv > qrow + p.off) || kv >= p.sk) r[c][e] = 0xff800000u;       // -inf
+          }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        mx0 = fmaxf(mx0, __uint_as_float(r[0][e])); mx1 = fmaxf(mx1, __uint_as_float(r[1][e]));
+        mx2 = fmaxf(mx2, __uint_as_float(r[2][e])); mx3 = fmaxf(mx3, __uint_as_float(r[3][e]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      const float m_new = fmaxf(m_ref, mx);
+      const bool resc = m_new > m_ref + 8.f;
+      float alpha = 1.f;
+      if (resc) { alpha = fast_exp2(m_ref - m_new); m_ref = m_new; l *= alpha; }
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float a0 = fast_exp2(fmaf(__uint_as_float(r[c][2 * e]), p.scale_log2, neg_m));
+          const float a1 = fast_exp2(fmaf(__uint_as_float(r[c][2 * e + 1]), p.scale_log2, neg_m));
+          ls0 += a0; ls1 += a1;
+          w[e] = pack_lp(a0, a1, p.lp_fmt);
+        }
+        tmem_st16(tS(i) + lane_base + c * 16, w);                       // keys [32 c, 32 c + 32) -> 16 packed columns
+      }
+      l += ls0 + ls1;
+      if (t > 0 && __any_sync(0xffffffffu, resc)) {
+        // O of this tile has to be rescaled: its last product (step t - 1) must have completed
+        if (!mbar_wait(B(OD + i), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 18)) { ok = false; break; }
+        fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tO(i) + lane_base + c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st32(tO(i) + lane_base + c, o);
+        }
+      }
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(PF + i));
+    }
+    if (ok && n_mine > 0 && mbar_wait(B(OD + i), (uint32_t)(n_mine - 1) & 1u, abort_flag, p.status, 19)) {
+      fence_after_sync();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      2 * ((long)qrow * p.o_s + (long)bb * p.o_b + (long)g * p.o_g + (long)j * p.o_j);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tO(i) + lane_base + c, o);
+        tmem_wait_ld();
+        if (qrow < p.sq) {
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(o[e]) * inv_l;
+          store_chunk_global(orow + c * 2, v, p.lp_fmt);
+        }
+      }
+      if (qrow < p.sq)
+        p.lse[(((long)bb * p.ng + g) * p.qpg + j) * p.sq + qrow] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
 // ============================================================================ delta = rowsum(O * dO)
 __global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, float* __restrict__ delta,
                                   int sq, int b, int ng, int qpg, int D, long o_s, long o_b, long o_g, long o_j,
@@ -865,8 +1100,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         bar_sync_compute();
       }
+      if (!ok) continue;              // a wait gave up: keep meeting the other warps at the barrier above, do no more
       const float* stat = sStat + (t & 1) * 128 + half * 32;
-      if (!mbar_wait(B(SF), (uint32_t)t & 1u, abort_flag, p.status, 37)) { ok = false; break; }
+      if (!mbar_wait(B(SF), (uint32_t)t & 1u, abort_flag, p.status, 37)) { ok = false; continue; }
       fence_after_sync();
       uint32_t wp[16], wd[16];
       uint32_t rs[32], rp[32];
@@ -904,7 +1140,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       if (t > 0) {
-        if (!mbar_wait(B(PD), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 38)) { ok = false; break; }
+        if (!mbar_wait(B(PD), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 38)) { ok = false; continue; }
       }
       store_half_row_sw128(sP, row, half, wp);
       store_half_row_sw128(sdS, row, half, wd);
@@ -913,6 +1149,239 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (lane == 0) mbar_arrive(B(PF));
     }
     if (ok && mbar_wait(B(PD), (uint32_t)(n_steps - 1) & 1u, abort_flag, p.status, 39)) {
+      fence_after_sync();
+      uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
+      uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
+#pragma unroll 1
+      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
+        uint32_t o[32];
+        float v[32];
+        tmem_ld32(tdV + lane_base + c, o);
+        tmem_wait_ld();
+        if (krow < p.sk) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+          store_chunk_global(vrow + c * 2, v, p.lp_fmt);
+        }
+        tmem_ld32(tdK + lane_base + c, o);
+        tmem_wait_ld();
+        if (krow < p.sk) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+          store_chunk_global(krow_p + c * 2, v, p.lp_fmt);
+        }
+      }
+    }
+  } else {
+    // no query can see this key tile: its gradients are zero
+    const int ct = threadIdx.x - 64;
+    if (ct >= 0 && ct < 128) {
+      const int krow = n0 + ct;
+      if (krow < p.sk) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* vrow = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g));
+        uint4* kr = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g));
+        for (int c = 0; c < D / 8; ++c) { vrow[c] = z; kr[c] = z; }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
+// ============================================================================ backward: dK, dV, P^T and dS^T in tensor memory
+// attn_bwd_dkv_kernel with P^T and dS^T written over the S^T / dP^T columns they were computed from and used as the
+// A operands of dV += P^T dO and dK += dS^T Q from there, and with two S^T / dP^T buffers: the products of step
+// t + 2 are issued right behind dV / dK of step t (products of one thread run in issue order, so they may overwrite
+// what those read), and the compute warps never wait for a buffer.  A warp that owns query columns [32 h, 32 h + 32)
+// of a step writes its 16 packed columns at offset 32 h - inside the range only it reads - and the reduction steps
+// pick their A operand up at 0, 8, 32, 40.
+// Tensor memory columns: dV | dK (D each) | S^T0 dP^T0 | S^T1 dP^T1 (64 each).
+template <int D>
+__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+attn_bwd_dkv_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const AttnParams p) {
+  constexpr int BM = 128, BN = 64;                 // BM key rows per CTA, BN query rows per step
+  constexpr int KB = D * 256, QB = D * 128, KC = 16384, QC = 8192;
+  constexpr uint32_t TCOLS = 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KB;
+  constexpr int NST = 4;                                       // Q / dO stages: held from S^T to dK of their step
+  uint8_t* sQ = sV + KB;
+  uint8_t* sdO = sQ + NST * QB;
+  float* sStat = reinterpret_cast<float*>(sdO + NST * QB);     // [2][2][64] lse2 / delta per step parity
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 256);
+  // 0 kv_full | q_full[4] | q_empty[4] | sdp_full[2] | pds_full[2] | all products done
+  constexpr int QF = 1, QE = 1 + NST, SF = 1 + 2 * NST, PF = SF + 2, DN = PF + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DN + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_ktiles = (p.sk + BM - 1) / BM;
+  const int kt = blockIdx.x / (p.ng * p.b);                    // early key tiles see the most queries
+  const int gb = blockIdx.x % (p.ng * p.b);
+  const int bb = gb / p.ng, g = gb % p.ng;
+  const int n0 = kt * BM;
+  (void)n_ktiles;
+  // query tiles that can see at least one key of this tile: q + off >= n0
+  int q_begin = 0;
+  if (p.causal) { q_begin = n0 - p.off; if (q_begin < 0) q_begin = 0; }
+  const int qt0 = q_begin / BN;
+  const int n_qt = (p.sq + BN - 1) / BN;
+  const int per_head = n_qt > qt0 ? n_qt - qt0 : 0;
+  const int n_steps = per_head * p.qpg;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(1 + i), 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(B(SF + i), 1); mbar_init(B(PF + i), 8); }
+    mbar_init(B(DN), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tdV = tmem, tdK = tmem + D;
+  auto tS = [&](int b) { return tmem + (uint32_t)(2 * D + 128 * b); };
+  auto tdP = [&](int b) { return tmem + (uint32_t)(2 * D + 128 * b + 64); };
+
+  if (warp == 0) {
+    if (lane == 0 && n_steps > 0) {
+      mbar_expect_tx(B(0), 2 * KB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_5d(smem_u32(sK) + c * KC, &tmK, B(0), c * 64, 0, g, bb, n0);
+        tma_load_5d(smem_u32(sV) + c * KC, &tmV, B(0), c * 64, 0, g, bb, n0);
+      }
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t % NST;
+        const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+        if (!mbar_wait(B(QE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
+        mbar_expect_tx(B(QF + st), 2 * QB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_5d(smem_u32(sQ) + st * QB + c * QC, &tmQ, B(QF + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sdO) + st * QB + c * QC, &tmdO, B(QF + st), c * 64, j, g, bb, q0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_steps > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);       // S^T, dP^T
+      const uint32_t idesc_g = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dV, dK: A K-major, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      bool ok = true;
+      auto issue_sdp = [&](int t) -> bool {
+        const int b = t & 1;
+        if (!mbar_wait(B(QF + t % NST), ((uint32_t)(t / NST)) & 1u, abort_flag, p.status, 34)) return false;
+        fence_after_sync();
+        const uint32_t qb = aQ + (t % NST) * QB, ob = adO + (t % NST) * QB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS(b), kmajor_desc(aK, kk, KC), kmajor_desc(qb, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP(b), kmajor_desc(aV, kk, KC), kmajor_desc(ob, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF + b));
+        return true;
+      };
+      ok = mbar_wait(B(0), 0, abort_flag, p.status, 32);
+      if (ok) ok = issue_sdp(0);
+      if (ok && n_steps > 1) ok = issue_sdp(1);
+      for (int t = 0; t < n_steps && ok; ++t) {
+        const int b = t & 1;
+        if (!mbar_wait(B(PF + b), ((uint32_t)(t >> 1)) & 1u, abort_flag, p.status, 36)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t qb = aQ + (t % NST) * QB, ob = adO + (t % NST) * QB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tdV, tS(b) + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(ob, kk, QC), idesc_g,
+                     (t > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tdK, tdP(b) + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(qb, kk, QC), idesc_g,
+                     (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(QE + (t % NST)));
+        if (t + 2 < n_steps) ok = issue_sdp(t + 2);
+      }
+      if (ok) mma_commit(B(DN));
+    }
+  } else if (n_steps > 0) {
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                 // which 32 of a step's 64 query columns this warp takes
+    const int row = quad * 32 + lane;
+    const int ct = threadIdx.x - 64;                 // 0..255 among the compute threads
+    const int krow = n0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    bool ok = true;
+    for (int t = 0; t < n_steps; ++t) {
+      const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+      // stage this step's per-query statistics (64 lse2 + 64 delta) in shared memory
+      {
+        float* dst = sStat + (t & 1) * 128;
+        if (ct < 128) {
+          const int qi = q0 + (ct & 63);
+          const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
+          float v = 0.f;
+          if (qi < p.sq) v = (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
+          dst[ct] = v;
+        }
+        bar_sync_compute();
+      }
+      if (!ok) continue;              // a wait gave up: keep meeting the other warps at the barrier above, do no more
+      const float* stat = sStat + (t & 1) * 128 + half * 32;
+      const int b = t & 1;
+      if (!mbar_wait(B(SF + b), ((uint32_t)(t >> 1)) & 1u, abort_flag, p.status, 37)) { ok = false; continue; }
+      fence_after_sync();
+      uint32_t wp[16], wd[16];
+      uint32_t rs[32], rp[32];
+      tmem_ld32(tS(b) + lane_base + half * 32, rs);
+      tmem_ld32(tdP(b) + lane_base + half * 32, rp);
+      tmem_wait_ld();
+      // per-element masks only where the step touches the diagonal or the ends of the sequences
+      const bool need_mask = (p.causal && (n0 + BM - 1 > q0 + p.off)) || (q0 + BN > p.sq) || (n0 + BM > p.sk);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = 2 * c + e;
+            const int qi = q0 + half * 32 + col;
+            const bool masked = (p.causal && krow > qi + p.off) || qi >= p.sq || krow >= p.sk;
+            pr[e] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[col]), p.scale_log2, -stat[col]));
+            ds[e] = pr[e] * (__uint_as_float(rp[col]) - stat[64 + col]) * p.scale;
+          }
+          wp[c] = pack_lp(pr[0], pr[1], p.lp_fmt);
+          wd[c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[2 * c]), p.scale_log2, -stat[2 * c]));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[2 * c + 1]), p.scale_log2, -stat[2 * c + 1]));
+          wp[c] = pack_lp(p0, p1, p.lp_fmt);
+          wd[c] = pack_lp(p0 * (__uint_as_float(rp[2 * c]) - stat[64 + 2 * c]) * p.scale,
+                          p1 * (__uint_as_float(rp[2 * c + 1]) - stat[64 + 2 * c + 1]) * p.scale, p.lp_fmt);
+        }
+      }
+      tmem_st16(tS(b) + lane_base + half * 32, wp);
+      tmem_st16(tdP(b) + lane_base + half * 32, wd);
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(PF + b));
+    }
+    if (ok && mbar_wait(B(DN), 0, abort_flag, p.status, 39)) {
       fence_after_sync();
       uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
       uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
@@ -992,6 +1461,26 @@ MLB_API int mlb_attn_fwd(int lp_fmt, const void* q, const void* k, const void* v
   p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
   p.o = o; p.o_s = o_s; p.o_b = o_b; p.o_g = o_g; p.o_j = o_j; p.lse = lse;
+  static int use_v2 = -1;                                    // MLB_ATTN_FWD2=0: two independent 128-row CTAs per SM
+  if (use_v2 < 0) { const char* e = getenv("MLB_ATTN_FWD2"); use_v2 = (e && e[0] == '0') ? 0 : 1; }
+  if (use_v2) {
+    CUtensorMap tmK2, tmV2;
+    if ((rc = make_tmap5(&tmK2, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
+    if ((rc = make_tmap5(&tmV2, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
+    const int grid2 = ((sq + 255) / 256) * ng * qpg * b;
+    const int smem2 = 2 * D * 256 + 5 * D * 256 + 256;
+    if (D == 128) {
+      static bool set = false;
+      if (!set) { if ((rc = set_smem(attn_fwd2_kernel<128>, smem2))) return rc; set = true; }
+      attn_fwd2_kernel<128><<<grid2, kAttnFwd2Threads, smem2, st>>>(tmQ, tmK2, tmV2, p);
+    } else {
+      static bool set = false;
+      if (!set) { if ((rc = set_smem(attn_fwd2_kernel<64>, smem2))) return rc; set = true; }
+      attn_fwd2_kernel<64><<<grid2, kAttnFwd2Threads, smem2, st>>>(tmQ, tmK2, tmV2, p);
+    }
+    MLB_CHECK_LAUNCH();
+    return 0;
+  }
   const int grid = ((sq + 127) / 128) * ng * qpg * b;
   const int smem = D * 256 + 4 * D * 128 + 16384 + 128;
   if (D == 128) {
@@ -1076,15 +1565,30 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
     if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
     const int grid = ((sk + 127) / 128) * ng * b;
-    const int smem = 2 * D * 256 + 6 * D * 128 + 2 * 16384 + 1024 + 128;  // K, V, three Q/dO stages, P, dS, stats
-    if (D == 128) {
-      static bool set = false;
-      if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, smem))) return rc; set = true; }
-      attn_bwd_dkv_kernel<128><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+    static int use_ts = -1;                                            // MLB_ATTN_TS=0: P^T, dS^T through shared memory
+    if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
+    if (use_ts) {
+      const int smem_ts = 2 * D * 256 + 8 * D * 128 + 1024 + 256;      // K, V, four Q/dO stages, stats
+      if (D == 128) {
+        static bool set = false;
+        if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<128>, smem_ts))) return rc; set = true; }
+        attn_bwd_dkv_ts_kernel<128><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+      } else {
+        static bool set = false;
+        if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<64>, smem_ts))) return rc; set = true; }
+        attn_bwd_dkv_ts_kernel<64><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+      }
     } else {
-      static bool set = false;
-      if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<64>, smem))) return rc; set = true; }
-      attn_bwd_dkv_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      const int smem = 2 * D * 256 + 6 * D * 128 + 2 * 16384 + 1024 + 128;  // K, V, three Q/dO stages, P, dS, stats
+      if (D == 128) {
+        static bool set = false;
+        if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, smem))) return rc; set = true; }
+        attn_bwd_dkv_kernel<128><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      } else {
+        static bool set = false;
+        if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<64>, smem))) return rc; set = true; }
+        attn_bwd_dkv_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+      }
     }
     MLB_CHECK_LAUNCH();
   }

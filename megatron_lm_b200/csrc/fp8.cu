@@ -134,63 +134,77 @@ __device__ __forceinline__ int e8m0_exponent_for(float amax, float fmax) {
 //   q_row  [rows, cols] : 32-element blocks along the row share a scale (operand with `cols` as reduction dim)
 //   q_colT [cols, rows] : x transposed, 32-element blocks along the *source column* share a scale (operand with
 //                         `rows` as reduction dim: data gradient of a weight, both weight-gradient operands)
-// with their scales in the atom layout.  64 x 64 tile per block of 256 threads.  Every thread quantises 16 values
-// of a row block (two neighbouring lanes share a 32-element block and agree on its maximum by one shuffle), writes
-// them with one 16-byte store, then does the same for 16 values of a column block read out of the shared tile.
-template <typename T>
+// with their scales in the atom layout.  64 x 128 tile per block of 256 threads.  A thread owns one whole scale
+// block in either phase - 32 values of a row (64 contiguous bytes in, 32 out), then 32 values of a column read out
+// of the shared tile with consecutive lanes on consecutive columns (conflict free) and written as 32 contiguous
+// bytes of the transposed copy - so there is no exchange between lanes and every global access fills its sectors.
+__device__ __forceinline__ int e8m0_exponent_bits(float amax, float fmax) {
+  // ceil(log2(amax / fmax)) from the bits of the quotient: exponent, plus one when the mantissa is not zero
+  if (!(amax > 0.f)) return -127;
+  const uint32_t q = __float_as_uint(amax / fmax);
+  const int e = (int)(q >> 23) - 127 + ((q & 0x7fffffu) ? 1 : 0);
+  return max(-127, min(127, e));
+}
+template <bool E5M2>
+__device__ __forceinline__ void quantize32(const float (&v)[32], float fmax, uint4 (&o)[2], int& e) {
+  float m0 = 0.f, m1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { m0 = fmaxf(m0, fabsf(v[2 * i])); m1 = fmaxf(m1, fabsf(v[2 * i + 1])); }
+  e = e8m0_exponent_bits(fmaxf(m0, m1), fmax);
+  const float sc = exp2f((float)-e);
+  uint16_t* h = reinterpret_cast<uint16_t*>(o);
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    h[i] = (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(v[2 * i] * sc, v[2 * i + 1] * sc), __NV_SATFINITE,
+                                              E5M2 ? __NV_E5M2 : __NV_E4M3);
+}
+template <typename T, bool E5M2>
 __global__ void __launch_bounds__(256)
 mxfp8_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__ q_row, uint8_t* __restrict__ sf_row,
-                  uint8_t* __restrict__ q_colT, uint8_t* __restrict__ sf_col, int rows, int cols, int e5m2) {
-  __shared__ float tile[64][65];
-  const float fmax = e5m2 ? 57344.f : 448.f;
-  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
-  const int tr = threadIdx.x >> 2, tq = threadIdx.x & 3;          // row of the tile, 16-column quarter
-  float v[16];
+                  uint8_t* __restrict__ q_colT, uint8_t* __restrict__ sf_col, int rows, int cols) {
+  constexpr int PAD = 16 / sizeof(T);
+  __shared__ __align__(16) T tile[64][128 + PAD];
+  const float fmax = E5M2 ? 57344.f : 448.f;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 128;
   {
-    const int r = r0 + tr, c = c0 + tq * 16;
-    if (r < rows && c < cols) {
-      load8(x + (size_t)r * cols + c, *reinterpret_cast<float(*)[8]>(v));
-      load8(x + (size_t)r * cols + c + 8, *reinterpret_cast<float(*)[8]>(v + 8));
-    } else {
+    const int tr = threadIdx.x >> 2, tq = threadIdx.x & 3;          // row of the tile, 32-column quarter
+    const int r = r0 + tr, c = c0 + tq * 32;
+    float v[32];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    for (int k = 0; k < 4; ++k) {
+      if (r < rows && c + 8 * k + 8 <= cols) {
+        load8(x + (size_t)r * cols + c + 8 * k, *reinterpret_cast<float(*)[8]>(v + 8 * k));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[8 * k + i] = 0.f;
+      }
     }
+    if (q_colT != nullptr) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) tile[tr][tq * 16 + i] = v[i];
-  }
-  if (q_row != nullptr) {
-    // row-wise: lanes (tq = 0, 1) and (tq = 2, 3) hold the two halves of a 32-element block
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    const int e = e8m0_exponent_for(m, fmax);
-    const float sc = exp2f((float)-e);
-    const int r = r0 + tr, c = c0 + tq * 16;
-    if (r < rows && c < cols) {
-      uint4 o; uint8_t* b = reinterpret_cast<uint8_t*>(&o);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) b[i] = to_fp8(v[i] * sc, e5m2);
-      *reinterpret_cast<uint4*>(q_row + (size_t)r * cols + c) = o;
-      if ((tq & 1) == 0) sf_row[mx_sf_offset(r, c >> 5, (cols + 127) >> 7)] = (uint8_t)(e + 127);
+      for (int i = 0; i < 32; ++i) tile[tr][tq * 32 + i] = from_f<T>(v[i]);
+    }
+    if (q_row != nullptr && r < rows && c < cols) {
+      uint4 o[2]; int e;
+      quantize32<E5M2>(v, fmax, o, e);
+      uint4* dst = reinterpret_cast<uint4*>(q_row + (size_t)r * cols + c);
+      dst[0] = o[0]; dst[1] = o[1];
+      sf_row[mx_sf_offset(r, c >> 5, (cols + 127) >> 7)] = (uint8_t)(e + 127);
     }
   }
+  if (q_colT == nullptr) return;
   __syncthreads();
-  if (q_colT != nullptr) {
-    // column-wise: thread (column tr, row quarter tq) takes tile rows [16 tq, 16 tq + 16) of column tr
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) { v[i] = tile[tq * 16 + i][tr]; m = fmaxf(m, fabsf(v[i])); }
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    const int e = e8m0_exponent_for(m, fmax);
-    const float sc = exp2f((float)-e);
-    const int c = c0 + tr, r = r0 + tq * 16;
+  {
+    const int tc = threadIdx.x & 127, th = threadIdx.x >> 7;        // column of the tile, 32-row half
+    const int c = c0 + tc, r = r0 + th * 32;
     if (c < cols && r < rows) {
-      uint4 o; uint8_t* b = reinterpret_cast<uint8_t*>(&o);
+      float v[32];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) b[i] = to_fp8(v[i] * sc, e5m2);
-      *reinterpret_cast<uint4*>(q_colT + (size_t)c * rows + r) = o;
-      if ((tq & 1) == 0) sf_col[mx_sf_offset(c, r >> 5, (rows + 127) >> 7)] = (uint8_t)(e + 127);
+      for (int i = 0; i < 32; ++i) v[i] = to_f(tile[th * 32 + i][tc]);
+      uint4 o[2]; int e;
+      quantize32<E5M2>(v, fmax, o, e);
+      uint4* dst = reinterpret_cast<uint4*>(q_colT + (size_t)c * rows + r);
+      dst[0] = o[0]; dst[1] = o[1];
+      sf_col[mx_sf_offset(c, r >> 5, (rows + 127) >> 7)] = (uint8_t)(e + 127);
     }
   }
 }
@@ -200,15 +214,19 @@ mxfp8_dual_kernel(const T* __restrict__ x, uint8_t* __restrict__ q_row, uint8_t*
 using namespace mlb;
 
 // x [rows, cols] -> q_row [rows, cols] + sf_row and/or q_colT [cols, rows] + sf_col (either pair may be null);
-// cols a multiple of 32 for the row-wise copy, rows a multiple of 32 for the column-wise one (both multiples of 16);
+// cols a multiple of 32 for the row-wise copy, rows a multiple of 32 for the column-wise one, cols a multiple of 8;
 // the scale buffers hold mlb_mx_sf_bytes(rows, cols) resp. (cols, rows) bytes.
 MLB_API int mlb_mxfp8_quantize_dual(int dtype, const void* x, void* q_row, void* sf_row, void* q_colT, void* sf_col,
                                     int rows, int cols, int e5m2, cudaStream_t st) {
-  if ((rows % 16) || (cols % 16) || (q_row && (cols % 32)) || (q_colT && (rows % 32))) return -3;
-  dim3 grid((cols + 63) / 64, (rows + 63) / 64);
-  MLB_DISPATCH_ACT(dtype, T, (mxfp8_dual_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (uint8_t*)q_row, (uint8_t*)sf_row,
-                                                                        (uint8_t*)q_colT, (uint8_t*)sf_col, rows, cols,
-                                                                        e5m2)));
+  if ((cols % 8) || (q_row && (cols % 32)) || (q_colT && (rows % 32))) return -3;
+  dim3 grid((cols + 127) / 128, (rows + 63) / 64);
+  if (e5m2) {
+    MLB_DISPATCH_ACT(dtype, T, (mxfp8_dual_kernel<T, true><<<grid, 256, 0, st>>>(
+        (const T*)x, (uint8_t*)q_row, (uint8_t*)sf_row, (uint8_t*)q_colT, (uint8_t*)sf_col, rows, cols)));
+  } else {
+    MLB_DISPATCH_ACT(dtype, T, (mxfp8_dual_kernel<T, false><<<grid, 256, 0, st>>>(
+        (const T*)x, (uint8_t*)q_row, (uint8_t*)sf_row, (uint8_t*)q_colT, (uint8_t*)sf_col, rows, cols)));
+  }
   MLB_CHECK_LAUNCH();
   return 0;
 }

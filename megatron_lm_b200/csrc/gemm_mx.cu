@@ -189,7 +189,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           // the next stage (of this or the next tile) has usually landed already: start its scale-factor copy now
           const int nst = (stage + 1 == kStages) ? 0 : stage + 1;
           const uint32_t nph = (stage + 1 == kStages) ? (phase ^ 1u) : phase;
-          if (cp_done == g + 1 && mbar_try_wait(full(nst), nph)) { fence_after_sync(); issue_cp(g + 1, nst); ++cp_done; }
+          if (cp_done == g + 1 && mbar_test_wait(full(nst), nph)) { fence_after_sync(); issue_cp(g + 1, nst); ++cp_done; }
           const uint32_t a_addr = smem_u32(sA + stage * S::kABytes), b_addr = smem_u32(sB + stage * S::kBBytes);
           const uint32_t tsf = tmem_sf + (g % 3u) * 12u;
 #pragma unroll

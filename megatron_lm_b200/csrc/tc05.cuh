@@ -39,6 +39,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok;
 }
+// one look at the barrier, never blocking (try_wait may suspend the thread for a while before it answers "not yet")
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\tmbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\tselp.u32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
 
 // Shared abort protocol.  `abort_flag` lives in shared memory; `status` in global memory.
 constexpr long long kWaitCycles = 4000000000LL;   // about two seconds at boost clock

@@ -203,8 +203,9 @@ def mxfp8_quantize_dual(x: torch.Tensor, fmt: int = 0, rowwise: bool = True, col
     megatron/core/fp8_utils.py:459-485)."""
     x2 = x.reshape(-1, x.shape[-1])
     rows, cols = x2.shape
-    if (rowwise and cols % 32) or (colwise and rows % 32) or rows % 16 or cols % 16:
-        raise ValueError("MXFP8 blocks of 32 need the scaled dimension to be a multiple of 32 (the other of 16)")
+    if (rowwise and cols % 32) or (colwise and rows % 32) or cols % 8:
+        raise ValueError("MXFP8 blocks of 32 need the scaled dimension to be a multiple of 32 (and rows of whole "
+                         "16-byte pieces)")
     dev = x.device
     if not x2.is_cuda:
         def one(m):      # m [R, K] float -> MxTensor, scaled along K
