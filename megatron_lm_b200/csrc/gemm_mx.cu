@@ -4,10 +4,16 @@
 // the accumulator needs no dequantisation pass.
 //
 // Tile: 256 rows (128 per CTA of the pair) x 192 columns.  Two 192-column fp32 accumulators take 384 of the 512
-// tensor-memory columns; the scale factors of the stage in flight need 12 more (4 for this CTA's 128 A rows, 8 for
-// up to 256 B rows), in three buffers: 420 columns.  (A 256-column tile would leave no room for them.)  The scale
-// factors of the next stage are copied to tensor memory before the MMAs of the current stage are issued, so the
-// copy's latency hides behind them.
+// tensor-memory columns; the scale factors of one K stage need 12 more (4 for this CTA's 128 A rows, 8 for up to
+// 256 B rows).  (A 256-column tile would leave no room for them.)
+//
+// Scale factors travel in chunks of four K stages, on a ring of their own (three 6 KB slots, own barriers): `tcgen05.cp`
+// runs in the MMA pipe in issue order, and every switch between products and copies costs the pipe a bubble - three
+// copies in front of the four MMAs of every stage kept the tensor pipe 40 % busy (1570 TFLOP/s at 4096 x 11008 x
+// 4096; 1890 with the copies left out).  So the MMA thread issues the twelve copies of a chunk back to back into one
+// of two 48-column tensor-memory buffers, then the sixteen MMAs of its four stages.  (Writing the scale factors with
+// `tcgen05.st` from four extra warps, which keeps them out of the MMA pipe altogether, measured 1060: that path's
+// latency per stage is longer than the stage.)
 //
 // Scale-factor layout in global memory ("atoms"): for a quantised matrix Q[rows, K] the scale of row r and K block
 // kb (32 elements) is the byte
@@ -60,9 +66,10 @@ struct GemmMxSmem {
   static constexpr int kStages = 5;
   static constexpr int kABytes = 128 * 128;            // this CTA's 128 rows of A, 128 bytes (K elements) each
   static constexpr int kBBytes = 96 * 128;             // this CTA's 96 of the tile's 192 B rows
-  static constexpr int kSfBytes = 512 + 1024;          // A atom + two B atoms
+  static constexpr int kSfSlots = 3;
+  static constexpr int kSfBytes = 3 * 2048;            // four K stages of: A atom, two B atoms (atom = 512 bytes)
   static constexpr int kEpiBytes = 8 * 2 * 4096;
-  static constexpr int kBytes = kStages * (kABytes + kBBytes + kSfBytes) + kEpiBytes + 1024 + 256;
+  static constexpr int kBytes = kStages * (kABytes + kBBytes) + kSfSlots * kSfBytes + kEpiBytes + 1024 + 256;
 };
 
 struct MxParams {
@@ -89,14 +96,16 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // they come right after the operand stages, the (un-swizzled) scale-factor stages after them
   uint8_t* sEpi = smem + kStages * (S::kABytes + S::kBBytes);
   uint8_t* sSF = sEpi + S::kEpiBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + kStages * S::kSfBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + S::kSfSlots * S::kSfBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4 + 2 * S::kSfSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
   auto tfull = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
   auto tempty = [&](int a) { return bar0 + 8u * (2 * kStages + 2 + a); };
+  auto sf_full = [&](int s) { return bar0 + 8u * (2 * kStages + 4 + s); };
+  auto sf_empty = [&](int s) { return bar0 + 8u * (2 * kStages + 4 + S::kSfSlots + s); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -104,6 +113,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 16); }
+    for (int i = 0; i < S::kSfSlots; ++i) { mbar_init(sf_full(i), 1); mbar_init(sf_empty(i), 1); }
     *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_fence_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmSFA); prefetch_tmap(&tmSFB); prefetch_tmap(&tmD);
@@ -114,7 +124,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   cluster_sync_all();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_sf = tmem_base + 2 * TN;           // 3 x 12 scale-factor columns behind the accumulators
+  const uint32_t tmem_sf = tmem_base + 2 * TN;           // 2 chunks x 4 stages x 12 columns behind the accumulators
 
   const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
@@ -133,6 +143,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
+      int slot = 0; uint32_t sphase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         int mb, nb; tile_mn(tile, mb, nb);
@@ -140,17 +151,24 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int sfa_atom = (m0 >> 7) * num_kb;                  // atom (m0 / 128, 0)
         const int sfb_atom0 = n0 >> 7;
         for (int kb = 0; kb < num_kb; ++kb) {
+          if ((kb & 3) == 0) {
+            // the scale factors of K stages kb .. kb + 3: three requests of four consecutive atoms each (rows past the
+            // end of the buffer are zero-filled and still counted; atoms past this tile's K range are not used)
+            if (!mbar_wait(sf_empty(slot), sphase ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
+            if (leader) mbar_expect_tx(sf_full(slot), 2 * S::kSfBytes);
+            const uint32_t sbar = map_to_cta(sf_full(slot), 0);
+            const uint32_t sf_dst = smem_u32(sSF + slot * S::kSfBytes);
+            tma_load_2d_pair(sf_dst, &tmSFA, sbar, 0, sfa_atom + kb);
+            tma_load_2d_pair(sf_dst + 2048, &tmSFB, sbar, 0, sfb_atom0 * num_kb + kb);
+            tma_load_2d_pair(sf_dst + 4096, &tmSFB, sbar, 0, (sfb_atom0 + 1) * num_kb + kb);
+            if (++slot == S::kSfSlots) { slot = 0; sphase ^= 1u; }
+          }
           if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
-          if (leader) mbar_expect_tx(full(stage), 2 * (S::kABytes + S::kBBytes + S::kSfBytes));
+          if (leader) mbar_expect_tx(full(stage), 2 * (S::kABytes + S::kBBytes));
           const uint32_t fbar = map_to_cta(full(stage), 0);
           const uint32_t a_dst = smem_u32(sA + stage * S::kABytes), b_dst = smem_u32(sB + stage * S::kBBytes);
-          const uint32_t sf_dst = smem_u32(sSF + stage * S::kSfBytes);
           tma_load_2d_pair(a_dst, &tmA, fbar, kb * 128, m0);                          // box [128 B, 128 rows]
           tma_load_2d_pair(b_dst, &tmB, fbar, kb * 128, n0 + 96 * (int)rank);         // box [128 B, 96 rows]
-          tma_load_2d_pair(sf_dst, &tmSFA, fbar, 0, sfa_atom + kb);                   // one atom = one 512-byte row
-          tma_load_2d_pair(sf_dst + 512, &tmSFB, fbar, 0, sfb_atom0 * num_kb + kb);
-          // the second B atom may lie past the end of the matrix: the copy is then zero-filled (and still counted)
-          tma_load_2d_pair(sf_dst + 1024, &tmSFB, fbar, 0, (sfb_atom0 + 1) * num_kb + kb);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -164,15 +182,9 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int k = 0; k < 4; ++k) idesc[k] = make_idesc_mx(256, TN, p.a_fmt, p.b_fmt, k);
       int stage = 0; uint32_t phase = 0;
       int t = 0;
-      uint32_t g = 0;                      // stages consumed so far (over all tiles)
-      uint32_t cp_done = 0;                // stages whose scale factors have been sent to tensor memory
-      auto issue_cp = [&](uint32_t gs, int st) {
-        const uint32_t sf_addr = smem_u32(sSF + st * S::kSfBytes);
-        const uint32_t tsf = tmem_sf + (gs % 3u) * 12u;
-        sf_copy_pair(tsf, make_sf_desc(sf_addr));
-        sf_copy_pair(tsf + 4, make_sf_desc(sf_addr + 512));
-        sf_copy_pair(tsf + 8, make_sf_desc(sf_addr + 1024));
-      };
+      int slot = 0; uint32_t sphase = 0;
+      uint32_t chunk = 0;                  // scale-factor chunks consumed so far: picks the tensor-memory buffer
+      uint32_t tsf_chunk = tmem_sf;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++t) {
         int mb, nb; tile_mn(tile, mb, nb);
@@ -182,16 +194,26 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
-        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if ((kb & 3) == 0) {
+            if (!mbar_wait(sf_full(slot), sphase, abort_flag, p.status, 6)) { ok = false; break; }
+            fence_after_sync();
+            tsf_chunk = tmem_sf + (chunk & 1u) * 48u;
+            const uint32_t sf_addr = smem_u32(sSF + slot * S::kSfBytes);
+            const int n_st = (num_kb - kb) < 4 ? (num_kb - kb) : 4;
+            for (int j = 0; j < n_st; ++j) {
+              sf_copy_pair(tsf_chunk + j * 12, make_sf_desc(sf_addr + j * 512));
+              sf_copy_pair(tsf_chunk + j * 12 + 4, make_sf_desc(sf_addr + 2048 + j * 512));
+              sf_copy_pair(tsf_chunk + j * 12 + 8, make_sf_desc(sf_addr + 4096 + j * 512));
+            }
+            mma_commit_pair(sf_empty(slot), 3);          // the slot may be refilled once these copies have run
+            ++chunk;
+            if (++slot == S::kSfSlots) { slot = 0; sphase ^= 1u; }
+          }
           if (!mbar_wait(full(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
           fence_after_sync();
-          if (cp_done == g) { issue_cp(g, stage); ++cp_done; }
-          // the next stage (of this or the next tile) has usually landed already: start its scale-factor copy now
-          const int nst = (stage + 1 == kStages) ? 0 : stage + 1;
-          const uint32_t nph = (stage + 1 == kStages) ? (phase ^ 1u) : phase;
-          if (cp_done == g + 1 && mbar_test_wait(full(nst), nph)) { fence_after_sync(); issue_cp(g + 1, nst); ++cp_done; }
           const uint32_t a_addr = smem_u32(sA + stage * S::kABytes), b_addr = smem_u32(sB + stage * S::kBBytes);
-          const uint32_t tsf = tmem_sf + (g % 3u) * 12u;
+          const uint32_t tsf = tsf_chunk + (uint32_t)((kb & 3) * 12);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_mx_pair(d_tmem, make_desc(a_addr + k * 32, 16, 1024), make_desc(b_addr + k * 32, 16, 1024), idesc[k],
@@ -278,14 +300,15 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) { fence_after_sync(); tmem_dealloc2(tmem_base, 512); }
 }
 
-// tensor map without swizzle over the scale-factor atoms: one row of 128 32-bit words (512 bytes) per atom, so an
-// atom is a single copy request and lands in shared memory as the dense 32 x 16-byte block tcgen05.cp reads
+// tensor map without swizzle over the scale-factor atoms: one row of 128 32-bit words (512 bytes) per atom; a request
+// moves four consecutive atoms (four K stages of one 128-row block), each landing in shared memory as the dense
+// 32 x 16-byte block tcgen05.cp reads
 static int make_sf_tmap(CUtensorMap* out, const void* base, long n_atoms) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
   cuuint64_t d[2] = {128, (cuuint64_t)n_atoms};
   cuuint64_t s[1] = {512};
-  cuuint32_t b[2] = {128, 1};
+  cuuint32_t b[2] = {128, 4};
   cuuint32_t e[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), d, s, b, e,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
