@@ -30,6 +30,7 @@ constexpr int kAttnThreads = 192;
 // backward kernels: warp 0 TMA, warp 1 MMA, warps 2-9 compute - two warps per TMEM lane quadrant, each taking
 // one half (32) of the 64 columns of a step, so eight warps instead of four hide the exp2 / TMEM-load latency
 constexpr int kAttnBwdThreads = 320;
+constexpr int kAttnDqThreads = 576;      // dQ kernel with 128-key steps: warp 0 TMA, warp 1 MMA, 16 compute warps
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -42,6 +43,8 @@ struct AttnParams {
   void* o; long o_s, o_b, o_g, o_j;
   float* lse;                               // [b, ng, qpg, sq] natural log
   // backward
+  const void* q; long q_s, q_b, q_g, q_j;    // raw operands for kernels that read rows themselves
+  const void* d_o; long do_s, do_b, do_g, do_j;
   const float* delta;                       // [b, ng, qpg, sq]
   void* dq; long dq_s, dq_b, dq_g, dq_j;
   void* dk; long dk_s, dk_b, dk_g;
@@ -58,7 +61,7 @@ __device__ __forceinline__ uint32_t pack_lp(float a, float b, int bf) {
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 // write 64 values of one row (as 32 packed words) into a [rows x 64] K-major 128B-swizzled tile
@@ -765,31 +768,40 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
 
-// ============================================================================ backward: dQ, dS kept in tensor memory
-// Same product as attn_bwd_dq_kernel with two changes that take shared-memory traffic and latency out of a step:
-//   * dS (bf16) is written by the compute warps into tensor memory and is the A operand of dQ += dS K straight from
-//     there (`tcgen05.mma` with A in TMEM): no 16 KB store + 16 KB re-read through shared memory per step;
-//   * S and dP are double buffered in tensor memory, so the products of step t + 1 are already complete when the
-//     compute warps finish step t, and those of step t + 2 are issued as soon as dQ of step t is.
-// Tensor memory columns: S0 | dP0 | S1 | dP1 (64 each) | dQ (D) | dS0 | dS1 (32 each).
+// ============================================================================ backward: dQ, 128-key steps
+// Same product as attn_bwd_dq_kernel, rebuilt around what the tensor core's instruction rate allows: one thread
+// gets a `tcgen05.mma` accepted about every 46 cycles whatever its size (measured: 16 instructions of 128 x 64 x 16
+// take 740 cycles to issue, 830 to complete - 32 cycles of arithmetic each; of 128 x 128 x 16, 72 cycles each from a
+// tensor-memory A operand, 82 from shared memory), so products of 64 columns run the tensor core at two thirds of
+// its rate at best and every product here is 128 wide:
+//   S = Q K^T and dP = dO V^T (128 x 128 per step) into tensor memory, each behind a barrier of its own so that the
+//   exponentials start while dP is still running; dS (16-bit) into tensor-memory columns of its own, from where it is
+//   the A operand of dQ += dS K.
+// S and dP are single buffers: the compute warps take a step's values into registers and release them at once, so
+// S / dP of step t + 1 are issued - ahead of dQ of step t - as soon as step t has been read, and run under its
+// arithmetic.  Sixteen compute warps (four per lane quadrant, 32 key columns each): a warp's step is a chain of
+// waits, tensor-memory loads, arithmetic and a tensor-memory store that does not overlap with itself.
+// Tensor memory columns: S | dP (128 each) | dQ (D) | dS (64).  Shared memory: Q, dO, three K stages (a K tile is
+// held until dQ of its step), two V stages.
 template <int D>
-__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+__global__ void __launch_bounds__(kAttnDqThreads, 1)
 attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                       const AttnParams p) {
-  constexpr int BM = 128, BN = 64;
-  constexpr int QB = D * 256, KVB = D * 128, QC = 16384, KC = 8192;
+  constexpr int BM = 128, BN = 128;
+  constexpr int TB = D * 256, CH = 16384;              // bytes of a 128-row tile / of one of its 64-column chunks
   constexpr uint32_t TCOLS = 512;
-  constexpr int NST = 4;
+  constexpr int NK = 3, NV = 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
-  uint8_t* sdO = sQ + QB;
-  uint8_t* sK = sdO + QB;
-  uint8_t* sV = sK + NST * KVB;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NST * KVB);
-  // 0 q_full | kv_full[4] | kv_empty[4] | sdp_full[2] | sdp_empty[2] | ds_full[2] | ds_free[2]
-  constexpr int KF = 1, KE = KF + NST, SF = KE + NST, SE = SF + 2, DF = SE + 2, DR = DF + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DR + 2);
+  uint8_t* sdO = sQ + TB;
+  uint8_t* sK = sdO + TB;
+  uint8_t* sV = sK + NK * TB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NV * TB);
+  // q_full | k_full[3] | k_empty[3] | v_full[2] | v_empty[2] | s_full | dp_full | s_read | dp_read | ds_full | ds_read | done
+  constexpr int KF = 1, KE = KF + NK, VF = KE + NK, VE = VF + NV, SF = VE + NV, PF = SF + 1, SE = PF + 1, PE = SE + 1,
+                DF = PE + 1, DR = DF + 1, DN = DR + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DN + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto B = [&](int i) { return bar0 + 8u * i; };
@@ -807,8 +819,9 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(B(0), 1);
-    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(KF + i), 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(B(SF + i), 1); mbar_init(B(SE + i), 8); mbar_init(B(DF + i), 8); mbar_init(B(DR + i), 1); }
+    for (int i = KF; i < SF; ++i) mbar_init(B(i), 1);
+    mbar_init(B(SF), 1); mbar_init(B(PF), 1); mbar_init(B(SE), 16); mbar_init(B(PE), 16); mbar_init(B(DF), 16);
+    mbar_init(B(DR), 1); mbar_init(B(DN), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -818,28 +831,28 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  auto tS = [&](int b) { return tmem + (uint32_t)(128 * b); };
-  auto tdP = [&](int b) { return tmem + (uint32_t)(128 * b + 64); };
-  const uint32_t tdQ = tmem + 256;
-  auto tdS = [&](int b) { return tmem + 256 + (uint32_t)D + (uint32_t)(32 * b); };
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256, tdS = tmem + 256 + D;
 
   if (warp == 0) {
     if (lane == 0 && n_kv > 0) {
-      mbar_expect_tx(B(0), 2 * QB);
+      mbar_expect_tx(B(0), 2 * TB);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
-        tma_load_5d(smem_u32(sQ) + c * QC, &tmQ, B(0), c * 64, j, g, bb, s0);
-        tma_load_5d(smem_u32(sdO) + c * QC, &tmdO, B(0), c * 64, j, g, bb, s0);
+        tma_load_5d(smem_u32(sQ) + c * CH, &tmQ, B(0), c * 64, j, g, bb, s0);
+        tma_load_5d(smem_u32(sdO) + c * CH, &tmdO, B(0), c * 64, j, g, bb, s0);
       }
       for (int t = 0; t < n_kv; ++t) {
-        const int st = t % NST;
-        if (!mbar_wait(B(KE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
-        mbar_expect_tx(B(KF + st), 2 * KVB);
+        const int ks = t % NK, vs = t % NV;
+        if (!mbar_wait(B(KE + ks), (((uint32_t)(t / NK)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(KF + ks), TB);
 #pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_5d(smem_u32(sK) + st * KVB + c * KC, &tmK, B(KF + st), c * 64, 0, g, bb, t * BN);
-          tma_load_5d(smem_u32(sV) + st * KVB + c * KC, &tmV, B(KF + st), c * 64, 0, g, bb, t * BN);
-        }
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sK) + ks * TB + c * CH, &tmK, B(KF + ks), c * 64, 0, g, bb, t * BN);
+        if (!mbar_wait(B(VE + vs), (((uint32_t)(t / NV)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(VF + vs), TB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sV) + vs * TB + c * CH, &tmV, B(VF + vs), c * 64, 0, g, bb, t * BN);
       }
     }
   } else if (warp == 1) {
@@ -847,43 +860,51 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);
       const uint32_t idesc_q = make_idesc(BM, D, p.lp_fmt, 0, 1);
       const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV);
-      bool ok = true;
-      // S and dP of step t into buffer t & 1 (its previous contents, step t - 2, are in the compute warps' registers)
-      auto issue_sdp = [&](int t) -> bool {
-        const int b = t & 1;
-        const uint32_t k = (uint32_t)(t >> 1);
-        if (!mbar_wait(B(KF + t % NST), ((uint32_t)(t / NST)) & 1u, abort_flag, p.status, 24)) return false;
-        if (!mbar_wait(B(SE + b), (k & 1u) ^ 1u, abort_flag, p.status, 25)) return false;
+      // S of step t once its K tile has landed and (t > 0) the compute warps hold S of step t - 1 in registers
+      auto issue_s = [&](int t) -> bool {
+        if (!mbar_wait(B(KF + t % NK), ((uint32_t)(t / NK)) & 1u, abort_flag, p.status, 24)) return false;
+        if (t > 0 && !mbar_wait(B(SE), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 25)) return false;
         fence_after_sync();
-        const uint32_t kb = aK + (t % NST) * KVB, vb = aV + (t % NST) * KVB;
+        const uint32_t kb = aK + (t % NK) * TB;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_f16(tS(b), kmajor_desc(aQ, kk, QC), kmajor_desc(kb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_f16(tdP(b), kmajor_desc(adO, kk, QC), kmajor_desc(vb, kk, KC), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(B(SF + b));
+          mma_f16(tS, kmajor_desc(aQ, kk, CH), kmajor_desc(kb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF));
         return true;
       };
-      ok = mbar_wait(B(0), 0, abort_flag, p.status, 22);
-      if (ok) ok = issue_sdp(0);
-      if (ok && n_kv > 1) ok = issue_sdp(1);
-      for (int t = 0; t < n_kv && ok; ++t) {
-        const int b = t & 1;
-        if (!mbar_wait(B(DF + b), ((uint32_t)(t >> 1)) & 1u, abort_flag, p.status, 26)) { ok = false; break; }
+      auto issue_dp = [&](int t) -> bool {
+        if (!mbar_wait(B(VF + t % NV), ((uint32_t)(t / NV)) & 1u, abort_flag, p.status, 24)) return false;
+        if (t > 0 && !mbar_wait(B(PE), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 25)) return false;
         fence_after_sync();
-        const uint32_t kb = aK + (t % NST) * KVB;
+        const uint32_t vb = aV + (t % NV) * TB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP, kmajor_desc(adO, kk, CH), kmajor_desc(vb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(PF));
+        mma_commit(B(VE + t % NV));            // this V tile may be overwritten
+        return true;
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 22);
+      if (ok) ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
+      for (int t = 0; t < n_kv && ok; ++t) {
+        if (t + 1 < n_kv) {
+          if (!issue_s(t + 1) || !issue_dp(t + 1)) { ok = false; break; }
+        }
+        if (!mbar_wait(B(DF), (uint32_t)t & 1u, abort_flag, p.status, 26)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t kb = aK + (t % NK) * TB;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          mma_f16_ts(tdQ, tdS(b) + (uint32_t)(kk * 8), mnmajor_desc(kb, kk, KC), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(B(KE + (t % NST)));         // K / V of this step may be overwritten
-        mma_commit(B(DR + b));                 // and so may dS of this buffer
-        if (t + 2 < n_kv) ok = issue_sdp(t + 2);
+          mma_f16_ts(tdQ, tdS + (uint32_t)(kk * 8), mnmajor_desc(kb, kk, CH), idesc_q, (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(KE + t % NK));            // this K tile may be overwritten
+        mma_commit(B(DR));                     // and dS rewritten
       }
+      if (ok) mma_commit(B(DN));
     }
   } else if (n_kv > 0) {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;               // which 32 of a step's 128 key columns
     const int row = quad * 32 + lane;
     const int qrow = s0 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
@@ -892,66 +913,67 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const float dlt = qrow < p.sq ? p.delta[stat_idx] : 0.f;
     bool ok = true;
     for (int t = 0; t < n_kv; ++t) {
-      const int n0 = t * BN;
-      const int b = t & 1;
-      const uint32_t k = (uint32_t)(t >> 1);
-      if (!mbar_wait(B(SF + b), k & 1u, abort_flag, p.status, 27)) { ok = false; break; }
+      const int n0 = t * BN + part * 32;            // first key of this warp's columns
+      const uint32_t par = (uint32_t)t & 1u;
+      uint32_t r[32];
+      float pr[32];
+      if (!mbar_wait(B(SF), par, abort_flag, p.status, 27)) { ok = false; break; }
       fence_after_sync();
-      uint32_t w[16];
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS(b) + lane_base + half * 32, rs);
-      tmem_ld32(tdP(b) + lane_base + half * 32, rp);
+      tmem_ld32(tS + lane_base + part * 32, r);
       tmem_wait_ld();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(SE + b));
-      const bool need_mask = (p.causal && (n0 + BN - 1 > s0 + p.off)) || (n0 + BN > p.sk) || (s0 + BM > p.sq);
+      if (lane == 0) mbar_arrive(B(SE));
+      const bool need_mask = (p.causal && (n0 + 31 > s0 + p.off)) || (n0 + 32 > p.sk) || (s0 + BM > p.sq);
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          float ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int kv = n0 + half * 32 + 2 * c + e;
-            const bool masked = (p.causal && kv > qrow + p.off) || kv >= p.sk || qrow >= p.sq;
-            const float pr = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[2 * c + e]), p.scale_log2, -lse2));
-            ds[e] = pr * (__uint_as_float(rp[2 * c + e]) - dlt) * p.scale;
-          }
-          w[c] = pack_lp(ds[0], ds[1], p.lp_fmt);
+        for (int e = 0; e < 32; ++e) {
+          const int kv = n0 + e;
+          const bool masked = (p.causal && kv > qrow + p.off) || kv >= p.sk || qrow >= p.sq;
+          pr[e] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -lse2));
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[2 * c]), p.scale_log2, -lse2));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[2 * c + 1]), p.scale_log2, -lse2));
-          w[c] = pack_lp(p0 * (__uint_as_float(rp[2 * c]) - dlt) * p.scale,
-                         p1 * (__uint_as_float(rp[2 * c + 1]) - dlt) * p.scale, p.lp_fmt);
-        }
+        for (int e = 0; e < 32; ++e) pr[e] = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -lse2));
       }
-      // dS of step t - 2 (same buffer) must have been consumed by its dQ product
-      if (!mbar_wait(B(DR + b), (k & 1u) ^ 1u, abort_flag, p.status, 28)) { ok = false; break; }
+      if (!mbar_wait(B(PF), par, abort_flag, p.status, 27)) { ok = false; break; }
       fence_after_sync();
-      tmem_st16(tdS(b) + lane_base + half * 16, w);     // keys [32 half, 32 half + 32) = 16 packed columns
+      tmem_ld32(tdP + lane_base + part * 32, r);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(PE));
+      uint32_t w[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        w[c] = pack_lp(pr[2 * c] * (__uint_as_float(r[2 * c]) - dlt) * p.scale,
+                       pr[2 * c + 1] * (__uint_as_float(r[2 * c + 1]) - dlt) * p.scale, p.lp_fmt);
+      // dS of the previous step must have been consumed by its dQ product
+      if (t > 0 && !mbar_wait(B(DR), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 28)) { ok = false; break; }
+      fence_after_sync();
+      tmem_st16(tdS + lane_base + part * 16, w);    // keys [32 part, 32 part + 32) = 16 packed columns
       tmem_wait_st();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(DF + b));
+      if (lane == 0) mbar_arrive(B(DF));
     }
-    const int bl = (n_kv - 1) & 1;
-    if (ok && mbar_wait(B(DR + bl), ((uint32_t)((n_kv - 1) >> 1)) & 1u, abort_flag, p.status, 29)) {
+    if (ok && mbar_wait(B(DN), 0, abort_flag, p.status, 29)) {
       fence_after_sync();
       uint8_t* drow = reinterpret_cast<uint8_t*>(p.dq) +
                       2 * ((long)qrow * p.dq_s + (long)bb * p.dq_b + (long)g * p.dq_g + (long)j * p.dq_j);
-#pragma unroll 1
-      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
-        uint32_t o[32];
-        tmem_ld32(tdQ + lane_base + c, o);
+#pragma unroll
+      for (int c = part * (D / 4); c < (part + 1) * (D / 4); c += 16) {
+        uint32_t o[16];
+        tmem_ld16(tdQ + lane_base + c, o);
         tmem_wait_ld();
         if (qrow < p.sq) {
-          float v[32];
+          uint4* d4 = reinterpret_cast<uint4*>(drow + c * 2);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
-          store_chunk_global(drow + c * 2, v, p.lp_fmt);
+          for (int q4 = 0; q4 < 2; ++q4)
+            d4[q4] = make_uint4(pack_lp(__uint_as_float(o[q4 * 8]), __uint_as_float(o[q4 * 8 + 1]), p.lp_fmt),
+                                pack_lp(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]), p.lp_fmt),
+                                pack_lp(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]), p.lp_fmt),
+                                pack_lp(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]), p.lp_fmt));
         }
       }
     }
@@ -1323,17 +1345,24 @@ attn_bwd_dkv_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int krow = n0 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     bool ok = true;
+    // per-query statistics of a step (64 lse2 + 64 delta): read from global memory one step ahead, so that the
+    // load's latency is not part of the step
+    auto load_stat = [&](int t) -> float {
+      const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+      const int qi = q0 + (ct & 63);
+      const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
+      if (qi >= p.sq) return 0.f;
+      return (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
+    };
+    float stat_next = ct < 128 ? load_stat(0) : 0.f;
     for (int t = 0; t < n_steps; ++t) {
       const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
-      // stage this step's per-query statistics (64 lse2 + 64 delta) in shared memory
+      (void)j;
       {
         float* dst = sStat + (t & 1) * 128;
         if (ct < 128) {
-          const int qi = q0 + (ct & 63);
-          const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
-          float v = 0.f;
-          if (qi < p.sq) v = (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
-          dst[ct] = v;
+          dst[ct] = stat_next;
+          if (t + 1 < n_steps) stat_next = load_stat(t + 1);
         }
         bar_sync_compute();
       }
@@ -1450,7 +1479,7 @@ MLB_API int mlb_attn_fwd(int lp_fmt, const void* q, const void* k, const void* v
                          long v_s, long v_b, long v_g, long o_s, long o_b, long o_g, long o_j,
                          float scale, int causal, int* status, cudaStream_t st) {
   if (D != 64 && D != 128) return -5;
-  if (sq <= 0 || sk <= 0 || sk < sq) return -6;
+  if (sq <= 0 || sk <= 0 || (causal && sk < sq)) return -6;
   if ((o_s % 8) || (o_b % 8) || (o_g % 8) || (o_j % 8) || (reinterpret_cast<uintptr_t>(o) & 15)) return -3;
   CUtensorMap tmQ, tmK, tmV;
   int rc;
@@ -1505,7 +1534,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
                          long dk_s, long dk_b, long dk_g, long dv_s, long dv_b, long dv_g,
                          float scale, int causal, int* status, cudaStream_t st) {
   if (D != 64 && D != 128) return -5;
-  if (sq <= 0 || sk <= 0 || sk < sq) return -6;
+  if (sq <= 0 || sk <= 0 || (causal && sk < sq)) return -6;
   const long chk[] = {dq_s, dq_b, dq_g, dq_j, dk_s, dk_b, dk_g, dv_s, dv_b, dv_g};
   for (long x : chk) if (x % 8) return -3;
   if ((reinterpret_cast<uintptr_t>(dq) & 15) || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15)) return -3;
@@ -1519,6 +1548,8 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
   p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
   p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.q = q; p.q_s = q_s; p.q_b = q_b; p.q_g = q_g; p.q_j = q_j;
+  p.d_o = d_o; p.do_s = do_s; p.do_b = do_b; p.do_g = do_g; p.do_j = do_j;
   p.dq = dq; p.dq_s = dq_s; p.dq_b = dq_b; p.dq_g = dq_g; p.dq_j = dq_j;
   p.dk = dk; p.dk_s = dk_s; p.dk_b = dk_b; p.dk_g = dk_g;
   p.dv = dv; p.dv_s = dv_s; p.dv_b = dv_b; p.dv_g = dv_g;
@@ -1533,15 +1564,18 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     static int use_ts = -1;                                            // MLB_ATTN_TS=0: dS through shared memory
     if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
     if (use_ts) {
-      const int smem_ts = 2 * D * 256 + 8 * D * 128 + 256;             // Q, dO, four K/V stages
+      CUtensorMap tmK2, tmV2;                                          // 128-key steps
+      if ((rc = make_tmap5(&tmK2, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
+      if ((rc = make_tmap5(&tmV2, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
+      const int smem_ts = 7 * D * 256 + 256;                           // Q, dO, three K stages, two V stages
       if (D == 128) {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<128>, smem_ts))) return rc; set = true; }
-        attn_bwd_dq_ts_kernel<128><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+        attn_bwd_dq_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK2, tmV2, tmdO, p);
       } else {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<64>, smem_ts))) return rc; set = true; }
-        attn_bwd_dq_ts_kernel<64><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+        attn_bwd_dq_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK2, tmV2, tmdO, p);
       }
       MLB_CHECK_LAUNCH();
     } else {

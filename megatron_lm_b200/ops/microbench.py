@@ -23,17 +23,33 @@ def _peaks():
         return {}
 
 
+_BLOCKER = {}
+
+
+def _blocker():
+    """A product of about a millisecond in front of every timed call: while the GPU works on it the host enqueues the
+    call and the closing event, so the events bracket device time only (an op of 50 us issued from Python is otherwise
+    timed at the host's launch rate), and its 400 MB of operands push the previous iteration's data out of L2."""
+    dev = torch.cuda.current_device()
+    if dev not in _BLOCKER:
+        a = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+        _BLOCKER[dev] = (a, torch.empty_like(a))
+    a, out = _BLOCKER[dev]
+    torch.matmul(a, a, out=out)
+
+
 def _time(fn, iters, warmup):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for e0, e1 in ev:
+        _blocker()
+        e0.record()
         fn()
-    e1.record()
+        e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    return sum(e0.elapsed_time(e1) for e0, e1 in ev) / iters
 
 
 def _report(name, ms, flops=None, bytes_=None):

@@ -72,6 +72,26 @@ def test_attention_rectangular_ragged_backward():
             assert _rel(a, r) < 3e-2
 
 
+def test_attention_full_more_queries_than_keys():
+    """Not causal, sq > sk: the shape of a ring-attention step that holds half of a peer's keys."""
+    torch.manual_seed(5)
+    sq, sk, d = 512, 256, 128
+    q = torch.randn(sq, 1, 2, 1, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(sk, 1, 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(sk, 1, 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = attention(q, k, v, causal=False)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = _ref_attention(qr, kr, vr, False, 1.0 / math.sqrt(d))
+    assert _rel(out, ref) < 2e-2
+    do = torch.randn_like(ref)
+    out.backward(do.to(out.dtype))
+    ref.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for a, r in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert _rel(a, r) < 3e-2
+
+
 def test_attention_large_scores_rescale():
     """Scores that grow along the keys force the running maximum up by more than the lazy-rescale threshold."""
     torch.manual_seed(4)
