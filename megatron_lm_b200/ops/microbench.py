@@ -266,6 +266,23 @@ def bench_tp_fused(a):
     dist.destroy_process_group()
 
 
+def bench_tcgen05(a):
+    """Issue and completion time of batches of 16 ``tcgen05.mma`` instructions on one SM (``csrc/probe.cu``)."""
+    from . import _lib
+    _lib.register_signatures({"mlb_tcgen05_probe": "ppp"})
+    out = torch.zeros(18, dtype=torch.int64, device="cuda")
+    _lib.check(_lib.lib().mlb_tcgen05_probe(out.data_ptr(), _lib.status_word().data_ptr(), _lib.stream()), "probe")
+    torch.cuda.synchronize()
+    v = out.tolist()
+    i = 0
+    for n in (64, 128, 256):
+        for name in ("A, B shared memory", "A tensor memory", "A tensor memory, B MN-major"):
+            math = n // 4 * 2                       # 128 x n x 16 at 8192 FLOP per cycle
+            print(f"16 x (128 x {n:3d} x 16), {name:28s}: issued in {v[2 * i]:5d} cycles, complete after {v[2 * i + 1]:5d} "
+                  f"({v[2 * i + 1] / 16:5.1f} per instruction; arithmetic alone {math})")
+            i += 1
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--iters", type=int, default=20)
@@ -289,8 +306,9 @@ def main(argv=None):
     tf = sub.add_parser("tp-fused", help="torchrun --nproc-per-node TP -m megatron_lm_b200.ops.microbench tp-fused")
     tf.add_argument("--hidden", type=int, default=4096); tf.add_argument("--ffn", type=int, default=11008)
     tf.add_argument("--seq", type=int, default=4096)
+    sub.add_parser("tcgen05", help="tensor-core instruction issue / completion times on one SM")
     a = ap.parse_args(argv)
-    {"tp-fused": bench_tp_fused, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam, "router": bench_router,
+    {"tcgen05": bench_tcgen05, "tp-fused": bench_tp_fused, "gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "adam": bench_adam, "router": bench_router,
      "sampling": bench_sampling, "gated-norm": bench_gated_norm}[a.op](a)
     from . import _lib
     _lib.check_status()
