@@ -1212,44 +1212,45 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
 
-// ============================================================================ backward: dK, dV, P^T and dS^T in tensor memory
-// attn_bwd_dkv_kernel with P^T and dS^T written over the S^T / dP^T columns they were computed from and used as the
-// A operands of dV += P^T dO and dK += dS^T Q from there, and with two S^T / dP^T buffers: the products of step
-// t + 2 are issued right behind dV / dK of step t (products of one thread run in issue order, so they may overwrite
-// what those read), and the compute warps never wait for a buffer.  A warp that owns query columns [32 h, 32 h + 32)
-// of a step writes its 16 packed columns at offset 32 h - inside the range only it reads - and the reduction steps
-// pick their A operand up at 0, 8, 32, 40.
-// Tensor memory columns: dV | dK (D each) | S^T0 dP^T0 | S^T1 dP^T1 (64 each).
+// ============================================================================ backward: dK, dV, 128-query steps
+// attn_bwd_dkv_kernel rebuilt like the dQ kernel above: every product 128 wide (one thread gets a `tcgen05.mma`
+// accepted about every 46 cycles whatever its size), P^T and dS^T written over the S^T / dP^T columns they were
+// computed from and taken from there as the A operands of dV += P^T dO and dK += dS^T Q, sixteen compute warps.
+// All 512 tensor-memory columns are taken (dV | dK | S^T | dP^T), so there is no second S^T / dP^T buffer; instead a
+// step runs in two phases that alternate on the tensor pipe:
+//   phase A: S^T ready -> exponentials -> P^T            | meanwhile the pipe runs dK of step t - 1, dP^T of step t
+//   phase B: dP^T ready -> dS^T = P (dP - delta) scale   | meanwhile the pipe runs dV of step t, S^T of step t + 1
+// (products of one thread run in issue order, which is what lets S^T of step t + 1 overwrite P^T of step t right
+// behind the dV product that reads it, and dP^T of step t + 1 the dS^T that dK reads).
+// Shared memory: K, V, two Q / dO stages of 128 rows, per-query statistics of two steps.
 template <int D>
-__global__ void __launch_bounds__(kAttnBwdThreads, 1)
+__global__ void __launch_bounds__(kAttnDqThreads, 1)
 attn_bwd_dkv_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const AttnParams p) {
-  constexpr int BM = 128, BN = 64;                 // BM key rows per CTA, BN query rows per step
-  constexpr int KB = D * 256, QB = D * 128, KC = 16384, QC = 8192;
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                       const AttnParams p) {
+  constexpr int BM = 128, BN = 128;                // BM key rows per CTA, BN query rows per step
+  constexpr int TB = D * 256, CH = 16384;          // bytes of a 128-row tile / of one of its 64-column chunks
   constexpr uint32_t TCOLS = 512;
+  constexpr int NST = 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
-  uint8_t* sV = sK + KB;
-  constexpr int NST = 4;                                       // Q / dO stages: held from S^T to dK of their step
-  uint8_t* sQ = sV + KB;
-  uint8_t* sdO = sQ + NST * QB;
-  float* sStat = reinterpret_cast<float*>(sdO + NST * QB);     // [2][2][64] lse2 / delta per step parity
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 256);
-  // 0 kv_full | q_full[4] | q_empty[4] | sdp_full[2] | pds_full[2] | all products done
-  constexpr int QF = 1, QE = 1 + NST, SF = 1 + 2 * NST, PF = SF + 2, DN = PF + 2;
+  uint8_t* sV = sK + TB;
+  uint8_t* sQ = sV + TB;
+  uint8_t* sdO = sQ + NST * TB;
+  float* sStat = reinterpret_cast<float*>(sdO + NST * TB);     // [2][2][128] lse2 / delta per step parity
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 512);
+  // kv_full | q_full[2] | q_empty[2] | s_full | dp_full | p_full | ds_full | done
+  constexpr int QF = 1, QE = QF + NST, SF = QE + NST, PF = SF + 1, AF = PF + 1, BF = AF + 1, DN = BF + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DN + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto B = [&](int i) { return bar0 + 8u * i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int n_ktiles = (p.sk + BM - 1) / BM;
   const int kt = blockIdx.x / (p.ng * p.b);                    // early key tiles see the most queries
   const int gb = blockIdx.x % (p.ng * p.b);
   const int bb = gb / p.ng, g = gb % p.ng;
   const int n0 = kt * BM;
-  (void)n_ktiles;
   // query tiles that can see at least one key of this tile: q + off >= n0
   int q_begin = 0;
   if (p.causal) { q_begin = n0 - p.off; if (q_begin < 0) q_begin = 0; }
@@ -1260,9 +1261,8 @@ attn_bwd_dkv_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(B(0), 1);
-    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(1 + i), 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(B(SF + i), 1); mbar_init(B(PF + i), 8); }
-    mbar_init(B(DN), 1);
+    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(QF + i), 1);
+    mbar_init(B(SF), 1); mbar_init(B(PF), 1); mbar_init(B(AF), 16); mbar_init(B(BF), 16); mbar_init(B(DN), 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
@@ -1272,165 +1272,179 @@ attn_bwd_dkv_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tdV = tmem, tdK = tmem + D;
-  auto tS = [&](int b) { return tmem + (uint32_t)(2 * D + 128 * b); };
-  auto tdP = [&](int b) { return tmem + (uint32_t)(2 * D + 128 * b + 64); };
+  const uint32_t tdV = tmem, tdK = tmem + D, tS = tmem + 2 * D, tdP = tmem + 2 * D + 128;
 
   if (warp == 0) {
     if (lane == 0 && n_steps > 0) {
-      mbar_expect_tx(B(0), 2 * KB);
+      mbar_expect_tx(B(0), 2 * TB);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
-        tma_load_5d(smem_u32(sK) + c * KC, &tmK, B(0), c * 64, 0, g, bb, n0);
-        tma_load_5d(smem_u32(sV) + c * KC, &tmV, B(0), c * 64, 0, g, bb, n0);
+        tma_load_5d(smem_u32(sK) + c * CH, &tmK, B(0), c * 64, 0, g, bb, n0);
+        tma_load_5d(smem_u32(sV) + c * CH, &tmV, B(0), c * 64, 0, g, bb, n0);
       }
       for (int t = 0; t < n_steps; ++t) {
         const int st = t % NST;
         const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
         if (!mbar_wait(B(QE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
-        mbar_expect_tx(B(QF + st), 2 * QB);
+        mbar_expect_tx(B(QF + st), 2 * TB);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_5d(smem_u32(sQ) + st * QB + c * QC, &tmQ, B(QF + st), c * 64, j, g, bb, q0);
-          tma_load_5d(smem_u32(sdO) + st * QB + c * QC, &tmdO, B(QF + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sQ) + st * TB + c * CH, &tmQ, B(QF + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sdO) + st * TB + c * CH, &tmdO, B(QF + st), c * 64, j, g, bb, q0);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_steps > 0) {
       const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);       // S^T, dP^T
-      const uint32_t idesc_g = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dV, dK: A K-major, B MN-major
+      const uint32_t idesc_g = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dV, dK: A from tensor memory, B MN-major
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
-      bool ok = true;
-      auto issue_sdp = [&](int t) -> bool {
-        const int b = t & 1;
-        if (!mbar_wait(B(QF + t % NST), ((uint32_t)(t / NST)) & 1u, abort_flag, p.status, 34)) return false;
-        fence_after_sync();
-        const uint32_t qb = aQ + (t % NST) * QB, ob = adO + (t % NST) * QB;
+      auto issue_s = [&](int t) {
+        const uint32_t qb = aQ + (t % NST) * TB;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_f16(tS(b), kmajor_desc(aK, kk, KC), kmajor_desc(qb, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_f16(tdP(b), kmajor_desc(aV, kk, KC), kmajor_desc(ob, kk, QC), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(B(SF + b));
-        return true;
+          mma_f16(tS, kmajor_desc(aK, kk, CH), kmajor_desc(qb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF));
       };
-      ok = mbar_wait(B(0), 0, abort_flag, p.status, 32);
-      if (ok) ok = issue_sdp(0);
-      if (ok && n_steps > 1) ok = issue_sdp(1);
+      auto issue_dp = [&](int t) {
+        const uint32_t ob = adO + (t % NST) * TB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP, kmajor_desc(aV, kk, CH), kmajor_desc(ob, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(PF));
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 32) && mbar_wait(B(QF), 0, abort_flag, p.status, 33);
+      if (ok) { fence_after_sync(); issue_s(0); issue_dp(0); }
       for (int t = 0; t < n_steps && ok; ++t) {
-        const int b = t & 1;
-        if (!mbar_wait(B(PF + b), ((uint32_t)(t >> 1)) & 1u, abort_flag, p.status, 36)) { ok = false; break; }
+        const uint32_t par = (uint32_t)t & 1u;
+        const uint32_t qb = aQ + (t % NST) * TB, ob = adO + (t % NST) * TB;
+        if (!mbar_wait(B(AF), par, abort_flag, p.status, 36)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t qb = aQ + (t % NST) * QB, ob = adO + (t % NST) * QB;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          mma_f16_ts(tdV, tS(b) + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(ob, kk, QC), idesc_g,
+          mma_f16_ts(tdV, tS + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(ob, kk, CH), idesc_g,
                      (t > 0 || kk > 0) ? 1u : 0u);
+        if (t + 1 < n_steps) {
+          if (!mbar_wait(B(QF + (t + 1) % NST), ((uint32_t)((t + 1) / NST)) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
+          fence_after_sync();
+          issue_s(t + 1);
+        }
+        if (!mbar_wait(B(BF), par, abort_flag, p.status, 36)) { ok = false; break; }
+        fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          mma_f16_ts(tdK, tdP(b) + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(qb, kk, QC), idesc_g,
+          mma_f16_ts(tdK, tdP + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(qb, kk, CH), idesc_g,
                      (t > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(B(QE + (t % NST)));
-        if (t + 2 < n_steps) ok = issue_sdp(t + 2);
+        mma_commit(B(QE + (t % NST)));         // Q / dO of this step may be overwritten
+        if (t + 1 < n_steps) issue_dp(t + 1);
       }
       if (ok) mma_commit(B(DN));
     }
   } else if (n_steps > 0) {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;                 // which 32 of a step's 64 query columns this warp takes
+    const int part = (warp - 2) >> 2;                 // which 32 of a step's 128 query columns this warp takes
     const int row = quad * 32 + lane;
-    const int ct = threadIdx.x - 64;                 // 0..255 among the compute threads
+    const int ct = threadIdx.x - 64;                 // 0..511 among the compute threads
     const int krow = n0 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     bool ok = true;
-    // per-query statistics of a step (64 lse2 + 64 delta): read from global memory one step ahead, so that the
-    // load's latency is not part of the step
+    // per-query statistics of a step (128 lse2 + 128 delta): read from global memory one step ahead
     auto load_stat = [&](int t) -> float {
       const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
-      const int qi = q0 + (ct & 63);
+      const int qi = q0 + (ct & 127);
       const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
       if (qi >= p.sq) return 0.f;
-      return (ct < 64) ? p.lse[idx] * kLog2e : p.delta[idx];
+      return (ct < 128) ? p.lse[idx] * kLog2e : p.delta[idx];
     };
-    float stat_next = ct < 128 ? load_stat(0) : 0.f;
+    float stat_next = ct < 256 ? load_stat(0) : 0.f;
     for (int t = 0; t < n_steps; ++t) {
-      const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
-      (void)j;
+      const int q0 = (qt0 + t % per_head) * BN + part * 32;        // first query of this warp's columns
+      const uint32_t par = (uint32_t)t & 1u;
       {
-        float* dst = sStat + (t & 1) * 128;
-        if (ct < 128) {
+        float* dst = sStat + (t & 1) * 256;
+        if (ct < 256) {
           dst[ct] = stat_next;
           if (t + 1 < n_steps) stat_next = load_stat(t + 1);
         }
-        bar_sync_compute();
+        asm volatile("bar.sync 1, 512;" ::: "memory");
       }
       if (!ok) continue;              // a wait gave up: keep meeting the other warps at the barrier above, do no more
-      const float* stat = sStat + (t & 1) * 128 + half * 32;
-      const int b = t & 1;
-      if (!mbar_wait(B(SF + b), ((uint32_t)(t >> 1)) & 1u, abort_flag, p.status, 37)) { ok = false; continue; }
+      const float* stat = sStat + (t & 1) * 256 + part * 32;
+      uint32_t r[32];
+      float pr[32];
+      uint32_t w[16];
+      // ---- phase A: P^T
+      if (!mbar_wait(B(SF), par, abort_flag, p.status, 37)) { ok = false; continue; }
       fence_after_sync();
-      uint32_t wp[16], wd[16];
-      uint32_t rs[32], rp[32];
-      tmem_ld32(tS(b) + lane_base + half * 32, rs);
-      tmem_ld32(tdP(b) + lane_base + half * 32, rp);
+      tmem_ld32(tS + lane_base + part * 32, r);
       tmem_wait_ld();
-      // per-element masks only where the step touches the diagonal or the ends of the sequences
-      const bool need_mask = (p.causal && (n0 + BM - 1 > q0 + p.off)) || (q0 + BN > p.sq) || (n0 + BM > p.sk);
-      if (need_mask) {
+      const bool need_mask = (p.causal && (n0 + BM - 1 > q0 + p.off)) || (q0 + 32 > p.sq) || (n0 + BM > p.sk);
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          float pr[2], ds[2];
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(stat + 4 * e4);
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = 2 * c + e;
-            const int qi = q0 + half * 32 + col;
-            const bool masked = (p.causal && krow > qi + p.off) || qi >= p.sq || krow >= p.sk;
-            pr[e] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[col]), p.scale_log2, -stat[col]));
-            ds[e] = pr[e] * (__uint_as_float(rp[col]) - stat[64 + col]) * p.scale;
+        for (int i = 0; i < 4; ++i) {
+          const int e = 4 * e4 + i;
+          float v = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -ls[i]));
+          if (need_mask) {
+            const int qi = q0 + e;
+            if ((p.causal && krow > qi + p.off) || qi >= p.sq || krow >= p.sk) v = 0.f;
           }
-          wp[c] = pack_lp(pr[0], pr[1], p.lp_fmt);
-          wd[c] = pack_lp(ds[0], ds[1], p.lp_fmt);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(rs[2 * c]), p.scale_log2, -stat[2 * c]));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(rs[2 * c + 1]), p.scale_log2, -stat[2 * c + 1]));
-          wp[c] = pack_lp(p0, p1, p.lp_fmt);
-          wd[c] = pack_lp(p0 * (__uint_as_float(rp[2 * c]) - stat[64 + 2 * c]) * p.scale,
-                          p1 * (__uint_as_float(rp[2 * c + 1]) - stat[64 + 2 * c + 1]) * p.scale, p.lp_fmt);
+          pr[e] = v;
         }
       }
-      tmem_st16(tS(b) + lane_base + half * 32, wp);
-      tmem_st16(tdP(b) + lane_base + half * 32, wd);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) w[c] = pack_lp(pr[2 * c], pr[2 * c + 1], p.lp_fmt);
+      // queries [32 part, 32 part + 32) as 16 packed columns over the start of the S^T columns this warp has just read
+      tmem_st16(tS + lane_base + part * 32, w);
       tmem_wait_st();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(B(PF + b));
+      if (lane == 0) mbar_arrive(B(AF));
+      // ---- phase B: dS^T
+      if (!mbar_wait(B(PF), par, abort_flag, p.status, 38)) { ok = false; continue; }
+      fence_after_sync();
+      tmem_ld32(tdP + lane_base + part * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const float4 d4 = *reinterpret_cast<const float4*>(stat + 128 + 4 * e4);
+        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int e = 4 * e4 + i;
+          pr[e] = pr[e] * (__uint_as_float(r[e]) - dl[i]) * p.scale;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 16; ++c) w[c] = pack_lp(pr[2 * c], pr[2 * c + 1], p.lp_fmt);
+      tmem_st16(tdP + lane_base + part * 32, w);
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(BF));
     }
     if (ok && mbar_wait(B(DN), 0, abort_flag, p.status, 39)) {
       fence_after_sync();
       uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
       uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
-#pragma unroll 1
-      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
-        uint32_t o[32];
-        float v[32];
-        tmem_ld32(tdV + lane_base + c, o);
-        tmem_wait_ld();
-        if (krow < p.sk) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
-          store_chunk_global(vrow + c * 2, v, p.lp_fmt);
-        }
-        tmem_ld32(tdK + lane_base + c, o);
-        tmem_wait_ld();
-        if (krow < p.sk) {
+      for (int c = part * (D / 4); c < (part + 1) * (D / 4); c += 16) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
-          store_chunk_global(krow_p + c * 2, v, p.lp_fmt);
+        for (int which = 0; which < 2; ++which) {
+          uint32_t o[16];
+          tmem_ld16((which ? tdK : tdV) + lane_base + c, o);
+          tmem_wait_ld();
+          if (krow < p.sk) {
+            uint4* d4 = reinterpret_cast<uint4*>((which ? krow_p : vrow) + c * 2);
+#pragma unroll
+            for (int q4 = 0; q4 < 2; ++q4)
+              d4[q4] = make_uint4(pack_lp(__uint_as_float(o[q4 * 8]), __uint_as_float(o[q4 * 8 + 1]), p.lp_fmt),
+                                  pack_lp(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]), p.lp_fmt),
+                                  pack_lp(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]), p.lp_fmt),
+                                  pack_lp(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]), p.lp_fmt));
+          }
         }
       }
     }
@@ -1602,15 +1616,18 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     static int use_ts = -1;                                            // MLB_ATTN_TS=0: P^T, dS^T through shared memory
     if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
     if (use_ts) {
-      const int smem_ts = 2 * D * 256 + 8 * D * 128 + 1024 + 256;      // K, V, four Q/dO stages, stats
+      CUtensorMap tmQ2, tmdO2;                                         // 128-query steps
+      if ((rc = make_tmap5(&tmQ2, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
+      if ((rc = make_tmap5(&tmdO2, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 128))) return rc;
+      const int smem_ts = 6 * D * 256 + 2048 + 256;                    // K, V, two Q/dO stages, stats
       if (D == 128) {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<128>, smem_ts))) return rc; set = true; }
-        attn_bwd_dkv_ts_kernel<128><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+        attn_bwd_dkv_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ2, tmK, tmV, tmdO2, p);
       } else {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<64>, smem_ts))) return rc; set = true; }
-        attn_bwd_dkv_ts_kernel<64><<<grid, kAttnBwdThreads, smem_ts, st>>>(tmQ, tmK, tmV, tmdO, p);
+        attn_bwd_dkv_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ2, tmK, tmV, tmdO2, p);
       }
     } else {
       const int smem = 2 * D * 256 + 6 * D * 128 + 2 * 16384 + 1024 + 128;  // K, V, three Q/dO stages, P, dS, stats
