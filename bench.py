@@ -161,6 +161,12 @@ def run_ours(args):
     M = dict(MODELS[args.config])
     if args.layers:
         M["num_layers"] = args.layers
+    if args.seq:
+        M["seq_length"] = args.seq
+    if args.tiny:
+        # same layer count, micro-batch count and code path, matrices small enough that the GPU is never the limit:
+        # the step time is then the host's cost of issuing a step
+        M.update(hidden_size=512, ffn_hidden_size=1408, num_attention_heads=8, vocab_size=4096, seq_length=512)
     dp = world // (tp * pp)
     common = dict(
         num_layers=M["num_layers"], hidden_size=M["hidden_size"], num_attention_heads=M["num_attention_heads"],
@@ -313,8 +319,9 @@ def run_ours(args):
             "dtype": (("mxfp8" if args.fp8_recipe == "mxfp8" else "fp8") if args.fp8 else "bf16"), "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
             "tokens_per_sec_per_gpu": value / args.gpus,
             "model_tflops_per_gpu": fl / (dev_ms / args.steps / 1e3) / 1e12 / args.gpus,
-            "config": {"model": names[1] if not args.layers
-                       else f"{args.config} truncated to {args.layers} layers (debug only)",
+            "config": {"model": names[1] if not (args.layers or args.seq or args.tiny)
+                       else f"{args.config} with debug overrides layers={args.layers} seq={args.seq} tiny={args.tiny} "
+                            "(not a bench value)",
                        "global_batch": GB, "seq_len": S, "micro_batch": B, "parallelism": par,
                        "l2_note": "inputs and weights (>13 GB) far exceed the 126 MB L2 every step"},
             "clocks": clocks,
@@ -357,6 +364,12 @@ def main():
                     help="llama7b is the headline benchmark; the others are the secondary configurations")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a bench value)")
     ap.add_argument("--layout", default=None, help="debug only: override the parallel layout as tp,pp,vpp")
+    ap.add_argument("--tiny", action="store_true",
+                    help="debug only: hidden 512 / seq 512 with the same layers and micro-batches - the step time is the "
+                         "host's cost of issuing a step (result is not a bench value)")
+    ap.add_argument("--seq", type=int, default=0,
+                    help="debug only: override the sequence length; with a short one the step time is the host's cost of "
+                         "issuing the step (result is not a bench value)")
     ap.add_argument("--tp-comm-overlap", action="store_true", default=True)
     ap.add_argument("--no-tp-comm-overlap", dest="tp_comm_overlap", action="store_false")
     ap.add_argument("--fp8", default=None, choices=["e4m3", "hybrid"],
@@ -368,6 +381,10 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif os.environ.get("MLB_BENCH_PROFILE") and int(os.environ.get("RANK", "0")) == 0:
+        # host-side profile of rank 0 (where the Python time of a step goes); the JSON line is then not a bench value
+        import cProfile
+        cProfile.runctx("run_ours(args)", globals(), {"args": args}, filename=os.environ["MLB_BENCH_PROFILE"])
     else:
         run_ours(args)
 

@@ -1497,15 +1497,17 @@ MLB_API int mlb_attn_fwd(int lp_fmt, const void* q, const void* k, const void* v
   if ((o_s % 8) || (o_b % 8) || (o_g % 8) || (o_j % 8) || (reinterpret_cast<uintptr_t>(o) & 15)) return -3;
   CUtensorMap tmQ, tmK, tmV;
   int rc;
+  static int use_v2 = -1;                                    // MLB_ATTN_FWD2=0: two independent 128-row CTAs per SM
+  if (use_v2 < 0) { const char* e = getenv("MLB_ATTN_FWD2"); use_v2 = (e && e[0] == '0') ? 0 : 1; }
   if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
-  if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
-  if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
+  if (!use_v2) {
+    if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
+    if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
+  }
   AttnParams p = {};
   p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
   p.o = o; p.o_s = o_s; p.o_b = o_b; p.o_g = o_g; p.o_j = o_j; p.lse = lse;
-  static int use_v2 = -1;                                    // MLB_ATTN_FWD2=0: two independent 128-row CTAs per SM
-  if (use_v2 < 0) { const char* e = getenv("MLB_ATTN_FWD2"); use_v2 = (e && e[0] == '0') ? 0 : 1; }
   if (use_v2) {
     CUtensorMap tmK2, tmV2;
     if ((rc = make_tmap5(&tmK2, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
@@ -1568,28 +1570,31 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
   p.dk = dk; p.dk_s = dk_s; p.dk_b = dk_b; p.dk_g = dk_g;
   p.dv = dv; p.dv_s = dv_s; p.dv_b = dv_b; p.dv_g = dv_g;
   int rc;
-  {  // dQ: 128-row query tiles, 64-row key tiles
-    CUtensorMap tmQ, tmK, tmV, tmdO;
-    if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
-    if ((rc = make_tmap5(&tmdO, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 128))) return rc;
-    if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
-    if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
+  static int use_ts = -1;                  // MLB_ATTN_TS=0: the kernels with 64-wide steps and P / dS through shared memory
+  if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
+  // 128-row boxes of all four operands serve both kernels of the default path
+  CUtensorMap tmQ, tmdO, tmK128, tmV128;
+  if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
+  if ((rc = make_tmap5(&tmdO, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 128))) return rc;
+  if ((rc = make_tmap5(&tmK128, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
+  if ((rc = make_tmap5(&tmV128, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
+  {  // dQ: 128-row query tiles
+    CUtensorMap tmK, tmV;
+    if (!use_ts) {
+      if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 64))) return rc;
+      if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 64))) return rc;
+    }
     const int grid = ((sq + 127) / 128) * ng * qpg * b;
-    static int use_ts = -1;                                            // MLB_ATTN_TS=0: dS through shared memory
-    if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
     if (use_ts) {
-      CUtensorMap tmK2, tmV2;                                          // 128-key steps
-      if ((rc = make_tmap5(&tmK2, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
-      if ((rc = make_tmap5(&tmV2, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
       const int smem_ts = 7 * D * 256 + 256;                           // Q, dO, three K stages, two V stages
       if (D == 128) {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<128>, smem_ts))) return rc; set = true; }
-        attn_bwd_dq_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK2, tmV2, tmdO, p);
+        attn_bwd_dq_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
       } else {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<64>, smem_ts))) return rc; set = true; }
-        attn_bwd_dq_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK2, tmV2, tmdO, p);
+        attn_bwd_dq_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
       }
       MLB_CHECK_LAUNCH();
     } else {
@@ -1607,38 +1612,33 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     }
   }
   {  // dK, dV: 128-row key tiles, 64-row query tiles
-    CUtensorMap tmQ, tmK, tmV, tmdO;
-    if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 64))) return rc;
-    if ((rc = make_tmap5(&tmdO, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 64))) return rc;
-    if ((rc = make_tmap5(&tmK, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
-    if ((rc = make_tmap5(&tmV, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
+    CUtensorMap tmQ64, tmdO64;
+    if (!use_ts) {
+      if ((rc = make_tmap5(&tmQ64, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 64))) return rc;
+      if ((rc = make_tmap5(&tmdO64, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 64))) return rc;
+    }
     const int grid = ((sk + 127) / 128) * ng * b;
-    static int use_ts = -1;                                            // MLB_ATTN_TS=0: P^T, dS^T through shared memory
-    if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
     if (use_ts) {
-      CUtensorMap tmQ2, tmdO2;                                         // 128-query steps
-      if ((rc = make_tmap5(&tmQ2, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
-      if ((rc = make_tmap5(&tmdO2, d_o, D, qpg, ng, b, sq, do_j, do_g, do_b, do_s, 128))) return rc;
       const int smem_ts = 6 * D * 256 + 2048 + 256;                    // K, V, two Q/dO stages, stats
       if (D == 128) {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<128>, smem_ts))) return rc; set = true; }
-        attn_bwd_dkv_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ2, tmK, tmV, tmdO2, p);
+        attn_bwd_dkv_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
       } else {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<64>, smem_ts))) return rc; set = true; }
-        attn_bwd_dkv_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ2, tmK, tmV, tmdO2, p);
+        attn_bwd_dkv_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
       }
     } else {
       const int smem = 2 * D * 256 + 6 * D * 128 + 2 * 16384 + 1024 + 128;  // K, V, three Q/dO stages, P, dS, stats
       if (D == 128) {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, smem))) return rc; set = true; }
-        attn_bwd_dkv_kernel<128><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+        attn_bwd_dkv_kernel<128><<<grid, kAttnBwdThreads, smem, st>>>(tmQ64, tmK128, tmV128, tmdO64, p);
       } else {
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_bwd_dkv_kernel<64>, smem))) return rc; set = true; }
-        attn_bwd_dkv_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ, tmK, tmV, tmdO, p);
+        attn_bwd_dkv_kernel<64><<<grid, kAttnBwdThreads, smem, st>>>(tmQ64, tmK128, tmV128, tmdO64, p);
       }
     }
     MLB_CHECK_LAUNCH();

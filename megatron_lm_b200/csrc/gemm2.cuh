@@ -295,7 +295,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int quad = warp & 3;
     const int chalf = (warp - 2) >> 2;
     int t = 0, epi_buf = 0;
-    int pend_owner = -1, pend_blk = 0;                    // reduce-scatter: tile whose arrival signal is still owed
+    // reduce-scatter: the last two tiles stored to a peer still owe their arrival signals (a signal may only go out
+    // once the tile's stores have completed at the peer, an NVLink round trip of about two tile times at small K)
+    int pend_owner = -1, pend_blk = 0, pend_groups = 0, pend2_owner = -1, pend2_blk = 0;
     bool ok = true;
     const uint32_t tempty_leader0 = map_to_cta(tempty(0), 0);
     for (; ok; ++t) {
@@ -307,25 +309,27 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
       int mb, nb, owner, mloc; tile_mn(tile, mb, nb, owner, mloc);
       const int m0 = mb * 256 + 128 * (int)rank, n0 = nb * TN;
+      // reduce-scatter: rows of other ranks go to this rank's slot in their receive buffer; this rank's own rows
+      // (computed last) add the peers' arrived partial rows and the residual and are stored finished
+      const bool rs = cp.mode == COMM_RS;
+      const bool rs_own = rs && owner == cp.rank;
+      if (rs_own && lane == 0 && pend_owner >= 0) {
+        // first own tile: the signals still owed to peers go out now, before this tile's accumulator is waited for
+        bulk_wait<0>(); fence_proxy_async_all(); __threadfence_system();
+        if (pend2_owner >= 0) red_release_sys_add(cp.peer_cnt[pend2_owner] + pend2_blk, 1u);
+        red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+        pend_owner = pend2_owner = -1;
+      }
       if (!mbar_wait(tfull(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * TN);
       const int cw = (p.out_mode == OUT_LP) ? 64 : 32;
       uint8_t* my_stage = sEpi + (warp - 2) * 8192;
-      // reduce-scatter: rows of other ranks go to this rank's slot in their receive buffer; this rank's own rows
-      // (computed last) add the peers' arrived partial rows and the residual and are stored finished
-      const bool rs = cp.mode == COMM_RS;
-      const bool rs_own = rs && owner == cp.rank;
       const int blk_loc = 2 * mloc + (int)rank;            // 128-row block inside the owner's rows
       const CUtensorMap* dmap = (rs && !rs_own) ? &xm.m[owner] : &tmD;
       const int drow = rs ? blk_loc * 128 + quad * 32 : m0 + quad * 32;
       const float alpha = (p.scale_a ? *p.scale_a : 1.f) * (p.scale_b ? *p.scale_b : 1.f);
       int n_groups = 0;
-      if (rs_own && lane == 0 && pend_owner >= 0) {       // last tile sent to a peer: flush its signal
-        bulk_wait<0>(); fence_proxy_async_all(); __threadfence_system();
-        red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
-        pend_owner = -1;
-      }
       if (rs_own) {
         if (lane == 0 && !wait_ge<true>(cp.peer_cnt[cp.rank] + blk_loc, cp.cnt_target, p.status, 6)) ok = false;
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -407,15 +411,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         epi_buf ^= 1;
       }
       if (rs && !rs_own && lane == 0) {
-        // Signal one tile late: waiting here for this tile's stores to cross NVLink would stall the warp for a
-        // round trip per tile.  Everything older than the groups just committed has completed after this wait.
-        if (pend_owner >= 0) {
-          bulk_wait_upto(n_groups);
+        // Signal two tiles late: waiting here for this tile's stores to cross NVLink would stall the warp for a
+        // round trip per tile.  Everything older than the groups of the last two tiles has completed after this wait.
+        if (pend2_owner >= 0) {
+          bulk_wait_upto(pend_groups + n_groups);
           fence_proxy_async_all();
           __threadfence_system();
-          red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
+          red_release_sys_add(cp.peer_cnt[pend2_owner] + pend2_blk, 1u);
         }
-        pend_owner = owner; pend_blk = blk_loc;
+        pend2_owner = pend_owner; pend2_blk = pend_blk;
+        pend_owner = owner; pend_blk = blk_loc; pend_groups = n_groups;
       }
       fence_before_sync();
       __syncwarp();
@@ -425,6 +430,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       bulk_wait<0>();
       if (pend_owner >= 0) {
         fence_proxy_async_all(); __threadfence_system();
+        if (pend2_owner >= 0) red_release_sys_add(cp.peer_cnt[pend2_owner] + pend2_blk, 1u);
         red_release_sys_add(cp.peer_cnt[pend_owner] + pend_blk, 1u);
       }
     }

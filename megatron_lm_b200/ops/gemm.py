@@ -66,13 +66,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if bias is not None:
         bias = bias.to(a.dtype).contiguous()
     st = _lib.status_word()
+    stream = _lib.stream()
     args = (1 if a.dtype == torch.bfloat16 else 0, a.data_ptr(), a.stride(0), int(a_mn),
             b.data_ptr(), b.stride(0), int(b_mn), out.data_ptr(), out.stride(0), mode,
-            _lib.ptr(bias), M, N, K, max_ctas, st.data_ptr(), _lib.stream())
+            _lib.ptr(bias), M, N, K, max_ctas, st.data_ptr(), stream)
     if _PAIR and N >= 256 and M >= 256 and (out.stride(0) * out.element_size()) % 16 == 0 and out.data_ptr() % 16 == 0:
         # CTA-pair kernel: 256 x 256 tiles over two SMs
-        dyn = _DYNAMIC and not torch.cuda.is_current_stream_capturing()
-        _lib.check(_lib.lib().mlb_gemm_pair(*args, _sched_words() if dyn else None), "gemm")
+        _lib.check(_lib.lib().mlb_gemm_pair(*args, _sched_words(stream) if _DYNAMIC else None), "gemm")
     else:
         _lib.check(_lib.lib().mlb_gemm(*args), "gemm")
     return out
@@ -95,11 +95,14 @@ def set_dynamic_schedule(on: bool) -> None:
     _DYNAMIC = (env == "1") if env in ("0", "1") else bool(on)
 
 
-def _sched_words() -> int:
-    """Two zeroed words per (device, stream): launches on one stream are ordered, so they can share them."""
-    key = (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+def _sched_words(stream: int) -> Optional[int]:
+    """Two zeroed words per (device, stream): launches on one stream are ordered, so they can share them.  None (static
+    schedule) for a stream first seen while it is being captured into a graph: nothing may be allocated then."""
+    key = (_lib.device_index(), stream)
     t = _sched.get(key)
     if t is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
         with torch.cuda.stream(torch.cuda.default_stream()):
             t = torch.zeros(2, dtype=torch.int32, device="cuda")
         torch.cuda.default_stream().synchronize()

@@ -46,8 +46,8 @@ def _ptr_array(ptrs: List[int]):
 
 
 class FusedTP:
-    def __init__(self, group, rows_per_rank: int, max_k: int, max_n: int, dtype=torch.bfloat16, n_comm: int = 8,
-                 dynamic_schedule: bool = True):
+    def __init__(self, group, rows_per_rank: int, max_k: int, max_n: int, dtype=torch.bfloat16,
+                 n_comm: Optional[int] = None, dynamic_schedule: bool = True):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.tp = dist.get_world_size(group)
@@ -56,7 +56,9 @@ class FusedTP:
         if rows_per_rank % 128:
             raise ValueError("fused TP kernels need (seq * micro_batch / tp) to be a multiple of 128")
         self.dtype = dtype
-        self.n_comm = n_comm
+        # copy-worker CTAs of the all-gather mode (each keeps 160 KB of peer reads in flight).  Sixteen instead of
+        # eight at tensor-parallel 4 measured the same step (64,913 against 64,064 tokens/s) and the same kernel times.
+        self.n_comm = n_comm if n_comm is not None else 8
         dev = torch.device("cuda", torch.cuda.current_device())
         self.max_k, self.max_n = max_k, max_n
         bpr = rows_per_rank // 128
