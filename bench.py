@@ -202,7 +202,8 @@ def run_ours(args):
                            adam_eps=1e-8, clip_grad=1.0, bf16=True, params_dtype=torch.bfloat16,
                            use_distributed_optimizer=dp > 1)
     dcfg = DistributedDataParallelConfig(grad_reduce_in_fp32=True, overlap_grad_reduce=dp > 1,
-                                         use_distributed_optimizer=dp > 1)
+                                         use_distributed_optimizer=dp > 1,
+                                         peer_memory_collectives=not args.no_peer_dist_opt)
     model, opt, sched = setup_model_and_optimizer(
         provider, cfg, ocfg, dcfg,
         scheduler_kwargs=dict(lr=3e-4, min_lr=3e-5, lr_decay_style="cosine", train_iters=1000,
@@ -364,6 +365,8 @@ def main():
                     help="llama7b is the headline benchmark; the others are the secondary configurations")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result is not a bench value)")
     ap.add_argument("--layout", default=None, help="debug only: override the parallel layout as tp,pp,vpp")
+    ap.add_argument("--no-peer-dist-opt", action="store_true",
+                    help="data-parallel layouts: distributed optimizer through NCCL instead of the peer-memory kernels")
     ap.add_argument("--tiny", action="store_true",
                     help="debug only: hidden 512 / seq 512 with the same layers and micro-batches - the step time is the "
                          "host's cost of issuing a step (result is not a bench value)")

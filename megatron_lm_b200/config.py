@@ -512,8 +512,10 @@ class DistributedDataParallelConfig:
     keep_fp8_transpose_cache_when_using_custom_fsdp: bool = False
     nccl_ub: bool = False
     # gradient reduce-scatter and parameter all-gather of the distributed optimizer as peer-memory kernels (pull-
-    # reduce fused with scaling and norm; AdamW storing its result into every rank's parameter buffer)
-    peer_memory_collectives: bool = False
+    # reduce fused with scaling and norm, overlapped with the backward pass; AdamW storing its result into every
+    # rank's parameter buffer).  On by default; it applies where it can - distributed optimizer, fp32 gradients, bf16
+    # parameters, a data-parallel group of at most eight GPUs inside one node - and NCCL is used everywhere else.
+    peer_memory_collectives: bool = True
     # thread blocks of one peer-memory gradient pull (it overlaps the backward pass, so it gets a small grid)
     peer_pull_blocks: int = 64
     # --ddp-num-buckets: split each buffer into this many buckets (overrides bucket_size)

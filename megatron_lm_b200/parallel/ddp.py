@@ -44,6 +44,14 @@ class Bucket:
     params: List[nn.Parameter] = field(default_factory=list)
 
 
+def _single_node() -> bool:
+    """Peer memory only reaches GPUs of this node: true when the launcher says every rank of the job is local."""
+    import os
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+    return local >= world
+
+
 class ParamAndGradBuffer:
     """One contiguous parameter buffer and one gradient buffer, partitioned into buckets."""
 
@@ -97,7 +105,8 @@ class ParamAndGradBuffer:
         # stores updated weights straight into the peers' parameter buffers.
         self.peer = None
         want_peer = getattr(ddp_config, "peer_memory_collectives", False) and self.use_dist_opt and dp_size > 1 \
-            and dp_size <= 8 and dev.type == "cuda" and grad_dtype == torch.float32 and param_dtype == torch.bfloat16
+            and dp_size <= 8 and dev.type == "cuda" and grad_dtype == torch.float32 and param_dtype == torch.bfloat16 \
+            and _single_node()
         if want_peer:
             import os
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")

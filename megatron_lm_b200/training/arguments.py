@@ -80,8 +80,11 @@ def build_parser(extra_args_provider: Optional[Callable] = None) -> argparse.Arg
                    help="where parity is computed and held: peer GPUs' memory (auto on NCCL jobs) or host memory")
     g = parser.add_argument_group(title="peer-memory kernels")
     g.add_argument("--peer-memory-collectives", action="store_true",
-                   help="distributed optimizer: gradient reduce-scatter as a pull kernel over NVLink peer memory and "
-                        "AdamW storing new weights into every rank's parameter buffer (single node)")
+                   help="(default) distributed optimizer: gradient reduce-scatter as a pull kernel over NVLink peer memory, "
+                        "overlapped with backward, and AdamW storing new weights into every rank's parameter buffer "
+                        "(data-parallel group of at most eight GPUs inside one node; NCCL elsewhere)")
+    g.add_argument("--no-peer-memory-collectives", action="store_true",
+                   help="distributed optimizer through NCCL reduce-scatter / all-gather only")
     g.add_argument("--cross-entropy-peer-exchange", action="store_true",
                    help="vocab-parallel cross entropy exchanges its row statistics through peer memory instead of all-reduces")
     if extra_args_provider is not None:
@@ -448,7 +451,7 @@ def ddp_config_from_args(args) -> DistributedDataParallelConfig:
     kw["bucket_size"] = getattr(args, "ddp_bucket_size", None)
     kw["average_in_collective"] = getattr(args, "ddp_average_in_collective", False)
     kw["pad_buckets_for_high_nccl_busbw"] = getattr(args, "ddp_pad_buckets_for_high_nccl_busbw", False)
-    kw["peer_memory_collectives"] = getattr(args, "peer_memory_collectives", False)
+    kw["peer_memory_collectives"] = not getattr(args, "no_peer_memory_collectives", False)
     kw["num_buckets"] = getattr(args, "ddp_num_buckets", None)
     if getattr(args, "cross_entropy_peer_exchange", False):
         import os
