@@ -119,7 +119,6 @@ class ModelParallelConfig:
 # communication-overlap tuning knobs) are accepted without effect: there is one implementation here.
 UNSUPPORTED_FIELDS = {
     "apply_residual_connection_post_layernorm": "the residual is always taken before the norm",
-    "window_size": "sliding-window attention is not built",
     "cpu_offloading": "activation / weight offloading to the host is not built",
     "fp8_dot_product_attention": "attention runs in bf16 / fp16",
     "fp8_multi_head_attention": "attention runs in bf16 / fp16",

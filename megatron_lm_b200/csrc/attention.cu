@@ -36,6 +36,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 struct AttnParams {
   int sq, sk, b, ng, qpg, causal, off;     // off = sk - sq (last query sees last key)
+  int win;                                 // causal sliding window: query q sees keys [q + off - win, q + off]; 2^30 = none
   float scale, scale_log2;
   int lp_fmt;
   int* status;
@@ -553,6 +554,249 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
 
+// The same kernel with a causal sliding window (query q sees keys [q + off - win, q + off]): a tile starts at the step
+// that holds the lowest key its first row sees, rings and barrier phases count from there, and tiles that the window
+// cuts get per-element masks.  Kept as a kernel of its own: the forward kernel sits at its register limit, and the
+// extra live values of the window logic cost calls without a window a fifth of their speed.
+template <int D>
+__global__ void __launch_bounds__(kAttnFwd2Threads, 1)
+attn_fwd2_win_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  constexpr int BM = 128, BN = 128;
+  constexpr int QB = D * 256, KVB = D * 256, CH = 16384;               // tile bytes; bytes of a 64-column chunk
+  constexpr int NSLOT = 5;                                              // ring of K0 V0 K1 V1 K2 ...
+  constexpr uint32_t TCOLS = 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + 2 * QB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + NSLOT * KVB);
+  constexpr int QF = 0, KF = 2, KE = KF + NSLOT, SF = KE + NSLOT, PF = SF + 2, OD = PF + 2, NBAR = OD + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_qtiles = (p.sq + 2 * BM - 1) / (2 * BM);
+  const int heads = p.ng * p.qpg;
+  const int qt = n_qtiles - 1 - (int)(blockIdx.x / (heads * p.b));      // heavy (late) tiles first
+  const int hb = blockIdx.x % (heads * p.b);
+  const int bb = hb / heads, hh = hb % heads, g = hh / p.qpg, j = hh % p.qpg;
+  const int s0 = qt * 2 * BM;
+  auto steps_of = [&](int i) {
+    const int s0i = s0 + i * BM;
+    int kv_end = p.sk;
+    if (p.causal) { kv_end = s0i + BM + p.off; if (kv_end > p.sk) kv_end = p.sk; }
+    return (s0i < p.sq && kv_end > 0) ? (kv_end + BN - 1) / BN : 0;
+  };
+  // first step of a tile: the step that holds the lowest key its first row sees (sliding window)
+  auto first_of = [&](int i) {
+    int lo = p.causal ? s0 + i * BM + p.off - p.win : 0;
+    return lo > 0 ? lo / BN : 0;
+  };
+  const int n_t0 = steps_of(0), n_t1 = steps_of(1);
+  const int b_t0 = first_of(0), b_t1 = first_of(1);
+  auto n_of = [&](int i) { return i ? n_t1 : n_t0; };
+  auto b_of = [&](int i) { return i ? b_t1 : b_t0; };
+  const int n_kv = n_t0 > n_t1 ? n_t0 : n_t1;
+  const int t_lo = n_t0 > 0 ? b_t0 : b_t1;             // steps [t_lo, n_kv) are loaded; tile i works on [b_of(i), n_of(i))
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(QF), 1); mbar_init(B(QF + 1), 1);
+    for (int i = 0; i < 2 * NSLOT; ++i) mbar_init(B(KF + i), 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(B(SF + i), 1); mbar_init(B(PF + i), 4); mbar_init(B(OD + i), 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  auto tS = [&](int i) { return tmem + (uint32_t)(128 * i); };
+  auto tO = [&](int i) { return tmem + 256u + (uint32_t)(D * i); };
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (n_of(i) > 0) {
+          mbar_expect_tx(B(QF + i), QB);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_5d(smem_u32(sQ) + i * QB + c * CH, &tmQ, B(QF + i), c * 64, j, g, bb, s0 + i * BM);
+        }
+      for (int u = 0; u < 2 * (n_kv - t_lo); ++u) {                     // u = 2 (t - t_lo): K of step t; + 1: V
+        const int slot = u % NSLOT;
+        if (!mbar_wait(B(KE + slot), (((uint32_t)(u / NSLOT)) & 1u) ^ 1u, abort_flag, p.status, 11)) break;
+        mbar_expect_tx(B(KF + slot), KVB);
+        const CUtensorMap* tm = (u & 1) ? &tmV : &tmK;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sKV) + slot * KVB + c * CH, tm, B(KF + slot), c * 64, 0, g, bb, (t_lo + (u >> 1)) * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);
+      const uint32_t idesc_o = make_idesc(BM, D, p.lp_fmt, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aKV = smem_u32(sKV);
+      auto kv_ready = [&](int u) {
+        return mbar_wait(B(KF + u % NSLOT), ((uint32_t)(u / NSLOT)) & 1u, abort_flag, p.status, 13);
+      };
+      auto issue_s = [&](int i, int t) {
+        const uint32_t kb = aKV + ((2 * (t - t_lo)) % NSLOT) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS(i), kmajor_desc(aQ + i * QB, kk, CH), kmajor_desc(kb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF + i));
+      };
+      auto issue_pv = [&](int i, int t) {
+        const uint32_t vb = aKV + ((2 * (t - t_lo) + 1) % NSLOT) * KVB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tO(i), tS(i) + (uint32_t)(kk * 8), mnmajor_desc(vb, kk, CH), idesc_o,
+                     (t > b_of(i) || kk > 0) ? 1u : 0u);
+        mma_commit(B(OD + i));
+      };
+      bool ok = true;
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        if (ok && n_of(i) > 0) ok = mbar_wait(B(QF + i), 0, abort_flag, p.status, 12);
+      if (ok) ok = kv_ready(0);
+      if (ok) {
+        fence_after_sync();
+        if (n_t0 > 0 && b_t0 == t_lo) issue_s(0, t_lo);
+        if (n_t1 > 0 && b_t1 == t_lo) issue_s(1, t_lo);
+        mma_commit(B(KE + 0));
+      }
+      for (int t = t_lo; t < n_kv && ok; ++t) {
+        const int u = 2 * (t - t_lo);
+        bool v_ready = false, k_next_ready = false;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (t >= b_of(i) && t < n_of(i)) {
+            if (!v_ready) { if (!kv_ready(u + 1)) { ok = false; break; } v_ready = true; }
+            if (!mbar_wait(B(PF + i), (uint32_t)(t - b_of(i)) & 1u, abort_flag, p.status, 16)) { ok = false; break; }
+            fence_after_sync();
+            issue_pv(i, t);
+          }
+          if (t + 1 >= b_of(i) && t + 1 < n_of(i)) {
+            if (!k_next_ready) { if (!kv_ready(u + 2)) { ok = false; break; } k_next_ready = true; fence_after_sync(); }
+            issue_s(i, t + 1);
+          }
+        }
+        if (!ok) break;
+        if (!v_ready) ok = kv_ready(u + 1);                            // a V tile nobody used is still consumed in order
+        if (ok && t + 1 < n_kv && !k_next_ready) ok = kv_ready(u + 2);
+        if (!ok) break;
+        mma_commit(B(KE + (u + 1) % NSLOT));                          // V of this step
+        if (t + 1 < n_kv) mma_commit(B(KE + (u + 2) % NSLOT));        // K of the next
+      }
+    }
+  } else {
+    const int i = (warp - 2) >> 2;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int s0i = s0 + i * BM;
+    const int qrow = s0i + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const int n_mine = n_of(i), b_mine = b_of(i);
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int t = b_mine; t < n_mine; ++t) {
+      const int n0 = t * BN;
+      const uint32_t par = (uint32_t)(t - b_mine) & 1u;
+      if (!mbar_wait(B(SF + i), par, abort_flag, p.status, 17)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS(i) + lane_base + c * 32, r[c]);
+      tmem_wait_ld();
+      const bool need_mask = (p.causal && (n0 + BN - 1 > s0i + p.off || (n0 + p.win < s0i + BM - 1 + p.off))) ||
+                             (n0 + BN > p.sk);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kv = n0 + c * 32 + e;
+            if ((p.causal && (kv > qrow + p.off || (kv + p.win < qrow + p.off))) || kv >= p.sk)
+              r[c][e] = 0xff800000u;                                                        // -inf
+          }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        mx0 = fmaxf(mx0, __uint_as_float(r[0][e])); mx1 = fmaxf(mx1, __uint_as_float(r[1][e]));
+        mx2 = fmaxf(mx2, __uint_as_float(r[2][e])); mx3 = fmaxf(mx3, __uint_as_float(r[3][e]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      const float m_new = fmaxf(m_ref, mx);
+      const bool resc = m_new > m_ref + 8.f;
+      float alpha = 1.f;
+      if (resc) { alpha = fast_exp2(m_ref - m_new); m_ref = m_new; l *= alpha; }
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float a0 = fast_exp2(fmaf(__uint_as_float(r[c][2 * e]), p.scale_log2, neg_m));
+          const float a1 = fast_exp2(fmaf(__uint_as_float(r[c][2 * e + 1]), p.scale_log2, neg_m));
+          ls0 += a0; ls1 += a1;
+          w[e] = pack_lp(a0, a1, p.lp_fmt);
+        }
+        tmem_st16(tS(i) + lane_base + c * 16, w);                       // keys [32 c, 32 c + 32) -> 16 packed columns
+      }
+      l += ls0 + ls1;
+      if (t > b_mine && __any_sync(0xffffffffu, resc)) {
+        // O of this tile has to be rescaled: its last product (step t - 1) must have completed
+        if (!mbar_wait(B(OD + i), par ^ 1u, abort_flag, p.status, 18)) { ok = false; break; }
+        fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tO(i) + lane_base + c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st32(tO(i) + lane_base + c, o);
+        }
+      }
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(PF + i));
+    }
+    if (ok && n_mine > 0 && mbar_wait(B(OD + i), (uint32_t)(n_mine - 1 - b_mine) & 1u, abort_flag, p.status, 19)) {
+      fence_after_sync();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                      2 * ((long)qrow * p.o_s + (long)bb * p.o_b + (long)g * p.o_g + (long)j * p.o_j);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tO(i) + lane_base + c, o);
+        tmem_wait_ld();
+        if (qrow < p.sq) {
+          float v[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(o[e]) * inv_l;
+          store_chunk_global(orow + c * 2, v, p.lp_fmt);
+        }
+      }
+      if (qrow < p.sq)
+        p.lse[(((long)bb * p.ng + g) * p.qpg + j) * p.sq + qrow] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
 // ============================================================================ delta = rowsum(O * dO)
 __global__ void attn_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o, float* __restrict__ delta,
                                   int sq, int b, int ng, int qpg, int D, long o_s, long o_b, long o_g, long o_j,
@@ -950,6 +1194,213 @@ attn_bwd_dq_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                        pr[2 * c + 1] * (__uint_as_float(r[2 * c + 1]) - dlt) * p.scale, p.lp_fmt);
       // dS of the previous step must have been consumed by its dQ product
       if (t > 0 && !mbar_wait(B(DR), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 28)) { ok = false; break; }
+      fence_after_sync();
+      tmem_st16(tdS + lane_base + part * 16, w);    // keys [32 part, 32 part + 32) = 16 packed columns
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(DF));
+    }
+    if (ok && mbar_wait(B(DN), 0, abort_flag, p.status, 29)) {
+      fence_after_sync();
+      uint8_t* drow = reinterpret_cast<uint8_t*>(p.dq) +
+                      2 * ((long)qrow * p.dq_s + (long)bb * p.dq_b + (long)g * p.dq_g + (long)j * p.dq_j);
+#pragma unroll
+      for (int c = part * (D / 4); c < (part + 1) * (D / 4); c += 16) {
+        uint32_t o[16];
+        tmem_ld16(tdQ + lane_base + c, o);
+        tmem_wait_ld();
+        if (qrow < p.sq) {
+          uint4* d4 = reinterpret_cast<uint4*>(drow + c * 2);
+#pragma unroll
+          for (int q4 = 0; q4 < 2; ++q4)
+            d4[q4] = make_uint4(pack_lp(__uint_as_float(o[q4 * 8]), __uint_as_float(o[q4 * 8 + 1]), p.lp_fmt),
+                                pack_lp(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]), p.lp_fmt),
+                                pack_lp(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]), p.lp_fmt),
+                                pack_lp(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]), p.lp_fmt));
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
+// The same kernel with a causal sliding window: steps start at the one that holds the lowest key the tile sees.
+template <int D>
+__global__ void __launch_bounds__(kAttnDqThreads, 1)
+attn_bwd_dq_ts_win_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                      const AttnParams p) {
+  constexpr int BM = 128, BN = 128;
+  constexpr int TB = D * 256, CH = 16384;              // bytes of a 128-row tile / of one of its 64-column chunks
+  constexpr uint32_t TCOLS = 512;
+  constexpr int NK = 3, NV = 2;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + TB;
+  uint8_t* sK = sdO + TB;
+  uint8_t* sV = sK + NK * TB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NV * TB);
+  // q_full | k_full[3] | k_empty[3] | v_full[2] | v_empty[2] | s_full | dp_full | s_read | dp_read | ds_full | ds_read | done
+  constexpr int KF = 1, KE = KF + NK, VF = KE + NK, VE = VF + NV, SF = VE + NV, PF = SF + 1, SE = PF + 1, PE = SE + 1,
+                DF = PE + 1, DR = DF + 1, DN = DR + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DN + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int n_qtiles = (p.sq + BM - 1) / BM;
+  const int heads = p.ng * p.qpg;
+  const int qt = n_qtiles - 1 - (int)(blockIdx.x / (heads * p.b));
+  const int hb = blockIdx.x % (heads * p.b);
+  const int bb = hb / heads, hh = hb % heads, g = hh / p.qpg, j = hh % p.qpg;
+  const int s0 = qt * BM;
+  int kv_end = p.sk;
+  if (p.causal) { kv_end = s0 + BM + p.off; if (kv_end > p.sk) kv_end = p.sk; }
+  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+  // lowest key the tile's first row sees (sliding window)
+  const int kv_lo = (p.causal) ? s0 + p.off - p.win : 0;
+  const int t_lo = kv_lo > 0 ? kv_lo / BN : 0;           // steps [t_lo, n_kv); rings and barrier phases count from t_lo
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    for (int i = KF; i < SF; ++i) mbar_init(B(i), 1);
+    mbar_init(B(SF), 1); mbar_init(B(PF), 1); mbar_init(B(SE), 16); mbar_init(B(PE), 16); mbar_init(B(DF), 16);
+    mbar_init(B(DR), 1); mbar_init(B(DN), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256, tdS = tmem + 256 + D;
+
+  if (warp == 0) {
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(B(0), 2 * TB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_5d(smem_u32(sQ) + c * CH, &tmQ, B(0), c * 64, j, g, bb, s0);
+        tma_load_5d(smem_u32(sdO) + c * CH, &tmdO, B(0), c * 64, j, g, bb, s0);
+      }
+      for (int t = t_lo; t < n_kv; ++t) {
+        const int u = t - t_lo;
+        const int ks = u % NK, vs = u % NV;
+        if (!mbar_wait(B(KE + ks), (((uint32_t)(u / NK)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(KF + ks), TB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sK) + ks * TB + c * CH, &tmK, B(KF + ks), c * 64, 0, g, bb, t * BN);
+        if (!mbar_wait(B(VE + vs), (((uint32_t)(u / NV)) & 1u) ^ 1u, abort_flag, p.status, 21)) break;
+        mbar_expect_tx(B(VF + vs), TB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_5d(smem_u32(sV) + vs * TB + c * CH, &tmV, B(VF + vs), c * 64, 0, g, bb, t * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);
+      const uint32_t idesc_q = make_idesc(BM, D, p.lp_fmt, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV);
+      // S of step t once its K tile has landed and (t > 0) the compute warps hold S of step t - 1 in registers
+      auto issue_s = [&](int u) -> bool {                 // u = step - t_lo
+        if (!mbar_wait(B(KF + u % NK), ((uint32_t)(u / NK)) & 1u, abort_flag, p.status, 24)) return false;
+        if (u > 0 && !mbar_wait(B(SE), (uint32_t)(u - 1) & 1u, abort_flag, p.status, 25)) return false;
+        fence_after_sync();
+        const uint32_t kb = aK + (u % NK) * TB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS, kmajor_desc(aQ, kk, CH), kmajor_desc(kb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF));
+        return true;
+      };
+      auto issue_dp = [&](int u) -> bool {
+        if (!mbar_wait(B(VF + u % NV), ((uint32_t)(u / NV)) & 1u, abort_flag, p.status, 24)) return false;
+        if (u > 0 && !mbar_wait(B(PE), (uint32_t)(u - 1) & 1u, abort_flag, p.status, 25)) return false;
+        fence_after_sync();
+        const uint32_t vb = aV + (u % NV) * TB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP, kmajor_desc(adO, kk, CH), kmajor_desc(vb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(PF));
+        mma_commit(B(VE + u % NV));            // this V tile may be overwritten
+        return true;
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 22);
+      if (ok) ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
+      const int n_u = n_kv - t_lo;
+      for (int u = 0; u < n_u && ok; ++u) {
+        if (u + 1 < n_u) {
+          if (!issue_s(u + 1) || !issue_dp(u + 1)) { ok = false; break; }
+        }
+        if (!mbar_wait(B(DF), (uint32_t)u & 1u, abort_flag, p.status, 26)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t kb = aK + (u % NK) * TB;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tdQ, tdS + (uint32_t)(kk * 8), mnmajor_desc(kb, kk, CH), idesc_q, (u > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(KE + u % NK));            // this K tile may be overwritten
+        mma_commit(B(DR));                     // and dS rewritten
+      }
+      if (ok) mma_commit(B(DN));
+    }
+  } else if (n_kv > 0) {
+    const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;               // which 32 of a step's 128 key columns
+    const int row = quad * 32 + lane;
+    const int qrow = s0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const long stat_idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qrow;
+    const float lse2 = qrow < p.sq ? p.lse[stat_idx] * kLog2e : 0.f;
+    const float dlt = qrow < p.sq ? p.delta[stat_idx] : 0.f;
+    bool ok = true;
+    for (int t = t_lo; t < n_kv; ++t) {
+      const int n0 = t * BN + part * 32;            // first key of this warp's columns
+      const uint32_t par = (uint32_t)(t - t_lo) & 1u;
+      uint32_t r[32];
+      float pr[32];
+      if (!mbar_wait(B(SF), par, abort_flag, p.status, 27)) { ok = false; break; }
+      fence_after_sync();
+      tmem_ld32(tS + lane_base + part * 32, r);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(SE));
+      const bool need_mask = (p.causal && (n0 + 31 > s0 + p.off || (n0 + p.win < s0 + BM - 1 + p.off))) ||
+                             (n0 + 32 > p.sk) || (s0 + BM > p.sq);
+      if (need_mask) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kv = n0 + e;
+          const bool masked = (p.causal && (kv > qrow + p.off || (kv + p.win < qrow + p.off))) || kv >= p.sk || qrow >= p.sq;
+          pr[e] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -lse2));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) pr[e] = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -lse2));
+      }
+      if (!mbar_wait(B(PF), par, abort_flag, p.status, 27)) { ok = false; break; }
+      fence_after_sync();
+      tmem_ld32(tdP + lane_base + part * 32, r);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(PE));
+      uint32_t w[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        w[c] = pack_lp(pr[2 * c] * (__uint_as_float(r[2 * c]) - dlt) * p.scale,
+                       pr[2 * c + 1] * (__uint_as_float(r[2 * c + 1]) - dlt) * p.scale, p.lp_fmt);
+      // dS of the previous step must have been consumed by its dQ product
+      if (t > t_lo && !mbar_wait(B(DR), par ^ 1u, abort_flag, p.status, 28)) { ok = false; break; }
       fence_after_sync();
       tmem_st16(tdS + lane_base + part * 16, w);    // keys [32 part, 32 part + 32) = 16 packed columns
       tmem_wait_st();
@@ -1466,6 +1917,254 @@ attn_bwd_dkv_ts_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
 }
 
+// The same kernel with a causal sliding window: query tiles end at the last query whose window reaches the key tile.
+template <int D>
+__global__ void __launch_bounds__(kAttnDqThreads, 1)
+attn_bwd_dkv_ts_win_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                       const AttnParams p) {
+  constexpr int BM = 128, BN = 128;                // BM key rows per CTA, BN query rows per step
+  constexpr int TB = D * 256, CH = 16384;          // bytes of a 128-row tile / of one of its 64-column chunks
+  constexpr uint32_t TCOLS = 512;
+  constexpr int NST = 2;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TB;
+  uint8_t* sQ = sV + TB;
+  uint8_t* sdO = sQ + NST * TB;
+  float* sStat = reinterpret_cast<float*>(sdO + NST * TB);     // [2][2][128] lse2 / delta per step parity
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 512);
+  // kv_full | q_full[2] | q_empty[2] | s_full | dp_full | p_full | ds_full | done
+  constexpr int QF = 1, QE = QF + NST, SF = QE + NST, PF = SF + 1, AF = PF + 1, BF = AF + 1, DN = BF + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DN + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto B = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int kt = blockIdx.x / (p.ng * p.b);                    // early key tiles see the most queries
+  const int gb = blockIdx.x % (p.ng * p.b);
+  const int bb = gb / p.ng, g = gb % p.ng;
+  const int n0 = kt * BM;
+  // query tiles that can see at least one key of this tile: q + off >= n0
+  int q_begin = 0;
+  if (p.causal) { q_begin = n0 - p.off; if (q_begin < 0) q_begin = 0; }
+  const int qt0 = q_begin / BN;
+  // ... and, with a sliding window, at most up to the last query whose window still reaches the tile's last key
+  int q_end = p.sq;
+  if (p.causal) { const long e = (long)n0 + BM + p.win - p.off; if (e < (long)q_end) q_end = (int)e; }
+  const int n_qt = q_end > 0 ? (q_end + BN - 1) / BN : 0;
+  const int per_head = n_qt > qt0 ? n_qt - qt0 : 0;
+  const int n_steps = per_head * p.qpg;
+
+  if (threadIdx.x == 0) {
+    mbar_init(B(0), 1);
+    for (int i = 0; i < 2 * NST; ++i) mbar_init(B(QF + i), 1);
+    mbar_init(B(SF), 1); mbar_init(B(PF), 1); mbar_init(B(AF), 16); mbar_init(B(BF), 16); mbar_init(B(DN), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmdO);
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TCOLS); tmem_relinquish(); }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tdV = tmem, tdK = tmem + D, tS = tmem + 2 * D, tdP = tmem + 2 * D + 128;
+
+  if (warp == 0) {
+    if (lane == 0 && n_steps > 0) {
+      mbar_expect_tx(B(0), 2 * TB);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_5d(smem_u32(sK) + c * CH, &tmK, B(0), c * 64, 0, g, bb, n0);
+        tma_load_5d(smem_u32(sV) + c * CH, &tmV, B(0), c * 64, 0, g, bb, n0);
+      }
+      for (int t = 0; t < n_steps; ++t) {
+        const int st = t % NST;
+        const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+        if (!mbar_wait(B(QE + st), (((uint32_t)(t / NST)) & 1u) ^ 1u, abort_flag, p.status, 31)) break;
+        mbar_expect_tx(B(QF + st), 2 * TB);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_5d(smem_u32(sQ) + st * TB + c * CH, &tmQ, B(QF + st), c * 64, j, g, bb, q0);
+          tma_load_5d(smem_u32(sdO) + st * TB + c * CH, &tmdO, B(QF + st), c * 64, j, g, bb, q0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_steps > 0) {
+      const uint32_t idesc_s = make_idesc(BM, BN, p.lp_fmt, 0, 0);       // S^T, dP^T
+      const uint32_t idesc_g = make_idesc(BM, D, p.lp_fmt, 0, 1);        // dV, dK: A from tensor memory, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), adO = smem_u32(sdO);
+      auto issue_s = [&](int t) {
+        const uint32_t qb = aQ + (t % NST) * TB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tS, kmajor_desc(aK, kk, CH), kmajor_desc(qb, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(SF));
+      };
+      auto issue_dp = [&](int t) {
+        const uint32_t ob = adO + (t % NST) * TB;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_f16(tdP, kmajor_desc(aV, kk, CH), kmajor_desc(ob, kk, CH), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(B(PF));
+      };
+      bool ok = mbar_wait(B(0), 0, abort_flag, p.status, 32) && mbar_wait(B(QF), 0, abort_flag, p.status, 33);
+      if (ok) { fence_after_sync(); issue_s(0); issue_dp(0); }
+      for (int t = 0; t < n_steps && ok; ++t) {
+        const uint32_t par = (uint32_t)t & 1u;
+        const uint32_t qb = aQ + (t % NST) * TB, ob = adO + (t % NST) * TB;
+        if (!mbar_wait(B(AF), par, abort_flag, p.status, 36)) { ok = false; break; }
+        fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tdV, tS + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(ob, kk, CH), idesc_g,
+                     (t > 0 || kk > 0) ? 1u : 0u);
+        if (t + 1 < n_steps) {
+          if (!mbar_wait(B(QF + (t + 1) % NST), ((uint32_t)((t + 1) / NST)) & 1u, abort_flag, p.status, 34)) { ok = false; break; }
+          fence_after_sync();
+          issue_s(t + 1);
+        }
+        if (!mbar_wait(B(BF), par, abort_flag, p.status, 36)) { ok = false; break; }
+        fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_f16_ts(tdK, tdP + (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8), mnmajor_desc(qb, kk, CH), idesc_g,
+                     (t > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(B(QE + (t % NST)));         // Q / dO of this step may be overwritten
+        if (t + 1 < n_steps) issue_dp(t + 1);
+      }
+      if (ok) mma_commit(B(DN));
+    }
+  } else if (n_steps > 0) {
+    const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;                 // which 32 of a step's 128 query columns this warp takes
+    const int row = quad * 32 + lane;
+    const int ct = threadIdx.x - 64;                 // 0..511 among the compute threads
+    const int krow = n0 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    bool ok = true;
+    // per-query statistics of a step (128 lse2 + 128 delta): read from global memory one step ahead
+    auto load_stat = [&](int t) -> float {
+      const int j = t / per_head, q0 = (qt0 + t % per_head) * BN;
+      const int qi = q0 + (ct & 127);
+      const long idx = (((long)bb * p.ng + g) * p.qpg + j) * p.sq + qi;
+      if (qi >= p.sq) return 0.f;
+      return (ct < 128) ? p.lse[idx] * kLog2e : p.delta[idx];
+    };
+    float stat_next = ct < 256 ? load_stat(0) : 0.f;
+    for (int t = 0; t < n_steps; ++t) {
+      const int q0 = (qt0 + t % per_head) * BN + part * 32;        // first query of this warp's columns
+      const uint32_t par = (uint32_t)t & 1u;
+      {
+        float* dst = sStat + (t & 1) * 256;
+        if (ct < 256) {
+          dst[ct] = stat_next;
+          if (t + 1 < n_steps) stat_next = load_stat(t + 1);
+        }
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+      }
+      if (!ok) continue;              // a wait gave up: keep meeting the other warps at the barrier above, do no more
+      const float* stat = sStat + (t & 1) * 256 + part * 32;
+      uint32_t r[32];
+      float pr[32];
+      uint32_t w[16];
+      // ---- phase A: P^T
+      if (!mbar_wait(B(SF), par, abort_flag, p.status, 37)) { ok = false; continue; }
+      fence_after_sync();
+      tmem_ld32(tS + lane_base + part * 32, r);
+      tmem_wait_ld();
+      const bool need_mask = (p.causal && (n0 + BM - 1 > q0 + p.off || (n0 + p.win < q0 + 31 + p.off))) ||
+                             (q0 + 32 > p.sq) || (n0 + BM > p.sk);
+#pragma unroll
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(stat + 4 * e4);
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int e = 4 * e4 + i;
+          float v = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, -ls[i]));
+          if (need_mask) {
+            const int qi = q0 + e;
+            if ((p.causal && (krow > qi + p.off || (krow + p.win < qi + p.off))) || qi >= p.sq || krow >= p.sk) v = 0.f;
+          }
+          pr[e] = v;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 16; ++c) w[c] = pack_lp(pr[2 * c], pr[2 * c + 1], p.lp_fmt);
+      // queries [32 part, 32 part + 32) as 16 packed columns over the start of the S^T columns this warp has just read
+      tmem_st16(tS + lane_base + part * 32, w);
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(AF));
+      // ---- phase B: dS^T
+      if (!mbar_wait(B(PF), par, abort_flag, p.status, 38)) { ok = false; continue; }
+      fence_after_sync();
+      tmem_ld32(tdP + lane_base + part * 32, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const float4 d4 = *reinterpret_cast<const float4*>(stat + 128 + 4 * e4);
+        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int e = 4 * e4 + i;
+          pr[e] = pr[e] * (__uint_as_float(r[e]) - dl[i]) * p.scale;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 16; ++c) w[c] = pack_lp(pr[2 * c], pr[2 * c + 1], p.lp_fmt);
+      tmem_st16(tdP + lane_base + part * 32, w);
+      tmem_wait_st();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(B(BF));
+    }
+    if (ok && mbar_wait(B(DN), 0, abort_flag, p.status, 39)) {
+      fence_after_sync();
+      uint8_t* vrow = reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g);
+      uint8_t* krow_p = reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g);
+#pragma unroll
+      for (int c = part * (D / 4); c < (part + 1) * (D / 4); c += 16) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          uint32_t o[16];
+          tmem_ld16((which ? tdK : tdV) + lane_base + c, o);
+          tmem_wait_ld();
+          if (krow < p.sk) {
+            uint4* d4 = reinterpret_cast<uint4*>((which ? krow_p : vrow) + c * 2);
+#pragma unroll
+            for (int q4 = 0; q4 < 2; ++q4)
+              d4[q4] = make_uint4(pack_lp(__uint_as_float(o[q4 * 8]), __uint_as_float(o[q4 * 8 + 1]), p.lp_fmt),
+                                  pack_lp(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]), p.lp_fmt),
+                                  pack_lp(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]), p.lp_fmt),
+                                  pack_lp(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]), p.lp_fmt));
+          }
+        }
+      }
+    }
+  } else {
+    // no query can see this key tile: its gradients are zero
+    const int ct = threadIdx.x - 64;
+    if (ct >= 0 && ct < 128) {
+      const int krow = n0 + ct;
+      if (krow < p.sk) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        uint4* vrow = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.dv) + 2 * ((long)krow * p.dv_s + (long)bb * p.dv_b + (long)g * p.dv_g));
+        uint4* kr = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.dk) + 2 * ((long)krow * p.dk_s + (long)bb * p.dk_b + (long)g * p.dk_g));
+        for (int c = 0; c < D / 8; ++c) { vrow[c] = z; kr[c] = z; }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc(tmem, TCOLS); }
+}
+
 // ---------------------------------------------------------------------------- host side
 static int make_tmap5(CUtensorMap* m, const void* base, int D, int nj, int ng, int b, int s, long st_j, long st_g,
                       long st_b, long st_s, int box_rows) {
@@ -1491,9 +2190,10 @@ MLB_API int mlb_attn_fwd(int lp_fmt, const void* q, const void* k, const void* v
                          int sq, int sk, int b, int ng, int qpg, int D,
                          long q_s, long q_b, long q_g, long q_j, long k_s, long k_b, long k_g,
                          long v_s, long v_b, long v_g, long o_s, long o_b, long o_g, long o_j,
-                         float scale, int causal, int* status, cudaStream_t st) {
+                         float scale, int causal, int window, int* status, cudaStream_t st) {
   if (D != 64 && D != 128) return -5;
   if (sq <= 0 || sk <= 0 || (causal && sk < sq)) return -6;
+  if (window >= 0 && !causal) return -6;              // the sliding window is the causal one: keys [q - window, q]
   if ((o_s % 8) || (o_b % 8) || (o_g % 8) || (o_j % 8) || (reinterpret_cast<uintptr_t>(o) & 15)) return -3;
   CUtensorMap tmQ, tmK, tmV;
   int rc;
@@ -1508,21 +2208,24 @@ MLB_API int mlb_attn_fwd(int lp_fmt, const void* q, const void* k, const void* v
   p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
   p.o = o; p.o_s = o_s; p.o_b = o_b; p.o_g = o_g; p.o_j = o_j; p.lse = lse;
+  p.win = window >= 0 ? window : (1 << 30);
+  if (window >= 0 && !use_v2) return -7;              // only the two-tile kernel knows windows
   if (use_v2) {
     CUtensorMap tmK2, tmV2;
     if ((rc = make_tmap5(&tmK2, k, D, 1, ng, b, sk, D, k_g, k_b, k_s, 128))) return rc;
     if ((rc = make_tmap5(&tmV2, v, D, 1, ng, b, sk, D, v_g, v_b, v_s, 128))) return rc;
     const int grid2 = ((sq + 255) / 256) * ng * qpg * b;
     const int smem2 = 2 * D * 256 + 5 * D * 256 + 256;
-    if (D == 128) {
-      static bool set = false;
-      if (!set) { if ((rc = set_smem(attn_fwd2_kernel<128>, smem2))) return rc; set = true; }
-      attn_fwd2_kernel<128><<<grid2, kAttnFwd2Threads, smem2, st>>>(tmQ, tmK2, tmV2, p);
-    } else {
-      static bool set = false;
-      if (!set) { if ((rc = set_smem(attn_fwd2_kernel<64>, smem2))) return rc; set = true; }
-      attn_fwd2_kernel<64><<<grid2, kAttnFwd2Threads, smem2, st>>>(tmQ, tmK2, tmV2, p);
-    }
+    auto launch = [&](auto kern, bool& set) -> int {
+      if (!set) { if (int e = set_smem(kern, smem2)) return e; set = true; }
+      kern<<<grid2, kAttnFwd2Threads, smem2, st>>>(tmQ, tmK2, tmV2, p);
+      return 0;
+    };
+    static bool set[4] = {false, false, false, false};
+    const bool w = window >= 0;
+    if (D == 128) rc = w ? launch(attn_fwd2_win_kernel<128>, set[0]) : launch(attn_fwd2_kernel<128>, set[1]);
+    else rc = w ? launch(attn_fwd2_win_kernel<64>, set[2]) : launch(attn_fwd2_kernel<64>, set[3]);
+    if (rc) return rc;
     MLB_CHECK_LAUNCH();
     return 0;
   }
@@ -1548,7 +2251,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
                          long v_s, long v_b, long v_g, long o_s, long o_b, long o_g, long o_j,
                          long do_s, long do_b, long do_g, long do_j, long dq_s, long dq_b, long dq_g, long dq_j,
                          long dk_s, long dk_b, long dk_g, long dv_s, long dv_b, long dv_g,
-                         float scale, int causal, int* status, cudaStream_t st) {
+                         float scale, int causal, int window, int* status, cudaStream_t st) {
   if (D != 64 && D != 128) return -5;
   if (sq <= 0 || sk <= 0 || (causal && sk < sq)) return -6;
   const long chk[] = {dq_s, dq_b, dq_g, dq_j, dk_s, dk_b, dk_g, dv_s, dv_b, dv_g};
@@ -1564,6 +2267,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
   p.sq = sq; p.sk = sk; p.b = b; p.ng = ng; p.qpg = qpg; p.causal = causal; p.off = sk - sq;
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.lp_fmt = lp_fmt; p.status = status;
   p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.win = window >= 0 ? window : (1 << 30);
   p.q = q; p.q_s = q_s; p.q_b = q_b; p.q_g = q_g; p.q_j = q_j;
   p.d_o = d_o; p.do_s = do_s; p.do_b = do_b; p.do_g = do_g; p.do_j = do_j;
   p.dq = dq; p.dq_s = dq_s; p.dq_b = dq_b; p.dq_g = dq_g; p.dq_j = dq_j;
@@ -1572,6 +2276,7 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
   int rc;
   static int use_ts = -1;                  // MLB_ATTN_TS=0: the kernels with 64-wide steps and P / dS through shared memory
   if (use_ts < 0) { const char* e = getenv("MLB_ATTN_TS"); use_ts = (e && e[0] == '0') ? 0 : 1; }
+  if (window >= 0 && (!use_ts || !causal)) return -7;
   // 128-row boxes of all four operands serve both kernels of the default path
   CUtensorMap tmQ, tmdO, tmK128, tmV128;
   if ((rc = make_tmap5(&tmQ, q, D, qpg, ng, b, sq, q_j, q_g, q_b, q_s, 128))) return rc;
@@ -1587,15 +2292,16 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     const int grid = ((sq + 127) / 128) * ng * qpg * b;
     if (use_ts) {
       const int smem_ts = 7 * D * 256 + 256;                           // Q, dO, three K stages, two V stages
-      if (D == 128) {
-        static bool set = false;
-        if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<128>, smem_ts))) return rc; set = true; }
-        attn_bwd_dq_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
-      } else {
-        static bool set = false;
-        if (!set) { if ((rc = set_smem(attn_bwd_dq_ts_kernel<64>, smem_ts))) return rc; set = true; }
-        attn_bwd_dq_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
-      }
+      auto launch = [&](auto kern, bool& set) -> int {
+        if (!set) { if (int e = set_smem(kern, smem_ts)) return e; set = true; }
+        kern<<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
+        return 0;
+      };
+      static bool set[4] = {false, false, false, false};
+      const bool w = window >= 0;
+      if (D == 128) rc = w ? launch(attn_bwd_dq_ts_win_kernel<128>, set[0]) : launch(attn_bwd_dq_ts_kernel<128>, set[1]);
+      else rc = w ? launch(attn_bwd_dq_ts_win_kernel<64>, set[2]) : launch(attn_bwd_dq_ts_kernel<64>, set[3]);
+      if (rc) return rc;
       MLB_CHECK_LAUNCH();
     } else {
     const int smem = 2 * D * 256 + 8 * D * 128 + 16384 + 128;         // Q, dO, four K/V stages, dS
@@ -1620,15 +2326,16 @@ MLB_API int mlb_attn_bwd(int lp_fmt, const void* q, const void* k, const void* v
     const int grid = ((sk + 127) / 128) * ng * b;
     if (use_ts) {
       const int smem_ts = 6 * D * 256 + 2048 + 256;                    // K, V, two Q/dO stages, stats
-      if (D == 128) {
-        static bool set = false;
-        if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<128>, smem_ts))) return rc; set = true; }
-        attn_bwd_dkv_ts_kernel<128><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
-      } else {
-        static bool set = false;
-        if (!set) { if ((rc = set_smem(attn_bwd_dkv_ts_kernel<64>, smem_ts))) return rc; set = true; }
-        attn_bwd_dkv_ts_kernel<64><<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
-      }
+      auto launch = [&](auto kern, bool& set) -> int {
+        if (!set) { if (int e = set_smem(kern, smem_ts)) return e; set = true; }
+        kern<<<grid, kAttnDqThreads, smem_ts, st>>>(tmQ, tmK128, tmV128, tmdO, p);
+        return 0;
+      };
+      static bool set[4] = {false, false, false, false};
+      const bool w = window >= 0;
+      if (D == 128) rc = w ? launch(attn_bwd_dkv_ts_win_kernel<128>, set[0]) : launch(attn_bwd_dkv_ts_kernel<128>, set[1]);
+      else rc = w ? launch(attn_bwd_dkv_ts_win_kernel<64>, set[2]) : launch(attn_bwd_dkv_ts_kernel<64>, set[3]);
+      if (rc) return rc;
     } else {
       const int smem = 2 * D * 256 + 6 * D * 128 + 2 * 16384 + 1024 + 128;  // K, V, three Q/dO stages, P, dS, stats
       if (D == 128) {

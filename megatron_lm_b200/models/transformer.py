@@ -185,7 +185,7 @@ def _rope_copy(qkv5, cos, sin, interleaved):
     return out
 
 
-def masked_attention(q5, k, v, attention_mask, scale, causal=False):
+def masked_attention(q5, k, v, attention_mask, scale, causal=False, window=None):
     """Attention with an arbitrary mask (True = may not attend), e.g. padding masks of BERT / T5 batches.
     q5 [sq, b, ng, qpg, d], k/v [sk, b, ng, d], mask broadcastable to [b, 1, sq, sk].  The flash kernels
     cover the causal and full cases; arbitrary masks go through torch's scaled-dot-product attention."""
@@ -197,6 +197,8 @@ def masked_attention(q5, k, v, attention_mask, scale, causal=False):
     allow = ~attention_mask.bool()
     if causal:
         allow = allow & torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(sk - sq)
+        if window is not None:
+            allow = allow & torch.ones(sq, sk, dtype=torch.bool, device=q.device).triu(sk - sq - window)
     o = torch.nn.functional.scaled_dot_product_attention(q, kk, vv, attn_mask=allow, scale=scale)
     return o.permute(2, 0, 1, 3).reshape(sq, b, ng * qpg * d)
 
@@ -226,6 +228,13 @@ class SelfAttention(nn.Module):
             self.q_layernorm = self.k_layernorm = None
         scale = config.softmax_scale if config.softmax_scale is not None else 1.0 / math.sqrt(self.hn)
         self.softmax_scale = scale
+        # sliding window: window_size = (left, 0) on a causal layer - a query sees itself and `left` keys before it
+        self.window = None
+        if config.window_size is not None:
+            left, right = config.window_size
+            if not causal or right not in (0, -1) or left < 0:
+                raise NotImplementedError("window_size is implemented as the causal window (left, 0)")
+            self.window = int(left)
         self.recompute_core = config.recompute_granularity == "selective" and "core_attn" in config.recompute_modules
         self.cp_size = state.get_context_parallel_world_size() if state.model_parallel_is_initialized() else 1
         ct = config.cp_comm_type
@@ -234,7 +243,7 @@ class SelfAttention(nn.Module):
     def _core(self, qkv5, cos=None, sin=None):
         rope = None if cos is None else (cos, sin)
         return fused_qkv_attention(qkv5, causal=self.causal, scale=self.softmax_scale, rope=rope,
-                                   rotary_interleaved=self.config.rotary_interleaved)
+                                   rotary_interleaved=self.config.rotary_interleaved, window=self.window)
 
     def forward(self, hidden_states, rotary=None, inference_context=None, attention_mask=None):
         qkv, _ = self.linear_qkv(hidden_states)                       # [s, b, (np+2ng)/tp * hn]
@@ -245,6 +254,9 @@ class SelfAttention(nn.Module):
             k = self.k_layernorm(qkv5[:, :, :, self.qpg:self.qpg + 1].contiguous())
             qkv5 = torch.cat((q, k, qkv5[:, :, :, self.qpg + 1:]), dim=3)
         cos, sin = rotary if rotary is not None else (None, None)
+        if self.window is not None and (inference_context is not None or self.cp_size > 1):
+            raise NotImplementedError("sliding-window attention is not available with context parallelism or the "
+                                      "inference engines' key/value caches")
         if self.cp_size > 1 and inference_context is None:
             # context parallel: q/k/v leave the fused buffer (K/V travel between ranks)
             from ..parallel.context_parallel import context_parallel_attention
@@ -275,7 +287,7 @@ class SelfAttention(nn.Module):
                 qkv5 = ops.apply_rope_qkv_(qkv5.clone() if qkv5.is_cuda else qkv5, cos, sin,
                                            self.config.rotary_interleaved)
             ctx_out = masked_attention(qkv5[:, :, :, :self.qpg], qkv5[:, :, :, self.qpg], qkv5[:, :, :, self.qpg + 1],
-                                       attention_mask, self.softmax_scale, self.causal)
+                                       attention_mask, self.softmax_scale, self.causal, self.window)
         elif inference_context is not None:
             if cos is not None:
                 qkv5 = _rope_copy(qkv5, cos, sin, self.config.rotary_interleaved) if qkv5.is_cuda else \

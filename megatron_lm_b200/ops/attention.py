@@ -19,13 +19,13 @@ from . import _lib
 
 _lib.register_signatures({
     # fmt, q,k,v,o,lse, sq,sk,b,ng,qpg,hn, q strides(s,b,g,j) k(s,b,g) v(s,b,g) o(s,b,g,j), scale, causal, status, stream
-    "mlb_attn_fwd": "ippppp" "iiiiii" "llll" "lll" "lll" "llll" "fi" "pp",
+    "mlb_attn_fwd": "ippppp" "iiiiii" "llll" "lll" "lll" "llll" "fii" "pp",
     # fmt, q,k,v,o,do,lse,delta, dq,dk,dv, sizes, strides q,k,v,o,do(s,b,g,j), dq(s,b,g,j), dk, dv, scale, causal, status, stream
-    "mlb_attn_bwd": "ipppppppppp" "iiiiii" "llll" "lll" "lll" "llll" "llll" "llll" "lll" "lll" "fi" "pp",
+    "mlb_attn_bwd": "ipppppppppp" "iiiiii" "llll" "lll" "lll" "llll" "llll" "llll" "lll" "lll" "fii" "pp",
 })
 
 
-def _ref_attention(q, k, v, causal: bool, scale: float, q_offset: int = 0):
+def _ref_attention(q, k, v, causal: bool, scale: float, q_offset: int = 0, window: Optional[int] = None):
     # q [sq, b, ng, qpg, d]; k, v [sk, b, ng, d]
     sq, b, ng, qpg, d = q.shape
     sk = k.shape[0]
@@ -37,6 +37,8 @@ def _ref_attention(q, k, v, causal: bool, scale: float, q_offset: int = 0):
         i = torch.arange(sq, device=q.device).unsqueeze(1) + q_offset + (sk - sq if q_offset == 0 else 0)
         j = torch.arange(sk, device=q.device).unsqueeze(0)
         s = s.masked_fill(j > i, float("-inf"))
+        if window is not None:
+            s = s.masked_fill(j < i - window, float("-inf"))
     p = torch.softmax(s, dim=-1)
     o = torch.matmul(p, vf)                                    # b ng qpg sq d
     return o.permute(3, 0, 1, 2, 4).reshape(sq, b, ng * qpg, d).to(q.dtype)
@@ -44,7 +46,7 @@ def _ref_attention(q, k, v, causal: bool, scale: float, q_offset: int = 0):
 
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
+    def forward(ctx, q, k, v, causal, scale, window=-1):
         sq, b, ng, qpg, d = q.shape
         sk = k.shape[0]
         assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
@@ -55,16 +57,16 @@ class _FlashAttnFn(torch.autograd.Function):
         _lib.check(_lib.lib().mlb_attn_fwd(
             1 if q.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
             lse.data_ptr(), sq, sk, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2],
-            vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), st.data_ptr(),
+            vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), int(window), st.data_ptr(),
             _lib.stream()), "attn_fwd")
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.cfg = (causal, scale)
+        ctx.cfg = (causal, scale, window)
         return o.view(sq, b, ng * qpg, d)
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
-        causal, scale = ctx.cfg
+        causal, scale, window = ctx.cfg
         sq, b, ng, qpg, d = q.shape
         sk = k.shape[0]
         do = do.reshape(sq, b, ng, qpg, d)
@@ -82,9 +84,9 @@ class _FlashAttnFn(torch.autograd.Function):
             do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             sq, sk, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2],
             os_[0], os_[1], os_[2], os_[3], dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3],
-            dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), st.data_ptr(),
+            dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), int(window), st.data_ptr(),
             _lib.stream()), "attn_bwd")
-        return dq, dk, dv, None, None
+        return dq, dk, dv, None, None, None
 
 
 class _FusedQKVAttnFn(torch.autograd.Function):
@@ -92,7 +94,7 @@ class _FusedQKVAttnFn(torch.autograd.Function):
     one tensor of the same layout, ready to be the QKV GEMM's output gradient."""
 
     @staticmethod
-    def forward(ctx, qkv, causal, scale, cos, sin, interleaved):
+    def forward(ctx, qkv, causal, scale, cos, sin, interleaved, window=-1):
         s, b, ng, tot, d = qkv.shape
         qpg = tot - 2
         if cos is not None:
@@ -110,16 +112,16 @@ class _FusedQKVAttnFn(torch.autograd.Function):
         _lib.check(_lib.lib().mlb_attn_fwd(
             1 if qkv.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
             lse.data_ptr(), s, s, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2],
-            vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), st.data_ptr(),
+            vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), int(window), st.data_ptr(),
             _lib.stream()), "attn_fwd")
         ctx.save_for_backward(qkv, o, lse)
-        ctx.cfg = (causal, scale)
+        ctx.cfg = (causal, scale, window)
         return o.view(s, b, ng * qpg * d)
 
     @staticmethod
     def backward(ctx, do):
         qkv, o, lse = ctx.saved_tensors
-        causal, scale = ctx.cfg
+        causal, scale, window = ctx.cfg
         s, b, ng, tot, d = qkv.shape
         qpg = tot - 2
         q, k, v = qkv[:, :, :, :qpg], qkv[:, :, :, qpg], qkv[:, :, :, qpg + 1]
@@ -137,14 +139,14 @@ class _FusedQKVAttnFn(torch.autograd.Function):
             do.data_ptr(), lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             s, s, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2],
             os_[0], os_[1], os_[2], os_[3], dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3],
-            dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), st.data_ptr(),
+            dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2], float(scale), int(causal), int(window), st.data_ptr(),
             _lib.stream()), "attn_bwd")
         cos, sin, interleaved = ctx.rope
         if cos is not None:
             from .core import _rope_launch
             dqk = dqkv[:, :, :, :qpg + 1]
             _rope_launch(dqk, dqk, cos, sin, interleaved, -1.0)       # inverse rotation of dq, dk
-        return dqkv, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None
 
 
 # ----------------------------------------------------------------------------- raw forward / backward
@@ -171,7 +173,7 @@ def attention_fwd_raw(q, k, v, causal: bool, scale: float) -> Tuple[torch.Tensor
     _lib.check(_lib.lib().mlb_attn_fwd(
         1 if q.dtype == torch.bfloat16 else 0, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
         sq, sk, b, ng, qpg, d, qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2],
-        os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), st.data_ptr(), _lib.stream()), "attn_fwd")
+        os_[0], os_[1], os_[2], os_[3], float(scale), int(causal), -1, st.data_ptr(), _lib.stream()), "attn_fwd")
     return o, lse
 
 
@@ -212,25 +214,31 @@ def attention_bwd_raw(q, k, v, o, do, lse, causal: bool, scale: float):
         lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), sq, sk, b, ng, qpg, d,
         qs[0], qs[1], qs[2], qs[3], ks[0], ks[1], ks[2], vs[0], vs[1], vs[2], os_[0], os_[1], os_[2], os_[3],
         dos[0], dos[1], dos[2], dos[3], dqs[0], dqs[1], dqs[2], dqs[3], dks[0], dks[1], dks[2], dvs[0], dvs[1], dvs[2],
-        float(scale), int(causal), st.data_ptr(), _lib.stream()), "attn_bwd")
+        float(scale), int(causal), -1, st.data_ptr(), _lib.stream()), "attn_bwd")
     return dq, dk, dv
 
 
-def attention(q, k, v, causal: bool = True, scale: Optional[float] = None):
+def attention(q, k, v, causal: bool = True, scale: Optional[float] = None, window: Optional[int] = None):
     """q [sq, b, ng, qpg, d], k/v [sk, b, ng, d] -> [sq, b, ng*qpg, d].  With ``causal`` the last
-    query row attends to the last key (sq <= sk)."""
+    query row attends to the last key (sq <= sk); ``window`` (causal only) limits a query to itself and the
+    ``window`` keys before it (reference: the ``window_size=(left, 0)`` the attention back end receives,
+    megatron/core/extensions/transformer_engine.py:786-800)."""
     d = q.shape[-1]
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
+    if window is not None and not causal:
+        raise ValueError("the sliding window is the causal one")
     if not q.is_cuda:
-        return _ref_attention(q, k, v, causal, scale)
-    return _FlashAttnFn.apply(q, k, v, causal, scale)
+        return _ref_attention(q, k, v, causal, scale, window=window)
+    return _FlashAttnFn.apply(q, k, v, causal, scale, -1 if window is None else int(window))
 
 
 def fused_qkv_attention(qkv5, causal: bool = True, scale: Optional[float] = None, rope=None,
-                        rotary_interleaved: bool = False):
+                        rotary_interleaved: bool = False, window: Optional[int] = None):
     """Self-attention straight from the fused projection [s, b, ng, qpg + 2, hn] -> [s, b, np*hn].
     ``rope=(cos, sin)`` (fp32 [s, rot/2]) rotates q and k first; on CUDA this happens in place in
-    ``qkv5``, which must therefore not be read again by the caller."""
+    ``qkv5``, which must therefore not be read again by the caller.  ``window``: causal sliding window."""
+    if window is not None and not causal:
+        raise ValueError("the sliding window is the causal one")
     s, b, ng, tot, d = qkv5.shape
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
     cos, sin = rope if rope is not None else (None, None)
@@ -239,6 +247,6 @@ def fused_qkv_attention(qkv5, causal: bool = True, scale: Optional[float] = None
         if cos is not None:
             from .core import apply_rope_qkv_
             qkv5 = apply_rope_qkv_(qkv5, cos, sin, rotary_interleaved)
-        o = _ref_attention(qkv5[:, :, :, :qpg], qkv5[:, :, :, qpg], qkv5[:, :, :, qpg + 1], causal, scale)
+        o = _ref_attention(qkv5[:, :, :, :qpg], qkv5[:, :, :, qpg], qkv5[:, :, :, qpg + 1], causal, scale, window=window)
         return o.reshape(s, b, ng * qpg * d)
-    return _FusedQKVAttnFn.apply(qkv5, causal, scale, cos, sin, rotary_interleaved)
+    return _FusedQKVAttnFn.apply(qkv5, causal, scale, cos, sin, rotary_interleaved, -1 if window is None else int(window))

@@ -39,6 +39,9 @@ def _blocker():
 
 
 def _time(fn, iters, warmup):
+    """Median device time of ``fn`` over ``iters`` calls (the median, because a call whose launch the host delivers
+    late - an allocator that has to go to the driver, a collection - leaves the GPU idle inside its interval)."""
+    _blocker()                                  # its buffers are allocated outside the timed calls
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -49,7 +52,8 @@ def _time(fn, iters, warmup):
         fn()
         e1.record()
     torch.cuda.synchronize()
-    return sum(e0.elapsed_time(e1) for e0, e1 in ev) / iters
+    t = sorted(e0.elapsed_time(e1) for e0, e1 in ev)
+    return t[len(t) // 2]
 
 
 def _report(name, ms, flops=None, bytes_=None):

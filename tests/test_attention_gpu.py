@@ -92,6 +92,30 @@ def test_attention_full_more_queries_than_keys():
         assert _rel(a, r) < 3e-2
 
 
+@pytest.mark.parametrize("s,qpg,d,window", [(1100, 1, 128, 100), (1100, 2, 128, 128), (640, 1, 128, 300), (1024, 1, 64, 255),
+                                            (512, 1, 128, 0), (700, 1, 128, 5000)])
+def test_attention_sliding_window(s, qpg, d, window):
+    """Causal sliding window (a query sees itself and ``window`` keys before it), forward and backward."""
+    torch.manual_seed(6)
+    q = torch.randn(s, 1, 2, qpg, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(s, 1, 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(s, 1, 2, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = attention(q, k, v, causal=True, window=window)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = _ref_attention(qr, kr, vr, True, 1.0 / math.sqrt(d), window=window)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert _rel(out, ref) < 2e-2
+    do = torch.randn_like(ref)
+    out.backward(do.to(out.dtype))
+    ref.backward(do)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for a, r in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        # with window 0 every query sees one key and dq, dk are exactly zero in the reference: absolute bound then
+        assert (a.float() - r).norm().item() < 3e-2 * max(r.norm().item(), 1.0)
+
+
 def test_attention_large_scores_rescale():
     """Scores that grow along the keys force the running maximum up by more than the lazy-rescale threshold."""
     torch.manual_seed(4)

@@ -209,3 +209,25 @@ def test_named_and_callable_activations():
         f = act if callable(act) else A.BY_NAME[act]
         z = f(z[..., :32]) * z[..., 32:] if gated else f(z)
         assert torch.allclose(out, z @ w2.t(), atol=1e-5)
+
+
+def test_sliding_window_attention_layer_on_cpu():
+    """window_size=(left, 0): the layer's output for a token does not depend on tokens further back than the window."""
+    import torch
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.transformer import SelfAttention
+    torch.manual_seed(0)
+    cfg = TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, window_size=(3, 0),
+                            hidden_dropout=0.0, attention_dropout=0.0)
+    attn = SelfAttention(cfg, 1)
+    x = torch.randn(12, 1, 64)
+    y, _ = attn(x)
+    x2 = x.clone()
+    x2[:5] = torch.randn(5, 1, 64)              # tokens 0..4 are outside the window of tokens 8..11
+    y2, _ = attn(x2)
+    assert torch.allclose(y[8:], y2[8:], atol=1e-6)
+    assert not torch.allclose(y[5:8], y2[5:8], atol=1e-4)
+    full = SelfAttention(TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, hidden_dropout=0.0,
+                                           attention_dropout=0.0), 1)
+    full.load_state_dict(attn.state_dict())
+    assert not torch.allclose(full(x)[0][8:], y[8:], atol=1e-4)
