@@ -69,7 +69,13 @@ def hf_llama_to_core(hf: Dict[str, torch.Tensor], num_layers: int, num_heads: in
         if s + "mlp.gate_proj.weight" in hf:
             sd[d + "mlp.linear_fc1.weight"] = torch.cat((hf[s + "mlp.gate_proj.weight"], hf[s + "mlp.up_proj.weight"]), 0)
             sd[d + "mlp.linear_fc2.weight"] = hf[s + "mlp.down_proj.weight"]
-        else:                                                       # Mixtral: block_sparse_moe
+        elif s + "mlp.experts.gate_up_proj" in hf:                  # Mixtral as newer library versions hold it in memory:
+            sd[d + "mlp.router.weight"] = hf[s + "mlp.gate.weight"]  # experts fused, [E, 2f, h] (gate ; up) and [E, h, f]
+            gu, dn = hf[s + "mlp.experts.gate_up_proj"], hf[s + "mlp.experts.down_proj"]
+            for e in range(gu.shape[0]):
+                sd[d + f"mlp.experts.local_experts.{e}.linear_fc1.weight"] = gu[e]
+                sd[d + f"mlp.experts.local_experts.{e}.linear_fc2.weight"] = dn[e]
+        else:                                                       # Mixtral checkpoint files: block_sparse_moe
             sd[d + "mlp.router.weight"] = hf[s + "block_sparse_moe.gate.weight"]
             e = 0
             while s + f"block_sparse_moe.experts.{e}.w1.weight" in hf:
@@ -98,6 +104,113 @@ def core_to_hf_llama(sd: Dict[str, torch.Tensor], num_layers: int, num_heads: in
         hf[d + "mlp.gate_proj.weight"], hf[d + "mlp.up_proj.weight"] = fc1.chunk(2, dim=0)
         hf[d + "mlp.down_proj.weight"] = sd[s + "mlp.linear_fc2.weight"]
     return hf
+
+
+def core_to_hf_mixtral(sd: Dict[str, torch.Tensor], num_layers: int, num_heads: int, num_query_groups: int,
+                       head_dim: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """Core MoE checkpoint (sequential experts: ``mlp.experts.local_experts.<e>.linear_fc1/2``, or grouped experts:
+    ``mlp.experts.weight1/weight2`` of shape [E, ...]) -> Hugging Face Mixtral names (``block_sparse_moe.gate``,
+    ``experts.<e>.w1 / w3 / w2``).  Reference: tools/checkpoint/loader_mixtral_hf.py:150-230 (the opposite way)."""
+    h = sd["embedding.word_embeddings.weight"].shape[1]
+    hn = head_dim or h // num_heads
+    hf = {"model.embed_tokens.weight": sd["embedding.word_embeddings.weight"],
+          "model.norm.weight": sd["decoder.final_layernorm.weight"],
+          "lm_head.weight": sd.get("output_layer.weight", sd["embedding.word_embeddings.weight"])}
+    for i in range(num_layers):
+        s_, d = f"decoder.layers.{i}.", f"model.layers.{i}."
+        q, k, v = _qkv_from_core(sd[s_ + "self_attention.linear_qkv.weight"], num_heads, num_query_groups, hn)
+        hf[d + "self_attn.q_proj.weight"], hf[d + "self_attn.k_proj.weight"], hf[d + "self_attn.v_proj.weight"] = q, k, v
+        hf[d + "self_attn.o_proj.weight"] = sd[s_ + "self_attention.linear_proj.weight"]
+        hf[d + "input_layernorm.weight"] = sd[s_ + "input_layernorm.weight"]
+        hf[d + "post_attention_layernorm.weight"] = sd[s_ + "pre_mlp_layernorm.weight"]
+        hf[d + "block_sparse_moe.gate.weight"] = sd[s_ + "mlp.router.weight"]
+        if s_ + "mlp.experts.weight1" in sd:                        # grouped experts: [E, h, 2f] and [E, f, h]
+            w1, w2 = sd[s_ + "mlp.experts.weight1"], sd[s_ + "mlp.experts.weight2"]
+            for e in range(w1.shape[0]):
+                gate, up = w1[e].t().chunk(2, dim=0)
+                hf[d + f"block_sparse_moe.experts.{e}.w1.weight"] = gate.contiguous()
+                hf[d + f"block_sparse_moe.experts.{e}.w3.weight"] = up.contiguous()
+                hf[d + f"block_sparse_moe.experts.{e}.w2.weight"] = w2[e].t().contiguous()
+        else:
+            e = 0
+            while s_ + f"mlp.experts.local_experts.{e}.linear_fc1.weight" in sd:
+                fc1 = sd[s_ + f"mlp.experts.local_experts.{e}.linear_fc1.weight"]
+                hf[d + f"block_sparse_moe.experts.{e}.w1.weight"], hf[d + f"block_sparse_moe.experts.{e}.w3.weight"] = \
+                    fc1.chunk(2, dim=0)
+                hf[d + f"block_sparse_moe.experts.{e}.w2.weight"] = sd[s_ + f"mlp.experts.local_experts.{e}.linear_fc2.weight"]
+                e += 1
+    return hf
+
+
+# ----------------------------------------------------------------------------- Mamba / hybrid: tensor-parallel size
+# A Mamba mixer's input projection is a concatenation of five segments per rank, [z | x | B | C | dt], and its
+# convolution of three, [x | B | C]: changing the tensor-parallel size has to re-cut every segment, not the whole
+# matrix (reference: tools/checkpoint/hybrid_conversion.py:60-190).  Heads, groups and inner channels are split
+# evenly; the state size is not split.
+def _mamba_dims(in_proj_rows_total: int, d_model: int, nheads: int, ngroups: int, d_state: int):
+    d_inner = (in_proj_rows_total - 2 * ngroups * d_state - nheads) // 2
+    if 2 * d_inner + 2 * ngroups * d_state + nheads != in_proj_rows_total or d_inner % nheads:
+        raise ValueError("in_proj size does not match the given heads / groups / state size")
+    return d_inner
+
+
+def mamba_merge_tp(shards: List[Dict[str, torch.Tensor]], nheads: int, ngroups: int, d_state: int,
+                   gated_mlp: bool = True) -> Dict[str, torch.Tensor]:
+    """Per-rank state dicts of a Mamba / hybrid model -> one unpartitioned state dict."""
+    tp = len(shards)
+    out: Dict[str, torch.Tensor] = {}
+    for name in shards[0]:
+        parts = [sd[name] for sd in shards]
+        if name.endswith("mixer.in_proj.weight"):
+            total = sum(p.shape[0] for p in parts)
+            d_inner = _mamba_dims(total, parts[0].shape[1], nheads, ngroups, d_state)
+            di, gn, hl = d_inner // tp, ngroups * d_state // tp, nheads // tp
+            segs = [torch.split(p, [di, di, gn, gn, hl], dim=0) for p in parts]
+            out[name] = torch.cat([torch.cat([sg[j] for sg in segs], dim=0) for j in range(5)], dim=0)
+        elif name.endswith(("mixer.conv_weight", "mixer.conv_bias")):
+            total = sum(p.shape[0] for p in parts)
+            d_inner = total - 2 * ngroups * d_state
+            di, gn = d_inner // tp, ngroups * d_state // tp
+            segs = [torch.split(p, [di, gn, gn], dim=0) for p in parts]
+            out[name] = torch.cat([torch.cat([sg[j] for sg in segs], dim=0) for j in range(3)], dim=0)
+        elif name.endswith(("mixer.dt_bias", "mixer.A_log", "mixer.D", "mixer.norm_weight")):
+            out[name] = torch.cat(parts, dim=0)
+        elif name.endswith("mixer.out_proj.weight"):
+            out[name] = torch.cat(parts, dim=1)
+    rest = [{k: v for k, v in sd.items() if k not in out} for sd in shards]
+    out.update(merge_tp(rest, gated_mlp))                 # attention / MLP layers of a hybrid model, embeddings, norms
+    return out
+
+
+def mamba_split_for_tp(sd: Dict[str, torch.Tensor], tp: int, nheads: int, ngroups: int, d_state: int,
+                       gated_mlp: bool = True) -> List[Dict[str, torch.Tensor]]:
+    """Unpartitioned Mamba / hybrid state dict -> ``tp`` per-rank state dicts."""
+    if nheads % tp or ngroups % tp:
+        raise ValueError("heads and groups must divide by the tensor-parallel size")
+    out: List[Dict[str, torch.Tensor]] = [dict() for _ in range(tp)]
+    for name, w in sd.items():
+        if name.endswith("mixer.in_proj.weight"):
+            d_inner = _mamba_dims(w.shape[0], w.shape[1], nheads, ngroups, d_state)
+            segs = torch.split(w, [d_inner, d_inner, ngroups * d_state, ngroups * d_state, nheads], dim=0)
+            cut = [sg.chunk(tp, dim=0) for sg in segs]
+            for r in range(tp):
+                out[r][name] = torch.cat([c[r] for c in cut], dim=0).contiguous()
+        elif name.endswith(("mixer.conv_weight", "mixer.conv_bias")):
+            d_inner = w.shape[0] - 2 * ngroups * d_state
+            segs = torch.split(w, [d_inner, ngroups * d_state, ngroups * d_state], dim=0)
+            cut = [sg.chunk(tp, dim=0) for sg in segs]
+            for r in range(tp):
+                out[r][name] = torch.cat([c[r] for c in cut], dim=0).contiguous()
+        elif name.endswith(("mixer.dt_bias", "mixer.A_log", "mixer.D", "mixer.norm_weight")):
+            for r, c in enumerate(w.chunk(tp, dim=0)):
+                out[r][name] = c.contiguous()
+        elif name.endswith("mixer.out_proj.weight"):
+            for r, c in enumerate(w.chunk(tp, dim=1)):
+                out[r][name] = c.contiguous()
+    rest = {k: v for k, v in sd.items() if k not in out[0]}
+    for r, part in enumerate(split_for_tp(rest, tp, gated_mlp)):
+        out[r].update(part)
+    return out
 
 
 # ----------------------------------------------------------------------------- legacy Megatron names -> core
@@ -288,7 +401,14 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--model-type", default="GPT")
     ap.add_argument("--loader", required=True, choices=["llama_hf", "mistral_hf", "mixtral_hf", "core", "legacy"])
-    ap.add_argument("--saver", required=True, choices=["core", "legacy", "llama_hf"])
+    ap.add_argument("--saver", required=True, choices=["core", "legacy", "llama_hf", "mixtral_hf"])
+    ap.add_argument("--num-attention-heads", type=int, default=None, help="core -> HF: heads (not stored in the tensors)")
+    ap.add_argument("--num-query-groups", type=int, default=None)
+    ap.add_argument("--mamba-heads", type=int, default=0,
+                    help="Mamba / hybrid checkpoints: heads, groups and state size of the mixers; the tensor-parallel split "
+                         "then re-cuts every segment of in_proj and conv (z | x | B | C | dt)")
+    ap.add_argument("--mamba-groups", type=int, default=8)
+    ap.add_argument("--mamba-state-dim", type=int, default=128)
     ap.add_argument("--load-dir", required=True)
     ap.add_argument("--save-dir", required=True)
     ap.add_argument("--target-tensor-parallel-size", type=int, default=1)
@@ -310,9 +430,13 @@ def main(argv=None):
         if a.loader == "legacy":
             sd = legacy_to_core(sd)
         meta = {"num_layers": 1 + max(int(m.group(1)) for m in (re.match(r"^decoder\.layers\.(\d+)\.", k) for k in sd) if m)}
-    if a.saver == "llama_hf":
-        hf = core_to_hf_llama(sd, meta["num_layers"], meta["num_attention_heads"], meta["num_query_groups"],
-                              meta.get("kv_channels"))
+    if a.num_attention_heads:
+        meta["num_attention_heads"] = a.num_attention_heads
+        meta["num_query_groups"] = a.num_query_groups or a.num_attention_heads
+    if a.saver in ("llama_hf", "mixtral_hf"):
+        to_hf = core_to_hf_mixtral if a.saver == "mixtral_hf" else core_to_hf_llama
+        hf = to_hf(sd, meta["num_layers"], meta["num_attention_heads"], meta["num_query_groups"],
+                   meta.get("kv_channels"))
         os.makedirs(a.save_dir, exist_ok=True)
         torch.save(hf, os.path.join(a.save_dir, "pytorch_model.bin"))
         return
@@ -321,7 +445,12 @@ def main(argv=None):
         save_core([[sd]], a.save_dir, 0, meta)
         return
     stages = split_for_pp(sd, a.target_pipeline_parallel_size, meta["num_layers"])
-    save_core([split_for_tp(st, a.target_tensor_parallel_size) for st in stages], a.save_dir, 0, meta)
+    if a.mamba_heads:
+        cut = lambda st: mamba_split_for_tp(st, a.target_tensor_parallel_size, a.mamba_heads, a.mamba_groups,   # noqa: E731
+                                            a.mamba_state_dim)
+    else:
+        cut = lambda st: split_for_tp(st, a.target_tensor_parallel_size)                                        # noqa: E731
+    save_core([cut(st) for st in stages], a.save_dir, 0, meta)
 
 
 if __name__ == "__main__":

@@ -46,3 +46,102 @@ def test_hf_llama_logits_match(tmp_path):
     legacy = convert.core_to_legacy(sd)
     assert "language_model.encoder.layers.1.self_attention.query_key_value.weight" in legacy
     assert set(convert.legacy_to_core(legacy)) == set(sd)
+
+
+def test_mamba_tensor_parallel_repartition_round_trip_and_layout():
+    """A Mamba mixer's in_proj / conv segments are re-cut per segment: splitting an unpartitioned state dict to 2 ranks
+    gives each rank [z_r | x_r | B_r | C_r | dt_r], and merging returns the original."""
+    import torch
+    from megatron_lm_b200.checkpoint.convert import mamba_merge_tp, mamba_split_for_tp
+    torch.manual_seed(0)
+    d_model, nheads, headdim, ngroups, d_state, d_conv = 32, 8, 8, 4, 16, 4
+    d_inner = nheads * headdim
+    rows = 2 * d_inner + 2 * ngroups * d_state + nheads
+    sd = {"decoder.layers.0.mixer.in_proj.weight": torch.randn(rows, d_model),
+          "decoder.layers.0.mixer.conv_weight": torch.randn(d_inner + 2 * ngroups * d_state, d_conv),
+          "decoder.layers.0.mixer.conv_bias": torch.randn(d_inner + 2 * ngroups * d_state),
+          "decoder.layers.0.mixer.dt_bias": torch.randn(nheads), "decoder.layers.0.mixer.A_log": torch.randn(nheads),
+          "decoder.layers.0.mixer.D": torch.randn(nheads), "decoder.layers.0.mixer.norm_weight": torch.randn(d_inner),
+          "decoder.layers.0.mixer.out_proj.weight": torch.randn(d_model, d_inner),
+          "decoder.layers.0.norm.weight": torch.randn(d_model),
+          "decoder.layers.1.mlp.linear_fc1.weight": torch.randn(2 * 48, d_model),
+          "decoder.layers.1.mlp.linear_fc2.weight": torch.randn(d_model, 48),
+          "embedding.word_embeddings.weight": torch.randn(64, d_model)}
+    parts = mamba_split_for_tp(sd, 2, nheads, ngroups, d_state)
+    w = sd["decoder.layers.0.mixer.in_proj.weight"]
+    z, x, B, C, dt = torch.split(w, [d_inner, d_inner, ngroups * d_state, ngroups * d_state, nheads], dim=0)
+    for r in range(2):
+        want = torch.cat([t.chunk(2, 0)[r] for t in (z, x, B, C, dt)], 0)
+        assert torch.equal(parts[r]["decoder.layers.0.mixer.in_proj.weight"], want)
+        assert parts[r]["decoder.layers.0.mixer.conv_weight"].shape[0] == (d_inner + 2 * ngroups * d_state) // 2
+        assert parts[r]["decoder.layers.0.mixer.out_proj.weight"].shape == (d_model, d_inner // 2)
+        assert torch.equal(parts[r]["decoder.layers.0.norm.weight"], sd["decoder.layers.0.norm.weight"])
+        assert parts[r]["decoder.layers.1.mlp.linear_fc1.weight"].shape[0] == 48
+    back = mamba_merge_tp(parts, nheads, ngroups, d_state)
+    assert back.keys() == sd.keys()
+    for k in sd:
+        assert torch.equal(back[k], sd[k]), k
+    four = mamba_split_for_tp(back, 4, nheads, ngroups, d_state)
+    assert torch.equal(mamba_merge_tp(four, nheads, ngroups, d_state)["decoder.layers.0.mixer.in_proj.weight"], w)
+
+
+def test_mamba_repartitioned_weights_run_a_mixer():
+    """The split layout is the one the mixer computes with: a TP1 mixer and its re-cut weights give the same in_proj
+    segments a TP2 rank would slice out."""
+    import torch
+    from megatron_lm_b200.checkpoint.convert import mamba_split_for_tp
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.mamba import MambaMixer
+    torch.manual_seed(1)
+    cfg = TransformerConfig(num_layers=1, hidden_size=32, num_attention_heads=4)
+    m = MambaMixer(cfg, 1, d_state=16, headdim=8, ngroups=4)
+    sd = {"decoder.layers.0.mixer." + k: v.detach() for k, v in m.state_dict().items()}
+    parts = mamba_split_for_tp(sd, 2, m.nheads, m.ngroups, m.d_state)
+    x = torch.randn(5, 1, 32)
+    full = torch.nn.functional.linear(x, sd["decoder.layers.0.mixer.in_proj.weight"])
+    z, xs, B, C, dt = torch.split(full, [m.d_inner, m.d_inner, m.ngroups * m.d_state, m.ngroups * m.d_state, m.nheads], -1)
+    for r in range(2):
+        loc = torch.nn.functional.linear(x, parts[r]["decoder.layers.0.mixer.in_proj.weight"])
+        want = torch.cat([t.chunk(2, -1)[r] for t in (z, xs, B, C, dt)], -1)
+        assert torch.allclose(loc, want, atol=1e-6)
+
+
+def test_hf_mixtral_round_trip_and_logits(tmp_path):
+    """HF Mixtral -> core -> HF is the identity, and the core weights reproduce the HF model's logits."""
+    import pytest
+    import torch
+    transformers = pytest.importorskip("transformers")
+    from megatron_lm_b200.checkpoint.convert import core_to_hf_mixtral, hf_llama_to_core
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    torch.manual_seed(0)
+    hcfg = transformers.MixtralConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=2, num_local_experts=4,
+                                      num_experts_per_tok=2, max_position_embeddings=64, rope_theta=10000.0,
+                                      rms_norm_eps=1e-5, tie_word_embeddings=False, router_jitter_noise=0.0)
+    hf_model = transformers.MixtralForCausalLM(hcfg).eval()
+    hf_sd = {k: v.detach().clone() for k, v in hf_model.state_dict().items()}
+    core = hf_llama_to_core(hf_sd, 2, 4, 2)
+    back = core_to_hf_mixtral(core, 2, 4, 2)            # checkpoint-file names: block_sparse_moe.experts.<e>.w1 / w3 / w2
+    again = hf_llama_to_core(back, 2, 4, 2)
+    assert again.keys() == core.keys()
+    for k, v in core.items():
+        assert torch.equal(v, again[k]), k
+    if "model.layers.0.mlp.experts.gate_up_proj" in hf_sd:
+        gu = hf_sd["model.layers.0.mlp.experts.gate_up_proj"]
+        assert torch.equal(back["model.layers.0.block_sparse_moe.experts.1.w1.weight"], gu[1][:96])
+        assert torch.equal(back["model.layers.0.block_sparse_moe.experts.1.w3.weight"], gu[1][96:])
+    cfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=96,
+                            moe_ffn_hidden_size=96, num_moe_experts=4, moe_router_topk=2, normalization="RMSNorm",
+                            layernorm_epsilon=1e-5, gated_linear_unit=True, activation_func="silu", add_bias_linear=False,
+                            hidden_dropout=0.0, attention_dropout=0.0, moe_aux_loss_coeff=0.0)
+    model = GPTModel(cfg, vocab_size=128, max_sequence_length=64, position_embedding_type="rope",
+                     share_embeddings_and_output_weights=False).eval()
+    missing, unexpected = model.load_state_dict(core, strict=False)
+    assert not unexpected, unexpected
+    assert all("_extra_state" in m or "rotary" in m for m in missing), missing
+    tokens = torch.randint(0, 128, (2, 16))
+    with torch.no_grad():
+        ours = model(tokens).transpose(0, 1) if model(tokens).shape[0] == 16 else model(tokens)
+        ref = hf_model(tokens).logits
+    assert torch.allclose(ours.float(), ref.float(), atol=2e-4, rtol=1e-3), (ours - ref).abs().max()
