@@ -132,3 +132,49 @@ class BertModel(nn.Module):
         loss = ops.cross_entropy(logits, tgt, vocab_start=self.tp_rank * logits.shape[-1], vocab_total=self.vocab_size,
                                  group=group)
         return loss.transpose(0, 1).contiguous(), binary_logits
+
+
+class _BertTower(nn.Module):
+    """Embedding + bidirectional encoder + pooler: what one side of the biencoder needs of a BERT model."""
+
+    def __init__(self, config: TransformerConfig, vocab_size: int, max_sequence_length: int):
+        super().__init__()
+        self.embedding = LanguageModelEmbedding(config, vocab_size, max_sequence_length, "learned_absolute", 2)
+        self.encoder = TransformerBlock(config, True, True, None, causal=False)
+        self.pooler = Pooler(config)
+
+    def forward(self, input_ids, attention_mask, tokentype_ids=None):
+        pos = torch.arange(input_ids.shape[1], device=input_ids.device).unsqueeze(0).expand_as(input_ids)
+        h = self.encoder(self.embedding(input_ids, pos, tokentype_ids),
+                         attention_mask=bert_extended_attention_mask(attention_mask))
+        return self.pooler(h, 0)                                                 # [b, h]
+
+
+class BiEncoderModel(nn.Module):
+    """Two BERT towers (query, context) whose pooled [CLS] vectors are compared by inner product - the retriever
+    trained by the inverse cloze task (reference: megatron/legacy/model/biencoder_model.py:57).  With
+    ``shared_query_context_model`` both sides use one tower; ``projection_dim`` > 0 adds a linear projection."""
+
+    def __init__(self, config, vocab_size: int, max_sequence_length: int, projection_dim: int = 0,
+                 shared_query_context_model: bool = False):
+        super().__init__()
+        self.config = config
+        self.query_model = _BertTower(config, vocab_size, max_sequence_length)
+        self.context_model = self.query_model if shared_query_context_model else \
+            _BertTower(config, vocab_size, max_sequence_length)
+        self.projection = None
+        if projection_dim > 0:
+            self.projection = nn.Linear(config.hidden_size, projection_dim, device=_device(config),
+                                        dtype=config.params_dtype)
+
+    def set_input_tensor(self, t):
+        pass
+
+    def _embed(self, model, tokens, pad_mask, types):
+        pooled = model(tokens, pad_mask, types)
+        return pooled if self.projection is None else self.projection(pooled)
+
+    def forward(self, query_tokens, query_pad_mask, query_types, context_tokens, context_pad_mask, context_types):
+        q = self._embed(self.query_model, query_tokens, query_pad_mask, query_types)
+        c = self._embed(self.context_model, context_tokens, context_pad_mask, context_types)
+        return q, c

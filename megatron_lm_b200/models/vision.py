@@ -143,3 +143,24 @@ class MultimodalProjector(nn.Module):
         x, _ = self.linear_fc1(h)
         x = F.gelu(x)
         return self.linear_fc2(x)[0]
+
+
+class VitClassificationModel(nn.Module):
+    """ViT backbone + linear head on the class token: image [b, c, h, w] -> logits [b, num_classes]
+    (reference: megatron/legacy/model/vision/classification.py:15, the model of pretrain_vision_classify.py)."""
+
+    def __init__(self, config: TransformerConfig, num_classes: int, img_h: int = 224, img_w: int = 224,
+                 patch_dim: int = 16, pre_process: bool = True, post_process: bool = True):
+        super().__init__()
+        self.config = config
+        self.backbone = CLIPViTModel(config, patch_dim=patch_dim, img_h=img_h, img_w=img_w, add_class_token=True)
+        self.head = nn.Linear(config.hidden_size, num_classes, device=_device(config), dtype=config.params_dtype)
+        nn.init.zeros_(self.head.weight)
+        nn.init.zeros_(self.head.bias)
+
+    def set_input_tensor(self, t):
+        self.backbone.set_input_tensor(t)
+
+    def forward(self, images: torch.Tensor) -> torch.Tensor:
+        h = self.backbone(images)                           # [b, 1 + patches, hidden]
+        return self.head(h[:, 0])

@@ -280,33 +280,30 @@ UNUSED_FLAGS = {
     "retro_cyclic_train_iters": (_R, "cyclic Retro training is not built"),
     "retro_attention_gate": (_R, "the Retro attention gate is fixed at 1"),
     "decoder_num_layers": (_R, "encoder-decoder layer split flags are not wired; use --num-layers"),
-    "retriever_seq_length": (_W, "biencoder programs are not built"), "sample_rate": (_W, "biencoder programs are not built"),
-    "ict_head_size": (_R, "pretrain_ict is not built"), "biencoder_projection_dim": (_R, "pretrain_ict is not built"),
-    "biencoder_shared_query_context_model": (_R, "pretrain_ict is not built"), "ict_load": (_R, "pretrain_ict is not built"),
-    "bert_load": (_R, "pretrain_ict is not built"), "titles_data_path": (_R, "pretrain_ict is not built"),
-    "query_in_block_prob": (_W, "pretrain_ict is not built"), "use_one_sent_docs": (_W, "pretrain_ict is not built"),
-    "evidence_data_path": (_R, "pretrain_ict is not built"), "retriever_report_topk_accuracies": (_W, "pretrain_ict is not built"),
-    "retriever_score_scaling": (_W, "pretrain_ict is not built"), "block_data_path": (_R, "pretrain_ict is not built"),
+    "sample_rate": (_W, "the retriever evaluation tasks are not built"),
+    "ict_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),
+    "bert_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),
+    "evidence_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
+    "block_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
     "embedding_path": (_R, "pretrain_ict is not built"), "indexer_batch_size": (_W, "pretrain_ict is not built"),
     "indexer_log_interval": (_W, "pretrain_ict is not built"),
-    "num_classes": (_W, "vision pre-training programs are not built"), "num_channels": (_W, "vision pre-training programs are not built"),
-    "classes_fraction": (_W, "vision pre-training programs are not built"),
-    "data_per_class_fraction": (_W, "vision pre-training programs are not built"),
-    "data_sharding": (_W, "vision pre-training programs are not built"), "head_lr_mult": (_W, "vision pre-training programs are not built"),
-    "vision_pretraining": (_R, "vision pre-training programs are not built"),
-    "vision_pretraining_type": (_W, "vision pre-training programs are not built"),
-    "vision_backbone_type": (_W, "vision pre-training programs are not built"),
-    "swin_backbone_type": (_W, "vision pre-training programs are not built"), "mask_type": (_W, "vision pre-training programs are not built"),
-    "mask_factor": (_W, "vision pre-training programs are not built"), "iter_per_epoch": (_W, "vision pre-training programs are not built"),
-    "dino_local_img_size": (_W, "vision pre-training programs are not built"),
-    "dino_local_crops_number": (_W, "vision pre-training programs are not built"),
-    "dino_head_hidden_size": (_W, "vision pre-training programs are not built"),
-    "dino_bottleneck_size": (_W, "vision pre-training programs are not built"),
-    "dino_freeze_last_layer": (_W, "vision pre-training programs are not built"),
-    "dino_norm_last_layer": (_W, "vision pre-training programs are not built"),
-    "dino_warmup_teacher_temp": (_W, "vision pre-training programs are not built"),
-    "dino_teacher_temp": (_W, "vision pre-training programs are not built"),
-    "dino_warmup_teacher_temp_epochs": (_W, "vision pre-training programs are not built"),
+    "classes_fraction": (_W, "only the classification program of the vision pre-training programs is built"),
+    "data_per_class_fraction": (_W, "only the classification program of the vision pre-training programs is built"),
+    "data_sharding": (_W, "only the classification program of the vision pre-training programs is built"), "head_lr_mult": (_W, "only the classification program of the vision pre-training programs is built"),
+    "vision_pretraining": (_W, "pretrain_vision_classify.py is the vision program; the flag itself selects nothing"),
+    "vision_pretraining_type": (_W, "only the classification program of the vision pre-training programs is built"),
+    "vision_backbone_type": (_W, "only the classification program of the vision pre-training programs is built"),
+    "swin_backbone_type": (_W, "only the classification program of the vision pre-training programs is built"), "mask_type": (_W, "only the classification program of the vision pre-training programs is built"),
+    "mask_factor": (_W, "only the classification program of the vision pre-training programs is built"), "iter_per_epoch": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_local_img_size": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_local_crops_number": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_head_hidden_size": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_bottleneck_size": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_freeze_last_layer": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_norm_last_layer": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_warmup_teacher_temp": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_teacher_temp": (_W, "only the classification program of the vision pre-training programs is built"),
+    "dino_warmup_teacher_temp_epochs": (_W, "only the classification program of the vision pre-training programs is built"),
     # resilience / logging services that run with fixed settings here
     "disable_straggler_on_startup": (_W, "the straggler detector has no remote toggle"),
     "straggler_ctrlr_port": (_W, "the straggler detector has no remote toggle"),

@@ -22,9 +22,10 @@ def _run(extra):
     return r.stdout
 
 
-def _iters(out):
+def _iters(out, loss_key="lm loss"):
     rows = {}
-    for m in re.finditer(r"iteration\s+(\d+)/\s*(\d+) .*?learning rate: ([0-9.E+-]+) .*?lm loss: ([0-9.E+-]+)", out):
+    for m in re.finditer(r"iteration\s+(\d+)/\s*(\d+) .*?learning rate: ([0-9.E+-]+) .*?" + loss_key +
+                         r": ([0-9.E+-]+)", out):
         rows[int(m.group(1))] = (float(m.group(3)), float(m.group(4)))
     return rows
 
@@ -85,7 +86,7 @@ def _sentence_corpus(tmp_path):
     return prefix, str(vocab)
 
 
-def _run_script(script, extra):
+def _run_script(script, extra, loss_key="lm loss"):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29618")
     common = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
               "--max-position-embeddings", "64", "--micro-batch-size", "2", "--global-batch-size", "4", "--train-iters",
@@ -95,7 +96,7 @@ def _run_script(script, extra):
                        timeout=300, cwd=ROOT, env=env)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-2500:]
-    rows = _iters(out)
+    rows = _iters(out, loss_key)
     assert sorted(rows) == [1, 2, 3] and all(0.5 < v[1] < 10 for v in rows.values()), rows
     assert "validation loss at iteration 2" in out and "test loss" in out
     return out
@@ -114,6 +115,42 @@ def test_mamba_and_vlm_programs_on_mock_data():
     mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64"]
     _run_script("pretrain_mamba.py", mock + ["--mamba-head-dim", "16", "--mamba-num-groups", "2", "--mamba-state-dim", "16"])
     _run_script("pretrain_vlm.py", mock + ["--img-h", "28", "--img-w", "28", "--patch-dim", "14"])
+
+
+def test_ict_and_vision_classification_programs(tmp_path):
+    """The retriever (inverse cloze task, in-batch softmax over pooled BERT embeddings) and the ViT classifier."""
+    prefix, vocab = _sentence_corpus(tmp_path)
+    out = _run_script("pretrain_ict.py", ["--data-path", prefix, "--split", "90,5,5", "--tokenizer-type",
+                                          "BertWordPieceLowerCase", "--vocab-file", vocab, "--retriever-seq-length", "32",
+                                          "--retriever-report-topk-accuracies", "1", "2", "--biencoder-projection-dim", "16"],
+                      loss_key="retrieval loss")
+    assert "top1_acc" in out
+    out = _run_script("pretrain_vision_classify.py", ["--mock-data", "--img-h", "32", "--img-w", "32", "--patch-dim", "8",
+                                                      "--num-classes", "4"], loss_key="loss")
+    assert "accuracy" in out
+
+
+def test_ict_blocks_and_samples(tmp_path):
+    import numpy as np
+    from megatron_lm_b200.data.ict_dataset import ICTDataset, build_blocks_mapping
+    from megatron_lm_b200.data.indexed_dataset import IndexedDataset
+    prefix, _ = _sentence_corpus(tmp_path)
+    ds = IndexedDataset(prefix)
+    doc_idx, sizes = np.asarray(ds.document_indices), np.asarray(ds.sequence_lengths)
+    m = build_blocks_mapping(doc_idx, sizes, None, 32)
+    assert len(m) >= 200 and (m[:, 1] - m[:, 0] >= 2).all()
+    for start, end, doc, _ in m[:50]:
+        assert doc_idx[doc] <= start < end <= doc_idx[doc + 1]
+        assert sizes[start:end].sum() <= 32 - 3 or end - start == 2
+    ict = ICTDataset(ds, None, 40, 32, cls_id=2, sep_id=3, pad_id=0, query_in_block_prob=0.0, seed=7)
+    s = ict[5]
+    q = s["query_tokens"][s["query_pad_mask"] == 1]
+    c = s["context_tokens"][s["context_pad_mask"] == 1]
+    assert q[0] == 2 and q[-1] == 3 and c[0] == 2 and c[-1] == 3
+    start, end = s["block_data"][:2]
+    block = [t for i in range(start, end) for t in ds[i]]
+    assert len(q) - 2 + len(c) - 2 == len(block)            # the query left its block
+    assert np.array_equal(ict[5]["query_tokens"], s["query_tokens"])      # deterministic per index
 
 
 def _torchrun(nproc, port, extra):
