@@ -124,6 +124,13 @@ class GpuECCheckpoint:
         """Snapshot + encode (+ host tier).  With ``overlap`` the encode and the host copies run on the manager's
         side stream and this call returns after the snapshot; ``wait()`` joins them."""
         cur = torch.cuda.current_stream()
+        cur.wait_stream(self.stream)                    # a previous overlapped encode / host copy still reads the snapshot
+        if getattr(self, "_events", None) is not None and overlap:
+            # device times of the previous (overlapped) save, complete by now
+            pe = self._events
+            if pe[3].query():
+                self.stats = {"snapshot_ms": pe[0].elapsed_time(pe[1]), "encode_ms": pe[2].elapsed_time(pe[3]),
+                              "bytes": self.stats.get("bytes", 0.0), "of_iteration": float(self.iteration or 0)}
         e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         e[0].record(cur)
         o = 0
@@ -154,6 +161,8 @@ class GpuECCheckpoint:
             torch.cuda.synchronize()
             self.stats = {"snapshot_ms": e[0].elapsed_time(e[1]), "encode_ms": e[2].elapsed_time(e[3]),
                           "bytes": float(o)}
+        else:
+            self.stats = dict(self.stats, bytes=float(o))
         return self.stats
 
     def wait(self):
@@ -164,6 +173,7 @@ class GpuECCheckpoint:
     # -- failure simulation / recovery -----------------------------------------------------
     def drop_device_state(self):
         """What a replacement GPU starts with: nothing in device memory."""
+        self.wait()                  # the last save's parity kernels (this rank's and the peers', behind its barrier)
         self.buf.zero_()
         torch.cuda.synchronize()
 
@@ -180,6 +190,7 @@ class GpuECCheckpoint:
         lost = sorted(set(int(r) for r in lost_ranks))
         if len(lost) > self.m:
             raise RuntimeError(f"{len(lost)} ranks lost but the code tolerates {self.m}")
+        self.wait()                                     # an overlapped encode / host copy of the last save
         self.hdl.barrier()
         if self.rank in lost:
             jobs = []

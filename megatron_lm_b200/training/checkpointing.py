@@ -346,7 +346,13 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
         for chunk in model:
             for buf in getattr(chunk, "buffers", []) + getattr(chunk, "expert_buffers", []):
                 tensors.append(buf.param_data)
-        stats = ec_manager.save(tensors, iteration)
+        if hasattr(ec_manager, "hdl"):
+            # GPU tier: the snapshot is taken on the training stream (a device-to-device copy); parity and the host
+            # copy run on the manager's side stream under the following steps.  The figures returned are the device
+            # times of the previous save (this one's are not known until it has run).
+            stats = dict(ec_manager.save(tensors, iteration, overlap=getattr(args, "ec_overlap", True)))
+        else:
+            stats = ec_manager.save(tensors, iteration)
         stats["total_s"] = time.time() - t0
         return stats
     save_dir = args.non_persistent_global_ckpt_dir if non_persistent else args.save

@@ -514,9 +514,13 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             st = checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, args, non_persistent=True,
                                                ec_manager=ec_manager)
             if "encode_ms" in st:        # GPU tier: device-timed snapshot and parity kernels
+                when = f" (device times of the save at iteration {int(st['of_iteration'])})" if "of_iteration" in st else ""
                 print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: snapshot "
-                             f"{st.get('snapshot_ms', 0.0):.2f} ms, encode {st['encode_ms']:.2f} ms, "
-                             f"{st.get('total_s', 0.0):.3f} s in all")
+                             f"{st.get('snapshot_ms', 0.0):.2f} ms, encode {st['encode_ms']:.2f} ms{when}, "
+                             f"{st.get('total_s', 0.0):.3f} s on the host")
+            elif hasattr(ec_manager, "hdl"):
+                print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: parity and host copy "
+                             f"running under the next steps, {st.get('total_s', 0.0):.3f} s on the host")
             else:
                 print_rank_0(f" in-memory erasure-coded checkpoint at iteration {iteration}: "
                              f"{st.get('encode_GBps', 0.0):.2f} GB/s encode, {st.get('total_s', 0.0):.3f} s")

@@ -51,3 +51,34 @@ def test_gpu_ec_rebuild(world, k, m, lose):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     run_on_gpus(_worker, world, k, m, lose)
+
+
+def _overlap_worker(rank, world):
+    """Two overlapped saves back to back while the 'training' tensors keep changing: the second save must not
+    overwrite the snapshot that the first one's parity kernel still reads, and recovery returns the second snapshot."""
+    import torch.distributed as dist
+    from megatron_lm_b200.checkpoint.ec_gpu import GpuECCheckpoint
+    chunk = 1 << 16
+    n = chunk * 40
+    g = torch.Generator(device="cuda").manual_seed(11 + rank)
+    a = torch.randint(0, 255, (n,), dtype=torch.uint8, device="cuda", generator=g)
+    mgr = GpuECCheckpoint(dist.group.WORLD, n, k=world - 1, m=1, chunk_bytes=chunk)
+    mgr.save([a], 5, overlap=True)
+    a.add_(3)                                       # the step after the save
+    keep = a.clone()
+    st = mgr.save([a], 6, overlap=True)
+    assert "bytes" in st
+    a.add_(1)
+    if rank == world - 1:
+        mgr.drop_device_state()                     # joins the side stream first: the peers' parity kernels read this rank
+    it = mgr.recover([world - 1], [a])
+    assert it == 6 and torch.equal(a, keep)
+    st = mgr.save([a], 7, overlap=True)             # the device times of save 6 are known by now
+    mgr.wait()
+    assert st.get("encode_ms", 0.0) > 0.0 and int(st.get("of_iteration", -1)) == 6
+
+
+def test_gpu_ec_overlapped_saves():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_on_gpus(_overlap_worker, 2)
