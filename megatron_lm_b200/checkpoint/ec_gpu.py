@@ -31,7 +31,7 @@ from .ec_plan import StripePlan, plan_stripes
 os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 _lib.register_signatures({"mlb_ec_apply_batch": "pilip", "mlb_ec_job_bytes": "",
-                          "mlb_ec_apply_batch_staged": "piliipp"})
+                          "mlb_ec_apply_batch_staged": "piliipp", "mlb_stream_copy": "pplip"})
 
 _JOB = np.dtype([("src", "<u8", 16), ("dst", "<u8", 4), ("coef", "u1", (4, 16)), ("k", "<i4"), ("m", "<i4"),
                  ("pad", "<i4", 2)])
@@ -39,7 +39,8 @@ _JOB = np.dtype([("src", "<u8", 16), ("dst", "<u8", 4), ("coef", "u1", (4, 16)),
 
 class GpuECCheckpoint:
     def __init__(self, group, state_bytes: int, k: Optional[int] = None, m: int = 2, chunk_bytes: int = 1 << 20,
-                 host_tier: bool = True, encode_blocks: int = 0, staged: bool = True):
+                 host_tier: bool = True, encode_blocks: int = 0, staged: bool = True, host_copy: str = "kernel",
+                 host_copy_blocks: int = 4):
         import torch.distributed._symmetric_memory as symm_mem
         assert _JOB.itemsize == _lib.lib().mlb_ec_job_bytes()
         self.group = group
@@ -51,6 +52,10 @@ class GpuECCheckpoint:
         self.chunk = int(chunk_bytes)
         self.encode_blocks = encode_blocks
         self.staged = staged
+        # "kernel": a few thread blocks store the snapshot and parity into pinned host memory; "dma": cudaMemcpyAsync
+        # (the copy engine then also serves the training stream's device-to-host reads one after the other)
+        self.host_copy = host_copy
+        self.host_copy_blocks = host_copy_blocks
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
         n = torch.tensor([(state_bytes + self.chunk - 1) // self.chunk], dtype=torch.int64, device=dev)
@@ -152,7 +157,12 @@ class GpuECCheckpoint:
         if self.host is not None:
             self.stream.wait_stream(st)
             with torch.cuda.stream(self.stream):
-                self.host.copy_(self.buf, non_blocking=True)
+                total = self.buf.numel()
+                if self.host_copy == "kernel" and total % 16 == 0:
+                    _lib.check(_lib.lib().mlb_stream_copy(self.host.data_ptr(), self.buf.data_ptr(), total,
+                                                          self.host_copy_blocks, self.stream.cuda_stream), "stream_copy")
+                else:
+                    self.host.copy_(self.buf, non_blocking=True)
                 self.host_event = torch.cuda.Event()
                 self.host_event.record(self.stream)
         self.iteration = iteration

@@ -78,6 +78,8 @@ def build_parser(extra_args_provider: Optional[Callable] = None) -> argparse.Arg
                         "group when it has at least k + m ranks, else the world")
     g.add_argument("--no-ec-overlap", dest="ec_overlap", action="store_false",
                    help="GPU tier: wait for the parity kernel and the host copy instead of running them under the next steps")
+    g.add_argument("--no-ec-host-tier", dest="ec_host_tier", action="store_false",
+                   help="GPU tier: keep snapshot and parity in the GPUs' memory only (no pinned-host copy)")
     g.add_argument("--ec-device", default="auto", choices=["auto", "gpu", "cpu"],
                    help="where parity is computed and held: peer GPUs' memory (auto on NCCL jobs) or host memory")
     g = parser.add_argument_group(title="peer-memory kernels")

@@ -334,7 +334,8 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
                 for buf in getattr(chunk, "buffers", []) + getattr(chunk, "expert_buffers", []):
                     tensors.append(buf.param_data)
             nbytes = sum(t.numel() * t.element_size() for t in tensors)
-            ec_manager = GpuECCheckpoint(grp, nbytes, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes)
+            ec_manager = GpuECCheckpoint(grp, nbytes, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes,
+                                         host_tier=getattr(args, "ec_host_tier", True))
         else:
             ec_manager = ECCheckpointManager(grp, args.ec_data_shards, args.ec_parity_shards, args.ec_chunk_bytes)
     timers("train/valid/test-data-iterators-setup", 0).start(barrier=True)
