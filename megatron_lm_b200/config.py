@@ -195,6 +195,7 @@ class TransformerConfig(ModelParallelConfig):
     window_size: Optional[Tuple[int, int]] = None
     normalization: str = "LayerNorm"
     qk_layernorm: bool = False
+    qk_l2_norm: bool = False          # parameter-free L2 normalisation of queries and keys (Llama-4 style)
     test_mode: bool = False
     calculate_per_token_loss: bool = False
     multi_latent_attention: bool = False

@@ -134,6 +134,70 @@ class BertModel(nn.Module):
         return loss.transpose(0, 1).contiguous(), binary_logits
 
 
+class Classification(nn.Module):
+    """Encoder + pooler + dropout + linear head over ``num_classes`` (sentence / sentence-pair classification).
+    ``MultipleChoice`` scores every choice with a one-logit head and returns [batch, choices].
+    Reference: megatron/legacy/model/classification.py:19-100, multiple_choice.py:19-110."""
+
+    def __init__(self, config: TransformerConfig, num_classes: int, vocab_size: int, max_sequence_length: int,
+                 num_tokentypes: int = 2, pre_process: bool = True, post_process: bool = True):
+        super().__init__()
+        self.config, self.num_classes = config, num_classes
+        self.pre_process, self.post_process = pre_process, post_process
+        if pre_process:
+            self.embedding = LanguageModelEmbedding(config, vocab_size, max_sequence_length, "learned_absolute",
+                                                    num_tokentypes)
+        self.encoder = TransformerBlock(config, pre_process, post_process, None, causal=False)
+        if post_process:
+            self.pooler = Pooler(config)
+            self.classification_dropout = nn.Dropout(config.hidden_dropout)
+            self.classification_head = nn.Linear(config.hidden_size, num_classes, device=_device(config),
+                                                 dtype=config.params_dtype)
+            if config.perform_initialization:
+                config.init_method(self.classification_head.weight)
+                nn.init.zeros_(self.classification_head.bias)
+
+    def set_input_tensor(self, t):
+        if isinstance(t, (list, tuple)):
+            t = t[0]
+        self.encoder.set_input_tensor(t)
+
+    def _encode(self, input_ids, attention_mask, tokentype_ids):
+        x = None
+        if self.pre_process:
+            pos = torch.arange(input_ids.shape[1], device=input_ids.device).unsqueeze(0).expand_as(input_ids)
+            x = self.embedding(input_ids, pos, tokentype_ids)
+        return self.encoder(x, attention_mask=bert_extended_attention_mask(attention_mask))
+
+    def forward(self, input_ids, attention_mask, tokentype_ids=None):
+        h = self._encode(input_ids, attention_mask, tokentype_ids)
+        if not self.post_process:
+            return h
+        return self.classification_head(self.classification_dropout(self.pooler(h, 0))).view(-1, self.num_classes)
+
+    def load_pretrained_encoder(self, bert_state_dict, strict: bool = False):
+        """Take embedding, encoder and pooler from a pre-trained ``BertModel`` state dict; the head stays fresh."""
+        own = self.state_dict()
+        take = {k: v for k, v in bert_state_dict.items() if k in own and own[k].shape == v.shape
+                and not k.startswith("classification_head")}
+        return self.load_state_dict(take, strict=strict)
+
+
+class MultipleChoice(Classification):
+    def __init__(self, config: TransformerConfig, vocab_size: int, max_sequence_length: int, num_tokentypes: int = 2,
+                 pre_process: bool = True, post_process: bool = True):
+        super().__init__(config, 1, vocab_size, max_sequence_length, num_tokentypes, pre_process, post_process)
+
+    def forward(self, input_ids, attention_mask, tokentype_ids=None):
+        # [batch, choices, seq] -> every choice is a row of the encoder's batch
+        b, c, s = input_ids.shape
+        flat = lambda t: None if t is None else t.reshape(b * c, s)
+        h = self._encode(flat(input_ids), flat(attention_mask), flat(tokentype_ids))
+        if not self.post_process:
+            return h
+        return self.classification_head(self.classification_dropout(self.pooler(h, 0))).view(b, c)
+
+
 class _BertTower(nn.Module):
     """Embedding + bidirectional encoder + pooler: what one side of the biencoder needs of a BERT model."""
 

@@ -221,7 +221,9 @@ class SelfAttention(nn.Module):
         self.linear_proj = RowParallelLinear(self.np * self.hn, config.hidden_size, config=config,
                                              init_method=config.output_layer_init_method,
                                              bias=config.add_bias_linear, skip_bias_add=True)
-        if config.qk_layernorm:
+        if getattr(config, "qk_l2_norm", False):
+            self.q_layernorm, self.k_layernorm = L2Norm(self.hn), L2Norm(self.hn)
+        elif config.qk_layernorm:
             self.q_layernorm = Norm(config, self.hn)
             self.k_layernorm = Norm(config, self.hn)
         else:

@@ -268,10 +268,14 @@ class ColumnParallelLinear(nn.Module):
         else:
             self.register_parameter("bias", None)
         self.fused = None    # set by the model builder when tp_comm_overlap is on
+        self.ptq = False     # post-training quantisation attached (post_training/ptq.py)
 
     def forward(self, x, weight: Optional[torch.Tensor] = None):
         w = self.weight if weight is None else weight
         b = self.bias if not self.skip_bias_add else None
+        if self.ptq:
+            from ..post_training.ptq import apply_quantizers
+            x, w = apply_quantizers(self, x, w)
         fmt = _fp8_format(self, x, w)
         if fmt is not None:
             linear_fp8 = _fp8_linear(self)
@@ -330,23 +334,28 @@ class RowParallelLinear(nn.Module):
         else:
             self.register_parameter("bias", None)
         self.fused = None
+        self.ptq = False
 
     def forward(self, x):
         if not self.input_is_parallel and self.tp_size > 1:
             from .mappings import scatter_to_tensor_model_parallel_region
             x = scatter_to_tensor_model_parallel_region(x, self.tp_group)
         red = "none" if self.tp_size == 1 else ("reduce_scatter" if self.sequence_parallel else "all_reduce")
-        fmt = _fp8_format(self, x, self.weight)
+        w = self.weight
+        if self.ptq:
+            from ..post_training.ptq import apply_quantizers
+            x, w = apply_quantizers(self, x, w)
+        fmt = _fp8_format(self, x, w)
         if fmt is not None:
             linear_fp8 = _fp8_linear(self)
             from .mappings import reduce_from_tensor_model_parallel_region, reduce_scatter_to_sequence_parallel_region
-            y = linear_fp8(x, self.weight, None, fmt)
+            y = linear_fp8(x, w, None, fmt)
             if red == "reduce_scatter":
                 y = reduce_scatter_to_sequence_parallel_region(y, self.tp_group)
             elif red == "all_reduce":
                 y = reduce_from_tensor_model_parallel_region(y, self.tp_group)
         else:
-            y = tp_linear(x, self.weight, None, group=self.tp_group, reduce_output=red, fused=self.fused)
+            y = tp_linear(x, w, None, group=self.tp_group, reduce_output=red, fused=self.fused)
         if self.skip_bias_add or self.bias is None:
             return y, self.bias
         return y + self.bias, None

@@ -285,6 +285,11 @@ def forward_backward_pipelining(*, forward_step_func, data_iterator, model, num_
     plan = build_pipeline_plan(num_microbatches, pp_size, pp_rank, v, config.microbatch_group_size_per_vp_stage,
                                forward_only)
     shape = get_tensor_shapes(seq_length, micro_batch_size, config)
+    # a wrapper that sends more than one activation per boundary (distillation: student and teacher hidden states
+    # side by side) widens the exchanged tensor (reference: schedules.py adjust_tensor_shapes_fn)
+    adjust = adjust_tensor_shapes_fn or getattr(config, "adjust_tensor_shapes_fn", None)
+    if adjust is not None:
+        shape = tuple(adjust(shape))
     dtype = config.pipeline_dtype or config.params_dtype
     pp_group = state.get_pipeline_model_parallel_group()
     comm = p2p.P2PCommunicator(pp_group, pp_rank, pp_size, shape, dtype, config)

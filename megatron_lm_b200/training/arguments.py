@@ -289,25 +289,15 @@ UNUSED_FLAGS = {
     "bert_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),
     "evidence_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
     "block_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
-    "embedding_path": (_R, "pretrain_ict is not built"), "indexer_batch_size": (_W, "pretrain_ict is not built"),
-    "indexer_log_interval": (_W, "pretrain_ict is not built"),
-    "classes_fraction": (_W, "only the classification program of the vision pre-training programs is built"),
-    "data_per_class_fraction": (_W, "only the classification program of the vision pre-training programs is built"),
-    "data_sharding": (_W, "only the classification program of the vision pre-training programs is built"), "head_lr_mult": (_W, "only the classification program of the vision pre-training programs is built"),
-    "vision_pretraining": (_W, "pretrain_vision_classify.py is the vision program; the flag itself selects nothing"),
-    "vision_pretraining_type": (_W, "only the classification program of the vision pre-training programs is built"),
-    "vision_backbone_type": (_W, "only the classification program of the vision pre-training programs is built"),
-    "swin_backbone_type": (_W, "only the classification program of the vision pre-training programs is built"), "mask_type": (_W, "only the classification program of the vision pre-training programs is built"),
-    "mask_factor": (_W, "only the classification program of the vision pre-training programs is built"), "iter_per_epoch": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_local_img_size": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_local_crops_number": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_head_hidden_size": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_bottleneck_size": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_freeze_last_layer": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_norm_last_layer": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_warmup_teacher_temp": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_teacher_temp": (_W, "only the classification program of the vision pre-training programs is built"),
-    "dino_warmup_teacher_temp_epochs": (_W, "only the classification program of the vision pre-training programs is built"),
+    "embedding_path": (_R, "the inverse-cloze program builds no block-embedding index"), "indexer_batch_size": (_W, "the inverse-cloze program builds no block-embedding index"),
+    "indexer_log_interval": (_W, "the inverse-cloze program builds no block-embedding index"),
+    "classes_fraction": (_W, "the image-folder dataset reads every class"),
+    "data_per_class_fraction": (_W, "the image-folder dataset reads every image of a class"),
+    "data_sharding": (_W, "the sampler always gives each data-parallel rank its own part"), "head_lr_mult": (_W, "the vision heads train with the backbone's learning rate"),
+    "vision_pretraining_type": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice"),
+    "vision_pretraining": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice; the flag selects nothing"),
+    "vision_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
+    "swin_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
     # resilience / logging services that run with fixed settings here
     "disable_straggler_on_startup": (_W, "the straggler detector has no remote toggle"),
     "straggler_ctrlr_port": (_W, "the straggler detector has no remote toggle"),

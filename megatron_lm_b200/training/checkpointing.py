@@ -121,6 +121,13 @@ def optimizer_sharded_state_dict(optimizer, model: Sequence[torch.nn.Module],
     for ci, chunk in enumerate(model):
         for n, p in _unwrap(chunk).named_parameters():
             name_of[p] = (ci, n)
+        # trained parameters that belong to a wrapper, not to the saved model (a distillation projection layer):
+        # their optimizer state is kept under the wrapper's name
+        m = chunk
+        while hasattr(m, "module"):
+            for n, p in m.named_parameters():
+                name_of.setdefault(p, (ci, "wrapper." + n))
+            m = m.module
     c = _coords()
     out: Dict[str, Any] = {"param_state": {}, "common": []}
     for oi, opt in enumerate(opts):
@@ -363,6 +370,10 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
                    num_floating_point_operations_so_far)
         stats["total_s"] = time.time() - t0
         return stats
+    from ..post_training.checkpointing import has_quantizers, save_quantizer_state
+    if fmt == "torch_dist" and has_quantizers(model):
+        raise NotImplementedError("a model with post-training quantisers is saved with --ckpt-format torch "
+                                  "(quantiser ranges and compressed weights are buffers of the per-rank state dict)")
     if fmt == "torch_dist":
         sd = generate_state_dict(args, model, optimizer, opt_param_scheduler, rng, iteration, True, rerun_state,
                                  num_floating_point_operations_so_far)
@@ -396,6 +407,7 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
         if _writes_model_file():
             os.makedirs(os.path.dirname(name), exist_ok=True)
             torch.save(sd, name)
+            save_quantizer_state(model, os.path.dirname(name))
         if dist.is_initialized():
             dist.barrier()
         _write_tracker(save_dir, iteration)
@@ -469,6 +481,8 @@ def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Op
     else:
         name = get_checkpoint_name(load_dir, iteration, release)
         sd = torch.load(name, map_location="cpu", weights_only=False)
+        from ..post_training.checkpointing import maybe_restore_quantizer_state
+        maybe_restore_quantizer_state(model, os.path.dirname(name))
         for i, chunk in enumerate(model):
             _unwrap(chunk).load_state_dict(sd["model" if len(model) == 1 else f"model{i}"], strict=strict)
         if optimizer is not None and not no_optim and "optimizer" in sd:

@@ -424,11 +424,19 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
                 and args.rank in (args.profile_ranks or [0]) and prof is None:
             torch.cuda.cudart().cudaProfilerStart()
         nvtx_range_push(f"iteration {iteration + 1}")
+        args.curr_iteration = iteration
         loss_dict, skipped, grad_norm, zeros = train_step(
             forward_step_func, its, model, optimizer, scheduler, config, num_microbatches=nmb,
             seq_length=args.seq_length, micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size,
             rerun_state_machine=rerun)
         nvtx_range_pop(f"iteration {iteration + 1}")
+        if not skipped:
+            # models that keep a second set of weights in step with the trained one (the momentum teacher of DINO:
+            # reference training.py, update_momentum after the optimizer step)
+            for chunk in model:
+                hook = getattr(checkpointing._unwrap(chunk), "after_optimizer_step", None)
+                if hook is not None:
+                    hook(iteration)
         for step_no, diag, what in rerun.diagnostics[reported:]:
             print(f" [rank {args.rank}] result validation, iteration {iteration + 1}: {diag.value} ({what})", flush=True)
         reported = len(rerun.diagnostics)

@@ -25,9 +25,7 @@ from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E
 from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 
 
-def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
-    args = get_args()
-    print_rank_0("building GPT model ...")
+def _gpt(args, config, pre_process, post_process, vp_stage):
     return GPTModel(config, vocab_size=args.padded_vocab_size, max_sequence_length=args.max_position_embeddings,
                     pre_process=pre_process, post_process=post_process, fp16_lm_cross_entropy=args.fp16_lm_cross_entropy,
                     parallel_output=True,
@@ -36,6 +34,57 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
                     rotary_base=args.rotary_base, rope_scaling=getattr(args, "use_rope_scaling", False),
                     rope_scaling_factor=getattr(args, "rope_scaling_factor", 8.0),
                     seq_len_interpolation_factor=args.rotary_seq_len_interpolation_factor, vp_stage=vp_stage)
+
+
+def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
+    args = get_args()
+    print_rank_0("building GPT model ...")
+    if getattr(args, "export_qk_l2_norm", False):
+        config.qk_l2_norm = True
+    model = _gpt(args, config, pre_process, post_process, vp_stage)
+    if getattr(args, "export_kd_teacher_load", None) or getattr(args, "export_kd_cfg", None):
+        model = _with_teacher(args, config, model, pre_process, post_process, vp_stage)
+    return model
+
+
+def _with_teacher(args, config, student, pre_process, post_process, vp_stage):
+    """Knowledge distillation (--export-kd-teacher-load / --export-kd-cfg): a frozen teacher of the architecture in
+    ``<teacher checkpoint>/model_config.yaml`` (the student's when that file is absent) rides along with the student
+    (reference: megatron/post_training/model_provider.py:36-117)."""
+    import copy
+    import yaml
+    from megatron_lm_b200.post_training.distillation import DistillationModel, load_distillation_config
+    from megatron_lm_b200.training import checkpointing
+    if vp_stage not in (None, 0) or (args.virtual_pipeline_model_parallel_size or 1) > 1:
+        raise NotImplementedError("distillation with interleaved pipeline stages")
+    t_cfg, t_args = copy.copy(config), copy.copy(args)
+    load = getattr(args, "export_kd_teacher_load", None)
+    if load and os.path.isfile(os.path.join(load, "model_config.yaml")):
+        with open(os.path.join(load, "model_config.yaml")) as f:
+            over = yaml.safe_load(f) or {}
+        for k, v in over.items():
+            if hasattr(t_cfg, k):
+                setattr(t_cfg, k, v)
+            if hasattr(t_args, k):
+                setattr(t_args, k, v)
+        if "num_query_groups" not in over and "num_attention_heads" in over and not over.get("group_query_attention"):
+            t_cfg.num_query_groups = t_cfg.num_attention_heads
+        if "kv_channels" not in over:
+            t_cfg.kv_channels = t_cfg.hidden_size // t_cfg.num_attention_heads
+    teacher = _gpt(t_args, t_cfg, pre_process, post_process, vp_stage)
+    if load:
+        t_args.load, t_args.finetune, t_args.no_load_optim, t_args.no_load_rng = load, True, True, True
+        checkpointing.load_checkpoint([teacher], None, None, t_args, load_dir=load)
+        print_rank_0(f"distillation teacher loaded from {load}")
+    offsets = (getattr(student.decoder, "layer_offset", 0), getattr(teacher.decoder, "layer_offset", 0))
+    kd = load_distillation_config(getattr(args, "export_kd_cfg", None), config, t_cfg,
+                                  tp_group=state.get_tensor_model_parallel_group()
+                                  if state.get_tensor_model_parallel_world_size() > 1 else None,
+                                  layer_offsets=offsets, last_stage=post_process)
+    model = DistillationModel(student, teacher, kd)
+    if state.get_pipeline_model_parallel_world_size() > 1:
+        config.adjust_tensor_shapes_fn = model.adjust_tensor_shapes
+    return model
 
 
 def get_batch(data_iterator):
@@ -56,10 +105,31 @@ def loss_func(loss_mask, output_tensor):
     return total[0], total[1].to(torch.int64), {"lm loss": total.detach().clone()}
 
 
+def distill_loss_func(loss_mask, model, output_tensor):
+    from megatron_lm_b200.post_training.distillation import distillation_loss_func
+    tp_group = state.get_tensor_model_parallel_group() if state.get_tensor_model_parallel_world_size() > 1 else None
+    total, tokens, report = distillation_loss_func(loss_mask, output_tensor, model, tp_group)
+    validate_loss(report["lm loss"][0], get_args())
+    return total, tokens, report
+
+
 def forward_step(data_iterator, model):
     tokens, labels, loss_mask, attention_mask, position_ids = get_batch(data_iterator)
     out = model(tokens, position_ids, attention_mask, labels=labels)
+    if _DISTILL[0] is None:
+        from megatron_lm_b200.post_training.distillation import unwrap_distillation_model
+        _DISTILL[0] = unwrap_distillation_model(model) is not None
+    if _DISTILL[0]:
+        return out, partial(distill_loss_func, loss_mask, model)
     return out, partial(loss_func, loss_mask)
+
+
+_DISTILL = [None]
+
+
+def extra_args(parser):
+    from megatron_lm_b200.post_training.arguments import add_modelopt_args
+    return add_modelopt_args(parser)
 
 
 def train_valid_test_datasets_provider(num_samples):
@@ -99,5 +169,5 @@ def train_valid_test_datasets_provider(num_samples):
 
 
 if __name__ == "__main__":
-    pretrain(train_valid_test_datasets_provider, model_provider, forward_step,
+    pretrain(train_valid_test_datasets_provider, model_provider, forward_step, extra_args_provider=extra_args,
              args_defaults={"tokenizer_type": "GPT2BPETokenizer"})

@@ -258,7 +258,7 @@ def _flags_nobody_reads():
             if not f.endswith(".py") or f == "flag_table.py":
                 continue
             t = open(os.path.join(base, f)).read()
-            if f == "arguments.py":
+            if f == "arguments.py" and os.path.basename(base) == "training":
                 a = t.index("UNUSED_FLAGS = {")
                 t = t[:a] + t[t.index("\n}\n", a):]
             texts.append(t)

@@ -353,3 +353,38 @@ def test_erasure_coded_checkpoint_over_the_whole_job_without_data_parallelism():
                                "--global-batch-size", "2", "--non-persistent-ckpt-type", "local",
                                "--non-persistent-save-interval", "2", "--ec-data-shards", "2", "--ec-parity-shards", "2"])
     assert "in-memory erasure-coded checkpoint at iteration 2" in out
+
+
+_VIT = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "17",
+        "--max-position-embeddings", "17", "--micro-batch-size", "4", "--global-batch-size", "8", "--lr", "2e-3",
+        "--min-lr", "1e-4", "--lr-decay-style", "cosine", "--mock-data", "--log-interval", "1", "--img-h", "32",
+        "--img-w", "32", "--patch-dim", "8", "--num-classes", "4", "--use-cpu-initialization", "--attention-dropout", "0",
+        "--hidden-dropout", "0", "--eval-iters", "2"]
+
+
+def _program(script, extra):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29655")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, script)] + _VIT + extra, capture_output=True, text=True,
+                       timeout=280, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    return r.stdout
+
+
+def test_vision_inpainting_program_reconstructs_and_reports_image_metrics():
+    out = _program("pretrain_vision_inpaint.py", ["--train-iters", "30", "--eval-interval", "30", "--mask-type", "row",
+                                                  "--mask-factor", "1.5"])
+    rows = _iters(out, "loss")
+    assert sorted(rows)[-1] == 30 and rows[30][1] < 0.6 * rows[1][1]
+    assert re.search(r"validation loss at iteration 30 .*psnr value: [0-9.E+-]+ .*ssim value: [0-9.E+-]+", out)
+
+
+def test_vision_dino_program_trains_with_momentum_teacher_and_knn_monitor():
+    out = _program("pretrain_vision_dino.py", ["--train-iters", "12", "--eval-interval", "12", "--dino-out-dim", "64",
+                                               "--dino-head-hidden-size", "48", "--dino-bottleneck-size", "16",
+                                               "--dino-local-crops-number", "2", "--dino-local-img-size", "16",
+                                               "--iter-per-epoch", "4", "--dino-freeze-last-layer", "1",
+                                               "--dino-warmup-teacher-temp-epochs", "2", "--knn-bank-size", "32"])
+    rows = _iters(out, "loss")
+    assert sorted(rows) == list(range(1, 13))
+    assert all(0 < v[1] < 6 for v in rows.values())                    # bounded by ln(64) = 4.16 at uniform outputs
+    assert re.search(r"validation loss at iteration 12 .*knn_acc_10 value: [0-9.E+-]+", out)
