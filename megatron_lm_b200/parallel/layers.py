@@ -273,12 +273,14 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, x, weight: Optional[torch.Tensor] = None):
         w = self.weight if weight is None else weight
         b = self.bias if not self.skip_bias_add else None
+        pre = False
         if self.ptq:
-            from ..post_training.ptq import apply_quantizers
+            from ..post_training.ptq import apply_quantizers, prequantized_linear
             x, w = apply_quantizers(self, x, w)
-        fmt = _fp8_format(self, x, w)
+            pre = getattr(w, "prequantized", False)      # compressed weight fed to the FP8 GEMM as stored
+        fmt = "prequant" if pre else _fp8_format(self, x, w)
         if fmt is not None:
-            linear_fp8 = _fp8_linear(self)
+            linear_fp8 = prequantized_linear if pre else _fp8_linear(self)
             from .mappings import copy_to_tensor_model_parallel_region, gather_from_sequence_parallel_region
             if self.sequence_parallel:
                 inp = gather_from_sequence_parallel_region(x, True, self.tp_group)
@@ -342,12 +344,14 @@ class RowParallelLinear(nn.Module):
             x = scatter_to_tensor_model_parallel_region(x, self.tp_group)
         red = "none" if self.tp_size == 1 else ("reduce_scatter" if self.sequence_parallel else "all_reduce")
         w = self.weight
+        pre = False
         if self.ptq:
-            from ..post_training.ptq import apply_quantizers
+            from ..post_training.ptq import apply_quantizers, prequantized_linear
             x, w = apply_quantizers(self, x, w)
-        fmt = _fp8_format(self, x, w)
+            pre = getattr(w, "prequantized", False)
+        fmt = "prequant" if pre else _fp8_format(self, x, w)
         if fmt is not None:
-            linear_fp8 = _fp8_linear(self)
+            linear_fp8 = prequantized_linear if pre else _fp8_linear(self)
             from .mappings import reduce_from_tensor_model_parallel_region, reduce_scatter_to_sequence_parallel_region
             y = linear_fp8(x, w, None, fmt)
             if red == "reduce_scatter":

@@ -13,7 +13,8 @@ w4a8_awq, nvfp4 and the two ``*_real_quant`` forms), megatron/core/post_training
   channel scales into the weights, and switches the quantisers to simulated quantisation (quantise-dequantise with a
   straight-through gradient, so quantisation-aware fine-tuning works too);
 * ``compress(model)`` replaces the 16-bit weight of every quantised linear by its FP8 image plus scales (per tensor or
-  per 128 x 128 block) and reports the bytes saved; the forward de-quantises on the fly;
+  per 128 x 128 block) and reports the bytes saved; on a GPU a per-tensor FP8 weight goes to the FP8 tensor-core
+  GEMM as stored (``prequantized_linear``), otherwise the forward de-quantises on the fly;
 * ``quantizer_state`` / ``restore_quantizer_state`` describe the attached quantisers so a checkpoint can be loaded
   into a freshly built model.
 """
@@ -178,13 +179,42 @@ class TensorQuantizer(nn.Module):
         return f"{self.spec.kind} block={self.spec.block} axis={self.spec.axis} enabled={self.spec.enabled}"
 
 
+class PrequantizedWeight:
+    """A compressed weight handed to the FP8 GEMM as it is stored (E4M3 bytes + one fp32 scale)."""
+    prequantized = True
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor):
+        self.q, self.scale, self.shape = q.view(torch.uint8), scale.reshape(1), q.shape
+
+
+FAST_PATH_CALLS = [0]          # how many linears took the stored-FP8 GEMM (tests read it)
+
+
 def apply_quantizers(linear, x: torch.Tensor, w: Optional[torch.Tensor]):
     """Called by the tensor-parallel linears when ``linear.ptq`` is set: returns the (x, w) the GEMM sees."""
-    if w is None:                                            # compressed: rebuild the 16-bit weight on the fly
+    if w is None:
+        # compressed weight.  On a GPU, without gradients, a per-tensor FP8 weight feeds the FP8 tensor-core GEMM
+        # directly (the activation is cast with its own range); otherwise the 16-bit weight is rebuilt on the fly.
+        q = linear.weight_q
+        if q.is_cuda and linear.weight_scale.numel() == 1 and not torch.is_grad_enabled() \
+                and x.dtype in (torch.bfloat16, torch.float16) and not getattr(linear, "ptq_dequantize_only", False) \
+                and (x.numel() // x.shape[-1]) % 16 == 0 and q.shape[0] % 16 == 0 and q.shape[1] % 16 == 0:
+            FAST_PATH_CALLS[0] += 1
+            return x, PrequantizedWeight(q, linear.weight_scale)
         w = dequantize_weight(linear)
     else:
         w = linear.weight_quantizer(w)
     return linear.input_quantizer(x), w
+
+
+def prequantized_linear(x: torch.Tensor, w: PrequantizedWeight, bias=None, _fmt=None) -> torch.Tensor:
+    """y = x W^T with W already in FP8: one cast of the activation, one FP8 GEMM."""
+    from ..ops.fp8 import gemm_fp8, quantize
+    x2 = x.reshape(-1, x.shape[-1])
+    xq = quantize(x2, 0, transpose=False)
+    y = gemm_fp8(xq.data, 0, xq.scale_inv, w.q, 0, w.scale, out_dtype=x.dtype,
+                 bias=None if bias is None else bias.to(x.dtype))
+    return y.view(*x.shape[:-1], w.shape[0])
 
 
 def quantized_linears(model) -> Iterable[Tuple[str, nn.Module]]:

@@ -222,3 +222,28 @@ def _program_rank(rank, world, out_dir, fmt):
 @pytest.mark.parametrize("world,fmt", [(1, "fp8_real_quant"), (2, "int8_sq")])
 def test_calibration_program_saves_a_loadable_quantised_model(world, fmt, tmp_path):
     run_distributed(_program_rank, world, str(tmp_path / "q"), fmt)
+
+
+@pytest.mark.gpu
+def test_compressed_weights_feed_the_fp8_gemm_directly():
+    """On a GPU the per-tensor FP8 weights go to the FP8 tensor-core GEMM as stored; the result matches the
+    de-quantise-then-multiply path up to the activation cast."""
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    cfg = TransformerConfig(num_layers=2, hidden_size=256, num_attention_heads=4, ffn_hidden_size=512,
+                            hidden_dropout=0.0, attention_dropout=0.0, gated_linear_unit=True, add_bias_linear=False,
+                            params_dtype=torch.bfloat16, bf16=True)
+    m = GPTModel(cfg, 96, 64, parallel_output=False).to(dev)
+    ids = torch.randint(0, 96, (4, 64), device=dev)
+    pos = torch.arange(64, device=dev).unsqueeze(0).expand(4, 64)
+    ref = _logits(m, ids, pos)
+    ptq.quantize(m, "fp8_real_quant", lambda mod: mod(ids, pos, None))
+    before = ptq.FAST_PATH_CALLS[0]
+    fast = _logits(m, ids, pos)
+    assert ptq.FAST_PATH_CALLS[0] - before == 8                     # every compressed linear took the FP8 GEMM
+    for _, lin in ptq.quantized_linears(m):
+        lin.ptq_dequantize_only = True
+    slow = _logits(m, ids, pos)
+    assert ptq.FAST_PATH_CALLS[0] - before == 8
+    assert ((fast - slow).norm() / slow.norm()).item() < 0.05
+    assert ((fast - ref).norm() / ref.norm()).item() < 0.15
