@@ -340,7 +340,12 @@ class BlendedMegatronDatasetBuilder:
     def _low_level(self, prefix: Optional[str]):
         if self.config.mock or prefix is None:
             return MockGPTLowLevelDataset(self.config.tokenizer)
-        return IndexedDataset(prefix, mmap=self.config.mmap_bin_files)
+        osc = None
+        cache = getattr(self.config, "object_storage_cache_path", None)
+        if cache:
+            from .object_storage import ObjectStorageConfig
+            osc = ObjectStorageConfig(path_to_idx_cache=cache)
+        return IndexedDataset(prefix, mmap=self.config.mmap_bin_files, object_storage_config=osc)
 
     def _split_one(self, prefix: Optional[str], sizes: Sequence[Optional[int]], split_matrix) -> List[Optional[GPTDataset]]:
         low = self._low_level(prefix)

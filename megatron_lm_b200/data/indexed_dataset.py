@@ -67,8 +67,21 @@ class _Index:
 class IndexedDataset:
     """Random access to the sequences of a ``.bin``/``.idx`` pair (mmap by default)."""
 
-    def __init__(self, path_prefix: str, multimodal: bool = False, mmap: bool = True):
+    def __init__(self, path_prefix: str, multimodal: bool = False, mmap: bool = True, object_storage_config=None):
         self.path_prefix, self.multimodal, self.mmap = path_prefix, multimodal, mmap
+        self._remote = None
+        from . import object_storage as osu
+        if osu.is_object_storage_path(path_prefix):
+            # index cached on local disk, tokens read from the store in large cached ranges
+            if object_storage_config is None:
+                raise ValueError(f"{path_prefix}: an object-storage dataset needs an ObjectStorageConfig "
+                                 "(where to cache the index, how large a ranged read is)")
+            local_idx = osu.get_index_cache_path(get_idx_path(path_prefix), object_storage_config)
+            osu.cache_index_file(get_idx_path(path_prefix), local_idx)
+            self.index = _Index(local_idx, multimodal)
+            self._remote = osu.ObjectStorageBinReader(get_bin_path(path_prefix), object_storage_config)
+            self.mmap = False
+            return
         self.index = _Index(get_idx_path(path_prefix), multimodal)
         if mmap:
             self._bin = np.memmap(get_bin_path(path_prefix), mode="r", order="C")
@@ -80,6 +93,8 @@ class IndexedDataset:
         return len(self.index)
 
     def _read(self, count: int, byte_offset: int) -> np.ndarray:
+        if self._remote is not None:
+            return self._remote.read(self.index.dtype, count, byte_offset)
         if self.mmap:
             return np.frombuffer(self._buf, dtype=self.index.dtype, count=count, offset=byte_offset)
         self._file.seek(byte_offset)
@@ -119,6 +134,9 @@ class IndexedDataset:
 
     @staticmethod
     def exists(path_prefix: str) -> bool:
+        from . import object_storage as osu
+        if osu.is_object_storage_path(path_prefix):
+            return osu.dataset_exists(path_prefix, get_idx_path(path_prefix), get_bin_path(path_prefix))
         return os.path.exists(get_idx_path(path_prefix)) and os.path.exists(get_bin_path(path_prefix))
 
 

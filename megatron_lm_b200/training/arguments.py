@@ -299,9 +299,6 @@ UNUSED_FLAGS = {
     "vision_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
     "swin_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
     # resilience / logging services that run with fixed settings here
-    "disable_straggler_on_startup": (_W, "the straggler detector has no remote toggle"),
-    "straggler_ctrlr_port": (_W, "the straggler detector has no remote toggle"),
-    "straggler_minmax_count": (_W, "the straggler report lists every rank"),
     "run_workload_inspector_server": (_W, "no workload-inspector server"),
     "inprocess_monitor_thread_interval": (_W, "the restart wrapper polls once per step"),
     "inprocess_monitor_process_interval": (_W, "the restart wrapper polls once per step"),

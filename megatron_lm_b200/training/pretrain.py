@@ -353,7 +353,12 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     rerun = RerunStateMachine(mode=getattr(args, "rerun_mode", None) or "disabled", error_injector=inj)
     set_rerun_state_machine(rerun)
     sig = DistributedSignalHandler().__enter__() if getattr(args, "exit_signal_handler", False) else None
-    straggler = StragglerDetector() if getattr(args, "log_straggler", False) else None
+    straggler = None
+    if getattr(args, "log_straggler", False):
+        port = getattr(args, "straggler_ctrlr_port", 65535)
+        straggler = StragglerDetector(enabled=not getattr(args, "disable_straggler_on_startup", False),
+                                      port=port if port and port != 65535 else None,
+                                      minmax_count=getattr(args, "straggler_minmax_count", 1))
     dp = state.get_data_parallel_world_size()
     nmb = args.global_batch_size // (args.micro_batch_size * dp)
     total_loss: Dict = {}
@@ -425,11 +430,15 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
             torch.cuda.cudart().cudaProfilerStart()
         nvtx_range_push(f"iteration {iteration + 1}")
         args.curr_iteration = iteration
+        if straggler is not None:
+            straggler.start()
         loss_dict, skipped, grad_norm, zeros = train_step(
             forward_step_func, its, model, optimizer, scheduler, config, num_microbatches=nmb,
             seq_length=args.seq_length, micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size,
             rerun_state_machine=rerun)
         nvtx_range_pop(f"iteration {iteration + 1}")
+        if straggler is not None:
+            straggler.stop()
         if not skipped:
             # models that keep a second set of weights in step with the trained one (the momentum teacher of DINO:
             # reference training.py, update_momentum after the optimizer step)

@@ -373,12 +373,72 @@ class DistributedSignalHandler:
 
 # ----------------------------------------------------------------------------- stragglers
 class StragglerDetector:
-    def __init__(self):
+    """Per-rank step times, gathered at report time: the slowest and fastest ``minmax_count`` ranks are printed.
+
+    Measurement can be switched on and off while the job runs: with ``port`` set, rank 0 listens on that TCP port and
+    every HTTP GET toggles its flag and answers with the new state; the flag travels to the other ranks with the next
+    report's gather, so all ranks switch at the same step (reference: megatron/core/utils.py ``StragglerDetector``
+    - ``--straggler-ctrlr-port``, ``--disable-straggler-on-startup``, ``--straggler-minmax-count``)."""
+
+    def __init__(self, enabled: bool = True, port: Optional[int] = None, minmax_count: int = 1):
         self.times: List[float] = []
         self._t0 = None
         self._ev = None
+        self.enabled = enabled                 # what start/stop obey (identical on all ranks between reports)
+        self._requested = enabled              # rank 0: what the controller last asked for
+        self.minmax_count = max(int(minmax_count), 1)
+        self.port = None
+        self._server = None
+        rank0 = not dist.is_initialized() or dist.get_rank() == 0
+        if port is not None and rank0:
+            self._serve(port)
 
+    # -- controller -----------------------------------------------------------------------------------------------
+    def _serve(self, port: int):
+        import socket
+        srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+        srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        try:
+            srv.bind(("0.0.0.0", port))
+        except OSError as e:
+            print(f" straggler controller: cannot listen on port {port} ({e}); the toggle is unavailable", flush=True)
+            srv.close()
+            return
+        srv.listen(4)
+        srv.settimeout(0.5)
+        self.port = srv.getsockname()[1]
+        self._server = srv
+        self._stop = threading.Event()
+
+        def loop():
+            while not self._stop.is_set():
+                try:
+                    conn, _ = srv.accept()
+                except OSError:
+                    continue
+                try:
+                    conn.settimeout(1.0)
+                    conn.recv(1024)
+                    self._requested = not self._requested
+                    body = json.dumps({"straggler_detector_enabled": self._requested})
+                    conn.sendall((f"HTTP/1.0 200 OK\r\nContent-Type: application/json\r\nContent-Length: {len(body)}"
+                                  f"\r\n\r\n{body}").encode())
+                except OSError:
+                    pass
+                finally:
+                    conn.close()
+        threading.Thread(target=loop, daemon=True).start()
+
+    def close(self):
+        if self._server is not None:
+            self._stop.set()
+            self._server.close()
+            self._server = None
+
+    # -- measurement ----------------------------------------------------------------------------------------------
     def start(self):
+        if not self.enabled:
+            return
         if torch.cuda.is_available():
             self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             self._ev[0].record()
@@ -396,21 +456,36 @@ class StragglerDetector:
             self._t0 = None
 
     def report(self, iteration: int, flops_per_step: Optional[float] = None) -> Optional[dict]:
+        was_enabled = self.enabled
         mine = sum(self.times) / max(len(self.times), 1) if self.times else 0.0
         self.times = []
         if not dist.is_initialized() or dist.get_world_size() == 1:
-            return {"min": (0, mine), "max": (0, mine)}
+            self.enabled = self._requested
+            if not was_enabled:
+                return None
+            print(f" straggler report @ {iteration}: one rank, {mine * 1e3:.1f} ms per step", flush=True)
+            return {"min": (0, mine), "max": (0, mine), "fastest": [(0, mine)], "slowest": [(0, mine)],
+                    "enabled": self.enabled}
         dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
-        t = torch.tensor([mine], dtype=torch.float32, device=dev)
+        t = torch.tensor([mine, 1.0 if self._requested else 0.0], dtype=torch.float32, device=dev)
         allt = [torch.zeros_like(t) for _ in range(dist.get_world_size())]
         dist.all_gather(allt, t)
-        vals = [float(x.item()) for x in allt]
-        lo, hi = min(range(len(vals)), key=vals.__getitem__), max(range(len(vals)), key=vals.__getitem__)
-        rep = {"min": (lo, vals[lo]), "max": (hi, vals[hi])}
+        self.enabled = self._requested = bool(allt[0][1].item() > 0.5)          # rank 0's controller decides
+        if not was_enabled:
+            return None
+        vals = [float(x[0].item()) for x in allt]
+        order = sorted(range(len(vals)), key=vals.__getitem__)
+        lo, hi = order[0], order[-1]
+        n = min(self.minmax_count, len(vals))
+        rep = {"min": (lo, vals[lo]), "max": (hi, vals[hi]), "fastest": [(r, vals[r]) for r in order[:n]],
+               "slowest": [(r, vals[r]) for r in order[::-1][:n]], "enabled": self.enabled}
         if dist.get_rank() == 0:
             msg = f" straggler report @ {iteration}: fastest rank {lo} {vals[lo] * 1e3:.1f} ms, slowest rank {hi} {vals[hi] * 1e3:.1f} ms"
             if flops_per_step:
                 msg += f" ({flops_per_step / max(vals[hi], 1e-9) / 1e12:.1f} vs {flops_per_step / max(vals[lo], 1e-9) / 1e12:.1f} TFLOP/s)"
+            if n > 1:
+                msg += " | slowest: " + ", ".join(f"{r}:{v * 1e3:.1f}" for r, v in rep["slowest"]) + \
+                       " | fastest: " + ", ".join(f"{r}:{v * 1e3:.1f}" for r, v in rep["fastest"])
             print(msg, flush=True)
         return rep
 

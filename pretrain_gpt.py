@@ -152,7 +152,8 @@ def train_valid_test_datasets_provider(num_samples):
                            path_to_cache=args.data_cache_path, mmap_bin_files=args.mmap_bin_files, mock=args.mock_data,
                            tokenizer=args.tokenizer, reset_position_ids=args.reset_position_ids,
                            reset_attention_mask=args.reset_attention_mask, eod_mask_loss=args.eod_mask_loss,
-                           create_attention_mask=args.create_attention_mask_in_dataloader)
+                           create_attention_mask=args.create_attention_mask_in_dataloader,
+                           object_storage_cache_path=getattr(args, "object_storage_cache_path", None))
     if getattr(args, "sft", False):
         # supervised fine-tuning: --data-path names a JSONL file of conversations; loss on the assistant turns only
         from megatron_lm_b200.data.sft_dataset import TEMPLATES, SFTDataset, default_chat_template

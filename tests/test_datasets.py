@@ -124,3 +124,69 @@ def test_tokenizers(tmp_path):
     args = A()
     build_tokenizer(args)
     assert args.padded_vocab_size == 1024
+
+
+def test_indexed_dataset_from_an_object_store(tmp_path):
+    """``s3://`` prefixes: the index is cached locally once, tokens come through ranged reads served from a chunk
+    cache (reference: tests/unit_tests/data/test_preprocess_data.py object-storage readers with a mock client)."""
+    from megatron_lm_b200.data import object_storage as osu
+    rng = np.random.default_rng(3)
+    docs = [rng.integers(0, 1000, rng.integers(5, 60)) for _ in range(40)]
+    root = tmp_path / "store"
+    (root / "corpora").mkdir(parents=True)
+    _write_corpus(str(root / "corpora" / "wiki"), docs)
+    client = osu.LocalDirectoryClient(str(root))
+    osu.register_client_factory("s3", lambda: client)
+    try:
+        prefix = "s3://corpora/wiki"
+        assert osu.is_object_storage_path(prefix) and not osu.is_object_storage_path("/data/wiki")
+        assert osu.parse_s3_path("s3://corpora/a/b.bin") == ("corpora", "a/b.bin")
+        assert osu.get_object_storage_access("msc://p/x") == "msc"
+        with pytest.raises(ValueError):
+            osu.parse_s3_path("/local/file")
+        assert IndexedDataset.exists(prefix) and not IndexedDataset.exists("s3://corpora/missing")
+        with pytest.raises(ValueError):
+            IndexedDataset(prefix)                                               # no cache configuration
+        cfg = osu.ObjectStorageConfig(path_to_idx_cache=str(tmp_path / "idx_cache"), bin_chunk_nbytes=256)
+        ds = IndexedDataset(prefix, object_storage_config=cfg)
+        assert os.path.isfile(osu.get_index_cache_path(prefix + ".idx", cfg))
+        assert len(ds) == 40
+        before = client.requests
+        for i in range(40):
+            assert np.array_equal(ds[i], docs[i])
+        used = client.requests - before
+        total_bytes = sum(len(d) for d in docs) * 2
+        assert used <= total_bytes // 256 + 2, (used, total_bytes)               # sequential reads: one per chunk
+        assert np.array_equal(ds.get(7, 2, 3), docs[7][2:5])
+        assert all(np.array_equal(a, b) for a, b in zip(ds[3:9], docs[3:9]))       # a slice larger than one chunk
+        # a second open finds the cached index: no download
+        before = client.requests
+        IndexedDataset(prefix, object_storage_config=cfg)
+        assert client.requests == before
+        # the GPT dataset builder reaches the store through its configuration
+        gcfg = GPTDatasetConfig(random_seed=1, sequence_length=8, blend=([prefix], None), split="1,0,0",
+                                tokenizer=NullTokenizer(999), path_to_cache=str(tmp_path / "cache"),
+                                object_storage_cache_path=str(tmp_path / "idx_cache"), mmap_bin_files=False)
+        train, _, _ = BlendedMegatronDatasetBuilder(GPTDataset, [20, None, None], lambda: True, gcfg).build()
+        assert train[0]["tokens"].shape == (8,)
+    finally:
+        osu.register_client_factory("s3", osu._boto3_client)
+
+
+def test_mock_multimodal_dataset():
+    from megatron_lm_b200.data.multimodal_dataset import MockMultimodalDataset, MultimodalDatasetConfig
+    with pytest.raises(ValueError):
+        MultimodalDatasetConfig(sequence_length=16, tokenizer=NullTokenizer(99), mock=True, image_h=8, image_w=8)
+    seen = []
+
+    def prep(sample):
+        seen.append(set(sample))
+        sample["tokens"] = torch.cat([torch.full((2,), -200), sample["tokens"]])      # image placeholder tokens
+        return sample
+    cfg = MultimodalDatasetConfig(random_seed=5, sequence_length=16, tokenizer=NullTokenizer(99), mock=True, image_h=8,
+                                  image_w=12, preprocess_func=prep, split="1,0,0")
+    train, _, _ = BlendedMegatronDatasetBuilder(MockMultimodalDataset, [10, None, None], lambda: True, cfg).build()
+    a, b = train[0], train[0]
+    assert a["image"].shape == (3, 8, 12) and 0 <= float(a["image"].min()) and float(a["image"].max()) < 1
+    assert torch.equal(a["image"], b["image"]) and not torch.equal(a["image"], train[1]["image"])
+    assert a["tokens"].shape == (18,) and "image" in seen[0] and "labels" in seen[0]

@@ -216,6 +216,38 @@ def test_straggler_report_names_the_slow_rank(tmp_path):
     assert rep["max"][0] == 1 and rep["min"][0] == 0 and rep["max"][1] > rep["min"][1]
 
 
+def _toggle_rank(rank, world, out):
+    import json
+    import urllib.request
+    d = StragglerDetector(enabled=False, port=0, minmax_count=2)         # port 0: the system picks a free one
+    log = []
+    d.start(); d.stop()
+    log.append(len(d.times))                                            # disabled: nothing measured
+    log.append(d.report(1))                                             # ... and nothing reported
+    if rank == 0:
+        assert d.port
+        reply = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{d.port}/", timeout=5).read())
+        assert reply == {"straggler_detector_enabled": True}
+    else:
+        assert d.port is None
+    torch.distributed.barrier()
+    log.append(d.enabled)                                               # still off: the flag travels with a report
+    d.report(2)
+    log.append(d.enabled)                                               # on, on every rank
+    d.start(); time.sleep(0.02 * (rank + 1)); d.stop()
+    rep = d.report(3)
+    log.append((rep["slowest"][0][0], len(rep["slowest"]), rep["enabled"]))
+    d.close()
+    torch.save(log, f"{out}.{rank}")
+
+
+def test_straggler_detector_is_toggled_through_its_port(tmp_path):
+    out = str(tmp_path / "t")
+    run_distributed(_toggle_rank, 2, out)
+    for r in range(2):
+        assert torch.load(f"{out}.{r}") == [0, None, False, True, (1, 2, True)]
+
+
 def test_heartbeat_timeout_fires_and_timeouts_persist(tmp_path):
     fired = []
     path = str(tmp_path / "ft_state.json")
