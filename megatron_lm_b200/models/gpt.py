@@ -166,6 +166,11 @@ class GPTModel(nn.Module):
                                                      init_method=config.init_method, bias=False,
                                                      skip_weight_param_allocation=skip)
             self.output_layer.fp8_eligible = False          # the vocabulary projection stays in 16 bits
+            if config.defer_embedding_wgrad_compute and self.output_layer.weight is not None and not config.mtp_num_layers:
+                # the pipelined schedule runs this layer's weight-gradient GEMM when the pipeline drains
+                self.output_layer.weight.defer_wgrad = True
+                # several microbatches' gradients then arrive during the last one: no early release of its bucket
+                self.output_layer.weight.expected_grad_signals = 2
         self._setup_shared_embeddings()
         if post_process and config.mtp_num_layers:
             # the prediction heads reuse the embedding and the output layer: several gradients per microbatch

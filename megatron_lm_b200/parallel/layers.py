@@ -73,6 +73,36 @@ def _init_sharded(weight: torch.Tensor, full_shape, partition_dim: int, init_met
         init_method(weight)
 
 
+# Weight gradients whose GEMM was put off (``weight.defer_wgrad``): (weight, dy [tokens, N], input [tokens, K]).
+# The output layer of the last pipeline stage uses this with ``defer_embedding_wgrad_compute``: its data gradient
+# goes upstream at once, the large vocabulary-sized weight-gradient product runs when the pipeline drains
+# (reference: megatron/core/utils.py drain_embedding_wgrad_compute, tensor_parallel/layers.py:480-500).
+_DEFERRED_WGRADS: list = []
+
+
+def _defer_or_compute_wgrad(weight, dy2, t2):
+    if getattr(weight, "defer_wgrad", False):
+        _DEFERRED_WGRADS.append((weight, dy2.detach(), t2.detach()))
+        return None
+    if t2.is_cuda:
+        return weight_grad(weight, dy2, t2)
+    return deliver(weight, dy2.float().t() @ t2.float())
+
+
+def drain_deferred_wgrads(keep: int = 0) -> int:
+    """Run the postponed weight-gradient products, oldest first, until at most ``keep`` remain.  The result lands in
+    the parameter's gradient buffer (or is added to ``.grad`` when there is none).  Returns how many ran."""
+    ran = 0
+    while len(_DEFERRED_WGRADS) > keep:
+        weight, dy2, t2 = _DEFERRED_WGRADS.pop(0)
+        with torch.no_grad():
+            g = weight_grad(weight, dy2, t2) if t2.is_cuda else deliver(weight, dy2.float().t() @ t2.float())
+        if g is not None:
+            weight.grad = g if weight.grad is None else weight.grad + g
+        ran += 1
+    return ran
+
+
 class _TPLinear(torch.autograd.Function):
     """y = f(x) W^T with optional input all-gather (sequence parallel), output
     reduce-scatter / all-reduce, and all-reduce of the data gradient.
@@ -162,10 +192,7 @@ class _TPLinear(torch.autograd.Function):
         gw = None
         if weight.requires_grad:
             t2 = _as2d(total) if total.is_cuda else total.reshape(-1, total.shape[-1])
-            if total.is_cuda:
-                gw = weight_grad(weight, dy2, t2)
-            else:
-                gw = deliver(weight, dy2.float().t() @ t2.float())
+            gw = _defer_or_compute_wgrad(weight, dy2, t2)
         gb = None
         if ctx.bias is not None and ctx.bias.requires_grad:
             gb = deliver(ctx.bias, column_sum(dy2))
@@ -185,7 +212,7 @@ class _TPLinear(torch.autograd.Function):
             if ctx.needs_input_grad[0]:
                 dx = fused.gemm_rs(dy2, weight, b_mn=True).view(ctx.x_shape)
             if weight.requires_grad:
-                gw = weight_grad(weight, dy2, saved)
+                gw = _defer_or_compute_wgrad(weight, dy2, saved)
             if ctx.bias is not None and ctx.bias.requires_grad:
                 gb = deliver(ctx.bias, column_sum(dy2))
         else:

@@ -383,6 +383,12 @@ def forward_backward_pipelining(*, forward_step_func, data_iterator, model, num_
             if bwd_count[c] == num_microbatches:
                 exit_no_sync()
             grad_in = backward_step(tensor_in_f, out, tensor_in, config)
+            if config.defer_embedding_wgrad_compute:
+                # postponed output-layer weight gradients: all of them once this chunk's last backward pass is done
+                # (before its gradients are reduced), otherwise only what exceeds the deferral limit
+                from .layers import drain_deferred_wgrads
+                done = bwd_count[c] == num_microbatches
+                drain_deferred_wgrads(0 if done else (config.wgrad_deferral_limit or num_microbatches))
             if bwd_count[c] == num_microbatches:
                 # this chunk's gradients are complete: launch whatever part of its data-parallel reduction the
                 # per-bucket triggers have not started yet, so it overlaps the other chunks' remaining backward

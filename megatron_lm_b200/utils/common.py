@@ -129,3 +129,11 @@ def ceil_div(a: int, b: int) -> int:
 
 def get_model_config(model):
     return unwrap_model(model).config
+
+
+def drain_embedding_wgrad_compute(config=None, *_unused, keep: int = 0) -> int:
+    """Run the output layer's postponed weight-gradient products (``defer_embedding_wgrad_compute``); the pipelined
+    schedule calls this by itself, a hand-written loop calls it before the gradients are reduced
+    (reference: megatron/core/utils.py drain_embedding_wgrad_compute)."""
+    from ..parallel.layers import drain_deferred_wgrads
+    return drain_deferred_wgrads(keep)

@@ -17,6 +17,10 @@ def _make_cfg(tp, pp, vpp, sp, kind):
         # stage outputs are dropped right after they are sent; backward runs from their grad_fn alone
         kind = "llama"
         kw.update(deallocate_pipeline_outputs=True)
+    if kind in ("llama-defer", "gpt-defer"):
+        # the output layer's weight-gradient GEMMs wait for the end of the pipeline (at most 2 queued at a time)
+        kind = kind.split("-")[0]
+        kw.update(defer_embedding_wgrad_compute=True, wgrad_deferral_limit=2)
     if kind == "moe":
         # a large balance-loss coefficient: a wrong scale of its gradient on an early stage moves the trajectory
         kw.update(normalization="RMSNorm", gated_linear_unit=True, activation_func="silu", add_bias_linear=False,
@@ -38,11 +42,12 @@ def _run(rank, world, tp, pp, vpp, sp, dist_opt, kind, out_path):
     state.initialize_model_parallel(tensor_model_parallel_size=tp, pipeline_model_parallel_size=pp,
                                     virtual_pipeline_model_parallel_size=vpp)
     cfg = _make_cfg(tp, pp, vpp, sp, kind)
-    tied = kind == "gpt"
+    tied = kind.startswith("gpt")
 
     def provider(pre_process=True, post_process=True, vp_stage=None):
         m = GPTModel(cfg, V, S, pre_process=pre_process, post_process=post_process, vp_stage=vp_stage,
-                     position_embedding_type="rope" if kind in ("llama", "moe", "llama-dealloc") else "learned_absolute",
+                     position_embedding_type="rope" if kind in ("llama", "moe", "llama-dealloc", "llama-defer")
+                     else "learned_absolute",
                      share_embeddings_and_output_weights=tied)
         reinit_by_global_name(m, cfg)
         if tied and post_process and not pre_process:
@@ -132,6 +137,13 @@ def test_interleaved_pipeline_matches(tmp_path, baseline):
 
 def test_interleaved_pipeline_with_deallocated_outputs(tmp_path, baseline):
     _close(_trajectory(tmp_path, 2, pp=2, vpp=2, kind="llama-dealloc"), baseline["llama"])
+
+
+@pytest.mark.parametrize("kind,vpp", [("llama", None), ("gpt", None), ("llama", 2)])
+def test_deferred_output_layer_weight_gradient_matches(tmp_path, baseline, kind, vpp):
+    from megatron_lm_b200.parallel import layers
+    _close(_trajectory(tmp_path, 2, pp=2, vpp=vpp, kind=kind + "-defer"), baseline[kind])
+    assert not layers._DEFERRED_WGRADS
 
 
 def test_pipeline_parallel_moe_aux_loss_scale(tmp_path):
