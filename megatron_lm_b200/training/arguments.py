@@ -343,7 +343,6 @@ UNUSED_FLAGS = {
     "replication_jump": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
     "replication_factor": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
     "data_args_path": (_R, "give the data paths on the command line"), "per_split_data_args_path": (_R, "give the data paths on the command line"),
-    "moe_use_upcycling": (_R, "upcycle offline with models.upcycling"), "moe_upcycling_granularity": (_W, "upcycle offline with models.upcycling"),
     "heterogeneous_layers_config_path": (_R, "build heterogeneous models through models.heterogeneous"),
     "heterogeneous_layers_config_encoded_json": (_R, "build heterogeneous models through models.heterogeneous"),
 }

@@ -25,7 +25,7 @@ from ..parallel import state
 from ..parallel.random import model_parallel_cuda_manual_seed
 from ..utils.timers import Timers
 from . import checkpointing
-from .arguments import (core_transformer_config_from_args, ddp_config_from_args, optimizer_config_from_args,
+from .arguments import (core_transformer_config_from_args, ddp_config_from_args, get_args, optimizer_config_from_args,
                         parse_args, set_args, validate_args)
 from .flops import flops_from_config
 from .resilience import DistributedSignalHandler, RerunStateMachine, StragglerDetector
@@ -262,6 +262,36 @@ def _maybe_host_fault(args, iteration: int, attempt: int) -> None:
         raise RuntimeError(f"injected host fault on rank {r} after iteration {it}")
 
 
+def _upcycle_from_dense(args, model, optimizer, model_provider, config):
+    """--moe-use-upcycling: ``--load`` names a dense checkpoint.  A dense model of the same layout is built and
+    loaded, its weights are spread over the experts, and the run starts at iteration 0 from the upcycled model
+    (saved at once when ``--save`` is set).  Reference: megatron/training/training.py (moe_use_upcycling branch),
+    core/transformer/moe/upcycling_utils.py ``load_and_upcycle_model``."""
+    from ..models.upcycling import dense_args_for_upcycling, upcycle_model
+    if args.load is None:
+        raise SystemExit("--moe-use-upcycling needs --load <dense checkpoint>")
+    if len(model) != 1:
+        raise NotImplementedError("upcycling with interleaved pipeline stages")
+    dargs = dense_args_for_upcycling(args)
+    dcfg = core_transformer_config_from_args(dargs)
+    saved = get_args()
+    set_args(dargs)
+    try:
+        dense = get_model(lambda **kw: model_provider(config=dcfg, **kw), dcfg, None, wrap_with_ddp=False)
+    finally:
+        set_args(saved)
+    ld = argparse_namespace_copy(dargs, finetune=True, no_load_optim=True, no_load_rng=True)
+    checkpointing.load_checkpoint(dense, None, None, ld, load_dir=args.load)
+    rep = upcycle_model(checkpointing._unwrap(dense[0]), checkpointing._unwrap(model[0]),
+                        granularity=getattr(args, "moe_upcycling_granularity", 1), seed=args.seed)
+    n = sum(1 for v in rep.values() if v not in ("copied", "kept", "router init"))
+    print_rank_0(f"upcycled the dense checkpoint {args.load}: {n} expert tensors filled from dense MLPs, "
+                 f"{sum(1 for v in rep.values() if v == 'copied')} tensors copied")
+    if optimizer is not None:
+        optimizer.reload_model_params()
+    del dense
+
+
 def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Callable, forward_step_func: Callable,
              extra_args_provider=None, args_defaults=None, argv=None, inprocess_call_wrapper=None):
     """Full program.  ``model_provider(pre_process, post_process, vp_stage=None)`` builds a model chunk;
@@ -312,7 +342,13 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         from ..ops.tp_fused import attach_fused_tp
         attach_fused_tp(model, config, args.seq_length, args.micro_batch_size)
     iteration, flops_so_far = 0, 0.0
-    if args.load is not None:
+    if getattr(args, "moe_use_upcycling", False):
+        # --load names the dense checkpoint; the mixture-of-experts run it seeds must start in a fresh --save
+        if args.save and os.path.isfile(checkpointing.get_checkpoint_tracker_filename(args.save)):
+            raise SystemExit(f"--moe-use-upcycling: {args.save} already holds a checkpoint; resume from it without "
+                             "the flag")
+        _upcycle_from_dense(args, model, optimizer, model_provider, config)
+    elif args.load is not None:
         iteration, flops_so_far = checkpointing.load_checkpoint(model, optimizer, scheduler, args)
         args.consumed_train_samples = iteration * args.global_batch_size
     if iteration == 0 and getattr(args, "pretrained_checkpoint", None):

@@ -302,7 +302,7 @@ def test_unused_flags_warn_or_refuse():
         validate_args(args)
     assert not [x for x in w if "has no effect here" in str(x.message)]
     # a flag that would change the layout or the numerics stops the run
-    for extra in (["--use-legacy-models"], ["--openai-gelu"], ["--moe-use-upcycling"]):
+    for extra in (["--use-legacy-models"], ["--openai-gelu"], ["--lazy-mpu-init", "true"]):
         args = parse_args(argv=base + extra)
         args.world_size, args.rank = 1, 0
         with pytest.raises(ValueError, match="not supported"):

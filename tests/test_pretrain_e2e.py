@@ -388,3 +388,30 @@ def test_vision_dino_program_trains_with_momentum_teacher_and_knn_monitor():
     assert sorted(rows) == list(range(1, 13))
     assert all(0 < v[1] < 6 for v in rows.values())                    # bounded by ln(64) = 4.16 at uniform outputs
     assert re.search(r"validation loss at iteration 12 .*knn_acc_10 value: [0-9.E+-]+", out)
+
+
+def test_moe_run_upcycled_from_a_dense_checkpoint(tmp_path):
+    """--moe-use-upcycling: the mixture-of-experts run starts as the dense model (identical experts, top-k weights
+    summing to one: the same validation loss), then trains and saves a checkpoint that resumes as a plain MoE run."""
+    dense_dir, moe_dir = str(tmp_path / "dense"), str(tmp_path / "moe")
+    common = ["--swiglu", "--disable-bias-linear", "--normalization", "RMSNorm", "--ffn-hidden-size", "64",
+              "--untie-embeddings-and-output-weights", "--attention-dropout", "0", "--hidden-dropout", "0"]
+
+    def val(out, it):
+        m = re.search(rf"validation loss at iteration {it} .*?lm loss value: ([0-9.E+-]+)", out)
+        return float(m.group(1))
+    dense_out = _run(common + ["--save", dense_dir, "--train-iters", "8", "--save-interval", "8", "--eval-interval", "8"])
+    moe_flags = ["--num-experts", "4", "--moe-router-topk", "2", "--moe-aux-loss-coeff", "0", "--moe-grouped-gemm"]
+    out = _run(common + moe_flags + ["--moe-use-upcycling", "--load", dense_dir, "--save", moe_dir, "--train-iters", "4",
+                                     "--save-interval", "4", "--lr", "1e-9", "--min-lr", "1e-10", "--eval-interval", "1"])
+    assert "upcycled the dense checkpoint" in out and "4 expert tensors" in out
+    assert sorted(_iters(out)) == [1, 2, 3, 4]
+    assert abs(val(out, 1) - val(dense_out, 8)) < 2e-4, (val(out, 1), val(dense_out, 8))
+    again = _run(common + moe_flags + ["--load", moe_dir, "--save", moe_dir, "--train-iters", "4", "--lr", "1e-9",
+                                       "--min-lr", "1e-10", "--eval-interval", "4"])
+    assert "upcycled" not in again
+    refused = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + BASE + common + moe_flags +
+                             ["--moe-use-upcycling", "--load", dense_dir, "--save", moe_dir], capture_output=True,
+                             text=True, timeout=200, cwd=ROOT,
+                             env=dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29619"))
+    assert refused.returncode != 0 and "already holds a checkpoint" in refused.stdout + refused.stderr

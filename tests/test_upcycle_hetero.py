@@ -35,3 +35,40 @@ def test_heterogeneous_layers():
         h = l(h)
     h.sum().backward()
     assert h.shape == x.shape and x.grad is not None
+
+
+def _dense_and_moe(granularity=1, grouped=True):
+    from megatron_lm_b200.models.gpt import GPTModel
+    base = dict(num_layers=2, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+                attention_dropout=0.0, gated_linear_unit=True, activation_func="silu", add_bias_linear=False,
+                normalization="RMSNorm", use_cpu_initialization=True)
+    torch.manual_seed(0)
+    dense = GPTModel(TransformerConfig(**base), 64, 16, parallel_output=False, share_embeddings_and_output_weights=False)
+    moe_cfg = TransformerConfig(**base, num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=64 // granularity,
+                                moe_grouped_gemm=grouped, moe_token_dispatcher_type="allgather")
+    torch.manual_seed(1)
+    moe = GPTModel(moe_cfg, 64, 16, parallel_output=False, share_embeddings_and_output_weights=False)
+    return dense, moe
+
+
+def test_upcycled_model_reproduces_the_dense_model():
+    import pytest
+    from megatron_lm_b200.models.upcycling import upcycle_model
+    ids = torch.randint(0, 64, (2, 16))
+    pos = torch.arange(16).unsqueeze(0).expand(2, 16)
+    for grouped in (True, False):
+        for g in (1, 2):
+            dense, moe = _dense_and_moe(g, grouped)
+            rep = upcycle_model(dense, moe, granularity=g)
+            assert sum(v == "router init" for v in rep.values()) == 2
+            assert not [k for k, v in rep.items() if v == "kept"], rep
+            with torch.no_grad():
+                a, b = dense(ids, pos, None), moe(ids, pos, None)
+            if g == 1:
+                # identical experts, top-k weights that sum to one: the mixture is the dense MLP
+                assert torch.allclose(a, b, atol=1e-5), (grouped, (a - b).abs().max())
+            else:
+                assert torch.isfinite(b).all() and b.shape == a.shape
+    dense, moe = _dense_and_moe(1)
+    with pytest.raises(ValueError):
+        upcycle_model(dense, moe, granularity=3)
