@@ -158,11 +158,19 @@ class DynamicInferenceContext(_ContextBase):
     request that is decoding."""
 
     def __init__(self, max_requests: int, max_sequence_length: int, chunk_size: int = 256,
-                 buffer_size_gb: Optional[float] = None, num_chunks: Optional[int] = None):
+                 buffer_size_gb: Optional[float] = None, num_chunks: Optional[int] = None, num_layers: int = 1,
+                 buffer_guaranteed_fraction: float = 0.0, max_tokens: Optional[int] = None):
+        """``buffer_size_gb`` is the whole cache (keys and values of all ``num_layers`` layers).
+        ``buffer_guaranteed_fraction`` of the chunks is kept out of reach of admissions, so that requests already
+        running can keep growing; ``max_tokens`` caps the tokens of one step (prompts of new requests + one token per
+        running request).  Reference: megatron/core/inference/contexts/dynamic_context.py:60-220."""
         self.max_requests, self.max_len, self.chunk = max_requests, max_sequence_length, chunk_size
         self.max_chunks = (max_sequence_length + chunk_size - 1) // chunk_size
         self.num_chunks = num_chunks
         self.buffer_gb = buffer_size_gb
+        self.num_layers = max(int(num_layers), 1)
+        self.guaranteed_fraction = float(buffer_guaranteed_fraction)
+        self.max_tokens = max_tokens
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
         self.alloc: Optional[ChunkAllocator] = None
@@ -179,7 +187,7 @@ class DynamicInferenceContext(_ContextBase):
         if self.alloc is None:
             if self.num_chunks is None:
                 if self.buffer_gb is not None:
-                    per_chunk = 2 * self.chunk * ng * d * torch.empty((), dtype=dtype).element_size()
+                    per_chunk = 2 * self.chunk * ng * d * torch.empty((), dtype=dtype).element_size() * self.num_layers
                     self.num_chunks = max(int(self.buffer_gb * 2 ** 30 // max(per_chunk, 1)), self.max_chunks)
                 else:
                     self.num_chunks = self.max_requests * self.max_chunks
@@ -196,11 +204,20 @@ class DynamicInferenceContext(_ContextBase):
         need = (slot_len + extra + self.chunk - 1) // self.chunk
         return need - have
 
-    def can_admit(self, prompt_len: int, reserve: int = 0) -> bool:
+    def total_chunks(self) -> int:
+        return self.num_chunks or self.max_requests * self.max_chunks
+
+    def free_chunks(self) -> int:
+        return self.alloc.available if self.alloc is not None else self.total_chunks()
+
+    def can_admit(self, prompt_len: int, reserve: int = 0, others_active: bool = False, committed: int = 0) -> bool:
+        """Room for a new request?  ``committed`` chunks are already promised to other requests of the same step.
+        While other requests run, an admission must leave the guaranteed part of the buffer free for their growth;
+        a lone request may use everything."""
         if not self.free_slots:
             return False
-        free = self.alloc.available if self.alloc is not None else (self.num_chunks or self.max_requests * self.max_chunks)
-        return self.chunks_needed(0, prompt_len + reserve) <= free
+        keep = int(self.guaranteed_fraction * self.total_chunks()) if others_active else 0
+        return self.chunks_needed(0, prompt_len + reserve) + keep + committed <= self.free_chunks()
 
     def admit(self) -> int:
         slot = self.free_slots.pop()
@@ -422,10 +439,32 @@ class DynamicInferenceEngine:
 
     def __init__(self, model, max_requests: int = 16, max_sequence_length: int = 2048, chunk_size: int = 256,
                  buffer_size_gb: Optional[float] = None, tokenizer=None, eod_id: Optional[int] = None,
-                 num_chunks: Optional[int] = None):
+                 num_chunks: Optional[int] = None, buffer_guaranteed_fraction: float = 0.0,
+                 buffer_overflow_factor: Optional[float] = None, max_requests_override: Optional[int] = None,
+                 max_tokens_override: Optional[int] = None):
+        """``buffer_overflow_factor`` f sizes the request slots at f x (requests of maximal length that fit the
+        buffer): more short requests than the worst case allows; ``max_requests_override`` / ``max_tokens_override``
+        set the slot count and the per-step token cap outright.  When the cache runs out under running requests the
+        youngest one is put back in the queue (its chunks are freed, its tokens so far become its prompt)."""
         self.model, self.tokenizer = model, tokenizer
-        self.context = DynamicInferenceContext(max_requests, max_sequence_length, chunk_size, buffer_size_gb, num_chunks)
+        cfg = getattr(model, "config", None)
+        layers = getattr(cfg, "num_layers", 1) or 1
+        if buffer_overflow_factor is not None and (num_chunks is not None or buffer_size_gb is not None) and cfg is not None:
+            chunks = num_chunks
+            if chunks is None:
+                ng = (cfg.num_query_groups or cfg.num_attention_heads) // max(getattr(cfg, "tensor_model_parallel_size", 1), 1)
+                d = cfg.kv_channels or cfg.hidden_size // cfg.num_attention_heads
+                elem = torch.empty((), dtype=cfg.params_dtype).element_size()
+                chunks = int(buffer_size_gb * 2 ** 30 // max(2 * chunk_size * ng * d * elem * layers, 1))
+            per_request = (max_sequence_length + chunk_size - 1) // chunk_size
+            max_requests = max(1, int(buffer_overflow_factor * chunks / per_request))
+        if max_requests_override is not None:
+            max_requests = int(max_requests_override)
+        self.context = DynamicInferenceContext(max_requests, max_sequence_length, chunk_size, buffer_size_gb, num_chunks,
+                                               num_layers=layers, buffer_guaranteed_fraction=buffer_guaranteed_fraction,
+                                               max_tokens=max_tokens_override)
         self.scheduler = Scheduler(max_requests)
+        self.preemptions = 0
         self.eod = eod_id if eod_id is not None else (tokenizer.eod if tokenizer is not None else None)
         self.max_len = max_sequence_length
 
@@ -442,18 +481,34 @@ class DynamicInferenceEngine:
     def step(self, generator=None) -> List[InferenceRequest]:
         sch, ctx = self.scheduler, self.context
         groups, feed, owners = [], [], []
-        for req in sch.active.values():                         # one token each for decoding requests
+        # running requests take one token each; when the cache cannot hold their growth, the youngest goes back
+        # to the head of the queue and is recomputed later
+        while len(sch.active) > 1 and \
+                sum(ctx.chunks_needed(ctx.lens[r.slot], 1) for r in sch.active.values()) > ctx.free_chunks():
+            self._preempt(max(sch.active.values(), key=lambda r: r.request_id))
+        for req in sch.active.values():
             groups.append((req.slot, 1))
             feed.append([req.generated_tokens[-1]])
             owners.append(req)
-        while sch.waiting and ctx.can_admit(len(sch.waiting[0].prompt_tokens), 1) and \
-                len(sch.active) < sch.max_batch_size:
+        n_tokens = len(groups)
+        committed = sum(ctx.chunks_needed(ctx.lens[r.slot], 1) for r in sch.active.values())
+        while sch.waiting and len(sch.active) < sch.max_batch_size:
+            nxt = sch.waiting[0]
+            n_new = len(nxt.prompt_tokens) + len(nxt.generated_tokens)
+            if ctx.max_tokens is not None and groups and n_tokens + n_new > ctx.max_tokens:
+                break
+            if not ctx.can_admit(n_new, 1, others_active=bool(sch.active), committed=committed):
+                break
+            committed += ctx.chunks_needed(0, n_new)
             req = sch.waiting.popleft()
             req.slot = ctx.admit()
             sch.activate(req)
-            groups.append((req.slot, len(req.prompt_tokens)))
-            feed.append(req.prompt_tokens)
+            # a request that was put back carries tokens it already produced: they are part of what is recomputed
+            toks = req.prompt_tokens + req.generated_tokens
+            groups.append((req.slot, len(toks)))
+            feed.append(toks)
             owners.append(req)
+            n_tokens += len(toks)
         if not groups:
             return []
         dev = next(self.model.parameters()).device
@@ -481,6 +536,13 @@ class DynamicInferenceEngine:
                     req.generated_text = self.tokenizer.detokenize(req.generated_tokens)
                 finished.append(req)
         return finished
+
+    def _preempt(self, req: InferenceRequest) -> None:
+        self.context.release(req.slot)
+        self.scheduler.active.pop(req.request_id, None)
+        req.slot, req.status = -1, "waiting"
+        self.scheduler.waiting.appendleft(req)
+        self.preemptions += 1
 
     def generate(self, prompts: Sequence, sampling_params: Optional[SamplingParams] = None, generator=None):
         ids = [self.add_request(p, sampling_params) for p in prompts]

@@ -21,7 +21,7 @@ def add_server_args(parser):
     g.add_argument("--port", type=int, default=5000)
     g.add_argument("--host", default="0.0.0.0")
     g.add_argument("--engine", default="static", choices=["static", "dynamic"])
-    g.add_argument("--max-batch-size", type=int, default=8)
+    g.add_argument("--max-batch-size", type=int, default=None, help="defaults to --inference-max-requests")
     g.add_argument("--server-max-sequence-length", type=int, default=None)
     return parser
 
@@ -43,10 +43,22 @@ def build_engine(args, tokenizer=None):
         from ..training import checkpointing
         checkpointing.load_checkpoint([model], None, None, args, strict=False)
     model.eval()
-    max_len = args.server_max_sequence_length or args.max_position_embeddings
-    if args.engine == "dynamic":
-        return DynamicInferenceEngine(model, tokenizer=tokenizer, max_requests=args.max_batch_size,
-                                      max_sequence_length=max_len)
+    # the reference's inference flags size the engines: --inference-max-requests, --inference-max-seq-length,
+    # --inference-dynamic-batching and its buffer settings
+    if args.max_batch_size is None:
+        args.max_batch_size = getattr(args, "inference_max_batch_size", 8)
+    max_len = args.server_max_sequence_length or min(getattr(args, "inference_max_seq_length", 1 << 30),
+                                                     args.max_position_embeddings)
+    if args.engine == "dynamic" or getattr(args, "inference_dynamic_batching", False):
+        return DynamicInferenceEngine(
+            model, tokenizer=tokenizer, max_requests=args.max_batch_size, max_sequence_length=max_len,
+            chunk_size=getattr(args, "inference_dynamic_batching_chunk_size", 256),
+            buffer_size_gb=getattr(args, "inference_dynamic_batching_buffer_size_gb", None)
+            if torch.cuda.is_available() else None,
+            buffer_guaranteed_fraction=getattr(args, "inference_dynamic_batching_buffer_guaranteed_fraction", 0.0) or 0.0,
+            buffer_overflow_factor=getattr(args, "inference_dynamic_batching_buffer_overflow_factor", None),
+            max_requests_override=getattr(args, "inference_dynamic_batching_max_requests_override", None),
+            max_tokens_override=getattr(args, "inference_dynamic_batching_max_tokens_override", None))
     return StaticInferenceEngine(model, tokenizer=tokenizer, max_batch_size=args.max_batch_size,
                                  max_sequence_length=max_len)
 

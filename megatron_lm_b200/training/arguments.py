@@ -269,15 +269,6 @@ UNUSED_FLAGS = {
     "max_tokens_to_oom": (_W, "the engines size their buffers from the context they are given"),
     "output_bert_embeddings": (_R, "BERT embedding extraction is not built"),
     "bert_embedder_type": (_W, "only used with --output-bert-embeddings"),
-    "inference_max_batch_size": (_W, "pass max_requests to the engine"),
-    "inference_max_seq_length": (_W, "pass max_sequence_length to the engine"),
-    "inference_dynamic_batching": (_W, "choose DynamicInferenceEngine in the serving program"),
-    "inference_dynamic_batching_buffer_size_gb": (_W, "pass buffer_size_gb to DynamicInferenceContext"),
-    "inference_dynamic_batching_chunk_size": (_W, "pass chunk_size_tokens to DynamicInferenceContext"),
-    "inference_dynamic_batching_buffer_guaranteed_fraction": (_W, "pass it to DynamicInferenceContext"),
-    "inference_dynamic_batching_buffer_overflow_factor": (_W, "pass it to DynamicInferenceContext"),
-    "inference_dynamic_batching_max_requests_override": (_W, "pass it to DynamicInferenceContext"),
-    "inference_dynamic_batching_max_tokens_override": (_W, "pass it to DynamicInferenceContext"),
     "inference_dynamic_batching_num_cuda_graphs": (_W, "the dynamic engine captures no graphs"),
     # Retro / biencoder / vision programs that are not (fully) built
     "retro_add_retriever": (_W, "pretrain_retro.py always builds the retriever"),

@@ -158,3 +158,51 @@ def test_vlm_engine_generates_from_an_image_and_a_prompt():
             logits = m(images, torch.tensor([ids]))
             ids.append(int(logits[0, -1].float().argmax()))
     assert out[0].generated_tokens == ids[3:]
+
+
+def test_dynamic_engine_preempts_when_the_cache_runs_out_and_recomputes():
+    """Three requests that together need twice the cache: the youngest is put back in the queue, recomputed later,
+    and every request still produces the tokens of an unconstrained run."""
+    model = _model()
+    prompts = [[5, 9, 2, 33, 7, 1], [11, 4, 6, 8, 3, 2], [7, 7, 9, 1, 2, 3]]
+    sp = SamplingParams(top_k=1, num_tokens_to_generate=10)
+    roomy = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=32, chunk_size=4)
+    want = [r.generated_tokens for r in roomy.generate(prompts, sp)]
+    assert roomy.preemptions == 0
+    tight = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=32, chunk_size=4, num_chunks=6)
+    got = tight.generate(prompts, sp)
+    assert tight.preemptions > 0
+    assert [r.generated_tokens for r in got] == want
+    assert tight.context.alloc.available == 6 and len(tight.context.free_slots) == 4
+
+
+def test_dynamic_engine_admission_limits():
+    model = _model()
+    prompts = [[5, 9, 2, 33, 7, 1], [11, 4, 6, 8, 3, 2], [7, 7, 9, 1, 2, 3]]
+    sp = SamplingParams(top_k=1, num_tokens_to_generate=3)
+    # a token cap per step: the second prompt (6 tokens) does not fit beside the first within 8 tokens
+    eng = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=32, chunk_size=4, max_tokens_override=8)
+    for p in prompts:
+        eng.add_request(p, sp)
+    eng.step()
+    assert len(eng.scheduler.active) == 1 and len(eng.scheduler.waiting) == 2
+    eng.step()                                          # 1 decode token + 6 prompt tokens = 7 <= 8
+    assert len(eng.scheduler.active) == 2
+    while eng.has_unfinished_requests():
+        eng.step()
+    ref = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=32, chunk_size=4).generate(prompts, sp)
+    assert [eng.scheduler.completed[i].generated_tokens for i in range(3)] == [r.generated_tokens for r in ref]
+    # guaranteed fraction: with half of 8 chunks kept for running requests, a second request (2 chunks + reserve)
+    # is admitted only while 4 chunks stay free
+    eng = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=32, chunk_size=4, num_chunks=8,
+                                 buffer_guaranteed_fraction=0.5)
+    for p in prompts:
+        eng.add_request(p, sp)
+    eng.step()
+    assert len(eng.scheduler.active) == 2 and len(eng.scheduler.waiting) == 1      # 2 + 2 chunks used, 4 kept
+    # slot count from the overflow factor: 16 chunks, 8 per request of maximal length, factor 2 -> 4 slots
+    eng = DynamicInferenceEngine(model, max_requests=1, max_sequence_length=32, chunk_size=4, num_chunks=16,
+                                 buffer_overflow_factor=2.0)
+    assert eng.context.max_requests == 4 and eng.scheduler.max_batch_size == 4
+    eng = DynamicInferenceEngine(model, max_requests=1, max_sequence_length=32, chunk_size=4, max_requests_override=3)
+    assert eng.context.max_requests == 3
