@@ -147,6 +147,103 @@ def core_to_hf_mixtral(sd: Dict[str, torch.Tensor], num_layers: int, num_heads: 
 # convolution of three, [x | B | C]: changing the tensor-parallel size has to re-cut every segment, not the whole
 # matrix (reference: tools/checkpoint/hybrid_conversion.py:60-190).  Heads, groups and inner channels are split
 # evenly; the state size is not split.
+def _hf_llava_parts(hf: Dict[str, torch.Tensor]):
+    """Prefixes of the three parts in either Hugging Face layout: checkpoint files of the original release
+    (``vision_tower.`` / ``multi_modal_projector.`` / ``language_model.model.`` + ``language_model.lm_head``) or the
+    in-memory names of newer library versions (everything under ``model.``, ``lm_head`` at the top)."""
+    if any(k.startswith("model.vision_tower.") for k in hf):
+        return "model.vision_tower.vision_model.", "model.multi_modal_projector.", "model.language_model.", "lm_head.weight"
+    return "vision_tower.vision_model.", "multi_modal_projector.", "language_model.model.", "language_model.lm_head.weight"
+
+
+def hf_llava_to_core(hf: Dict[str, torch.Tensor], *, num_layers: int, num_heads: int, num_query_groups: int,
+                     vision_layers: int, vision_heads: int, head_dim: Optional[int] = None) -> Dict[str, torch.Tensor]:
+    """Hugging Face LLaVA (CLIP vision tower + two-layer projector + Llama) -> ``LLaVAModel`` names.
+    ``vision_layers`` is the number of encoder layers the core model keeps: LLaVA reads the features of the
+    second-to-last CLIP layer, so the last one (and the tower's post-layernorm) is dropped.  The patch convolution
+    becomes the linear map on unfolded patches.  Reference: tools/checkpoint/loader_llava.py,
+    examples/multimodal/model_converter/clip_converter.py."""
+    vp, pp, lp, head = _hf_llava_parts(hf)
+    sd: Dict[str, torch.Tensor] = {}
+    conv = hf[vp + "embeddings.patch_embedding.weight"]                      # [hv, 3, p, p]
+    sd["vision_model.conv1.proj.weight"] = conv.reshape(conv.shape[0], -1)
+    sd["vision_model.class_token"] = hf[vp + "embeddings.class_embedding"].reshape(1, 1, -1)
+    sd["vision_model.position_embeddings.weight"] = hf[vp + "embeddings.position_embedding.weight"]
+    pre = "pre_layrnorm." if vp + "pre_layrnorm.weight" in hf else "pre_layernorm."   # the library's spelling
+    sd["vision_model.ln_pre.weight"], sd["vision_model.ln_pre.bias"] = hf[vp + pre + "weight"], hf[vp + pre + "bias"]
+    hv = conv.shape[0]
+    hnv = hv // vision_heads
+    for i in range(vision_layers):
+        s_, d = f"{vp}encoder.layers.{i}.", f"vision_model.decoder.layers.{i}."
+        for kind in ("weight", "bias"):
+            q, k, v = (hf[s_ + f"self_attn.{n}_proj.{kind}"] for n in "qkv")
+            if kind == "bias":
+                sd[d + "self_attention.linear_qkv.bias"] = _qkv_to_core(q.unsqueeze(1), k.unsqueeze(1), v.unsqueeze(1),
+                                                                         vision_heads, vision_heads, hnv).squeeze(1)
+            else:
+                sd[d + "self_attention.linear_qkv.weight"] = _qkv_to_core(q, k, v, vision_heads, vision_heads, hnv)
+            sd[d + f"self_attention.linear_proj.{kind}"] = hf[s_ + f"self_attn.out_proj.{kind}"]
+            sd[d + f"input_layernorm.{kind}"] = hf[s_ + f"layer_norm1.{kind}"]
+            sd[d + f"pre_mlp_layernorm.{kind}"] = hf[s_ + f"layer_norm2.{kind}"]
+            sd[d + f"mlp.linear_fc1.{kind}"] = hf[s_ + f"mlp.fc1.{kind}"]
+            sd[d + f"mlp.linear_fc2.{kind}"] = hf[s_ + f"mlp.fc2.{kind}"]
+    for kind in ("weight", "bias"):
+        sd[f"vision_projection.linear_fc1.{kind}"] = hf[pp + f"linear_1.{kind}"]
+        sd[f"vision_projection.linear_fc2.{kind}"] = hf[pp + f"linear_2.{kind}"]
+    llama = {"model." + k[len(lp):]: v for k, v in hf.items() if k.startswith(lp)}
+    llama["lm_head.weight"] = hf.get(head, llama["model.embed_tokens.weight"])
+    for k, v in hf_llama_to_core(llama, num_layers, num_heads, num_query_groups, head_dim).items():
+        sd["language_model." + k] = v
+    return sd
+
+
+def core_to_hf_llava(sd: Dict[str, torch.Tensor], *, num_layers: int, num_heads: int, num_query_groups: int,
+                     vision_layers: int, vision_heads: int, patch_dim: int, head_dim: Optional[int] = None,
+                     in_memory_names: bool = True) -> Dict[str, torch.Tensor]:
+    """``LLaVAModel`` names -> Hugging Face LLaVA.  The CLIP layer that LLaVA never reads and the tower's
+    post-layernorm do not exist in the core model: they are written as an identity-initialised copy of the last
+    kept layer and a unit layernorm, so the file loads into the library's class and computes the same features.
+    Reference: tools/checkpoint/saver_hf_llava.py."""
+    if in_memory_names:
+        vp, pp, lp, head = "model.vision_tower.vision_model.", "model.multi_modal_projector.", "model.language_model.", "lm_head.weight"
+    else:
+        vp, pp, lp, head = "vision_tower.vision_model.", "multi_modal_projector.", "language_model.model.", "language_model.lm_head.weight"
+    hf: Dict[str, torch.Tensor] = {}
+    w = sd["vision_model.conv1.proj.weight"]
+    hv = w.shape[0]
+    hf[vp + "embeddings.patch_embedding.weight"] = w.reshape(hv, 3, patch_dim, patch_dim)
+    hf[vp + "embeddings.class_embedding"] = sd["vision_model.class_token"].reshape(-1)
+    hf[vp + "embeddings.position_embedding.weight"] = sd["vision_model.position_embeddings.weight"]
+    hf[vp + "pre_layrnorm.weight"], hf[vp + "pre_layrnorm.bias"] = sd["vision_model.ln_pre.weight"], sd["vision_model.ln_pre.bias"]
+    hnv = hv // vision_heads
+    for i in range(vision_layers + 1):
+        src = min(i, vision_layers - 1)                                       # the extra layer repeats the last one
+        s_, d = f"vision_model.decoder.layers.{src}.", f"{vp}encoder.layers.{i}."
+        q, k, v = _qkv_from_core(sd[s_ + "self_attention.linear_qkv.weight"], vision_heads, vision_heads, hnv)
+        qb, kb, vb = (t.squeeze(1) for t in _qkv_from_core(sd[s_ + "self_attention.linear_qkv.bias"].unsqueeze(1),
+                                                           vision_heads, vision_heads, hnv))
+        for n, wt, bs in (("q", q, qb), ("k", k, kb), ("v", v, vb)):
+            hf[d + f"self_attn.{n}_proj.weight"], hf[d + f"self_attn.{n}_proj.bias"] = wt, bs
+        for kind in ("weight", "bias"):
+            hf[d + f"self_attn.out_proj.{kind}"] = sd[s_ + f"self_attention.linear_proj.{kind}"]
+            hf[d + f"layer_norm1.{kind}"] = sd[s_ + f"input_layernorm.{kind}"]
+            hf[d + f"layer_norm2.{kind}"] = sd[s_ + f"pre_mlp_layernorm.{kind}"]
+            hf[d + f"mlp.fc1.{kind}"] = sd[s_ + f"mlp.linear_fc1.{kind}"]
+            hf[d + f"mlp.fc2.{kind}"] = sd[s_ + f"mlp.linear_fc2.{kind}"]
+    hf[vp + "post_layernorm.weight"] = torch.ones(hv, dtype=w.dtype)
+    hf[vp + "post_layernorm.bias"] = torch.zeros(hv, dtype=w.dtype)
+    for kind in ("weight", "bias"):
+        hf[pp + f"linear_1.{kind}"] = sd[f"vision_projection.linear_fc1.{kind}"]
+        hf[pp + f"linear_2.{kind}"] = sd[f"vision_projection.linear_fc2.{kind}"]
+    lm = {k[len("language_model."):]: v for k, v in sd.items() if k.startswith("language_model.")}
+    for k, v in core_to_hf_llama(lm, num_layers, num_heads, num_query_groups, head_dim).items():
+        if k == "lm_head.weight":
+            hf[head] = v
+        else:
+            hf[lp + k[len("model."):]] = v
+    return hf
+
+
 def _mamba_dims(in_proj_rows_total: int, d_model: int, nheads: int, ngroups: int, d_state: int):
     d_inner = (in_proj_rows_total - 2 * ngroups * d_state - nheads) // 2
     if 2 * d_inner + 2 * ngroups * d_state + nheads != in_proj_rows_total or d_inner % nheads:
@@ -400,8 +497,11 @@ def load_core(load_dir: str):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--model-type", default="GPT")
-    ap.add_argument("--loader", required=True, choices=["llama_hf", "mistral_hf", "mixtral_hf", "core", "legacy"])
-    ap.add_argument("--saver", required=True, choices=["core", "legacy", "llama_hf", "mixtral_hf"])
+    ap.add_argument("--loader", required=True, choices=["llama_hf", "mistral_hf", "mixtral_hf", "llava_hf", "core", "legacy"])
+    ap.add_argument("--saver", required=True, choices=["core", "legacy", "llama_hf", "mixtral_hf", "llava_hf"])
+    ap.add_argument("--vision-layers", type=int, default=None, help="LLaVA, core -> HF: encoder layers of the vision model")
+    ap.add_argument("--vision-heads", type=int, default=None)
+    ap.add_argument("--patch-dim", type=int, default=14)
     ap.add_argument("--num-attention-heads", type=int, default=None, help="core -> HF: heads (not stored in the tensors)")
     ap.add_argument("--num-query-groups", type=int, default=None)
     ap.add_argument("--mamba-heads", type=int, default=0,
@@ -415,7 +515,21 @@ def main(argv=None):
     ap.add_argument("--target-pipeline-parallel-size", type=int, default=1)
     a = ap.parse_args(argv)
     meta = {}
-    if a.loader.endswith("_hf"):
+    if a.loader == "llava_hf":
+        with open(os.path.join(a.load_dir, "config.json")) as f:
+            c = json.load(f)
+        t, v = c["text_config"], c["vision_config"]
+        keep = v["num_hidden_layers"] + (c.get("vision_feature_layer", -2) + 1)       # -2: all but the last layer
+        meta = {"num_layers": t["num_hidden_layers"], "num_attention_heads": t["num_attention_heads"],
+                "num_query_groups": t.get("num_key_value_heads", t["num_attention_heads"]),
+                "hidden_size": t["hidden_size"], "ffn_hidden_size": t["intermediate_size"],
+                "kv_channels": t.get("head_dim"), "padded_vocab_size": t["vocab_size"],
+                "vision_layers": keep, "vision_heads": v["num_attention_heads"], "patch_dim": v["patch_size"],
+                "img_h": v["image_size"], "img_w": v["image_size"], "image_token_index": c.get("image_token_index")}
+        sd = hf_llava_to_core(load_hf_dir(a.load_dir), num_layers=meta["num_layers"],
+                              num_heads=meta["num_attention_heads"], num_query_groups=meta["num_query_groups"],
+                              vision_layers=keep, vision_heads=meta["vision_heads"], head_dim=meta["kv_channels"])
+    elif a.loader.endswith("_hf"):
         with open(os.path.join(a.load_dir, "config.json")) as f:
             c = json.load(f)
         meta = {"num_layers": c["num_hidden_layers"], "num_attention_heads": c["num_attention_heads"],
@@ -429,10 +543,24 @@ def main(argv=None):
         sd = load_core(a.load_dir)
         if a.loader == "legacy":
             sd = legacy_to_core(sd)
-        meta = {"num_layers": 1 + max(int(m.group(1)) for m in (re.match(r"^decoder\.layers\.(\d+)\.", k) for k in sd) if m)}
+        meta = {"num_layers": 1 + max(int(m.group(1)) for m in
+                                      (re.match(r"^(?:language_model\.)?decoder\.layers\.(\d+)\.", k) for k in sd) if m)}
     if a.num_attention_heads:
         meta["num_attention_heads"] = a.num_attention_heads
         meta["num_query_groups"] = a.num_query_groups or a.num_attention_heads
+    if a.saver == "llava_hf":
+        vl = a.vision_layers or 1 + max(int(m.group(1)) for m in
+                                        (re.match(r"^vision_model\.decoder\.layers\.(\d+)\.", k) for k in sd) if m)
+        if not (a.vision_heads or meta.get("vision_heads")):
+            raise SystemExit("--saver llava_hf needs --vision-heads (and --num-attention-heads / --num-query-groups)")
+        hf = core_to_hf_llava(sd, num_layers=meta["num_layers"], num_heads=meta["num_attention_heads"],
+                              num_query_groups=meta["num_query_groups"], vision_layers=vl,
+                              vision_heads=a.vision_heads or meta["vision_heads"],
+                              patch_dim=meta.get("patch_dim", a.patch_dim), head_dim=meta.get("kv_channels"),
+                              in_memory_names=False)
+        os.makedirs(a.save_dir, exist_ok=True)
+        torch.save(hf, os.path.join(a.save_dir, "pytorch_model.bin"))
+        return
     if a.saver in ("llama_hf", "mixtral_hf"):
         to_hf = core_to_hf_mixtral if a.saver == "mixtral_hf" else core_to_hf_llama
         hf = to_hf(sd, meta["num_layers"], meta["num_attention_heads"], meta["num_query_groups"],
@@ -443,6 +571,16 @@ def main(argv=None):
     if a.saver == "legacy":
         sd = core_to_legacy(sd)
         save_core([[sd]], a.save_dir, 0, meta)
+        return
+    if any(k.startswith("vision_model.") for k in sd):
+        # vision-language model: one pipeline stage; the vision tower and the projector have plain (un-gated) MLPs
+        if a.target_pipeline_parallel_size != 1:
+            raise SystemExit("vision-language checkpoints are written for one pipeline stage")
+        tp = a.target_tensor_parallel_size
+        lang = {k: v for k, v in sd.items() if k.startswith("language_model.")}
+        rest = {k: v for k, v in sd.items() if not k.startswith("language_model.")}
+        shards = [dict(x, **y) for x, y in zip(split_for_tp(lang, tp, True), split_for_tp(rest, tp, False))]
+        save_core([shards], a.save_dir, 0, meta)
         return
     stages = split_for_pp(sd, a.target_pipeline_parallel_size, meta["num_layers"])
     if a.mamba_heads:

@@ -145,3 +145,79 @@ def test_hf_mixtral_round_trip_and_logits(tmp_path):
         ours = model(tokens).transpose(0, 1) if model(tokens).shape[0] == 16 else model(tokens)
         ref = hf_model(tokens).logits
     assert torch.allclose(ours.float(), ref.float(), atol=2e-4, rtol=1e-3), (ours - ref).abs().max()
+
+
+def test_hf_llava_round_trip_and_logits(tmp_path):
+    """HF LLaVA (CLIP tower, second-to-last layer features without the class token, two-layer projector, Llama) ->
+    core ``LLaVAModel`` reproduces the library's logits; core -> HF -> core is the identity; the command line reads a
+    Hugging Face directory and writes tensor-parallel core shards."""
+    import json
+    import pytest
+    import torch
+    transformers = pytest.importorskip("transformers")
+    from megatron_lm_b200.checkpoint import convert
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.multimodal import LLaVAModel
+    torch.manual_seed(0)
+    v = transformers.CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=2,
+                                      image_size=28, patch_size=14, hidden_act="quick_gelu", layer_norm_eps=1e-5)
+    t = transformers.LlamaConfig(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                 num_key_value_heads=2, vocab_size=128, max_position_embeddings=64, rms_norm_eps=1e-5,
+                                 rope_theta=10000.0, tie_word_embeddings=False)
+    hcfg = transformers.LlavaConfig(vision_config=v, text_config=t, image_token_index=127, vision_feature_layer=-2,
+                                    vision_feature_select_strategy="default", projector_hidden_act="gelu",
+                                    image_seq_length=4)
+    hf_model = transformers.LlavaForConditionalGeneration(hcfg).eval()
+    hf_sd = {k: p.detach().clone() for k, p in hf_model.state_dict().items()}
+    kw = dict(num_layers=2, num_heads=4, num_query_groups=2, vision_layers=2, vision_heads=2)
+    core = convert.hf_llava_to_core(hf_sd, **kw)
+    back = convert.core_to_hf_llava(core, patch_dim=14, **kw)
+    again = convert.hf_llava_to_core(back, **kw)
+    assert again.keys() == core.keys() and all(torch.equal(core[k], again[k]) for k in core)
+    for k, p in back.items():                                  # everything LLaVA reads is restored bit for bit
+        if "encoder.layers.2." not in k and "post_layernorm" not in k:
+            assert torch.equal(p, hf_sd[k]), k
+    files = convert.core_to_hf_llava(core, patch_dim=14, in_memory_names=False, **kw)   # names of the released files
+    assert "language_model.model.layers.0.self_attn.q_proj.weight" in files and "language_model.lm_head.weight" in files
+    assert all(torch.equal(core[k], x) for k, x in convert.hf_llava_to_core(files, **kw).items())
+    lcfg = TransformerConfig(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=96,
+                             normalization="RMSNorm", layernorm_epsilon=1e-5, gated_linear_unit=True,
+                             activation_func="silu", add_bias_linear=False, hidden_dropout=0.0, attention_dropout=0.0)
+    vcfg = TransformerConfig(num_layers=2, hidden_size=32, num_attention_heads=2, ffn_hidden_size=64,
+                             activation_func="quick_gelu", layernorm_epsilon=1e-5, hidden_dropout=0.0,
+                             attention_dropout=0.0)
+    pcfg = TransformerConfig(num_layers=1, hidden_size=64, num_attention_heads=4, ffn_hidden_size=64,
+                             activation_func="gelu", hidden_dropout=0.0, attention_dropout=0.0)
+    model = LLaVAModel(lcfg, 128, 64, vcfg, pcfg, drop_vision_class_token=True, img_h=28, img_w=28, patch_dim=14,
+                       language_position_embedding_type="rope", image_token_index=127, parallel_output=False).eval()
+    missing, unexpected = model.load_state_dict(core, strict=False)
+    assert not unexpected and all("_extra_state" in m or "rotary" in m for m in missing), (missing, unexpected)
+    images = torch.randn(2, 3, 28, 28)
+    ids = torch.randint(0, 120, (2, 12))
+    hf_ids = ids.clone()
+    hf_ids[:, 2:6] = 127                                       # the library wants one placeholder per image embedding
+    our_ids = torch.cat([ids[:, :2], torch.full((2, 1), 127), ids[:, 6:]], dim=1)   # ours splices at a single token
+    with torch.no_grad():
+        ref = hf_model(input_ids=hf_ids, pixel_values=images).logits
+        out = model(images, our_ids)
+    out = out if out.shape[0] == 2 else out.transpose(0, 1)
+    assert out.shape == ref.shape
+    assert torch.allclose(out.float(), ref.float(), atol=3e-4, rtol=1e-3), (out - ref).abs().max()
+    # command line: HF directory in, two tensor-parallel core shards out (vision MLP cut as a plain MLP)
+    hf_dir, out_dir = tmp_path / "hf", tmp_path / "core"
+    hf_dir.mkdir()
+    torch.save(files, hf_dir / "pytorch_model.bin")
+    (hf_dir / "config.json").write_text(json.dumps({
+        "text_config": {"num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "hidden_size": 64,
+                        "intermediate_size": 96, "vocab_size": 128},
+        "vision_config": {"num_hidden_layers": 3, "num_attention_heads": 2, "patch_size": 14, "image_size": 28},
+        "vision_feature_layer": -2, "image_token_index": 127}))
+    convert.main(["--loader", "llava_hf", "--saver", "core", "--load-dir", str(hf_dir), "--save-dir", str(out_dir),
+                  "--target-tensor-parallel-size", "2"])
+    r0 = torch.load(out_dir / "release" / "mp_rank_00" / "model_optim_rng.pt", weights_only=False)["model"]
+    r1 = torch.load(out_dir / "release" / "mp_rank_01" / "model_optim_rng.pt", weights_only=False)["model"]
+    fc1 = core["vision_model.decoder.layers.0.mlp.linear_fc1.weight"]
+    assert torch.equal(torch.cat([r0["vision_model.decoder.layers.0.mlp.linear_fc1.weight"],
+                                  r1["vision_model.decoder.layers.0.mlp.linear_fc1.weight"]]), fc1)
+    g = core["language_model.decoder.layers.0.mlp.linear_fc1.weight"]
+    assert torch.equal(r1["language_model.decoder.layers.0.mlp.linear_fc1.weight"], torch.cat([g[48:96], g[144:192]]))
