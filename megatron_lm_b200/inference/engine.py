@@ -79,6 +79,17 @@ def sample_from_logits(logits: torch.Tensor, params: SamplingParams, vocab_size:
 
 # ----------------------------------------------------------------------------- contexts
 class _ContextBase:
+    def ssm_cache(self, layer_number, mixer, like):
+        """Convolution window and state-space state of a Mamba mixer (pure and hybrid Mamba models decode through
+        the same engines as attention models; reference: tools/run_mamba_text_generation_server.py)."""
+        if not getattr(self, "supports_ssm", False):
+            raise NotImplementedError("state-space layers decode with the static engine (one state per batch row); "
+                                      "the paged dynamic context holds attention keys and values only")
+        if not hasattr(self, "_ssm"):
+            from ..models.mamba import MambaInferenceCache
+            self._ssm = MambaInferenceCache()
+        return self._ssm.ssm_cache(layer_number, mixer, like)
+
     def rope_span(self, input_ids) -> Tuple[int, int]:
         """(number of positions the rotary table must cover from ``offset``, offset) for this step."""
         raise NotImplementedError
@@ -86,6 +97,8 @@ class _ContextBase:
 
 class StaticInferenceContext(_ContextBase):
     """Contiguous KV cache [max_batch, max_len, ng, hn] per layer; all sequences advance together."""
+
+    supports_ssm = True
 
     def __init__(self, max_batch_size: int, max_sequence_length: int):
         self.max_batch, self.max_len = max_batch_size, max_sequence_length

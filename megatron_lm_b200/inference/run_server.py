@@ -4,7 +4,9 @@ serves ``PUT /api`` (the request / response format of the reference's server).
     python -m megatron_lm_b200.inference.run_server --load <dir> --num-layers ... --tokenizer-type ... --port 5000
 
 Single GPU (or CPU) serving; tensor-parallel serving would run one such process per rank behind rank 0's HTTP
-front end.  Reference: tools/run_text_generation_server.py (model + checkpoint + ``MegatronServer.run``).
+front end.  ``--server-model-type mamba`` serves pure and hybrid state-space models.
+Reference: tools/run_text_generation_server.py, tools/run_mamba_text_generation_server.py (model + checkpoint +
+``MegatronServer.run``).
 """
 from __future__ import annotations
 
@@ -21,6 +23,8 @@ def add_server_args(parser):
     g.add_argument("--port", type=int, default=5000)
     g.add_argument("--host", default="0.0.0.0")
     g.add_argument("--engine", default="static", choices=["static", "dynamic"])
+    g.add_argument("--server-model-type", default="gpt", choices=["gpt", "mamba"],
+                   help="mamba: pure or hybrid state-space model (--hybrid-override-pattern ...), static engine")
     g.add_argument("--max-batch-size", type=int, default=None, help="defaults to --inference-max-requests")
     g.add_argument("--server-max-sequence-length", type=int, default=None)
     return parser
@@ -33,10 +37,24 @@ def build_engine(args, tokenizer=None):
     vocab = args.padded_vocab_size or getattr(args, "vocab_size", None)
     if vocab is None:
         raise SystemExit("the vocabulary size is unknown: give --vocab-size or a tokenizer")
-    model = GPTModel(cfg, vocab_size=vocab, max_sequence_length=args.max_position_embeddings, parallel_output=False,
-                     share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights,
-                     position_embedding_type=args.position_embedding_type, rotary_percent=args.rotary_percent,
-                     rotary_base=args.rotary_base)
+    if getattr(args, "server_model_type", "gpt") == "mamba":
+        # reference: tools/run_mamba_text_generation_server.py
+        from ..models.mamba import MambaModel
+        if args.engine == "dynamic" or getattr(args, "inference_dynamic_batching", False):
+            raise SystemExit("state-space models are served by the static engine")
+        model = MambaModel(cfg, vocab_size=vocab, max_sequence_length=args.max_position_embeddings, parallel_output=False,
+                           hybrid_attention_ratio=getattr(args, "hybrid_attention_ratio", 0.0),
+                           hybrid_mlp_ratio=getattr(args, "hybrid_mlp_ratio", 0.0),
+                           hybrid_override_pattern=getattr(args, "hybrid_override_pattern", None),
+                           share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights,
+                           position_embedding_type=args.position_embedding_type, rotary_percent=args.rotary_percent,
+                           rotary_base=args.rotary_base, d_state=getattr(args, "mamba_state_dim", 128),
+                           headdim=getattr(args, "mamba_head_dim", 64), ngroups=getattr(args, "mamba_num_groups", 8))
+    else:
+        model = GPTModel(cfg, vocab_size=vocab, max_sequence_length=args.max_position_embeddings, parallel_output=False,
+                         share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights,
+                         position_embedding_type=args.position_embedding_type, rotary_percent=args.rotary_percent,
+                         rotary_base=args.rotary_base)
     if torch.cuda.is_available():
         model = model.cuda()
     if args.load is not None:

@@ -228,11 +228,18 @@ class MambaModel(nn.Module):
 
     def forward(self, input_ids, position_ids=None, attention_mask=None, decoder_input=None, labels=None,
                 inference_context=None):
+        span = None
+        if inference_context is not None and hasattr(inference_context, "rope_span"):
+            # a generation step of an engine: (positions covered, first position) for attention layers of hybrids
+            span = inference_context.rope_span(input_ids)
+            if position_ids is None:
+                position_ids = (torch.arange(input_ids.shape[1], device=input_ids.device) + span[1]).unsqueeze(0)
         if decoder_input is None and self.pre_process:
             decoder_input = self.embedding(input_ids, position_ids)
         rotary = None
         if self.rotary_pos_emb is not None:
-            rotary = self.rotary_pos_emb(input_ids.shape[1], input_ids.device)
+            rotary = self.rotary_pos_emb(input_ids.shape[1], input_ids.device) if span is None else \
+                self.rotary_pos_emb(span[0], input_ids.device, span[1])
         h = self.decoder(decoder_input, rotary=rotary, inference_context=inference_context)
         if not self.post_process:
             return h

@@ -81,3 +81,29 @@ def test_server_program_builds_from_training_flags_and_serves_http():
     bad = cli.request(f"http://127.0.0.1:{port}/api", [], 3)
     assert bad["error"] == 400 and bad["message"]
     srv.httpd.shutdown()
+
+
+def test_server_program_serves_a_hybrid_mamba_model_and_sizes_engines_from_inference_flags():
+    from megatron_lm_b200.inference import DynamicInferenceEngine
+    from megatron_lm_b200.inference.run_server import main
+    from megatron_lm_b200.models.mamba import MambaModel
+    base = ["--num-layers", "3", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
+            "--max-position-embeddings", "32", "--vocab-size", "64", "--untie-embeddings-and-output-weights",
+            "--normalization", "RMSNorm", "--disable-bias-linear", "--use-cpu-initialization"]
+    srv = main(base + ["--server-model-type", "mamba", "--hybrid-override-pattern", "M*-", "--mamba-state-dim", "16",
+                       "--mamba-head-dim", "16", "--mamba-num-groups", "2", "--position-embedding-type", "none",
+                       "--inference-max-requests", "3"], serve=False, tokenizer=_Tok())
+    assert isinstance(srv.engine.model, MambaModel) and srv.engine.max_batch == 3
+    code, resp = srv.handle(json.dumps({"prompts": ["5 9 2 4", "7 7"], "tokens_to_generate": 3, "top_k": 1}).encode())
+    assert code == 200 and resp["text"][0].startswith("5 9 2 4") and len(resp["text"][1].split()) == 7      # generation runs to the longest prompt + 3
+    dyn = main(base[:1] + ["2"] + base[2:] + ["--position-embedding-type", "rope", "--inference-dynamic-batching",
+                                              "--inference-max-requests", "5", "--inference-max-seq-length", "24",
+                                              "--inference-dynamic-batching-chunk-size", "8",
+                                              "--inference-dynamic-batching-buffer-guaranteed-fraction", "0.25",
+                                              "--inference-dynamic-batching-max-tokens-override", "40"],
+               serve=False, tokenizer=_Tok())
+    eng = dyn.engine
+    assert isinstance(eng, DynamicInferenceEngine) and eng.context.max_requests == 5 and eng.max_len == 24
+    assert eng.context.chunk == 8 and eng.context.guaranteed_fraction == 0.25 and eng.context.max_tokens == 40
+    code, resp = dyn.handle(json.dumps({"prompts": ["3 4 5"], "tokens_to_generate": 3, "top_k": 1}).encode())
+    assert code == 200 and len(resp["text"][0].split()) == 6

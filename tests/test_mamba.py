@@ -109,3 +109,27 @@ def test_gated_rmsnorm_gpu(C, G):
         assert torch.allclose(y.grad.float(), y2.grad, atol=tol * 8, rtol=tol * 2)
         assert torch.allclose(z.grad.float(), z2.grad, atol=tol * 8, rtol=tol * 2)
         assert torch.allclose(w.grad.float(), w2.grad, atol=tol * 200, rtol=tol * 4)
+
+
+@pytest.mark.parametrize("pattern,pos", [("M-M", "none"), ("M*-M", "rope"), ("M*M-", "learned_absolute")])
+def test_mamba_and_hybrid_models_generate_through_the_static_engine(pattern, pos):
+    """Prompts of different lengths in one batch: state-space states advance token by token with the forced prompt
+    tokens, attention layers of hybrids use the engine's key / value cache with the right positions."""
+    from megatron_lm_b200.inference import DynamicInferenceEngine, SamplingParams, StaticInferenceEngine
+    torch.manual_seed(0)
+    cfg = TransformerConfig(num_layers=len(pattern), hidden_size=32, num_attention_heads=4, ffn_hidden_size=64,
+                            hidden_dropout=0.0, attention_dropout=0.0, normalization="RMSNorm", add_bias_linear=False)
+    m = MambaModel(cfg, 64, 64, hybrid_override_pattern=pattern, d_state=16, headdim=16, ngroups=2, chunk_size=8,
+                   position_embedding_type=pos).eval()
+    prompts = [[5, 9, 2, 33, 7, 1, 4], [11, 4, 6]]
+    out = StaticInferenceEngine(m, max_batch_size=2, max_sequence_length=32).generate(
+        prompts, SamplingParams(top_k=1, num_tokens_to_generate=6))
+    for req, p in zip(out, prompts):
+        toks = list(p)
+        with torch.no_grad():
+            for _ in range(len(req.generated_tokens)):
+                toks.append(int(m(torch.tensor([toks]))[0, -1].float().argmax()))
+        assert req.generated_tokens == toks[len(p):], (pattern, req.generated_tokens, toks[len(p):])
+    with pytest.raises(NotImplementedError):
+        DynamicInferenceEngine(m, max_requests=2, max_sequence_length=32, chunk_size=4).generate(
+            prompts, SamplingParams(top_k=1, num_tokens_to_generate=2))

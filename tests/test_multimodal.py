@@ -63,3 +63,36 @@ def test_mimo_alignment():
     assert out.shape == (2, 4)
     out.mean().backward()
     assert sub.encoders["e"].l.weight.grad.abs().sum() > 0
+
+
+def test_vlm_generation_program_writes_one_record_per_image(tmp_path):
+    import json
+    import numpy as np
+    from megatron_lm_b200.inference import run_vlm_generation as prog
+
+    class Tok:
+        eod, vocab_size = 0, 64
+        def tokenize(self, s): return [1 + (ord(c) % 60) for c in s.strip()][:6]
+        def detokenize(self, ids): return " ".join(str(i) for i in ids)
+    img_dir = tmp_path / "imgs"
+    img_dir.mkdir()
+    rng = np.random.RandomState(0)
+    np.save(img_dir / "a.npy", rng.randint(0, 255, (40, 30, 3)).astype(np.uint8))      # h, w, c bytes: resized
+    np.save(img_dir / "b.npy", rng.rand(3, 28, 28).astype(np.float32))
+    meta = tmp_path / "q.jsonl"
+    meta.write_text(json.dumps({"image": "b.npy", "question": "what", "question_id": 7}) + "\n")
+    flags = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "48",
+             "--max-position-embeddings", "48", "--vocab-size", "64", "--position-embedding-type", "rope",
+             "--untie-embeddings-and-output-weights", "--img-h", "28", "--img-w", "28", "--patch-dim", "14",
+             "--use-cpu-initialization", "--attention-dropout", "0", "--hidden-dropout", "0",
+             "--input-image-path", str(img_dir), "--out-seq-length", "4"]
+    recs = prog.main(flags + ["--output-path", str(tmp_path / "o.jsonl"), "--prompt", "<image>\nhi"], tokenizer=Tok())
+    lines = [json.loads(l) for l in (tmp_path / "o.jsonl").read_text().splitlines()]
+    assert [r["image"] for r in lines] == ["a.npy", "b.npy"] and lines == recs
+    assert all(1 <= len(r["text"].split()) <= 4 for r in lines)
+    recs = prog.main(flags + ["--output-path", str(tmp_path / "o2.jsonl"), "--input-metadata-path", str(meta)],
+                     tokenizer=Tok())
+    assert len(recs) == 1 and recs[0]["sample_id"] == 7 and recs[0]["prompt"].endswith("what")
+    assert prog.tokenize_prompt("ab<image>cd", Tok(), -200)[2] == -200
+    img = prog.load_image(str(img_dir / "a.npy"), 28, 28)
+    assert img.shape == (3, 28, 28) and -2.5 < float(img.min()) and float(img.max()) < 2.5
