@@ -153,6 +153,30 @@ class ECCheckpointManager:
                     yield owner, i, ss
 
     # ------------------------------------------------------------------ recover
+    # -- state-dict form -------------------------------------------------------------------------------------------
+    def save_state_dict(self, state_dict, iteration: int) -> Dict[str, float]:
+        """Protect every tensor of a (nested, possibly sharded) state dict; its tensor-free structure is kept so
+        that ``recover_state_dict`` can hand the same structure back."""
+        from .tensor_aware import TensorAwareStateDict
+        ta = TensorAwareStateDict.from_state_dict(state_dict, remove_redundant_data=False)
+        tensors = ta.pop_tensors()
+        self.hollow = ta
+        return self.save(tensors, iteration)
+
+    def recover_state_dict(self, lost_ranks: Sequence[int], hollow=None):
+        """All ranks call.  Returns (iteration, state dict of this rank at that iteration).  A replacement rank has
+        no structure of its own: it passes ``hollow``, a ``TensorAwareStateDict`` of a freshly built state dict
+        (after ``pop_tensors``)."""
+        ta = hollow if hollow is not None else getattr(self, "hollow", None)
+        if ta is None:
+            raise RuntimeError("no state-dict structure: pass hollow=TensorAwareStateDict.from_state_dict(...)")
+        if not ta.is_hollow:
+            ta.pop_tensors()
+        ta.init_tensors()
+        it = self.recover(lost_ranks, list(ta.tensors))
+        self.hollow = ta
+        return it, ta.to_state_dict()
+
     def drop_local_state(self) -> None:
         """Forget everything this rank holds (what a replacement process starts with)."""
         self.snapshot = None

@@ -37,3 +37,46 @@ def _worker(rank, world):
 
 def test_fully_parallel_assignment():
     run_distributed(_worker, 2)
+
+
+def test_tensor_aware_state_dict_round_trip():
+    """Tensors out (hollow, picklable structure), tensors back in, device moves, sharded leaves keep their placement
+    and only main replicas carry data."""
+    import pickle
+    import pytest
+    from megatron_lm_b200.checkpoint.sharded import ShardedTensor
+    from megatron_lm_b200.checkpoint.tensor_aware import TensorAwareStateDict
+    w = torch.arange(12.0).view(3, 4)
+    main = ShardedTensor.from_rank_offsets("layer.w", torch.ones(2, 4), (0, 1, 2), replica_id=0)
+    copy = ShardedTensor.from_rank_offsets("layer.b", torch.zeros(4), replica_id=(0, 0, 1))
+    sd = {"iteration": 7, "model": {"w": w, "nested": [torch.zeros(2, dtype=torch.int64), "text"], "sh": main,
+                                    "replica": copy}, "opt": ({"step": 3}, torch.full((2,), 5.0))}
+    ta = TensorAwareStateDict.from_state_dict(sd)
+    assert not ta.is_hollow and len(list(ta.tensors)) == 4 and ta.nbytes() == 12 * 4 + 2 * 8 + 8 * 4 + 2 * 4
+    tensors = ta.pop_tensors()
+    assert ta.is_hollow and tensors[0] is w
+    blob = pickle.dumps(ta)                                     # the hollow form travels / is kept on the host
+    assert len(blob) < 4000
+    with pytest.raises(RuntimeError):
+        ta.to_state_dict()
+    with pytest.raises(ValueError):
+        ta.insert_tensors(tensors[:-1])
+    with pytest.raises(ValueError):
+        ta.insert_tensors([tensors[0].view(4, 3)] + tensors[1:])
+    other = pickle.loads(blob)
+    other.init_tensors()
+    for dst, src in zip(other.tensors, tensors):
+        dst.copy_(src)
+    back = other.to_state_dict()
+    assert back["iteration"] == 7 and back["model"]["nested"][1] == "text" and back["opt"][0] == {"step": 3}
+    assert torch.equal(back["model"]["w"], w) and torch.equal(back["opt"][1], torch.full((2,), 5.0))
+    sh = back["model"]["sh"]
+    assert isinstance(sh, ShardedTensor) and sh.global_offset == (2, 0) and torch.equal(sh.data, torch.ones(2, 4))
+    assert back["model"]["replica"].data is None                # not the main replica: protected elsewhere
+    keep_all = TensorAwareStateDict.from_state_dict(sd, remove_redundant_data=False)
+    assert len(list(keep_all.tensors)) == 5
+    ta.insert_tensors(tensors)
+    ta.copy_tensors_to_cpu()
+    assert all(t.device.type == "cpu" for t in ta.tensors) and next(iter(ta.tensors)) is not w
+    ta.restore_tensor_device()
+    assert torch.equal(ta.to_state_dict()["model"]["w"], w)

@@ -68,3 +68,35 @@ def _save_lose_recover(rank, world, k, m, lost, chunk):
                                             (8, 6, 2, [2, 5])])
 def test_save_lose_recover_gloo(world, k, m, lost):
     run_distributed(_save_lose_recover, world, k, m, lost, 4096)
+
+
+def _state_dict_rank(rank, world):
+    from megatron_lm_b200.checkpoint.ec_checkpoint import ECCheckpointManager
+    from megatron_lm_b200.checkpoint.tensor_aware import TensorAwareStateDict
+    torch.manual_seed(10 + rank)
+
+    def fresh():
+        return {"iteration": 0, "model": {"w": torch.randn(40, 30), "b": torch.randn(30)},
+                "optimizer": {"state": [torch.randn(1200), torch.randn(1200)], "step": 0}}
+    sd = fresh()
+    sd["iteration"], sd["optimizer"]["step"] = 9, 9
+    ref = {"w": sd["model"]["w"].clone(), "m": sd["optimizer"]["state"][1].clone()}
+    mgr = ECCheckpointManager(k=1, m=1, chunk_bytes=2048)
+    mgr.save_state_dict(sd, iteration=9)
+    sd["model"]["w"].add_(1.0)
+    if rank == 1:
+        # a replacement process: nothing in memory, structure from a freshly built state dict
+        mgr.drop_local_state()
+        mgr.hollow = None
+        hollow = TensorAwareStateDict.from_state_dict(fresh())
+        hollow.pop_tensors()
+        it, back = mgr.recover_state_dict([1], hollow=hollow)
+    else:
+        it, back = mgr.recover_state_dict([1])
+    assert it == 9
+    assert torch.equal(back["model"]["w"], ref["w"]) and torch.equal(back["optimizer"]["state"][1], ref["m"])
+    assert set(back) == {"iteration", "model", "optimizer"}
+
+
+def test_state_dict_form_of_the_in_memory_checkpoint():
+    run_distributed(_state_dict_rank, 2)
