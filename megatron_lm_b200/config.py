@@ -118,15 +118,9 @@ class ModelParallelConfig:
 # only pick between implementations of the same mathematics (fusion switches, library back ends, CUDA-graph and
 # communication-overlap tuning knobs) are accepted without effect: there is one implementation here.
 UNSUPPORTED_FIELDS = {
-    "apply_residual_connection_post_layernorm": "the residual is always taken before the norm",
     "cpu_offloading": "activation / weight offloading to the host is not built",
     "fp8_dot_product_attention": "attention runs in bf16 / fp16",
     "fp8_multi_head_attention": "attention runs in bf16 / fp16",
-    "no_rope_freq": "layers without rotary embedding are not built",
-    "moe_router_force_load_balancing": "forced uniform routing is not built",
-    "moe_apply_probs_on_input": "routing weights are applied to the expert output",
-    "moe_router_topk_limited_devices": "device-limited routing is expressed with moe_router_num_groups / group_topk",
-    "moe_layer_recompute": "use recompute_granularity / recompute_modules",
     "delay_wgrad_compute": "weight gradients are computed with their layer's backward",
     "init_model_with_meta_device": "parameters are created on their device",
     "use_kitchen": "the Kitchen quantisation back end is not built",
@@ -349,6 +343,12 @@ class TransformerConfig(ModelParallelConfig):
                 raise ValueError("num_moe_experts must be divisible by expert_model_parallel_size")
             if self.moe_ffn_hidden_size is None:
                 self.moe_ffn_hidden_size = self.ffn_hidden_size
+        if self.moe_router_topk_limited_devices and self.moe_router_num_groups is None:
+            # older name of group-limited routing: one group per expert-parallel rank
+            self.moe_router_num_groups = self.expert_model_parallel_size
+            self.moe_router_group_topk = self.moe_router_topk_limited_devices
+        if self.moe_apply_probs_on_input and self.moe_router_topk != 1:
+            raise ValueError("moe_apply_probs_on_input needs moe_router_topk == 1")
         if self.moe_expert_capacity_factor is not None:
             if self.moe_expert_capacity_factor < 0:
                 self.moe_expert_capacity_factor = None

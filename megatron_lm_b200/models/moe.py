@@ -192,6 +192,19 @@ def topk_softmax_with_capacity(logits, topk: int, capacity_factor=None, pad_to_c
     return full * final, final, tokens_per_expert
 
 
+class _RandomSTE(torch.autograd.Function):
+    """Forward: uniform random scores of the same shape (the same on every rank that holds the same tokens is not
+    required - each rank routes its own tokens); backward: identity."""
+
+    @staticmethod
+    def forward(ctx, logits):
+        return torch.rand_like(logits)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
 class TopKRouter(nn.Module):
     def __init__(self, config: TransformerConfig, layer_number: int):
         super().__init__()
@@ -272,6 +285,10 @@ class TopKRouter(nn.Module):
             eps = cfg.moe_input_jitter_eps
             h = h * torch.empty_like(h).uniform_(1.0 - eps, 1.0 + eps)
         logits = self.gating(h)
+        if cfg.moe_router_force_load_balancing:
+            # benchmarking aid: routing by random scores spreads the tokens evenly over the experts whatever the
+            # router has learnt; gradients pass straight through (reference: moe_utils.py RandomSTE)
+            logits = _RandomSTE.apply(logits)
         T = logits.shape[0]
         if self._fused_eligible(logits):
             return self._forward_fused(logits)
@@ -575,6 +592,10 @@ class MoELayer(nn.Module):
 
     def forward(self, hidden):
         probs, rmap = self.router(hidden)
+        if self.config.moe_apply_probs_on_input:
+            # top-1 routing with the weight applied before the expert: E(p x) instead of p E(x)
+            hidden = (hidden.reshape(-1, hidden.shape[-1]) * probs.sum(dim=-1, keepdim=True).to(hidden.dtype)).view_as(hidden)
+            probs = rmap.to(probs.dtype)
         tokens, tpe = self.token_dispatcher.dispatch(hidden, probs, rmap)
         out, _ = self.experts(tokens, tpe)
         out = self.token_dispatcher.combine(out)

@@ -238,6 +238,14 @@ class SelfAttention(nn.Module):
                 raise NotImplementedError("window_size is implemented as the causal window (left, 0)")
             self.window = int(left)
         self.recompute_core = config.recompute_granularity == "selective" and "core_attn" in config.recompute_modules
+        # layers without rotary embedding: every no_rope_freq-th layer, or an explicit 0 / 1 list (1 = no rotary)
+        nrf = getattr(config, "no_rope_freq", None)
+        if isinstance(nrf, int) and nrf > 0:
+            self.no_rope = layer_number % nrf == 0
+        elif isinstance(nrf, (list, tuple)):
+            self.no_rope = bool(nrf[(layer_number - 1) % len(nrf)])
+        else:
+            self.no_rope = False
         self.cp_size = state.get_context_parallel_world_size() if state.model_parallel_is_initialized() else 1
         ct = config.cp_comm_type
         self.cp_comm_type = (ct[(layer_number - 1) % len(ct)] if isinstance(ct, (list, tuple)) else ct) or "p2p"
@@ -255,7 +263,7 @@ class SelfAttention(nn.Module):
             q = self.q_layernorm(qkv5[:, :, :, :self.qpg].contiguous())
             k = self.k_layernorm(qkv5[:, :, :, self.qpg:self.qpg + 1].contiguous())
             qkv5 = torch.cat((q, k, qkv5[:, :, :, self.qpg + 1:]), dim=3)
-        cos, sin = rotary if rotary is not None else (None, None)
+        cos, sin = rotary if rotary is not None and not self.no_rope else (None, None)
         if self.window is not None and (inference_context is not None or self.cp_size > 1):
             raise NotImplementedError("sliding-window attention is not available with context parallelism or the "
                                       "inference engines' key/value caches")
@@ -447,8 +455,9 @@ class TransformerLayer(nn.Module):
         self.is_moe = isinstance(self.mlp, _MoE)
         self.hidden_dropout = config.hidden_dropout
         mods = config.recompute_modules if config.recompute_granularity == "selective" else []
-        self.recompute_input_ln = "layernorm" in mods
-        self.recompute_mlp = "mlp" in mods
+        self.post_ln_residual = config.apply_residual_connection_post_layernorm
+        self.recompute_input_ln = "layernorm" in mods and not self.post_ln_residual
+        self.recompute_mlp = "mlp" in mods or (self.is_moe and ("moe" in mods or config.moe_layer_recompute))
         if config.fp8:
             from ..fp8_utils import mark_layer_precision
             mark_layer_precision(self, config, layer_number - 1)       # first / last layers may stay in 16 bits
@@ -469,6 +478,8 @@ class TransformerLayer(nn.Module):
             ln = ck.checkpoint(self.input_layernorm, hidden_states)
         else:
             ck, ln = None, self.input_layernorm(hidden_states)
+        if self.post_ln_residual:
+            residual = ln                         # the residual branch starts after the norm
         attn_out, attn_bias = self.self_attention(ln, rotary=rotary, inference_context=inference_context,
                                                   attention_mask=attention_mask)
         if ck is not None:
@@ -485,6 +496,8 @@ class TransformerLayer(nn.Module):
             ln = ck.checkpoint(self.pre_mlp_layernorm, hidden_states)
         else:
             ck, ln = None, self.pre_mlp_layernorm(hidden_states)
+        if self.post_ln_residual:
+            residual = ln
         if self.recompute_mlp and self.training:
             mlp_out, mlp_bias = checkpoint(self.mlp, False, ln)
         else:

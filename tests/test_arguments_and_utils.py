@@ -329,7 +329,7 @@ def test_unsupported_config_fields_are_refused():
     from megatron_lm_b200.config import UNSUPPORTED_FIELDS, TransformerConfig
     base = dict(num_layers=1, hidden_size=32, num_attention_heads=4)
     TransformerConfig(**base)                                           # defaults pass
-    for name, value in (("apply_residual_connection_post_layernorm", True),
+    for name, value in (("init_model_with_meta_device", True),
                         ("cpu_offloading", True), ("fp8_dot_product_attention", True)):
         assert name in UNSUPPORTED_FIELDS
         with pytest.raises(ValueError, match="not supported"):

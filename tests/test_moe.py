@@ -317,3 +317,69 @@ def test_expert_parallel_grad_norm_is_global(tmp_path):
     for (la, ga), (lb, gb) in zip(a, b):
         assert ga == pytest.approx(gb, rel=1e-6), (a, b)     # one global norm on both expert-parallel ranks
     assert a[0][1] > 0.5                                       # clipping was active
+
+
+# ------------------------------------------------------------------------------------------------ routing variants
+def test_forced_load_balancing_spreads_tokens_and_keeps_gradients():
+    """Random routing scores: even a router that prefers one expert sends every expert about its share, and the
+    router weight still receives a gradient (reference: test_routers.py test_force_load_balancing)."""
+    from megatron_lm_b200.models.moe import MoELayer
+    torch.manual_seed(0)
+    layer = MoELayer(_cfg(moe_router_force_load_balancing=True, moe_grouped_gemm=True), 1)
+    with torch.no_grad():
+        layer.router.weight.zero_()
+        layer.router.weight[0] += 5.0                          # learnt preference: everything to expert 0
+    x = torch.randn(64, 8, 16).abs()
+    probs, rmap = layer.router(x)
+    counts = rmap.sum(0).float()
+    assert counts.min() > 0.6 * counts.mean() and counts.max() < 1.4 * counts.mean()
+    layer(x)[0].sum().backward()
+    assert layer.router.weight.grad is not None and layer.router.weight.grad.abs().sum() > 0
+    plain = MoELayer(_cfg(moe_grouped_gemm=True), 1)
+    with torch.no_grad():
+        plain.router.weight.zero_()
+        plain.router.weight[0] += 5.0
+    assert plain.router(x)[1][:, 0].all()
+
+
+def test_probabilities_applied_before_the_expert():
+    from megatron_lm_b200.models.moe import MoELayer
+    import torch.nn.functional as F
+    with pytest.raises(ValueError):
+        _cfg(moe_apply_probs_on_input=True)                    # needs top-1 routing
+    torch.manual_seed(1)
+    layer = MoELayer(_cfg(moe_apply_probs_on_input=True, moe_router_topk=1, moe_grouped_gemm=True,
+                          moe_router_pre_softmax=True), 1)
+    x = torch.randn(6, 2, 16)
+    y, _ = layer(x)
+    probs, rmap = layer.router(x)
+    h = x.reshape(-1, 16)
+    want = torch.zeros_like(h)
+    for t in range(h.shape[0]):
+        e = int(rmap[t].float().argmax())
+        a = (probs[t, e] * h[t]) @ layer.experts.weight1[e].t()
+        g, u = a.chunk(2, -1)
+        want[t] = (F.silu(g) * u) @ layer.experts.weight2[e].t()
+    assert torch.allclose(y.reshape(-1, 16), want, atol=1e-5)
+
+
+def test_device_limited_routing_is_group_limited_routing():
+    cfg = _cfg(num_moe_experts=8, moe_router_topk=2, moe_router_topk_limited_devices=1, expert_model_parallel_size=4)
+    assert cfg.moe_router_num_groups == 4 and cfg.moe_router_group_topk == 1
+
+
+def test_moe_layer_recompute_gives_the_same_gradients():
+    from megatron_lm_b200.models.gpt import GPTModel
+    grads = []
+    for recompute in (False, True):
+        torch.manual_seed(3)
+        cfg = _cfg(moe_layer_recompute=recompute, moe_grouped_gemm=True)
+        m = GPTModel(cfg, 32, 16, parallel_output=False, position_embedding_type="rope")
+        assert m.decoder.layers[0].recompute_mlp == recompute
+        ids = torch.randint(0, 32, (2, 16))
+        m.train()
+        m(ids, labels=ids).mean().backward()
+        grads.append({n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None})
+    assert grads[0].keys() == grads[1].keys()
+    for k in grads[0]:
+        assert torch.allclose(grads[0][k], grads[1][k], atol=1e-6), k

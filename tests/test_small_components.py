@@ -231,3 +231,44 @@ def test_sliding_window_attention_layer_on_cpu():
                                            attention_dropout=0.0), 1)
     full.load_state_dict(attn.state_dict())
     assert not torch.allclose(full(x)[0][8:], y[8:], atol=1e-4)
+
+
+def test_layers_without_rotary_embedding_and_post_norm_residual():
+    """no_rope_freq: every n-th layer (or the layers of an explicit list) attends without rotary positions;
+    apply_residual_connection_post_layernorm: the residual branch starts after the norm."""
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    base = dict(num_layers=4, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+                attention_dropout=0.0, use_cpu_initialization=True)
+    m = GPTModel(TransformerConfig(no_rope_freq=2, **base), 32, 16, position_embedding_type="rope", parallel_output=False)
+    assert [l.self_attention.no_rope for l in m.decoder.layers] == [False, True, False, True]
+    m2 = GPTModel(TransformerConfig(no_rope_freq=[1, 0, 0, 1], **base), 32, 16, position_embedding_type="rope",
+                  parallel_output=False)
+    assert [l.self_attention.no_rope for l in m2.decoder.layers] == [True, False, False, True]
+    # a layer without rotary positions is permutation-equivariant over the keys it sees: with a single layer and the
+    # last query, shuffling the earlier tokens leaves the last position's output unchanged
+    one = dict(base, num_layers=1)
+    torch.manual_seed(0)
+    nope = GPTModel(TransformerConfig(no_rope_freq=1, **one), 32, 16, position_embedding_type="rope",
+                    parallel_output=False).eval()
+    torch.manual_seed(0)
+    rope = GPTModel(TransformerConfig(**one), 32, 16, position_embedding_type="rope", parallel_output=False).eval()
+    ids = torch.randint(0, 32, (1, 9))
+    perm = torch.cat([ids[:, :8].flip(1), ids[:, 8:]], dim=1)
+    with torch.no_grad():
+        assert torch.allclose(nope(ids)[0, -1], nope(perm)[0, -1], atol=1e-5)
+        assert not torch.allclose(rope(ids)[0, -1], rope(perm)[0, -1], atol=1e-5)
+    # post-norm residual: y = norm(x) + f(norm(x))
+    torch.manual_seed(0)
+    post = GPTModel(TransformerConfig(apply_residual_connection_post_layernorm=True, **one), 32, 16,
+                    parallel_output=False).eval()
+    layer = post.decoder.layers[0]
+    x = torch.randn(5, 2, 32)
+    with torch.no_grad():
+        ln1 = layer.input_layernorm(x)
+        a, ab = layer.self_attention(ln1)
+        h = ln1 + a + (ab if ab is not None else 0)
+        ln2 = layer.pre_mlp_layernorm(h)
+        f, fb = layer.mlp(ln2)
+        want = ln2 + f + (fb if fb is not None else 0)
+        assert torch.allclose(layer(x), want, atol=1e-5)
