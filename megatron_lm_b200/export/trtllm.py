@@ -10,7 +10,7 @@ conversion (pure tensor work) runs anywhere.
 from __future__ import annotations
 
 import re
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -55,6 +55,7 @@ class TRTLLMHelper:
         and a gated fc1 [gate ; up] is split into ``mlp.gate`` / ``mlp.fc`` the way that runtime expects."""
         c = self.cfg
         out = {}
+        seq_experts: Dict[str, Dict[int, torch.Tensor]] = {}
         for k, v in state_dict.items():
             v = v.to(dtype)
             if k == "embedding.word_embeddings.weight":
@@ -83,15 +84,122 @@ class TRTLLMHelper:
                         out[base + "mlp.fc.weight"], out[base + "mlp.gate.weight"] = gate, up
                     else:
                         out[base + "mlp.fc.weight"] = v
+                elif re.match(r"^mlp\.experts\.local_experts\.\d+\.linear_fc[12]\.weight$", rest):
+                    e, which = re.match(r"^mlp\.experts\.local_experts\.(\d+)\.linear_fc([12])", rest).groups()
+                    key = base + ("mlp.fc.weight" if which == "1" else "mlp.proj.weight")
+                    seq_experts.setdefault(key, {})[int(e)] = v
                 elif rest == "mlp.experts.weight1":
                     out[base + "mlp.fc.weight"] = v
                 elif rest == "mlp.experts.weight2":
                     out[base + "mlp.proj.weight"] = v
                 elif rest in _LAYER:
                     out[base + _LAYER[rest]] = v
+        for key, by_e in seq_experts.items():                         # per-expert modules -> one [E, ...] tensor
+            out[key] = torch.stack([by_e[e] for e in sorted(by_e)])
         if self.share and "lm_head.weight" not in out:
             out["lm_head.weight"] = out["transformer.vocab_embedding.weight"]
         return out
+
+    # -- tensor / pipeline parallel checkpoints -----------------------------------------------------------------------
+    def split_for_mapping(self, weights: Dict[str, torch.Tensor], tp: int = 1, pp: int = 1,
+                          use_parallel_embedding: bool = False) -> List[Dict[str, torch.Tensor]]:
+        """Converted (full) weights -> one dict per rank of a ``tp x pp`` mapping, rank = pp_rank * tp + tp_rank, in
+        the runtime's per-rank layout: fused QKV cut by heads (each rank keeps its own q, k and v heads, again as
+        [q ; k ; v]), column-parallel weights along their rows, row-parallel weights along their columns, experts along
+        the FFN width, layers dealt to pipeline stages in order with the embedding on the first and the final norm
+        and head on the last.  Reference: trtllm_weights_converter/distributed_trtllm_model_weights_converter.py:60-293
+        and single_device_trtllm_model_weights_converter.py:300-489."""
+        c = self.cfg
+        if c.num_layers % pp or c.num_attention_heads % tp or (c.num_query_groups or c.num_attention_heads) % tp:
+            raise ValueError("layers must divide by the pipeline size and heads / query groups by the tensor size")
+        per_stage = c.num_layers // pp
+        ng = c.num_query_groups or c.num_attention_heads
+        hn = c.kv_channels or c.hidden_size // c.num_attention_heads
+        q_rows, kv_rows = c.num_attention_heads * hn, ng * hn
+        ranks: List[Dict[str, torch.Tensor]] = [dict() for _ in range(tp * pp)]
+
+        def cut(name, v, t):
+            if name.endswith("attention.qkv.weight") or name.endswith("attention.qkv.bias"):
+                q, k, vv = v[:q_rows], v[q_rows:q_rows + kv_rows], v[q_rows + kv_rows:]
+                return torch.cat([x.chunk(tp, 0)[t] for x in (q, k, vv)], 0)
+            if name.endswith(("mlp.fc.weight", "mlp.gate.weight", "mlp.fc.bias", "mlp.gate.bias")) and v.dim() <= 2:
+                return v.chunk(tp, 0)[t]
+            if name.endswith(("attention.dense.weight", "mlp.proj.weight")) and v.dim() == 2:
+                return v.chunk(tp, 1)[t]
+            if v.dim() == 3 and name.endswith("mlp.fc.weight"):        # experts [E, (2)f, h]
+                if c.gated_linear_unit:
+                    g, u = v.chunk(2, 1)
+                    return torch.cat((g.chunk(tp, 1)[t], u.chunk(tp, 1)[t]), 1)
+                return v.chunk(tp, 1)[t]
+            if v.dim() == 3 and name.endswith("mlp.proj.weight"):      # experts [E, h, f]
+                return v.chunk(tp, 2)[t]
+            if name == "lm_head.weight":
+                return v.chunk(tp, 0)[t]
+            if name == "transformer.vocab_embedding.weight" and use_parallel_embedding:
+                return v.chunk(tp, 0)[t]
+            return v
+        for name, v in weights.items():
+            m = re.match(r"^transformer\.layers\.(\d+)\.(.*)$", name)
+            if m:
+                layer = int(m.group(1))
+                stages = [layer // per_stage]
+                out_name = f"transformer.layers.{layer % per_stage}.{m.group(2)}" if pp > 1 else name
+            elif name.startswith(("transformer.vocab_embedding", "transformer.position_embedding")):
+                stages, out_name = [0], name
+            else:                                                     # final norm, head
+                stages, out_name = [pp - 1], name
+            for st in stages:
+                for t in range(tp):
+                    ranks[st * tp + t][out_name] = cut(name, v, t).contiguous() if tp > 1 else v
+        return ranks
+
+    def fp8_scaling_factors(self, model) -> Dict[str, torch.Tensor]:
+        """Scaling factors of a model quantised by ``post_training.ptq`` (per-tensor FP8) under the runtime's names:
+        ``...weights_scaling_factor`` and ``...activation_scaling_factor`` = range / 448 per linear (reference:
+        single_device_trtllm_model_weights_converter.py:60-120, scales taken from the FP8 metadata of the layers)."""
+        names = {"self_attention.linear_qkv": "attention.qkv", "self_attention.linear_proj": "attention.dense",
+                 "mlp.linear_fc1": "mlp.fc", "mlp.linear_fc2": "mlp.proj"}
+        out: Dict[str, torch.Tensor] = {}
+        for mod_name, mod in model.named_modules():
+            m = re.match(r"^(?:.*\.)?decoder\.layers\.(\d+)\.(self_attention\.linear_qkv|self_attention\.linear_proj|"
+                         r"mlp\.linear_fc1|mlp\.linear_fc2)$", mod_name)
+            if not m or not getattr(mod, "ptq", False) or not hasattr(mod, "weight_quantizer"):
+                continue
+            base = f"transformer.layers.{m.group(1)}.{names[m.group(2)]}."
+            wq, iq = mod.weight_quantizer, mod.input_quantizer
+            if wq.spec.kind != "fp8" or wq.spec.block is not None:
+                continue
+            if getattr(mod, "weight_scale", None) is not None and mod.weight is None:
+                out[base + "weights_scaling_factor"] = mod.weight_scale.reshape(1).float()
+            elif wq.amax is not None:
+                out[base + "weights_scaling_factor"] = (wq.amax.float() / 448.0).reshape(1)
+            if iq.amax is not None:
+                out[base + "activation_scaling_factor"] = (iq.amax.float() / 448.0).reshape(1)
+            if m.group(2) == "mlp.linear_fc1" and self.cfg.gated_linear_unit:
+                for k in ("weights_scaling_factor", "activation_scaling_factor"):
+                    if base + k in out:
+                        out[base.replace("mlp.fc.", "mlp.gate.") + k] = out[base + k]
+        return out
+
+    def save_checkpoint(self, out_dir: str, weights_by_rank: List[Dict[str, torch.Tensor]], config: dict) -> List[str]:
+        """``config.json`` + one weight file per rank (``rank<N>.safetensors`` when that package is importable, else
+        ``rank<N>.pt``): the checkpoint directory the runtime's engine builder reads."""
+        import json
+        import os
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, "config.json"), "w") as f:
+            json.dump(config, f, indent=2)
+        files = []
+        for r, w in enumerate(weights_by_rank):
+            try:
+                from safetensors.torch import save_file
+                path = os.path.join(out_dir, f"rank{r}.safetensors")
+                save_file({k: v.contiguous().clone() for k, v in w.items()}, path)
+            except ImportError:
+                path = os.path.join(out_dir, f"rank{r}.pt")
+                torch.save(w, path)
+            files.append(path)
+        return files
 
     def build_and_save_engine(self, engine_dir: str, weights: Dict[str, torch.Tensor], config: dict, **build_kw):
         try:

@@ -58,3 +58,52 @@ def test_distillation_losses_and_recipe():
     chosen = apply_recipe(m, rec)
     assert chosen["decoder.layers.0.mlp.linear_fc1"] == "bf16" and chosen["decoder.layers.1.mlp.linear_fc1"] == "fp8"
     assert m.decoder.layers[0].mlp.linear_fc1.fp8_eligible is False
+
+
+def test_trtllm_rank_files_and_fp8_scales(tmp_path):
+    import json
+    import os
+    from megatron_lm_b200.post_training import ptq
+    torch.manual_seed(0)
+    cfg = TransformerConfig(num_layers=4, hidden_size=32, num_attention_heads=4, num_query_groups=2, ffn_hidden_size=64,
+                            hidden_dropout=0.0, attention_dropout=0.0, gated_linear_unit=True, add_bias_linear=False)
+    m = GPTModel(cfg, 64, 32, parallel_output=False, share_embeddings_and_output_weights=False)
+    h = TRTLLMHelper(cfg, "llama")
+    full = h.convert(m.state_dict(), torch.float32)
+    ranks = h.split_for_mapping(full, tp=2, pp=2)
+    assert len(ranks) == 4
+    # pipeline: two layers per stage, renumbered from zero; embedding first, head and final norm last
+    assert "transformer.vocab_embedding.weight" in ranks[0] and "transformer.vocab_embedding.weight" not in ranks[2]
+    assert "lm_head.weight" in ranks[3] and "transformer.ln_f.weight" in ranks[2] and "lm_head.weight" not in ranks[0]
+    assert set(k.split(".")[2] for k in ranks[2] if k.startswith("transformer.layers.")) == {"0", "1"}
+    # tensor: QKV by heads, so that every rank holds [its q ; its k ; its v]
+    qkv = full["transformer.layers.2.attention.qkv.weight"]                       # [32 q + 16 k + 16 v, 32]
+    r0, r1 = ranks[2]["transformer.layers.0.attention.qkv.weight"], ranks[3]["transformer.layers.0.attention.qkv.weight"]
+    assert r0.shape == (32, 32)
+    assert torch.equal(r1, torch.cat((qkv[16:32], qkv[40:48], qkv[56:64])))
+    assert torch.equal(torch.cat((ranks[2]["transformer.layers.0.mlp.proj.weight"],
+                                  ranks[3]["transformer.layers.0.mlp.proj.weight"]), 1),
+                       full["transformer.layers.2.mlp.proj.weight"])
+    assert ranks[1]["transformer.layers.1.mlp.gate.weight"].shape == (32, 32) and ranks[3]["lm_head.weight"].shape == (32, 32)
+    with __import__("pytest").raises(ValueError):
+        h.split_for_mapping(full, tp=3)
+    files = h.save_checkpoint(str(tmp_path / "ck"), ranks, h.pretrained_config(tp=2, pp=2, vocab_size=64))
+    assert len(files) == 4 and all(os.path.isfile(f) for f in files)
+    assert json.load(open(tmp_path / "ck" / "config.json"))["mapping"] == {"world_size": 4, "tp_size": 2, "pp_size": 2}
+    # FP8 scales of a calibrated model
+    ids = torch.randint(0, 64, (2, 16))
+    pos = torch.arange(16).unsqueeze(0).expand(2, 16)
+    ptq.quantize(m, "fp8", lambda mod: mod(ids, pos, None))
+    sc = h.fp8_scaling_factors(m)
+    lin = m.decoder.layers[1].mlp.linear_fc1
+    assert torch.allclose(sc["transformer.layers.1.mlp.fc.weights_scaling_factor"], lin.weight_quantizer.amax / 448.0)
+    assert torch.equal(sc["transformer.layers.1.mlp.gate.activation_scaling_factor"],
+                       sc["transformer.layers.1.mlp.fc.activation_scaling_factor"])
+    assert len(sc) == 4 * (4 * 2 + 2)
+    # per-expert modules become one stacked tensor
+    moe_cfg = TransformerConfig(num_layers=1, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64,
+                                num_moe_experts=4, moe_ffn_hidden_size=48, gated_linear_unit=True, add_bias_linear=False,
+                                moe_grouped_gemm=False)
+    moe = GPTModel(moe_cfg, 64, 32, parallel_output=False)
+    w = TRTLLMHelper(moe_cfg, "mixtral").convert(moe.state_dict(), torch.float32)
+    assert w["transformer.layers.0.mlp.fc.weight"].shape == (4, 96, 32) and w["transformer.layers.0.mlp.proj.weight"].shape == (4, 32, 48)
