@@ -185,11 +185,14 @@ namespace mlb {
 constexpr int kGnThreads = 256;
 constexpr int kGnMaxIt = 8;                 // channels <= 8 * 256 * 8 = 16384
 constexpr int kGnMaxGroups = 64;
+// the kernels keep a row's NIT x 8 values per thread in registers: NIT = ceil(channels / 2048) is a template
+// parameter, so that narrow rows leave registers for more resident blocks
+constexpr int gn_blocks_per_sm(int nit) { return nit <= 2 ? 4 : (nit <= 4 ? 2 : 1); }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
-template <typename T>
-__global__ void __launch_bounds__(kGnThreads)
+template <typename T, int NIT>
+__global__ void __launch_bounds__(kGnThreads, gn_blocks_per_sm(NIT))
 gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const float* __restrict__ w,
                          T* __restrict__ out, float* __restrict__ rstd, int rows, int C, int G, long long ys,
                          long long zs, float eps) {
@@ -199,9 +202,9 @@ gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     if (threadIdx.x < G) gsum[threadIdx.x] = 0.f;
     __syncthreads();
-    float u[kGnMaxIt][8];
+    float u[NIT][8];
 #pragma unroll
-    for (int it = 0; it < kGnMaxIt; ++it) {
+    for (int it = 0; it < NIT; ++it) {
       const int c = threadIdx.x * 8 + it * kGnThreads * 8;
       float part = 0.f;
       if (c < C) {
@@ -222,7 +225,7 @@ gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const
     }
     __syncthreads();
 #pragma unroll
-    for (int it = 0; it < kGnMaxIt; ++it) {
+    for (int it = 0; it < NIT; ++it) {
       const int c = threadIdx.x * 8 + it * kGnThreads * 8;
       if (c < C) {
         const float rs = rsqrtf(gsum[c / gs] / gs + eps);
@@ -238,8 +241,8 @@ gated_rmsnorm_fwd_kernel(const T* __restrict__ y, const T* __restrict__ z, const
   }
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kGnThreads)
+template <typename T, int NIT>
+__global__ void __launch_bounds__(kGnThreads, NIT <= 2 ? 3 : (NIT <= 4 ? 2 : 1))
 gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, const T* __restrict__ z,
                          const float* __restrict__ w, const float* __restrict__ rstd, T* __restrict__ dy,
                          T* __restrict__ dz, float* __restrict__ dw, int rows, int C, int G, long long ys,
@@ -247,9 +250,9 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
   __shared__ float gdot[kGnMaxGroups];
   const int gs = C / G;
   const bool warp_groups = (gs % 256) == 0;
-  float wacc[kGnMaxIt][8];
+  float wacc[NIT][8];
 #pragma unroll
-  for (int it = 0; it < kGnMaxIt; ++it)
+  for (int it = 0; it < NIT; ++it)
 #pragma unroll
     for (int k = 0; k < 8; ++k) wacc[it][k] = 0.f;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -257,7 +260,7 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
     __syncthreads();
     // pass 1: mean over the group of (dout * w) * n, n = u * rstd
 #pragma unroll
-    for (int it = 0; it < kGnMaxIt; ++it) {
+    for (int it = 0; it < NIT; ++it) {
       const int c = threadIdx.x * 8 + it * kGnThreads * 8;
       float part = 0.f;
       if (c < C) {
@@ -284,7 +287,7 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
     }
     __syncthreads();
 #pragma unroll
-    for (int it = 0; it < kGnMaxIt; ++it) {
+    for (int it = 0; it < NIT; ++it) {
       const int c = threadIdx.x * 8 + it * kGnThreads * 8;
       if (c < C) {
         float a[8], b[8], g[8], wv[8], oy[8], oz[8];
@@ -310,7 +313,7 @@ gated_rmsnorm_bwd_kernel(const T* __restrict__ dout, const T* __restrict__ y, co
     __syncthreads();
   }
 #pragma unroll
-  for (int it = 0; it < kGnMaxIt; ++it) {
+  for (int it = 0; it < NIT; ++it) {
     const int c = threadIdx.x * 8 + it * kGnThreads * 8;
     if (c < C) {
 #pragma unroll
@@ -332,8 +335,11 @@ MLB_API int mlb_gated_rmsnorm_fwd(int dtype, const void* y, const void* z, const
   using namespace mlb;
   if (!gn_ok(rows, C, G, y_stride, z_stride)) return -3;
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  MLB_DISPATCH_ACT(dtype, T, (gated_rmsnorm_fwd_kernel<T><<<grid, kGnThreads, 0, st>>>(
-      (const T*)y, (const T*)z, w, (T*)out, rstd, rows, C, G, y_stride, z_stride, eps)));
+  const int nit = (C + kGnThreads * 8 - 1) / (kGnThreads * 8);
+#define GN_FWD(N) MLB_DISPATCH_ACT(dtype, T, (gated_rmsnorm_fwd_kernel<T, N><<<grid, kGnThreads, 0, st>>>( \
+      (const T*)y, (const T*)z, w, (T*)out, rstd, rows, C, G, y_stride, z_stride, eps)))
+  if (nit <= 1) { GN_FWD(1); } else if (nit <= 2) { GN_FWD(2); } else if (nit <= 4) { GN_FWD(4); } else { GN_FWD(8); }
+#undef GN_FWD
   MLB_CHECK_LAUNCH();
   return 0;
 }
@@ -345,10 +351,14 @@ MLB_API int mlb_gated_rmsnorm_bwd(int dtype, const void* dout, const void* y, co
                                   cudaStream_t st) {
   using namespace mlb;
   if (!gn_ok(rows, C, G, y_stride, z_stride) || dy_stride % 8 != 0 || dz_stride % 8 != 0) return -3;
-  const int grid = rows < 148 * 2 ? rows : 148 * 2;
-  MLB_DISPATCH_ACT(dtype, T, (gated_rmsnorm_bwd_kernel<T><<<grid, kGnThreads, 0, st>>>(
-      (const T*)dout, (const T*)y, (const T*)z, w, rstd, (T*)dy, (T*)dz, dw, rows, C, G, y_stride, z_stride,
-      dy_stride, dz_stride)));
+  const int nit = (C + kGnThreads * 8 - 1) / (kGnThreads * 8);
+  const int per_sm = nit <= 2 ? 3 : 2;       // every block ends with one atomic per channel into dw: keep the grid small
+  const int grid = rows < 148 * per_sm ? rows : 148 * per_sm;
+#define GN_BWD(N) MLB_DISPATCH_ACT(dtype, T, (gated_rmsnorm_bwd_kernel<T, N><<<grid, kGnThreads, 0, st>>>( \
+      (const T*)dout, (const T*)y, (const T*)z, w, rstd, (T*)dy, (T*)dz, dw, rows, C, G, y_stride, z_stride, \
+      dy_stride, dz_stride)))
+  if (nit <= 1) { GN_BWD(1); } else if (nit <= 2) { GN_BWD(2); } else if (nit <= 4) { GN_BWD(4); } else { GN_BWD(8); }
+#undef GN_BWD
   MLB_CHECK_LAUNCH();
   return 0;
 }

@@ -90,7 +90,7 @@ def test_mamba_kernels_gpu():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("C,G", [(256, 1), (1024, 8), (4096, 2), (2560, 5)])
+@pytest.mark.parametrize("C,G", [(256, 1), (1024, 8), (4096, 2), (2560, 5), (8192, 8), (16384, 4)])
 def test_gated_rmsnorm_gpu(C, G):
     from megatron_lm_b200.ops.mamba import _gated_rmsnorm_ref, gated_rmsnorm
     for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
