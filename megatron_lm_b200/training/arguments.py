@@ -307,8 +307,6 @@ UNUSED_FLAGS = {
     "app_tag_run_version": (_W, "the one-logger adapter records locally"),
     "calc_ft_timeouts": (_W, "heartbeat timeouts are fixed"),
     "log_throughput": (_W, "throughput is part of every log line"),
-    "log_progress": (_W, "no progress.txt file"), "tensorboard_log_interval": (_W, "scalars are written every --log-interval"),
-    "log_memory_to_tensorboard": (_W, "memory is reported on the console (--log-memory-interval)"),
     "result_rejected_tracker_filename": (_W, "rejections are reported on the console"),
     "adlr_autoresume_interval": (_W, "no cluster auto-resume service"),
     # checkpoint options

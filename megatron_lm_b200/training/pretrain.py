@@ -166,9 +166,10 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
             f" throughput per GPU (TFLOP/s/GPU): {throughput:.1f} |"
             f" tokens/s/GPU: {tokens_per_iter / elapsed_per_iter / args.world_size:.1f} |"
             f" learning rate: {lr:.6E} | global batch size: {args.global_batch_size:5d} |")
+    tb_every = max(getattr(args, "tensorboard_log_interval", 1) or 1, 1)
     for k in list(total_loss_dict.keys()):
         line += f" {k}: {total_loss_dict[k] / n:.6E} |"
-        if _WRITER is not None:
+        if _WRITER is not None and iteration % tb_every == 0:
             _WRITER.add_scalar(k, total_loss_dict[k] / n, iteration)
         total_loss_dict[k] = 0.0
     line += f" loss scale: {loss_scale:.1f} |"
@@ -177,7 +178,7 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
     if num_zeros is not None:
         line += f" num zeros: {int(num_zeros)} |"
     line += f" number of skipped iterations: {skipped_tot:3d} |"
-    if _WRITER is not None:
+    if _WRITER is not None and iteration % tb_every == 0:
         _WRITER.add_scalar("iteration-time", elapsed_per_iter, iteration)
         _WRITER.add_scalar("learning-rate", lr, iteration)
         _WRITER.add_scalar("throughput", throughput, iteration)
@@ -190,13 +191,35 @@ def training_log(loss_dict: Dict, total_loss_dict: Dict, lr: float, iteration: i
         if torch.cuda.is_available():
             _WRITER.add_scalar("mem-allocated-bytes", torch.cuda.memory_allocated(), iteration)
             _WRITER.add_scalar("mem-max-allocated-bytes", torch.cuda.max_memory_allocated(), iteration)
+            if getattr(args, "log_memory_to_tensorboard", False):
+                st = torch.cuda.memory_stats()
+                _WRITER.add_scalar("mem-reserved-bytes", st.get("reserved_bytes.all.current", 0), iteration)
+                _WRITER.add_scalar("mem-allocated-count", st.get("allocation.all.current", 0), iteration)
     print_rank_last(line)
+    if getattr(args, "log_progress", False) and getattr(args, "save", None):
+        append_to_progress_log(args, f"iteration: {iteration:8d}\tthroughput: {throughput:.1f} TFLOP/s/GPU\t"
+                                     f"tokens: {args.consumed_train_samples * args.seq_length}")
     if getattr(args, "log_timers_to_tensorboard", False) and _TIMERS is not None:
         # a collective over all ranks: outside the writer-only branch
         _TIMERS.write(["forward-backward", "optimizer", "save-checkpoint"], _WRITER, iteration,
                       normalizer=args.log_interval, reset=False)
     if _TIMERS is not None:
         _TIMERS.log(normalizer=args.log_interval)
+
+
+def append_to_progress_log(args, text: str, barrier: bool = False) -> None:
+    """--log-progress: one line per event (start, log step, checkpoint) in ``<save>/progress.txt`` - job id, time,
+    world size, then the event (reference: megatron/training/training.py:439 ``append_to_progress_log``)."""
+    if getattr(args, "save", None) is None:
+        return
+    if barrier and dist.is_initialized():
+        dist.barrier()
+    if args.rank != 0:
+        return
+    os.makedirs(args.save, exist_ok=True)
+    job = os.environ.get("SLURM_JOB_ID", os.environ.get("JOB_ID", ""))
+    with open(os.path.join(args.save, "progress.txt"), "a") as f:
+        f.write(f"{time.strftime('%Y-%m-%d %H:%M:%S')}\tJob ID: {job}\t# GPUs: {args.world_size}\t{text}\n")
 
 
 def ec_protection_group(args):
@@ -591,6 +614,9 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
                                           num_floating_point_operations_so_far=flops_so_far)
             timers("save-checkpoint").stop(barrier=True)
             timers.log(["save-checkpoint"])
+            if getattr(args, "log_progress", False):
+                append_to_progress_log(args, f"Saved checkpoint\tIteration: {iteration}\t"
+                                             f"Floating-point operations: {flops_so_far:.2e}")
         if exiting:
             print_rank_0(f"exiting program at iteration {iteration}")
             break

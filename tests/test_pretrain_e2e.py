@@ -237,8 +237,14 @@ def test_loop_options_on_two_ranks(tmp_path):
     out = _torchrun(2, 29649, ["--global-batch-size", "4", "--manual-gc", "--manual-gc-interval", "1",
                                "--check-weight-hash-across-dp-replicas-interval", "1", "--enable-ft-package",
                                "--tensorboard-dir", tb, "--log-timers-to-tensorboard", "--log-world-size-to-tensorboard",
-                               "--log-validation-ppl-to-tensorboard"])
+                               "--log-validation-ppl-to-tensorboard", "--log-straggler", "--straggler-minmax-count", "2",
+                               "--log-progress", "--save", str(tmp_path / "ck"), "--save-interval", "2",
+                               "--tensorboard-log-interval", "2", "--log-memory-to-tensorboard"])
     assert "PPL" in out and os.listdir(tb)
+    assert "straggler report @ 1" in out and "slowest:" in out
+    progress = open(tmp_path / "ck" / "progress.txt").read().splitlines()
+    assert sum("Saved checkpoint" in l for l in progress) >= 1 and sum("throughput:" in l for l in progress) == 3
+    assert all("# GPUs: 2" in l for l in progress)
     mock = ["--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64"]
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29619")
     r = subprocess.run([sys.executable, os.path.join(ROOT, "pretrain_gpt.py")] + BASE + ["--skip-train"],
