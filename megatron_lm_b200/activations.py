@@ -18,5 +18,10 @@ def fast_gelu(x: torch.Tensor) -> torch.Tensor:
     return 0.5 * x * (1.0 + torch.tanh(0.7978845608 * x * (1.0 + 0.044715 * x * x)))
 
 
-BY_NAME = {"squared_relu": squared_relu, "quick_gelu": quick_gelu, "fast_gelu": fast_gelu, "relu": torch.relu,
+def openai_gelu(x: torch.Tensor) -> torch.Tensor:
+    """The tanh approximation of GELU (``--openai-gelu``; reference: megatron/legacy/model/utils.py:52)."""
+    return F.gelu(x, approximate="tanh")
+
+
+BY_NAME = {"openai_gelu": openai_gelu, "squared_relu": squared_relu, "quick_gelu": quick_gelu, "fast_gelu": fast_gelu, "relu": torch.relu,
            "silu": F.silu, "gelu": F.gelu}

@@ -505,6 +505,7 @@ class DistributedDataParallelConfig:
     reuse_grad_buf_for_mxfp8_param_ag: bool = False
     use_custom_fsdp: bool = False
     use_torch_fsdp2: bool = False
+    torch_fsdp2_reshard_after_forward: bool = True
     data_parallel_sharding_strategy: str = "no_shard"
     gradient_reduce_div_fusion: bool = True
     suggested_communication_unit_size: Optional[int] = None

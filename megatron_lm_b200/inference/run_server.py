@@ -91,7 +91,8 @@ def main(argv=None, serve: bool = True, tokenizer=None):
         tokenizer = build_tokenizer(args)
         if args.padded_vocab_size is None:
             args.padded_vocab_size = getattr(tokenizer, "vocab_size", None)
-    server = MegatronServer(build_engine(args, tokenizer), max_batch=args.max_batch_size)
+    server = MegatronServer(build_engine(args, tokenizer), max_batch=args.max_batch_size,
+                            max_tokens_to_oom=getattr(args, "max_tokens_to_oom", None))
     if serve:
         print(f" > serving on {args.host}:{args.port}", flush=True)
         server.run(args.host, args.port)

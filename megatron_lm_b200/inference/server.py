@@ -142,8 +142,10 @@ def generate_and_post_process(engine, req: dict):
 
 
 class MegatronServer:
-    def __init__(self, engine, max_batch: int = 128):
-        self.engine, self.max_batch = engine, max_batch
+    def __init__(self, engine, max_batch: int = 128, max_tokens_to_oom: Optional[int] = None):
+        """``max_tokens_to_oom``: a request whose batch x (longest prompt + tokens to generate) exceeds it is refused
+        instead of being allowed to exhaust memory (reference: text_generation/generation.py --max-tokens-to-oom)."""
+        self.engine, self.max_batch, self.max_tokens_to_oom = engine, max_batch, max_tokens_to_oom
         self.lock = threading.Lock()
 
     def handle(self, body: bytes):
@@ -154,6 +156,12 @@ class MegatronServer:
         err, norm = validate_request(req, self.max_batch)
         if err:
             return 400, {"message": err}
+        if self.max_tokens_to_oom is not None:
+            tok = getattr(self.engine, "tokenizer", None)
+            longest = max(len(tok.tokenize(p)) if tok is not None else len(p.split()) for p in norm["prompts"])
+            total = len(norm["prompts"]) * (longest + norm["tokens_to_generate"])
+            if total > self.max_tokens_to_oom:
+                return 400, {"message": f"Too many tokens.  {total} is greater than {self.max_tokens_to_oom}"}
         with self.lock:                       # one generation at a time, like the reference
             try:
                 return 200, generate_and_post_process(self.engine, norm)

@@ -467,6 +467,8 @@ class TorchFullyShardedDataParallel(nn.Module):
         if group is not None:
             from torch.distributed.device_mesh import DeviceMesh
             kw["mesh"] = DeviceMesh.from_group(group, "cuda" if torch.cuda.is_available() else "cpu")
+        if not getattr(ddp_config, "torch_fsdp2_reshard_after_forward", True):
+            kw["reshard_after_forward"] = False           # keep the gathered parameters until backward (more memory, no re-gather)
         for m in module.modules():
             if isinstance(m, tuple(sub_modules_to_wrap)):
                 fully_shard(m, **kw)

@@ -178,6 +178,18 @@ def validate_args(args, defaults: Optional[dict] = None):
         raise ValueError("--min-lr exceeds --lr")
     if args.save is not None and args.save_interval is None:
         raise ValueError("--save needs --save-interval")
+    # --data-args-path: a text file with what --data-path would hold; --per-split-data-args-path: a JSON file with
+    # "train" / "valid" / "test" lists (reference: training/arguments.py data group, utils.get_blend_and_blend_per_split)
+    if getattr(args, "data_args_path", None):
+        with open(args.data_args_path) as f:
+            args.data_path = f.read().split()
+    if getattr(args, "per_split_data_args_path", None):
+        import json as _json
+        with open(args.per_split_data_args_path) as f:
+            per = _json.load(f)
+        for split in ("train", "valid", "test"):
+            if per.get(split):
+                setattr(args, f"{split}_data_path", [str(x) for x in per[split]])
     # one corpus (or mock data) without an explicit split: the customary 969 / 30 / 1 parts
     if getattr(args, "split", None) is None and (getattr(args, "mock_data", False) or getattr(args, "data_path", None)) \
             and not getattr(args, "train_data_path", None):
@@ -251,7 +263,6 @@ UNUSED_FLAGS = {
     "deprecated_use_mcore_models": (_W, "deprecated in the reference"),
     "use_legacy_models": (_R, "the legacy model classes are not built"),
     "checkpoint_activations": (_R, "deprecated: use --recompute-granularity full --recompute-method uniform"),
-    "openai_gelu": (_R, "the tanh-approximated GELU variant is not built"),
     "onnx_safe": (_W, "no ONNX export path"),
     "nccl_all_reduce_for_prefill": (_W, "inference prefill uses the same collectives as training"),
     "scatter_gather_tensors_in_pipeline": (_W, "pipeline transfers always carry the sequence-parallel shard"),
@@ -266,7 +277,6 @@ UNUSED_FLAGS = {
     "kitchen_recipe_number": (_R, "the Kitchen quantisation back end is not built"),
     # inference engine knobs read by the engines' own constructors, not from the training arguments
     "inference_batch_times_seqlen_threshold": (_W, "inference uses no pipelined micro-batching threshold"),
-    "max_tokens_to_oom": (_W, "the engines size their buffers from the context they are given"),
     "output_bert_embeddings": (_R, "BERT embedding extraction is not built"),
     "bert_embedder_type": (_W, "only used with --output-bert-embeddings"),
     "inference_dynamic_batching_num_cuda_graphs": (_W, "the dynamic engine captures no graphs"),
@@ -282,9 +292,7 @@ UNUSED_FLAGS = {
     "block_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
     "embedding_path": (_R, "the inverse-cloze program builds no block-embedding index"), "indexer_batch_size": (_W, "the inverse-cloze program builds no block-embedding index"),
     "indexer_log_interval": (_W, "the inverse-cloze program builds no block-embedding index"),
-    "classes_fraction": (_W, "the image-folder dataset reads every class"),
-    "data_per_class_fraction": (_W, "the image-folder dataset reads every image of a class"),
-    "data_sharding": (_W, "the sampler always gives each data-parallel rank its own part"), "head_lr_mult": (_W, "the vision heads train with the backbone's learning rate"),
+    "data_sharding": (_W, "the sampler always gives each data-parallel rank its own part"),
     "vision_pretraining_type": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice"),
     "vision_pretraining": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice; the flag selects nothing"),
     "vision_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
@@ -301,16 +309,12 @@ UNUSED_FLAGS = {
     "inprocess_completion_timeout": (_W, "one timeout: --inprocess-barrier-timeout"),
     "inprocess_last_call_wait": (_W, "no last-call phase"), "inprocess_termination_grace_time": (_W, "no external monitor process"),
     "inprocess_granularity": (_W, "restarts are per rank"), "inprocess_active_world_size": (_R, "spare ranks are not built"),
-    "inprocess_empty_cuda_cache": (_W, "the cache is kept across attempts"),
     "one_logger_project": (_W, "the one-logger adapter records locally"), "one_logger_run_name": (_W, "the one-logger adapter records locally"),
     "one_logger_async": (_W, "the one-logger adapter records locally"), "app_tag_run_name": (_W, "the one-logger adapter records locally"),
     "app_tag_run_version": (_W, "the one-logger adapter records locally"),
-    "calc_ft_timeouts": (_W, "heartbeat timeouts are fixed"),
     "log_throughput": (_W, "throughput is part of every log line"),
-    "result_rejected_tracker_filename": (_W, "rejections are reported on the console"),
     "adlr_autoresume_interval": (_W, "no cluster auto-resume service"),
     # checkpoint options
-    "save_retain_interval": (_W, "no checkpoint is deleted"),
     "load_main_params_from_ckpt": (_R, "loading fp32 main parameters separately is not built"),
     "non_persistent_local_ckpt_dir": (_W, "local checkpoints live in memory (erasure-coded), not in a directory"),
     "non_persistent_local_ckpt_algo": (_W, "the in-memory checkpoint has one algorithm (erasure coding)"),
@@ -320,18 +324,14 @@ UNUSED_FLAGS = {
     "use_dist_ckpt_deprecated": (_W, "deprecated in the reference"), "dist_ckpt_format_deprecated": (_W, "deprecated in the reference"),
     "use_persistent_ckpt_worker": (_W, "asynchronous saves use one background thread"),
     "auto_detect_ckpt_format": (_W, "the format of a checkpoint is always detected at load"),
-    "ckpt_convert_format": (_R, "convert with python -m megatron_lm_b200.checkpoint.convert"),
-    "ckpt_convert_save": (_R, "convert with python -m megatron_lm_b200.checkpoint.convert"),
     "ckpt_convert_update_legacy_dist_opt_format": (_R, "the legacy distributed-optimizer format is not read"),
     "ckpt_fully_parallel_save_deprecated": (_W, "sharded saves are always spread over the data-parallel ranks"),
     "ckpt_fully_parallel_save": (_W, "sharded saves are always spread over the data-parallel ranks"),
     "ckpt_fully_parallel_load": (_W, "sharded loads read each piece once per data-parallel group"),
     "ckpt_assume_constant_structure": (_W, "no save-plan cache"),
     "load_model_opt_format": (_R, "ModelOpt checkpoints are not read"),
-    "torch_fsdp2_reshard_after_forward": (_W, "FSDP2 keeps its default resharding"),
     "replication_jump": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
     "replication_factor": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
-    "data_args_path": (_R, "give the data paths on the command line"), "per_split_data_args_path": (_R, "give the data paths on the command line"),
     "heterogeneous_layers_config_path": (_R, "build heterogeneous models through models.heterogeneous"),
     "heterogeneous_layers_config_encoded_json": (_R, "build heterogeneous models through models.heterogeneous"),
 }
@@ -390,7 +390,8 @@ def core_transformer_config_from_args(args, config_class=None) -> TransformerCon
         layernorm_epsilon=getattr(args, "norm_epsilon", 1e-5),
         layernorm_zero_centered_gamma=getattr(args, "apply_layernorm_1p", False),
         gated_linear_unit=bool(args.swiglu), activation_func="silu" if args.swiglu else
-        ("squared_relu" if getattr(args, "squared_relu", False) else "gelu"),
+        ("squared_relu" if getattr(args, "squared_relu", False) else
+         ("openai_gelu" if getattr(args, "openai_gelu", False) else "gelu")),
         add_bias_linear=getattr(args, "add_bias_linear", True),
         bias_activation_fusion=getattr(args, "bias_gelu_fusion", True), position_embedding_type=args.position_embedding_type,
         rotary_percent=getattr(args, "rotary_percent", 1.0), rotary_base=getattr(args, "rotary_base", 10000),

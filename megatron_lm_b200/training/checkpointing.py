@@ -268,6 +268,26 @@ def _write_tracker(save_dir: str, iteration: int) -> None:
             f.write(str(iteration))
 
 
+def cleanup_old_checkpoints(save_dir: str, iteration: int, retain_interval: Optional[int]) -> List[int]:
+    """--save-retain-interval N: once iteration ``iteration`` is safely written, every older ``iter_*`` directory
+    whose iteration is not a multiple of N is deleted (the newest checkpoint always stays).  Rank 0 only; returns the
+    iterations removed (reference: megatron/training/checkpointing.py, save_retain_interval clean-up)."""
+    if not retain_interval or (dist.is_initialized() and dist.get_rank() != 0) or not os.path.isdir(save_dir):
+        return []
+    import re as _re
+    import shutil
+    removed = []
+    for name in os.listdir(save_dir):
+        m = _re.match(r"^iter_(\d+)$", name)
+        if not m:
+            continue
+        it = int(m.group(1))
+        if it < iteration and it % retain_interval != 0:
+            shutil.rmtree(os.path.join(save_dir, name), ignore_errors=True)
+            removed.append(it)
+    return sorted(removed)
+
+
 # ----------------------------------------------------------------------------- sharded data parallel (FSDP) models
 def _is_fsdp_optimizer(optimizer) -> bool:
     from ..parallel.fsdp import ShardedAdam, TorchOptimizerAdapter
@@ -413,6 +433,8 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
         _write_tracker(save_dir, iteration)
     else:
         raise ValueError(f"unknown checkpoint format {fmt}")
+    if not non_persistent and not getattr(args, "async_save", False):
+        cleanup_old_checkpoints(save_dir, iteration, getattr(args, "save_retain_interval", None))
     stats["total_s"] = time.time() - t0
     return stats
 

@@ -271,6 +271,11 @@ def _teardown_attempt():
     except Exception:
         pass
     from .global_vars import unset_global_variables
+    try:
+        if getattr(get_args(), "inprocess_empty_cuda_cache", False) and torch.cuda.is_available():
+            torch.cuda.empty_cache()
+    except Exception:
+        pass
     unset_global_variables()
 
 
@@ -349,7 +354,14 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     ocfg, dcfg = optimizer_config_from_args(args), ddp_config_from_args(args)
     timers("model-and-optimizer-setup", 0).start(barrier=True)
     model = get_model(lambda **kw: model_provider(config=config, **kw), config, dcfg)
-    optimizer = build_optimizer(ocfg, model)
+    head_mult = getattr(args, "head_lr_mult", 1.0) or 1.0
+    if head_mult != 1.0:
+        # --head-lr-mult: the task heads (classification / decoder heads of the vision programs) learn at a multiple
+        # of the backbone's rate (reference: pretrain_vision_classify.py scale_lr_cond)
+        optimizer = build_optimizer(ocfg, model, scale_lr_cond=lambda name, p: "head" in name or "linear_decoder" in name,
+                                    lr_mult=head_mult)
+    else:
+        optimizer = build_optimizer(ocfg, model)
     scheduler = get_optimizer_param_scheduler(
         optimizer, lr=args.lr, min_lr=args.min_lr, lr_decay_style=args.lr_decay_style, train_iters=args.train_iters,
         global_batch_size=args.global_batch_size, lr_decay_iters=args.lr_decay_iters,
@@ -374,6 +386,20 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     elif args.load is not None:
         iteration, flops_so_far = checkpointing.load_checkpoint(model, optimizer, scheduler, args)
         args.consumed_train_samples = iteration * args.global_batch_size
+    if getattr(args, "ckpt_convert_format", None):
+        # load in whatever format the checkpoint has, write it again in the requested one, stop
+        # (reference: training/training.py --ckpt-convert-format / --ckpt-convert-save)
+        out_dir = getattr(args, "ckpt_convert_save", None)
+        if args.load is None or out_dir is None:
+            raise SystemExit("--ckpt-convert-format needs --load and --ckpt-convert-save")
+        conv = argparse_namespace_copy(args, ckpt_format=args.ckpt_convert_format, save=os.path.join(out_dir, args.ckpt_convert_format),
+                                       async_save=False)
+        checkpointing.save_checkpoint(iteration, model, optimizer, scheduler, conv,
+                                      num_floating_point_operations_so_far=flops_so_far)
+        print_rank_0(f"converted the checkpoint of iteration {iteration} to {args.ckpt_convert_format} in {conv.save}")
+        if dist.is_initialized():
+            dist.barrier()
+        sys.exit(0)
     if iteration == 0 and getattr(args, "pretrained_checkpoint", None):
         # nothing to resume from: start from the weights of a pre-trained checkpoint (no optimizer state, no
         # iteration count), as --finetune does (reference: training/checkpointing.py load of pretrained_checkpoint)
@@ -410,6 +436,7 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
     inj = RerunErrorInjector(getattr(args, "error_injection_rate", 0) or 0,
                              getattr(args, "error_injection_type", None) or "transient_error")
     rerun = RerunStateMachine(mode=getattr(args, "rerun_mode", None) or "disabled", error_injector=inj)
+    rerun.rejected_tracker_filename = getattr(args, "result_rejected_tracker_filename", None)
     set_rerun_state_machine(rerun)
     sig = DistributedSignalHandler().__enter__() if getattr(args, "exit_signal_handler", False) else None
     straggler = None
@@ -632,7 +659,8 @@ def pretrain(train_valid_test_datasets_provider: Callable, model_provider: Calla
         prof.stop()
     if heart is not None:
         heart.end_section()
-        heart.calculate_and_persist_timeouts()
+        if getattr(args, "calc_ft_timeouts", False):
+            heart.calculate_and_persist_timeouts()
         heart.shutdown()
     if energy is not None:
         print_rank_last(f" total energy: {energy.get_total():.1f} J")

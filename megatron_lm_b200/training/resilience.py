@@ -228,6 +228,20 @@ class RerunStateMachine:
         self.first_result = None
         return False
 
+    def _track_rejection(self, value: float, message: str, injected: bool) -> None:
+        """--result-rejected-tracker-filename: one JSON line per rejected result (iteration, rank, value, reason), so
+        that a scheduler can spot the device that keeps producing them (reference: rerun_state_machine.py:700-760)."""
+        path = getattr(self, "rejected_tracker_filename", None)
+        if not path:
+            return
+        rec = {"step": self.step, "rank": dist.get_rank() if dist.is_initialized() else 0, "value": value,
+               "message": message, "injected": bool(injected), "time": time.time()}
+        try:
+            with open(path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+        except OSError:
+            pass
+
     # -- validation ---------------------------------------------------------------
     def validate_result(self, result, rejection_func: Callable[[Any], bool], message: str = "unexpected result",
                         tolerance: float = 0.0, fatal: bool = True) -> None:
@@ -256,6 +270,7 @@ class RerunStateMachine:
                 self.rerun_requested = True
                 self._suspect_idx = idx
                 self.suspicious_device = f"rank {dist.get_rank() if dist.is_initialized() else 0}"
+                self._track_rejection(val, message, injected)
         elif self.state == RerunState.RERUNNING_IN_PLACE:
             if self.mode == RerunMode.REPORT_DETERMINISM_STATS:
                 first = self._first_results.get(idx, self.first_result)

@@ -52,11 +52,18 @@ class MockImageDataset(torch.utils.data.Dataset):
 
 
 class ImageFolderDataset(torch.utils.data.Dataset):
-    def __init__(self, root, c, h, w, n=0):
+    def __init__(self, root, c, h, w, n=0, classes_fraction=1.0, data_per_class_fraction=1.0):
+        """``classes_fraction`` keeps the first part of the (sorted) classes, ``data_per_class_fraction`` the first
+        part of every class's (sorted) files (reference: megatron/legacy/data/image_folder.py:80-140)."""
         self.c, self.h, self.w = c, h, w
         classes = sorted(d for d in os.listdir(root) if os.path.isdir(os.path.join(root, d)))
-        self.items = [(os.path.join(root, k, f), i) for i, k in enumerate(classes)
-                      for f in sorted(os.listdir(os.path.join(root, k)))]
+        classes = classes[:max(1, int(len(classes) * classes_fraction))]
+        self.classes = classes
+        self.items = []
+        for i, k in enumerate(classes):
+            files = sorted(os.listdir(os.path.join(root, k)))
+            files = files[:max(1, int(len(files) * data_per_class_fraction))]
+            self.items.extend((os.path.join(root, k, f), i) for f in files)
         if not self.items:
             raise ValueError(f"no images under {root}")
         self.n = n or len(self.items)
@@ -113,7 +120,9 @@ def train_valid_test_datasets_provider(num_samples):
     out = []
     for n, sub in zip(num_samples, ("train", "val", "test")):
         d = os.path.join(root, sub)
-        out.append(ImageFolderDataset(d, *shape, n) if n and os.path.isdir(d) else None)
+        out.append(ImageFolderDataset(d, *shape, n, getattr(args, "classes_fraction", 1.0),
+                                      getattr(args, "data_per_class_fraction", 1.0) if sub == "train" else 1.0)
+                   if n and os.path.isdir(d) else None)
     return tuple(out)
 
 

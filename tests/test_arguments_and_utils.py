@@ -289,11 +289,11 @@ def test_unused_flags_warn_or_refuse():
             "--max-position-embeddings", "16", "--micro-batch-size", "1", "--train-iters", "1", "--lr", "1e-3"]
     with warnings.catch_warnings(record=True) as w:
         warnings.simplefilter("always")
-        args = parse_args(argv=base + ["--use-flash-attn", "--save-retain-interval", "10"])
+        args = parse_args(argv=base + ["--use-flash-attn", "--adlr-autoresume-interval", "10"])
         args.world_size, args.rank = 1, 0
         validate_args(args)
     msgs = [str(x.message) for x in w]
-    assert any("--use-flash-attn" in m for m in msgs) and any("--save-retain-interval" in m for m in msgs)
+    assert any("--use-flash-attn" in m for m in msgs) and any("--adlr-autoresume-interval" in m for m in msgs)
     # defaults do not warn
     with warnings.catch_warnings(record=True) as w:
         warnings.simplefilter("always")
@@ -302,7 +302,7 @@ def test_unused_flags_warn_or_refuse():
         validate_args(args)
     assert not [x for x in w if "has no effect here" in str(x.message)]
     # a flag that would change the layout or the numerics stops the run
-    for extra in (["--use-legacy-models"], ["--openai-gelu"], ["--lazy-mpu-init", "true"]):
+    for extra in (["--use-legacy-models"], ["--checkpoint-activations"], ["--lazy-mpu-init", "true"]):
         args = parse_args(argv=base + extra)
         args.world_size, args.rank = 1, 0
         with pytest.raises(ValueError, match="not supported"):
@@ -334,3 +334,46 @@ def test_unsupported_config_fields_are_refused():
         assert name in UNSUPPORTED_FIELDS
         with pytest.raises(ValueError, match="not supported"):
             TransformerConfig(**base, **{name: value})
+
+
+def test_flags_that_used_to_do_nothing(tmp_path, monkeypatch):
+    """--openai-gelu, --data-args-path / --per-split-data-args-path, --save-retain-interval, the rejected-result
+    tracker file, the server's token limit."""
+    import os
+    import torch.nn.functional as F
+    from megatron_lm_b200.activations import BY_NAME
+    a = A.validate_args(_args(["--openai-gelu"], monkeypatch=monkeypatch))
+    assert A.core_transformer_config_from_args(a).activation_func == "openai_gelu"
+    x = torch.linspace(-3, 3, 13)
+    assert torch.allclose(BY_NAME["openai_gelu"](x), F.gelu(x, approximate="tanh"))
+    assert not torch.allclose(BY_NAME["openai_gelu"](x), F.gelu(x), atol=1e-6)
+    (tmp_path / "paths.txt").write_text("0.3 /data/a\n0.7 /data/b\n")
+    (tmp_path / "split.json").write_text(json.dumps({"train": ["/d/t"], "valid": ["0.5", "/d/v1", "0.5", "/d/v2"]}))
+    a = A.validate_args(_args(["--data-args-path", str(tmp_path / "paths.txt")], monkeypatch=monkeypatch))
+    assert a.data_path == ["0.3", "/data/a", "0.7", "/data/b"]
+    a = A.validate_args(_args(["--per-split-data-args-path", str(tmp_path / "split.json")], monkeypatch=monkeypatch))
+    assert a.train_data_path == ["/d/t"] and a.valid_data_path == ["0.5", "/d/v1", "0.5", "/d/v2"]
+    # retained checkpoints: multiples of the interval and the newest
+    from megatron_lm_b200.training.checkpointing import cleanup_old_checkpoints
+    for it in (2, 4, 6, 8, 10):
+        os.makedirs(tmp_path / "ck" / f"iter_{it:07d}")
+    os.makedirs(tmp_path / "ck" / "release")
+    assert cleanup_old_checkpoints(str(tmp_path / "ck"), 10, 4) == [2, 6]
+    assert sorted(os.listdir(tmp_path / "ck")) == ["iter_0000004", "iter_0000008", "iter_0000010", "release"]
+    assert cleanup_old_checkpoints(str(tmp_path / "ck"), 10, None) == []
+    # rejected results are written down
+    from megatron_lm_b200.training.resilience import RerunStateMachine
+    m = RerunStateMachine("validate_results")
+    m.rejected_tracker_filename = str(tmp_path / "rejected.jsonl")
+    assert m.should_run_forward_backward(None)
+    m.validate_result(torch.tensor(float("nan")), lambda v: bool(torch.isnan(v)), "NaN loss")
+    rec = json.loads(open(tmp_path / "rejected.jsonl").read().splitlines()[0])
+    assert rec["message"] == "NaN loss" and rec["rank"] == 0 and not rec["injected"]
+    # the server refuses requests that would need more tokens than allowed
+    from megatron_lm_b200.inference.server import MegatronServer
+
+    class Eng:
+        tokenizer = None
+    srv = MegatronServer(Eng(), max_tokens_to_oom=40)
+    code, resp = srv.handle(json.dumps({"prompts": ["a b c d", "e f"], "tokens_to_generate": 20}).encode())
+    assert code == 400 and "Too many tokens" in resp["message"] and "48" in resp["message"]

@@ -421,3 +421,37 @@ def test_moe_run_upcycled_from_a_dense_checkpoint(tmp_path):
                              text=True, timeout=200, cwd=ROOT,
                              env=dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29619"))
     assert refused.returncode != 0 and "already holds a checkpoint" in refused.stdout + refused.stderr
+
+
+def test_checkpoint_format_conversion_and_retained_checkpoints(tmp_path):
+    ck, out = str(tmp_path / "ck"), str(tmp_path / "conv")
+    _run(["--save", ck, "--save-interval", "2", "--save-retain-interval", "4", "--train-iters", "8", "--exit-interval", "7",
+          "--eval-interval", "1000"])
+    kept = sorted(d for d in os.listdir(ck) if d.startswith("iter_"))
+    assert kept == ["iter_0000004", "iter_0000007"], kept              # multiples of 4 and the newest
+    conv = _run(["--load", ck, "--ckpt-convert-format", "torch", "--ckpt-convert-save", out, "--train-iters", "8"])
+    assert "converted the checkpoint of iteration 7 to torch" in conv and not _iters(conv)
+    assert os.path.isfile(os.path.join(out, "torch", "iter_0000007", "mp_rank_00", "model_optim_rng.pt"))
+    resumed = _iters(_run(["--load", os.path.join(out, "torch"), "--train-iters", "8", "--eval-interval", "1000"]))
+    again = _iters(_run(["--load", ck, "--train-iters", "8", "--eval-interval", "1000"]))
+    assert sorted(resumed) == [8] and abs(resumed[8][1] - again[8][1]) < 1e-5
+
+
+def test_vision_classifier_head_learning_rate_and_dataset_fractions(tmp_path):
+    import numpy as np
+    root = tmp_path / "imgs"
+    rng = np.random.RandomState(0)
+    for split, per in (("train", 6), ("val", 2)):
+        for k in range(4):
+            d = root / split / f"class{k}"
+            d.mkdir(parents=True)
+            for i in range(per):
+                np.save(d / f"{i}.npy", (rng.rand(3, 32, 32) + 0.5 * k).astype(np.float32))
+    sys.path.insert(0, ROOT)
+    import pretrain_vision_classify as prog
+    ds = prog.ImageFolderDataset(str(root / "train"), 3, 32, 32, 0, classes_fraction=0.5, data_per_class_fraction=0.5)
+    assert ds.classes == ["class0", "class1"] and len(ds.items) == 2 * 3
+    out = _program("pretrain_vision_classify.py", ["--train-iters", "3", "--eval-interval", "1000", "--head-lr-mult", "10",
+                                                   "--data-path", str(root), "--classes-fraction", "0.5"])
+    out = out.replace("--mock-data", "")
+    assert sorted(_iters(out, "loss")) == [1, 2, 3]
