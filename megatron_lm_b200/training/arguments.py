@@ -318,9 +318,6 @@ UNUSED_FLAGS = {
     "load_main_params_from_ckpt": (_R, "loading fp32 main parameters separately is not built"),
     "non_persistent_local_ckpt_dir": (_W, "local checkpoints live in memory (erasure-coded), not in a directory"),
     "non_persistent_local_ckpt_algo": (_W, "the in-memory checkpoint has one algorithm (erasure coding)"),
-    "use_checkpoint_args": (_R, "arguments are not read back from checkpoints"),
-    "use_mp_args_from_checkpoint_args": (_R, "arguments are not read back from checkpoints"),
-    "use_tokenizer_model_from_checkpoint_args": (_W, "arguments are not read back from checkpoints"),
     "use_dist_ckpt_deprecated": (_W, "deprecated in the reference"), "dist_ckpt_format_deprecated": (_W, "deprecated in the reference"),
     "use_persistent_ckpt_worker": (_W, "asynchronous saves use one background thread"),
     "auto_detect_ckpt_format": (_W, "the format of a checkpoint is always detected at load"),

@@ -439,6 +439,59 @@ def save_checkpoint(iteration: int, model, optimizer, opt_param_scheduler, args,
     return stats
 
 
+_ARCH_ARGS = ("num_layers", "hidden_size", "ffn_hidden_size", "seq_length", "num_attention_heads", "num_query_groups",
+              "group_query_attention", "kv_channels", "max_position_embeddings", "position_embedding_type",
+              "rotary_percent", "rotary_base", "add_position_embedding", "swiglu", "squared_relu", "openai_gelu",
+              "normalization", "norm_epsilon", "apply_layernorm_1p", "untie_embeddings_and_output_weights",
+              "add_bias_linear", "add_qkv_bias", "qk_layernorm", "num_experts", "moe_router_topk", "moe_ffn_hidden_size",
+              "moe_layer_freq", "moe_shared_expert_intermediate_size", "moe_grouped_gemm", "multi_latent_attention",
+              "hybrid_override_pattern", "hybrid_attention_ratio", "hybrid_mlp_ratio", "mamba_state_dim",
+              "mamba_head_dim", "mamba_num_groups", "is_hybrid_model", "padded_vocab_size", "vocab_size",
+              "make_vocab_size_divisible_by", "mtp_num_layers", "window_size")
+_MP_ARGS = ("tensor_model_parallel_size", "pipeline_model_parallel_size", "virtual_pipeline_model_parallel_size",
+            "num_layers_per_virtual_pipeline_stage", "expert_model_parallel_size", "expert_tensor_parallel_size",
+            "context_parallel_size", "sequence_parallel")
+_TOKENIZER_ARGS = ("tokenizer_type", "tokenizer_model", "vocab_file", "merge_file", "tiktoken_pattern")
+
+
+def load_args_from_checkpoint(args, load_dir: Optional[str] = None) -> bool:
+    """--use-checkpoint-args: take the model's architecture from the arguments stored in the checkpoint, so that a
+    run needs ``--load`` only; --use-mp-args-from-checkpoint-args adds the parallel layout,
+    --use-tokenizer-model-from-checkpoint-args the tokenizer files.  Returns False when there is no checkpoint.
+    Reference: megatron/training/checkpointing.py:1075-1210 ``load_args_from_checkpoint``."""
+    load_dir = load_dir or getattr(args, "load", None)
+    if load_dir is None:
+        return False
+    tracker = get_checkpoint_tracker_filename(load_dir)
+    if not os.path.isfile(tracker):
+        return False
+    iteration, release = read_metadata(tracker)
+    base = get_checkpoint_name(load_dir, iteration, release, return_base_dir=True)
+    if ds.check_is_distributed_checkpoint(base):
+        saved = ds.load_common_state_dict(base).get("args")
+    else:
+        name = get_checkpoint_name(load_dir, iteration, release, tp_rank=0, pp_rank=0)
+        if not os.path.isfile(name):
+            cands = sorted(d for d in os.listdir(base) if d.startswith("mp_rank_00"))
+            if not cands:
+                return False
+            name = os.path.join(base, cands[0], "model_optim_rng.pt")
+        saved = torch.load(name, map_location="cpu", weights_only=False).get("args")
+    if saved is None:
+        return False
+    get = saved.get if isinstance(saved, dict) else (lambda k, d=None: getattr(saved, k, d))
+    names = list(_ARCH_ARGS)
+    if getattr(args, "use_mp_args_from_checkpoint_args", False):
+        names += list(_MP_ARGS)
+    if getattr(args, "use_tokenizer_model_from_checkpoint_args", True):
+        names += list(_TOKENIZER_ARGS)
+    for k in names:
+        v = get(k, None)
+        if v is not None:
+            setattr(args, k, v)
+    return True
+
+
 def load_checkpoint(model, optimizer, opt_param_scheduler, args, *, load_dir: Optional[str] = None,
                     strict: bool = True):
     """Returns (iteration, num_floating_point_operations_so_far).  (0, 0) when nothing to load."""

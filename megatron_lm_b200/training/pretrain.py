@@ -59,6 +59,9 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
     if getattr(args, "yaml_cfg", None):
         from .arguments import load_yaml_args
         args = load_yaml_args(args.yaml_cfg, args)
+    if getattr(args, "use_checkpoint_args", False) or getattr(args, "use_mp_args_from_checkpoint_args", False):
+        if not checkpointing.load_args_from_checkpoint(args):
+            raise SystemExit("--use-checkpoint-args: no checkpoint with stored arguments under --load")
     validate_args(args, args_defaults)
     set_args(args)
     from ..utils.log_handler import setup_logging

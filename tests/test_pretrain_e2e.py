@@ -455,3 +455,19 @@ def test_vision_classifier_head_learning_rate_and_dataset_fractions(tmp_path):
                                                    "--data-path", str(root), "--classes-fraction", "0.5"])
     out = out.replace("--mock-data", "")
     assert sorted(_iters(out, "loss")) == [1, 2, 3]
+
+
+def test_architecture_is_read_back_from_the_checkpoint(tmp_path):
+    """--use-checkpoint-args: a run that names only the checkpoint resumes the model that was saved."""
+    ck = str(tmp_path / "ck")
+    _run(["--save", ck, "--exit-interval", "4", "--swiglu", "--normalization", "RMSNorm", "--disable-bias-linear",
+          "--position-embedding-type", "rope", "--untie-embeddings-and-output-weights", "--ffn-hidden-size", "48"])
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29618")
+    # wrong sizes on the command line: the stored ones win
+    cmd = [sys.executable, os.path.join(ROOT, "pretrain_gpt.py"), "--load", ck, "--use-checkpoint-args", "--num-layers", "5",
+           "--hidden-size", "64", "--num-attention-heads", "8", "--micro-batch-size", "2", "--global-batch-size", "4",
+           "--train-iters", "8", "--lr", "1e-3", "--min-lr", "1e-4", "--lr-decay-style", "cosine", "--mock-data",
+           "--log-interval", "1", "--eval-interval", "1000", "--eval-iters", "0", "--use-cpu-initialization"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert sorted(_iters(r.stdout)) == [5, 6, 7, 8]
