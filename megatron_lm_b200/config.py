@@ -303,6 +303,9 @@ class TransformerConfig(ModelParallelConfig):
     use_mamba_mem_eff_path: bool = True
     mlp_chunks_for_prefill: int = 1
     heterogeneous_block_specs: bool = False
+    # per-layer block configuration (JSON text, the format of models/heterogeneous.py): layers may drop or replace
+    # their attention / MLP and choose their own widths
+    heterogeneous_layers_config_encoded_json: Optional[str] = None
     hetereogenous_dist_checkpoint: bool = False
     quant_recipe: Any = None
 

@@ -538,6 +538,14 @@ class TransformerBlock(nn.Module):
             raise TypeError(f"unsupported transformer layer spec {type(spec).__name__}")
 
         layers = []
+        hetero = getattr(config, "heterogeneous_layers_config_encoded_json", None)
+        if hetero:
+            # every layer from its own block configuration (attention / MLP absent, linear, or of another width)
+            from .heterogeneous import build_heterogeneous_layers
+            if not causal or cross_attention:
+                raise NotImplementedError("heterogeneous layer configurations are for decoder-only models")
+            layers = list(build_heterogeneous_layers(config, hetero, offset=self.layer_offset, count=n))
+            n = 0
         for i in range(n):
             ls = layer_spec(i)
             cls = get_module(ls) if ls is not None else TransformerLayer

@@ -329,8 +329,6 @@ UNUSED_FLAGS = {
     "load_model_opt_format": (_R, "ModelOpt checkpoints are not read"),
     "replication_jump": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
     "replication_factor": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
-    "heterogeneous_layers_config_path": (_R, "build heterogeneous models through models.heterogeneous"),
-    "heterogeneous_layers_config_encoded_json": (_R, "build heterogeneous models through models.heterogeneous"),
 }
 
 
@@ -399,6 +397,9 @@ def core_transformer_config_from_args(args, config_class=None) -> TransformerCon
                       and len(args.cp_comm_type) == 1 else getattr(args, "cp_comm_type", None)),
     )
     kw = _copy_fields(cls, args, ov)
+    if getattr(args, "heterogeneous_layers_config_path", None) and not kw.get("heterogeneous_layers_config_encoded_json"):
+        with open(args.heterogeneous_layers_config_path) as f:
+            kw["heterogeneous_layers_config_encoded_json"] = f.read()
     for k in ("init_method", "output_layer_init_method", "embedding_init_method", "timers", "finalize_model_grads_func",
               "grad_scale_func", "no_sync_func", "grad_sync_func", "param_sync_func", "_cpu_offloading_context"):
         kw.pop(k, None)

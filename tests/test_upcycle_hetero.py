@@ -72,3 +72,34 @@ def test_upcycled_model_reproduces_the_dense_model():
     dense, moe = _dense_and_moe(1)
     with pytest.raises(ValueError):
         upcycle_model(dense, moe, granularity=3)
+
+
+def test_gpt_model_from_a_heterogeneous_block_configuration(tmp_path):
+    """The block configuration reaches the model through the transformer config (and the command line): pipeline
+    stages take their slice of it, and the model trains."""
+    from megatron_lm_b200.models.gpt import GPTModel
+    from megatron_lm_b200.training import arguments as A
+    blocks = {"block_configs": [
+        {"attention": {"n_heads_in_group": 2}, "ffn": {"intermediate_size": 48}},
+        {"attention": {"no_op": True}, "ffn": {"replace_with_linear": True}},
+        {"attention": {"replace_with_linear": True}, "ffn": {"no_op": True}},
+        {"attention": {}, "ffn": {"ffn_mult": 1.0}}]}
+    path = tmp_path / "blocks.json"
+    path.write_text(json.dumps(blocks))
+    args = A.parse_args(argv=["--num-layers", "4", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "16",
+                              "--micro-batch-size", "1", "--train-iters", "1", "--lr", "1e-3",
+                              "--heterogeneous-layers-config-path", str(path), "--use-cpu-initialization",
+                              "--attention-dropout", "0", "--hidden-dropout", "0"])
+    args.world_size, args.rank = 1, 0
+    args = A.validate_args(args)
+    cfg = A.core_transformer_config_from_args(args)
+    assert json.loads(cfg.heterogeneous_layers_config_encoded_json) == blocks
+    m = GPTModel(cfg, 64, 16, parallel_output=False)
+    layers = m.decoder.layers
+    assert len(layers) == 4 and layers[0].mlp.linear_fc1.weight.shape[0] == 48
+    assert not hasattr(layers[1], "self_attention") and not hasattr(layers[2], "mlp")
+    assert layers[3].mlp.linear_fc1.weight.shape[0] == 256          # 2/3 * 32 rounded up to a multiple of 256
+    ids = torch.randint(0, 64, (2, 16))
+    loss = m(ids, labels=ids).mean()
+    loss.backward()
+    assert torch.isfinite(loss) and layers[2].self_attention.linear.weight.grad is not None
