@@ -159,6 +159,8 @@ def validate_args(args, defaults: Optional[dict] = None):
     if getattr(args, "replication", False) and getattr(args, "non_persistent_ckpt_type", None) != "local":
         raise ValueError("--replication needs --non-persistent-ckpt-type local")
     # model sizes
+    if args.num_layers is None and (getattr(args, "decoder_num_layers", None) or getattr(args, "encoder_num_layers", None)):
+        args.num_layers = getattr(args, "decoder_num_layers", None) or args.encoder_num_layers
     for req in ("num_layers", "hidden_size", "num_attention_heads"):
         if getattr(args, req) is None:
             raise ValueError(f"--{req.replace('_', '-')} is required")
@@ -284,7 +286,6 @@ UNUSED_FLAGS = {
     "retro_add_retriever": (_W, "pretrain_retro.py always builds the retriever"),
     "retro_cyclic_train_iters": (_R, "cyclic Retro training is not built"),
     "retro_attention_gate": (_R, "the Retro attention gate is fixed at 1"),
-    "decoder_num_layers": (_R, "encoder-decoder layer split flags are not wired; use --num-layers"),
     "sample_rate": (_W, "the retriever evaluation tasks are not built"),
     "ict_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),
     "bert_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),

@@ -24,7 +24,19 @@ from megatron_lm_b200.training.resilience import validate_loss  # noqa: E402
 def model_provider(pre_process=True, post_process=True, vp_stage=None, config=None):
     args = get_args()
     print_rank_0("building T5 model ...")
-    return T5Model(config, vocab_size=args.padded_vocab_size, max_sequence_length=args.max_position_embeddings,
+    enc_cfg = None
+    enc_n, dec_n = getattr(args, "encoder_num_layers", None), getattr(args, "decoder_num_layers", None)
+    if enc_n or dec_n:
+        # --encoder-num-layers / --decoder-num-layers: stacks of different depth (one pipeline stage)
+        import copy
+        from megatron_lm_b200.parallel import state
+        if state.get_pipeline_model_parallel_world_size() > 1:
+            raise NotImplementedError("separate encoder / decoder depths with pipeline parallelism")
+        enc_cfg = copy.copy(config)
+        enc_cfg.num_layers = enc_n or config.num_layers
+        config = copy.copy(config)
+        config.num_layers = dec_n or config.num_layers
+    return T5Model(config, encoder_config=enc_cfg, vocab_size=args.padded_vocab_size, max_sequence_length=args.max_position_embeddings,
                    pre_process=pre_process, post_process=post_process, parallel_output=True,
                    share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights,
                    position_embedding_type=args.position_embedding_type, rotary_percent=args.rotary_percent)

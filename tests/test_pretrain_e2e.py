@@ -107,8 +107,10 @@ def test_bert_and_t5_programs_on_a_sentence_corpus(tmp_path):
     data = ["--data-path", prefix, "--split", "90,5,5", "--tokenizer-type", "BertWordPieceLowerCase", "--vocab-file", vocab]
     out = _run_script("pretrain_bert.py", data)
     assert "sop loss" in out
-    _run_script("pretrain_t5.py", data + ["--encoder-seq-length", "32", "--decoder-seq-length", "16",
-                                          "--vocab-extra-ids", "10"])
+    out = _run_script("pretrain_t5.py", data + ["--encoder-seq-length", "32", "--decoder-seq-length", "16",
+                                                "--vocab-extra-ids", "10", "--encoder-num-layers", "3",
+                                                "--decoder-num-layers", "1", "--log-params-norm"])
+    assert "params norm" in out
 
 
 def test_mamba_and_vlm_programs_on_mock_data():
