@@ -89,7 +89,7 @@ class ModelParallelConfig:
     cpu_offloading_num_layers: int = 0
     _cpu_offloading_context: Any = None
     cpu_offloading_activations: bool = True
-    cpu_offloading_weights: bool = True
+    cpu_offloading_weights: bool = False
     barrier_with_L1_time: bool = True
 
     def __post_init__(self):
@@ -118,7 +118,6 @@ class ModelParallelConfig:
 # only pick between implementations of the same mathematics (fusion switches, library back ends, CUDA-graph and
 # communication-overlap tuning knobs) are accepted without effect: there is one implementation here.
 UNSUPPORTED_FIELDS = {
-    "cpu_offloading": "activation / weight offloading to the host is not built",
     "fp8_dot_product_attention": "attention runs in bf16 / fp16",
     "fp8_multi_head_attention": "attention runs in bf16 / fp16",
     "delay_wgrad_compute": "weight gradients are computed with their layer's backward",
@@ -346,6 +345,13 @@ class TransformerConfig(ModelParallelConfig):
                 raise ValueError("num_moe_experts must be divisible by expert_model_parallel_size")
             if self.moe_ffn_hidden_size is None:
                 self.moe_ffn_hidden_size = self.ffn_hidden_size
+        if self.cpu_offloading:
+            if self.cpu_offloading_weights:
+                raise ValueError("cpu_offloading_weights is not supported: only activations are offloaded")
+            if self.recompute_granularity == "full":
+                raise ValueError("cpu_offloading and full activation recomputation exclude each other")
+            if not 0 < self.cpu_offloading_num_layers <= self.num_layers:
+                raise ValueError("cpu_offloading needs 0 < cpu_offloading_num_layers <= num_layers")
         if self.moe_router_topk_limited_devices and self.moe_router_num_groups is None:
             # older name of group-limited routing: one group per expert-parallel rank
             self.moe_router_num_groups = self.expert_model_parallel_size

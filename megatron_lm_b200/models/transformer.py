@@ -10,6 +10,7 @@ Activations are [s, b, h] throughout.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import List, Optional
 
@@ -598,10 +599,18 @@ class TransformerBlock(nn.Module):
                     else:
                         hidden_states = self.layers[i](hidden_states, rotary=rotary)
         else:
-            for layer in self.layers:
-                hidden_states = layer(hidden_states, rotary=rotary, inference_context=inference_context,
-                                      encoder_output=encoder_output, attention_mask=attention_mask,
-                                      enc_dec_attn_mask=enc_dec_attn_mask)
+            # cpu_offloading: what the first cpu_offloading_num_layers layers keep for backward lives in (pinned) host
+            # memory between the passes and comes back when backward reaches the layer
+            # (reference: megatron/core/extensions/transformer_engine.py get_cpu_offload_context)
+            n_off = cfg.cpu_offloading_num_layers if (cfg.cpu_offloading and self.training
+                                                      and torch.is_grad_enabled()) else 0
+            for i, layer in enumerate(self.layers):
+                ctx = torch.autograd.graph.save_on_cpu(pin_memory=hidden_states.is_cuda) if i < n_off \
+                    else contextlib.nullcontext()
+                with ctx:
+                    hidden_states = layer(hidden_states, rotary=rotary, inference_context=inference_context,
+                                          encoder_output=encoder_output, attention_mask=attention_mask,
+                                          enc_dec_attn_mask=enc_dec_attn_mask)
         if self.final_layernorm is not None:
             hidden_states = self.final_layernorm(hidden_states)
         return hidden_states

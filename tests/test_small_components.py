@@ -272,3 +272,38 @@ def test_layers_without_rotary_embedding_and_post_norm_residual():
         f, fb = layer.mlp(ln2)
         want = ln2 + f + (fb if fb is not None else 0)
         assert torch.allclose(layer(x), want, atol=1e-5)
+
+
+def test_activation_offloading_to_the_host_keeps_the_gradients():
+    """cpu_offloading: the saved tensors of the first layers pass through host memory; losses and gradients are
+    those of the plain run."""
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    base = dict(num_layers=3, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+                attention_dropout=0.0, use_cpu_initialization=True)
+    with pytest.raises(ValueError):
+        TransformerConfig(cpu_offloading=True, cpu_offloading_num_layers=0, **base)
+    with pytest.raises(ValueError):
+        TransformerConfig(cpu_offloading=True, cpu_offloading_num_layers=2, cpu_offloading_weights=True, **base)
+    ids = torch.randint(0, 32, (2, 16))
+    grads, packed = [], []
+    for off in (False, True):
+        torch.manual_seed(0)
+        cfg = TransformerConfig(cpu_offloading=off, cpu_offloading_num_layers=2 if off else 0, **base)
+        m = GPTModel(cfg, 32, 16, parallel_output=False).train()
+        real = torch.autograd.graph.save_on_cpu
+        calls = []
+
+        class Counting(real):
+            def __init__(self, *a, **kw):
+                calls.append(1)
+                super().__init__(*a, **kw)
+        torch.autograd.graph.save_on_cpu = Counting
+        try:
+            m(ids, labels=ids).mean().backward()
+        finally:
+            torch.autograd.graph.save_on_cpu = real
+        packed.append(len(calls))
+        grads.append({n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None})
+    assert packed == [0, 2]                                      # one offloading context per offloaded layer
+    assert grads[0].keys() == grads[1].keys() and all(torch.equal(grads[0][k], grads[1][k]) for k in grads[0])
