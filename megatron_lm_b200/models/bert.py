@@ -234,6 +234,18 @@ class BiEncoderModel(nn.Module):
     def set_input_tensor(self, t):
         pass
 
+    def init_from_bert(self, bert_state_dict) -> int:
+        """Start both towers from a pre-trained ``BertModel`` (embedding, encoder, pooler; the language-model and
+        binary heads are dropped).  Returns how many tensors were taken (reference: biencoder_model.py:138-190
+        ``init_state_dict_from_bert``)."""
+        taken = 0
+        for tower in {id(self.query_model): self.query_model, id(self.context_model): self.context_model}.values():
+            own = tower.state_dict()
+            pick = {k: v for k, v in bert_state_dict.items() if k in own and own[k].shape == v.shape}
+            tower.load_state_dict(pick, strict=False)
+            taken += len(pick)
+        return taken
+
     def _embed(self, model, tokens, pad_mask, types):
         pooled = model(tokens, pad_mask, types)
         return pooled if self.projection is None else self.projection(pooled)

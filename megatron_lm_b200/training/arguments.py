@@ -287,8 +287,6 @@ UNUSED_FLAGS = {
     "retro_cyclic_train_iters": (_R, "cyclic Retro training is not built"),
     "retro_attention_gate": (_R, "the Retro attention gate is fixed at 1"),
     "sample_rate": (_W, "the retriever evaluation tasks are not built"),
-    "ict_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),
-    "bert_load": (_R, "pretrain_ict.py starts its towers from random weights or --load"),
     "evidence_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
     "block_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
     "embedding_path": (_R, "the inverse-cloze program builds no block-embedding index"), "indexer_batch_size": (_W, "the inverse-cloze program builds no block-embedding index"),

@@ -30,9 +30,25 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
     if state.get_pipeline_model_parallel_world_size() > 1:
         raise NotImplementedError("the biencoder is trained without pipeline parallelism")
     print_rank_0("building the biencoder ...")
-    return BiEncoderModel(config, args.padded_vocab_size, args.max_position_embeddings,
-                          projection_dim=args.biencoder_projection_dim or (args.ict_head_size or 0),
-                          shared_query_context_model=args.biencoder_shared_query_context_model)
+    model = BiEncoderModel(config, args.padded_vocab_size, args.max_position_embeddings,
+                           projection_dim=args.biencoder_projection_dim or (args.ict_head_size or 0),
+                           shared_query_context_model=args.biencoder_shared_query_context_model)
+    from megatron_lm_b200.training import checkpointing
+    from megatron_lm_b200.training.pretrain import argparse_namespace_copy
+    if getattr(args, "bert_load", None) and args.load is None:
+        # --bert-load: both towers start from a pre-trained BERT checkpoint
+        from megatron_lm_b200.models.bert import BertModel
+        bert = BertModel(config, 2, args.padded_vocab_size, args.max_position_embeddings, add_binary_head=True)
+        ft = argparse_namespace_copy(args, finetune=True, no_load_optim=True, no_load_rng=True)
+        checkpointing.load_checkpoint([bert], None, None, ft, load_dir=args.bert_load, strict=False)
+        n = model.init_from_bert(bert.state_dict())
+        print_rank_0(f"biencoder towers initialised from the BERT checkpoint {args.bert_load} ({n} tensors)")
+    elif getattr(args, "ict_load", None) and args.load is None:
+        # --ict-load: a trained biencoder to continue from (weights only)
+        ft = argparse_namespace_copy(args, finetune=True, no_load_optim=True, no_load_rng=True)
+        checkpointing.load_checkpoint([model], None, None, ft, load_dir=args.ict_load, strict=False)
+        print_rank_0(f"biencoder loaded from {args.ict_load}")
+    return model
 
 
 class _AllGatherWithGrad(torch.autograd.Function):

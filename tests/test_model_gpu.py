@@ -132,3 +132,28 @@ def test_packed_sequences_run_on_the_flash_kernel_per_document():
     torch.cuda.synchronize()
     _lib.check_status()
     assert torch.isfinite(loss.float()).all() and (g_packed is None or torch.isfinite(g_packed).all())
+
+
+@pytest.mark.gpu
+def test_activation_offloading_on_gpu_matches_plain_run():
+    """Saved tensors of the offloaded layers go to pinned host memory and come back for backward: same loss and
+    gradients as the run that keeps them on the device."""
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.gpt import GPTModel
+    base = dict(num_layers=3, hidden_size=256, num_attention_heads=4, ffn_hidden_size=512, hidden_dropout=0.0,
+                attention_dropout=0.0, normalization="RMSNorm", gated_linear_unit=True, activation_func="silu",
+                add_bias_linear=False, params_dtype=torch.bfloat16, bf16=True)
+    ids = torch.randint(0, 128, (2, 128), device="cuda")
+    outs = []
+    for off in (False, True):
+        torch.manual_seed(0)
+        cfg = TransformerConfig(cpu_offloading=off, cpu_offloading_num_layers=2 if off else 0, **base)
+        m = GPTModel(cfg, 128, 128, parallel_output=False, position_embedding_type="rope").cuda().train()
+        loss = m(ids, labels=ids).float().mean()
+        loss.backward()
+        torch.cuda.synchronize()
+        outs.append((loss.item(), {n: p.grad.float().clone() for n, p in m.named_parameters() if p.grad is not None}))
+    assert outs[0][0] == outs[1][0]
+    assert outs[0][1].keys() == outs[1][1].keys()
+    for k in outs[0][1]:
+        assert torch.equal(outs[0][1][k], outs[1][1][k]), k

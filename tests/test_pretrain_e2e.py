@@ -127,6 +127,13 @@ def test_ict_and_vision_classification_programs(tmp_path):
                                           "--retriever-report-topk-accuracies", "1", "2", "--biencoder-projection-dim", "16"],
                       loss_key="retrieval loss")
     assert "top1_acc" in out
+    # towers started from a pre-trained BERT checkpoint
+    bert_ck = str(tmp_path / "bert_ck")
+    data = ["--data-path", prefix, "--split", "90,5,5", "--tokenizer-type", "BertWordPieceLowerCase", "--vocab-file", vocab]
+    _run_script("pretrain_bert.py", data + ["--save", bert_ck, "--save-interval", "3"])
+    out = _run_script("pretrain_ict.py", data + ["--retriever-seq-length", "32", "--bert-load", bert_ck],
+                      loss_key="retrieval loss")
+    assert "biencoder towers initialised from the BERT checkpoint" in out
     out = _run_script("pretrain_vision_classify.py", ["--mock-data", "--img-h", "32", "--img-w", "32", "--patch-dim", "8",
                                                       "--num-classes", "4"], loss_key="loss")
     assert "accuracy" in out
