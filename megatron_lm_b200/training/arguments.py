@@ -279,8 +279,6 @@ UNUSED_FLAGS = {
     "kitchen_recipe_number": (_R, "the Kitchen quantisation back end is not built"),
     # inference engine knobs read by the engines' own constructors, not from the training arguments
     "inference_batch_times_seqlen_threshold": (_W, "inference uses no pipelined micro-batching threshold"),
-    "output_bert_embeddings": (_R, "BERT embedding extraction is not built"),
-    "bert_embedder_type": (_W, "only used with --output-bert-embeddings"),
     "inference_dynamic_batching_num_cuda_graphs": (_W, "the dynamic engine captures no graphs"),
     # Retro / biencoder / vision programs that are not (fully) built
     "retro_add_retriever": (_W, "pretrain_retro.py always builds the retriever"),

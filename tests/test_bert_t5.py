@@ -50,3 +50,34 @@ def test_t5_causal_decoder_and_cross_mask():
     m.train()
     loss = m(enc, dec, enc_mask, None, x_mask, lm_labels=dec).mean()
     loss.backward()
+
+
+def test_bert_embedding_tool(tmp_path):
+    """One vector per line, independent of batching and of the other texts in a batch, written in input order."""
+    import numpy as np
+    from megatron_lm_b200.data import bert_embedding as be
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("\n".join(["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"] + [f"w{i}" for i in range(40)]) + "\n")
+    texts = ["w1 w2 w3", "w4", "w5 w6 w7 w8 w9 w10 w11", "w2 w2"]
+    (tmp_path / "in.txt").write_text("\n".join(texts) + "\n")
+    flags = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "16",
+             "--max-position-embeddings", "16", "--tokenizer-type", "BertWordPieceLowerCase", "--vocab-file", str(vocab),
+             "--use-cpu-initialization", "--attention-dropout", "0", "--hidden-dropout", "0", "--train-iters", "1",
+             "--lr", "1e-3", "--input", str(tmp_path / "in.txt"), "--output", str(tmp_path / "emb.npy"),
+             "--output-bert-embeddings", "--seed", "3"]
+    torch.manual_seed(0)
+    emb = be.main(flags + ["--embed-batch-size", "2"])
+    assert emb.shape == (4, 32) and np.isfinite(emb).all() and np.array_equal(np.load(tmp_path / "emb.npy"), emb)
+    torch.manual_seed(0)
+    one = be.main(flags + ["--embed-batch-size", "1"])
+    assert np.allclose(emb, one, atol=1e-5)
+    assert not np.allclose(emb[0], emb[1], atol=1e-3)
+    import pytest
+    with pytest.raises(SystemExit):
+        be.main([f for f in flags if f != "--output-bert-embeddings"])
+    ds = be.BertEmbeddingDataset(["w1 " * 40], __import__("megatron_lm_b200.data.tokenizer", fromlist=["x"]).build_tokenizer(
+        __import__("types").SimpleNamespace(tokenizer_type="BertWordPieceLowerCase", vocab_file=str(vocab), rank=0,
+                                            make_vocab_size_divisible_by=1, tensor_model_parallel_size=1,
+                                            vocab_extra_ids=0, padded_vocab_size=None)), 16)
+    item = ds[0]
+    assert item["length"] == 16 and item["text"][0] == 2 and item["text"][-1] == 3
