@@ -47,6 +47,8 @@ def add_vlm_generation_args(parser):
     g.add_argument("--top-k", type=int, default=1)
     g.add_argument("--top-p", type=float, default=0.0)
     g.add_argument("--generation-batch-size", type=int, default=1)
+    g.add_argument("--disable-vision-class-token", action="store_true",
+                   help="drop the class token of the vision model before the projection (LLaVA)")
     return parser
 
 

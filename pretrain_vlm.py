@@ -27,12 +27,16 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
     vis.context_parallel_size = 1
     proj = deepcopy(config)
     proj.num_layers = 2
-    return LLaVAModel(config, args.padded_vocab_size, args.max_position_embeddings, vis, proj,
-                      img_h=getattr(args, "img_h", 336), img_w=getattr(args, "img_w", 336),
-                      patch_dim=getattr(args, "patch_dim", 14), pre_process=pre_process, post_process=post_process,
-                      language_position_embedding_type=args.position_embedding_type,
-                      drop_vision_class_token=getattr(args, "disable_vision_class_token", False),
-                      share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights)
+    model = LLaVAModel(config, args.padded_vocab_size, args.max_position_embeddings, vis, proj,
+                       img_h=getattr(args, "img_h", 336), img_w=getattr(args, "img_w", 336),
+                       patch_dim=getattr(args, "patch_dim", 14), pre_process=pre_process, post_process=post_process,
+                       language_position_embedding_type=args.position_embedding_type,
+                       drop_vision_class_token=getattr(args, "disable_vision_class_token", False),
+                       share_embeddings_and_output_weights=not args.untie_embeddings_and_output_weights)
+    if getattr(args, "freeze_LM", False) or getattr(args, "freeze_ViT", False):
+        model.freeze(freeze_language_model=getattr(args, "freeze_LM", False),
+                     freeze_vision_model=getattr(args, "freeze_ViT", False), freeze_vision_projection=False)
+    return model
 
 
 class MockMultimodalDataset(torch.utils.data.Dataset):
@@ -74,6 +78,16 @@ def forward_step(data_iterator, model):
     return out, partial(loss_func, new_mask)
 
 
+def add_vlm_args(parser):
+    """Flags of the vision-language program (reference: pretrain_vlm.py:384 ``add_vlm_extra_args``)."""
+    g = parser.add_argument_group(title="vision language model")
+    g.add_argument("--disable-vision-class-token", action="store_true",
+                   help="drop the class token of the vision model before the projection")
+    g.add_argument("--freeze-LM", action="store_true", dest="freeze_LM", help="train without updating the language model")
+    g.add_argument("--freeze-ViT", action="store_true", dest="freeze_ViT", help="train without updating the vision model")
+    return parser
+
+
 if __name__ == "__main__":
-    pretrain(train_valid_test_datasets_provider, model_provider, forward_step,
+    pretrain(train_valid_test_datasets_provider, model_provider, forward_step, extra_args_provider=add_vlm_args,
              args_defaults={"tokenizer_type": "NullTokenizer"})

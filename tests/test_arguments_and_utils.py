@@ -377,3 +377,37 @@ def test_flags_that_used_to_do_nothing(tmp_path, monkeypatch):
     srv = MegatronServer(Eng(), max_tokens_to_oom=40)
     code, resp = srv.handle(json.dumps({"prompts": ["a b c d", "e f"], "tokens_to_generate": 20}).encode())
     assert code == 400 and "Too many tokens" in resp["message"] and "48" in resp["message"]
+
+
+def test_example_scripts_use_known_flags():
+    """Every ``--flag`` of the launch scripts under examples/ is known to the parser of the program it starts."""
+    import glob
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    from megatron_lm_b200.inference.run_server import add_server_args
+    from megatron_lm_b200.inference.run_vlm_generation import add_vlm_generation_args
+    from megatron_lm_b200.post_training.arguments import add_modelopt_args
+    from megatron_lm_b200.tasks.quantize_gpt import add_calib_args
+
+    def extra(parser):
+        for fn in (add_server_args, add_vlm_generation_args, add_calib_args):
+            try:
+                fn(parser)
+            except Exception:
+                pass
+        g = parser.add_argument_group("program-specific")
+        for f in ("--dino-out-dim", "--knn-bank-size"):
+            g.add_argument(f)
+        return parser
+    parser = A.build_parser(extra)
+    known = {o for a in parser._actions for o in a.option_strings}
+    launcher = {"--nnodes", "--nproc-per-node", "--master-addr", "--master-port", "--standalone", "--local-addr",
+                "--node-rank", "--rdzv-backend", "--rdzv-endpoint", "--rdzv-id", "--max-restarts",
+                "--loader", "--saver", "--load-dir", "--save-dir", "--tokens-to-generate"}
+    scripts = glob.glob(os.path.join(root, "examples", "**", "*.sh"), recursive=True)
+    assert len(scripts) >= 8
+    for path in scripts:
+        text = "\n".join(l for l in open(path).read().splitlines() if not l.lstrip().startswith("#"))
+        for flag in set(re.findall(r"(?<![\w-])--[a-z][a-z0-9-]*", text)):
+            assert flag in known or flag in launcher, (os.path.relpath(path, root), flag)
