@@ -19,7 +19,9 @@ from ..ops.fp8 import DelayedScalingState
 from ..ops.grouped_gemm import grouped_linear
 from ..parallel import state
 from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, _device
+from ..parallel.random import CudaRNGStatesTracker as _CudaRNGStatesTracker
 from ..parallel.random import checkpoint as _checkpoint
+from ..models.transformer import MLP as _MLP
 from ..models.transformer import Norm, masked_attention
 
 HAVE_TE = False          # no external library is used; kept because callers of the reference test this name
@@ -211,3 +213,64 @@ def get_cpu_offload_context(enabled, num_layers, model_layers, activation_offloa
         return contextlib.nullcontext(), (lambda t: t)
     ctx = torch.autograd.graph.save_on_cpu(pin_memory=torch.cuda.is_available())
     return ctx, (lambda t: t)
+
+
+class TEFusedMLP(_MLP):
+    """The MLP with norm, bias, activation and both projections as fused kernels - which the native MLP already is
+    (fused norm + GEMM epilogues + SwiGLU kernel), so the class only carries the adapter's name
+    (reference: transformer_engine.py:1353 ``TEFusedMLP`` built from the library's fusible ops)."""
+
+
+class TECudaRNGStatesTracker(_CudaRNGStatesTracker):
+    """The adapter's name for the RNG-state tracker (reference: transformer_engine.py:1498)."""
+
+    def is_initialized(self) -> bool:
+        return bool(getattr(self, "states_", None))
+
+
+def SplitAlongDim(tensor: torch.Tensor, dim: int, split_sizes):
+    """Views of ``tensor`` cut along ``dim`` (reference: the library's ``_SplitAlongDim.apply``; autograd handles the
+    concatenation of the gradients)."""
+    return torch.split(tensor, list(split_sizes), dim=dim)
+
+
+def fused_apply_rotary_pos_emb(t: torch.Tensor, freqs: torch.Tensor, transpose_output_memory: bool = False,
+                               interleaved: bool = False) -> torch.Tensor:
+    """Rotary embedding of ``t`` [s, b, h, d] with angles ``freqs`` [s, 1, 1, d_rot] through the native kernel
+    (reference: transformer_engine.py:1602)."""
+    from ..ops import core as ops
+    ang = freqs.reshape(freqs.shape[0], -1).float()
+    # the reference's table repeats every angle (two halves, or neighbouring pairs when interleaved); the kernel
+    # takes each angle once
+    ang = ang[:, 0::2] if interleaved else ang[:, : ang.shape[1] // 2]
+    return ops.apply_rope(t, torch.cos(ang).contiguous(), torch.sin(ang).contiguous(), interleaved)
+
+
+def te_general_gemm(A: torch.Tensor, B: torch.Tensor, out_dtype=None, layout: str = "TN", out=None, bias=None,
+                    grad: bool = False):
+    """The library's general GEMM entry in its column-major convention: ``layout="TN"`` computes ``B @ A^T`` for
+    row-major ``A`` [n, k], ``B`` [m, k] (reference: transformer_engine.py:1697).  Runs the native tcgen05 GEMM on a
+    GPU.  Returns a list whose first entry is the product, like the library."""
+    from ..ops.gemm import gemm
+    if layout == "TN":
+        x, w, kw = B, A, {}
+    elif layout == "NN":
+        x, w, kw = B, A, {"b_mn": True}
+    elif layout == "NT":
+        x, w, kw = B, A, {"a_mn": True, "b_mn": True}
+    else:
+        raise ValueError(f"layout {layout!r}")
+    if x.is_cuda:
+        y = gemm(x, w, bias=bias, out=out, out_dtype=out_dtype, **kw) if out_dtype is not None or out is not None \
+            else gemm(x, w, bias=bias, **kw)
+    else:
+        xa = x.t() if kw.get("a_mn") else x
+        wa = w if kw.get("b_mn") else w.t()
+        y = xa.float() @ wa.float()
+        if bias is not None:
+            y = y + bias.float()
+        y = y.to(out_dtype or x.dtype)
+        if out is not None:
+            out.copy_(y)
+            y = out
+    return [y, None, None, None]

@@ -66,3 +66,23 @@ def get_fp8_context(config, layer_no: int = -1, is_init: bool = False):
         yield
     finally:
         config.fp8 = saved
+
+
+def prepare_model_for_fp8_inference(model: torch.nn.Module, fp8_format: str = "e4m3", recipe: str = "tensorwise"):
+    """Switch the transformer-layer linears of a (bf16 / fp16) model to the FP8 GEMM path for inference: the config
+    is marked, every eligible linear keeps a cached FP8 image of its weight (quantised once, since weights no longer
+    change), and token counts that the 8-bit tensor-core path cannot take (not a multiple of 16, e.g. single-token
+    decoding) fall back to 16 bits by themselves.  Returns the number of linears switched
+    (reference: megatron/core/fp8_utils.py:604 ``prepare_model_for_fp8_inference``, which pads such inputs instead)."""
+    from .parallel.layers import ColumnParallelLinear, RowParallelLinear
+    n = 0
+    for mod in model.modules():
+        cfg = getattr(mod, "config", None)
+        if cfg is not None and hasattr(cfg, "fp8"):
+            cfg.fp8, cfg.fp8_recipe = fp8_format, recipe
+        if isinstance(mod, (ColumnParallelLinear, RowParallelLinear)) and getattr(mod, "fp8_eligible", True) \
+                and mod.weight is not None and mod.weight.shape[0] % 16 == 0 and mod.weight.shape[1] % 16 == 0:
+            mod.weight.requires_grad_(False)
+            n += 1
+    model.eval()
+    return n

@@ -192,6 +192,20 @@ def topk_softmax_with_capacity(logits, topk: int, capacity_factor=None, pad_to_c
     return full * final, final, tokens_per_expert
 
 
+def pad_routing_map(routing_map: torch.Tensor, pad_multiple: int) -> torch.Tensor:
+    """Raise every expert's token count to the next multiple of ``pad_multiple`` by routing extra tokens (the first
+    ones not yet routed to that expert) to it - FP8 grouped GEMMs want aligned row counts per expert.  The added
+    entries carry probability zero, so the layer's output does not change
+    (reference: megatron/core/transformer/moe/moe_utils.py:494 ``pad_routing_map``)."""
+    rm = routing_map.bool()
+    counts = rm.sum(dim=0)
+    target = (counts + pad_multiple - 1) // pad_multiple * pad_multiple
+    need = (target - counts).clamp(max=rm.shape[0] - counts)            # cannot exceed the tokens that exist
+    # rank of every not-yet-routed token within its expert column: the first `need` of them are switched on
+    free_rank = torch.cumsum((~rm).long(), dim=0)
+    return rm | ((~rm) & (free_rank <= need.unsqueeze(0)))
+
+
 class _RandomSTE(torch.autograd.Function):
     """Forward: uniform random scores of the same shape (the same on every rank that holds the same tokens is not
     required - each rank routes its own tokens); backward: identity."""
@@ -254,7 +268,8 @@ class TopKRouter(nn.Module):
                 and self.routing_type in ("aux_loss", "none") and cfg.moe_expert_capacity_factor is None
                 and not cfg.moe_router_group_topk and logits.dtype == torch.float32
                 and self.num_experts <= fused_router.MAX_EXPERTS
-                and cfg.moe_router_score_function in ("softmax", "sigmoid"))
+                and cfg.moe_router_score_function in ("softmax", "sigmoid")
+                and not (cfg.moe_router_padding_for_fp8 and cfg.fp8))
 
     def _forward_fused(self, logits):
         cfg = self.config
@@ -314,6 +329,8 @@ class TopKRouter(nn.Module):
             cfg.moe_token_drop_policy, cfg.moe_router_pre_softmax, cfg.moe_router_num_groups,
             cfg.moe_router_group_topk, cfg.moe_router_topk_scaling_factor, cfg.moe_router_score_function,
             self.expert_bias)
+        if cfg.moe_router_padding_for_fp8 and cfg.fp8:
+            rmap = pad_routing_map(rmap, 16)          # probabilities of the added entries stay zero
         if self.training and cfg.moe_aux_loss_coeff > 0 and self.routing_type in ("aux_loss", "seq_aux_loss"):
             scores = torch.softmax(logits, dim=-1, dtype=torch.float32) if cfg.moe_router_score_function == "softmax" \
                 else torch.sigmoid(logits.float())

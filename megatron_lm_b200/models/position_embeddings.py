@@ -73,3 +73,19 @@ class MultimodalRotaryEmbedding(nn.Module):
             o += n
         a = torch.cat(pieces, dim=-1).transpose(0, 1)                            # [s, b, rot/2]
         return a.cos().contiguous(), a.sin().contiguous()
+
+
+def get_pos_emb_on_this_cp_rank(pos_emb: torch.Tensor, seq_dim: int, cp_size: int = None, cp_rank: int = None):
+    """The rows of a full-sequence position table that this context-parallel rank holds: the sequence is cut into
+    2 x cp chunks and rank r keeps chunks r and 2 cp - 1 - r, which balances causal attention work
+    (reference: megatron/core/models/common/embeddings/rope_utils.py:48)."""
+    from ..parallel import state
+    from ..parallel.context_parallel import zigzag_indices
+    if cp_size is None:
+        cp_size = state.get_context_parallel_world_size() if state.model_parallel_is_initialized() else 1
+    if cp_size == 1:
+        return pos_emb
+    if cp_rank is None:
+        cp_rank = state.get_context_parallel_rank()
+    idx = zigzag_indices(pos_emb.shape[seq_dim], cp_size, cp_rank, pos_emb.device)
+    return pos_emb.index_select(seq_dim, idx)

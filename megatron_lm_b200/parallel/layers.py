@@ -429,3 +429,18 @@ def linear_with_frozen_weight(x, weight, bias=None):
     """Linear whose weight takes no gradient (reference: layers.py:317)."""
     w = weight.detach()
     return tp_linear(x, w, bias)
+
+
+class LinearWithFrozenWeight:
+    """Call-compatible name of the reference's autograd function (layers.py:317): ``LinearWithFrozenWeight.apply(x,
+    weight, bias, allreduce_dgrad)`` - the weight receives no gradient, the data gradient is all-reduced over the
+    tensor-parallel group when asked."""
+
+    @staticmethod
+    def apply(x, weight, bias=None, allreduce_dgrad: bool = False, group=None):
+        w = weight.detach()
+        if allreduce_dgrad:
+            group = group if group is not None else (state.get_tensor_model_parallel_group()
+                                                     if state.model_parallel_is_initialized() else None)
+            return tp_linear(x, w, bias, group=group, allreduce_dgrad=True)
+        return tp_linear(x, w, bias)

@@ -85,6 +85,9 @@ class RNGStatesTracker:
 _TRACKER = RNGStatesTracker()
 
 
+CudaRNGStatesTracker = RNGStatesTracker          # the reference's name (tensor_parallel/random.py:126)
+
+
 def get_cuda_rng_tracker() -> RNGStatesTracker:
     return _TRACKER
 

@@ -461,3 +461,21 @@ def get_args():
     if _GLOBAL_ARGS is None:
         raise RuntimeError("arguments are not initialised")
     return _GLOBAL_ARGS
+
+
+def validate_yaml(args, defaults=None):
+    """Validation of a YAML-built namespace: the same rules as the command line
+    (reference: megatron/training/yaml_arguments.py:41)."""
+    return validate_args(args, defaults)
+
+
+def core_transformer_config_from_yaml(args, transfomer_key: str = "language_model"):
+    """``TransformerConfig`` from a namespace loaded by ``load_yaml_args`` (sections are flattened at load time, so
+    the section name is accepted for call compatibility only; reference: yaml_arguments.py:403)."""
+    return core_transformer_config_from_args(args)
+
+
+def load_yaml(yaml_path: str, args=None):
+    """A YAML file as an argument namespace on top of the parser's defaults (reference: yaml_arguments.py:442)."""
+    base = args if args is not None else parse_args(argv=[])
+    return load_yaml_args(yaml_path, base)

@@ -137,3 +137,29 @@ def drain_embedding_wgrad_compute(config=None, *_unused, keep: int = 0) -> int:
     (reference: megatron/core/utils.py drain_embedding_wgrad_compute)."""
     from ..parallel.layers import drain_deferred_wgrads
     return drain_deferred_wgrads(keep)
+
+
+# ---------------------------------------------------------------------------------------------- multi-tensor fallbacks
+def local_multi_tensor_applier(op, noop_flag_buffer, tensor_lists, *args):
+    """Call convention of the fused multi-tensor kernels (reference: megatron/core/utils.py:1032-1051): ``op`` gets the
+    chunk size (unused here), the no-op flag, the tensor lists and the extra arguments."""
+    return op(2048 * 32, noop_flag_buffer, tensor_lists, *args)
+
+
+def local_multi_tensor_l2_norm(chunk_size, noop_flag, tensor_lists, per_tensor: bool = False, *args):
+    """L2 norm over all tensors of ``tensor_lists[0]`` as a one-element fp32 tensor (and the per-tensor norms when
+    asked): ``torch._foreach_norm`` does the work in a few launches on a GPU."""
+    tensors = list(tensor_lists[0])
+    if not tensors:
+        z = torch.zeros(1, dtype=torch.float32)
+        return z, (z.clone() if per_tensor else None)
+    norms = torch.stack([n.float() for n in torch._foreach_norm(tensors, 2)])
+    total = torch.linalg.vector_norm(norms, 2).reshape(1)
+    return total, (norms if per_tensor else None)
+
+
+def local_multi_tensor_scale(chunk_size, noop_flag, tensor_lists, scale):
+    """``dst[i] = src[i] * scale`` for the tensor pairs of ``tensor_lists = [srcs, dsts]``."""
+    srcs, dsts = tensor_lists
+    for s, d in zip(srcs, dsts):
+        d.copy_(s * scale)

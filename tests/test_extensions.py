@@ -85,3 +85,60 @@ def test_spec_providers_answer_with_native_classes():
     assert cls.__name__ == "GroupedMLP" and sub is None
     cls, sub = tep.grouped_mlp_modules(False, False)
     assert cls.__name__ == "SequentialMLP" and sub.linear_fc1 is te.TEColumnParallelLinear
+
+
+def test_remaining_adapter_names_and_small_helpers():
+    """TEFusedMLP, the RNG tracker name, SplitAlongDim, the rotary entry, the general GEMM in the library's
+    convention; multi-tensor fallbacks, routing-map padding, frozen-weight linear, YAML helpers, the
+    context-parallel slice of a position table."""
+    import torch
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.extensions import transformer_engine as te
+    from megatron_lm_b200.models.moe import pad_routing_map
+    from megatron_lm_b200.models.position_embeddings import get_pos_emb_on_this_cp_rank
+    from megatron_lm_b200.parallel.layers import LinearWithFrozenWeight
+    from megatron_lm_b200.utils.common import (local_multi_tensor_applier, local_multi_tensor_l2_norm,
+                                               local_multi_tensor_scale)
+    cfg = TransformerConfig(num_layers=1, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64,
+                            use_cpu_initialization=True)
+    mlp = te.TEFusedMLP(cfg)
+    y, _ = mlp(torch.randn(5, 2, 32))
+    assert y.shape == (5, 2, 32)
+    assert not te.TECudaRNGStatesTracker().is_initialized()
+    a, b = te.SplitAlongDim(torch.arange(12.0).view(2, 6), 1, (2, 4))
+    assert a.shape == (2, 2) and b.shape == (2, 4)
+    A, B = torch.randn(7, 16), torch.randn(5, 16)                       # TN: B @ A^T
+    out = te.te_general_gemm(A, B, torch.float32, layout="TN")[0]
+    assert torch.allclose(out, B @ A.t(), atol=1e-5)
+    t = torch.randn(6, 2, 4, 8)
+    f = torch.randn(6, 1, 1, 4)
+    freqs = torch.cat((f, f), dim=-1)
+    rot = te.fused_apply_rotary_pos_emb(t, freqs)
+    half = t.shape[-1] // 2
+    ang = freqs.reshape(6, -1)
+    cos, sin = torch.cos(ang)[:, None, None, :], torch.sin(ang)[:, None, None, :]
+    rotated = torch.cat((-t[..., half:], t[..., :half]), dim=-1)
+    assert torch.allclose(rot, t * cos + rotated * sin, atol=1e-5)
+    # multi-tensor fallbacks
+    ts = [torch.randn(5), torch.randn(3, 4)]
+    total, per = local_multi_tensor_applier(local_multi_tensor_l2_norm, None, [ts], True)
+    assert torch.allclose(total, torch.cat([x.flatten() for x in ts]).norm().reshape(1)) and per.shape == (2,)
+    dst = [torch.zeros(5), torch.zeros(3, 4)]
+    local_multi_tensor_applier(local_multi_tensor_scale, None, [ts, dst], 0.5)
+    assert torch.allclose(dst[1], ts[1] * 0.5)
+    # routing-map padding: every expert's count becomes a multiple of 4, earlier choices stay
+    rm = torch.zeros(10, 3, dtype=torch.bool)
+    rm[[0, 3, 4], 0] = True
+    rm[:, 1] = True
+    padded = pad_routing_map(rm, 4)
+    assert padded.sum(0).tolist() == [4, 10, 0] and (padded | rm).equal(padded) and padded[1, 0]
+    # frozen weight
+    w = torch.randn(6, 4, requires_grad=True)
+    x = torch.randn(3, 4, requires_grad=True)
+    LinearWithFrozenWeight.apply(x, w).sum().backward()
+    assert w.grad is None and x.grad is not None
+    # context-parallel rows of a table
+    tab = torch.arange(16.0).view(16, 1)
+    assert get_pos_emb_on_this_cp_rank(tab, 0, 2, 0).flatten().tolist() == [0, 1, 2, 3, 12, 13, 14, 15]
+    assert get_pos_emb_on_this_cp_rank(tab, 0, 2, 1).flatten().tolist() == [4, 5, 6, 7, 8, 9, 10, 11]
+    assert get_pos_emb_on_this_cp_rank(tab, 0, 1, 0) is tab
