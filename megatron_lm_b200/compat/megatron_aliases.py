@@ -102,10 +102,28 @@ _MAP: Dict[str, Union[str, List[Tuple[str, List[str]]]]] = {
     "megatron.training.global_vars": f"{P}.training.global_vars",
     "megatron.training.training": f"{P}.training.pretrain",
     "megatron.training.tokenizer": f"{P}.data.tokenizer",
+    "megatron.training.yaml_arguments": [(f"{P}.training.arguments", ["validate_yaml", "core_transformer_config_from_yaml",
+                                                                      "load_yaml"])],
+    "megatron.core.dist_checkpointing.tensor_aware_state_dict": f"{P}.checkpoint.tensor_aware",
+    "megatron.core.datasets.multimodal_dataset": f"{P}.data.multimodal_dataset",
+    "megatron.core.datasets.object_storage_utils": f"{P}.data.object_storage",
+    "megatron.core.transformer.moe.upcycling_utils": f"{P}.models.upcycling",
+    "megatron.core.transformer.heterogeneous.heterogeneous_config": f"{P}.models.heterogeneous",
+    "megatron.core.models.vision.clip_vit_model": [(f"{P}.models.vision", ["CLIPViTModel", "get_num_image_embeddings"])],
+    "megatron.core.models.multimodal.llava_model": [(f"{P}.models.multimodal", ["LLaVAModel"])],
+    "megatron.core.export.trtllm.trtllm_helper": [(f"{P}.export.trtllm", ["TRTLLMHelper"])],
+    "megatron.core.quantization.quant_config": f"{P}.post_training.quant_config",
+    "megatron.post_training.arguments": f"{P}.post_training.arguments",
+    "megatron.post_training.checkpointing": f"{P}.post_training.checkpointing",
+    "megatron.post_training.algos.distillation": f"{P}.post_training.distillation",
+    "megatron.post_training.loss_func": [(f"{P}.post_training.distillation", ["distillation_loss_func", "masked_token_mean"])],
 }
 _PARENTS = ["megatron", "megatron.core", "megatron.core.models", "megatron.core.models.bert", "megatron.core.models.T5",
             "megatron.core.models.mamba", "megatron.core.transformer.moe", "megatron.core.extensions",
-            "megatron.core.datasets", "megatron.core.inference"]
+            "megatron.core.datasets", "megatron.core.inference", "megatron.core.transformer.heterogeneous",
+            "megatron.core.models.vision", "megatron.core.models.multimodal", "megatron.core.export",
+            "megatron.core.export.trtllm", "megatron.core.quantization", "megatron.post_training",
+            "megatron.post_training.algos"]
 
 _installed: List[str] = []
 

@@ -24,6 +24,14 @@ def test_reference_import_paths_resolve_after_install():
         from megatron.core.rerun_state_machine import RerunStateMachine
         from megatron.training import get_args, pretrain
         from megatron.training.arguments import parse_args
+        from megatron.training.yaml_arguments import core_transformer_config_from_yaml
+        from megatron.core.dist_checkpointing.tensor_aware_state_dict import TensorAwareStateDict
+        from megatron.core.datasets.multimodal_dataset import MockMultimodalDataset
+        from megatron.core.transformer.moe.upcycling_utils import upcycle_state_dict
+        from megatron.core.models.multimodal.llava_model import LLaVAModel
+        from megatron.core.export.trtllm.trtllm_helper import TRTLLMHelper
+        from megatron.post_training.algos.distillation import LogitsKLLoss, load_distillation_config
+        from megatron.post_training.arguments import add_modelopt_args
         import megatron_lm_b200.models.gpt as native
         assert GPTModel is native.GPTModel
         assert parallel_state.initialize_model_parallel.__module__ == "megatron_lm_b200.parallel.state"
