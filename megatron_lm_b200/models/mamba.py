@@ -89,6 +89,57 @@ class MambaMixer(nn.Module):
         self.out_proj = RowParallelLinear(self.d_inner, d_model, config=config,
                                           init_method=config.output_layer_init_method, bias=False, skip_bias_add=True)
         self.eps = config.layernorm_epsilon
+        # context parallelism: the convolution and the scan need the whole sequence, so the mixer trades its
+        # sequence shard for a head shard (all-to-all over the context-parallel group), runs on all positions of
+        # 1 / cp of its heads and groups, and trades back (reference: megatron/core/ssm/mamba_context_parallel.py:17)
+        self.cp = state.get_context_parallel_world_size() if state.model_parallel_is_initialized() else 1
+        if self.cp > 1 and (self.h_loc % self.cp or self.g_loc % self.cp):
+            raise ValueError("Mamba heads and groups per tensor-parallel rank must divide by the context-parallel size")
+
+    # -- context parallel <-> head parallel -------------------------------------------------------------------------
+    def _cp_parts(self, xBC, dt):
+        """Channel pieces that go to each context-parallel rank: its heads of x and dt, its groups of B and C."""
+        cp, di, gn = self.cp, self.di_loc, self.g_loc * self.d_state
+        x, Bm, Cm = torch.split(xBC, [di, gn, gn], dim=-1)
+        return [torch.cat((xx, bb, cc, dd), dim=-1)
+                for xx, bb, cc, dd in zip(x.chunk(cp, -1), Bm.chunk(cp, -1), Cm.chunk(cp, -1), dt.chunk(cp, -1))]
+
+    def _cp_to_heads(self, xBC, dt):
+        """[b, s/cp, channels] on every rank -> [b, s, channels/cp] in natural token order."""
+        from ..parallel.context_parallel import natural_order_permutation
+        from ..parallel.mappings import all_to_all
+        cp, group = self.cp, state.get_context_parallel_group()
+        b, sl, _ = xBC.shape
+        send = torch.stack(self._cp_parts(xBC, dt), dim=0)                      # [cp (destination), b, s/cp, c]
+        c = send.shape[-1]
+        recv = all_to_all(group, send.reshape(cp * b * sl, c)).view(cp, b, sl, c)  # [cp (source), ...]
+        seq = recv.permute(1, 0, 2, 3).reshape(b, cp * sl, c)                    # rank-concatenated zig-zag order
+        seq = seq.index_select(1, natural_order_permutation(cp * sl, cp, seq.device))
+        di, gn, h = self.di_loc // cp, self.g_loc * self.d_state // cp, self.h_loc // cp
+        x, Bm, Cm, dtp = torch.split(seq, [di, gn, gn, h], dim=-1)
+        return torch.cat((x, Bm, Cm), dim=-1), dtp
+
+    def _heads_to_cp(self, y):
+        """[b, s, channels/cp] in natural order -> this rank's [b, s/cp, channels]."""
+        from ..parallel.context_parallel import zigzag_indices
+        from ..parallel.mappings import all_to_all
+        cp, group = self.cp, state.get_context_parallel_group()
+        b, S, c = y.shape
+        order = torch.cat([zigzag_indices(S, cp, r, y.device) for r in range(cp)])
+        send = y.index_select(1, order).view(b, cp, S // cp, c).permute(1, 0, 2, 3).contiguous()
+        recv = all_to_all(group, send.reshape(cp * b * (S // cp), c)).view(cp, b, S // cp, c)   # [cp (head part), ...]
+        return recv.permute(1, 2, 0, 3).reshape(b, S // cp, cp * c)
+
+    def _cp_params(self):
+        """This context-parallel rank's rows of the convolution and its heads' scan parameters."""
+        cp, r = self.cp, state.get_context_parallel_rank()
+        di, gn = self.di_loc, self.g_loc * self.d_state
+
+        def conv_rows(p):
+            x, Bm, Cm = torch.split(p, [di, gn, gn], dim=0)
+            return torch.cat((x.chunk(cp, 0)[r], Bm.chunk(cp, 0)[r], Cm.chunk(cp, 0)[r]), dim=0)
+        return (conv_rows(self.conv_weight), conv_rows(self.conv_bias), self.dt_bias.chunk(cp)[r],
+                self.A_log.chunk(cp)[r], self.D.chunk(cp)[r])
 
     def _split(self, zxbcdt):
         di, gn = self.di_loc, self.g_loc * self.d_state
@@ -104,6 +155,10 @@ class MambaMixer(nn.Module):
         zxbcdt = zxbcdt.transpose(0, 1)                                # [b, s, local]
         z, xBC, dt = self._split(zxbcdt)
         cache = None if inference_context is None else inference_context.ssm_cache(self.layer_number, self, zxbcdt)
+        if self.cp > 1:
+            if cache is not None:
+                raise NotImplementedError("token-by-token decoding of a context-parallel Mamba model")
+            return self._forward_context_parallel(z, xBC, dt)
         b, s, _ = xBC.shape
         if cache is not None and s == 1 and cache["filled"]:
             xBC = causal_conv1d_update(xBC[:, 0], cache["conv"], self.conv_weight, self.conv_bias, True).unsqueeze(1)
@@ -127,6 +182,27 @@ class MambaMixer(nn.Module):
             y = ssd_scan(x, dtv, A, Bm, Cm, self.D, None, None, False, self.chunk)
         y = self._gated_norm(y.reshape(b, s, self.di_loc), z)
         return self.out_proj(y.transpose(0, 1).contiguous())
+
+
+def _mixer_forward_context_parallel(self, z, xBC, dt):
+    cp = self.cp
+    xBC, dt = self._cp_to_heads(xBC, dt)                                     # all positions, 1 / cp of the heads
+    conv_w, conv_b, dt_bias, A_log, D = self._cp_params()
+    b, s, _ = xBC.shape
+    h, g, di = self.h_loc // cp, self.g_loc // cp, self.di_loc // cp
+    xBC = causal_conv1d(xBC.contiguous(), conv_w.contiguous(), conv_b.contiguous(), True)
+    gn = g * self.d_state
+    x, Bm, Cm = torch.split(xBC, [di, gn, gn], dim=-1)
+    dtv = F.softplus(dt.float() + dt_bias)
+    A = -torch.exp(A_log.float())
+    y = ssd_scan(x.reshape(b, s, h, self.headdim), dtv, A, Bm.reshape(b, s, g, self.d_state),
+                 Cm.reshape(b, s, g, self.d_state), D, None, None, False, self.chunk)
+    y = self._heads_to_cp(y.reshape(b, s, di))                               # this rank's positions, all local heads
+    y = self._gated_norm(y, z)
+    return self.out_proj(y.transpose(0, 1).contiguous())
+
+
+MambaMixer._forward_context_parallel = _mixer_forward_context_parallel
 
 
 class MambaLayer(nn.Module):
@@ -240,6 +316,11 @@ class MambaModel(nn.Module):
         if self.rotary_pos_emb is not None:
             rotary = self.rotary_pos_emb(input_ids.shape[1], input_ids.device) if span is None else \
                 self.rotary_pos_emb(span[0], input_ids.device, span[1])
+            cp = state.get_context_parallel_world_size() if state.model_parallel_is_initialized() else 1
+            if cp > 1 and span is None:
+                # attention layers of a hybrid under context parallelism: the table is built for the whole sequence
+                # and holds the rows of this rank's two chunks
+                rotary = self.rotary_pos_emb(input_ids.shape[1] * cp, input_ids.device)
         h = self.decoder(decoder_input, rotary=rotary, inference_context=inference_context)
         if not self.post_process:
             return h
