@@ -162,10 +162,10 @@ def test_ict_blocks_and_samples(tmp_path):
     assert np.array_equal(ict[5]["query_tokens"], s["query_tokens"])      # deterministic per index
 
 
-def _torchrun(nproc, port, extra):
+def _torchrun(nproc, port, extra, script="pretrain_gpt.py"):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(nproc), "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "pretrain_gpt.py"), "--distributed-backend", "gloo",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, script), "--distributed-backend", "gloo",
            "--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "4", "--seq-length", "32",
            "--max-position-embeddings", "32", "--micro-batch-size", "1", "--train-iters", "3", "--lr", "1e-3",
            "--mock-data", "--tokenizer-type", "NullTokenizer", "--vocab-size", "64", "--log-interval", "1",
@@ -480,3 +480,11 @@ def test_architecture_is_read_back_from_the_checkpoint(tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
     assert sorted(_iters(r.stdout)) == [5, 6, 7, 8]
+
+
+def test_hybrid_mamba_program_with_context_parallelism():
+    """Two context-parallel ranks: the mixers swap sequence shards for head shards, the attention layer runs the ring."""
+    _torchrun(2, 29663, ["--context-parallel-size", "2", "--global-batch-size", "2", "--num-layers", "3",
+                         "--mamba-head-dim", "16", "--mamba-num-groups", "2", "--mamba-state-dim", "16",
+                         "--hybrid-override-pattern", "M*-", "--position-embedding-type", "rope"],
+              script="pretrain_mamba.py")
