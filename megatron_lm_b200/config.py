@@ -120,7 +120,6 @@ class ModelParallelConfig:
 UNSUPPORTED_FIELDS = {
     "fp8_dot_product_attention": "attention runs in bf16 / fp16",
     "fp8_multi_head_attention": "attention runs in bf16 / fp16",
-    "delay_wgrad_compute": "weight gradients are computed with their layer's backward",
     "init_model_with_meta_device": "parameters are created on their device",
     "use_kitchen": "the Kitchen quantisation back end is not built",
     "quant_recipe": "per-layer quantisation recipes are not built",
@@ -345,6 +344,9 @@ class TransformerConfig(ModelParallelConfig):
                 raise ValueError("num_moe_experts must be divisible by expert_model_parallel_size")
             if self.moe_ffn_hidden_size is None:
                 self.moe_ffn_hidden_size = self.ffn_hidden_size
+        if self.delay_wgrad_compute and not self.overlap_moe_expert_parallel_comm:
+            raise ValueError("delay_wgrad_compute needs overlap_moe_expert_parallel_comm (the schedule that runs the "
+                             "postponed weight gradients)")
         if self.cpu_offloading:
             if self.cpu_offloading_weights:
                 raise ValueError("cpu_offloading_weights is not supported: only activations are offloaded")

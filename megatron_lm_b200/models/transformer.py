@@ -462,6 +462,19 @@ class TransformerLayer(nn.Module):
         if config.fp8:
             from ..fp8_utils import mark_layer_precision
             mark_layer_precision(self, config, layer_number - 1)       # first / last layers may stay in 16 bits
+        if getattr(config, "delay_wgrad_compute", False):
+            # the weight-gradient GEMMs of this layer's linears are queued by backward and run by backward_dw():
+            # the expert-parallel overlap schedule places them under the other micro-batch's communication
+            # (reference: transformer_layer.py backward_dw, attention.py:~970, --delay-wgrad-compute)
+            from ..parallel.layers import ColumnParallelLinear, RowParallelLinear
+            for m in self.modules():
+                if isinstance(m, (ColumnParallelLinear, RowParallelLinear)) and m.weight is not None:
+                    m.weight.defer_wgrad = True
+
+    def backward_dw(self) -> int:
+        """Run the queued weight-gradient products of this layer's linears; returns how many ran."""
+        from ..parallel.layers import drain_deferred_wgrads
+        return drain_deferred_wgrads(only={id(p) for p in self.parameters()})
 
     def _bda(self, x, bias, residual):
         p = self.hidden_dropout

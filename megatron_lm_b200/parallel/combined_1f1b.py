@@ -21,6 +21,8 @@ from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 
+from .layers import _DEFERRED_WGRADS, drain_deferred_wgrads
+
 _COMP, _COMM = None, None
 
 
@@ -206,6 +208,10 @@ def schedule_chunk_1f1b(f_plan: Optional[ModelChunkSchedulePlan], b_plan: Option
         if fi < len(f_nodes):
             f_carry = _run_forward_node(f_nodes[fi], f_carry)
             fi += 1
+        if _DEFERRED_WGRADS:
+            # delay_wgrad_compute: the weight gradients of the backward node above run after the forward node that
+            # followed it, i.e. under whatever communication that node started
+            drain_deferred_wgrads(0)
     if f_plan is not None:
         f_plan.loss = f_carry[0]
         return f_plan.loss

@@ -89,12 +89,19 @@ def _defer_or_compute_wgrad(weight, dy2, t2):
     return deliver(weight, dy2.float().t() @ t2.float())
 
 
-def drain_deferred_wgrads(keep: int = 0) -> int:
-    """Run the postponed weight-gradient products, oldest first, until at most ``keep`` remain.  The result lands in
-    the parameter's gradient buffer (or is added to ``.grad`` when there is none).  Returns how many ran."""
+def drain_deferred_wgrads(keep: int = 0, only=None) -> int:
+    """Run the postponed weight-gradient products, oldest first, until at most ``keep`` remain (``only``: a set of
+    ``id(weight)`` - run just the products of those weights, e.g. one layer's).  The result lands in the parameter's
+    gradient buffer (or is added to ``.grad`` when there is none).  Returns how many ran."""
     ran = 0
-    while len(_DEFERRED_WGRADS) > keep:
-        weight, dy2, t2 = _DEFERRED_WGRADS.pop(0)
+    if only is not None:
+        mine = [e for e in _DEFERRED_WGRADS if id(e[0]) in only]
+        _DEFERRED_WGRADS[:] = [e for e in _DEFERRED_WGRADS if id(e[0]) not in only]
+        todo = mine
+    else:
+        todo = None
+    while (todo if todo is not None else len(_DEFERRED_WGRADS) > keep):
+        weight, dy2, t2 = todo.pop(0) if todo is not None else _DEFERRED_WGRADS.pop(0)
         with torch.no_grad():
             g = weight_grad(weight, dy2, t2) if t2.is_cuda else deliver(weight, dy2.float().t() @ t2.float())
         if g is not None:

@@ -330,7 +330,7 @@ def test_unsupported_config_fields_are_refused():
     base = dict(num_layers=1, hidden_size=32, num_attention_heads=4)
     TransformerConfig(**base)                                           # defaults pass
     for name, value in (("init_model_with_meta_device", True),
-                        ("delay_wgrad_compute", True), ("fp8_dot_product_attention", True)):
+                        ("fp8_multi_head_attention", True), ("fp8_dot_product_attention", True)):
         assert name in UNSUPPORTED_FIELDS
         with pytest.raises(ValueError, match="not supported"):
             TransformerConfig(**base, **{name: value})
