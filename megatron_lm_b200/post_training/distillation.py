@@ -242,13 +242,16 @@ class DistillationModel(nn.Module):
 
     def forward(self, *args, **kwargs):
         self._kept.clear()
-        if not self.only_student:
+        # evaluation needs the student only; between pipeline stages the two hidden states still travel together,
+        # so the teacher keeps running there to hold the exchanged shape
+        run_teacher = not self.only_student and (self.training or not (self.pre_process and self.post_process))
+        if run_teacher:
             t_kwargs = dict(kwargs)
             t_kwargs.pop("labels", None)                     # the teacher's own loss is never needed
             with torch.no_grad():
                 t_out = self._teacher(*args, **t_kwargs)
         s_out = self.student(*args, **kwargs)
-        if self.post_process or self.only_student:
+        if self.post_process or not run_teacher:
             return s_out
         return torch.cat([s_out, t_out.detach().to(s_out.dtype)], dim=-1)
 
