@@ -42,6 +42,18 @@ class SamplingParams:
     top_n_logprobs: int = 0
     return_prompt_top_n_logprobs: bool = False
 
+    def add_attributes(self, attribute_value_pair: dict) -> None:
+        """Extra request-level attributes (e.g. ``{"min_length": 4}``) carried along with the standard ones."""
+        for k, v in attribute_value_pair.items():
+            setattr(self, k, v)
+
+
+def top_n_log_probs(logits_row: torch.Tensor, n: int) -> Dict[int, float]:
+    """{token id: log probability} of the ``n`` most likely next tokens."""
+    lp = torch.log_softmax(logits_row.float(), dim=-1)
+    vals, idx = lp.topk(min(n, lp.numel()))
+    return {int(i): float(v) for i, v in zip(idx.tolist(), vals.tolist())}
+
 
 def sample_from_logits(logits: torch.Tensor, params: SamplingParams, vocab_size: Optional[int] = None,
                        generator=None) -> torch.Tensor:
@@ -346,6 +358,9 @@ class InferenceRequest:
     slot: int = -1
     prompt: Optional[str] = None
     generated_text: Optional[str] = None
+    segments: Optional[List[str]] = None                       # every token detokenised on its own (return_segments)
+    generated_top_n_logprobs: List[Dict[int, float]] = field(default_factory=list)
+    prompt_top_n_logprobs: List[Dict[int, float]] = field(default_factory=list)
 
 
 class Scheduler:
@@ -409,6 +424,10 @@ class StaticInferenceEngine:
         self.model.eval()
         done = torch.zeros(b, dtype=torch.bool, device=dev)
         log_probs = [[] for _ in range(b)]
+        top_n = [[] for _ in range(b)]
+        if sp.return_prompt_top_n_logprobs:
+            raise NotImplementedError("top-n log probabilities of the prompt come from the dynamic engine "
+                                      "(the static engine steps through ragged prompts token by token)")
         prev = 0
         for pos in range(min_len, total):
             logits = self.model(ids[:, prev:pos], inference_context=ctx)            # [b, pos-prev, v]
@@ -424,6 +443,10 @@ class StaticInferenceEngine:
                 for i in range(b):
                     if not bool(in_prompt[i]) and not bool(done[i]):
                         log_probs[i].append(float(lp[i]))
+            if sp.top_n_logprobs > 0:
+                for i in range(b):
+                    if not bool(in_prompt[i]) and not bool(done[i]):
+                        top_n[i].append(top_n_log_probs(last[i], sp.top_n_logprobs))
             ids[:, pos] = new
             if self.eod is not None:
                 done |= (new == self.eod) & ~in_prompt
@@ -439,8 +462,11 @@ class StaticInferenceEngine:
             if self.eod is not None and self.eod in gen:
                 gen = gen[:gen.index(self.eod) + 1]
             req = InferenceRequest(i, toks[i], sp, gen, log_probs[i], "completed")
+            req.generated_top_n_logprobs = top_n[i][:len(gen)]
             if self.tokenizer is not None:
                 req.generated_text = self.tokenizer.detokenize(gen)
+                if sp.return_segments:
+                    req.segments = [self.tokenizer.detokenize([t]) for t in toks[i] + gen]
             out.append(req)
         return out
 
@@ -538,8 +564,16 @@ class DynamicInferenceEngine:
             last = logits[start + n - 1].float().unsqueeze(0)
             tok = int(sample_from_logits(last, req.sampling_params, None, generator)[0])
             req.generated_tokens.append(tok)
-            if req.sampling_params.return_log_probs:
+            sp = req.sampling_params
+            if sp.return_log_probs:
                 req.generated_log_probs.append(float(torch.log_softmax(last, -1)[0, tok]))
+            if sp.top_n_logprobs > 0:
+                req.generated_top_n_logprobs.append(top_n_log_probs(last[0], sp.top_n_logprobs))
+                if sp.return_prompt_top_n_logprobs and n > 1 and not req.prompt_top_n_logprobs:
+                    # the prefill step: position i of the prompt predicts token i + 1
+                    npr = len(req.prompt_tokens)
+                    req.prompt_top_n_logprobs = [top_n_log_probs(logits[start + i], sp.top_n_logprobs)
+                                                 for i in range(min(n, npr) - 1)]
             total = len(req.prompt_tokens) + len(req.generated_tokens)
             if (self.eod is not None and tok == self.eod) or total >= self.max_len or \
                     len(req.generated_tokens) >= req.sampling_params.num_tokens_to_generate:
@@ -547,6 +581,8 @@ class DynamicInferenceEngine:
                 sch.complete(req)
                 if self.tokenizer is not None:
                     req.generated_text = self.tokenizer.detokenize(req.generated_tokens)
+                    if req.sampling_params.return_segments:
+                        req.segments = [self.tokenizer.detokenize([t]) for t in req.prompt_tokens + req.generated_tokens]
                 finished.append(req)
         return finished
 

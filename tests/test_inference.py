@@ -206,3 +206,37 @@ def test_dynamic_engine_admission_limits():
     assert eng.context.max_requests == 4 and eng.scheduler.max_batch_size == 4
     eng = DynamicInferenceEngine(model, max_requests=1, max_sequence_length=32, chunk_size=4, max_requests_override=3)
     assert eng.context.max_requests == 3
+
+
+def test_top_n_log_probabilities_and_segments():
+    model = _model()
+
+    class Tok:
+        eod = None
+        def tokenize(self, s): return [int(x) for x in s.split()]
+        def detokenize(self, ids): return " ".join(f"<{i}>" for i in ids)
+    prompts = [[5, 9, 2, 33], [11, 4, 6, 8]]
+    sp = SamplingParams(top_k=1, num_tokens_to_generate=3, return_log_probs=True, top_n_logprobs=4,
+                        return_prompt_top_n_logprobs=True, return_segments=True)
+    sp.add_attributes({"min_length": 2})
+    assert sp.min_length == 2
+    dyn = DynamicInferenceEngine(model, max_requests=4, max_sequence_length=32, chunk_size=4, tokenizer=Tok())
+    for req, p in zip(dyn.generate(prompts, sp), prompts):
+        assert len(req.generated_top_n_logprobs) == 3 and all(len(d) == 4 for d in req.generated_top_n_logprobs)
+        # greedy decoding: the chosen token is the most likely one and its log probability matches
+        for tok, lp, alts in zip(req.generated_tokens, req.generated_log_probs, req.generated_top_n_logprobs):
+            best = max(alts, key=alts.get)
+            assert best == tok and abs(alts[tok] - lp) < 1e-5
+        assert len(req.prompt_top_n_logprobs) == len(p) - 1
+        with torch.no_grad():
+            full = torch.log_softmax(model(torch.tensor([p]))[0].float(), -1)
+        for i, alts in enumerate(req.prompt_top_n_logprobs):
+            want = full[i].topk(4)
+            assert sorted(alts) == sorted(want.indices.tolist())
+            assert abs(max(alts.values()) - float(want.values[0])) < 1e-4
+        assert req.segments == [f"<{t}>" for t in p + req.generated_tokens]
+    sp2 = SamplingParams(top_k=1, num_tokens_to_generate=3, top_n_logprobs=2, return_segments=True)
+    st = StaticInferenceEngine(model, tokenizer=Tok(), max_batch_size=2, max_sequence_length=32).generate(prompts, sp2)
+    assert all(len(r.generated_top_n_logprobs) == 3 and len(r.segments) == 7 for r in st)
+    with pytest.raises(NotImplementedError):
+        StaticInferenceEngine(model, max_batch_size=2, max_sequence_length=32).generate(prompts, sp)
