@@ -40,6 +40,7 @@ class RetroConfig(TransformerConfig):
     retro_retrieved_length: Optional[int] = None
     retro_split_preprocessing: Optional[str] = None
     retro_verify_neighbor_count: bool = True
+    retro_attention_gate: float = 1.0           # multiplies the retrieval update (0 switches retrieval off)
 
     def __post_init__(self):
         super().__post_init__()
@@ -108,7 +109,8 @@ class RetroDecoderCrossAttention(nn.Module):
             out = out + bias
         out = out.view(m, b, l, h).permute(2, 0, 1, 3).reshape(l * m, b, h)
         out = F.pad(out, (0, 0, 0, 0, pad, 0))[:n]                 # undo the shift; first m-1 rows get zeros
-        return hidden + F.dropout(out, self.config.hidden_dropout, self.training), context
+        gate = getattr(self.config, "retro_attention_gate", 1.0)
+        return hidden + gate * F.dropout(out, self.config.hidden_dropout, self.training), context
 
 
 class RetroModel(GPTModel):

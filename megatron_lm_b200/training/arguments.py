@@ -283,7 +283,6 @@ UNUSED_FLAGS = {
     # Retro / biencoder / vision programs that are not (fully) built
     "retro_add_retriever": (_W, "pretrain_retro.py always builds the retriever"),
     "retro_cyclic_train_iters": (_R, "cyclic Retro training is not built"),
-    "retro_attention_gate": (_R, "the Retro attention gate is fixed at 1"),
     "sample_rate": (_W, "the retriever evaluation tasks are not built"),
     "evidence_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
     "block_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),

@@ -38,7 +38,10 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
     kw = {f.name: getattr(config, f.name) for f in dataclasses.fields(config) if f.init}
     rcfg = RetroConfig(**kw, retro_chunk_length=args.retro_chunk_length, retro_num_neighbors=args.retro_num_neighbors,
                        retro_num_retrieved_chunks=args.retro_num_retrieved_chunks,
-                       retro_encoder_num_layers=args.retro_encoder_layers, retro_project_dir=args.retro_project_dir)
+                       retro_encoder_num_layers=args.retro_encoder_layers, retro_project_dir=args.retro_project_dir,
+                       retro_attention_gate=getattr(args, "retro_attention_gate", 1.0),
+                       retro_encoder_hidden_dropout=getattr(args, "retro_encoder_hidden_dropout", 0.1),
+                       retro_encoder_attention_dropout=getattr(args, "retro_encoder_attention_dropout", 0.1))
     for name in ("no_sync_func", "grad_sync_func", "param_sync_func", "finalize_model_grads_func", "grad_scale_func"):
         setattr(rcfg, name, getattr(config, name, None))
     return RetroModel(rcfg, args.padded_vocab_size, args.max_position_embeddings, pre_process=pre_process,

@@ -33,6 +33,11 @@ def test_retro_causality_and_grad():
     p = m.retro_layers["6"].attn.linear_q.weight
     g = p.grad if p.grad is not None else p.main_grad
     assert g.abs().sum() > 0
+    # a closed gate takes the retrieval out: the neighbours no longer matter
+    cfg.retro_attention_gate = 0.0
+    m.eval()
+    with torch.no_grad():
+        assert torch.allclose(m(ids, context_input_ids=ctx), m(ids, context_input_ids=ctx2), atol=1e-6)
 
 
 def _corpus(tmp_path, ndocs=12, seed=0):
