@@ -96,13 +96,41 @@ def _boto3_client():
     return boto3.client("s3")
 
 
+class _MscClient:
+    """The five client methods on top of the multi-storage client's file interface (profile = bucket)."""
+
+    def __init__(self, msc):
+        self.msc = msc
+
+    def _url(self, bucket, key):
+        return f"{MSC_PREFIX}{bucket}/{key}"
+
+    def download_file(self, Bucket, Key, Filename):
+        self.msc.download_file(self._url(Bucket, Key), Filename)
+
+    def upload_file(self, Filename, Bucket, Key):
+        self.msc.upload_file(self._url(Bucket, Key), Filename)
+
+    def head_object(self, Bucket, Key):
+        info = self.msc.info(self._url(Bucket, Key))
+        return {"ContentLength": getattr(info, "content_length", None)}
+
+    def get_object(self, Bucket, Key, Range):
+        lo, _, hi = Range.partition("=")[2].partition("-")
+        with self.msc.open(self._url(Bucket, Key), "rb") as f:
+            f.seek(int(lo))
+            return {"Body": _Body(f.read(int(hi) - int(lo) + 1))}
+
+    def close(self):
+        pass
+
+
 def _msc_client():
+    from ..utils.msc import MultiStorageClientFeature
     try:
-        import multistorageclient as msc          # noqa: F401
-    except ImportError as e:
-        raise RuntimeError("msc:// paths need the multistorageclient package, or a client registered with "
-                           "register_client_factory('msc', ...)") from e
-    raise RuntimeError("register a client for msc:// with register_client_factory('msc', ...)")
+        return _MscClient(MultiStorageClientFeature.import_package())
+    except RuntimeError as e:
+        raise RuntimeError(f"msc:// paths: {e}; or register a client with register_client_factory('msc', ...)") from e
 
 
 _FACTORIES: Dict[str, Callable[[], ObjectStorageClient]] = {"s3": _boto3_client, "msc": _msc_client}

@@ -274,7 +274,6 @@ UNUSED_FLAGS = {
     "tp_comm_overlap_cfg": (_W, "the fused tensor-parallel kernels take no user-buffer configuration"),
     "enable_experimental": (_W, "no experimental-API gate"),
     "disable_mamba_mem_eff_path": (_W, "one Mamba forward path"),
-    "enable_msc": (_W, "the multi-storage client is not built; paths are local"),
     "kitchen_config_file": (_R, "the Kitchen quantisation back end is not built"),
     "kitchen_recipe_number": (_R, "the Kitchen quantisation back end is not built"),
     # inference engine knobs read by the engines' own constructors, not from the training arguments

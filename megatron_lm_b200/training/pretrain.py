@@ -66,6 +66,8 @@ def initialize_megatron(extra_args_provider=None, args_defaults=None, ignore_unk
     set_args(args)
     from ..utils.log_handler import setup_logging
     setup_logging(getattr(args, "logging_level", None))
+    from ..utils.msc import configure_from_args as _configure_msc
+    _configure_msc(args)                       # --disable-msc: paths are opened as plain files
     use_cuda = torch.cuda.is_available() and args.distributed_backend == "nccl"
     if use_cuda:
         torch.cuda.set_device(args.local_rank)

@@ -307,3 +307,28 @@ def test_activation_offloading_to_the_host_keeps_the_gradients():
         grads.append({n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None})
     assert packed == [0, 2]                                      # one offloading context per offloaded layer
     assert grads[0].keys() == grads[1].keys() and all(torch.equal(grads[0][k], grads[1][k]) for k in grads[0])
+
+
+def test_multi_storage_client_switch(tmp_path):
+    """Without the package the feature reports off whatever the flag says, and file helpers use the local file
+    system; msc:// dataset paths name the missing package in their error."""
+    import pickle
+    from types import SimpleNamespace
+    from megatron_lm_b200.data import object_storage as osu
+    from megatron_lm_b200.utils import msc
+    have = msc._msc is not None
+    assert msc.configure_from_args(SimpleNamespace(enable_msc=True)) == have
+    assert msc.configure_from_args(SimpleNamespace(enable_msc=False)) is False
+    assert not msc.MultiStorageClientFeature.is_enabled()
+    with pytest.raises(RuntimeError):
+        msc.MultiStorageClientFeature.import_package()
+    flag = pickle.loads(pickle.dumps(msc.MultiStorageClientFeature))
+    assert flag._enabled is False
+    p = tmp_path / "d" / "x.txt"
+    msc.makedirs(str(p.parent))
+    with msc.open_file(str(p), "w") as f:
+        f.write("hi")
+    assert msc.path_exists(str(p)) and not msc.path_exists(str(p) + ".none")
+    if not have:
+        with pytest.raises(RuntimeError, match="multistorageclient|switched off"):
+            osu.get_client("msc://profile/data.bin")
