@@ -121,6 +121,9 @@ UNSUPPORTED_FIELDS = {
     "fp8_dot_product_attention": "attention runs in bf16 / fp16",
     "fp8_multi_head_attention": "attention runs in bf16 / fp16",
     "init_model_with_meta_device": "parameters are created on their device",
+    "enable_cuda_graph": "the training loop captures no graphs; wrap single modules with utils.cuda_graphs.GraphedModule "
+                         "or a whole step with FullIterationGraph from a hand-written loop",
+    "external_cuda_graph": "the training loop captures no graphs",
     "use_kitchen": "the Kitchen quantisation back end is not built",
     "quant_recipe": "per-layer quantisation recipes are not built",
     "heterogeneous_block_specs": "build heterogeneous models through models.heterogeneous",

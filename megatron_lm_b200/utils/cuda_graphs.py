@@ -36,18 +36,26 @@ class GraphedModule(nn.Module):
         self.pool = pool
         self._captured = False
         self._calls = 0
+        self._n_rot = 0
+
+    def _call(self, flat):
+        """The wrapped module on the flat tensor list: positional inputs, then (cos, sin) when the call came with a
+        ``rotary`` pair."""
+        if self._n_rot:
+            return self.module(*flat[:-2], rotary=(flat[-2], flat[-1]))
+        return self.module(*flat)
 
     # -- capture --------------------------------------------------------------------
     def _capture(self, args):
-        mod = self.module
-        params = [p for p in mod.parameters() if p.requires_grad]
+        mod = self
+        params = [p for p in self.module.parameters() if p.requires_grad]
         self.params = params
         self.static_in = [a.detach().clone().requires_grad_(a.requires_grad) if torch.is_tensor(a) else a for a in args]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(self.num_warmup):
-                out = mod(*self.static_in)
+                out = mod._call(self.static_in)
                 outs = out if isinstance(out, (tuple, list)) else (out,)
                 outs_t = [o for o in outs if torch.is_tensor(o) and o.requires_grad]
                 gin = [a for a in self.static_in if torch.is_tensor(a) and a.requires_grad]
@@ -60,7 +68,7 @@ class GraphedModule(nn.Module):
                 p.main_grad.zero_()
         self.fwd_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.fwd_graph, pool=self.pool):
-            out = mod(*self.static_in)
+            out = mod._call(self.static_in)
         self.out_is_tuple = isinstance(out, (tuple, list))
         outs = list(out) if self.out_is_tuple else [out]
         self.static_out = outs
@@ -80,10 +88,19 @@ class GraphedModule(nn.Module):
         self._captured = True
 
     # -- replay ----------------------------------------------------------------------
-    def forward(self, *args):
+    def forward(self, *args, rotary=None, **kwargs):
+        """Positional tensors and an optional ``rotary=(cos, sin)`` pair are graph inputs; any other argument that is
+        not None (masks, inference contexts, encoder outputs) sends the call down the eager path."""
+        if any(v is not None for v in kwargs.values()):
+            return self.module(*args, rotary=rotary, **kwargs)
+        n_rot = 0 if rotary is None else 2
+        if self._captured and n_rot != self._n_rot:
+            return self.module(*args, rotary=rotary)
+        args = tuple(args) + (tuple(rotary) if rotary is not None else ())
         if not _is_cuda(args) or not torch.is_grad_enabled() and not self._captured:
-            return self.module(*args)
+            return self.module(*args[:len(args) - n_rot], rotary=rotary) if n_rot else self.module(*args)
         if not self._captured:
+            self._n_rot = n_rot
             self._capture(args)
         runner = self
 
@@ -115,6 +132,19 @@ class GraphedModule(nn.Module):
         tensors = [a if torch.is_tensor(a) else torch.empty(0) for a in args]
         outs = _Replay.apply(*tensors, *self.params)
         return outs if self.out_is_tuple else outs[0]
+
+
+def _graphed_getattr(self, name):
+    try:
+        return nn.Module.__getattr__(self, name)
+    except AttributeError:
+        mod = self.__dict__.get("_modules", {}).get("module")
+        if mod is None:
+            raise
+        return getattr(mod, name)
+
+
+GraphedModule.__getattr__ = _graphed_getattr          # layer_number, self_attention, ... of the wrapped layer
 
 
 class CudaGraphManager:

@@ -332,3 +332,21 @@ def test_multi_storage_client_switch(tmp_path):
     if not have:
         with pytest.raises(RuntimeError, match="multistorageclient|switched off"):
             osu.get_client("msc://profile/data.bin")
+
+
+def test_graphed_module_passes_other_arguments_through_on_the_eager_path():
+    """Off a GPU, and whenever a call carries a mask / context, ``GraphedModule`` is a transparent wrapper: keyword
+    arguments reach the layer, attributes of the layer stay visible."""
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.transformer import TransformerLayer
+    from megatron_lm_b200.utils.cuda_graphs import GraphedModule
+    cfg = TransformerConfig(num_layers=1, hidden_size=32, num_attention_heads=4, ffn_hidden_size=64, hidden_dropout=0.0,
+                            attention_dropout=0.0, use_cpu_initialization=True)
+    torch.manual_seed(0)
+    layer = TransformerLayer(cfg, 1)
+    g = GraphedModule(layer)
+    x = torch.randn(6, 2, 32)
+    cos, sin = torch.randn(6, 4).cos(), torch.randn(6, 4).sin()
+    assert torch.equal(g(x, rotary=(cos, sin)), layer(x, rotary=(cos, sin)))
+    assert torch.equal(g(x), layer(x)) and not g._captured
+    assert g.layer_number == 1 and g.self_attention is layer.self_attention
