@@ -304,9 +304,6 @@ UNUSED_FLAGS = {
     "inprocess_completion_timeout": (_W, "one timeout: --inprocess-barrier-timeout"),
     "inprocess_last_call_wait": (_W, "no last-call phase"), "inprocess_termination_grace_time": (_W, "no external monitor process"),
     "inprocess_granularity": (_W, "restarts are per rank"), "inprocess_active_world_size": (_R, "spare ranks are not built"),
-    "one_logger_project": (_W, "the one-logger adapter records locally"), "one_logger_run_name": (_W, "the one-logger adapter records locally"),
-    "one_logger_async": (_W, "the one-logger adapter records locally"), "app_tag_run_name": (_W, "the one-logger adapter records locally"),
-    "app_tag_run_version": (_W, "the one-logger adapter records locally"),
     "log_throughput": (_W, "throughput is part of every log line"),
     "adlr_autoresume_interval": (_W, "no cluster auto-resume service"),
     # checkpoint options

@@ -67,8 +67,12 @@ class _JsonlWriter:
 class OneLoggerStub:
     """Accepts the callback surface of the one-logger integration and records the last values."""
 
-    def __init__(self):
-        self.store = {}
+    def __init__(self, project: str = "", run_name: str = "", app_tag_run_name: str = "", app_tag_run_version: str = "",
+                 is_async: bool = False):
+        """The identity of the run as the flags give it (``--one-logger-project``, ``--one-logger-run-name``,
+        ``--app-tag-run-name``, ``--app-tag-run-version``, ``--one-logger-async``) goes into the record."""
+        self.store = {"project": project, "run_name": run_name, "app_tag_run_name": app_tag_run_name,
+                      "app_tag_run_version": app_tag_run_version, "async": bool(is_async)}
 
     def log_metrics(self, metrics: dict):
         self.store.update(metrics)
@@ -110,7 +114,11 @@ def set_global_variables(args, build_tokenizer: bool = True):
             _GLOBALS["wandb"] = _JsonlWriter(os.path.join(getattr(args, "wandb_save_dir", None) or "wandb",
                                                           "metrics.jsonl"))
     if getattr(args, "enable_one_logger", False) and _is_last_rank(args):
-        _GLOBALS["one_logger"] = OneLoggerStub()
+        _GLOBALS["one_logger"] = OneLoggerStub(getattr(args, "one_logger_project", "") or "",
+                                               getattr(args, "one_logger_run_name", "") or "",
+                                               getattr(args, "app_tag_run_name", "") or "",
+                                               getattr(args, "app_tag_run_version", "") or "",
+                                               getattr(args, "one_logger_async", False))
     if getattr(args, "exit_signal_handler", False):
         from .resilience import DistributedSignalHandler
         _GLOBALS["signal_handler"] = DistributedSignalHandler().__enter__()

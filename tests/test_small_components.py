@@ -76,7 +76,9 @@ def test_global_variables_and_fallback_writers(tmp_path):
         G.get_args()
     args = SimpleNamespace(rank=0, world_size=1, timing_log_level=1, timing_log_option="max",
                            tensorboard_dir=str(tmp_path / "tb"), wandb_project=None, enable_one_logger=True,
-                           exit_signal_handler=False, log_energy=False, tokenizer_type=None)
+                           exit_signal_handler=False, log_energy=False, tokenizer_type=None,
+                           one_logger_project="proj", one_logger_run_name="run-7", app_tag_run_name="tag",
+                           app_tag_run_version="1.2", one_logger_async=True)
     G.set_global_variables(args, build_tokenizer=False)
     assert G.get_args() is args and G.get_timers() is not None
     w = G.get_tensorboard_writer()
@@ -86,6 +88,8 @@ def test_global_variables_and_fallback_writers(tmp_path):
     one.on_train_start(train_iterations_start=0)
     one.log_metrics({"a": 1})
     assert one.store_has_key("train_iterations_start")
+    assert one.store_get("project") == "proj" and one.store_get("run_name") == "run-7" and one.store_get("async") is True
+    assert one.store_get("app_tag_run_version") == "1.2"
     jw = G._JsonlWriter(str(tmp_path / "m" / "x.jsonl"))
     jw.add_scalar("lr", 0.1, 2)
     jw.log({"loss": 2.0}, step=3)
