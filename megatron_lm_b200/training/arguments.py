@@ -158,6 +158,14 @@ def validate_args(args, defaults: Optional[dict] = None):
         raise ValueError("--tp-comm-overlap needs --sequence-parallel")
     if getattr(args, "replication", False) and getattr(args, "non_persistent_ckpt_type", None) != "local":
         raise ValueError("--replication needs --non-persistent-ckpt-type local")
+    if getattr(args, "replication", False):
+        # the reference's clique replication (a copy on factor - 1 other ranks) is the code with one data member and
+        # factor - 1 parity members per stripe: every parity member then IS a copy.  The erasure-coded manager
+        # places the members itself, so --replication-jump (the rank distance between copies) has nothing to set.
+        factor = getattr(args, "replication_factor", 2) or 2
+        if factor < 2:
+            raise ValueError("--replication-factor must be at least 2")
+        args.ec_data_shards, args.ec_parity_shards = 1, factor - 1
     # model sizes
     if args.num_layers is None and (getattr(args, "decoder_num_layers", None) or getattr(args, "encoder_num_layers", None)):
         args.num_layers = getattr(args, "decoder_num_layers", None) or args.encoder_num_layers
@@ -319,8 +327,7 @@ UNUSED_FLAGS = {
     "ckpt_fully_parallel_load": (_W, "sharded loads read each piece once per data-parallel group"),
     "ckpt_assume_constant_structure": (_W, "no save-plan cache"),
     "load_model_opt_format": (_R, "ModelOpt checkpoints are not read"),
-    "replication_jump": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
-    "replication_factor": (_W, "in-memory checkpoints are erasure-coded, not replicated"),
+    "replication_jump": (_W, "the in-memory checkpoint manager chooses where the copies of a stripe live"),
 }
 
 

