@@ -267,7 +267,7 @@ def cosine_schedule(base: float, final: float, total_iters: int) -> torch.Tensor
 
 
 class DINOPretrainModel(nn.Module):
-    """Student and momentum teacher (ViT backbone + ``DINOHead`` each).  Training: ``forward(list of crops)`` runs the
+    """Student and momentum teacher (a backbone - ViT, or MiT / Swin with ``backbone_type`` - + ``DINOHead`` each).  Training: ``forward(list of crops)`` runs the
     student over all crops (one backbone pass per resolution) and the teacher over the two global crops, and returns
     (student output, teacher output); evaluation returns the teacher's class-token features for the k-NN monitor.
     ``after_optimizer_step`` moves the teacher towards the student with a momentum that follows a cosine from 0.996
@@ -277,18 +277,26 @@ class DINOPretrainModel(nn.Module):
                  out_dim: int = 65536, head_hidden: int = 2048, bottleneck: int = 256, norm_last_layer: bool = False,
                  local_crops: int = 10, warmup_teacher_temp: float = 0.04, teacher_temp: float = 0.07,
                  warmup_teacher_temp_iters: int = 0, total_iters: int = 1, freeze_last_layer_iters: int = 0,
-                 base_momentum: float = 0.996, dp_group=None):
+                 base_momentum: float = 0.996, dp_group=None, backbone_type: str = "vit", swin_type: str = "tiny"):
         super().__init__()
         self.config = config
+        self.backbone_type = backbone_type
         dev, dt = _device(config), config.params_dtype
 
-        def tower(norm_last):
+        def tower(norm_last, teacher):
+            if backbone_type == "vit":
+                backbone, width = CLIPViTModel(config, patch_dim=patch_dim, img_h=img_h, img_w=img_w,
+                                               add_class_token=True), config.hidden_size
+            else:       # hierarchical backbones return the pooled feature vector themselves
+                from .vision_backbones import build_feature_backbone
+                backbone, width = build_feature_backbone(backbone_type, config, img_h=img_h, img_w=img_w,
+                                                         patch_dim=patch_dim, swin_type=swin_type, teacher=teacher)
             return nn.ModuleDict({
-                "backbone": CLIPViTModel(config, patch_dim=patch_dim, img_h=img_h, img_w=img_w, add_class_token=True),
-                "head": DINOHead(config.hidden_size, out_dim, head_hidden, bottleneck, norm_last_layer=norm_last,
+                "backbone": backbone,
+                "head": DINOHead(width, out_dim, head_hidden, bottleneck, norm_last_layer=norm_last,
                                  device=dev, dtype=dt)})
-        self.student = tower(norm_last_layer)
-        self.teacher = tower(True)
+        self.student = tower(norm_last_layer, False)
+        self.teacher = tower(True, True)
         self.teacher.load_state_dict(self.student.state_dict())
         for p in self.teacher.parameters():
             p.requires_grad_(False)
@@ -303,9 +311,9 @@ class DINOPretrainModel(nn.Module):
     def set_input_tensor(self, t):
         pass
 
-    @staticmethod
-    def _features(tower, images):
-        return tower["backbone"](images)[:, 0]
+    def _features(self, tower, images):
+        out = tower["backbone"](images)
+        return out[:, 0] if self.backbone_type == "vit" else out
 
     def forward(self, images):
         if not self.training:

@@ -298,8 +298,6 @@ UNUSED_FLAGS = {
     "data_sharding": (_W, "the sampler always gives each data-parallel rank its own part"),
     "vision_pretraining_type": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice"),
     "vision_pretraining": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice; the flag selects nothing"),
-    "vision_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
-    "swin_backbone_type": (_W, "the vision programs use the ViT backbone (no MiT / Swin)"),
     # resilience / logging services that run with fixed settings here
     "run_workload_inspector_server": (_W, "no workload-inspector server"),
     "inprocess_monitor_thread_interval": (_W, "the restart wrapper polls once per step"),

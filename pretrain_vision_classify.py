@@ -16,6 +16,7 @@ import torch.nn.functional as F
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from megatron_lm_b200.models.vision import VitClassificationModel  # noqa: E402
+from megatron_lm_b200.models.vision_backbones import MitClassificationModel  # noqa: E402
 from megatron_lm_b200.parallel import state  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.batch import broadcast_data  # noqa: E402
@@ -27,8 +28,18 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
     args = get_args()
     if state.get_pipeline_model_parallel_world_size() > 1:
         raise NotImplementedError("the vision classifier is trained without pipeline parallelism")
-    print_rank_0("building the ViT classification model ...")
+    print_rank_0(f"building the {args.vision_backbone_type} classification model ...")
+    if args.vision_backbone_type == "mit":
+        _data_parallel_only(args)
+        return MitClassificationModel(config, args.num_classes)
+    if args.vision_backbone_type != "vit":
+        raise ValueError(f"no classification model on the {args.vision_backbone_type} backbone (vit or mit)")
     return VitClassificationModel(config, args.num_classes, args.img_h, args.img_w, args.patch_dim)
+
+
+def _data_parallel_only(args):
+    if args.tensor_model_parallel_size > 1:
+        raise NotImplementedError("the MiT and Swin backbones are data parallel only")
 
 
 class MockImageDataset(torch.utils.data.Dataset):

@@ -47,7 +47,7 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
         warmup_teacher_temp=args.dino_warmup_teacher_temp, teacher_temp=args.dino_teacher_temp,
         warmup_teacher_temp_iters=args.dino_warmup_teacher_temp_epochs * args.iter_per_epoch,
         total_iters=args.train_iters, freeze_last_layer_iters=int(args.dino_freeze_last_layer * args.iter_per_epoch),
-        dp_group=dp)
+        dp_group=dp, backbone_type=args.vision_backbone_type, swin_type=args.swin_backbone_type)
 
 
 def _crop(img: torch.Tensor, scale, out_hw, rng) -> torch.Tensor:

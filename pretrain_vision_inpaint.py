@@ -15,6 +15,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import pretrain_vision_classify as base  # noqa: E402
 from megatron_lm_b200.models.vision import VitInpaintingModel, psnr, random_patch_mask, ssim  # noqa: E402
+from megatron_lm_b200.models.vision_backbones import MitInpaintingModel  # noqa: E402
 from megatron_lm_b200.parallel import state  # noqa: E402
 from megatron_lm_b200.training.arguments import get_args  # noqa: E402
 from megatron_lm_b200.training.pretrain import pretrain, print_rank_0  # noqa: E402
@@ -25,7 +26,14 @@ def model_provider(pre_process=True, post_process=True, vp_stage=None, config=No
     args = get_args()
     if state.get_pipeline_model_parallel_world_size() > 1:
         raise NotImplementedError("the in-painting model is trained without pipeline parallelism")
-    print_rank_0("building the ViT in-painting model ...")
+    print_rank_0(f"building the {args.vision_backbone_type} in-painting model ...")
+    if args.vision_backbone_type == "mit":
+        if args.tensor_model_parallel_size > 1:
+            raise NotImplementedError("the MiT backbone is data parallel only")
+        dp = state.get_data_parallel_group() if state.get_data_parallel_world_size() > 1 else None
+        return MitInpaintingModel(config, args.img_h, args.img_w, args.patch_dim, sync_group=dp)
+    if args.vision_backbone_type != "vit":
+        raise ValueError(f"no in-painting model on the {args.vision_backbone_type} backbone (vit or mit)")
     return VitInpaintingModel(config, args.img_h, args.img_w, args.patch_dim)
 
 

@@ -405,6 +405,23 @@ def test_vision_dino_program_trains_with_momentum_teacher_and_knn_monitor():
     assert re.search(r"validation loss at iteration 12 .*knn_acc_10 value: [0-9.E+-]+", out)
 
 
+def test_vision_programs_on_the_mit_and_swin_backbones():
+    """--vision-backbone-type mit | swin: the classifier and the in-painting model on MiT-B3, DINO towers on Swin."""
+    out = _program("pretrain_vision_classify.py", ["--train-iters", "3", "--eval-interval", "3",
+                                                   "--vision-backbone-type", "mit"])
+    assert "building the mit classification model" in out and sorted(_iters(out, "loss")) == [1, 2, 3]
+    assert "accuracy" in out
+    out = _program("pretrain_vision_inpaint.py", ["--train-iters", "3", "--eval-interval", "3", "--patch-dim", "4",
+                                                  "--vision-backbone-type", "mit"])
+    assert sorted(_iters(out, "loss")) == [1, 2, 3] and "psnr value" in out
+    out = _program("pretrain_vision_dino.py", ["--train-iters", "3", "--eval-interval", "3", "--dino-out-dim", "64",
+                                               "--dino-head-hidden-size", "48", "--dino-bottleneck-size", "16",
+                                               "--dino-local-crops-number", "2", "--dino-local-img-size", "16",
+                                               "--iter-per-epoch", "4", "--knn-bank-size", "16",
+                                               "--vision-backbone-type", "swin", "--swin-backbone-type", "tiny"])
+    assert sorted(_iters(out, "loss")) == [1, 2, 3] and "knn_acc_10" in out
+
+
 def test_moe_run_upcycled_from_a_dense_checkpoint(tmp_path):
     """--moe-use-upcycling: the mixture-of-experts run starts as the dense model (identical experts, top-k weights
     summing to one: the same validation loss), then trains and saves a checkpoint that resumes as a plain MoE run."""
