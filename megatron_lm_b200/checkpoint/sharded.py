@@ -390,7 +390,9 @@ def model_sharded_state_dict(model: torch.nn.Module, prefix: str = "", *, tp_ran
     layer index from the key and gain a leading global layer axis (reference:
     transformer_block.py:622-698); TP-sharded parameters are placed along their partition dim;
     a strided partition (gated FC1: [gate; up] per rank) is described as ``stride`` separate
-    tensors so that the TP size can change on load (reference: mlp.py:219)."""
+    tensors so that the TP size can change on load (reference: mlp.py:219), and so is a parameter whose rows are
+    a concatenation of unequal segments (``partition_sizes`` / ``partition_names``: the [z | x | B | C | dt] rows of a
+    Mamba mixer's input projection, reference: ssm/mamba_mixer.py ``sharded_state_dict``)."""
     import re
     out: Dict[str, ShardedTensor] = {}
     for name, p in model.state_dict(keep_vars=True).items():
@@ -411,10 +413,14 @@ def model_sharded_state_dict(model: torch.nn.Module, prefix: str = "", *, tp_ran
         stride = int(getattr(p, "partition_stride", 1)) if getattr(p, "tensor_model_parallel", False) else 1
         dim = int(getattr(p, "partition_dim", -1))
         data = p.detach()
-        if stride > 1 and dim >= 0:
-            for i, piece in enumerate(torch.chunk(data, stride, dim=dim)):
+        sizes = getattr(p, "partition_sizes", None) if getattr(p, "tensor_model_parallel", False) else None
+        if (stride > 1 or sizes) and dim >= 0:
+            pieces = torch.split(data, list(sizes), dim=dim) if sizes else torch.chunk(data, stride, dim=dim)
+            names = getattr(p, "partition_names", None) if sizes else None
+            for i, piece in enumerate(pieces):
                 off = list(offsets) + ([(dim + prepend, tp_rank, tp_size)] if is_tp else [])
-                out[f"{name}.part{i}"] = ShardedTensor.from_rank_offsets(f"{key}.part{i}", piece.contiguous(), *off,
+                suffix = names[i] if names else f"part{i}"
+                out[f"{name}.part{i}"] = ShardedTensor.from_rank_offsets(f"{key}.{suffix}", piece.contiguous(), *off,
                                                                          replica_id=replica, prepend_axis_num=prepend)
             continue
         if is_tp and dim >= 0:

@@ -86,6 +86,11 @@ class MambaMixer(nn.Module):
             p.tensor_model_parallel = True
             p.partition_dim = 0
         self.dt_bias._no_weight_decay = self.A_log._no_weight_decay = self.D._no_weight_decay = True
+        # a sharded checkpoint stores every segment as a tensor of its own, so the tensor-parallel size can change
+        seg = [self.di_loc, self.di_loc, self.g_loc * d_state, self.g_loc * d_state, self.h_loc]
+        self.in_proj.weight.partition_sizes, self.in_proj.weight.partition_names = seg, ["z", "x", "B", "C", "dt"]
+        for p in (self.conv_weight, self.conv_bias):
+            p.partition_sizes, p.partition_names = seg[1:4], ["x", "B", "C"]
         self.out_proj = RowParallelLinear(self.d_inner, d_model, config=config,
                                           init_method=config.output_layer_init_method, bias=False, skip_bias_add=True)
         self.eps = config.layernorm_epsilon

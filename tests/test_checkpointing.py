@@ -217,3 +217,67 @@ def test_native_container_still_round_trips(tmp_path):
     assert os.path.isfile(os.path.join(d, "shard_0.pt"))
     out = ds.load({"w": ds.ShardedTensor.from_rank_offsets("w", torch.zeros(2, 3))}, d)
     assert torch.equal(out["w"], torch.arange(6.0).view(2, 3)) and out["it"] == 3
+
+
+# ----------------------------------------------------------------------- Mamba mixers under another tensor-parallel size
+_MAMBA = dict(d_state=8, headdim=8, ngroups=2)
+
+
+def _mamba_global(kind):
+    """The mixer's parameters at tensor-parallel size 1 (hidden 16: inner 32, 4 heads, 2 groups of state 8), each
+    value unique."""
+    g = torch.Generator().manual_seed(77)
+    shapes = {"in_proj.weight": (2 * 32 + 2 * 2 * 8 + 4, 16), "conv_weight": (32 + 2 * 2 * 8, 4), "conv_bias": (32 + 2 * 2 * 8,),
+              "dt_bias": (4,), "A_log": (4,), "D": (4,), "norm_weight": (32,), "out_proj.weight": (16, 32)}
+    return {k: torch.randn(*s, generator=g) for k, s in shapes.items()}[kind] if kind else shapes
+
+
+def _mamba_local(name, full, rank, tp):
+    """The rows (columns of the output projection) that rank ``rank`` of ``tp`` holds: every segment is cut on its
+    own."""
+    def cut(t, sizes, dim=0):
+        return torch.cat([seg.chunk(tp, dim=dim)[rank] for seg in torch.split(t, sizes, dim=dim)], dim=dim)
+    if name == "in_proj.weight":
+        return cut(full, [32, 32, 16, 16, 4])
+    if name in ("conv_weight", "conv_bias"):
+        return cut(full, [32, 16, 16])
+    if name == "out_proj.weight":
+        return full.chunk(tp, dim=1)[rank]
+    return full.chunk(tp, dim=0)[rank]
+
+
+def _mamba_rank(rank, world, tp, d, phase):
+    from megatron_lm_b200.checkpoint import sharded as ds
+    from megatron_lm_b200.config import TransformerConfig
+    from megatron_lm_b200.models.mamba import MambaMixer
+    from megatron_lm_b200.parallel import state
+    state.initialize_model_parallel(tensor_model_parallel_size=tp)
+    cfg = TransformerConfig(num_layers=1, hidden_size=16, num_attention_heads=2, tensor_model_parallel_size=tp,
+                            use_cpu_initialization=True, params_dtype=torch.float32)
+    mixer = MambaMixer(cfg, 1, **_MAMBA)
+    r = state.get_tensor_model_parallel_rank()
+    names = list(_mamba_global(None))
+    params = dict(mixer.named_parameters())
+    assert sorted(params) == sorted(names)
+    with torch.no_grad():
+        for n in names:
+            if phase == "save":
+                params[n].copy_(_mamba_local(n, _mamba_global(n), r, tp))
+            else:
+                params[n].zero_()
+    desc = ds.model_sharded_state_dict(mixer, "mixer.", tp_rank=r, tp_size=tp, dp_rank=rank // tp)
+    assert {"in_proj.weight.part4", "conv_bias.part2"} <= set(desc) and desc["in_proj.weight.part0"].key == "mixer.in_proj.weight.z"
+    if phase == "save":
+        ds.save(desc, d)
+        return
+    ds.load_model_from_sharded(mixer, ds.load(desc, d))
+    for n in names:
+        assert torch.equal(params[n].detach(), _mamba_local(n, _mamba_global(n), r, tp)), n
+
+
+@pytest.mark.parametrize("save_tp,load_tp", [(2, 1), (1, 2), (2, 2)])
+def test_mamba_mixer_sharded_checkpoint_changes_tensor_parallel_size(tmp_path, save_tp, load_tp):
+    d = str(tmp_path / "mamba")
+    os.makedirs(d)
+    run_distributed(_mamba_rank, save_tp, save_tp, d, "save")
+    run_distributed(_mamba_rank, load_tp, load_tp, d, "load")
