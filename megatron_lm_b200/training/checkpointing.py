@@ -111,6 +111,23 @@ def model_sharded_state_dicts(model: Sequence[torch.nn.Module]) -> List[Dict[str
     return out
 
 
+def _part_spans(model_sd, name, p):
+    """A parameter that the model's description stores in several pieces along its first dimension (gated FC1
+    halves, a Mamba mixer's segments): [(description of the piece, first, one-past-last flat index inside the
+    parameter)].  Rows are contiguous, so a flat range of the parameter is a flat range of each piece it crosses."""
+    if int(getattr(p, "partition_dim", -1)) != 0 or f"{name}.part0" not in model_sd:
+        return None
+    spans, at, i = [], 0, 0
+    while f"{name}.part{i}" in model_sd:
+        d = model_sd[f"{name}.part{i}"]
+        n = 1
+        for e in d.local_shape:
+            n *= int(e)
+        spans.append((d, at, at + n))
+        at, i = at + n, i + 1
+    return spans if at == p.numel() else None
+
+
 def optimizer_sharded_state_dict(optimizer, model: Sequence[torch.nn.Module],
                                  model_sd: List[Dict[str, ds.ShardedTensor]]) -> Dict[str, Any]:
     """Optimizer state in model space: for every parameter piece this rank owns,
@@ -138,22 +155,32 @@ def optimizer_sharded_state_dict(optimizer, model: Sequence[torch.nn.Module],
             for piece in st.pieces:
                 p = piece["param"]
                 ci, n = name_of[p]
-                desc = model_sd[ci].get(n)
-                if desc is None:          # strided (gated) weights: describe in the parameter's own flat space
-                    desc = ds.ShardedTensor.from_rank_offsets(
-                        f"chunk{ci}.{n}.tp{c['tp_rank']}of{c['tp_size']}.pp{c['pp_rank']}", p.detach(),
-                        replica_id=(0, 0, c["dp_rank"]))
                 lo = piece["param_start"]
                 hi = lo + piece["numel"]
-                whole = (lo == 0 and hi == p.numel())
-                for kind, flat in (("fp32_param", st.master), ("exp_avg", st.exp_avg), ("exp_avg_sq", st.exp_avg_sq)):
-                    data = flat[piece["local_start"]:piece["local_start"] + piece["numel"]]
-                    replica = desc.replica_id if not sharded_over_dp else (desc.replica_id[0], desc.replica_id[1], 0)
-                    stn = ds.ShardedTensor(f"optimizer.state.{kind}.{desc.key}", data if not whole else data.view(p.shape),
-                                           torch.float32, desc.local_shape, desc.global_shape, desc.global_offset,
-                                           desc.axis_fragmentations, replica, desc.prepend_axis_num, False,
-                                           None if whole else slice(lo, hi))
-                    out["param_state"][f"{oi}.{kind}.{ci}.{n}.{lo}"] = stn
+                desc = model_sd[ci].get(n)
+                if desc is not None:
+                    spans = [(desc, 0, p.numel())]
+                else:
+                    spans = _part_spans(model_sd[ci], n, p)
+                if spans is None:         # pieces along an inner dimension: describe in the parameter's own flat space
+                    spans = [(ds.ShardedTensor.from_rank_offsets(
+                        f"chunk{ci}.{n}.tp{c['tp_rank']}of{c['tp_size']}.pp{c['pp_rank']}", p.detach(),
+                        replica_id=(0, 0, c["dp_rank"])), 0, p.numel())]
+                for desc, a, b in spans:
+                    s_lo, s_hi = max(lo, a), min(hi, b)
+                    if s_lo >= s_hi:
+                        continue
+                    whole = (s_lo == a and s_hi == b)
+                    at = piece["local_start"] + (s_lo - lo)
+                    for kind, flat in (("fp32_param", st.master), ("exp_avg", st.exp_avg), ("exp_avg_sq", st.exp_avg_sq)):
+                        data = flat[at:at + (s_hi - s_lo)]
+                        replica = desc.replica_id if not sharded_over_dp else (desc.replica_id[0], desc.replica_id[1], 0)
+                        stn = ds.ShardedTensor(f"optimizer.state.{kind}.{desc.key}",
+                                               data if not whole else data.view(desc.local_shape),
+                                               torch.float32, desc.local_shape, desc.global_shape, desc.global_offset,
+                                               desc.axis_fragmentations, replica, desc.prepend_axis_num, False,
+                                               None if whole else slice(s_lo - a, s_hi - a))
+                        out["param_state"][f"{oi}.{kind}.{ci}.{n}.{s_lo}"] = stn
     return out
 
 

@@ -117,6 +117,11 @@ def _load_rank(rank, world, tp, pp, d, check_optim):
         for st in opt.states:
             st.reload_master_from_params()
             assert torch.allclose(st.exp_avg, 2 * st.master) and torch.allclose(st.exp_avg_sq, 3 * st.master)
+            # every element was restored, the halves of the gated FC1 included (a rank's share may be small, but the
+            # name-seeded weights are nowhere exactly zero)
+            for piece in st.pieces:
+                part = st.exp_avg[piece["local_start"]:piece["local_start"] + piece["numel"]]
+                assert bool((part != 0).all()), [n for n, q in model[0].module.named_parameters() if q is piece["param"]]
 
 
 @pytest.mark.parametrize("save_cfg,load_cfg,optim", [((2, 2, 1), (1, 1, 1), False), ((2, 1, 2), (2, 2, 1), False),
