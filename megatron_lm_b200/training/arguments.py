@@ -290,11 +290,7 @@ UNUSED_FLAGS = {
     # Retro / biencoder / vision programs that are not (fully) built
     "retro_add_retriever": (_W, "pretrain_retro.py always builds the retriever"),
     "retro_cyclic_train_iters": (_R, "cyclic Retro training is not built"),
-    "sample_rate": (_W, "the retriever evaluation tasks are not built"),
-    "evidence_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
-    "block_data_path": (_R, "the retriever evaluation / indexing tasks are not built"),
-    "embedding_path": (_R, "the inverse-cloze program builds no block-embedding index"), "indexer_batch_size": (_W, "the inverse-cloze program builds no block-embedding index"),
-    "indexer_log_interval": (_W, "the inverse-cloze program builds no block-embedding index"),
+    "block_data_path": (_R, "block-data files of the REALM index are not read: the evidence index is built from --evidence-data-path into --embedding-path"),
     "data_sharding": (_W, "the sampler always gives each data-parallel rank its own part"),
     "vision_pretraining_type": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice"),
     "vision_pretraining": (_W, "the program that is launched (pretrain_vision_classify / _dino / _inpaint) is the choice; the flag selects nothing"),
