@@ -2,6 +2,8 @@
 # Vision transformer pre-training on 8 GPUs (data parallel): supervised classification, DINO self-distillation or
 # in-painting.  Data: <root>/train/<class>/*.npy|png|jpg and <root>/val/..., or --mock-data.
 # Usage: bash examples/vision/pretrain_vit.sh <classify|dino|inpaint> <image root|--mock-data> [extra flags]
+# Other backbones: append `--vision-backbone-type mit` (classify, dino; inpaint with `--patch-dim 4`) or
+# `--vision-backbone-type swin --swin-backbone-type tiny|base|h3` (dino).
 set -euo pipefail
 TASK=${1:?classify, dino or inpaint}; DATA=${2:---mock-data}; shift 2 || true
 [ "$DATA" = "--mock-data" ] && DATA_ARGS="--mock-data" || DATA_ARGS="--data-path $DATA"
