@@ -141,7 +141,8 @@ def test_dino_towers_on_hierarchical_backbones(monkeypatch):
 
 @pytest.mark.gpu
 def test_mit_and_swin_on_gpu_match_cpu_reference():
-    """bf16 on the GPU (fused layer norm, flash attention in MiT) against the fp32 CPU model with the same weights."""
+    """The same weights on the GPU and on the host: fp32 agrees closely (forward and input gradient), bf16 stays
+    within the precision of the format."""
     torch.manual_seed(6)
     x = torch.randn(2, 3, 64, 64)
     for build in (lambda **kw: MixVisionTransformer(widths=(64, 128, 128, 128), heads=(1, 2, 2, 2), depths=(1, 1, 1, 1),
@@ -149,13 +150,18 @@ def test_mit_and_swin_on_gpu_match_cpu_reference():
                   lambda **kw: SwinTransformer(width=32, depths=(2, 1, 1, 1), heads=(2, 2, 4, 4), window=4,
                                                drop_path_rate=0.0, **kw)):
         ref = build()
-        dev = build(device="cuda", dtype=torch.bfloat16)
-        dev.load_state_dict(ref.state_dict())
         xr = x.clone().requires_grad_(True)
-        xd = x.cuda().requires_grad_(True)
-        out_r, out_d = ref(xr), dev(xd)
-        torch.testing.assert_close(out_d.float().cpu(), out_r, atol=0.06, rtol=0.06)
+        out_r = ref(xr)
         out_r.sum().backward()
-        out_d.float().sum().backward()
-        gr, gd = xr.grad, xd.grad.float().cpu()
-        assert torch.nn.functional.cosine_similarity(gr.flatten(), gd.flatten(), dim=0) > 0.98
+        dev = build(device="cuda", dtype=torch.float32)
+        dev.load_state_dict(ref.state_dict())
+        xd = x.cuda().requires_grad_(True)
+        out_d = dev(xd)
+        out_d.sum().backward()
+        torch.testing.assert_close(out_d.cpu(), out_r, atol=2e-2, rtol=2e-2)       # convolutions may run in TF32
+        assert torch.nn.functional.cosine_similarity(xr.grad.flatten(), xd.grad.cpu().flatten(), dim=0) > 0.99
+        half = build(device="cuda", dtype=torch.bfloat16)
+        half.load_state_dict(ref.state_dict())
+        out_h = half(x.cuda()).float().cpu()
+        assert torch.isfinite(out_h).all()
+        assert (out_h - out_r).norm() / out_r.norm() < 0.2
