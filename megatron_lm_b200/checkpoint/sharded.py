@@ -385,12 +385,15 @@ def check_is_distributed_checkpoint(checkpoint_dir: str) -> bool:
 # ----------------------------------------------------------------------------- model -> sharded state dict
 def model_sharded_state_dict(model: torch.nn.Module, prefix: str = "", *, tp_rank: int = 0, tp_size: int = 1,
                              dp_rank: int = 0, pp_layer_offset: int = 0, num_layers_global: Optional[int] = None,
-                             etp_rank: Optional[int] = None, ep_rank: int = 0, ep_size: int = 1) -> Dict[str, ShardedTensor]:
+                             etp_rank: Optional[int] = None, ep_rank: int = 0, ep_size: int = 1,
+                             stack_layers: bool = True) -> Dict[str, ShardedTensor]:
     """Describe every parameter of a model chunk.  Transformer-layer parameters lose their local
     layer index from the key and gain a leading global layer axis (reference:
     transformer_block.py:622-698); TP-sharded parameters are placed along their partition dim;
     a strided partition (gated FC1: [gate; up] per rank) is described as ``stride`` separate
-    tensors so that the TP size can change on load (reference: mlp.py:219), and so is a parameter whose rows are
+    tensors so that the TP size can change on load (reference: mlp.py:219).  ``stack_layers=False`` is for stacks
+    whose layers differ (hybrid Mamba / attention / MLP patterns, dense and expert layers interleaved): a parameter
+    that only some layers have cannot fill a layer axis, so each layer keeps its own key with its global index.  So is a parameter whose rows are
     a concatenation of unequal segments (``partition_sizes`` / ``partition_names``: the [z | x | B | C | dt] rows of a
     Mamba mixer's input projection, reference: ssm/mamba_mixer.py ``sharded_state_dict``)."""
     import re
@@ -402,7 +405,9 @@ def model_sharded_state_dict(model: torch.nn.Module, prefix: str = "", *, tp_ran
         offsets = []
         prepend = 0
         m = re.search(r"(^|\.)layers\.(\d+)\.", name)
-        if m and num_layers_global is not None:
+        if m and num_layers_global is not None and not stack_layers:
+            key = prefix + name[:m.start(2)] + str(pp_layer_offset + int(m.group(2))) + name[m.end(2):]
+        elif m and num_layers_global is not None:
             local_idx = int(m.group(2))
             key = prefix + name[:m.start(2) - 1 - len("layers")] + "layers." + name[m.end():]
             key = key.replace("..", ".")

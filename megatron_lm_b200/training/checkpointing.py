@@ -100,6 +100,19 @@ def _coords():
                 pp_size=state.get_pipeline_model_parallel_world_size() if init else 1)
 
 
+def _uniform_layer_stack(m) -> bool:
+    """Whether every layer of the model has the same parameters (decided from the configuration, so that all
+    pipeline stages agree): only then can a parameter be stored as one tensor with a layer axis."""
+    cfg = m.config
+    if type(m).__name__ == "MambaModel" or getattr(cfg, "heterogeneous_layers_config_encoded_json", None):
+        return False
+    freq = getattr(cfg, "moe_layer_freq", 1)
+    if getattr(cfg, "num_moe_experts", None) and freq not in (None, 1):
+        if isinstance(freq, int) or len(set(freq)) > 1:
+            return False
+    return True
+
+
 def model_sharded_state_dicts(model: Sequence[torch.nn.Module]) -> List[Dict[str, ds.ShardedTensor]]:
     c = _coords()
     out = []
@@ -107,7 +120,8 @@ def model_sharded_state_dicts(model: Sequence[torch.nn.Module]) -> List[Dict[str
         m = _unwrap(chunk)
         off = getattr(getattr(m, "decoder", None), "layer_offset", 0)
         out.append(ds.model_sharded_state_dict(m, tp_rank=c["tp_rank"], tp_size=c["tp_size"], dp_rank=c["dp_rank"],
-                                               pp_layer_offset=off, num_layers_global=m.config.num_layers))
+                                               pp_layer_offset=off, num_layers_global=m.config.num_layers,
+                                               stack_layers=_uniform_layer_stack(m)))
     return out
 
 

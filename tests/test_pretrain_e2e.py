@@ -505,3 +505,30 @@ def test_hybrid_mamba_program_with_context_parallelism():
                          "--mamba-head-dim", "16", "--mamba-num-groups", "2", "--mamba-state-dim", "16",
                          "--hybrid-override-pattern", "M*-", "--position-embedding-type", "rope"],
               script="pretrain_mamba.py")
+
+
+def test_hybrid_mamba_checkpoint_resumes_under_another_tensor_parallel_size(tmp_path):
+    """Saved by two tensor-parallel ranks (distributed optimizer), loaded by one: the mixers' projection and
+    convolution segments are re-cut, the test loss of the loaded model is the saved model's."""
+    ck = str(tmp_path / "ck")
+    model = ["--global-batch-size", "2", "--num-layers", "3", "--mamba-head-dim", "16", "--mamba-num-groups", "2",
+             "--mamba-state-dim", "16", "--hybrid-override-pattern", "M*-", "--position-embedding-type", "rope"]
+    first = _torchrun(2, 29664, model + ["--tensor-model-parallel-size", "2", "--use-distributed-optimizer", "--save", ck,
+                                         "--save-interval", "3"], script="pretrain_mamba.py")
+
+    def test_loss(out):
+        return float(re.search(r"test loss \| lm loss value: ([0-9.E+-]+)", out).group(1))
+
+    def resume(train_iters):
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES="", MASTER_ADDR="127.0.0.1", MASTER_PORT="29665")
+        cmd = [sys.executable, os.path.join(ROOT, "pretrain_mamba.py"), "--distributed-backend", "gloo", "--hidden-size", "32",
+               "--num-attention-heads", "4", "--seq-length", "32", "--max-position-embeddings", "32", "--micro-batch-size", "1",
+               "--train-iters", str(train_iters), "--lr", "1e-3", "--mock-data", "--tokenizer-type", "NullTokenizer",
+               "--vocab-size", "64", "--log-interval", "1", "--eval-interval", "2", "--eval-iters", "1",
+               "--use-cpu-initialization", "--attention-dropout", "0", "--hidden-dropout", "0", "--load", ck,
+               "--make-vocab-size-divisible-by", "256"] + model      # the padded vocabulary of the two-rank run
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=280, cwd=ROOT, env=env)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        return r.stdout
+    same = resume(3)                                           # nothing left to train: evaluates the loaded weights
+    assert not _iters(same) and abs(test_loss(same) - test_loss(first)) < 2e-4, (test_loss(same), test_loss(first))
